@@ -1,0 +1,90 @@
+// Host-side state of one backend context: model geometry, device weights, activation
+// buffers, KV slots and the captured decode graphs.  Everything is owned per context (the
+// reference shares name-keyed buffers process-wide, src/utils/device/memory.h:89-109, which
+// makes two engines in one process unsafe; here two contexts never alias).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <map>
+#include <string>
+#include <vector>
+
+#include "../../../../include/efm_b200.h"
+#include "../../operators/common.cuh"
+
+namespace efm {
+
+struct LayerWeights {
+    __nv_bfloat16* in_norm = nullptr;     // [H]
+    __nv_bfloat16* post_norm = nullptr;   // [H]
+    __nv_bfloat16* qkv = nullptr;         // [(q+2kv)*D, H] rows: q | k | v
+    __nv_bfloat16* qkv_bias = nullptr;    // [(q+2kv)*D]
+    __nv_bfloat16* o = nullptr;           // [H, q*D]
+    __nv_bfloat16* gate_up = nullptr;     // [2I, H] blocks of 64 gate rows then 64 up rows
+    __nv_bfloat16* down = nullptr;        // [H, I]
+    uint32_t seen = 0;                    // bit per HF tensor received
+};
+
+struct KvSlot {
+    int max_tokens = 0;
+    std::vector<__nv_bfloat16*> k;        // per layer; V block follows K block in the same allocation
+    std::vector<__nv_bfloat16*> v;
+    cudaGraphExec_t graph = nullptr;      // decode step captured against this slot's pointers
+    int graph_nodes = 0;
+    int n_splits = 1, chunk_cap = 1;
+};
+
+}  // namespace efm
+
+struct efm_b200_ctx {
+    efm_model_desc d{};
+    int device = 0, tp_rank = 0, tp_size = 1, num_sms = 148;
+    cudaStream_t stream = nullptr;
+    std::string error;
+    bool finalized = false;
+    bool pdl = true;
+
+    // weights
+    __nv_bfloat16* embed = nullptr;       // [V, H]
+    __nv_bfloat16* lm_head = nullptr;     // [V, H] (aliases embed when tied)
+    __nv_bfloat16* final_norm = nullptr;
+    bool seen_embed = false, seen_lm_head = false, seen_final_norm = false;
+    std::vector<efm::LayerWeights> layers;
+    float* inv_freq = nullptr;            // [D/2]
+
+    // activations (prefill rows x width) and decode vectors
+    int max_s = 0;
+    int32_t* ids = nullptr;               // [max_s]
+    int32_t* pos3 = nullptr;              // [3 * max_s]
+    __nv_bfloat16* resid = nullptr;       // [max_s, H]
+    __nv_bfloat16* norm = nullptr;        // [max_s, H]
+    __nv_bfloat16* qkv = nullptr;         // [max_s, (q+2kv)*D]
+    __nv_bfloat16* qbuf = nullptr;        // [max_s, q*D]
+    __nv_bfloat16* attn = nullptr;        // [max_s, q*D]
+    float* gu = nullptr;                  // [max_s, 2I] fp32
+    __nv_bfloat16* act = nullptr;         // [max_s, I]
+    __nv_bfloat16* custom_embeds = nullptr;
+    size_t custom_embeds_cap = 0;
+    __nv_bfloat16* resid_d = nullptr;     // decode residual stream [H]
+    __nv_bfloat16* q_d = nullptr;         // [q*D]
+    __nv_bfloat16* attn_d = nullptr;      // [q*D]
+    __nv_bfloat16* act_d = nullptr;       // [I]
+    float* logits = nullptr;              // [V]
+    float* part_val = nullptr;            // [max gemv grid]
+    int* part_idx = nullptr;
+    uint32_t* wbuf = nullptr;             // [V] sampler scratch
+    float* attn_part_o = nullptr;         // decode attention scratch
+    float* attn_part_ml = nullptr;
+    unsigned int* attn_counters = nullptr;
+    efm::DecodeState* state = nullptr;
+    int32_t* tokens_out = nullptr;        // [max_response_tokens]
+
+    efm_sampling sampling{0.f, 1.f, 1, 0, 0};
+    std::map<int, efm::KvSlot> slots;
+    int bound_slot = -1;
+    int64_t launches = 0;
+    cudaEvent_t events[16] = {};
+    std::vector<void*> allocations;
+};

@@ -1,0 +1,636 @@
+// Implementation of the C ABI declared in include/efm_b200.h: context lifetime, weight
+// ingestion (fusing q|k|v and interleaving gate/up as the kernels expect), KV slots, the
+// prefill and decode entry points with CUDA-graph capture of the decode step, and the
+// single-operator entry points used by the parity tests.
+#include <cstdio>
+#include <cstring>
+#include <cmath>
+#include <new>
+#include <string>
+
+#include "../../layers/launch.cuh"
+#include "../../layers/qwen_text.h"
+#include "../../operators/gemm_mma.cuh"
+#define EFM_DECLARATIONS_ONLY
+#include "../../operators/sample.cuh"
+#undef EFM_DECLARATIONS_ONLY
+#include "ctx.h"
+
+using namespace efm;
+
+namespace {
+
+thread_local std::string g_create_error;
+
+efm_status fail(efm_b200_ctx* c, efm_status st, const std::string& msg) {
+    if (c != nullptr) c->error = msg; else g_create_error = msg;
+    return st;
+}
+efm_status cuda_fail(efm_b200_ctx* c, cudaError_t e, const char* what) {
+    const efm_status st = e == cudaErrorMemoryAllocation ? EFM_ERR_OUT_OF_MEMORY : EFM_ERR_CUDA;
+    return fail(c, st, std::string(what) + ": " + cudaGetErrorString(e));
+}
+#define EFM_CK(ctx, call)                                              \
+    do {                                                               \
+        cudaError_t e_ = (call);                                       \
+        if (e_ != cudaSuccess) return cuda_fail(ctx, e_, #call);       \
+    } while (0)
+
+template <typename T>
+cudaError_t dev_alloc(efm_b200_ctx* c, T** p, size_t count, bool zero = true) {
+    void* raw = nullptr;
+    const size_t bytes = std::max<size_t>(count * sizeof(T), 16);
+    cudaError_t e = cudaMalloc(&raw, bytes);
+    if (e != cudaSuccess) return e;
+    c->allocations.push_back(raw);
+    if (zero) e = cudaMemsetAsync(raw, 0, bytes, c->stream);
+    *p = static_cast<T*>(raw);
+    return e;
+}
+
+// a usable sm_100 device, or an error: there is no CPU path behind this library
+efm_status require_b200(efm_b200_ctx* c, int device_id) {
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess || n == 0)
+        return fail(c, EFM_ERR_CUDA, std::string("no CUDA device available: ") + cudaGetErrorString(e));
+    if (device_id < 0 || device_id >= n) return fail(c, EFM_ERR_INVALID_ARGUMENT, "device_id out of range");
+    int major = 0;
+    EFM_CK(c, cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device_id));
+    if (major != 10) return fail(c, EFM_ERR_CUDA, "device is not sm_100 (this library carries sm_100a code only)");
+    EFM_CK(c, cudaSetDevice(device_id));
+    return EFM_OK;
+}
+
+Launcher make_launcher(efm_b200_ctx* c) {
+    Launcher L;
+    L.stream = c->stream;
+    L.pdl = c->pdl;
+    L.counter = &c->launches;
+    return L;
+}
+
+enum : uint32_t { kQw = 1, kQb = 2, kKw = 4, kKb = 8, kVw = 16, kVb = 32, kO = 64, kGate = 128, kUp = 256,
+                  kDown = 512, kInNorm = 1024, kPostNorm = 2048 };
+constexpr uint32_t kRequired = kQw | kKw | kVw | kO | kGate | kUp | kDown | kInNorm | kPostNorm;
+
+efm_status copy_rows(efm_b200_ctx* c, void* dst, const void* src, size_t bytes, int mem_kind) {
+    EFM_CK(c, cudaMemcpyAsync(dst, src, bytes, mem_kind == EFM_MEM_DEVICE ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, c->stream));
+    return EFM_OK;
+}
+
+bool shape_is(const int64_t* shape, int ndim, int64_t a, int64_t b = -1) {
+    if (b < 0) return ndim == 1 && shape[0] == a;
+    return ndim == 2 && shape[0] == a && shape[1] == b;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* efm_b200_version(void) { return "efm_b200 0.1 (sm_100a)"; }
+
+const char* efm_b200_last_error(const efm_b200_ctx* ctx) {
+    return ctx != nullptr ? ctx->error.c_str() : g_create_error.c_str();
+}
+
+efm_status efm_b200_create(const efm_model_desc* desc, int32_t device_id, int32_t tp_rank, int32_t tp_size,
+                           efm_b200_ctx** out) {
+    if (desc == nullptr || out == nullptr) return fail(nullptr, EFM_ERR_INVALID_ARGUMENT, "null argument");
+    *out = nullptr;
+    if (desc->struct_size != (int32_t)sizeof(efm_model_desc))
+        return fail(nullptr, EFM_ERR_INVALID_ARGUMENT, "efm_model_desc.struct_size mismatch");
+    const efm_model_desc& d = *desc;
+    if (d.num_layers <= 0 || d.hidden <= 0 || d.q_heads <= 0 || d.kv_heads <= 0 || d.vocab <= 0 || d.intermediate <= 0)
+        return fail(nullptr, EFM_ERR_INVALID_ARGUMENT, "non-positive model dimension");
+    if (d.head_dim != 64 && d.head_dim != 128) return fail(nullptr, EFM_ERR_UNSUPPORTED, "head_dim must be 64 or 128");
+    if (d.q_heads % d.kv_heads != 0 || d.q_heads / d.kv_heads > kMaxGroup)
+        return fail(nullptr, EFM_ERR_UNSUPPORTED, "q_heads / kv_heads must be an integer <= 8");
+    if (d.hidden % 32 != 0 || d.intermediate % 64 != 0 || d.vocab % 2 != 0)
+        return fail(nullptr, EFM_ERR_UNSUPPORTED, "hidden % 32, intermediate % 64 and vocab % 2 must be 0");
+    if (d.use_mrope && d.mrope_section[0] + d.mrope_section[1] + d.mrope_section[2] != d.head_dim / 2)
+        return fail(nullptr, EFM_ERR_INVALID_ARGUMENT, "mrope_section must sum to head_dim / 2");
+    if (tp_size != 1 || tp_rank != 0) return fail(nullptr, EFM_ERR_UNSUPPORTED, "tensor parallel size > 1 is not built yet");
+    if (d.max_prefill_tokens <= 0 || d.max_response_tokens <= 0)
+        return fail(nullptr, EFM_ERR_INVALID_ARGUMENT, "max_prefill_tokens and max_response_tokens must be positive");
+    efm_status st = require_b200(nullptr, device_id);
+    if (st != EFM_OK) return st;
+
+    efm_b200_ctx* c = new (std::nothrow) efm_b200_ctx();
+    if (c == nullptr) return fail(nullptr, EFM_ERR_OUT_OF_MEMORY, "host allocation failed");
+    c->d = d;
+    c->device = device_id;
+    c->tp_rank = tp_rank;
+    c->tp_size = tp_size;
+    c->pdl = std::getenv("EFM_B200_NO_PDL") == nullptr;
+    auto bail = [&](cudaError_t e, const char* what) {
+        efm_status s = cuda_fail(nullptr, e, what);
+        efm_b200_destroy(c);
+        return s;
+    };
+#define EFM_TRY(call) do { cudaError_t e_ = (call); if (e_ != cudaSuccess) return bail(e_, #call); } while (0)
+    EFM_TRY(cudaDeviceGetAttribute(&c->num_sms, cudaDevAttrMultiProcessorCount, device_id));
+    EFM_TRY(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
+    for (auto& ev : c->events) EFM_TRY(cudaEventCreate(&ev));
+
+    const size_t H = d.hidden, D = d.head_dim, QD = (size_t)d.q_heads * D, KVD = (size_t)d.kv_heads * D, I = d.intermediate,
+                 V = d.vocab, S = d.max_prefill_tokens;
+    EFM_TRY(dev_alloc(c, &c->embed, V * H, false));
+    if (d.tied_lm_head) c->lm_head = c->embed; else EFM_TRY(dev_alloc(c, &c->lm_head, V * H, false));
+    EFM_TRY(dev_alloc(c, &c->final_norm, H));
+    c->layers.resize(d.num_layers);
+    for (auto& w : c->layers) {
+        EFM_TRY(dev_alloc(c, &w.in_norm, H));
+        EFM_TRY(dev_alloc(c, &w.post_norm, H));
+        EFM_TRY(dev_alloc(c, &w.qkv, (QD + 2 * KVD) * H, false));
+        EFM_TRY(dev_alloc(c, &w.qkv_bias, QD + 2 * KVD));
+        EFM_TRY(dev_alloc(c, &w.o, H * QD, false));
+        EFM_TRY(dev_alloc(c, &w.gate_up, 2 * I * H, false));
+        EFM_TRY(dev_alloc(c, &w.down, H * I, false));
+    }
+    {
+        std::vector<float> f(D / 2);
+        for (size_t i = 0; i < D / 2; ++i) f[i] = (float)std::pow((double)d.rope_theta, -2.0 * (double)i / (double)D);
+        EFM_TRY(dev_alloc(c, &c->inv_freq, D / 2));
+        EFM_TRY(cudaMemcpyAsync(c->inv_freq, f.data(), f.size() * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+        EFM_TRY(cudaStreamSynchronize(c->stream));
+    }
+    c->max_s = (int)S;
+    EFM_TRY(dev_alloc(c, &c->ids, S));
+    EFM_TRY(dev_alloc(c, &c->pos3, 3 * S));
+    EFM_TRY(dev_alloc(c, &c->resid, S * H));
+    EFM_TRY(dev_alloc(c, &c->norm, S * H));
+    EFM_TRY(dev_alloc(c, &c->qkv, S * (QD + 2 * KVD)));
+    EFM_TRY(dev_alloc(c, &c->qbuf, S * QD));
+    EFM_TRY(dev_alloc(c, &c->attn, S * QD));
+    EFM_TRY(dev_alloc(c, &c->gu, S * 2 * I));
+    EFM_TRY(dev_alloc(c, &c->act, S * I));
+    EFM_TRY(dev_alloc(c, &c->resid_d, H));
+    EFM_TRY(dev_alloc(c, &c->q_d, QD));
+    EFM_TRY(dev_alloc(c, &c->attn_d, QD));
+    EFM_TRY(dev_alloc(c, &c->act_d, I));
+    EFM_TRY(dev_alloc(c, &c->logits, V));
+    EFM_TRY(dev_alloc(c, &c->part_val, 2 * (size_t)c->num_sms + 8));
+    EFM_TRY(dev_alloc(c, &c->part_idx, 2 * (size_t)c->num_sms + 8));
+    EFM_TRY(dev_alloc(c, &c->wbuf, V));
+    EFM_TRY(dev_alloc(c, &c->attn_part_o, (size_t)d.q_heads * 64 * D));
+    EFM_TRY(dev_alloc(c, &c->attn_part_ml, (size_t)d.q_heads * 64 * 2));
+    EFM_TRY(dev_alloc(c, &c->attn_counters, (size_t)d.kv_heads));
+    EFM_TRY(dev_alloc(c, &c->state, 1));
+    EFM_TRY(dev_alloc(c, &c->tokens_out, (size_t)d.max_response_tokens));
+    EFM_TRY(cudaStreamSynchronize(c->stream));
+#undef EFM_TRY
+    *out = c;
+    return EFM_OK;
+}
+
+efm_status efm_b200_destroy(efm_b200_ctx* c) {
+    if (c == nullptr) return EFM_OK;
+    cudaSetDevice(c->device);
+    if (c->stream != nullptr) cudaStreamSynchronize(c->stream);
+    for (auto& kv : c->slots)
+        if (kv.second.graph != nullptr) cudaGraphExecDestroy(kv.second.graph);
+    for (void* p : c->allocations) cudaFree(p);
+    for (auto& ev : c->events)
+        if (ev != nullptr) cudaEventDestroy(ev);
+    if (c->stream != nullptr) cudaStreamDestroy(c->stream);
+    delete c;
+    return EFM_OK;
+}
+
+efm_status efm_b200_set_weight(efm_b200_ctx* c, const char* hf_name, const void* data, const int64_t* shape,
+                               int32_t ndim, int32_t dtype, int32_t mem_kind) {
+    if (c == nullptr || hf_name == nullptr || data == nullptr || shape == nullptr)
+        return fail(c, EFM_ERR_INVALID_ARGUMENT, "null argument");
+    if (c->finalized) return fail(c, EFM_ERR_STATE, "weights are already finalized");
+    EFM_CK(c, cudaSetDevice(c->device));
+    const efm_model_desc& d = c->d;
+    const int64_t H = d.hidden, D = d.head_dim, QD = d.q_heads * D, KVD = d.kv_heads * D, I = d.intermediate, V = d.vocab;
+    const std::string name(hf_name);
+    auto bad_shape = [&]() { return fail(c, EFM_ERR_INVALID_ARGUMENT, "unexpected shape for " + name); };
+    auto known = [&]() -> efm_status {
+        if (dtype != EFM_BF16) return fail(c, EFM_ERR_UNSUPPORTED, "weights must be bf16: " + name);
+        return EFM_OK;
+    };
+    efm_status st = EFM_OK;
+    if (name == "model.embed_tokens.weight") {
+        if ((st = known()) != EFM_OK) return st;
+        if (!shape_is(shape, ndim, V, H)) return bad_shape();
+        st = copy_rows(c, c->embed, data, (size_t)V * H * 2, mem_kind);
+        c->seen_embed = true;
+    } else if (name == "lm_head.weight") {
+        if ((st = known()) != EFM_OK) return st;
+        if (!shape_is(shape, ndim, V, H)) return bad_shape();
+        if (!d.tied_lm_head) st = copy_rows(c, c->lm_head, data, (size_t)V * H * 2, mem_kind);
+        c->seen_lm_head = true;
+    } else if (name == "model.norm.weight") {
+        if ((st = known()) != EFM_OK) return st;
+        if (!shape_is(shape, ndim, H)) return bad_shape();
+        st = copy_rows(c, c->final_norm, data, (size_t)H * 2, mem_kind);
+        c->seen_final_norm = true;
+    } else if (name.rfind("model.layers.", 0) == 0) {
+        const size_t dot = name.find('.', 13);
+        if (dot == std::string::npos) return EFM_OK;
+        const int l = std::atoi(name.substr(13, dot - 13).c_str());
+        if (l < 0 || l >= d.num_layers) return EFM_OK;      // e.g. extra layers of a draft model: ignored
+        const std::string rest = name.substr(dot + 1);
+        LayerWeights& w = c->layers[l];
+        struct Spec { const char* n; uint32_t bit; };
+        if ((st = known()) != EFM_OK) return st;
+        const size_t rowb = (size_t)H * 2;
+        if (rest == "input_layernorm.weight") {
+            if (!shape_is(shape, ndim, H)) return bad_shape();
+            st = copy_rows(c, w.in_norm, data, rowb, mem_kind); w.seen |= kInNorm;
+        } else if (rest == "post_attention_layernorm.weight") {
+            if (!shape_is(shape, ndim, H)) return bad_shape();
+            st = copy_rows(c, w.post_norm, data, rowb, mem_kind); w.seen |= kPostNorm;
+        } else if (rest == "self_attn.q_proj.weight") {
+            if (!shape_is(shape, ndim, QD, H)) return bad_shape();
+            st = copy_rows(c, w.qkv, data, (size_t)QD * rowb, mem_kind); w.seen |= kQw;
+        } else if (rest == "self_attn.k_proj.weight") {
+            if (!shape_is(shape, ndim, KVD, H)) return bad_shape();
+            st = copy_rows(c, w.qkv + QD * H, data, (size_t)KVD * rowb, mem_kind); w.seen |= kKw;
+        } else if (rest == "self_attn.v_proj.weight") {
+            if (!shape_is(shape, ndim, KVD, H)) return bad_shape();
+            st = copy_rows(c, w.qkv + (QD + KVD) * H, data, (size_t)KVD * rowb, mem_kind); w.seen |= kVw;
+        } else if (rest == "self_attn.q_proj.bias") {
+            if (!shape_is(shape, ndim, QD)) return bad_shape();
+            st = copy_rows(c, w.qkv_bias, data, (size_t)QD * 2, mem_kind); w.seen |= kQb;
+        } else if (rest == "self_attn.k_proj.bias") {
+            if (!shape_is(shape, ndim, KVD)) return bad_shape();
+            st = copy_rows(c, w.qkv_bias + QD, data, (size_t)KVD * 2, mem_kind); w.seen |= kKb;
+        } else if (rest == "self_attn.v_proj.bias") {
+            if (!shape_is(shape, ndim, KVD)) return bad_shape();
+            st = copy_rows(c, w.qkv_bias + QD + KVD, data, (size_t)KVD * 2, mem_kind); w.seen |= kVb;
+        } else if (rest == "self_attn.o_proj.weight") {
+            if (!shape_is(shape, ndim, H, QD)) return bad_shape();
+            st = copy_rows(c, w.o, data, (size_t)H * QD * 2, mem_kind); w.seen |= kO;
+        } else if (rest == "mlp.gate_proj.weight" || rest == "mlp.up_proj.weight") {
+            if (!shape_is(shape, ndim, I, H)) return bad_shape();
+            const bool up = rest[4] == 'u';
+            // 64-row blocks: gate block b -> fused rows [128b, 128b+64), up block b -> [128b+64, 128b+128)
+            EFM_CK(c, cudaMemcpy2DAsync(w.gate_up + (up ? 64 * H : 0), 128 * rowb, data, 64 * rowb, 64 * rowb, (size_t)(I / 64),
+                                        mem_kind == EFM_MEM_DEVICE ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, c->stream));
+            w.seen |= up ? kUp : kGate;
+        } else if (rest == "mlp.down_proj.weight") {
+            if (!shape_is(shape, ndim, H, I)) return bad_shape();
+            st = copy_rows(c, w.down, data, (size_t)H * I * 2, mem_kind); w.seen |= kDown;
+        } else {
+            return EFM_OK;
+        }
+    } else {
+        return EFM_OK;   // visual tower etc.: not part of this path
+    }
+    if (st != EFM_OK) return st;
+    EFM_CK(c, cudaStreamSynchronize(c->stream));   // the caller may release `data` on return
+    return EFM_OK;
+}
+
+efm_status efm_b200_finalize_weights(efm_b200_ctx* c) {
+    if (c == nullptr) return fail(c, EFM_ERR_INVALID_ARGUMENT, "null context");
+    if (!c->seen_embed) return fail(c, EFM_ERR_STATE, "missing model.embed_tokens.weight");
+    if (!c->seen_final_norm) return fail(c, EFM_ERR_STATE, "missing model.norm.weight");
+    if (!c->d.tied_lm_head && !c->seen_lm_head) return fail(c, EFM_ERR_STATE, "missing lm_head.weight (untied model)");
+    for (int l = 0; l < c->d.num_layers; ++l)
+        if ((c->layers[l].seen & kRequired) != kRequired)
+            return fail(c, EFM_ERR_STATE, "missing weights in layer " + std::to_string(l));
+    EFM_CK(c, cudaStreamSynchronize(c->stream));
+    c->finalized = true;
+    return EFM_OK;
+}
+
+efm_status efm_b200_alloc_kv_slot(efm_b200_ctx* c, int32_t slot, int32_t max_tokens) {
+    if (c == nullptr) return fail(c, EFM_ERR_INVALID_ARGUMENT, "null context");
+    if (max_tokens <= 0) return fail(c, EFM_ERR_INVALID_ARGUMENT, "max_tokens must be positive");
+    if (c->slots.count(slot)) return fail(c, EFM_ERR_STATE, "slot already allocated");
+    EFM_CK(c, cudaSetDevice(c->device));
+    KvSlot s;
+    s.max_tokens = max_tokens;
+    const size_t block = (size_t)max_tokens * c->d.kv_heads * c->d.head_dim;
+    for (int l = 0; l < c->d.num_layers; ++l) {
+        __nv_bfloat16* base = nullptr;
+        EFM_CK(c, dev_alloc(c, &base, 2 * block));
+        s.k.push_back(base);
+        s.v.push_back(base + block);
+    }
+    const AttnPlan plan = plan_decode_attention(max_tokens, c->d.kv_heads, c->num_sms);
+    s.n_splits = plan.n_splits;
+    s.chunk_cap = plan.chunk_cap;
+    EFM_CK(c, cudaStreamSynchronize(c->stream));
+    c->slots[slot] = s;
+    return EFM_OK;
+}
+
+efm_status efm_b200_kv_layer_ptr(efm_b200_ctx* c, int32_t slot, int32_t layer, void** k_base, int32_t* max_tokens) {
+    if (c == nullptr || k_base == nullptr) return fail(c, EFM_ERR_INVALID_ARGUMENT, "null argument");
+    auto it = c->slots.find(slot);
+    if (it == c->slots.end() || layer < 0 || layer >= c->d.num_layers) return fail(c, EFM_ERR_INVALID_ARGUMENT, "no such slot/layer");
+    *k_base = it->second.k[layer];
+    if (max_tokens != nullptr) *max_tokens = it->second.max_tokens;
+    return EFM_OK;
+}
+
+efm_status efm_b200_set_sampling(efm_b200_ctx* c, const efm_sampling* s) {
+    if (c == nullptr || s == nullptr) return fail(c, EFM_ERR_INVALID_ARGUMENT, "null argument");
+    if (!(s->temperature >= 0.f)) return fail(c, EFM_ERR_INVALID_ARGUMENT, "temperature must be >= 0");
+    const bool changed = std::memcmp(&c->sampling, s, sizeof(*s)) != 0;
+    c->sampling = *s;
+    if (changed)     // sampling parameters are baked into the captured step
+        for (auto& kv : c->slots)
+            if (kv.second.graph != nullptr) { cudaGraphExecDestroy(kv.second.graph); kv.second.graph = nullptr; }
+    return EFM_OK;
+}
+
+efm_status efm_b200_prefill(efm_b200_ctx* c, int32_t slot, const int32_t* token_ids, int32_t n_tokens, int32_t kv_offset,
+                            const void* embeds, int32_t n_embeds, int32_t embed_token_id, int32_t embeds_mem,
+                            const int32_t* pos_ids3, int32_t sample) {
+    if (c == nullptr || token_ids == nullptr) return fail(c, EFM_ERR_INVALID_ARGUMENT, "null argument");
+    if (!c->finalized) return fail(c, EFM_ERR_STATE, "weights not finalized");
+    auto it = c->slots.find(slot);
+    if (it == c->slots.end()) return fail(c, EFM_ERR_INVALID_ARGUMENT, "unknown KV slot " + std::to_string(slot));
+    KvSlot& s = it->second;
+    if (n_tokens <= 0 || kv_offset < 0) return fail(c, EFM_ERR_INVALID_ARGUMENT, "n_tokens must be > 0 and kv_offset >= 0");
+    if ((int64_t)kv_offset + n_tokens > s.max_tokens)
+        return fail(c, EFM_ERR_INVALID_ARGUMENT, "prefill exceeds the slot's max_tokens");
+    if (c->d.use_mrope && pos_ids3 == nullptr) return fail(c, EFM_ERR_INVALID_ARGUMENT, "M-RoPE model needs position ids");
+    EFM_CK(c, cudaSetDevice(c->device));
+    const size_t H = c->d.hidden;
+    if (embeds != nullptr && n_embeds > 0) {
+        const size_t need = (size_t)n_embeds * H;
+        if (need > c->custom_embeds_cap) {
+            EFM_CK(c, dev_alloc(c, &c->custom_embeds, need, false));
+            c->custom_embeds_cap = need;
+        }
+        EFM_CK(c, cudaMemcpyAsync(c->custom_embeds, embeds, need * 2,
+                                  embeds_mem == EFM_MEM_DEVICE ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, c->stream));
+    } else {
+        n_embeds = 0;
+    }
+    if (sample) {
+        DecodeState st{};
+        st.token = -1;
+        st.kv_len = (uint32_t)(kv_offset + n_tokens);
+        EFM_CK(c, cudaMemcpyAsync(c->state, &st, sizeof(st), cudaMemcpyHostToDevice, c->stream));
+    }
+    Launcher L = make_launcher(c);
+    for (int off = 0; off < n_tokens; off += c->max_s) {
+        const int S = std::min(c->max_s, n_tokens - off);
+        EFM_CK(c, cudaMemcpyAsync(c->ids, token_ids + off, (size_t)S * 4, cudaMemcpyHostToDevice, c->stream));
+        if (pos_ids3 != nullptr)
+            for (int r = 0; r < 3; ++r)
+                EFM_CK(c, cudaMemcpyAsync(c->pos3 + (size_t)r * S, pos_ids3 + (size_t)r * n_tokens + off, (size_t)S * 4,
+                                          cudaMemcpyHostToDevice, c->stream));
+        const bool last = off + S >= n_tokens;
+        qwen_prefill_chunk(*c, s, S, kv_offset + off, n_embeds, embed_token_id, last && sample != 0, L);
+        if (L.err != cudaSuccess) return cuda_fail(c, L.err, "prefill launch");
+    }
+    return EFM_OK;
+}
+
+efm_status efm_b200_decode_begin(efm_b200_ctx* c, int32_t slot, int32_t kv_len, const int32_t mrope_pos[3], int32_t step) {
+    if (c == nullptr) return fail(c, EFM_ERR_INVALID_ARGUMENT, "null context");
+    auto it = c->slots.find(slot);
+    if (it == c->slots.end()) return fail(c, EFM_ERR_INVALID_ARGUMENT, "unknown KV slot " + std::to_string(slot));
+    if (kv_len < 0 || kv_len >= it->second.max_tokens) return fail(c, EFM_ERR_INVALID_ARGUMENT, "kv_len leaves no room in the slot");
+    if (step < 0) return fail(c, EFM_ERR_INVALID_ARGUMENT, "step must be >= 0");
+    EFM_CK(c, cudaSetDevice(c->device));
+    struct { uint32_t kv_len; int32_t pos[3]; int32_t step; int32_t error; } tail;
+    tail.kv_len = (uint32_t)kv_len + 1u;      // the step appends its own K/V before attending
+    for (int i = 0; i < 3; ++i) tail.pos[i] = mrope_pos != nullptr ? mrope_pos[i] : 0;
+    tail.step = step;
+    tail.error = 0;
+    static_assert(offsetof(DecodeState, kv_len) == 4 && sizeof(tail) == 24, "DecodeState layout");
+    EFM_CK(c, cudaMemcpyAsync(reinterpret_cast<char*>(c->state) + 4, &tail, sizeof(tail), cudaMemcpyHostToDevice, c->stream));
+    c->bound_slot = slot;
+    return EFM_OK;
+}
+
+efm_status efm_b200_set_token(efm_b200_ctx* c, int32_t token) {
+    if (c == nullptr) return fail(c, EFM_ERR_INVALID_ARGUMENT, "null context");
+    EFM_CK(c, cudaMemcpyAsync(&c->state->token, &token, 4, cudaMemcpyHostToDevice, c->stream));
+    return EFM_OK;
+}
+
+static efm_status ensure_graph(efm_b200_ctx* c, KvSlot& s) {
+    if (s.graph != nullptr) return EFM_OK;
+    Launcher L = make_launcher(c);
+    cudaGraph_t g = nullptr;
+    const int64_t before = c->launches;
+    EFM_CK(c, cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
+    qwen_decode_step(*c, s, L);
+    cudaError_t e = cudaStreamEndCapture(c->stream, &g);
+    s.graph_nodes = (int)(c->launches - before);
+    c->launches = before;                 // capture records, it does not run
+    if (L.err != cudaSuccess) { if (g) cudaGraphDestroy(g); return cuda_fail(c, L.err, "decode capture launch"); }
+    if (e != cudaSuccess) return cuda_fail(c, e, "cudaStreamEndCapture");
+    e = cudaGraphInstantiate(&s.graph, g, 0);
+    cudaGraphDestroy(g);
+    if (e != cudaSuccess) { s.graph = nullptr; return cuda_fail(c, e, "cudaGraphInstantiate"); }
+    return EFM_OK;
+}
+
+efm_status efm_b200_capture_decode(efm_b200_ctx* c, int32_t slot) {
+    if (c == nullptr) return fail(c, EFM_ERR_INVALID_ARGUMENT, "null context");
+    if (!c->finalized) return fail(c, EFM_ERR_STATE, "weights not finalized");
+    auto it = c->slots.find(slot);
+    if (it == c->slots.end()) return fail(c, EFM_ERR_INVALID_ARGUMENT, "unknown KV slot " + std::to_string(slot));
+    EFM_CK(c, cudaSetDevice(c->device));
+    return ensure_graph(c, it->second);
+}
+
+efm_status efm_b200_decode_steps(efm_b200_ctx* c, int32_t n_steps, int32_t use_graph) {
+    if (c == nullptr) return fail(c, EFM_ERR_INVALID_ARGUMENT, "null context");
+    if (c->bound_slot < 0) return fail(c, EFM_ERR_STATE, "decode_begin has not been called");
+    if (n_steps <= 0) return EFM_OK;
+    KvSlot& s = c->slots[c->bound_slot];
+    EFM_CK(c, cudaSetDevice(c->device));
+    if (!use_graph) {
+        Launcher L = make_launcher(c);
+        for (int i = 0; i < n_steps; ++i) qwen_decode_step(*c, s, L);
+        if (L.err != cudaSuccess) return cuda_fail(c, L.err, "decode launch");
+        return EFM_OK;
+    }
+    const efm_status st = ensure_graph(c, s);
+    if (st != EFM_OK) return st;
+    for (int i = 0; i < n_steps; ++i) {
+        EFM_CK(c, cudaGraphLaunch(s.graph, c->stream));
+        c->launches += s.graph_nodes;
+    }
+    return EFM_OK;
+}
+
+static efm_status check_device_state(efm_b200_ctx* c) {
+    DecodeState st{};
+    EFM_CK(c, cudaMemcpyAsync(&st, c->state, sizeof(st), cudaMemcpyDeviceToHost, c->stream));
+    EFM_CK(c, cudaStreamSynchronize(c->stream));
+    if (st.error != 0) {
+        int zero = 0;
+        cudaMemcpyAsync(&c->state->error, &zero, 4, cudaMemcpyHostToDevice, c->stream);
+        return fail(c, EFM_ERR_DEVICE_WAIT, "a kernel refused an out-of-range cache row (device status " + std::to_string(st.error) + ")");
+    }
+    return EFM_OK;
+}
+
+efm_status efm_b200_read_tokens(efm_b200_ctx* c, int32_t* host_out, int32_t first, int32_t n) {
+    if (c == nullptr || host_out == nullptr) return fail(c, EFM_ERR_INVALID_ARGUMENT, "null argument");
+    if (first < 0 || n < 0 || first + n > c->d.max_response_tokens) return fail(c, EFM_ERR_INVALID_ARGUMENT, "token range outside the response buffer");
+    EFM_CK(c, cudaSetDevice(c->device));
+    if (n > 0) EFM_CK(c, cudaMemcpyAsync(host_out, c->tokens_out + first, (size_t)n * 4, cudaMemcpyDeviceToHost, c->stream));
+    return check_device_state(c);
+}
+
+efm_status efm_b200_read_logits(efm_b200_ctx* c, float* host_out, int32_t n) {
+    if (c == nullptr || host_out == nullptr) return fail(c, EFM_ERR_INVALID_ARGUMENT, "null argument");
+    if (n < 0 || n > c->d.vocab) return fail(c, EFM_ERR_INVALID_ARGUMENT, "n exceeds vocab");
+    EFM_CK(c, cudaSetDevice(c->device));
+    EFM_CK(c, cudaMemcpyAsync(host_out, c->logits, (size_t)n * 4, cudaMemcpyDeviceToHost, c->stream));
+    EFM_CK(c, cudaStreamSynchronize(c->stream));
+    return EFM_OK;
+}
+
+efm_status efm_b200_synchronize(efm_b200_ctx* c) {
+    if (c == nullptr) return fail(c, EFM_ERR_INVALID_ARGUMENT, "null context");
+    EFM_CK(c, cudaStreamSynchronize(c->stream));
+    return EFM_OK;
+}
+
+efm_status efm_b200_event_record(efm_b200_ctx* c, int32_t idx) {
+    if (c == nullptr || idx < 0 || idx >= 16) return fail(c, EFM_ERR_INVALID_ARGUMENT, "event index out of range");
+    EFM_CK(c, cudaEventRecord(c->events[idx], c->stream));
+    return EFM_OK;
+}
+
+efm_status efm_b200_event_elapsed_ms(efm_b200_ctx* c, int32_t a, int32_t b, float* ms) {
+    if (c == nullptr || ms == nullptr || a < 0 || a >= 16 || b < 0 || b >= 16) return fail(c, EFM_ERR_INVALID_ARGUMENT, "bad event arguments");
+    EFM_CK(c, cudaEventSynchronize(c->events[b]));
+    EFM_CK(c, cudaEventElapsedTime(ms, c->events[a], c->events[b]));
+    return EFM_OK;
+}
+
+efm_status efm_b200_launch_count(efm_b200_ctx* c, int64_t* count) {
+    if (c == nullptr || count == nullptr) return fail(c, EFM_ERR_INVALID_ARGUMENT, "null argument");
+    *count = c->launches;
+    return EFM_OK;
+}
+
+efm_status efm_b200_decode_step_bytes(efm_b200_ctx* c, int32_t kv_len, int64_t* bytes) {
+    if (c == nullptr || bytes == nullptr) return fail(c, EFM_ERR_INVALID_ARGUMENT, "null argument");
+    const efm_model_desc& d = c->d;
+    const int64_t H = d.hidden, D = d.head_dim, q = d.q_heads, kv = d.kv_heads, I = d.intermediate, V = d.vocab, L = d.num_layers;
+    const int64_t per_layer = (q + 2 * kv) * D * H + (q + 2 * kv) * D + q * D * H + 3 * I * H + 2 * H;
+    const int64_t w = 2 * (L * per_layer + H + V * H) + 2 * H;      // + final norm, lm_head matrix, one embedding row
+    *bytes = w + L * 2 * (int64_t)kv_len * kv * D * 2;
+    return EFM_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// single operators on caller-provided device buffers (default stream, synchronous)
+// ---------------------------------------------------------------------------------------------
+static efm_status op_prepare(int* num_sms) {
+    int dev = 0;
+    efm_status st = EFM_OK;
+    if (cudaGetDevice(&dev) != cudaSuccess) return fail(nullptr, EFM_ERR_CUDA, "no CUDA device available");
+    if ((st = require_b200(nullptr, dev)) != EFM_OK) return st;
+    if (num_sms != nullptr) cudaDeviceGetAttribute(num_sms, cudaDevAttrMultiProcessorCount, dev);
+    return EFM_OK;
+}
+static efm_status op_finish(Launcher& L) {
+    if (L.err != cudaSuccess) return cuda_fail(nullptr, L.err, "operator launch");
+    cudaError_t e = cudaStreamSynchronize(L.stream);
+    if (e != cudaSuccess) return cuda_fail(nullptr, e, "operator execution");
+    return EFM_OK;
+}
+
+efm_status efm_b200_op_gemv(const void* w, const void* x, const void* norm_w, float eps, void* y_bf16, void* residual,
+                            int32_t n, int32_t k) {
+    int sms = 148;
+    efm_status st = op_prepare(&sms);
+    if (st != EFM_OK) return st;
+    if (w == nullptr || x == nullptr || (y_bf16 == nullptr && residual == nullptr) || n <= 0 || n % 2 || k <= 0 || k % 8)
+        return fail(nullptr, EFM_ERR_INVALID_ARGUMENT, "op_gemv: bad arguments (n even, k % 8 == 0)");
+    GemvParams p{};
+    p.W = (const __nv_bfloat16*)w; p.N = n; p.K = k; p.n_items = n / 2;
+    p.prologue = norm_w != nullptr ? kProRmsNorm : kProPlain;
+    p.x = (const __nv_bfloat16*)x; p.norm_w = (const __nv_bfloat16*)norm_w; p.eps = eps;
+    p.y = (__nv_bfloat16*)y_bf16; p.residual = (__nv_bfloat16*)residual;
+    Launcher L; L.pdl = false;
+    if (residual != nullptr) launch_gemv<Epi::Residual>(L, p, sms); else launch_gemv<Epi::Plain>(L, p, sms);
+    return op_finish(L);
+}
+
+efm_status efm_b200_op_gemm(const void* x, const void* w, const void* bias, void* y_bf16, int32_t m, int32_t n, int32_t k) {
+    efm_status st = op_prepare(nullptr);
+    if (st != EFM_OK) return st;
+    if (x == nullptr || w == nullptr || y_bf16 == nullptr || m <= 0 || n <= 0 || n % 2 || k <= 0 || k % 32)
+        return fail(nullptr, EFM_ERR_INVALID_ARGUMENT, "op_gemm: bad arguments (n even, k % 32 == 0)");
+    GemmParams g{(const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)bias, (__nv_bfloat16*)y_bf16, nullptr, m, n, k};
+    Launcher L; L.pdl = false;
+    launch_gemm_bf16(L, g);
+    return op_finish(L);
+}
+
+efm_status efm_b200_op_decode_attention(const void* q, const void* k_cache, const void* v_cache, void* out_bf16,
+                                        int32_t q_heads, int32_t kv_heads, int32_t head_dim, int32_t kv_len, int32_t max_tokens) {
+    int sms = 148;
+    efm_status st = op_prepare(&sms);
+    if (st != EFM_OK) return st;
+    if (q == nullptr || k_cache == nullptr || v_cache == nullptr || out_bf16 == nullptr || kv_heads <= 0 || q_heads % kv_heads ||
+        q_heads / kv_heads > kMaxGroup || (head_dim != 64 && head_dim != 128) || kv_len <= 0 || kv_len > max_tokens)
+        return fail(nullptr, EFM_ERR_INVALID_ARGUMENT, "op_decode_attention: bad arguments");
+    const AttnPlan plan = plan_decode_attention(max_tokens, kv_heads, sms);
+    float* part_o = nullptr; float* part_ml = nullptr; unsigned int* counters = nullptr;
+    cudaError_t e = cudaMalloc(&part_o, (size_t)q_heads * plan.n_splits * head_dim * 4);
+    if (e == cudaSuccess) e = cudaMalloc(&part_ml, (size_t)q_heads * plan.n_splits * 2 * 4);
+    if (e == cudaSuccess) e = cudaMalloc(&counters, (size_t)kv_heads * 4);
+    if (e == cudaSuccess) e = cudaMemset(counters, 0, (size_t)kv_heads * 4);
+    if (e == cudaSuccess) {
+        DecodeAttnParams a{};
+        a.q = (const __nv_bfloat16*)q; a.k_cache = (const __nv_bfloat16*)k_cache; a.v_cache = (const __nv_bfloat16*)v_cache;
+        a.out = (__nv_bfloat16*)out_bf16; a.state = nullptr; a.kv_len_static = kv_len;
+        a.q_heads = q_heads; a.kv_heads = kv_heads; a.group = q_heads / kv_heads;
+        a.n_splits = plan.n_splits; a.chunk_cap = plan.chunk_cap; a.max_tokens = max_tokens;
+        a.scale = 1.0f / sqrtf((float)head_dim);
+        a.part_o = part_o; a.part_ml = part_ml; a.counters = counters;
+        Launcher L; L.pdl = false;
+        launch_decode_attention(L, a, head_dim);
+        st = op_finish(L);
+    } else {
+        st = cuda_fail(nullptr, e, "op_decode_attention scratch");
+    }
+    cudaFree(part_o); cudaFree(part_ml); cudaFree(counters);
+    return st;
+}
+
+efm_status efm_b200_op_prefill_attention(const void* q, const void* k_cache, const void* v_cache, void* out_bf16, int32_t s,
+                                         int32_t kv_offset, int32_t q_heads, int32_t kv_heads, int32_t head_dim) {
+    efm_status st = op_prepare(nullptr);
+    if (st != EFM_OK) return st;
+    if (q == nullptr || k_cache == nullptr || v_cache == nullptr || out_bf16 == nullptr || s <= 0 || kv_offset < 0 || kv_heads <= 0 ||
+        q_heads % kv_heads || (head_dim != 64 && head_dim != 128))
+        return fail(nullptr, EFM_ERR_INVALID_ARGUMENT, "op_prefill_attention: bad arguments");
+    Launcher L; L.pdl = false;
+    launch_prefill_attention(L, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
+                             (__nv_bfloat16*)out_bf16, s, kv_offset, q_heads, kv_heads, head_dim);
+    return op_finish(L);
+}
+
+efm_status efm_b200_op_sample(const float* logits, int32_t vocab, const efm_sampling* s, uint32_t rng_step, int32_t* token_out) {
+    efm_status st = op_prepare(nullptr);
+    if (st != EFM_OK) return st;
+    if (logits == nullptr || s == nullptr || token_out == nullptr || vocab <= 0)
+        return fail(nullptr, EFM_ERR_INVALID_ARGUMENT, "op_sample: bad arguments");
+    uint32_t* wbuf = nullptr;
+    cudaError_t e = cudaMalloc(&wbuf, (size_t)vocab * 4);
+    if (e != cudaSuccess) return cuda_fail(nullptr, e, "op_sample scratch");
+    SampleParams p{};
+    p.logits = logits; p.vocab = vocab; p.n_part = 0;
+    p.temperature = s->temperature; p.top_p = s->top_p; p.seed = s->seed; p.rng_step = rng_step;
+    p.state = nullptr; p.token_single = token_out; p.wbuf = wbuf;
+    Launcher L; L.pdl = false;
+    launch_sample(L, p);
+    st = op_finish(L);
+    cudaFree(wbuf);
+    return st;
+}
+
+}  // extern "C"

@@ -1,0 +1,106 @@
+// Host-side launch plumbing shared by the layer sequences: a launcher that attaches the
+// programmatic-dependent-launch attribute and counts launches, and the shape heuristics that
+// pick a GEMV variant and a split count for decode attention.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdint>
+
+#include "../operators/decode_attention.cuh"
+#include "../operators/gemv.cuh"
+
+namespace efm {
+
+struct Launcher {
+    cudaStream_t stream = nullptr;
+    bool pdl = true;                 // programmatic stream serialization between consecutive kernels
+    int64_t* counter = nullptr;
+    cudaError_t err = cudaSuccess;   // first failure sticks
+
+    template <typename... KArgs, typename... Args>
+    void launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, Args&&... args) {
+        if (err != cudaSuccess) return;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid;
+        cfg.blockDim = block;
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = pdl ? attr : nullptr;
+        cfg.numAttrs = pdl ? 1 : 0;
+        err = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+        if (counter != nullptr) ++*counter;
+    }
+};
+
+struct GemvPlan { int items, ksplit, grid; };
+
+// Cost model: a warp's serial work is (128-bit loads per lane) per wave plus a fixed reduce /
+// epilogue cost; pick the variant with the shortest critical path and size the grid so that
+// every row group slot gets the same number of waves.
+inline GemvPlan plan_gemv(int n_items, int K, int num_sms) {
+    const int max_ctas = 2 * num_sms;
+    const int nch = K / 8;
+    GemvPlan best{2, 1, max_ctas};
+    long best_cost = -1;
+    for (int items = 2; items >= 1; --items) {
+        for (int ks = 1; ks <= 8; ks *= 2) {
+            const int gp = 8 / ks;
+            const int n_ig = (n_items + items - 1) / items;
+            const long slots = (long)max_ctas * gp;
+            const long waves = (n_ig + slots - 1) / slots;
+            const long per_wave = (long)((nch + 32 * ks - 1) / (32 * ks)) * items * 2 + 8 + (ks > 1 ? 4 : 0);
+            const long cost = waves * per_wave;
+            if (best_cost < 0 || cost < best_cost) {
+                best_cost = cost;
+                int grid = (int)((n_ig + waves * gp - 1) / (waves * gp));
+                best = GemvPlan{items, ks, std::max(1, std::min(grid, max_ctas))};
+            }
+        }
+    }
+    return best;
+}
+
+template <Epi EPI>
+inline void launch_gemv(Launcher& L, const GemvParams& p, int num_sms) {
+    const GemvPlan plan = plan_gemv(p.n_items, p.K, num_sms);
+    const size_t smem = gemv_smem_bytes(p.K, plan.items);
+    const dim3 grid(plan.grid), block(256);
+#define EFM_GEMV_CASE(I, S)                                                                   \
+    if (plan.items == I && plan.ksplit == S) {                                                \
+        if (smem > 48 * 1024)                                                                 \
+            cudaFuncSetAttribute(gemv_kernel<EPI, I, S>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        L.launch(gemv_kernel<EPI, I, S>, grid, block, smem, p);                               \
+        return;                                                                               \
+    }
+    EFM_GEMV_CASE(2, 1) EFM_GEMV_CASE(2, 2) EFM_GEMV_CASE(2, 4) EFM_GEMV_CASE(2, 8)
+    EFM_GEMV_CASE(1, 1) EFM_GEMV_CASE(1, 2) EFM_GEMV_CASE(1, 4) EFM_GEMV_CASE(1, 8)
+#undef EFM_GEMV_CASE
+}
+
+struct AttnPlan { int n_splits, chunk_cap; };
+inline AttnPlan plan_decode_attention(int max_tokens, int kv_heads, int num_sms) {
+    int n = (max_tokens + 31) / 32;
+    n = std::min(n, std::max(1, num_sms / std::max(1, kv_heads)));
+    n = std::max(1, std::min(n, 64));
+    return AttnPlan{n, (max_tokens + n - 1) / n};
+}
+
+inline void launch_decode_attention(Launcher& L, const DecodeAttnParams& p, int head_dim) {
+    const size_t smem = decode_attention_smem_bytes(head_dim, p.chunk_cap);
+    const dim3 grid(p.n_splits, p.kv_heads), block(128);
+    if (head_dim == 128) {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(decode_attention_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        L.launch(decode_attention_kernel<128>, grid, block, smem, p);
+    } else {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(decode_attention_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        L.launch(decode_attention_kernel<64>, grid, block, smem, p);
+    }
+}
+
+}  // namespace efm

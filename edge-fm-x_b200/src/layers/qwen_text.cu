@@ -1,0 +1,205 @@
+// Launch sequences of the Qwen2.5 / Qwen2.5-VL text tower: one decode step and one prefill
+// chunk.  Layer order and residual dataflow follow the reference's forward
+// (src/models/qwen2_5/qwen2_5.cpp:534-930); what the reference runs as 9-10 kernels per layer
+// at decode is five launches here:
+//   [embed +] RMSNorm + QKV GEMV + bias + RoPE + KV append | attention | o_proj + residual |
+//   RMSNorm + gate/up GEMV + SiLU*mul | down_proj + residual
+// and norm + lm_head + block argmax | sampler + state advance at the end of the step.
+#include "qwen_text.h"
+
+#include "../operators/gemm_mma.cuh"
+#include "../operators/prefill.cuh"
+#include "../operators/sample.cuh"
+#include "launch.cuh"
+
+namespace efm {
+
+static GemvParams base_gemv(const __nv_bfloat16* W, int N, int K) {
+    GemvParams p{};
+    p.W = W;
+    p.N = N;
+    p.K = K;
+    p.n_items = N / 2;
+    p.prologue = kProPlain;
+    return p;
+}
+
+void launch_sample(Launcher& L, const SampleParams& p) { L.launch(sample_kernel, dim3(1), dim3(1024), 0, p); }
+
+void launch_lm_head_and_sample(efm_b200_ctx& c, Launcher& L, const __nv_bfloat16* resid_row, int advance) {
+    const efm_model_desc& d = c.d;
+    GemvParams p = base_gemv(c.lm_head, d.vocab, d.hidden);
+    p.prologue = kProRmsNorm;
+    p.x = resid_row;
+    p.norm_w = c.final_norm;
+    p.eps = d.rms_eps;
+    p.logits = c.logits;
+    p.part_val = c.part_val;
+    p.part_idx = c.part_idx;
+    const GemvPlan plan = plan_gemv(p.n_items, p.K, c.num_sms);
+    launch_gemv<Epi::Logits>(L, p, c.num_sms);
+
+    SampleParams s{};
+    s.logits = c.logits;
+    s.vocab = d.vocab;
+    s.part_val = c.part_val;
+    s.part_idx = c.part_idx;
+    s.n_part = plan.grid;
+    s.temperature = c.sampling.temperature;
+    s.top_p = c.sampling.top_p;
+    s.seed = c.sampling.seed;
+    s.state = c.state;
+    s.tokens_out = c.tokens_out;
+    s.max_response = d.max_response_tokens;
+    s.advance = advance;
+    s.wbuf = c.wbuf;
+    launch_sample(L, s);
+}
+
+void qwen_decode_step(efm_b200_ctx& c, KvSlot& slot, Launcher& L) {
+    const efm_model_desc& d = c.d;
+    const int H = d.hidden, D = d.head_dim, QD = d.q_heads * D, KVD = d.kv_heads * D, I = d.intermediate;
+    for (int l = 0; l < d.num_layers; ++l) {
+        const LayerWeights& w = c.layers[l];
+        {
+            GemvParams p = base_gemv(w.qkv, QD + 2 * KVD, H);
+            p.prologue = l == 0 ? kProEmbedRmsNorm : kProRmsNorm;
+            p.x = c.resid_d;
+            p.norm_w = w.in_norm;
+            p.eps = d.rms_eps;
+            p.embed_table = c.embed;
+            p.vocab = d.vocab;
+            p.resid_out = c.resid_d;
+            p.state = c.state;
+            p.bias = w.qkv_bias;
+            p.q_out = c.q_d;
+            p.k_cache = slot.k[l];
+            p.v_cache = slot.v[l];
+            p.inv_freq = c.inv_freq;
+            p.q_heads = d.q_heads;
+            p.kv_heads = d.kv_heads;
+            p.head_dim = D;
+            p.use_mrope = d.use_mrope;
+            p.sec0 = d.mrope_section[0];
+            p.sec1 = d.mrope_section[0] + d.mrope_section[1];
+            p.max_tokens = slot.max_tokens;
+            launch_gemv<Epi::QkvRope>(L, p, c.num_sms);
+        }
+        {
+            DecodeAttnParams a{};
+            a.q = c.q_d;
+            a.k_cache = slot.k[l];
+            a.v_cache = slot.v[l];
+            a.out = c.attn_d;
+            a.state = c.state;
+            a.q_heads = d.q_heads;
+            a.kv_heads = d.kv_heads;
+            a.group = d.q_heads / d.kv_heads;
+            a.n_splits = slot.n_splits;
+            a.chunk_cap = slot.chunk_cap;
+            a.max_tokens = slot.max_tokens;
+            a.scale = 1.0f / sqrtf((float)D);
+            a.part_o = c.attn_part_o;
+            a.part_ml = c.attn_part_ml;
+            a.counters = c.attn_counters;
+            launch_decode_attention(L, a, D);
+        }
+        {
+            GemvParams p = base_gemv(w.o, H, QD);
+            p.x = c.attn_d;
+            p.residual = c.resid_d;
+            launch_gemv<Epi::Residual>(L, p, c.num_sms);
+        }
+        {
+            GemvParams p = base_gemv(w.gate_up, 2 * I, H);
+            p.prologue = kProRmsNorm;
+            p.x = c.resid_d;
+            p.norm_w = w.post_norm;
+            p.eps = d.rms_eps;
+            p.y = c.act_d;
+            launch_gemv<Epi::SwiGlu>(L, p, c.num_sms);
+        }
+        {
+            GemvParams p = base_gemv(w.down, H, I);
+            p.x = c.act_d;
+            p.residual = c.resid_d;
+            launch_gemv<Epi::Residual>(L, p, c.num_sms);
+        }
+    }
+    launch_lm_head_and_sample(c, L, c.resid_d, /*advance=*/1);
+}
+
+template <GemmEpi EPI>
+static void launch_gemm(Launcher& L, const GemmParams& p) {
+    const size_t smem = gemm_mma_smem_bytes();
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaFuncSetAttribute(gemm_mma_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        attr_set = true;
+    }
+    const dim3 grid((p.N + 127) / 128, (p.M + 127) / 128), block(256);
+    const bool pdl = L.pdl;
+    L.pdl = false;     // prefill kernels do not use the dependent-launch protocol
+    L.launch(gemm_mma_kernel<EPI>, grid, block, smem, p);
+    L.pdl = pdl;
+}
+
+void launch_gemm_bf16(Launcher& L, const GemmParams& p) { launch_gemm<GemmEpi::Bf16Bias>(L, p); }
+
+void launch_prefill_attention(Launcher& L, const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v,
+                              __nv_bfloat16* out, int S, int kv_offset, int q_heads, int kv_heads, int D) {
+    const dim3 grid((S + 3) / 4, q_heads), block(128);
+    const float scale = 1.0f / sqrtf((float)D);
+    const bool pdl = L.pdl;
+    L.pdl = false;
+    if (D == 128) L.launch(prefill_attention_kernel<128>, grid, block, 0, q, k, v, out, S, kv_offset, q_heads, kv_heads, scale);
+    else L.launch(prefill_attention_kernel<64>, grid, block, 0, q, k, v, out, S, kv_offset, q_heads, kv_heads, scale);
+    L.pdl = pdl;
+}
+
+void qwen_prefill_chunk(efm_b200_ctx& c, KvSlot& slot, int S, int kv_offset, int n_custom, int embed_token_id,
+                        bool sample_last, Launcher& L) {
+    const efm_model_desc& d = c.d;
+    const int H = d.hidden, D = d.head_dim, QD = d.q_heads * D, KVD = d.kv_heads * D, I = d.intermediate;
+    const bool pdl = L.pdl;
+    L.pdl = false;
+    L.launch(embed_rows_kernel, dim3(S), dim3(128), 0, (const int32_t*)c.ids, (const __nv_bfloat16*)c.embed,
+             (const __nv_bfloat16*)(n_custom > 0 ? c.custom_embeds : nullptr), c.resid, d.vocab, H, embed_token_id, n_custom);
+    for (int l = 0; l < d.num_layers; ++l) {
+        const LayerWeights& w = c.layers[l];
+        L.launch(rmsnorm_rows_kernel, dim3(S), dim3(256), 0, (const __nv_bfloat16*)c.resid,
+                 (const __nv_bfloat16*)w.in_norm, c.norm, H, d.rms_eps);
+        {
+            GemmParams g{c.norm, w.qkv, w.qkv_bias, c.qkv, nullptr, S, QD + 2 * KVD, H};
+            launch_gemm<GemmEpi::Bf16Bias>(L, g);
+        }
+        L.launch(rope_scatter_kernel, dim3(S, d.q_heads + 2 * d.kv_heads), dim3(D / 2), 0,
+                 (const __nv_bfloat16*)c.qkv, c.qbuf, slot.k[l], slot.v[l], (const float*)c.inv_freq,
+                 (const int32_t*)c.pos3, S, d.q_heads, d.kv_heads, D, kv_offset, d.use_mrope, d.mrope_section[0],
+                 d.mrope_section[0] + d.mrope_section[1]);
+        launch_prefill_attention(L, c.qbuf, slot.k[l], slot.v[l], c.attn, S, kv_offset, d.q_heads, d.kv_heads, D);
+        {
+            GemmParams g{c.attn, w.o, nullptr, c.resid, nullptr, S, H, QD};
+            launch_gemm<GemmEpi::Residual>(L, g);
+        }
+        L.launch(rmsnorm_rows_kernel, dim3(S), dim3(256), 0, (const __nv_bfloat16*)c.resid,
+                 (const __nv_bfloat16*)w.post_norm, c.norm, H, d.rms_eps);
+        {
+            GemmParams g{c.norm, w.gate_up, nullptr, nullptr, c.gu, S, 2 * I, H};
+            launch_gemm<GemmEpi::F32>(L, g);
+        }
+        {
+            const size_t total = (size_t)S * I;
+            const int grid = (int)std::min<size_t>((total + 255) / 256, (size_t)c.num_sms * 8);
+            L.launch(swiglu_rows_kernel, dim3(grid), dim3(256), 0, (const float*)c.gu, c.act, S, I);
+        }
+        {
+            GemmParams g{c.act, w.down, nullptr, c.resid, nullptr, S, H, I};
+            launch_gemm<GemmEpi::Residual>(L, g);
+        }
+    }
+    if (sample_last) launch_lm_head_and_sample(c, L, c.resid + (size_t)(S - 1) * H, /*advance=*/0);
+    L.pdl = pdl;
+}
+
+}  // namespace efm

@@ -1,0 +1,23 @@
+// Launch sequences of the text tower (definitions in qwen_text.cu).
+#pragma once
+#include "../backends/b200/ctx.h"
+
+namespace efm {
+struct Launcher;
+struct GemmParams;
+struct SampleParams;
+
+// One decode step: reads the device state (token, kv_len, positions), appends K/V at row
+// kv_len-1, samples, advances the state.  All launches go through L (graph-capturable).
+void qwen_decode_step(efm_b200_ctx& c, KvSlot& slot, Launcher& L);
+// One prefill chunk over c.ids[0:S] (already on the device), KV rows [kv_offset, kv_offset+S).
+void qwen_prefill_chunk(efm_b200_ctx& c, KvSlot& slot, int S, int kv_offset, int n_custom, int embed_token_id,
+                        bool sample_last, Launcher& L);
+// Final norm + lm_head + sampler on one residual row.
+void launch_lm_head_and_sample(efm_b200_ctx& c, Launcher& L, const __nv_bfloat16* resid_row, int advance);
+// Single operators (used by the per-operator C entry points).
+void launch_gemm_bf16(Launcher& L, const GemmParams& p);
+void launch_sample(Launcher& L, const SampleParams& p);
+void launch_prefill_attention(Launcher& L, const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v,
+                              __nv_bfloat16* out, int S, int kv_offset, int q_heads, int kv_heads, int D);
+}  // namespace efm

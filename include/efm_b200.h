@@ -1,0 +1,189 @@
+/*
+ * efm_b200.h — C ABI of the B200 (sm_100a) device backend for EdgeFM's single-request
+ * generate() path.
+ *
+ * The reference engine (windog-labs/edge-fm-x) has no FFI boundary on this path: its
+ * StandardEngine calls C++ Model/Layer/Operator objects directly.  This header is the
+ * boundary a reference-side engine binds instead; each entry point names the reference
+ * interface it replaces (paths relative to the reference tree).  Style follows the one
+ * thin backend boundary the reference does have, IRuntimeBackend
+ * (src/backends/runtime_backend.h:56-75): integer status + last_error().
+ *
+ * Rules: plain C types only; every call returns efm_status (0 = ok) and records a message
+ * retrievable with efm_b200_last_error(); no exceptions cross the boundary; a context is
+ * owned by one host thread at a time; all device work runs on the context's own stream.
+ * There is no CPU fallback: every entry point fails with EFM_ERR_CUDA when no sm_100 device
+ * is usable.
+ */
+#ifndef EFM_B200_H_
+#define EFM_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define EFM_API
+#else
+#define EFM_API __attribute__((visibility("default")))
+#endif
+
+typedef int32_t efm_status;
+enum {
+    EFM_OK = 0,
+    EFM_ERR_INVALID_ARGUMENT = 1,
+    EFM_ERR_CUDA = 2,
+    EFM_ERR_OUT_OF_MEMORY = 3,
+    EFM_ERR_STATE = 4,         /* call order violated (e.g. decode before prefill) */
+    EFM_ERR_UNSUPPORTED = 5,   /* shape / dtype outside what the kernels are built for */
+    EFM_ERR_DEVICE_WAIT = 6    /* a bounded device-side wait gave up; context still usable */
+};
+
+/* element types, numbered like edge_fm::DType (include/edge-fm/core.h:17-25) */
+enum { EFM_F32 = 0, EFM_F16 = 1, EFM_BF16 = 2, EFM_I32 = 3, EFM_I64 = 4, EFM_U8 = 5, EFM_I8 = 6 };
+/* where a caller buffer lives */
+enum { EFM_MEM_HOST = 0, EFM_MEM_DEVICE = 1 };
+
+/* Model geometry: the fields the reference reads from the HF config.json
+ * (src/models/model.cpp:56-71, src/models/qwen2_5/qwen2_5.cpp:89-93,172-200). */
+typedef struct efm_model_desc {
+    int32_t struct_size;          /* = sizeof(efm_model_desc) */
+    int32_t num_layers;
+    int32_t hidden;
+    int32_t q_heads;
+    int32_t kv_heads;
+    int32_t head_dim;             /* 64 or 128 */
+    int32_t intermediate;         /* multiple of 64 */
+    int32_t vocab;                /* even */
+    float rms_eps;
+    float rope_theta;
+    int32_t tied_lm_head;         /* 1: lm_head reads model.embed_tokens.weight */
+    int32_t use_mrope;            /* 1: positions come as [3,S] rows (Qwen2.5-VL) */
+    int32_t mrope_section[3];     /* rotary pairs per row, e.g. {16,24,24} */
+    int32_t max_prefill_tokens;   /* activation rows; longer prefills are chunked */
+    int32_t max_response_tokens;  /* capacity of the device-side response buffer */
+} efm_model_desc;
+
+/* sampling.{temperature,top_p,top_k,seed} of the engine JSON (src/layers/sampler.cu:121-133).
+ * temperature < 1e-6 -> greedy (ties -> lowest id).  top_k is accepted and ignored, as in
+ * the reference. */
+typedef struct efm_sampling {
+    float temperature;
+    float top_p;
+    int32_t top_k;
+    uint32_t reserved;
+    uint64_t seed;
+} efm_sampling;
+
+typedef struct efm_b200_ctx efm_b200_ctx;
+
+/* ---- lifetime -------------------------------------------------------------------------- */
+/* Replaces Model::create + Qwen2_5 ctor (src/models/model.cpp:74-85, qwen2_5.cpp:84-246).
+ * tp_rank/tp_size: tensor-parallel coordinates (1 rank = whole model). */
+EFM_API efm_status efm_b200_create(const efm_model_desc* desc, int32_t device_id, int32_t tp_rank,
+                                   int32_t tp_size, efm_b200_ctx** out);
+EFM_API efm_status efm_b200_destroy(efm_b200_ctx* ctx);
+/* Message of the last failing call on this context (ctx may be NULL: last create failure). */
+EFM_API const char* efm_b200_last_error(const efm_b200_ctx* ctx);
+EFM_API const char* efm_b200_version(void);
+
+/* ---- weights --------------------------------------------------------------------------- */
+/* Replaces WeightLoader::load_weights_from_file + per-layer load_weights
+ * (src/utils/device/weight_loader.cpp:80-171, src/layers/linear.cu:1691-1717,1926-1943).
+ * hf_name: e.g. "model.layers.3.self_attn.q_proj.weight"; data is row-major [out,in] bf16.
+ * Unknown names are ignored (returns EFM_OK), like the reference's name filter. */
+EFM_API efm_status efm_b200_set_weight(efm_b200_ctx* ctx, const char* hf_name, const void* data,
+                                       const int64_t* shape, int32_t ndim, int32_t dtype, int32_t mem_kind);
+/* Checks that every tensor arrived; after this call weights are immutable. */
+EFM_API efm_status efm_b200_finalize_weights(efm_b200_ctx* ctx);
+
+/* ---- KV slots -------------------------------------------------------------------------- */
+/* Replaces KVManager slot allocation (src/engine/tasks/token_generation/kv_manager.cpp:45-201):
+ * per layer one buffer [K: max_tokens x kv_heads x head_dim | V: same], bf16. */
+EFM_API efm_status efm_b200_alloc_kv_slot(efm_b200_ctx* ctx, int32_t slot, int32_t max_tokens);
+/* Device address of layer's K block for the slot (V block follows at +max_tokens*kv*D elements);
+ * KVManager::get_read_kvcache (kv_manager.cpp:203-230). */
+EFM_API efm_status efm_b200_kv_layer_ptr(efm_b200_ctx* ctx, int32_t slot, int32_t layer, void** k_base,
+                                         int32_t* max_tokens);
+
+/* ---- generate path --------------------------------------------------------------------- */
+/* Replaces SamplerLayer configuration (src/layers/sampler.cu:121-133). */
+EFM_API efm_status efm_b200_set_sampling(efm_b200_ctx* ctx, const efm_sampling* s);
+
+/* Replaces prepare_prefill_tensors + Qwen2_5::prefill + run_sampler
+ * (standard_engine.cpp:1200-1477,925-971; qwen2_5.cpp:534-930).
+ * Runs the model over n_tokens ids (host int32) whose KV lands at cache rows
+ * [kv_offset, kv_offset+n_tokens); rows [0,kv_offset) must already be resident (fixed prefix).
+ * embeds (bf16 [n_embeds, hidden], host or device per embeds_mem) replace ids in
+ * [embed_token_id, embed_token_id+n_embeds) (src/layers/embed_head.cu:93-116); pass NULL/0/-1
+ * for none.  pos_ids3: host int32 [3, n_tokens] for M-RoPE models, else NULL.
+ * When sample != 0 the last row's logits are sampled (RNG counter 0) into the device token
+ * slot and response position 0. */
+EFM_API efm_status efm_b200_prefill(efm_b200_ctx* ctx, int32_t slot, const int32_t* token_ids,
+                                    int32_t n_tokens, int32_t kv_offset, const void* embeds,
+                                    int32_t n_embeds, int32_t embed_token_id, int32_t embeds_mem,
+                                    const int32_t* pos_ids3, int32_t sample);
+
+/* Replaces prepare_decode_tensors / DecodeRuntimeStateLayout (standard_engine.cpp:128-150,
+ * 1479-1572): binds the slot and sets the device state {kv_len, positions, step}.  kv_len =
+ * tokens resident before the first decode step; mrope_pos = position of the first decoded
+ * token on each axis (ignored for text models); step = response index the first decoded
+ * token is written to (1 after a sampled prefill). */
+EFM_API efm_status efm_b200_decode_begin(efm_b200_ctx* ctx, int32_t slot, int32_t kv_len,
+                                         const int32_t mrope_pos[3], int32_t step);
+/* Overwrites the device token slot (teacher forcing in tests). */
+EFM_API efm_status efm_b200_set_token(efm_b200_ctx* ctx, int32_t token);
+/* Replaces the decode loop body: Qwen2_5::decode_step + sampler + state advance, captured as
+ * one CUDA graph when use_graph != 0 (standard_engine.cpp:772-859,975-1035).  Asynchronous. */
+EFM_API efm_status efm_b200_decode_steps(efm_b200_ctx* ctx, int32_t n_steps, int32_t use_graph);
+/* Captures the decode-step graph for a slot without running it (the reference captures during
+ * warmup(): standard_engine.cpp:515-556).  Optional: decode_steps captures on first use. */
+EFM_API efm_status efm_b200_capture_decode(efm_b200_ctx* ctx, int32_t slot);
+/* One D2H copy of response tokens [first, first+n) + stream sync (standard_engine.cpp:1043-1057).
+ * Also surfaces device-side status words (EFM_ERR_DEVICE_WAIT). */
+EFM_API efm_status efm_b200_read_tokens(efm_b200_ctx* ctx, int32_t* host_out, int32_t first, int32_t n);
+/* fp32 logits of the most recent forward ([vocab]); synchronises. */
+EFM_API efm_status efm_b200_read_logits(efm_b200_ctx* ctx, float* host_out, int32_t n);
+EFM_API efm_status efm_b200_synchronize(efm_b200_ctx* ctx);
+
+/* ---- timing / accounting (CudaMetricRecorder, standard_engine.cpp:405-460) -------------- */
+/* Records CUDA event `idx` (0..15) on the context stream. */
+EFM_API efm_status efm_b200_event_record(efm_b200_ctx* ctx, int32_t idx);
+EFM_API efm_status efm_b200_event_elapsed_ms(efm_b200_ctx* ctx, int32_t start_idx, int32_t stop_idx, float* ms);
+/* Kernels launched by this context since creation (graph replays count their nodes). */
+EFM_API efm_status efm_b200_launch_count(efm_b200_ctx* ctx, int64_t* count);
+/* Bytes of weights / KV one decode step must stream at the given kv_len (roofline numerator). */
+EFM_API efm_status efm_b200_decode_step_bytes(efm_b200_ctx* ctx, int32_t kv_len, int64_t* bytes);
+
+/* ---- single operators on caller-provided DEVICE buffers (parity tests per kernel; the
+ * reference exposes the same granularity through its debug bindings, pybind_debug.cpp) ----- */
+/* y[n] = W[n,:] . x   (+ optional rmsnorm prologue when norm_w != NULL; + optional residual
+ * epilogue r[n] = bf16(r[n] + bf16(y[n])) when residual != NULL, else y_bf16[n] written).
+ * LinearLayer decode GEMV (src/operators/linear_impl.cu:457-469). */
+EFM_API efm_status efm_b200_op_gemv(const void* w, const void* x, const void* norm_w, float eps,
+                                    void* y_bf16, void* residual, int32_t n, int32_t k);
+/* Y[m,n] = X[m,k] . W[n,k]^T (+bias[n]) -> bf16 (prefill linear; linear_impl.cu:457-469,482-706). */
+EFM_API efm_status efm_b200_op_gemm(const void* x, const void* w, const void* bias, void* y_bf16,
+                                    int32_t m, int32_t n, int32_t k);
+/* Batch-1 GQA decode attention over a [max_tokens, kv, D] bf16 cache
+ * (src/operators/attention_op.cu:1428-1466).  q: [q_heads, D] bf16 (already rotated). */
+EFM_API efm_status efm_b200_op_decode_attention(const void* q, const void* k_cache, const void* v_cache,
+                                                void* out_bf16, int32_t q_heads, int32_t kv_heads,
+                                                int32_t head_dim, int32_t kv_len, int32_t max_tokens);
+/* Causal GQA prefill attention, queries at cache rows [kv_offset, kv_offset+s)
+ * (attention_op.cu:1221-1343).  q: [s, q_heads, D] bf16. */
+EFM_API efm_status efm_b200_op_prefill_attention(const void* q, const void* k_cache, const void* v_cache,
+                                                 void* out_bf16, int32_t s, int32_t kv_offset,
+                                                 int32_t q_heads, int32_t kv_heads, int32_t head_dim);
+/* Sampler on fp32 logits [vocab] -> one int32 (device).  SamplerLayer::forward
+ * (src/layers/sampler.cu:146-299). */
+EFM_API efm_status efm_b200_op_sample(const float* logits, int32_t vocab, const efm_sampling* s,
+                                      uint32_t rng_step, int32_t* token_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* EFM_B200_H_ */

@@ -1,0 +1,234 @@
+"""ctypes binding of include/efm_b200.h for the tests, smoke() and bench.py.
+
+Loads the in-tree lib/libefm_b200.so; raises if it is missing (there is no fallback).  The
+signatures below are checked against the header by tests/test_cabi_exports.py.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+PKG = os.path.join(ROOT, "edge-fm-x_b200")
+LIB_PATH = os.path.join(PKG, "lib", "libefm_b200.so")
+PY_DIR = os.path.join(PKG, "python")
+
+EFM_OK = 0
+EFM_F32, EFM_F16, EFM_BF16, EFM_I32 = 0, 1, 2, 3
+EFM_MEM_HOST, EFM_MEM_DEVICE = 0, 1
+
+
+class ModelDesc(C.Structure):
+    _fields_ = [("struct_size", C.c_int32), ("num_layers", C.c_int32), ("hidden", C.c_int32),
+                ("q_heads", C.c_int32), ("kv_heads", C.c_int32), ("head_dim", C.c_int32),
+                ("intermediate", C.c_int32), ("vocab", C.c_int32), ("rms_eps", C.c_float),
+                ("rope_theta", C.c_float), ("tied_lm_head", C.c_int32), ("use_mrope", C.c_int32),
+                ("mrope_section", C.c_int32 * 3), ("max_prefill_tokens", C.c_int32),
+                ("max_response_tokens", C.c_int32)]
+
+
+class Sampling(C.Structure):
+    _fields_ = [("temperature", C.c_float), ("top_p", C.c_float), ("top_k", C.c_int32),
+                ("reserved", C.c_uint32), ("seed", C.c_uint64)]
+
+
+P = C.c_void_p
+I32 = C.c_int32
+SIGNATURES = {
+    "efm_b200_create": (I32, [C.POINTER(ModelDesc), I32, I32, I32, C.POINTER(P)]),
+    "efm_b200_destroy": (I32, [P]),
+    "efm_b200_last_error": (C.c_char_p, [P]),
+    "efm_b200_version": (C.c_char_p, []),
+    "efm_b200_set_weight": (I32, [P, C.c_char_p, P, C.POINTER(C.c_int64), I32, I32, I32]),
+    "efm_b200_finalize_weights": (I32, [P]),
+    "efm_b200_alloc_kv_slot": (I32, [P, I32, I32]),
+    "efm_b200_kv_layer_ptr": (I32, [P, I32, I32, C.POINTER(P), C.POINTER(I32)]),
+    "efm_b200_set_sampling": (I32, [P, C.POINTER(Sampling)]),
+    "efm_b200_prefill": (I32, [P, I32, C.POINTER(I32), I32, I32, P, I32, I32, I32, C.POINTER(I32), I32]),
+    "efm_b200_decode_begin": (I32, [P, I32, I32, C.POINTER(I32), I32]),
+    "efm_b200_set_token": (I32, [P, I32]),
+    "efm_b200_decode_steps": (I32, [P, I32, I32]),
+    "efm_b200_capture_decode": (I32, [P, I32]),
+    "efm_b200_read_tokens": (I32, [P, C.POINTER(I32), I32, I32]),
+    "efm_b200_read_logits": (I32, [P, C.POINTER(C.c_float), I32]),
+    "efm_b200_synchronize": (I32, [P]),
+    "efm_b200_event_record": (I32, [P, I32]),
+    "efm_b200_event_elapsed_ms": (I32, [P, I32, I32, C.POINTER(C.c_float)]),
+    "efm_b200_launch_count": (I32, [P, C.POINTER(C.c_int64)]),
+    "efm_b200_decode_step_bytes": (I32, [P, I32, C.POINTER(C.c_int64)]),
+    "efm_b200_op_gemv": (I32, [P, P, P, C.c_float, P, P, I32, I32]),
+    "efm_b200_op_gemm": (I32, [P, P, P, P, I32, I32, I32]),
+    "efm_b200_op_decode_attention": (I32, [P, P, P, P, I32, I32, I32, I32, I32]),
+    "efm_b200_op_prefill_attention": (I32, [P, P, P, P, I32, I32, I32, I32, I32]),
+    "efm_b200_op_sample": (I32, [C.POINTER(C.c_float), I32, C.POINTER(Sampling), C.c_uint32, C.POINTER(I32)]),
+}
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(f"{LIB_PATH} is missing: run `python edge-fm-x_b200/build.py` (there is no fallback path)")
+        _lib = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(_lib, name)
+            fn.restype, fn.argtypes = res, args
+    return _lib
+
+
+class BackendError(RuntimeError):
+    pass
+
+
+def _i32_array(values):
+    return (I32 * len(values))(*[int(v) for v in values])
+
+
+class Backend:
+    """Thin object wrapper over one efm_b200_ctx."""
+
+    def __init__(self, cfg, *, max_prefill_tokens=256, max_response_tokens=512, device_id=0):
+        self.L = lib()
+        self.cfg = cfg
+        d = ModelDesc()
+        d.struct_size = C.sizeof(ModelDesc)
+        d.num_layers, d.hidden, d.q_heads, d.kv_heads = cfg.num_layers, cfg.hidden, cfg.q_heads, cfg.kv_heads
+        d.head_dim, d.intermediate, d.vocab = cfg.head_dim, cfg.intermediate, cfg.vocab
+        d.rms_eps, d.rope_theta = cfg.rms_eps, cfg.rope_theta
+        d.tied_lm_head = 1 if cfg.tied else 0
+        d.use_mrope = 1 if cfg.mrope_section is not None else 0
+        if cfg.mrope_section is not None:
+            d.mrope_section[:] = cfg.mrope_section
+        d.max_prefill_tokens, d.max_response_tokens = max_prefill_tokens, max_response_tokens
+        self.ctx = P()
+        st = self.L.efm_b200_create(C.byref(d), device_id, 0, 1, C.byref(self.ctx))
+        if st != EFM_OK:
+            raise BackendError(f"create failed ({st}): {self.L.efm_b200_last_error(None).decode()}")
+
+    def check(self, st, what=""):
+        if st != EFM_OK:
+            raise BackendError(f"{what} failed ({st}): {self.L.efm_b200_last_error(self.ctx).decode()}")
+
+    def close(self):
+        if self.ctx:
+            self.L.efm_b200_destroy(self.ctx)
+            self.ctx = P()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def load_weights(self, weights):
+        """weights: dict name -> torch bf16 tensor (CPU or CUDA)."""
+        for name, t in weights.items():
+            t = t.contiguous()
+            shape = (C.c_int64 * t.dim())(*t.shape)
+            mem = EFM_MEM_DEVICE if t.is_cuda else EFM_MEM_HOST
+            self.check(self.L.efm_b200_set_weight(self.ctx, name.encode(), P(t.data_ptr()), shape, t.dim(),
+                                                  EFM_BF16, mem), "set_weight " + name)
+        self.check(self.L.efm_b200_finalize_weights(self.ctx), "finalize_weights")
+
+    def alloc_slot(self, slot, max_tokens):
+        self.check(self.L.efm_b200_alloc_kv_slot(self.ctx, slot, max_tokens), "alloc_kv_slot")
+
+    def set_sampling(self, temperature=0.0, top_p=1.0, seed=0, top_k=1):
+        s = Sampling(temperature, top_p, top_k, 0, seed)
+        self.check(self.L.efm_b200_set_sampling(self.ctx, C.byref(s)), "set_sampling")
+
+    def prefill(self, slot, ids, kv_offset=0, embeds=None, embed_token_id=-1, pos3=None, sample=True):
+        n = len(ids)
+        ep, ne, em = None, 0, EFM_MEM_HOST
+        if embeds is not None:
+            embeds = embeds.contiguous()
+            ep, ne = P(embeds.data_ptr()), embeds.shape[0]
+            em = EFM_MEM_DEVICE if embeds.is_cuda else EFM_MEM_HOST
+        pp = None
+        if pos3 is not None:
+            flat = [int(v) for row in pos3 for v in row]
+            assert len(flat) == 3 * n
+            pp = _i32_array(flat)
+        self.check(self.L.efm_b200_prefill(self.ctx, slot, _i32_array(ids), n, kv_offset, ep, ne, embed_token_id, em,
+                                           pp, 1 if sample else 0), "prefill")
+
+    def decode_begin(self, slot, kv_len, mrope_pos=None, step=1):
+        mp = _i32_array(mrope_pos) if mrope_pos is not None else None
+        self.check(self.L.efm_b200_decode_begin(self.ctx, slot, kv_len, mp, step), "decode_begin")
+
+    def set_token(self, tok):
+        self.check(self.L.efm_b200_set_token(self.ctx, int(tok)), "set_token")
+
+    def decode_steps(self, n, use_graph=True):
+        self.check(self.L.efm_b200_decode_steps(self.ctx, n, 1 if use_graph else 0), "decode_steps")
+
+    def capture_decode(self, slot):
+        self.check(self.L.efm_b200_capture_decode(self.ctx, slot), "capture_decode")
+
+    def read_tokens(self, first, n):
+        buf = (I32 * max(n, 1))()
+        self.check(self.L.efm_b200_read_tokens(self.ctx, buf, first, n), "read_tokens")
+        return list(buf[:n])
+
+    def read_logits(self):
+        import numpy as np
+        out = np.empty(self.cfg.vocab, dtype=np.float32)
+        self.check(self.L.efm_b200_read_logits(self.ctx, out.ctypes.data_as(C.POINTER(C.c_float)), self.cfg.vocab),
+                   "read_logits")
+        return out
+
+    def synchronize(self):
+        self.check(self.L.efm_b200_synchronize(self.ctx), "synchronize")
+
+    def event_record(self, idx):
+        self.check(self.L.efm_b200_event_record(self.ctx, idx), "event_record")
+
+    def elapsed_ms(self, a, b):
+        ms = C.c_float()
+        self.check(self.L.efm_b200_event_elapsed_ms(self.ctx, a, b, C.byref(ms)), "event_elapsed")
+        return ms.value
+
+    def launch_count(self):
+        n = C.c_int64()
+        self.check(self.L.efm_b200_launch_count(self.ctx, C.byref(n)), "launch_count")
+        return n.value
+
+    def decode_step_bytes(self, kv_len):
+        n = C.c_int64()
+        self.check(self.L.efm_b200_decode_step_bytes(self.ctx, kv_len, C.byref(n)), "decode_step_bytes")
+        return n.value
+
+    def kv_layer(self, slot, layer):
+        p, mt = P(), I32()
+        self.check(self.L.efm_b200_kv_layer_ptr(self.ctx, slot, layer, C.byref(p), C.byref(mt)), "kv_layer_ptr")
+        return p.value, mt.value
+
+
+def generate(be: Backend, slot, prompt, max_new_tokens, *, prefix_len=0, embeds=None, embed_token_id=-1, pos3=None,
+             mrope_last_pos=None, use_graph=True, forced=None, collect_logits=False):
+    """generate() through the C ABI: prefill of prompt[prefix_len:], then decode steps.
+    forced: teacher-forced feed tokens (step by step, no graph batching).  Returns (tokens, logits list)."""
+    ids = list(prompt[prefix_len:])
+    p3 = None if pos3 is None else [list(r[prefix_len:]) for r in pos3]
+    be.prefill(slot, ids, kv_offset=prefix_len, embeds=embeds, embed_token_id=embed_token_id, pos3=p3, sample=True)
+    logits = [be.read_logits()] if collect_logits else []
+    mp = None
+    if be.cfg.mrope_section is not None:
+        if mrope_last_pos is None:
+            mrope_last_pos = [max(max(r) for r in pos3)] * 3
+        mp = [m + 1 for m in mrope_last_pos]
+    n_dec = max_new_tokens - 1
+    if n_dec > 0:
+        be.decode_begin(slot, len(prompt), mp, 1)
+        if forced is None and not collect_logits:
+            be.decode_steps(n_dec, use_graph)
+        else:
+            for s in range(n_dec):
+                if forced is not None:
+                    be.set_token(forced[s])
+                be.decode_steps(1, use_graph)
+                if collect_logits:
+                    logits.append(be.read_logits())
+    return be.read_tokens(0, max_new_tokens), logits

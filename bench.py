@@ -1,0 +1,345 @@
+"""Benchmark of the single-request generate() hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config 0..3]
+
+Workload (default --config 1, the configuration the decode tok/s metric is quoted on):
+Qwen2.5-1.5B-shaped random bf16 model, 512-token fixed prefix resident in the KV slot, 256-token
+prompt, 256 generated tokens at batch 1 with temperature 0.7 / top-p 0.9 / seed 0.  One "step" is
+one request: prefill of the prompt over the prefix + sample + 255 decode steps.
+  value  decode tok/s from CUDA events around the decode phase (inputs resident on the device);
+  e2e    tokens/s of edge_fm.EdgeFM.generate() with host token ids in and host ids out;
+  N > 1  independent replicas, one process per GPU (the path has no data-parallel exchange).
+Prints exactly one JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for p in (ROOT, os.path.join(ROOT, "tests"), os.path.join(ROOT, "edge-fm-x_b200", "python")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+METRIC, UNIT = "decode_tokens_per_second_batch1", "tok/s"
+NAMES = {0: "qwen2.5-0.5b", 1: "qwen2.5-1.5b", 2: "qwen2.5-vl-3b-llm", 3: "qwen2.5-vl-7b-llm"}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        return float(json.load(open(path))["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle samples of one GPU while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu):
+        self.gpu, self.rows, self.proc = gpu, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=3)
+            except Exception:
+                self.proc.kill()
+        sm = sorted(float(r[1]) for r in self.rows if len(r) >= 9 and r[1].replace(".", "").isdigit())
+        mx = [float(r[2]) for r in self.rows if len(r) >= 9 and r[2].replace(".", "").isdigit()]
+        reasons = set()
+        for r in self.rows:
+            if len(r) >= 9:
+                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def workload(cfg_id):
+    from oracle import synth
+    cfg = synth.CONFIGS[cfg_id]
+    prefix_n, prompt_n, steps, temp, top_p = synth.WORKLOADS[cfg_id]
+    ids = synth.make_token_ids(prefix_n + prompt_n, seed=0)
+    return cfg, ids[:prefix_n], ids, steps, temp, top_p
+
+
+def position_ids(cfg, n):
+    if cfg.mrope_section is None:
+        return None
+    return [list(range(n)) for _ in range(3)]
+
+
+# --------------------------------------------------------------------------------------------------
+def run_reference(args, rank):
+    """The reference has no CPU implementation of this path (it throws without CUDA), so this arm
+    times the CPU restatement (oracle, exact_fp32) on the host cores.  One step = a bounded sample:
+    `sample_tokens` decode steps at the workload's context length."""
+    if rank != 0:
+        return
+    import torch
+    from oracle import qwen_text, synth
+    cfg, prefix, ids, steps, temp, top_p = workload(args.config)
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    w = synth.make_weights(cfg, seed=0)
+    o = qwen_text.QwenTextOracle(cfg, w, "exact_fp32")
+    pos = position_ids(cfg, len(ids))
+    ctx = min(len(ids), args.ref_context)
+    with torch.no_grad():
+        o.forward(ids[:ctx], position_ids=None if pos is None else torch.tensor(pos)[:, :ctx])
+        sample_tokens = 2
+        tok = ids[-1]
+
+        def one_step():
+            n0 = o.kv_len
+            for i in range(sample_tokens):
+                p3 = None if pos is None else torch.full((3, 1), n0 + i)
+                o.forward([tok], position_ids=p3)
+            o.truncate(n0)
+        for _ in range(args.warmup):
+            one_step()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            one_step()
+        dt = time.perf_counter() - t0
+    value = args.steps * sample_tokens / dt
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"{NAMES[args.config]} decode at context {ctx} (CPU restatement of the reference path)"},
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
+                             "sample": f"{sample_tokens} decode steps per bench step at context {ctx}, fp32 torch-CPU"},
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------------------------------
+def cpu_baseline(cfg_id, budget_s=25.0):
+    import torch
+    from oracle import qwen_text, synth
+    cfg, prefix, ids, steps, temp, top_p = workload(cfg_id)
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    w = synth.make_weights(cfg, seed=0)
+    o = qwen_text.QwenTextOracle(cfg, w, "exact_fp32")
+    ctx = min(len(ids), 256)                      # bounded: a 256-token context instead of the full one
+    pos = position_ids(cfg, len(ids))
+    with torch.no_grad():
+        o.forward(ids[:ctx], position_ids=None if pos is None else torch.tensor(pos)[:, :ctx])
+        o.forward([ids[-1]], position_ids=None if pos is None else torch.full((3, 1), ctx))
+        n, t0 = 0, time.perf_counter()
+        while n < 64 and time.perf_counter() - t0 < budget_s / 2:
+            o.forward([ids[-1]], position_ids=None if pos is None else torch.full((3, 1), ctx + 1 + n))
+            n += 1
+        dt = time.perf_counter() - t0
+    return {"value": n / dt, "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": f"{n} decode steps at context {ctx} (fp32 torch-CPU restatement; the full workload runs at context "
+                      f"{len(ids)})"}
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch
+    import cabi
+    from oracle import synth
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    cfg, prefix, ids, gen_tokens, temp, top_p = workload(args.config)
+    if args.tokens:
+        gen_tokens = args.tokens
+    prompt_n = len(ids) - len(prefix)
+    max_tokens = len(ids) + gen_tokens + 8
+    pos = position_ids(cfg, len(ids))
+
+    t_setup = time.perf_counter()
+    w = synth.make_weights(cfg, seed=0)
+    be = cabi.Backend(cfg, max_prefill_tokens=min(2048, max_tokens), max_response_tokens=gen_tokens + 8, device_id=local_rank)
+    be.load_weights(w)
+    be.alloc_slot(0, max_tokens)
+    be.set_sampling(temp, top_p, 0)
+    if prefix:
+        be.prefill(0, prefix, kv_offset=0, pos3=None if pos is None else [r[:len(prefix)] for r in pos], sample=False)
+    be.capture_decode(0)
+    be.synchronize()
+
+    # public API engine for the end-to-end leg (weights travel through a safetensors checkpoint)
+    import edge_fm
+    tmp = tempfile.mkdtemp(prefix=f"efm_bench_{rank}_")
+    model_dir = synth.write_checkpoint(os.path.join(tmp, "model"), cfg, w)
+    name = "Qwen2.5-VL" if cfg.mrope_section is not None else "Qwen2.5"
+    eng_cfg = synth.write_engine_config(os.path.join(tmp, "engine.json"), model_dir, model_name=name, prefix_ids=prefix,
+                                        max_tokens=max_tokens, max_new_tokens=gen_tokens, temperature=temp, top_p=top_p,
+                                        seed=0, use_cuda_graph=True, device_id=local_rank)
+    del w
+    engine = edge_fm.EdgeFM(eng_cfg)
+    os.remove(os.path.join(model_dir, "model.safetensors"))
+    setup_s = time.perf_counter() - t_setup
+
+    suffix = ids[len(prefix):]
+    pos_suffix = None if pos is None else [r[len(prefix):] for r in pos]
+    mp = None if pos is None else [len(ids)] * 3
+
+    def one_request():
+        be.event_record(0)
+        be.prefill(0, suffix, kv_offset=len(prefix), pos3=pos_suffix, sample=True)
+        be.event_record(1)
+        be.decode_begin(0, len(ids), mp, 1)
+        be.decode_steps(gen_tokens - 1, True)
+        be.event_record(2)
+        be.synchronize()
+        return be.elapsed_ms(0, 1), be.elapsed_ms(1, 2)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        one_request()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    launches0 = be.launch_count()
+    barrier()
+    t0 = time.perf_counter()
+    pre_ms, dec_ms = 0.0, 0.0
+    for _ in range(args.steps):
+        a, b = one_request()
+        pre_ms += a
+        dec_ms += b
+    barrier()
+    wall_s = time.perf_counter() - t0
+    launches = be.launch_count() - launches0
+    tokens = be.read_tokens(0, gen_tokens)
+
+    # end to end through the public API: host ids in, host ids out
+    def e2e_request():
+        if pos is None:
+            req = edge_fm.Request(0, ids)
+        else:
+            pt = torch.tensor(pos, dtype=torch.int32)
+            dummy = torch.zeros(1, cfg.hidden, dtype=torch.bfloat16)
+            req = edge_fm.Request(0, ids, edge_fm.Tensor(dummy.data_ptr(), [1, cfg.hidden], edge_fm.DType.BFloat16, edge_fm.Device.CPU),
+                                  cfg.vocab + 100,
+                                  edge_fm.Tensor(pt.data_ptr(), [3, len(ids)], edge_fm.DType.Int32, edge_fm.Device.CPU), mp and [m - 1 for m in mp])
+        req.set_ignore_stop_tokens(True)
+        return list(engine.generate(req).token_ids())
+    for _ in range(max(1, args.warmup // 2)):
+        e2e_tokens = e2e_request()
+    barrier()
+    t1 = time.perf_counter()
+    for _ in range(args.steps):
+        e2e_tokens = e2e_request()
+    barrier()
+    e2e_s = time.perf_counter() - t1
+    clocks = sampler.stop()
+    m = engine.last_generate_metrics()
+
+    # per-kernel device time of a few un-overlapped steps (after the timed region)
+    be.decode_begin(0, len(ids), mp, 1)
+    breakdown = be.decode_breakdown(4)
+    step_bytes = be.decode_step_bytes(len(ids) + gen_tokens // 2)
+
+    dec_steps = args.steps * (gen_tokens - 1)
+    local = torch.tensor([dec_ms, pre_ms, wall_s, e2e_s], dtype=torch.float64, device="cuda")
+    if dist is not None:
+        dist.all_reduce(local, op=dist.ReduceOp.MAX)
+    dec_ms_max, pre_ms_max, wall_max, e2e_max = [float(x) for x in local.tolist()]
+    value = world * dec_steps / (dec_ms_max / 1e3)
+    e2e_value = world * args.steps * gen_tokens / e2e_max
+    step_ms = dec_ms_max / dec_steps
+    peak, peak_kind = peaks()
+    achieved = step_bytes / (step_ms * 1e-3) / 1e9
+    H, I, L = cfg.hidden, cfg.intermediate, cfg.num_layers
+    qd, kvd = cfg.q_heads * cfg.head_dim, cfg.kv_heads * cfg.head_dim
+    kbytes = {"qkv": (qd + 2 * kvd) * H * 2, "o_proj": H * qd * 2, "gate_up": 2 * I * H * 2, "down_proj": H * I * 2,
+              "lm_head": cfg.vocab * H * 2}
+    kernels = {}
+    for k, ms in breakdown.items():
+        n_launch = 4 * (L if k not in ("lm_head", "sampler") else 1)
+        us = ms / n_launch * 1e3
+        kernels[k] = {"us_per_launch": round(us, 2)}
+        if k in kbytes:
+            kernels[k]["gbs"] = round(kbytes[k] / (us * 1e-6) / 1e9, 1)
+            kernels[k]["frac"] = round(kbytes[k] / (us * 1e-6) / 1e9 / peak, 3)
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": (pre_ms_max + dec_ms_max) / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"{NAMES[args.config]}: {len(prefix)}-token resident prefix + {prompt_n}-token prompt, "
+                                   f"{gen_tokens} generated tokens, batch 1, temperature {temp}, top_p {top_p}",
+                       "parallelism": "single GPU" if world == 1 else f"{world} independent replicas",
+                       "l2_policy": "weights streamed per decode step exceed L2 (%.2f GB vs 126 MB)" % (step_bytes / 1e9),
+                       "cuda_graph": True},
+            "decode_ms_per_token": step_ms, "prefill_ms": pre_ms_max / args.steps,
+            "ttft_ms": pre_ms_max / args.steps, "wall_s": wall_max, "setup_s": setup_s,
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 4 * prompt_n + (12 * len(ids) if pos else 0),
+                    "d2h_bytes_per_step": 4 * gen_tokens + 32, "api": "edge_fm.EdgeFM.generate",
+                    "engine_decode_tok_s": m.get("decode_tokens_per_second"), "engine_prefill_ms": m.get("prefill_ms")},
+            "gpu_launches": launches,
+            "clocks": clocks,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "peak_kind": peak_kind, "launch": "one decode step (CUDA graph of %d kernels)" % (5 * L + 2),
+                         "bytes_per_launch": step_bytes, "us_per_launch": step_ms * 1e3, "kernels": kernels},
+            "tokens_head": tokens[:8], "e2e_tokens_equal": e2e_tokens == tokens,
+        }
+        if world == 1 and not args.no_cpu:
+            line["cpu_baseline"] = cpu_baseline(args.config)
+        print(json.dumps(line), flush=True)
+    be.close()
+    del engine
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", type=int, default=1, choices=[0, 1, 2, 3])
+    ap.add_argument("--tokens", type=int, default=0, help="override the number of generated tokens")
+    ap.add_argument("--ref-context", type=int, default=256, help="context length of the CPU arm's bounded sample")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else max(args.warmup, 1)
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -513,6 +513,40 @@ efm_status efm_b200_launch_count(efm_b200_ctx* c, int64_t* count) {
     return EFM_OK;
 }
 
+efm_status efm_b200_decode_breakdown(efm_b200_ctx* c, int32_t n_steps, float* ms_out) {
+    if (c == nullptr || ms_out == nullptr) return fail(c, EFM_ERR_INVALID_ARGUMENT, "null argument");
+    if (c->bound_slot < 0) return fail(c, EFM_ERR_STATE, "decode_begin has not been called");
+    KvSlot& s = c->slots[c->bound_slot];
+    EFM_CK(c, cudaSetDevice(c->device));
+    for (int i = 0; i < 7; ++i) ms_out[i] = 0.f;
+    const int per_step = 5 * c->d.num_layers + 2;
+    for (int step = 0; step < n_steps; ++step) {
+        std::vector<cudaEvent_t> ev;
+        Launcher L = make_launcher(c);
+        L.pdl = false;
+        L.trace = &ev;
+        cudaEvent_t first = nullptr;
+        EFM_CK(c, cudaEventCreate(&first));
+        EFM_CK(c, cudaEventRecord(first, c->stream));
+        qwen_decode_step(*c, s, L);
+        cudaError_t e = L.err != cudaSuccess ? L.err : cudaStreamSynchronize(c->stream);
+        if (e == cudaSuccess && (int)ev.size() == per_step) {
+            cudaEvent_t prev = first;
+            for (int i = 0; i < per_step; ++i) {
+                float ms = 0.f;
+                cudaEventElapsedTime(&ms, prev, ev[i]);
+                const int kind = i < 5 * c->d.num_layers ? i % 5 : 5 + (i - 5 * c->d.num_layers);
+                ms_out[kind] += ms;
+                prev = ev[i];
+            }
+        }
+        cudaEventDestroy(first);
+        for (cudaEvent_t x : ev) cudaEventDestroy(x);
+        if (e != cudaSuccess) return cuda_fail(c, e, "decode breakdown");
+    }
+    return EFM_OK;
+}
+
 efm_status efm_b200_decode_step_bytes(efm_b200_ctx* c, int32_t kv_len, int64_t* bytes) {
     if (c == nullptr || bytes == nullptr) return fail(c, EFM_ERR_INVALID_ARGUMENT, "null argument");
     const efm_model_desc& d = c->d;

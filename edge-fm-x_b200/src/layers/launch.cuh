@@ -6,6 +6,7 @@
 
 #include <algorithm>
 #include <cstdint>
+#include <vector>
 
 #include "../operators/decode_attention.cuh"
 #include "../operators/gemv.cuh"
@@ -17,6 +18,7 @@ struct Launcher {
     bool pdl = true;                 // programmatic stream serialization between consecutive kernels
     int64_t* counter = nullptr;
     cudaError_t err = cudaSuccess;   // first failure sticks
+    std::vector<cudaEvent_t>* trace = nullptr;   // when set: one event recorded after every launch
 
     template <typename... KArgs, typename... Args>
     void launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, Args&&... args) {
@@ -33,6 +35,10 @@ struct Launcher {
         cfg.numAttrs = pdl ? 1 : 0;
         err = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
         if (counter != nullptr) ++*counter;
+        if (trace != nullptr && err == cudaSuccess) {
+            cudaEvent_t ev = nullptr;
+            if (cudaEventCreate(&ev) == cudaSuccess) { cudaEventRecord(ev, stream); trace->push_back(ev); }
+        }
     }
 };
 

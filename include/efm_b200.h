@@ -155,6 +155,10 @@ EFM_API efm_status efm_b200_event_record(efm_b200_ctx* ctx, int32_t idx);
 EFM_API efm_status efm_b200_event_elapsed_ms(efm_b200_ctx* ctx, int32_t start_idx, int32_t stop_idx, float* ms);
 /* Kernels launched by this context since creation (graph replays count their nodes). */
 EFM_API efm_status efm_b200_launch_count(efm_b200_ctx* ctx, int64_t* count);
+/* Runs n_steps decode steps as plain launches (no graph, no dependent-launch overlap) with an
+ * event after every kernel and returns the summed device time per kernel kind in ms_out[7]:
+ * qkv, attention, o_proj, gate_up, down_proj, lm_head, sampler.  Advances the decode state. */
+EFM_API efm_status efm_b200_decode_breakdown(efm_b200_ctx* ctx, int32_t n_steps, float* ms_out);
 /* Bytes of weights / KV one decode step must stream at the given kv_len (roofline numerator). */
 EFM_API efm_status efm_b200_decode_step_bytes(efm_b200_ctx* ctx, int32_t kv_len, int64_t* bytes);
 

@@ -55,6 +55,7 @@ SIGNATURES = {
     "efm_b200_event_record": (I32, [P, I32]),
     "efm_b200_event_elapsed_ms": (I32, [P, I32, I32, C.POINTER(C.c_float)]),
     "efm_b200_launch_count": (I32, [P, C.POINTER(C.c_int64)]),
+    "efm_b200_decode_breakdown": (I32, [P, I32, C.POINTER(C.c_float)]),
     "efm_b200_decode_step_bytes": (I32, [P, I32, C.POINTER(C.c_int64)]),
     "efm_b200_op_gemv": (I32, [P, P, P, C.c_float, P, P, I32, I32]),
     "efm_b200_op_gemm": (I32, [P, P, P, P, I32, I32, I32]),
@@ -194,6 +195,11 @@ class Backend:
         n = C.c_int64()
         self.check(self.L.efm_b200_launch_count(self.ctx, C.byref(n)), "launch_count")
         return n.value
+
+    def decode_breakdown(self, n_steps):
+        out = (C.c_float * 7)()
+        self.check(self.L.efm_b200_decode_breakdown(self.ctx, n_steps, out), "decode_breakdown")
+        return dict(zip(("qkv", "attention", "o_proj", "gate_up", "down_proj", "lm_head", "sampler"), list(out)))
 
     def decode_step_bytes(self, kv_len):
         n = C.c_int64()

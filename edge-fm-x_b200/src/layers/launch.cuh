@@ -6,6 +6,7 @@
 
 #include <algorithm>
 #include <cstdint>
+#include <cstdlib>
 #include <vector>
 
 #include "../operators/decode_attention.cuh"
@@ -47,8 +48,17 @@ struct GemvPlan { int items, ksplit, grid; };
 // Cost model: a warp's serial work is (128-bit loads per lane) per wave plus a fixed reduce /
 // epilogue cost; pick the variant with the shortest critical path and size the grid so that
 // every row group slot gets the same number of waves.
+inline int gemv_ctas_per_sm() {
+    static const int v = [] {
+        const char* e = std::getenv("EFM_B200_GEMV_CTAS_PER_SM");     // tuning knob, 1 or 2
+        const int x = e != nullptr ? std::atoi(e) : 2;
+        return x == 1 ? 1 : 2;
+    }();
+    return v;
+}
+
 inline GemvPlan plan_gemv(int n_items, int K, int num_sms) {
-    const int max_ctas = 2 * num_sms;
+    const int max_ctas = gemv_ctas_per_sm() * num_sms;
     const int nch = K / 8;
     GemvPlan best{2, 1, max_ctas};
     long best_cost = -1;
@@ -89,24 +99,26 @@ inline void launch_gemv(Launcher& L, const GemvParams& p, int num_sms) {
 
 struct AttnPlan { int n_splits, chunk_cap; };
 inline AttnPlan plan_decode_attention(int max_tokens, int kv_heads, int num_sms) {
-    int n = (max_tokens + 31) / 32;
+    int n = (max_tokens + kAttnTile - 1) / kAttnTile;
     n = std::min(n, std::max(1, num_sms / std::max(1, kv_heads)));
-    n = std::max(1, std::min(n, 64));
+    n = std::max(1, std::min(n, kMaxSplits));
     return AttnPlan{n, (max_tokens + n - 1) / n};
+}
+
+// Opt-in shared-memory sizes; called once per device at set-up, never inside a stream capture.
+inline cudaError_t configure_decode_attention() {
+    cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)decode_attention_smem_bytes(128, 0));
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(decode_attention_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                (int)decode_attention_smem_bytes(64, 0));
 }
 
 inline void launch_decode_attention(Launcher& L, const DecodeAttnParams& p, int head_dim) {
     const size_t smem = decode_attention_smem_bytes(head_dim, p.chunk_cap);
-    const dim3 grid(p.n_splits, p.kv_heads), block(128);
-    if (head_dim == 128) {
-        if (smem > 48 * 1024)
-            cudaFuncSetAttribute(decode_attention_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        L.launch(decode_attention_kernel<128>, grid, block, smem, p);
-    } else {
-        if (smem > 48 * 1024)
-            cudaFuncSetAttribute(decode_attention_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        L.launch(decode_attention_kernel<64>, grid, block, smem, p);
-    }
+    const dim3 grid(p.n_splits, p.kv_heads), block(256);
+    if (head_dim == 128) L.launch(decode_attention_kernel<128>, grid, block, smem, p);
+    else L.launch(decode_attention_kernel<64>, grid, block, smem, p);
 }
 
 }  // namespace efm

@@ -3,20 +3,23 @@
 // (src/operators/attention_op.cu:1428-1466): split-KV, kv_len read from a device word so one
 // captured graph serves every step.  q arrives rotated and K is cached rotated, so no RoPE here.
 //
-// Grid (n_splits, kv_heads), 128 threads.  A block owns one contiguous chunk of cache rows of
-// one kv head and serves all `group` query heads that share it, so K and V are read once.
-//   1. scores: 4 threads per cache row, 128-bit loads, fp32 dot with q held in shared memory;
-//   2. chunk-local softmax statistics (max m, sum l) per query head, fp32;
-//   3. o = sum_t p_t * v_t with 8 channels per thread, reduced over the row groups;
-//   4. the (m, l, o) triple goes to scratch; the last block to finish for a kv head (atomic
-//      ticket, no spinning) merges all chunks and writes the bf16 output.
-// Bound: HBM (2 * kv_len * kv_heads * D * 2 bytes per layer), in practice launch/latency.
+// Grid (n_splits, kv_heads), 256 threads.  A block owns one contiguous chunk of cache rows of one
+// kv head and serves all `group` query heads that share it, so K and V are read once.  The chunk
+// is walked in tiles of 64 rows (normally exactly one tile):
+//   1. every thread issues its quarter-row of K and of V together (one DRAM round trip);
+//   2. scores against q (fp32, shared memory), tile max, p = exp(s - max), running (m, l);
+//   3. o += P.V from shared memory, 8 channels per thread, folded over the row groups;
+//   4. (m, l, o) go to scratch; the last block to finish for a kv head (atomic ticket, nobody
+//      spins) computes the merge weights once and folds all chunks with independent loads.
+// Bound: HBM (2 * kv_len * kv_heads * D * 2 bytes per layer); in practice latency.
 #pragma once
 #include "common.cuh"
 
 namespace efm {
 
 constexpr int kMaxGroup = 8;
+constexpr int kAttnTile = 64;
+constexpr int kMaxSplits = 64;
 
 struct DecodeAttnParams {
     const __nv_bfloat16* q;        // [q_heads, D]
@@ -33,18 +36,27 @@ struct DecodeAttnParams {
 };
 
 template <int D>
-__global__ void __launch_bounds__(128) decode_attention_kernel(const DecodeAttnParams p) {
-    constexpr int NT = 128;
-    constexpr int QV = D / 32;            // uint4 loads per thread and row in the score phase
-    constexpr int TPR = D / 8;            // threads per V row
+struct DecodeAttnSmem {
+    static constexpr int QP = D / 4 + 4;                    // padded quarter-row of q
+    float q[kMaxGroup][4][QP];
+    float ored[8][kMaxGroup][D];                            // per-warp partial outputs
+    float p[kMaxGroup][kAttnTile];
+    float wmax[8][kMaxGroup];
+    float wsum[8][kMaxGroup];
+    float run_m[kMaxGroup], run_l[kMaxGroup], rescale[kMaxGroup];
+    float mw[kMaxGroup][kMaxSplits];                        // merge weights
+    __nv_bfloat16 v[kAttnTile][D];
+    unsigned int ticket;
+};
+
+template <int D>
+__global__ void __launch_bounds__(256) decode_attention_kernel(const DecodeAttnParams p) {
+    constexpr int NT = 256;
+    constexpr int QV = D / 32;            // uint4 per thread and row (a quarter row)
+    constexpr int TPR = D / 8;            // threads per V row in the P.V phase
     constexpr int TG = NT / TPR;          // row groups in the P.V phase
     extern __shared__ __align__(16) unsigned char attn_smem[];
-    constexpr int QP = D / 4 + 4;         // padded quarter-row of q: the 4 threads of a row hit 4 banks
-    float* qs = reinterpret_cast<float*>(attn_smem);            // [kMaxGroup][4][QP]
-    float* ored = qs + kMaxGroup * 4 * QP;                       // [4][kMaxGroup][D]
-    float* ml = ored + 4 * kMaxGroup * D;                        // [kMaxGroup][2]
-    float* sc = ml + kMaxGroup * 2;                              // [kMaxGroup][chunk_cap]
-    __shared__ unsigned int ticket_s;
+    DecodeAttnSmem<D>& sm = *reinterpret_cast<DecodeAttnSmem<D>*>(attn_smem);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int split = blockIdx.x, kvh = blockIdx.y;
@@ -64,154 +76,205 @@ __global__ void __launch_bounds__(128) decode_attention_kernel(const DecodeAttnP
     n = n < 0 ? 0 : (n > chunk ? chunk : n);
     const size_t row_stride = (size_t)p.kv_heads * D;
 
+    const int tok = tid >> 2, part = tid & 3;                    // score phase: 4 threads per row
+    const int dpart = tid % TPR, tg = tid / TPR;                 // P.V phase
+    float acc[kMaxGroup][8];
+#pragma unroll
+    for (int g = 0; g < kMaxGroup; ++g)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[g][e] = 0.f;
+
     for (int i = tid; i < G * D; i += NT) {
         const int g = i / D, d = i - g * D;
-        qs[(g * 4 + d / (D / 4)) * QP + d % (D / 4)] = __bfloat162float(p.q[(size_t)(kvh * G) * D + i]);
+        sm.q[g][d / (D / 4)][d % (D / 4)] = __bfloat162float(p.q[(size_t)(kvh * G) * D + i]);
     }
-    __syncthreads();
+    if (tid < kMaxGroup) { sm.run_m[tid] = -INFINITY; sm.run_l[tid] = 0.f; }
 
-    // ---- 1. scores ------------------------------------------------------------------------
-    {
-        const int tsub = tid >> 2, part = tid & 3;
-        for (int t0 = 0; t0 < n; t0 += NT / 4) {
-            const int t = t0 + tsub;
-            float dot[kMaxGroup];
+    for (int t0 = 0; t0 < n; t0 += kAttnTile) {
+        const int nt = min(kAttnTile, n - t0);
+        const bool valid = tok < nt;
+        // ---- 1. K and V quarter rows in flight together -------------------------------------
+        uint4 kq[QV], vq[QV];
+        if (valid) {
+            const size_t off = (size_t)(start + t0 + tok) * row_stride + (size_t)kvh * D + part * (D / 4);
 #pragma unroll
-            for (int g = 0; g < kMaxGroup; ++g) dot[g] = 0.f;
-            if (t < n) {
-                const __nv_bfloat16* kr = p.k_cache + (size_t)(start + t) * row_stride + (size_t)kvh * D + part * (D / 4);
-                uint4 kvv[QV];
+            for (int j = 0; j < QV; ++j) kq[j] = ld_cached(p.k_cache + off + j * 8);
 #pragma unroll
-                for (int j = 0; j < QV; ++j) kvv[j] = ld_cached(kr + j * 8);
+            for (int j = 0; j < QV; ++j) vq[j] = ld_cached(p.v_cache + off + j * 8);
+        }
+        __syncthreads();      // q staged (first tile) / previous tile's p and v fully consumed
+        // ---- 2. scores ----------------------------------------------------------------------
+        float s[kMaxGroup];
 #pragma unroll
-                for (int j = 0; j < QV; ++j) {
-                    float kf[8];
-                    unpack8(kvv[j], kf);
+        for (int g = 0; g < kMaxGroup; ++g) s[g] = 0.f;
+        if (valid) {
 #pragma unroll
-                    for (int g = 0; g < kMaxGroup; ++g) {
-                        if (g < G) {
-                            const float* qg = qs + (g * 4 + part) * QP + j * 8;
+            for (int j = 0; j < QV; ++j) {
+                float kf[8];
+                unpack8(kq[j], kf);
 #pragma unroll
-                            for (int e = 0; e < 8; ++e) dot[g] = fmaf(kf[e], qg[e], dot[g]);
-                        }
+                for (int g = 0; g < kMaxGroup; ++g) {
+                    if (g < G) {
+                        const float* qg = &sm.q[g][part][j * 8];
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) s[g] = fmaf(kf[e], qg[e], s[g]);
                     }
                 }
             }
 #pragma unroll
-            for (int g = 0; g < kMaxGroup; ++g) {
-                dot[g] += __shfl_xor_sync(0xffffffffu, dot[g], 1);
-                dot[g] += __shfl_xor_sync(0xffffffffu, dot[g], 2);
-            }
-            if (t < n && part == 0) {
+            for (int j = 0; j < QV; ++j)
+                *reinterpret_cast<uint4*>(&sm.v[tok][part * (D / 4) + j * 8]) = vq[j];
+        }
 #pragma unroll
-                for (int g = 0; g < kMaxGroup; ++g)
-                    if (g < G) sc[g * p.chunk_cap + t] = dot[g] * p.scale;
+        for (int g = 0; g < kMaxGroup; ++g) {
+            s[g] += __shfl_xor_sync(0xffffffffu, s[g], 1);
+            s[g] += __shfl_xor_sync(0xffffffffu, s[g], 2);
+            s[g] = valid ? s[g] * p.scale : -INFINITY;
+            float m = s[g];
+            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 4));
+            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 8));
+            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 16));
+            if (lane == 0) sm.wmax[warp][g] = m;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int g = 0; g < kMaxGroup; ++g) {
+            if (g < G) {
+                float m_new = sm.run_m[g];
+#pragma unroll
+                for (int w = 0; w < 8; ++w) m_new = fmaxf(m_new, sm.wmax[w][g]);
+                const float pv = valid ? expf(s[g] - m_new) : 0.f;
+                if (part == 0 && tok < kAttnTile) sm.p[g][tok] = pv;
+                float ps = pv;
+                ps += __shfl_xor_sync(0xffffffffu, ps, 4);
+                ps += __shfl_xor_sync(0xffffffffu, ps, 8);
+                ps += __shfl_xor_sync(0xffffffffu, ps, 16);
+                if (lane == 0) sm.wsum[warp][g] = ps;
+                if (tid == 0) sm.rescale[g] = m_new;      // new running max (read after the barrier)
             }
         }
-    }
-    __syncthreads();
-
-    // ---- 2. chunk-local softmax ---------------------------------------------------------------
-    for (int g = warp; g < G; g += 4) {
-        float m = -INFINITY;
-        for (int t = lane; t < n; t += 32) m = fmaxf(m, sc[g * p.chunk_cap + t]);
-        m = warp_max(m);
-        float l = 0.f;
-        for (int t = lane; t < n; t += 32) {
-            const float e = expf(sc[g * p.chunk_cap + t] - m);
-            sc[g * p.chunk_cap + t] = e;
-            l += e;
+        __syncthreads();
+        // ---- 3. o = o * rescale + P.V -----------------------------------------------------------
+#pragma unroll
+        for (int g = 0; g < kMaxGroup; ++g) {
+            if (g < G) {
+                const float m_old = sm.run_m[g], m_new = sm.rescale[g];
+                const float f = m_old == -INFINITY ? 0.f : expf(m_old - m_new);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) acc[g][e] *= f;
+            }
         }
-        l = warp_sum(l);
-        if (lane == 0) { ml[g * 2] = m; ml[g * 2 + 1] = l; }
-    }
-    __syncthreads();
-
-    // ---- 3. o = P.V ------------------------------------------------------------------------------
-    {
-        const int dpart = tid % TPR, tg = tid / TPR;
-        float acc[kMaxGroup][8];
-#pragma unroll
-        for (int g = 0; g < kMaxGroup; ++g)
-#pragma unroll
-            for (int e = 0; e < 8; ++e) acc[g][e] = 0.f;
-        for (int t = tg; t < n; t += TG) {
-            const uint4 vv = ld_cached(p.v_cache + (size_t)(start + t) * row_stride + (size_t)kvh * D + dpart * 8);
+        for (int t = tg; t < nt; t += TG) {
             float vf[8];
-            unpack8(vv, vf);
+            unpack8(*reinterpret_cast<const uint4*>(&sm.v[t][dpart * 8]), vf);
 #pragma unroll
             for (int g = 0; g < kMaxGroup; ++g) {
                 if (g < G) {
-                    const float pg = sc[g * p.chunk_cap + t];
+                    const float pg = sm.p[g][t];
 #pragma unroll
                     for (int e = 0; e < 8; ++e) acc[g][e] = fmaf(pg, vf[e], acc[g][e]);
                 }
             }
         }
-        // fold the row groups that live in the same warp, then the four warps
+        __syncthreads();      // everyone has read run_m / rescale / wsum inputs of this tile
+        if (tid < G) {
+            const float m_old = sm.run_m[tid], m_new = sm.rescale[tid];
+            float l = sm.run_l[tid] * (m_old == -INFINITY ? 0.f : expf(m_old - m_new));
+#pragma unroll
+            for (int w = 0; w < 8; ++w) l += sm.wsum[w][tid];
+            sm.run_l[tid] = l;
+            sm.run_m[tid] = m_new;
+        }
+    }
+
+    // ---- fold the row groups: lanes of a warp first, then the eight warps -----------------------
+#pragma unroll
+    for (int g = 0; g < kMaxGroup; ++g)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            float v = acc[g][e];
+#pragma unroll
+            for (int o = TPR; o < 32; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            acc[g][e] = v;
+        }
+    if (lane < TPR) {
 #pragma unroll
         for (int g = 0; g < kMaxGroup; ++g)
+            if (g < G) {
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                float v = acc[g][e];
-#pragma unroll
-                for (int o = TPR; o < 32; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-                acc[g][e] = v;
+                for (int e = 0; e < 8; ++e) sm.ored[warp][g][lane * 8 + e] = acc[g][e];
             }
-        if (lane < TPR) {
-#pragma unroll
-            for (int g = 0; g < kMaxGroup; ++g)
-                if (g < G) {
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) ored[(warp * kMaxGroup + g) * D + lane * 8 + e] = acc[g][e];
-                }
-        }
     }
     __syncthreads();
 
-    // ---- 4. publish the partial, merge if last ---------------------------------------------------
+    // ---- 4. publish the partial, merge if last -------------------------------------------------
     for (int i = tid; i < G * D; i += NT) {
         const int g = i / D, d = i - g * D;
-        const float o = ored[(0 * kMaxGroup + g) * D + d] + ored[(1 * kMaxGroup + g) * D + d] +
-                        ored[(2 * kMaxGroup + g) * D + d] + ored[(3 * kMaxGroup + g) * D + d];
-        const int qh = kvh * G + g;
-        p.part_o[((size_t)qh * p.n_splits + split) * D + d] = o;
+        float o = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) o += sm.ored[w][g][d];
+        p.part_o[((size_t)(kvh * G + g) * p.n_splits + split) * D + d] = o;
     }
     if (tid < G) {
         const int qh = kvh * G + tid;
-        float m = ml[tid * 2], l = ml[tid * 2 + 1];
-        if (n == 0) { m = -INFINITY; l = 0.f; }
-        p.part_ml[((size_t)qh * p.n_splits + split) * 2] = m;
-        p.part_ml[((size_t)qh * p.n_splits + split) * 2 + 1] = l;
+        p.part_ml[((size_t)qh * p.n_splits + split) * 2] = sm.run_m[tid];
+        p.part_ml[((size_t)qh * p.n_splits + split) * 2 + 1] = sm.run_l[tid];
     }
     __threadfence();
     __syncthreads();
-    if (tid == 0) ticket_s = atomicAdd(&p.counters[kvh], 1u);
+    if (tid == 0) sm.ticket = atomicAdd(&p.counters[kvh], 1u);
     __syncthreads();
-    if (ticket_s != (unsigned)(p.n_splits - 1)) return;
+    if (sm.ticket != (unsigned)(p.n_splits - 1)) return;
     __threadfence();
+    // merge weights: warp g handles query head g, lanes over chunks
+    for (int g = warp; g < G; g += 8) {
+        const float* mlp = p.part_ml + (size_t)(kvh * G + g) * p.n_splits * 2;
+        float ms[kMaxSplits / 32], ls[kMaxSplits / 32];
+        float M = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < kMaxSplits / 32; ++j) {
+            const int s = lane + j * 32;
+            ms[j] = s < p.n_splits ? __ldcg(mlp + s * 2) : -INFINITY;
+            ls[j] = s < p.n_splits ? __ldcg(mlp + s * 2 + 1) : 0.f;
+            M = fmaxf(M, ms[j]);
+        }
+        M = warp_max(M);
+        float L = 0.f, w[kMaxSplits / 32];
+#pragma unroll
+        for (int j = 0; j < kMaxSplits / 32; ++j) {
+            w[j] = ls[j] > 0.f ? expf(ms[j] - M) : 0.f;
+            L = fmaf(ls[j], w[j], L);
+        }
+        L = warp_sum(L);
+        const float inv = L > 0.f ? 1.0f / L : 0.f;
+#pragma unroll
+        for (int j = 0; j < kMaxSplits / 32; ++j) {
+            const int s = lane + j * 32;
+            if (s < p.n_splits) sm.mw[g][s] = w[j] * inv;
+        }
+    }
+    __syncthreads();
     for (int i = tid; i < G * D; i += NT) {
         const int g = i / D, d = i - g * D;
-        const int qh = kvh * G + g;
-        const float* mlp = p.part_ml + (size_t)qh * p.n_splits * 2;
-        float M = -INFINITY;
-        for (int s = 0; s < p.n_splits; ++s) M = fmaxf(M, __ldcg(mlp + s * 2));
-        float L = 0.f, O = 0.f;
-        for (int s = 0; s < p.n_splits; ++s) {
-            const float ms = __ldcg(mlp + s * 2), ls = __ldcg(mlp + s * 2 + 1);
-            if (ls > 0.f) {
-                const float w = expf(ms - M);
-                L = fmaf(ls, w, L);
-                O = fmaf(__ldcg(p.part_o + ((size_t)qh * p.n_splits + s) * D + d), w, O);
-            }
+        const float* po = p.part_o + (size_t)(kvh * G + g) * p.n_splits * D + d;
+        float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+        int s = 0;
+        for (; s + 4 <= p.n_splits; s += 4) {
+            const float a = __ldcg(po + (size_t)s * D), b = __ldcg(po + (size_t)(s + 1) * D);
+            const float c = __ldcg(po + (size_t)(s + 2) * D), e = __ldcg(po + (size_t)(s + 3) * D);
+            o0 = fmaf(a, sm.mw[g][s], o0);
+            o1 = fmaf(b, sm.mw[g][s + 1], o1);
+            o2 = fmaf(c, sm.mw[g][s + 2], o2);
+            o3 = fmaf(e, sm.mw[g][s + 3], o3);
         }
-        p.out[(size_t)qh * D + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+        for (; s < p.n_splits; ++s) o0 = fmaf(__ldcg(po + (size_t)s * D), sm.mw[g][s], o0);
+        p.out[(size_t)(kvh * G + g) * D + d] = __float2bfloat16_rn((o0 + o1) + (o2 + o3));
     }
     if (tid == 0) p.counters[kvh] = 0u;
 }
 
-inline size_t decode_attention_smem_bytes(int D, int chunk_cap) {
-    return (size_t)(kMaxGroup * 4 * (D / 4 + 4) + 4 * kMaxGroup * D + kMaxGroup * 2 + kMaxGroup * chunk_cap) * sizeof(float);
+inline size_t decode_attention_smem_bytes(int D, int /*chunk_cap*/) {
+    return D == 128 ? sizeof(DecodeAttnSmem<128>) : sizeof(DecodeAttnSmem<64>);
 }
 
 }  // namespace efm

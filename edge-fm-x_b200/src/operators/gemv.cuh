@@ -135,8 +135,10 @@ template <Epi EPI, int ITEMS, int KSPLIT>
 __global__ void __launch_bounds__(256, 2) gemv_kernel(const GemvParams p) {
     constexpr int ROWS = ITEMS * 2, U = 8 / ITEMS, GP = 8 / KSPLIT;
     extern __shared__ __align__(16) unsigned char gemv_smem[];
-    __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(gemv_smem);
-    float* red = reinterpret_cast<float*>(gemv_smem + (((size_t)p.K * 2 + 15) & ~(size_t)15));  // [2][8][ROWS]
+    const size_t xbytes = ((size_t)p.K * 2 + 15) & ~(size_t)15;
+    __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(gemv_smem);                 // activations [K]
+    __nv_bfloat16* gs = reinterpret_cast<__nv_bfloat16*>(gemv_smem + xbytes);        // norm weight [K]
+    float* red = reinterpret_cast<float*>(gemv_smem + 2 * xbytes);                    // [2][8][ROWS]
     float* misc = red + 2 * 8 * ROWS;                                                            // [16]
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -175,6 +177,9 @@ __global__ void __launch_bounds__(256, 2) gemv_kernel(const GemvParams p) {
     // this one is resident, then prefetch (independent of every earlier kernel), then wait.
     pdl_launch_dependents();
     if (ig < n_ig) { set_rows(ig); load_batch(0); }
+    if (p.prologue != kProPlain)          // the norm weight is a weight too: stage it before waiting
+        for (int c = tid; c < nch; c += 256)
+            reinterpret_cast<uint4*>(gs)[c] = ld_cached(p.norm_w + (size_t)c * 8);
     pdl_wait();
 
     // ---- prologue: stage the activation vector in shared memory -------------------------
@@ -208,7 +213,7 @@ __global__ void __launch_bounds__(256, 2) gemv_kernel(const GemvParams p) {
         const float inv = 1.0f / sqrtf(tot / (float)p.K + p.eps);
         for (int c = tid; c < nch; c += 256) {
             uint4 v = zero ? make_uint4(0, 0, 0, 0) : ld_cached(src + (size_t)c * 8);
-            uint4 g = ld_cached(p.norm_w + (size_t)c * 8);
+            const uint4 g = reinterpret_cast<const uint4*>(gs)[c];      // written by this same thread
             float f[8], w[8];
             unpack8(v, f);
             unpack8(g, w);
@@ -300,7 +305,7 @@ __global__ void __launch_bounds__(256, 2) gemv_kernel(const GemvParams p) {
 }
 
 inline size_t gemv_smem_bytes(int K, int items) {
-    return (((size_t)K * 2 + 15) & ~(size_t)15) + (size_t)(2 * 8 * items * 2 + 16) * sizeof(float);
+    return 2 * (((size_t)K * 2 + 15) & ~(size_t)15) + (size_t)(2 * 8 * items * 2 + 16) * sizeof(float);
 }
 
 }  // namespace efm

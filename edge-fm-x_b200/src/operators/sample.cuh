@@ -18,8 +18,9 @@
 //            else reject it (which also rules out everything after it in the order).
 // Accepted tokens are distributed exactly as nucleus sampling; a round succeeds with
 // probability >= top_p, so 1-2 rounds are typical.  Integer mass makes the result independent
-// of thread count and summation order.  One block of 1024 threads; the logits (<= 0.6 MB) are
-// L2-resident when this runs.
+// of thread count and summation order.  One block of 1024 threads; each warp owns a contiguous
+// id segment and reads it 4 ids per lane, so every pass over the vocabulary is coalesced; the
+// logits (<= 0.6 MB) are L2-resident when this runs.
 #pragma once
 #include "common.cuh"
 
@@ -86,9 +87,25 @@ __device__ __forceinline__ unsigned long long block_scan_u64(unsigned long long 
     return v;
 }
 
+// four 128-id strides of integer weights for one lane (ids past `hi` read as 0)
+__device__ __forceinline__ void load_weights16(const uint32_t* wbuf, int base0, int hi, bool vec_ok, unsigned int (&w)[4][4]) {
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const int base = base0 + u * 128;
+        if (vec_ok && base < hi) {
+            const uint4 v = *reinterpret_cast<const uint4*>(wbuf + base);
+            w[u][0] = v.x; w[u][1] = v.y; w[u][2] = v.z; w[u][3] = v.w;
+        } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) w[u][e] = (!vec_ok && base + e < hi) ? wbuf[base + e] : 0u;
+        }
+    }
+}
+
 __global__ void __launch_bounds__(1024) sample_kernel(const SampleParams p) {
     constexpr int NT = 1024;
     __shared__ unsigned long long scan_tmp[33];
+    __shared__ unsigned long long seg_mass[32];
     __shared__ float rv[32];
     __shared__ int ri[32];
     __shared__ unsigned int sel_w;
@@ -143,54 +160,125 @@ __global__ void __launch_bounds__(1024) sample_kernel(const SampleParams p) {
         double top_p = (double)p.top_p;
         top_p = top_p > 1.0 ? 1.0 : (top_p < 1e-9 ? 1e-9 : top_p);
         const uint32_t step = p.state != nullptr ? (uint32_t)p.state->step : p.rng_step;
-        const int per = (p.vocab + NT - 1) / NT;          // contiguous id slice per thread
-        const int lo = min(p.vocab, tid * per), hi = min(p.vocab, lo + per);
-        // integer weights
-        for (int i = lo; i < hi; ++i) {
-            const float s = expf((p.logits[i] - M) * inv_t) * 2147483648.0f;
-            p.wbuf[i] = s >= 2147483648.0f ? 0x7fffffffu : (unsigned int)s;   // NaN -> 0
+        // Each warp owns one contiguous id segment (a multiple of 128 ids) and walks it 128 ids at a
+        // time, 4 consecutive ids per lane: every pass over the vocabulary is coalesced.
+        const int seg = ((p.vocab + 32 * 128 - 1) / (32 * 128)) * 128;
+        const int seg_lo = min(p.vocab, warp * seg), seg_hi = min(p.vocab, seg_lo + seg);
+        const bool vec_ok = (p.vocab & 3) == 0;
+
+        // pass 0: integer weights (four 128-id strides per trip so that the loads overlap)
+        for (int base0 = seg_lo + lane * 4; base0 < seg_hi; base0 += 512) {
+            float lg[4][4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int base = base0 + u * 128;
+                if (vec_ok && base < seg_hi) {
+                    const float4 v = *reinterpret_cast<const float4*>(p.logits + base);
+                    lg[u][0] = v.x; lg[u][1] = v.y; lg[u][2] = v.z; lg[u][3] = v.w;
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) lg[u][e] = base + e < seg_hi ? p.logits[base + e] : -INFINITY;
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int base = base0 + u * 128;
+                unsigned int w4[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float s = expf((lg[u][e] - M) * inv_t) * 2147483648.0f;
+                    w4[e] = s >= 2147483648.0f ? 0x7fffffffu : (unsigned int)s;   // NaN -> 0
+                }
+                if (vec_ok) { if (base < seg_hi) *reinterpret_cast<uint4*>(p.wbuf + base) = make_uint4(w4[0], w4[1], w4[2], w4[3]); }
+                else {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) if (base + e < seg_hi) p.wbuf[base + e] = w4[e];
+                }
+            }
         }
+        __syncthreads();
+
         unsigned int piv_w = 0u;          // last rejected token (w, id); none yet
         int piv_id = -1;
         double target = 0.0;
         bool accepted = false;
 #pragma unroll 1
         for (uint32_t round = 0; round < 32u && !accepted; ++round) {
-            // candidate mass of this thread's slice
+            // (a) candidate mass per segment
             unsigned long long mass = 0ull;
-            for (int i = lo; i < hi; ++i) {
-                const unsigned int w = p.wbuf[i];
-                const bool cand = piv_id < 0 ? (w > 0u) : (w > piv_w || (w == piv_w && i < piv_id));
-                if (cand) mass += w;
+            for (int base0 = seg_lo + lane * 4; base0 < seg_hi; base0 += 512) {
+                unsigned int w4[4][4];
+                load_weights16(p.wbuf, base0, seg_hi, vec_ok, w4);
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int i = base0 + u * 128 + e;
+                        const bool cand = piv_id < 0 ? true : (w4[u][e] > piv_w || (w4[u][e] == piv_w && i < piv_id));
+                        if (cand) mass += w4[u][e];
+                    }
             }
-            unsigned long long Wc;
-            const unsigned long long incl = block_scan_u64(mass, scan_tmp, &Wc);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) mass += __shfl_xor_sync(0xffffffffu, mass, o);
+            if (lane == 0) seg_mass[warp] = mass;
+            __syncthreads();
+            // (b) owner segment of r
+            unsigned long long Wc = 0ull;
+            for (int w = 0; w < 32; ++w) Wc += seg_mass[w];
             if (round == 0) target = (double)Wc * top_p;
             if (Wc == 0ull) break;
             const uint32_t x = philox4x32_10_first(step, round, (uint32_t)(p.seed & 0xffffffffull),
                                                    (uint32_t)(p.seed >> 32));
             const unsigned long long r =
                 __double2ull_rd(__dmul_rn(__dmul_rn((double)x, (double)Wc), 2.3283064365386963e-10));
-            const unsigned long long excl = incl - mass;
+            int ow = 0;
+            unsigned long long before_seg = 0ull;
+            for (int w = 0; w < 32; ++w) {
+                if (r >= before_seg + seg_mass[w]) before_seg += seg_mass[w]; else { ow = w; break; }
+            }
+            // (c) inside the owner segment: a few consecutive ids per thread, exact block scan
+            const int olo = min(p.vocab, ow * seg), ohi = min(p.vocab, olo + seg);
+            const int per = (ohi - olo + NT - 1) / NT;
+            const int lo = min(ohi, olo + tid * per), hi = min(ohi, lo + per);
+            unsigned long long m2 = 0ull;
+            for (int i = lo; i < hi; ++i) {
+                const unsigned int w = p.wbuf[i];
+                if (piv_id < 0 || w > piv_w || (w == piv_w && i < piv_id)) m2 += w;
+            }
+            unsigned long long tot2;
+            const unsigned long long incl = block_scan_u64(m2, scan_tmp, &tot2) + before_seg;
+            const unsigned long long excl = incl - m2;
             if (excl <= r && r < incl) {
                 unsigned long long run = excl;
                 for (int i = lo; i < hi; ++i) {
                     const unsigned int w = p.wbuf[i];
-                    const bool cand = piv_id < 0 ? (w > 0u) : (w > piv_w || (w == piv_w && i < piv_id));
-                    if (cand) { run += w; if (run > r) { sel_id = i; sel_w = w; break; } }
+                    if (piv_id < 0 || w > piv_w || (w == piv_w && i < piv_id)) {
+                        run += w;
+                        if (run > r) { sel_id = i; sel_w = w; break; }
+                    }
                 }
             }
             __syncthreads();
             const int j = sel_id;
             const unsigned int wj = sel_w;
-            // mass strictly before j in (w desc, id asc) order
+            // (d) mass strictly before j in (w desc, id asc) order
             unsigned long long before = 0ull;
-            for (int i = lo; i < hi; ++i) {
-                const unsigned int w = p.wbuf[i];
-                if (w > wj || (w == wj && i < j)) before += w;
+            for (int base0 = seg_lo + lane * 4; base0 < seg_hi; base0 += 512) {
+                unsigned int w4[4][4];
+                load_weights16(p.wbuf, base0, seg_hi, vec_ok, w4);
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                        if (w4[u][e] > wj || (w4[u][e] == wj && base0 + u * 128 + e < j)) before += w4[u][e];
             }
-            unsigned long long E;
-            block_scan_u64(before, scan_tmp, &E);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) before += __shfl_xor_sync(0xffffffffu, before, o);
+            __syncthreads();                       // seg_mass of step (a) fully consumed
+            if (lane == 0) seg_mass[warp] = before;
+            __syncthreads();
+            unsigned long long E = 0ull;
+            for (int w = 0; w < 32; ++w) E += seg_mass[w];
             if ((double)E < target) { accepted = true; token = j; }
             else { piv_w = wj; piv_id = j; }
             __syncthreads();

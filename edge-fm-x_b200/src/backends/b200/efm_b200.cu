@@ -636,6 +636,63 @@ efm_status efm_b200_op_decode_attention(const void* q, const void* k_cache, cons
     return st;
 }
 
+// ---- decode attention without any allocation -------------------------------------------------
+// Scratch for the split-KV partials lives in the library image.  In host code the symbol below is
+// only a stand-in for the device array: its device address has to be asked for, per device.
+namespace {
+constexpr int kNoAllocMaxQD = 4096;       // q_heads * head_dim
+constexpr int kNoAllocMaxKvHeads = 16;
+constexpr int kNoAllocMaxQHeads = 64;     // head_dim >= 64
+// layout in 32-bit words: partial outputs [q_heads][n_splits][D] | (max, sum) pairs
+// [q_heads][n_splits][2] | block tickets [kv_heads] (these must read zero when a launch starts)
+constexpr size_t kNoAllocPartO = (size_t)kNoAllocMaxQD * kMaxSplits;
+constexpr size_t kNoAllocPartMl = (size_t)kNoAllocMaxQHeads * kMaxSplits * 2;
+constexpr size_t kNoAllocWords = kNoAllocPartO + kNoAllocPartMl + kNoAllocMaxKvHeads;     // ~1.06 MB
+static __device__ __align__(256) float g_noalloc_scratch[kNoAllocWords];
+constexpr int kNoAllocMaxDevices = 64;
+float* g_noalloc_ptr[kNoAllocMaxDevices] = {};
+}  // namespace
+
+efm_status efm_b200_op_decode_attention_noalloc(const void* q, const void* k_cache, const void* v_cache, void* out_bf16,
+                                                int32_t q_heads, int32_t kv_heads, int32_t head_dim, int32_t kv_len,
+                                                int32_t max_tokens) {
+    int sms = 148;
+    efm_status st = op_prepare(&sms);
+    if (st != EFM_OK) return st;
+    if (q == nullptr || k_cache == nullptr || v_cache == nullptr || out_bf16 == nullptr || kv_heads <= 0 || q_heads % kv_heads ||
+        q_heads / kv_heads > kMaxGroup || (head_dim != 64 && head_dim != 128) || kv_len <= 0 || kv_len > max_tokens)
+        return fail(nullptr, EFM_ERR_INVALID_ARGUMENT, "op_decode_attention_noalloc: bad arguments");
+    if (q_heads * head_dim > kNoAllocMaxQD || kv_heads > kNoAllocMaxKvHeads || q_heads > kNoAllocMaxQHeads)
+        return fail(nullptr, EFM_ERR_UNSUPPORTED,
+                    "op_decode_attention_noalloc: shape exceeds the built-in scratch (q_heads * head_dim <= 4096, "
+                    "kv_heads <= 16); use efm_b200_op_decode_attention");
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(nullptr, e, "cudaGetDevice");
+    if (dev < 0 || dev >= kNoAllocMaxDevices) return fail(nullptr, EFM_ERR_UNSUPPORTED, "device index above 63");
+    if (g_noalloc_ptr[dev] == nullptr) {      // once per device, with that device current
+        float* ptr = nullptr;
+        e = cudaGetSymbolAddress((void**)&ptr, g_noalloc_scratch);
+        if (e != cudaSuccess || ptr == nullptr) return cuda_fail(nullptr, e, "cudaGetSymbolAddress(scratch)");
+        g_noalloc_ptr[dev] = ptr;
+    }
+    float* scratch = g_noalloc_ptr[dev];
+    unsigned int* tickets = reinterpret_cast<unsigned int*>(scratch + kNoAllocPartO + kNoAllocPartMl);
+    const AttnPlan plan = plan_decode_attention(max_tokens, kv_heads, sms);
+    e = cudaMemsetAsync(tickets, 0, kNoAllocMaxKvHeads * sizeof(unsigned int), nullptr);
+    if (e != cudaSuccess) return cuda_fail(nullptr, e, "clearing the scratch tickets");
+    DecodeAttnParams a{};
+    a.q = (const __nv_bfloat16*)q; a.k_cache = (const __nv_bfloat16*)k_cache; a.v_cache = (const __nv_bfloat16*)v_cache;
+    a.out = (__nv_bfloat16*)out_bf16; a.state = nullptr; a.kv_len_static = kv_len;
+    a.q_heads = q_heads; a.kv_heads = kv_heads; a.group = q_heads / kv_heads;
+    a.n_splits = plan.n_splits; a.chunk_cap = plan.chunk_cap; a.max_tokens = max_tokens;
+    a.scale = 1.0f / sqrtf((float)head_dim);
+    a.part_o = scratch; a.part_ml = scratch + kNoAllocPartO; a.counters = tickets;
+    Launcher L; L.pdl = false;
+    launch_decode_attention(L, a, head_dim);
+    return op_finish(L);
+}
+
 efm_status efm_b200_op_prefill_attention(const void* q, const void* k_cache, const void* v_cache, void* out_bf16, int32_t s,
                                          int32_t kv_offset, int32_t q_heads, int32_t kv_heads, int32_t head_dim) {
     efm_status st = op_prepare(nullptr);

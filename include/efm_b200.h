@@ -177,6 +177,26 @@ EFM_API efm_status efm_b200_op_gemm(const void* x, const void* w, const void* bi
 EFM_API efm_status efm_b200_op_decode_attention(const void* q, const void* k_cache, const void* v_cache,
                                                 void* out_bf16, int32_t q_heads, int32_t kv_heads,
                                                 int32_t head_dim, int32_t kv_len, int32_t max_tokens);
+/* Same computation and arguments as efm_b200_op_decode_attention, for callers that must not
+ * allocate device memory.  (No counterpart in the reference, whose attention call sizes a 32 MB
+ * workspace itself.)  Some hosts of this library cannot call cudaMalloc at the point where they
+ * need attention: a real-time control loop that promised its integrator a fixed memory footprint,
+ * a plugin running inside another runtime's memory pool or inside a region where that runtime
+ * forbids allocation, a process whose device memory was pre-partitioned at start-up.  This entry
+ * point therefore keeps the split-KV scratch (partial outputs, softmax statistics, block tickets)
+ * in a fixed array that is part of the library image: about 1 MB on every GPU that loads the
+ * library, held until the process exits.  It calls no cudaMalloc / cudaFree and no allocating
+ * library routine.
+ * Limits: q_heads * head_dim <= 4096 and kv_heads <= 16; larger shapes are refused with
+ * EFM_ERR_UNSUPPORTED (use efm_b200_op_decode_attention for those).
+ * The first call on each device looks up the device address of that array (with that device
+ * current) and caches it; make that first call before starting any stream capture.
+ * All calls share the one array and it keeps whatever the previous call left in it (the tickets
+ * are re-zeroed at the start of every call): two calls whose kernels overlap on the GPU race on
+ * it, so issue them one after the other.  Runs on the default stream and returns when done. */
+EFM_API efm_status efm_b200_op_decode_attention_noalloc(const void* q, const void* k_cache, const void* v_cache,
+                                                        void* out_bf16, int32_t q_heads, int32_t kv_heads,
+                                                        int32_t head_dim, int32_t kv_len, int32_t max_tokens);
 /* Causal GQA prefill attention, queries at cache rows [kv_offset, kv_offset+s)
  * (attention_op.cu:1221-1343).  q: [s, q_heads, D] bf16. */
 EFM_API efm_status efm_b200_op_prefill_attention(const void* q, const void* k_cache, const void* v_cache,

@@ -60,6 +60,7 @@ SIGNATURES = {
     "efm_b200_op_gemv": (I32, [P, P, P, C.c_float, P, P, I32, I32]),
     "efm_b200_op_gemm": (I32, [P, P, P, P, I32, I32, I32]),
     "efm_b200_op_decode_attention": (I32, [P, P, P, P, I32, I32, I32, I32, I32]),
+    "efm_b200_op_decode_attention_noalloc": (I32, [P, P, P, P, I32, I32, I32, I32, I32]),
     "efm_b200_op_prefill_attention": (I32, [P, P, P, P, I32, I32, I32, I32, I32]),
     "efm_b200_op_sample": (I32, [C.POINTER(C.c_float), I32, C.POINTER(Sampling), C.c_uint32, C.POINTER(I32)]),
 }

@@ -34,6 +34,7 @@ struct KvSlot {
     cudaGraphExec_t graph = nullptr;      // decode step captured against this slot's pointers
     int graph_nodes = 0;
     int n_splits = 1, chunk_cap = 1;
+    void* mega_layers = nullptr;          // device array of per-layer pointers for the persistent decode kernel
 };
 
 }  // namespace efm
@@ -45,6 +46,9 @@ struct efm_b200_ctx {
     std::string error;
     bool finalized = false;
     bool pdl = true;
+    bool mega = true;                     // decode step as one persistent cooperative kernel
+    unsigned int* mega_barrier = nullptr; // [2] grid-barrier counters + [1] abort flag
+    unsigned long long* mega_timing = nullptr;   // [5L + 2] phase stamps (debug breakdown)
 
     // weights
     __nv_bfloat16* embed = nullptr;       // [V, H]

@@ -124,6 +124,10 @@ efm_status efm_b200_create(const efm_model_desc* desc, int32_t device_id, int32_
     c->tp_rank = tp_rank;
     c->tp_size = tp_size;
     c->pdl = std::getenv("EFM_B200_NO_PDL") == nullptr;
+    {   // decode step form: "1" = one persistent cooperative kernel, "0" = one launch per phase
+        const char* m = std::getenv("EFM_B200_MEGA");
+        c->mega = m != nullptr && m[0] == '1';
+    }
     auto bail = [&](cudaError_t e, const char* what) {
         efm_status s = cuda_fail(nullptr, e, what);
         efm_b200_destroy(c);
@@ -177,6 +181,15 @@ efm_status efm_b200_create(const efm_model_desc* desc, int32_t device_id, int32_
     EFM_TRY(dev_alloc(c, &c->attn_part_o, (size_t)d.q_heads * 64 * D));
     EFM_TRY(dev_alloc(c, &c->attn_part_ml, (size_t)d.q_heads * 64 * 2));
     EFM_TRY(dev_alloc(c, &c->attn_counters, (size_t)d.kv_heads));
+    EFM_TRY(dev_alloc(c, &c->mega_barrier, 4));
+    EFM_TRY(dev_alloc(c, &c->mega_timing, (size_t)5 * d.num_layers + 8));
+    {
+        int optin = 0;
+        EFM_TRY(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device_id));
+        const size_t need = mega_gemv_smem_bytes((int)H, (int)QD, (int)I) + decode_attention_smem_bytes((int)D, 0);
+        if (need > (size_t)optin) c->mega = false;       // does not fit: phase-per-launch form
+        else EFM_TRY(configure_decode_mega((int)need));
+    }
     EFM_TRY(dev_alloc(c, &c->state, 1));
     EFM_TRY(dev_alloc(c, &c->tokens_out, (size_t)d.max_response_tokens));
     EFM_TRY(cudaStreamSynchronize(c->stream));
@@ -317,6 +330,18 @@ efm_status efm_b200_alloc_kv_slot(efm_b200_ctx* c, int32_t slot, int32_t max_tok
     const AttnPlan plan = plan_decode_attention(max_tokens, c->d.kv_heads, c->num_sms);
     s.n_splits = plan.n_splits;
     s.chunk_cap = plan.chunk_cap;
+    {
+        std::vector<MegaLayer> ml(c->d.num_layers);
+        for (int l = 0; l < c->d.num_layers; ++l) {
+            const LayerWeights& w = c->layers[l];
+            ml[l] = MegaLayer{w.in_norm, w.post_norm, w.qkv, w.qkv_bias, w.o, w.gate_up, w.down, s.k[l], s.v[l]};
+        }
+        MegaLayer* dev = nullptr;
+        EFM_CK(c, dev_alloc(c, &dev, ml.size(), false));
+        EFM_CK(c, cudaMemcpyAsync(dev, ml.data(), ml.size() * sizeof(MegaLayer), cudaMemcpyHostToDevice, c->stream));
+        EFM_CK(c, cudaStreamSynchronize(c->stream));
+        s.mega_layers = dev;
+    }
     EFM_CK(c, cudaStreamSynchronize(c->stream));
     c->slots[slot] = s;
     return EFM_OK;
@@ -402,6 +427,7 @@ efm_status efm_b200_decode_begin(efm_b200_ctx* c, int32_t slot, int32_t kv_len, 
     tail.error = 0;
     static_assert(offsetof(DecodeState, kv_len) == 4 && sizeof(tail) == 24, "DecodeState layout");
     EFM_CK(c, cudaMemcpyAsync(reinterpret_cast<char*>(c->state) + 4, &tail, sizeof(tail), cudaMemcpyHostToDevice, c->stream));
+    EFM_CK(c, cudaMemsetAsync(c->mega_barrier, 0, 4 * sizeof(unsigned int), c->stream));   // barrier counters, abort flag
     c->bound_slot = slot;
     return EFM_OK;
 }
@@ -467,7 +493,7 @@ static efm_status check_device_state(efm_b200_ctx* c) {
     if (st.error != 0) {
         int zero = 0;
         cudaMemcpyAsync(&c->state->error, &zero, 4, cudaMemcpyHostToDevice, c->stream);
-        return fail(c, EFM_ERR_DEVICE_WAIT, "a kernel refused an out-of-range cache row (device status " + std::to_string(st.error) + ")");
+        return fail(c, EFM_ERR_DEVICE_WAIT, "a kernel refused an out-of-range cache row or abandoned a bounded wait (device status " + std::to_string(st.error) + ")");
     }
     return EFM_OK;
 }
@@ -521,6 +547,29 @@ efm_status efm_b200_decode_breakdown(efm_b200_ctx* c, int32_t n_steps, float* ms
     EFM_CK(c, cudaSetDevice(c->device));
     for (int i = 0; i < 7; ++i) ms_out[i] = 0.f;
     const int per_step = 5 * c->d.num_layers + 2;
+    if (c->mega) {
+        // persistent kernel: block 0 stamps %globaltimer at every phase boundary
+        std::vector<unsigned long long> t((size_t)per_step + 1);
+        for (int step = 0; step < n_steps; ++step) {
+            Launcher L = make_launcher(c);
+            L.phase_timing = true;
+            cudaEvent_t e0 = nullptr, e1 = nullptr, e2 = nullptr;
+            cudaEventCreate(&e0); cudaEventCreate(&e1); cudaEventCreate(&e2);
+            qwen_decode_step(*c, s, L);
+            cudaError_t e = L.err != cudaSuccess ? L.err : cudaStreamSynchronize(c->stream);
+            if (e == cudaSuccess)
+                e = cudaMemcpy(t.data(), c->mega_timing, (size_t)per_step * sizeof(unsigned long long), cudaMemcpyDeviceToHost);
+            cudaEventDestroy(e0); cudaEventDestroy(e1); cudaEventDestroy(e2);
+            if (e != cudaSuccess) return cuda_fail(c, e, "decode breakdown");
+            // stamps: 0 = start, then one per barrier (5 per layer), then the end of lm_head
+            for (int i = 0; i + 1 < per_step; ++i) {
+                const float ms = (float)((double)(t[i + 1] - t[i]) * 1e-6);
+                const int kind = i < 5 * c->d.num_layers ? i % 5 : 5;
+                ms_out[kind] += ms;
+            }
+        }
+        return EFM_OK;
+    }
     for (int step = 0; step < n_steps; ++step) {
         std::vector<cudaEvent_t> ev;
         Launcher L = make_launcher(c);

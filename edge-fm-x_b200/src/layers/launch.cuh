@@ -10,6 +10,7 @@
 #include <vector>
 
 #include "../operators/decode_attention.cuh"
+#include "../operators/decode_mega.cuh"
 #include "../operators/gemv.cuh"
 
 namespace efm {
@@ -17,9 +18,11 @@ namespace efm {
 struct Launcher {
     cudaStream_t stream = nullptr;
     bool pdl = true;                 // programmatic stream serialization between consecutive kernels
+    bool cooperative = false;        // next launch only: all blocks co-resident (they wait on each other)
     int64_t* counter = nullptr;
     cudaError_t err = cudaSuccess;   // first failure sticks
     std::vector<cudaEvent_t>* trace = nullptr;   // when set: one event recorded after every launch
+    bool phase_timing = false;       // persistent decode kernel: stamp %globaltimer at every phase boundary
 
     template <typename... KArgs, typename... Args>
     void launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, Args&&... args) {
@@ -30,10 +33,16 @@ struct Launcher {
         cfg.dynamicSmemBytes = smem;
         cfg.stream = stream;
         cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = pdl ? attr : nullptr;
-        cfg.numAttrs = pdl ? 1 : 0;
+        if (cooperative) {
+            attr[0].id = cudaLaunchAttributeCooperative;
+            attr[0].val.cooperative = 1;
+        } else {
+            attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[0].val.programmaticStreamSerializationAllowed = 1;
+        }
+        cfg.attrs = (pdl || cooperative) ? attr : nullptr;
+        cfg.numAttrs = (pdl || cooperative) ? 1 : 0;
+        cooperative = false;
         err = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
         if (counter != nullptr) ++*counter;
         if (trace != nullptr && err == cudaSuccess) {
@@ -95,6 +104,28 @@ inline void launch_gemv(Launcher& L, const GemvParams& p, int num_sms) {
     EFM_GEMV_CASE(2, 1) EFM_GEMV_CASE(2, 2) EFM_GEMV_CASE(2, 4) EFM_GEMV_CASE(2, 8)
     EFM_GEMV_CASE(1, 1) EFM_GEMV_CASE(1, 2) EFM_GEMV_CASE(1, 4) EFM_GEMV_CASE(1, 8)
 #undef EFM_GEMV_CASE
+}
+
+// Persistent decode kernel: how many of a block's 16 warps share one row pair in a phase.
+// Fewest dependent load rounds (waves x batches) wins; ties go to the smaller split.
+inline int plan_mega_ksplit(int n_items, int K, int n_blocks) {
+    const int nch = K / 8;
+    int best = 1;
+    long best_cost = -1;
+    for (int ks = 1; ks <= kMegaWarps; ks *= 2) {
+        const long slots = (long)n_blocks * (kMegaWarps / ks);
+        const long waves = (n_items + slots - 1) / slots;
+        const long batches = (nch + 32 * ks * kMegaU - 1) / (32 * ks * kMegaU);
+        const long cost = waves * batches * 64 + ks;
+        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = ks; }
+    }
+    return best;
+}
+
+inline cudaError_t configure_decode_mega(int max_smem_optin) {
+    cudaError_t e = cudaFuncSetAttribute(decode_mega_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem_optin);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(decode_mega_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem_optin);
 }
 
 struct AttnPlan { int n_splits, chunk_cap; };

@@ -56,7 +56,64 @@ void launch_lm_head_and_sample(efm_b200_ctx& c, Launcher& L, const __nv_bfloat16
     launch_sample(L, s);
 }
 
+static void launch_sample_only(efm_b200_ctx& c, Launcher& L, int n_part, int advance) {
+    const efm_model_desc& d = c.d;
+    SampleParams s{};
+    s.logits = c.logits;
+    s.vocab = d.vocab;
+    s.part_val = c.part_val;
+    s.part_idx = c.part_idx;
+    s.n_part = n_part;
+    s.temperature = c.sampling.temperature;
+    s.top_p = c.sampling.top_p;
+    s.seed = c.sampling.seed;
+    s.state = c.state;
+    s.tokens_out = c.tokens_out;
+    s.max_response = d.max_response_tokens;
+    s.advance = advance;
+    s.wbuf = c.wbuf;
+    launch_sample(L, s);
+}
+
+// One decode step as the persistent cooperative kernel + the sampler.
+static void qwen_decode_step_mega(efm_b200_ctx& c, KvSlot& slot, Launcher& L) {
+    const efm_model_desc& d = c.d;
+    const int D = d.head_dim, nb = c.num_sms;
+    MegaParams P{};
+    P.layers = static_cast<const MegaLayer*>(slot.mega_layers);
+    P.L = d.num_layers; P.H = d.hidden; P.QD = d.q_heads * D; P.KVD = d.kv_heads * D; P.I = d.intermediate;
+    P.V = d.vocab; P.vocab = d.vocab; P.q_heads = d.q_heads; P.kv_heads = d.kv_heads;
+    P.eps = d.rms_eps;
+    P.ks_qkv = plan_mega_ksplit((P.QD + 2 * P.KVD) / 2, P.H, nb);
+    P.ks_o = plan_mega_ksplit(P.H / 2, P.QD, nb);
+    P.ks_gu = plan_mega_ksplit(P.I, P.H, nb);
+    P.ks_down = plan_mega_ksplit(P.H / 2, P.I, nb);
+    P.ks_lm = plan_mega_ksplit(P.V / 2, P.H, nb);
+    P.embed = c.embed; P.final_norm = c.final_norm; P.lm_head = c.lm_head;
+    P.resid = c.resid_d; P.q = c.q_d; P.attn = c.attn_d; P.act = c.act_d;
+    P.logits = c.logits; P.part_val = c.part_val; P.part_idx = c.part_idx;
+    P.state = c.state; P.inv_freq = c.inv_freq;
+    P.use_mrope = d.use_mrope; P.sec0 = d.mrope_section[0]; P.sec1 = d.mrope_section[0] + d.mrope_section[1];
+    P.max_tokens = slot.max_tokens;
+    P.n_splits = slot.n_splits; P.chunk_cap = slot.chunk_cap;
+    P.scale = 1.0f / sqrtf((float)D);
+    P.part_o = c.attn_part_o; P.part_ml = c.attn_part_ml; P.attn_counters = c.attn_counters;
+    P.barrier = c.mega_barrier;
+    P.abort_flag = reinterpret_cast<int*>(c.mega_barrier + 2);
+    P.gemv_smem_bytes = (unsigned int)mega_gemv_smem_bytes(P.H, P.QD, P.I);
+    P.timing = L.phase_timing ? c.mega_timing : nullptr;
+    const size_t smem = P.gemv_smem_bytes + decode_attention_smem_bytes(D, 0);
+    L.cooperative = true;
+    if (D == 128) L.launch(decode_mega_kernel<128>, dim3(nb), dim3(kMegaThreads), smem, P);
+    else L.launch(decode_mega_kernel<64>, dim3(nb), dim3(kMegaThreads), smem, P);
+    launch_sample_only(c, L, nb, /*advance=*/1);
+}
+
 void qwen_decode_step(efm_b200_ctx& c, KvSlot& slot, Launcher& L) {
+    if (c.mega && L.trace == nullptr) {      // per-kernel tracing needs the phase-per-launch form
+        qwen_decode_step_mega(c, slot, L);
+        return;
+    }
     const efm_model_desc& d = c.d;
     const int H = d.hidden, D = d.head_dim, QD = d.q_heads * D, KVD = d.kv_heads * D, I = d.intermediate;
     for (int l = 0; l < d.num_layers; ++l) {

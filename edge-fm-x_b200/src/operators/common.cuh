@@ -57,6 +57,9 @@ __device__ __forceinline__ uint4 ld_stream(const void* p) {
     return v;
 }
 __device__ __forceinline__ uint4 ld_cached(const void* p) { return *reinterpret_cast<const uint4*>(p); }
+// L2-only load for data that another block wrote earlier in the same kernel.
+__device__ __forceinline__ uint4 ld_cg(const void* p) { return __ldcg(reinterpret_cast<const uint4*>(p)); }
+__device__ __forceinline__ float bf16_bits_to_f32(unsigned short v) { return __uint_as_float((uint32_t)v << 16); }
 
 // ---- reductions ------------------------------------------------------------------------
 __device__ __forceinline__ float warp_sum(float v) {

@@ -8,7 +8,7 @@
 // is walked in tiles of 64 rows (normally exactly one tile):
 //   1. every thread issues its quarter-row of K and of V together (one DRAM round trip);
 //   2. scores against q (fp32, shared memory), tile max, p = exp(s - max), running (m, l);
-//   3. o += P.V from shared memory, 8 channels per thread, folded over the row groups;
+//   3. o += P.V from shared memory, 4 channels per thread, folded over the row groups;
 //   4. (m, l, o) go to scratch; the last block to finish for a kv head (atomic ticket, nobody
 //      spins) computes the merge weights once and folds all chunks with independent loads.
 // Bound: HBM (2 * kv_len * kv_heads * D * 2 bytes per layer); in practice latency.
@@ -49,20 +49,28 @@ struct DecodeAttnSmem {
     unsigned int ticket;
 };
 
-template <int D>
-__global__ void __launch_bounds__(256) decode_attention_kernel(const DecodeAttnParams p) {
+// The 256 threads of one attention work item synchronise either with the whole-block barrier
+// (stand-alone kernel) or with named barrier 9 (inside the persistent decode kernel, where the
+// block has more warps than the work item uses).
+template <bool NAMED>
+__device__ __forceinline__ void attn_sync() {
+    if constexpr (NAMED) asm volatile("bar.sync 9, 256;" ::: "memory");
+    else __syncthreads();
+}
+
+// One (chunk, kv head) work item.  Every load of data another block may have written in this
+// step (q, the newest cache row, the partials) bypasses L1.
+template <int D, bool NAMED>
+__device__ __forceinline__ void decode_attention_body(const DecodeAttnParams& p, const int split, const int kvh,
+                                                      unsigned char* attn_smem) {
     constexpr int NT = 256;
     constexpr int QV = D / 32;            // uint4 per thread and row (a quarter row)
-    constexpr int TPR = D / 8;            // threads per V row in the P.V phase
+    constexpr int TPR = D / 4;            // threads per V row in the P.V phase (4 channels each)
     constexpr int TG = NT / TPR;          // row groups in the P.V phase
-    extern __shared__ __align__(16) unsigned char attn_smem[];
     DecodeAttnSmem<D>& sm = *reinterpret_cast<DecodeAttnSmem<D>*>(attn_smem);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int split = blockIdx.x, kvh = blockIdx.y;
     const int G = p.group;
-    pdl_launch_dependents();
-    pdl_wait();
 
     int kv_len = p.state != nullptr ? (int)p.state->kv_len : p.kv_len_static;
     if (kv_len > p.max_tokens) {
@@ -78,15 +86,15 @@ __global__ void __launch_bounds__(256) decode_attention_kernel(const DecodeAttnP
 
     const int tok = tid >> 2, part = tid & 3;                    // score phase: 4 threads per row
     const int dpart = tid % TPR, tg = tid / TPR;                 // P.V phase
-    float acc[kMaxGroup][8];
+    float acc[kMaxGroup][4];
 #pragma unroll
     for (int g = 0; g < kMaxGroup; ++g)
 #pragma unroll
-        for (int e = 0; e < 8; ++e) acc[g][e] = 0.f;
+        for (int e = 0; e < 4; ++e) acc[g][e] = 0.f;
 
     for (int i = tid; i < G * D; i += NT) {
         const int g = i / D, d = i - g * D;
-        sm.q[g][d / (D / 4)][d % (D / 4)] = __bfloat162float(p.q[(size_t)(kvh * G) * D + i]);
+        sm.q[g][d / (D / 4)][d % (D / 4)] = bf16_bits_to_f32(__ldcg(reinterpret_cast<const unsigned short*>(p.q) + (size_t)(kvh * G) * D + i));
     }
     if (tid < kMaxGroup) { sm.run_m[tid] = -INFINITY; sm.run_l[tid] = 0.f; }
 
@@ -98,11 +106,11 @@ __global__ void __launch_bounds__(256) decode_attention_kernel(const DecodeAttnP
         if (valid) {
             const size_t off = (size_t)(start + t0 + tok) * row_stride + (size_t)kvh * D + part * (D / 4);
 #pragma unroll
-            for (int j = 0; j < QV; ++j) kq[j] = ld_cached(p.k_cache + off + j * 8);
+            for (int j = 0; j < QV; ++j) kq[j] = ld_cg(p.k_cache + off + j * 8);
 #pragma unroll
-            for (int j = 0; j < QV; ++j) vq[j] = ld_cached(p.v_cache + off + j * 8);
+            for (int j = 0; j < QV; ++j) vq[j] = ld_cg(p.v_cache + off + j * 8);
         }
-        __syncthreads();      // q staged (first tile) / previous tile's p and v fully consumed
+        attn_sync<NAMED>();      // q staged (first tile) / previous tile's p and v fully consumed
         // ---- 2. scores ----------------------------------------------------------------------
         float s[kMaxGroup];
 #pragma unroll
@@ -136,7 +144,7 @@ __global__ void __launch_bounds__(256) decode_attention_kernel(const DecodeAttnP
             m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 16));
             if (lane == 0) sm.wmax[warp][g] = m;
         }
-        __syncthreads();
+        attn_sync<NAMED>();
 #pragma unroll
         for (int g = 0; g < kMaxGroup; ++g) {
             if (g < G) {
@@ -153,7 +161,7 @@ __global__ void __launch_bounds__(256) decode_attention_kernel(const DecodeAttnP
                 if (tid == 0) sm.rescale[g] = m_new;      // new running max (read after the barrier)
             }
         }
-        __syncthreads();
+        attn_sync<NAMED>();
         // ---- 3. o = o * rescale + P.V -----------------------------------------------------------
 #pragma unroll
         for (int g = 0; g < kMaxGroup; ++g) {
@@ -161,22 +169,22 @@ __global__ void __launch_bounds__(256) decode_attention_kernel(const DecodeAttnP
                 const float m_old = sm.run_m[g], m_new = sm.rescale[g];
                 const float f = m_old == -INFINITY ? 0.f : expf(m_old - m_new);
 #pragma unroll
-                for (int e = 0; e < 8; ++e) acc[g][e] *= f;
+                for (int e = 0; e < 4; ++e) acc[g][e] *= f;
             }
         }
         for (int t = tg; t < nt; t += TG) {
-            float vf[8];
-            unpack8(*reinterpret_cast<const uint4*>(&sm.v[t][dpart * 8]), vf);
+            const uint2 vv = *reinterpret_cast<const uint2*>(&sm.v[t][dpart * 4]);
+            const float vf[4] = {bf16lo(vv.x), bf16hi(vv.x), bf16lo(vv.y), bf16hi(vv.y)};
 #pragma unroll
             for (int g = 0; g < kMaxGroup; ++g) {
                 if (g < G) {
                     const float pg = sm.p[g][t];
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) acc[g][e] = fmaf(pg, vf[e], acc[g][e]);
+                    for (int e = 0; e < 4; ++e) acc[g][e] = fmaf(pg, vf[e], acc[g][e]);
                 }
             }
         }
-        __syncthreads();      // everyone has read run_m / rescale / wsum inputs of this tile
+        attn_sync<NAMED>();      // everyone has read run_m / rescale / wsum inputs of this tile
         if (tid < G) {
             const float m_old = sm.run_m[tid], m_new = sm.rescale[tid];
             float l = sm.run_l[tid] * (m_old == -INFINITY ? 0.f : expf(m_old - m_new));
@@ -191,7 +199,7 @@ __global__ void __launch_bounds__(256) decode_attention_kernel(const DecodeAttnP
 #pragma unroll
     for (int g = 0; g < kMaxGroup; ++g)
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
+        for (int e = 0; e < 4; ++e) {
             float v = acc[g][e];
 #pragma unroll
             for (int o = TPR; o < 32; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -200,12 +208,9 @@ __global__ void __launch_bounds__(256) decode_attention_kernel(const DecodeAttnP
     if (lane < TPR) {
 #pragma unroll
         for (int g = 0; g < kMaxGroup; ++g)
-            if (g < G) {
-#pragma unroll
-                for (int e = 0; e < 8; ++e) sm.ored[warp][g][lane * 8 + e] = acc[g][e];
-            }
+            if (g < G) *reinterpret_cast<float4*>(&sm.ored[warp][g][lane * 4]) = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
     }
-    __syncthreads();
+    attn_sync<NAMED>();
 
     // ---- 4. publish the partial, merge if last -------------------------------------------------
     for (int i = tid; i < G * D; i += NT) {
@@ -221,9 +226,9 @@ __global__ void __launch_bounds__(256) decode_attention_kernel(const DecodeAttnP
         p.part_ml[((size_t)qh * p.n_splits + split) * 2 + 1] = sm.run_l[tid];
     }
     __threadfence();
-    __syncthreads();
+    attn_sync<NAMED>();
     if (tid == 0) sm.ticket = atomicAdd(&p.counters[kvh], 1u);
-    __syncthreads();
+    attn_sync<NAMED>();
     if (sm.ticket != (unsigned)(p.n_splits - 1)) return;
     __threadfence();
     // merge weights: warp g handles query head g, lanes over chunks
@@ -253,24 +258,36 @@ __global__ void __launch_bounds__(256) decode_attention_kernel(const DecodeAttnP
             if (s < p.n_splits) sm.mw[g][s] = w[j] * inv;
         }
     }
-    __syncthreads();
+    attn_sync<NAMED>();
     for (int i = tid; i < G * D; i += NT) {
         const int g = i / D, d = i - g * D;
         const float* po = p.part_o + (size_t)(kvh * G + g) * p.n_splits * D + d;
         float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
-        int s = 0;
-        for (; s + 4 <= p.n_splits; s += 4) {
-            const float a = __ldcg(po + (size_t)s * D), b = __ldcg(po + (size_t)(s + 1) * D);
-            const float c = __ldcg(po + (size_t)(s + 2) * D), e = __ldcg(po + (size_t)(s + 3) * D);
-            o0 = fmaf(a, sm.mw[g][s], o0);
-            o1 = fmaf(b, sm.mw[g][s + 1], o1);
-            o2 = fmaf(c, sm.mw[g][s + 2], o2);
-            o3 = fmaf(e, sm.mw[g][s + 3], o3);
+        for (int s0 = 0; s0 < p.n_splits; s0 += 16) {          // 16 independent L2 loads per round trip
+            float v[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = s0 + j < p.n_splits ? __ldcg(po + (size_t)(s0 + j) * D) : 0.f;
+#pragma unroll
+            for (int j = 0; j < 16; j += 4) {
+                if (s0 + j < p.n_splits) {
+                    o0 = fmaf(v[j], sm.mw[g][min(s0 + j, kMaxSplits - 1)], o0);
+                    o1 = fmaf(v[j + 1], s0 + j + 1 < p.n_splits ? sm.mw[g][s0 + j + 1] : 0.f, o1);
+                    o2 = fmaf(v[j + 2], s0 + j + 2 < p.n_splits ? sm.mw[g][s0 + j + 2] : 0.f, o2);
+                    o3 = fmaf(v[j + 3], s0 + j + 3 < p.n_splits ? sm.mw[g][s0 + j + 3] : 0.f, o3);
+                }
+            }
         }
-        for (; s < p.n_splits; ++s) o0 = fmaf(__ldcg(po + (size_t)s * D), sm.mw[g][s], o0);
         p.out[(size_t)(kvh * G + g) * D + d] = __float2bfloat16_rn((o0 + o1) + (o2 + o3));
     }
     if (tid == 0) p.counters[kvh] = 0u;
+}
+
+template <int D>
+__global__ void __launch_bounds__(256) decode_attention_kernel(const DecodeAttnParams p) {
+    extern __shared__ __align__(16) unsigned char attn_smem_raw[];
+    pdl_launch_dependents();
+    pdl_wait();
+    decode_attention_body<D, false>(p, blockIdx.x, blockIdx.y, attn_smem_raw);
 }
 
 inline size_t decode_attention_smem_bytes(int D, int /*chunk_cap*/) {

@@ -80,9 +80,10 @@ __device__ __forceinline__ void item_epilogue(const GemvParams& p, int item, flo
         p.y[item * 2] = __float2bfloat16_rn(a0);
         p.y[item * 2 + 1] = __float2bfloat16_rn(a1);
     } else if constexpr (EPI == Epi::Residual) {
-        const float r0 = __bfloat162float(p.residual[item * 2]) + round_bf16(a0);
-        const float r1 = __bfloat162float(p.residual[item * 2 + 1]) + round_bf16(a1);
-        *reinterpret_cast<uint32_t*>(p.residual + item * 2) = pack_bf16(r0, r1);
+        // L2 load: inside the persistent decode kernel another block wrote this value
+        const uint32_t old = __ldcg(reinterpret_cast<const unsigned int*>(p.residual + item * 2));
+        *reinterpret_cast<uint32_t*>(p.residual + item * 2) =
+            pack_bf16(bf16lo(old) + round_bf16(a0), bf16hi(old) + round_bf16(a1));
     } else if constexpr (EPI == Epi::SwiGlu) {
         const float s = a0 / (1.0f + expf(-a0));
         p.y[item] = __float2bfloat16_rn(s * a1);

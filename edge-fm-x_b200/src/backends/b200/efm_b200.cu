@@ -60,6 +60,7 @@ efm_status require_b200(efm_b200_ctx* c, int device_id) {
     if (major != 10) return fail(c, EFM_ERR_CUDA, "device is not sm_100 (this library carries sm_100a code only)");
     EFM_CK(c, cudaSetDevice(device_id));
     EFM_CK(c, configure_decode_attention());
+    EFM_CK(c, configure_gemv(96 * 1024));
     return EFM_OK;
 }
 

@@ -52,74 +52,37 @@ struct Launcher {
     }
 };
 
-struct GemvPlan { int items, ksplit, grid; };
-
-// Cost model: a warp's serial work is (128-bit loads per lane) per wave plus a fixed reduce /
-// epilogue cost; pick the variant with the shortest critical path and size the grid so that
-// every row group slot gets the same number of waves.
-inline int gemv_ctas_per_sm() {
-    static const int v = [] {
-        const char* e = std::getenv("EFM_B200_GEMV_CTAS_PER_SM");     // tuning knob, 1 or 2
-        const int x = e != nullptr ? std::atoi(e) : 2;
-        return x == 1 ? 1 : 2;
-    }();
-    return v;
-}
-
-inline GemvPlan plan_gemv(int n_items, int K, int num_sms) {
-    const int max_ctas = gemv_ctas_per_sm() * num_sms;
-    const int nch = K / 8;
-    GemvPlan best{2, 1, max_ctas};
-    long best_cost = -1;
-    for (int items = 2; items >= 1; --items) {
-        for (int ks = 1; ks <= 8; ks *= 2) {
-            const int gp = 8 / ks;
-            const int n_ig = (n_items + items - 1) / items;
-            const long slots = (long)max_ctas * gp;
-            const long waves = (n_ig + slots - 1) / slots;
-            const long per_wave = (long)((nch + 32 * ks - 1) / (32 * ks)) * items * 2 + 8 + (ks > 1 ? 4 : 0);
-            const long cost = waves * per_wave;
-            if (best_cost < 0 || cost < best_cost) {
-                best_cost = cost;
-                int grid = (int)((n_ig + waves * gp - 1) / (waves * gp));
-                best = GemvPlan{items, ks, std::max(1, std::min(grid, max_ctas))};
-            }
-        }
-    }
-    return best;
-}
-
-template <Epi EPI>
-inline void launch_gemv(Launcher& L, const GemvParams& p, int num_sms) {
-    const GemvPlan plan = plan_gemv(p.n_items, p.K, num_sms);
-    const size_t smem = gemv_smem_bytes(p.K, plan.items);
-    const dim3 grid(plan.grid), block(256);
-#define EFM_GEMV_CASE(I, S)                                                                   \
-    if (plan.items == I && plan.ksplit == S) {                                                \
-        if (smem > 48 * 1024)                                                                 \
-            cudaFuncSetAttribute(gemv_kernel<EPI, I, S>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        L.launch(gemv_kernel<EPI, I, S>, grid, block, smem, p);                               \
-        return;                                                                               \
-    }
-    EFM_GEMV_CASE(2, 1) EFM_GEMV_CASE(2, 2) EFM_GEMV_CASE(2, 4) EFM_GEMV_CASE(2, 8)
-    EFM_GEMV_CASE(1, 1) EFM_GEMV_CASE(1, 2) EFM_GEMV_CASE(1, 4) EFM_GEMV_CASE(1, 8)
-#undef EFM_GEMV_CASE
-}
-
-// Persistent decode kernel: how many of a block's 16 warps share one row pair in a phase.
-// Fewest dependent load rounds (waves x batches) wins; ties go to the smaller split.
-inline int plan_mega_ksplit(int n_items, int K, int n_blocks) {
+// How many of a block's 16 warps share one row pair (ks).  The serial length of a warp's work is
+// waves x units per item; the shortest wins, ties go to the smaller split (less reduction).
+inline int plan_gemv_ksplit(int n_items, int K, int n_blocks) {
     const int nch = K / 8;
     int best = 1;
     long best_cost = -1;
-    for (int ks = 1; ks <= kMegaWarps; ks *= 2) {
-        const long slots = (long)n_blocks * (kMegaWarps / ks);
+    for (int ks = 1; ks <= kGemvWarps; ks *= 2) {
+        const long slots = (long)n_blocks * (kGemvWarps / ks);
         const long waves = (n_items + slots - 1) / slots;
-        const long batches = (nch + 32 * ks * kMegaU - 1) / (32 * ks * kMegaU);
-        const long cost = waves * batches * 64 + ks;
+        const long cpl = (nch + 32 * ks - 1) / (32 * ks);
+        const long units = (cpl + kGemvU - 1) / kGemvU;
+        const long cost = waves * units * 64 + ks;
         if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = ks; }
     }
     return best;
+}
+
+// One GEMV phase as its own launch: one block per SM.
+template <Epi EPI>
+inline void launch_gemv(Launcher& L, const GemvParams& p, int num_sms) {
+    const int ks = plan_gemv_ksplit(p.n_items, p.K, num_sms);
+    L.launch(gemv_kernel<EPI>, dim3(num_sms), dim3(kGemvThreads), gemv_smem_bytes(p.K), p, ks);
+}
+
+inline cudaError_t configure_gemv(int max_smem_optin) {
+    cudaError_t e = cudaFuncSetAttribute(gemv_kernel<Epi::Plain>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem_optin);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_kernel<Epi::Residual>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem_optin);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_kernel<Epi::QkvRope>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem_optin);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_kernel<Epi::SwiGlu>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem_optin);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_kernel<Epi::Logits>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem_optin);
+    return e;
 }
 
 inline cudaError_t configure_decode_mega(int max_smem_optin) {
@@ -147,7 +110,7 @@ inline cudaError_t configure_decode_attention() {
 
 inline void launch_decode_attention(Launcher& L, const DecodeAttnParams& p, int head_dim) {
     const size_t smem = decode_attention_smem_bytes(head_dim, p.chunk_cap);
-    const dim3 grid(p.n_splits, p.kv_heads), block(256);
+    const dim3 grid(p.n_splits, p.kv_heads), block(kAttnThreads);
     if (head_dim == 128) L.launch(decode_attention_kernel<128>, grid, block, smem, p);
     else L.launch(decode_attention_kernel<64>, grid, block, smem, p);
 }

@@ -8,6 +8,7 @@
 #include "qwen_text.h"
 
 #include "../operators/gemm_mma.cuh"
+#include "../operators/gemm_tc.cuh"
 #include "../operators/prefill.cuh"
 #include "../operators/sample.cuh"
 #include "launch.cuh"
@@ -36,7 +37,6 @@ void launch_lm_head_and_sample(efm_b200_ctx& c, Launcher& L, const __nv_bfloat16
     p.logits = c.logits;
     p.part_val = c.part_val;
     p.part_idx = c.part_idx;
-    const GemvPlan plan = plan_gemv(p.n_items, p.K, c.num_sms);
     launch_gemv<Epi::Logits>(L, p, c.num_sms);
 
     SampleParams s{};
@@ -44,7 +44,7 @@ void launch_lm_head_and_sample(efm_b200_ctx& c, Launcher& L, const __nv_bfloat16
     s.vocab = d.vocab;
     s.part_val = c.part_val;
     s.part_idx = c.part_idx;
-    s.n_part = plan.grid;
+    s.n_part = c.num_sms;
     s.temperature = c.sampling.temperature;
     s.top_p = c.sampling.top_p;
     s.seed = c.sampling.seed;
@@ -84,11 +84,11 @@ static void qwen_decode_step_mega(efm_b200_ctx& c, KvSlot& slot, Launcher& L) {
     P.L = d.num_layers; P.H = d.hidden; P.QD = d.q_heads * D; P.KVD = d.kv_heads * D; P.I = d.intermediate;
     P.V = d.vocab; P.vocab = d.vocab; P.q_heads = d.q_heads; P.kv_heads = d.kv_heads;
     P.eps = d.rms_eps;
-    P.ks_qkv = plan_mega_ksplit((P.QD + 2 * P.KVD) / 2, P.H, nb);
-    P.ks_o = plan_mega_ksplit(P.H / 2, P.QD, nb);
-    P.ks_gu = plan_mega_ksplit(P.I, P.H, nb);
-    P.ks_down = plan_mega_ksplit(P.H / 2, P.I, nb);
-    P.ks_lm = plan_mega_ksplit(P.V / 2, P.H, nb);
+    P.ks_qkv = plan_gemv_ksplit((P.QD + 2 * P.KVD) / 2, P.H, nb);
+    P.ks_o = plan_gemv_ksplit(P.H / 2, P.QD, nb);
+    P.ks_gu = plan_gemv_ksplit(P.I, P.H, nb);
+    P.ks_down = plan_gemv_ksplit(P.H / 2, P.I, nb);
+    P.ks_lm = plan_gemv_ksplit(P.V / 2, P.H, nb);
     P.embed = c.embed; P.final_norm = c.final_norm; P.lm_head = c.lm_head;
     P.resid = c.resid_d; P.q = c.q_d; P.attn = c.attn_d; P.act = c.act_d;
     P.logits = c.logits; P.part_val = c.part_val; P.part_idx = c.part_idx;
@@ -186,18 +186,53 @@ void qwen_decode_step(efm_b200_ctx& c, KvSlot& slot, Launcher& L) {
     launch_lm_head_and_sample(c, L, c.resid_d, /*advance=*/1);
 }
 
+// ---- tensor maps for the TMA-fed GEMM --------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = [] {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult st;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &st) != cudaSuccess ||
+            st != cudaDriverEntryPointSuccess)
+            f = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(f);
+    }();
+    return fn;
+}
+
+// bf16 row-major [rows, cols] tensor, box = 64 columns x 128 rows, 128-byte swizzle, zero fill
+// outside the tensor.
+static bool make_tile_map(CUtensorMap* map, const void* ptr, int rows, int cols) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (fn == nullptr) return false;
+    const cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t gstride[1] = {(cuuint64_t)cols * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)tc::BK, (cuuint32_t)tc::BM};
+    const cuuint32_t estride[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), gdim, gstride, box, estride,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <GemmEpi EPI>
-static void launch_gemm(Launcher& L, const GemmParams& p) {
-    const size_t smem = gemm_mma_smem_bytes();
+static void launch_gemm(Launcher& L, const GemmParams& p, int* error_word = nullptr) {
     static bool attr_set = false;
     if (!attr_set) {
-        cudaFuncSetAttribute(gemm_mma_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(gemm_tc_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc::SMEM_BYTES);
         attr_set = true;
     }
-    const dim3 grid((p.N + 127) / 128, (p.M + 127) / 128), block(256);
+    CUtensorMap ma, mb;
+    if (!make_tile_map(&ma, p.A, p.M, p.K) || !make_tile_map(&mb, p.B, p.N, p.K)) {
+        if (L.err == cudaSuccess) L.err = cudaErrorInvalidValue;
+        return;
+    }
+    const dim3 grid((p.N + tc::BN - 1) / tc::BN, (p.M + tc::BM - 1) / tc::BM), block(tc::kThreads);
     const bool pdl = L.pdl;
     L.pdl = false;     // prefill kernels do not use the dependent-launch protocol
-    L.launch(gemm_mma_kernel<EPI>, grid, block, smem, p);
+    L.launch(gemm_tc_kernel<EPI>, grid, block, tc::SMEM_BYTES, ma, mb, p, error_word);
     L.pdl = pdl;
 }
 
@@ -228,7 +263,7 @@ void qwen_prefill_chunk(efm_b200_ctx& c, KvSlot& slot, int S, int kv_offset, int
                  (const __nv_bfloat16*)w.in_norm, c.norm, H, d.rms_eps);
         {
             GemmParams g{c.norm, w.qkv, w.qkv_bias, c.qkv, nullptr, S, QD + 2 * KVD, H};
-            launch_gemm<GemmEpi::Bf16Bias>(L, g);
+            launch_gemm<GemmEpi::Bf16Bias>(L, g, &c.state->error);
         }
         L.launch(rope_scatter_kernel, dim3(S, d.q_heads + 2 * d.kv_heads), dim3(D / 2), 0,
                  (const __nv_bfloat16*)c.qkv, c.qbuf, slot.k[l], slot.v[l], (const float*)c.inv_freq,
@@ -237,13 +272,13 @@ void qwen_prefill_chunk(efm_b200_ctx& c, KvSlot& slot, int S, int kv_offset, int
         launch_prefill_attention(L, c.qbuf, slot.k[l], slot.v[l], c.attn, S, kv_offset, d.q_heads, d.kv_heads, D);
         {
             GemmParams g{c.attn, w.o, nullptr, c.resid, nullptr, S, H, QD};
-            launch_gemm<GemmEpi::Residual>(L, g);
+            launch_gemm<GemmEpi::Residual>(L, g, &c.state->error);
         }
         L.launch(rmsnorm_rows_kernel, dim3(S), dim3(256), 0, (const __nv_bfloat16*)c.resid,
                  (const __nv_bfloat16*)w.post_norm, c.norm, H, d.rms_eps);
         {
             GemmParams g{c.norm, w.gate_up, nullptr, nullptr, c.gu, S, 2 * I, H};
-            launch_gemm<GemmEpi::F32>(L, g);
+            launch_gemm<GemmEpi::F32>(L, g, &c.state->error);
         }
         {
             const size_t total = (size_t)S * I;
@@ -252,7 +287,7 @@ void qwen_prefill_chunk(efm_b200_ctx& c, KvSlot& slot, int S, int kv_offset, int
         }
         {
             GemmParams g{c.act, w.down, nullptr, c.resid, nullptr, S, H, I};
-            launch_gemm<GemmEpi::Residual>(L, g);
+            launch_gemm<GemmEpi::Residual>(L, g, &c.state->error);
         }
     }
     if (sample_last) launch_lm_head_and_sample(c, L, c.resid + (size_t)(S - 1) * H, /*advance=*/0);

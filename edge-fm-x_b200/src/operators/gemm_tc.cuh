@@ -1,0 +1,238 @@
+// Prefill linear on the 5th-generation tensor cores: C[M,N] = A[M,K] . B[N,K]^T, bf16 operands,
+// fp32 accumulation in tensor memory.
+// (reference: cublasLtMatmul / CUTLASS sm80 prefill linears, src/operators/linear_impl.cu:457-469,482-706;
+//  the reference has no sm_100 kernel.)
+//
+// One 128 x 128 output tile per block, 192 threads:
+//   warp 0      one lane issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle, no multicast) of
+//               a 128 x 64 A tile and a 128 x 64 B tile per stage into a 6-stage ring;
+//   warp 1      allocates 128 TMEM columns; one lane issues tcgen05.mma (M 128, N 128, K 16, four
+//               per stage) and tcgen05.commit, which releases the stage to the producer;
+//   warps 2-5   epilogue: tcgen05.ld the accumulator (row = TMEM lane, 32 columns at a time) and
+//               write bf16 (+bias) | residual add | fp32.
+// Rows past M and columns past N are zero-filled by TMA on load and masked on store.
+// Every mbarrier wait is bounded; a wait that gives up raises *error, the block frees its TMEM and
+// returns.  Bound: tensor pipe (2 M N K flops).
+#pragma once
+#include <cuda.h>
+
+#include "common.cuh"
+#include "gemm_mma.cuh"      // GemmParams / GemmEpi
+
+namespace efm {
+namespace tc {
+
+constexpr int BM = 128, BN = 128, BK = 64, STAGES = 6, UMMA_K = 16;
+constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int kThreads = 192;
+constexpr int TMEM_COLS = 128;
+constexpr int kWaitLimit = 1 << 20;                        // try_wait polls before giving up
+constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Bounded wait for the phase with the given parity; false when it gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    for (int i = 0; i < kWaitLimit; ++i) {
+        if ((i & 0xff) == 0xff && *abort_flag != 0) return false;      // another role already gave up
+        uint32_t ok;
+        asm volatile(
+            "{\n"
+            ".reg .pred p;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n"
+            "}\n"
+            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+// K-major operand tile written by TMA with the 128-byte swizzle: rows of 128 bytes, 8-row groups
+// 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);        // start address / 16
+    d |= (uint64_t)1 << 16;                               // leading byte offset (unused with swizzle)
+    d |= (uint64_t)(1024 >> 4) << 32;                     // stride byte offset: 8 rows x 128 B
+    d |= (uint64_t)1 << 46;                               // descriptor version of sm_100
+    d |= (uint64_t)2 << 61;                               // SWIZZLE_128B
+    return d;
+}
+// kind::f16, A = B = bf16, D = fp32, both operands K-major, M = 128, N = 128.
+constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(kInstrDesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+}  // namespace tc
+
+template <GemmEpi EPI>
+__global__ void __launch_bounds__(tc::kThreads) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                               const __grid_constant__ CUtensorMap map_b,
+                                                               const GemmParams p, int* error) {
+    using namespace tc;
+    extern __shared__ unsigned char gemm_tc_smem[];
+    const uint32_t raw = smem_u32(gemm_tc_smem);
+    const uint32_t base = (raw + 1023u) & ~1023u;                     // swizzle atoms need 1024-byte alignment
+    unsigned char* base_ptr = gemm_tc_smem + (base - raw);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(base_ptr + (size_t)STAGES * STAGE_BYTES);
+    const uint32_t full0 = base + STAGES * STAGE_BYTES;               // full[s]  = full0 + 8 s
+    const uint32_t empty0 = full0 + 8 * STAGES;                       // empty[s] = empty0 + 8 s
+    const uint32_t done_bar = empty0 + 8 * STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
+    volatile int* abort_s = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int KB = (p.K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        mbar_init(done_bar, 1);
+        *abort_s = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int kb = 0; kb < KB; ++kb) {
+                const int s = kb % STAGES;
+                const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
+                if (!mbar_wait(empty0 + 8 * s, ph ^ 1u, abort_s)) { *abort_s = 1; break; }
+                mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+                tma_load_2d(base + s * STAGE_BYTES, &map_a, kb * BK, m0, full0 + 8 * s);
+                tma_load_2d(base + s * STAGE_BYTES + A_BYTES, &map_b, kb * BK, n0, full0 + 8 * s);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            for (int kb = 0; kb < KB; ++kb) {
+                const int s = kb % STAGES;
+                const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
+                if (!mbar_wait(full0 + 8 * s, ph, abort_s)) { *abort_s = 1; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint64_t da = umma_desc(base + s * STAGE_BYTES), db = umma_desc(base + s * STAGE_BYTES + A_BYTES);
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k)               // 32 bytes further along K inside the swizzle atom
+                    umma(tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), (kb | k) != 0 ? 1u : 0u);
+                umma_commit(empty0 + 8 * s);                         // stage free once these MMAs have read it
+            }
+            umma_commit(done_bar);                                   // accumulator complete
+        }
+    } else {
+        // epilogue warps 2..5: TMEM lane group = warp % 4
+        const int q = warp & 3;
+        const bool ok = mbar_wait(done_bar, 0u, abort_s);
+        if (!ok) *abort_s = 1;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const int m = m0 + q * 32 + lane;
+        if (ok && *abort_s == 0) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
+                const int n = n0 + c0;
+                if (m < p.M && n < p.N) {
+                    const size_t off = (size_t)m * p.N + n;
+                    const int nv = min(32, p.N - n);               // N is even
+                    float v[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+                    if constexpr (EPI == GemmEpi::Bf16Bias) {
+                        if (p.bias != nullptr) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) if (j < nv) v[j] += __bfloat162float(p.bias[n + j]);
+                        }
+                    }
+                    const bool wide = nv == 32 && (p.N & 7) == 0;  // 16-byte aligned row segments
+                    if constexpr (EPI == GemmEpi::F32) {
+                        if (wide) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4)
+                                *reinterpret_cast<float4*>(p.Cf + off + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                        } else {
+                            for (int j = 0; j < nv; j += 2) *reinterpret_cast<float2*>(p.Cf + off + j) = make_float2(v[j], v[j + 1]);
+                        }
+                    } else if constexpr (EPI == GemmEpi::Bf16Bias) {
+                        if (wide) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 8)
+                                *reinterpret_cast<uint4*>(p.C + off + j) = make_uint4(pack_bf16(v[j], v[j + 1]), pack_bf16(v[j + 2], v[j + 3]),
+                                                                                       pack_bf16(v[j + 4], v[j + 5]), pack_bf16(v[j + 6], v[j + 7]));
+                        } else {
+                            for (int j = 0; j < nv; j += 2) *reinterpret_cast<uint32_t*>(p.C + off + j) = pack_bf16(v[j], v[j + 1]);
+                        }
+                    } else {
+                        if (wide) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 8) {
+                                const uint4 o = *reinterpret_cast<const uint4*>(p.C + off + j);
+                                uint4 w;
+                                w.x = pack_bf16(bf16lo(o.x) + round_bf16(v[j]), bf16hi(o.x) + round_bf16(v[j + 1]));
+                                w.y = pack_bf16(bf16lo(o.y) + round_bf16(v[j + 2]), bf16hi(o.y) + round_bf16(v[j + 3]));
+                                w.z = pack_bf16(bf16lo(o.z) + round_bf16(v[j + 4]), bf16hi(o.z) + round_bf16(v[j + 5]));
+                                w.w = pack_bf16(bf16lo(o.w) + round_bf16(v[j + 6]), bf16hi(o.w) + round_bf16(v[j + 7]));
+                                *reinterpret_cast<uint4*>(p.C + off + j) = w;
+                            }
+                        } else {
+                            for (int j = 0; j < nv; j += 2) {
+                                const uint32_t old = *reinterpret_cast<const uint32_t*>(p.C + off + j);
+                                *reinterpret_cast<uint32_t*>(p.C + off + j) =
+                                    pack_bf16(bf16lo(old) + round_bf16(v[j]), bf16hi(old) + round_bf16(v[j + 1]));
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (*abort_s != 0 && threadIdx.x == 0 && error != nullptr) atomicExch(error, 1);
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+}  // namespace efm

@@ -13,11 +13,14 @@
 //             SwiGlu           act = bf16(silu(gate) * up)          (fused_gate_up_activation_op.cu:198-277)
 //             Logits           fp32 logits + per-block (max, argmax) (src/layers/linear.cu:187-270)
 //
-// Bound: HBM.  Each weight byte is read once, as 128-bit streaming loads, 16 loads in flight per
-// lane; activations live in shared memory; dot products reduce with warp shuffles (and, when
-// KSPLIT warps share one row group, a shared-memory exchange).  The first batch of weight
-// loads is issued BEFORE griddepcontrol.wait, so that it overlaps the tail of the previous
-// kernel when launched with programmatic dependent launch.
+// Bound: HBM.  One block of 16 warps per SM.  Each weight byte is read once, as 128-bit streaming
+// loads.  A warp (or `ks` warps sharing one row pair) walks its rows in units of 8 x 2 loads: 16
+// loads of 16 bytes in flight per lane, ~19 MB chip-wide, which is what it takes to cover the
+// ~2 us loaded DRAM latency at full bandwidth (halving it to 8 measurably costs 20 %).  Activations
+// live in shared memory; dot products reduce with warp shuffles (and a named-barrier exchange
+// when ks > 1).  The first unit and the norm weight are fetched BEFORE the dependency wait
+// (griddepcontrol.wait, or the grid barrier of the persistent decode kernel), because weights
+// do not depend on the previous phase.
 #pragma once
 #include "common.cuh"
 
@@ -131,93 +134,116 @@ __device__ __forceinline__ void item_epilogue(const GemvParams& p, int item, flo
     }
 }
 
-// 256 threads; ITEMS row pairs per group iteration; KSPLIT warps share one group.
-template <Epi EPI, int ITEMS, int KSPLIT>
-__global__ void __launch_bounds__(256, 2) gemv_kernel(const GemvParams p) {
-    constexpr int ROWS = ITEMS * 2, U = 8 / ITEMS, GP = 8 / KSPLIT;
-    extern __shared__ __align__(16) unsigned char gemv_smem[];
-    const size_t xbytes = ((size_t)p.K * 2 + 15) & ~(size_t)15;
-    __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(gemv_smem);                 // activations [K]
-    __nv_bfloat16* gs = reinterpret_cast<__nv_bfloat16*>(gemv_smem + xbytes);        // norm weight [K]
-    float* red = reinterpret_cast<float*>(gemv_smem + 2 * xbytes);                    // [2][8][ROWS]
-    float* misc = red + 2 * 8 * ROWS;                                                            // [16]
+constexpr int kGemvThreads = 512, kGemvWarps = 16, kGemvU = 8;
 
+struct GemvRegs { uint4 a[kGemvU][2]; };
+
+// Per-thread view of the static schedule: which row pairs (items) this warp group walks and in
+// how many units.
+struct GemvSched {
+    int ks, gi, wk, gl, stride, nch, upi, ig0, ig_stride, total;
+};
+
+__device__ __forceinline__ GemvSched gemv_sched(const GemvParams& p, const int ks, const int block, const int n_blocks) {
+    GemvSched sc;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int gp = kGemvWarps / ks;
+    sc.ks = ks;
+    sc.gi = warp / ks;
+    sc.wk = warp % ks;
+    sc.gl = sc.wk * 32 + lane;
+    sc.stride = ks * 32;
+    sc.nch = p.K >> 3;
+    const int cpl = (sc.nch + sc.stride - 1) / sc.stride;        // chunks per lane and row
+    sc.upi = (cpl + kGemvU - 1) / kGemvU;                         // units per item
+    sc.ig0 = block * gp + sc.gi;
+    sc.ig_stride = n_blocks * gp;
+    const int n_my = sc.ig0 < p.n_items ? (p.n_items - sc.ig0 + sc.ig_stride - 1) / sc.ig_stride : 0;
+    sc.total = n_my * sc.upi;
+    return sc;
+}
+
+template <Epi EPI>
+__device__ __forceinline__ void gemv_load_unit(const GemvParams& p, const GemvSched& sc, const int u, uint4 (&buf)[kGemvU][2]) {
+    if (u >= sc.total) return;
+    const int j = u / sc.upi, part = u - j * sc.upi;
+    int r0, r1;
+    item_rows<EPI>(p, sc.ig0 + j * sc.ig_stride, r0, r1);
+    const __nv_bfloat16* a = p.W + (size_t)r0 * p.K;
+    const __nv_bfloat16* b = p.W + (size_t)r1 * p.K;
+#pragma unroll
+    for (int uu = 0; uu < kGemvU; ++uu) {
+        const int c = (part * kGemvU + uu) * sc.stride + sc.gl;
+        if (c < sc.nch) {
+            buf[uu][0] = ld_stream(a + (size_t)c * 8);
+            buf[uu][1] = ld_stream(b + (size_t)c * 8);
+        }
+    }
+}
+
+// Weights only: the first two units into registers, the norm weight into shared memory.
+template <Epi EPI>
+__device__ __forceinline__ void gemv_prefetch(const GemvParams& p, const GemvSched& sc, GemvRegs& r, unsigned char* smem,
+                                              const unsigned int xbytes) {
+    gemv_load_unit<EPI>(p, sc, 0, r.a);
+    if (p.prologue != kProPlain) {
+        uint4* gs = reinterpret_cast<uint4*>(smem + xbytes);
+        for (int c = threadIdx.x; c < sc.nch; c += kGemvThreads) gs[c] = ld_cached(p.norm_w + (size_t)c * 8);
+    }
+}
+
+// Stage activations (with the fused norm), stream the rows, reduce, epilogue.
+// smem: [xs: xbytes][norm weight: xbytes][red: 2 x 16 x 2 floats][misc: 16 floats]
+template <Epi EPI>
+__device__ __forceinline__ void gemv_run(const GemvParams& p, const GemvSched& sc, GemvRegs& r, unsigned char* smem,
+                                         const unsigned int xbytes, float& best_v, int& best_i) {
+    __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem);
+    const uint4* gs = reinterpret_cast<const uint4*>(smem + xbytes);
+    float* red = reinterpret_cast<float*>(smem + 2 * xbytes);
+    float* misc = red + 2 * kGemvWarps * 2;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int gi = warp / KSPLIT, wk = warp % KSPLIT;
-    const int gl = wk * 32 + lane, stride = KSPLIT * 32;
-    const int nch = p.K >> 3;
-    const int n_ig = (p.n_items + ITEMS - 1) / ITEMS;
-    const int ig_stride = gridDim.x * GP;
-    int ig = blockIdx.x * GP + gi;
+    const int nch = sc.nch;
 
-    const __nv_bfloat16* rowp[ROWS];
-    uint4 wv[U][ROWS];
-    auto set_rows = [&](int g) {
-#pragma unroll
-        for (int it = 0; it < ITEMS; ++it) {
-            int item = g * ITEMS + it;
-            if (item >= p.n_items) item = p.n_items - 1;   // duplicate work, result discarded
-            int r0, r1;
-            item_rows<EPI>(p, item, r0, r1);
-            rowp[2 * it] = p.W + (size_t)r0 * p.K;
-            rowp[2 * it + 1] = p.W + (size_t)r1 * p.K;
-        }
-    };
-    auto load_batch = [&](int cb) {
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int c = cb + u * stride + gl;
-            if (c < nch) {
-#pragma unroll
-                for (int r = 0; r < ROWS; ++r) wv[u][r] = ld_stream(rowp[r] + (size_t)c * 8);
-            }
-        }
-    };
-
-    // Let the next kernel of the step start its own weight prefetch as soon as every block of
-    // this one is resident, then prefetch (independent of every earlier kernel), then wait.
-    pdl_launch_dependents();
-    if (ig < n_ig) { set_rows(ig); load_batch(0); }
-    if (p.prologue != kProPlain)          // the norm weight is a weight too: stage it before waiting
-        for (int c = tid; c < nch; c += 256)
-            reinterpret_cast<uint4*>(gs)[c] = ld_cached(p.norm_w + (size_t)c * 8);
-    pdl_wait();
-
-    // ---- prologue: stage the activation vector in shared memory -------------------------
+    // residual pair of the first item, fetched under the weight stream
+    uint32_t old_first = 0u;
+    if constexpr (EPI == Epi::Residual) {
+        if (sc.wk == 0 && lane == 0 && sc.total > 0)
+            old_first = __ldcg(reinterpret_cast<const unsigned int*>(p.residual + sc.ig0 * 2));
+    }
+    // ---- activations (L2 loads: another block may have produced them) ------------------------
     if (p.prologue == kProPlain) {
-        for (int c = tid; c < nch; c += 256)
-            reinterpret_cast<uint4*>(xs)[c] = ld_cached(p.x + (size_t)c * 8);
+        for (int c = tid; c < nch; c += kGemvThreads) reinterpret_cast<uint4*>(xs)[c] = ld_cg(p.x + (size_t)c * 8);
     } else {
         const __nv_bfloat16* src = p.x;
-        bool zero = false;
+        bool zero = false, from_table = false;
         if (p.prologue == kProEmbedRmsNorm) {
             const int tok = p.state->token;
             zero = tok < 0 || tok >= p.vocab;
             src = p.embed_table + (size_t)(zero ? 0 : tok) * p.K;
+            from_table = true;
         }
         float ss = 0.f;
-        for (int c = tid; c < nch; c += 256) {
-            uint4 v = zero ? make_uint4(0, 0, 0, 0) : ld_cached(src + (size_t)c * 8);
+        for (int c = tid; c < nch; c += kGemvThreads) {
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (!zero) v = from_table ? ld_cached(src + (size_t)c * 8) : ld_cg(src + (size_t)c * 8);
             float f[8];
             unpack8(v, f);
 #pragma unroll
             for (int j = 0; j < 8; ++j) ss = fmaf(f[j], f[j], ss);
-            if (p.prologue == kProEmbedRmsNorm && blockIdx.x == 0)
-                reinterpret_cast<uint4*>(p.resid_out)[c] = v;
+            reinterpret_cast<uint4*>(xs)[c] = v;
+            if (from_table && blockIdx.x == 0) reinterpret_cast<uint4*>(p.resid_out)[c] = v;
         }
         ss = warp_sum(ss);
         if (lane == 0) misc[warp] = ss;
         __syncthreads();
         float tot = 0.f;
 #pragma unroll
-        for (int w = 0; w < 8; ++w) tot += misc[w];
+        for (int w = 0; w < kGemvWarps; ++w) tot += misc[w];
         const float inv = 1.0f / sqrtf(tot / (float)p.K + p.eps);
-        for (int c = tid; c < nch; c += 256) {
-            uint4 v = zero ? make_uint4(0, 0, 0, 0) : ld_cached(src + (size_t)c * 8);
-            const uint4 g = reinterpret_cast<const uint4*>(gs)[c];      // written by this same thread
+        for (int c = tid; c < nch; c += kGemvThreads) {       // same thread, same chunks as above
             float f[8], w[8];
-            unpack8(v, f);
-            unpack8(g, w);
+            unpack8(reinterpret_cast<const uint4*>(xs)[c], f);
+            unpack8(gs[c], w);
             uint4 o;
             o.x = pack_bf16(f[0] * inv * w[0], f[1] * inv * w[1]);
             o.y = pack_bf16(f[2] * inv * w[2], f[3] * inv * w[3]);
@@ -228,85 +254,97 @@ __global__ void __launch_bounds__(256, 2) gemv_kernel(const GemvParams p) {
     }
     __syncthreads();
 
-    // ---- main loop ----------------------------------------------------------------------
-    float best_v = -INFINITY;
-    int best_i = 0x7fffffff;
-    bool first = true;
+    // ---- rows ------------------------------------------------------------------------------------
+    float acc0 = 0.f, acc1 = 0.f;
     int parity = 0;
-    for (; ig < n_ig; ig += ig_stride) {
-        if (!first) set_rows(ig);
-        float acc[ROWS];
+    auto compute_unit = [&](const int u, const uint4 (&buf)[kGemvU][2]) {
+        const int j = u / sc.upi, part = u - j * sc.upi;
 #pragma unroll
-        for (int r = 0; r < ROWS; ++r) acc[r] = 0.f;
-        for (int cb = 0; cb < nch; cb += U * stride) {
-            if (!(first && cb == 0)) load_batch(cb);
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const int c = cb + u * stride + gl;
-                if (c < nch) {
-                    float xf[8];
-                    unpack8(reinterpret_cast<const uint4*>(xs)[c], xf);
-#pragma unroll
-                    for (int r = 0; r < ROWS; ++r) acc[r] = dot8(wv[u][r], xf, acc[r]);
-                }
+        for (int uu = 0; uu < kGemvU; ++uu) {
+            const int c = (part * kGemvU + uu) * sc.stride + sc.gl;
+            if (c < nch) {
+                float xf[8];
+                unpack8(reinterpret_cast<const uint4*>(xs)[c], xf);
+                acc0 = dot8(buf[uu][0], xf, acc0);
+                acc1 = dot8(buf[uu][1], xf, acc1);
             }
         }
-        first = false;
-#pragma unroll
-        for (int r = 0; r < ROWS; ++r) acc[r] = warp_sum(acc[r]);
-        if constexpr (KSPLIT > 1) {
-            float* buf = red + parity * 8 * ROWS;
-            if (lane == 0) {
-#pragma unroll
-                for (int r = 0; r < ROWS; ++r) buf[warp * ROWS + r] = acc[r];
-            }
-            group_barrier(1 + gi, KSPLIT * 32);
-            if (wk == 0) {
-#pragma unroll
-                for (int r = 0; r < ROWS; ++r) {
-                    float t = 0.f;
-#pragma unroll
-                    for (int w = 0; w < KSPLIT; ++w) t += buf[(gi * KSPLIT + w) * ROWS + r];
-                    acc[r] = t;
-                }
+        if (part != sc.upi - 1) return;
+        // item complete
+        const int ig = sc.ig0 + j * sc.ig_stride;
+        float t0 = warp_sum(acc0), t1 = warp_sum(acc1);
+        acc0 = 0.f;
+        acc1 = 0.f;
+        if (sc.ks > 1) {
+            float* buf2 = red + parity * kGemvWarps * 2;
+            if (lane == 0) { buf2[warp * 2] = t0; buf2[warp * 2 + 1] = t1; }
+            group_barrier(1 + sc.gi, sc.ks * 32);
+            if (sc.wk == 0) {
+                t0 = 0.f;
+                t1 = 0.f;
+                for (int w = 0; w < sc.ks; ++w) { t0 += buf2[(sc.gi * sc.ks + w) * 2]; t1 += buf2[(sc.gi * sc.ks + w) * 2 + 1]; }
             }
             parity ^= 1;
         }
-        if (wk == 0) {
-#pragma unroll
-            for (int it = 0; it < ITEMS; ++it) {
-                const int item = ig * ITEMS + it;
-                if (lane == it && item < p.n_items)
-                    item_epilogue<EPI>(p, item, acc[2 * it], acc[2 * it + 1], best_v, best_i);
+        if (sc.wk == 0 && lane == 0) {
+            if constexpr (EPI == Epi::Residual) {
+                const uint32_t old = j == 0 ? old_first : __ldcg(reinterpret_cast<const unsigned int*>(p.residual + ig * 2));
+                *reinterpret_cast<uint32_t*>(p.residual + ig * 2) =
+                    pack_bf16(bf16lo(old) + round_bf16(t0), bf16hi(old) + round_bf16(t1));
+            } else {
+                item_epilogue<EPI>(p, ig, t0, t1, best_v, best_i);
             }
         }
-    }
-
-    if constexpr (EPI == Epi::Logits) {
-        // lanes 0..ITEMS-1 of the wk==0 warps hold candidates; reduce to one per block
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, best_v, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
-            if (ov > best_v || (ov == best_v && oi < best_i)) { best_v = ov; best_i = oi; }
-        }
-        __shared__ float bv[8];
-        __shared__ int bi[8];
-        if (lane == 0) { bv[warp] = best_v; bi[warp] = best_i; }
-        __syncthreads();
-        if (tid == 0) {
-            float v = bv[0];
-            int i = bi[0];
-            for (int w = 1; w < 8; ++w)
-                if (bv[w] > v || (bv[w] == v && bi[w] < i)) { v = bv[w]; i = bi[w]; }
-            p.part_val[blockIdx.x] = v;
-            p.part_idx[blockIdx.x] = i;
-        }
+    };
+    for (int u = 0; u < sc.total; ++u) {
+        if (u > 0) gemv_load_unit<EPI>(p, sc, u, r.a);       // unit 0 was fetched before the dependency wait
+        compute_unit(u, r.a);
     }
 }
 
-inline size_t gemv_smem_bytes(int K, int items) {
-    return 2 * (((size_t)K * 2 + 15) & ~(size_t)15) + (size_t)(2 * 8 * items * 2 + 16) * sizeof(float);
+// Per-block (max, argmax) of the Logits epilogue -> part_val / part_idx[block].
+__device__ __forceinline__ void gemv_publish_best(const GemvParams& p, float best_v, int best_i, float* bv, int* bi) {
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best_v, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+        if (ov > best_v || (ov == best_v && oi < best_i)) { best_v = ov; best_i = oi; }
+    }
+    if (lane == 0) { bv[warp] = best_v; bi[warp] = best_i; }
+    __syncthreads();
+    if (tid == 0) {
+        float v = bv[0];
+        int i = bi[0];
+        for (int w = 1; w < kGemvWarps; ++w)
+            if (bv[w] > v || (bv[w] == v && bi[w] < i)) { v = bv[w]; i = bi[w]; }
+        p.part_val[blockIdx.x] = v;
+        p.part_idx[blockIdx.x] = i;
+    }
+}
+
+// One GEMV phase as its own launch (phase-per-launch decode form, prefill lm_head, operator API).
+template <Epi EPI>
+__global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams p, const int ks) {
+    extern __shared__ __align__(16) unsigned char gemv_smem[];
+    __shared__ float bv[kGemvWarps];
+    __shared__ int bi[kGemvWarps];
+    const unsigned int xbytes = ((unsigned int)p.K * 2 + 15) & ~15u;
+    GemvRegs regs;
+    float best_v = -INFINITY;
+    int best_i = 0x7fffffff;
+    // Let the next kernel of the step start its own weight prefetch as soon as every block of this
+    // one is resident, then prefetch (independent of every earlier kernel), then wait.
+    pdl_launch_dependents();
+    const GemvSched sc = gemv_sched(p, ks, blockIdx.x, gridDim.x);
+    gemv_prefetch<EPI>(p, sc, regs, gemv_smem, xbytes);
+    pdl_wait();
+    gemv_run<EPI>(p, sc, regs, gemv_smem, xbytes, best_v, best_i);
+    if constexpr (EPI == Epi::Logits) gemv_publish_best(p, best_v, best_i, bv, bi);
+}
+
+inline size_t gemv_smem_bytes(int K) {
+    return 2 * (((size_t)K * 2 + 15) & ~(size_t)15) + (size_t)(2 * kGemvWarps * 2 + 16) * sizeof(float);
 }
 
 }  // namespace efm

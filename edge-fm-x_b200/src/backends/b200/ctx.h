@@ -40,7 +40,17 @@ struct KvSlot {
 }  // namespace efm
 
 struct efm_b200_ctx {
-    efm_model_desc d{};
+    efm_model_desc d{};                   // geometry as THIS RANK sees it (heads / MLP columns already sharded)
+    efm_model_desc full{};                // geometry of the whole model (weight slicing)
+    // tensor parallel layout: attention is sharded att_shards ways (each shard held by att_rep ranks,
+    // which split the o_proj input columns between them); MLP columns and lm_head rows tp_size ways
+    int att_shards = 1, att_rep = 1, att_shard = 0, att_rep_idx = 0;
+    int o_k = 0;                          // o_proj input columns handled by this rank
+    int vocab_l = 0, vocab_off = 0;       // lm_head rows of this rank
+    void* nccl_comm = nullptr;
+    float* ybuf = nullptr;                // [max_s, H] fp32 partial outputs of row-parallel linears
+    float* ysum = nullptr;                // [max_s, H] their sum over ranks
+    float* logits_l = nullptr;            // [vocab_l]
     int device = 0, tp_rank = 0, tp_size = 1, num_sms = 148;
     cudaStream_t stream = nullptr;
     std::string error;
@@ -72,6 +82,7 @@ struct efm_b200_ctx {
     __nv_bfloat16* custom_embeds = nullptr;
     size_t custom_embeds_cap = 0;
     __nv_bfloat16* resid_d = nullptr;     // decode residual stream [H]
+    __nv_bfloat16* resid_d2 = nullptr;    // second copy (tensor parallel: the add-and-norm prologue ping-pongs)
     __nv_bfloat16* q_d = nullptr;         // [q*D]
     __nv_bfloat16* attn_d = nullptr;      // [q*D]
     __nv_bfloat16* act_d = nullptr;       // [I]

@@ -10,11 +10,12 @@
 
 #include "../../layers/launch.cuh"
 #include "../../layers/qwen_text.h"
-#include "../../operators/gemm_mma.cuh"
+#include "../../operators/gemm_tc.cuh"
 #define EFM_DECLARATIONS_ONLY
 #include "../../operators/sample.cuh"
 #undef EFM_DECLARATIONS_ONLY
 #include "ctx.h"
+#include "nccl_glue.h"
 
 using namespace efm;
 
@@ -112,7 +113,15 @@ efm_status efm_b200_create(const efm_model_desc* desc, int32_t device_id, int32_
         return fail(nullptr, EFM_ERR_UNSUPPORTED, "hidden % 32, intermediate % 64 and vocab % 2 must be 0");
     if (d.use_mrope && d.mrope_section[0] + d.mrope_section[1] + d.mrope_section[2] != d.head_dim / 2)
         return fail(nullptr, EFM_ERR_INVALID_ARGUMENT, "mrope_section must sum to head_dim / 2");
-    if (tp_size != 1 || tp_rank != 0) return fail(nullptr, EFM_ERR_UNSUPPORTED, "tensor parallel size > 1 is not built yet");
+    if (tp_size < 1 || tp_rank < 0 || tp_rank >= tp_size) return fail(nullptr, EFM_ERR_INVALID_ARGUMENT, "bad tensor-parallel coordinates");
+    // heads are sharded min(tp, kv_heads) ways; beyond that, ranks pair up on a head shard and split o_proj's input
+    const int att_shards = std::min(tp_size, d.kv_heads);
+    if (tp_size % att_shards != 0 || d.kv_heads % att_shards != 0 || d.q_heads % att_shards != 0)
+        return fail(nullptr, EFM_ERR_UNSUPPORTED, "tensor-parallel size must divide (or be a multiple of) the kv head count");
+    const int att_rep = tp_size / att_shards;
+    if (d.intermediate % (64 * tp_size) != 0 || d.vocab % (2 * tp_size) != 0 ||
+        ((d.q_heads / att_shards) * d.head_dim) % (32 * att_rep) != 0)
+        return fail(nullptr, EFM_ERR_UNSUPPORTED, "intermediate / vocab / attention width do not split evenly over the ranks");
     if (d.max_prefill_tokens <= 0 || d.max_response_tokens <= 0)
         return fail(nullptr, EFM_ERR_INVALID_ARGUMENT, "max_prefill_tokens and max_response_tokens must be positive");
     efm_status st = require_b200(nullptr, device_id);
@@ -120,7 +129,18 @@ efm_status efm_b200_create(const efm_model_desc* desc, int32_t device_id, int32_
 
     efm_b200_ctx* c = new (std::nothrow) efm_b200_ctx();
     if (c == nullptr) return fail(nullptr, EFM_ERR_OUT_OF_MEMORY, "host allocation failed");
+    c->full = d;
     c->d = d;
+    c->d.q_heads = d.q_heads / att_shards;
+    c->d.kv_heads = d.kv_heads / att_shards;
+    c->d.intermediate = d.intermediate / tp_size;
+    c->att_shards = att_shards;
+    c->att_rep = att_rep;
+    c->att_shard = tp_rank / att_rep;
+    c->att_rep_idx = tp_rank % att_rep;
+    c->o_k = c->d.q_heads * d.head_dim / att_rep;
+    c->vocab_l = d.vocab / tp_size;
+    c->vocab_off = tp_rank * c->vocab_l;
     c->device = device_id;
     c->tp_rank = tp_rank;
     c->tp_size = tp_size;
@@ -139,10 +159,18 @@ efm_status efm_b200_create(const efm_model_desc* desc, int32_t device_id, int32_
     EFM_TRY(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
     for (auto& ev : c->events) EFM_TRY(cudaEventCreate(&ev));
 
-    const size_t H = d.hidden, D = d.head_dim, QD = (size_t)d.q_heads * D, KVD = (size_t)d.kv_heads * D, I = d.intermediate,
-                 V = d.vocab, S = d.max_prefill_tokens;
+    const efm_model_desc& dl = c->d;
+    const size_t H = dl.hidden, D = dl.head_dim, QD = (size_t)dl.q_heads * D, KVD = (size_t)dl.kv_heads * D, I = dl.intermediate,
+                 V = dl.vocab, S = dl.max_prefill_tokens;
     EFM_TRY(dev_alloc(c, &c->embed, V * H, false));
-    if (d.tied_lm_head) c->lm_head = c->embed; else EFM_TRY(dev_alloc(c, &c->lm_head, V * H, false));
+    if (d.tied_lm_head) c->lm_head = c->embed + (size_t)c->vocab_off * H;      // this rank's rows of the shared table
+    else EFM_TRY(dev_alloc(c, &c->lm_head, (size_t)c->vocab_l * H, false));
+    if (tp_size > 1) {
+        c->mega = false;      // the persistent decode kernel has no collective phase
+        EFM_TRY(dev_alloc(c, &c->ybuf, S * H));
+        EFM_TRY(dev_alloc(c, &c->ysum, S * H));
+        EFM_TRY(dev_alloc(c, &c->logits_l, (size_t)c->vocab_l));
+    }
     EFM_TRY(dev_alloc(c, &c->final_norm, H));
     c->layers.resize(d.num_layers);
     for (auto& w : c->layers) {
@@ -150,7 +178,7 @@ efm_status efm_b200_create(const efm_model_desc* desc, int32_t device_id, int32_
         EFM_TRY(dev_alloc(c, &w.post_norm, H));
         EFM_TRY(dev_alloc(c, &w.qkv, (QD + 2 * KVD) * H, false));
         EFM_TRY(dev_alloc(c, &w.qkv_bias, QD + 2 * KVD));
-        EFM_TRY(dev_alloc(c, &w.o, H * QD, false));
+        EFM_TRY(dev_alloc(c, &w.o, H * (size_t)c->o_k, false));
         EFM_TRY(dev_alloc(c, &w.gate_up, 2 * I * H, false));
         EFM_TRY(dev_alloc(c, &w.down, H * I, false));
     }
@@ -172,6 +200,7 @@ efm_status efm_b200_create(const efm_model_desc* desc, int32_t device_id, int32_
     EFM_TRY(dev_alloc(c, &c->gu, S * 2 * I));
     EFM_TRY(dev_alloc(c, &c->act, S * I));
     EFM_TRY(dev_alloc(c, &c->resid_d, H));
+    EFM_TRY(dev_alloc(c, &c->resid_d2, H));
     EFM_TRY(dev_alloc(c, &c->q_d, QD));
     EFM_TRY(dev_alloc(c, &c->attn_d, QD));
     EFM_TRY(dev_alloc(c, &c->act_d, I));
@@ -179,9 +208,9 @@ efm_status efm_b200_create(const efm_model_desc* desc, int32_t device_id, int32_
     EFM_TRY(dev_alloc(c, &c->part_val, 2 * (size_t)c->num_sms + 8));
     EFM_TRY(dev_alloc(c, &c->part_idx, 2 * (size_t)c->num_sms + 8));
     EFM_TRY(dev_alloc(c, &c->wbuf, V));
-    EFM_TRY(dev_alloc(c, &c->attn_part_o, (size_t)d.q_heads * 64 * D));
-    EFM_TRY(dev_alloc(c, &c->attn_part_ml, (size_t)d.q_heads * 64 * 2));
-    EFM_TRY(dev_alloc(c, &c->attn_counters, (size_t)d.kv_heads));
+    EFM_TRY(dev_alloc(c, &c->attn_part_o, (size_t)dl.q_heads * 64 * D));
+    EFM_TRY(dev_alloc(c, &c->attn_part_ml, (size_t)dl.q_heads * 64 * 2));
+    EFM_TRY(dev_alloc(c, &c->attn_counters, (size_t)dl.kv_heads));
     EFM_TRY(dev_alloc(c, &c->mega_barrier, 4));
     EFM_TRY(dev_alloc(c, &c->mega_timing, (size_t)5 * d.num_layers + 8));
     {
@@ -203,13 +232,35 @@ efm_status efm_b200_destroy(efm_b200_ctx* c) {
     if (c == nullptr) return EFM_OK;
     cudaSetDevice(c->device);
     if (c->stream != nullptr) cudaStreamSynchronize(c->stream);
-    for (auto& kv : c->slots)
+    for (auto& kv : c->slots)      // graphs that hold collective nodes go before their communicator
         if (kv.second.graph != nullptr) cudaGraphExecDestroy(kv.second.graph);
+    if (c->nccl_comm != nullptr && nccl_api().ok) nccl_api().comm_destroy(c->nccl_comm);
     for (void* p : c->allocations) cudaFree(p);
     for (auto& ev : c->events)
         if (ev != nullptr) cudaEventDestroy(ev);
     if (c->stream != nullptr) cudaStreamDestroy(c->stream);
     delete c;
+    return EFM_OK;
+}
+
+efm_status efm_b200_tp_unique_id(void* out128) {
+    if (out128 == nullptr) return fail(nullptr, EFM_ERR_INVALID_ARGUMENT, "null argument");
+    const NcclApi& api = nccl_api();
+    if (!api.ok) return fail(nullptr, EFM_ERR_UNSUPPORTED, api.error);
+    const int r = api.get_unique_id(out128);
+    if (r != 0) return fail(nullptr, EFM_ERR_CUDA, std::string("ncclGetUniqueId: ") + api.error_string(r));
+    return EFM_OK;
+}
+
+efm_status efm_b200_tp_init(efm_b200_ctx* c, const void* id128) {
+    if (c == nullptr || id128 == nullptr) return fail(c, EFM_ERR_INVALID_ARGUMENT, "null argument");
+    if (c->tp_size == 1) return EFM_OK;
+    if (c->nccl_comm != nullptr) return fail(c, EFM_ERR_STATE, "communicator already initialised");
+    const NcclApi& api = nccl_api();
+    if (!api.ok) return fail(c, EFM_ERR_UNSUPPORTED, api.error);
+    EFM_CK(c, cudaSetDevice(c->device));
+    const int r = api.comm_init_rank(&c->nccl_comm, c->tp_size, id128, c->tp_rank);
+    if (r != 0) { c->nccl_comm = nullptr; return fail(c, EFM_ERR_CUDA, std::string("ncclCommInitRank: ") + api.error_string(r)); }
     return EFM_OK;
 }
 
@@ -219,9 +270,17 @@ efm_status efm_b200_set_weight(efm_b200_ctx* c, const char* hf_name, const void*
         return fail(c, EFM_ERR_INVALID_ARGUMENT, "null argument");
     if (c->finalized) return fail(c, EFM_ERR_STATE, "weights are already finalized");
     EFM_CK(c, cudaSetDevice(c->device));
-    const efm_model_desc& d = c->d;
-    const int64_t H = d.hidden, D = d.head_dim, QD = d.q_heads * D, KVD = d.kv_heads * D, I = d.intermediate, V = d.vocab;
+    // The caller always hands over the WHOLE tensor; this rank keeps its slice: q/k/v rows of its head
+    // shard, its o_proj input columns, its gate/up rows and down columns, its lm_head rows.
+    const efm_model_desc& d = c->d;          // local
+    const efm_model_desc& F = c->full;       // whole model
+    const int64_t H = d.hidden, D = d.head_dim, I = d.intermediate, V = d.vocab;
+    const int64_t QD = d.q_heads * D, KVD = d.kv_heads * D;              // local widths
+    const int64_t FQD = F.q_heads * D, FKVD = F.kv_heads * D, FI = F.intermediate;
+    const int64_t q_off = (int64_t)c->att_shard * QD, kv_off = (int64_t)c->att_shard * KVD, i_off = (int64_t)c->tp_rank * I;
     const std::string name(hf_name);
+    const char* src = static_cast<const char*>(data);
+    const cudaMemcpyKind kind = mem_kind == EFM_MEM_DEVICE ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice;
     auto bad_shape = [&]() { return fail(c, EFM_ERR_INVALID_ARGUMENT, "unexpected shape for " + name); };
     auto known = [&]() -> efm_status {
         if (dtype != EFM_BF16) return fail(c, EFM_ERR_UNSUPPORTED, "weights must be bf16: " + name);
@@ -236,7 +295,7 @@ efm_status efm_b200_set_weight(efm_b200_ctx* c, const char* hf_name, const void*
     } else if (name == "lm_head.weight") {
         if ((st = known()) != EFM_OK) return st;
         if (!shape_is(shape, ndim, V, H)) return bad_shape();
-        if (!d.tied_lm_head) st = copy_rows(c, c->lm_head, data, (size_t)V * H * 2, mem_kind);
+        if (!d.tied_lm_head) st = copy_rows(c, c->lm_head, src + (size_t)c->vocab_off * H * 2, (size_t)c->vocab_l * H * 2, mem_kind);
         c->seen_lm_head = true;
     } else if (name == "model.norm.weight") {
         if ((st = known()) != EFM_OK) return st;
@@ -250,7 +309,6 @@ efm_status efm_b200_set_weight(efm_b200_ctx* c, const char* hf_name, const void*
         if (l < 0 || l >= d.num_layers) return EFM_OK;      // e.g. extra layers of a draft model: ignored
         const std::string rest = name.substr(dot + 1);
         LayerWeights& w = c->layers[l];
-        struct Spec { const char* n; uint32_t bit; };
         if ((st = known()) != EFM_OK) return st;
         const size_t rowb = (size_t)H * 2;
         if (rest == "input_layernorm.weight") {
@@ -260,36 +318,42 @@ efm_status efm_b200_set_weight(efm_b200_ctx* c, const char* hf_name, const void*
             if (!shape_is(shape, ndim, H)) return bad_shape();
             st = copy_rows(c, w.post_norm, data, rowb, mem_kind); w.seen |= kPostNorm;
         } else if (rest == "self_attn.q_proj.weight") {
-            if (!shape_is(shape, ndim, QD, H)) return bad_shape();
-            st = copy_rows(c, w.qkv, data, (size_t)QD * rowb, mem_kind); w.seen |= kQw;
+            if (!shape_is(shape, ndim, FQD, H)) return bad_shape();
+            st = copy_rows(c, w.qkv, src + (size_t)q_off * rowb, (size_t)QD * rowb, mem_kind); w.seen |= kQw;
         } else if (rest == "self_attn.k_proj.weight") {
-            if (!shape_is(shape, ndim, KVD, H)) return bad_shape();
-            st = copy_rows(c, w.qkv + QD * H, data, (size_t)KVD * rowb, mem_kind); w.seen |= kKw;
+            if (!shape_is(shape, ndim, FKVD, H)) return bad_shape();
+            st = copy_rows(c, w.qkv + QD * H, src + (size_t)kv_off * rowb, (size_t)KVD * rowb, mem_kind); w.seen |= kKw;
         } else if (rest == "self_attn.v_proj.weight") {
-            if (!shape_is(shape, ndim, KVD, H)) return bad_shape();
-            st = copy_rows(c, w.qkv + (QD + KVD) * H, data, (size_t)KVD * rowb, mem_kind); w.seen |= kVw;
+            if (!shape_is(shape, ndim, FKVD, H)) return bad_shape();
+            st = copy_rows(c, w.qkv + (QD + KVD) * H, src + (size_t)kv_off * rowb, (size_t)KVD * rowb, mem_kind); w.seen |= kVw;
         } else if (rest == "self_attn.q_proj.bias") {
-            if (!shape_is(shape, ndim, QD)) return bad_shape();
-            st = copy_rows(c, w.qkv_bias, data, (size_t)QD * 2, mem_kind); w.seen |= kQb;
+            if (!shape_is(shape, ndim, FQD)) return bad_shape();
+            st = copy_rows(c, w.qkv_bias, src + (size_t)q_off * 2, (size_t)QD * 2, mem_kind); w.seen |= kQb;
         } else if (rest == "self_attn.k_proj.bias") {
-            if (!shape_is(shape, ndim, KVD)) return bad_shape();
-            st = copy_rows(c, w.qkv_bias + QD, data, (size_t)KVD * 2, mem_kind); w.seen |= kKb;
+            if (!shape_is(shape, ndim, FKVD)) return bad_shape();
+            st = copy_rows(c, w.qkv_bias + QD, src + (size_t)kv_off * 2, (size_t)KVD * 2, mem_kind); w.seen |= kKb;
         } else if (rest == "self_attn.v_proj.bias") {
-            if (!shape_is(shape, ndim, KVD)) return bad_shape();
-            st = copy_rows(c, w.qkv_bias + QD + KVD, data, (size_t)KVD * 2, mem_kind); w.seen |= kVb;
+            if (!shape_is(shape, ndim, FKVD)) return bad_shape();
+            st = copy_rows(c, w.qkv_bias + QD + KVD, src + (size_t)kv_off * 2, (size_t)KVD * 2, mem_kind); w.seen |= kVb;
         } else if (rest == "self_attn.o_proj.weight") {
-            if (!shape_is(shape, ndim, H, QD)) return bad_shape();
-            st = copy_rows(c, w.o, data, (size_t)H * QD * 2, mem_kind); w.seen |= kO;
+            if (!shape_is(shape, ndim, H, FQD)) return bad_shape();
+            // this rank's input columns: its head shard, then its share of the shard when ranks pair up
+            const int64_t col0 = q_off + (int64_t)c->att_rep_idx * c->o_k;
+            EFM_CK(c, cudaMemcpy2DAsync(w.o, (size_t)c->o_k * 2, src + (size_t)col0 * 2, (size_t)FQD * 2, (size_t)c->o_k * 2,
+                                        (size_t)H, kind, c->stream));
+            w.seen |= kO;
         } else if (rest == "mlp.gate_proj.weight" || rest == "mlp.up_proj.weight") {
-            if (!shape_is(shape, ndim, I, H)) return bad_shape();
+            if (!shape_is(shape, ndim, FI, H)) return bad_shape();
             const bool up = rest[4] == 'u';
             // 64-row blocks: gate block b -> fused rows [128b, 128b+64), up block b -> [128b+64, 128b+128)
-            EFM_CK(c, cudaMemcpy2DAsync(w.gate_up + (up ? 64 * H : 0), 128 * rowb, data, 64 * rowb, 64 * rowb, (size_t)(I / 64),
-                                        mem_kind == EFM_MEM_DEVICE ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, c->stream));
+            EFM_CK(c, cudaMemcpy2DAsync(w.gate_up + (up ? 64 * H : 0), 128 * rowb, src + (size_t)i_off * rowb, 64 * rowb, 64 * rowb,
+                                        (size_t)(I / 64), kind, c->stream));
             w.seen |= up ? kUp : kGate;
         } else if (rest == "mlp.down_proj.weight") {
-            if (!shape_is(shape, ndim, H, I)) return bad_shape();
-            st = copy_rows(c, w.down, data, (size_t)H * I * 2, mem_kind); w.seen |= kDown;
+            if (!shape_is(shape, ndim, H, FI)) return bad_shape();
+            EFM_CK(c, cudaMemcpy2DAsync(w.down, (size_t)I * 2, src + (size_t)i_off * 2, (size_t)FI * 2, (size_t)I * 2, (size_t)H, kind,
+                                        c->stream));
+            w.seen |= kDown;
         } else {
             return EFM_OK;
         }
@@ -373,6 +437,7 @@ efm_status efm_b200_prefill(efm_b200_ctx* c, int32_t slot, const int32_t* token_
                             const int32_t* pos_ids3, int32_t sample) {
     if (c == nullptr || token_ids == nullptr) return fail(c, EFM_ERR_INVALID_ARGUMENT, "null argument");
     if (!c->finalized) return fail(c, EFM_ERR_STATE, "weights not finalized");
+    if (c->tp_size > 1 && c->nccl_comm == nullptr) return fail(c, EFM_ERR_STATE, "tensor-parallel context without efm_b200_tp_init");
     auto it = c->slots.find(slot);
     if (it == c->slots.end()) return fail(c, EFM_ERR_INVALID_ARGUMENT, "unknown KV slot " + std::to_string(slot));
     KvSlot& s = it->second;

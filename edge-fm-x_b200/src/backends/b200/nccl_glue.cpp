@@ -1,0 +1,75 @@
+#include "nccl_glue.h"
+
+#include <dlfcn.h>
+#include <nccl.h>
+
+#include <cstdlib>
+#include <cstring>
+
+namespace efm {
+
+namespace {
+decltype(&ncclGetUniqueId) p_get_id = nullptr;
+decltype(&ncclCommInitRank) p_init = nullptr;
+decltype(&ncclCommDestroy) p_destroy = nullptr;
+decltype(&ncclAllReduce) p_all_reduce = nullptr;
+decltype(&ncclAllGather) p_all_gather = nullptr;
+decltype(&ncclGetErrorString) p_err = nullptr;
+
+int get_unique_id(void* id128) {
+    ncclUniqueId id;
+    const ncclResult_t r = p_get_id(&id);
+    if (r == ncclSuccess) std::memcpy(id128, &id, sizeof(id));
+    return (int)r;
+}
+int comm_init_rank(void** comm, int nranks, const void* id128, int rank) {
+    ncclUniqueId id;
+    std::memcpy(&id, id128, sizeof(id));
+    ncclComm_t c = nullptr;
+    const ncclResult_t r = p_init(&c, nranks, id, rank);
+    *comm = c;
+    return (int)r;
+}
+int comm_destroy(void* comm) { return (int)p_destroy(static_cast<ncclComm_t>(comm)); }
+int all_reduce_f32_sum(const void* send, void* recv, size_t count, void* comm, cudaStream_t stream) {
+    return (int)p_all_reduce(send, recv, count, ncclFloat32, ncclSum, static_cast<ncclComm_t>(comm), stream);
+}
+int all_gather_f32(const void* send, void* recv, size_t count, void* comm, cudaStream_t stream) {
+    return (int)p_all_gather(send, recv, count, ncclFloat32, static_cast<ncclComm_t>(comm), stream);
+}
+const char* error_string(int r) { return p_err != nullptr ? p_err(static_cast<ncclResult_t>(r)) : "nccl error"; }
+}  // namespace
+
+const NcclApi& nccl_api() {
+    static NcclApi api = [] {
+        NcclApi a;
+        static_assert(sizeof(ncclUniqueId) == 128, "unique id is 128 bytes in the C ABI");
+        const char* override_path = std::getenv("EFM_NCCL_LIB");
+        void* h = dlopen(override_path != nullptr ? override_path : "libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+        if (h == nullptr) {
+            a.error = std::string("cannot load libnccl.so.2 (set EFM_NCCL_LIB): ") + dlerror();
+            return a;
+        }
+        p_get_id = reinterpret_cast<decltype(p_get_id)>(dlsym(h, "ncclGetUniqueId"));
+        p_init = reinterpret_cast<decltype(p_init)>(dlsym(h, "ncclCommInitRank"));
+        p_destroy = reinterpret_cast<decltype(p_destroy)>(dlsym(h, "ncclCommDestroy"));
+        p_all_reduce = reinterpret_cast<decltype(p_all_reduce)>(dlsym(h, "ncclAllReduce"));
+        p_all_gather = reinterpret_cast<decltype(p_all_gather)>(dlsym(h, "ncclAllGather"));
+        p_err = reinterpret_cast<decltype(p_err)>(dlsym(h, "ncclGetErrorString"));
+        if (!p_get_id || !p_init || !p_destroy || !p_all_reduce || !p_all_gather || !p_err) {
+            a.error = "libnccl.so.2 lacks an expected symbol";
+            return a;
+        }
+        a.get_unique_id = get_unique_id;
+        a.comm_init_rank = comm_init_rank;
+        a.comm_destroy = comm_destroy;
+        a.all_reduce_f32_sum = all_reduce_f32_sum;
+        a.all_gather_f32 = all_gather_f32;
+        a.error_string = error_string;
+        a.ok = true;
+        return a;
+    }();
+    return api;
+}
+
+}  // namespace efm

@@ -1,0 +1,25 @@
+// NCCL through dlopen: single-GPU users need no NCCL at link or load time; tensor-parallel
+// contexts load libnccl.so.2 (already resident in a torch process, else from the loader path or
+// EFM_NCCL_LIB) on first use.
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+
+#include <string>
+
+namespace efm {
+
+struct NcclApi {
+    bool ok = false;
+    std::string error;
+    int (*get_unique_id)(void* id128) = nullptr;
+    int (*comm_init_rank)(void** comm, int nranks, const void* id128, int rank) = nullptr;   // wrapper, see .cpp
+    int (*comm_destroy)(void* comm) = nullptr;
+    int (*all_reduce_f32_sum)(const void* send, void* recv, size_t count, void* comm, cudaStream_t stream) = nullptr;
+    int (*all_gather_f32)(const void* send, void* recv, size_t count, void* comm, cudaStream_t stream) = nullptr;
+    const char* (*error_string)(int) = nullptr;
+};
+
+const NcclApi& nccl_api();
+
+}  // namespace efm

@@ -7,10 +7,10 @@
 // and norm + lm_head + block argmax | sampler + state advance at the end of the step.
 #include "qwen_text.h"
 
-#include "../operators/gemm_mma.cuh"
 #include "../operators/gemm_tc.cuh"
 #include "../operators/prefill.cuh"
 #include "../operators/sample.cuh"
+#include "../backends/b200/nccl_glue.h"
 #include "launch.cuh"
 
 namespace efm {
@@ -25,19 +25,30 @@ static GemvParams base_gemv(const __nv_bfloat16* W, int N, int K) {
     return p;
 }
 
+static void tp_all_reduce(efm_b200_ctx& c, Launcher& L, const float* send, float* recv, size_t count);
+static void tp_all_gather(efm_b200_ctx& c, Launcher& L, const float* send, float* recv, size_t count);
+static void launch_sample_only(efm_b200_ctx& c, Launcher& L, int n_part, int advance);
+
 void launch_sample(Launcher& L, const SampleParams& p) { L.launch(sample_kernel, dim3(1), dim3(1024), 0, p); }
 
 void launch_lm_head_and_sample(efm_b200_ctx& c, Launcher& L, const __nv_bfloat16* resid_row, int advance) {
     const efm_model_desc& d = c.d;
-    GemvParams p = base_gemv(c.lm_head, d.vocab, d.hidden);
+    GemvParams p = base_gemv(c.lm_head, c.vocab_l, d.hidden);      // this rank's rows (all of them without TP)
     p.prologue = kProRmsNorm;
     p.x = resid_row;
     p.norm_w = c.final_norm;
     p.eps = d.rms_eps;
-    p.logits = c.logits;
+    p.logits = c.tp_size > 1 ? c.logits_l : c.logits;
     p.part_val = c.part_val;
     p.part_idx = c.part_idx;
     launch_gemv<Epi::Logits>(L, p, c.num_sms);
+    if (c.tp_size > 1) {
+        const bool pdl = L.pdl;
+        tp_all_gather(c, L, c.logits_l, c.logits, (size_t)c.vocab_l);
+        launch_sample_only(c, L, /*n_part=*/0, advance);
+        L.pdl = pdl;
+        return;
+    }
 
     SampleParams s{};
     s.logits = c.logits;
@@ -109,7 +120,93 @@ static void qwen_decode_step_mega(efm_b200_ctx& c, KvSlot& slot, Launcher& L) {
     launch_sample_only(c, L, nb, /*advance=*/1);
 }
 
+// Collectives on the context stream (graph-capturable).  A failure is recorded like a launch failure.
+static void tp_all_reduce(efm_b200_ctx& c, Launcher& L, const float* send, float* recv, size_t count) {
+    if (L.err != cudaSuccess) return;
+    const NcclApi& api = nccl_api();
+    if (!api.ok || c.nccl_comm == nullptr || api.all_reduce_f32_sum(send, recv, count, c.nccl_comm, L.stream) != 0)
+        L.err = cudaErrorUnknown;
+    else if (L.counter != nullptr) ++*L.counter;
+}
+static void tp_all_gather(efm_b200_ctx& c, Launcher& L, const float* send, float* recv, size_t count) {
+    if (L.err != cudaSuccess) return;
+    const NcclApi& api = nccl_api();
+    if (!api.ok || c.nccl_comm == nullptr || api.all_gather_f32(send, recv, count, c.nccl_comm, L.stream) != 0)
+        L.err = cudaErrorUnknown;
+    else if (L.counter != nullptr) ++*L.counter;
+}
+
+// Tensor-parallel decode step: column-parallel QKV / gate-up, row-parallel o_proj / down with an
+// all-reduce of the fp32 partial [H]; the residual add moves into the next kernel's norm prologue
+// (x = bf16(x + bf16(sum)), ping-ponging between two residual buffers so no block re-reads a row that
+// block 0 already updated); lm_head rows are split and the logits all-gathered before sampling.
+static void qwen_decode_step_tp(efm_b200_ctx& c, KvSlot& slot, Launcher& L) {
+    const efm_model_desc& d = c.d;
+    const int H = d.hidden, D = d.head_dim, QD = d.q_heads * D, KVD = d.kv_heads * D, I = d.intermediate;
+    __nv_bfloat16* RA = c.resid_d;
+    __nv_bfloat16* RB = c.resid_d2;
+    for (int l = 0; l < d.num_layers; ++l) {
+        const LayerWeights& w = c.layers[l];
+        {
+            GemvParams p = base_gemv(w.qkv, QD + 2 * KVD, H);
+            p.prologue = l == 0 ? kProEmbedRmsNorm : kProRmsNorm;
+            p.x = RB;                        // l > 0: residual after the previous layer's attention add
+            p.addend = l == 0 ? nullptr : c.ysum;
+            p.resid_out = RA;
+            p.norm_w = w.in_norm; p.eps = d.rms_eps; p.embed_table = c.embed; p.vocab = d.vocab; p.state = c.state;
+            p.bias = w.qkv_bias; p.q_out = c.q_d; p.k_cache = slot.k[l]; p.v_cache = slot.v[l]; p.inv_freq = c.inv_freq;
+            p.q_heads = d.q_heads; p.kv_heads = d.kv_heads; p.head_dim = D; p.use_mrope = d.use_mrope;
+            p.sec0 = d.mrope_section[0]; p.sec1 = d.mrope_section[0] + d.mrope_section[1]; p.max_tokens = slot.max_tokens;
+            launch_gemv<Epi::QkvRope>(L, p, c.num_sms);
+        }
+        {
+            DecodeAttnParams a{};
+            a.q = c.q_d; a.k_cache = slot.k[l]; a.v_cache = slot.v[l]; a.out = c.attn_d; a.state = c.state;
+            a.q_heads = d.q_heads; a.kv_heads = d.kv_heads; a.group = d.q_heads / d.kv_heads;
+            a.n_splits = slot.n_splits; a.chunk_cap = slot.chunk_cap; a.max_tokens = slot.max_tokens;
+            a.scale = 1.0f / sqrtf((float)D);
+            a.part_o = c.attn_part_o; a.part_ml = c.attn_part_ml; a.counters = c.attn_counters;
+            launch_decode_attention(L, a, D);
+        }
+        {
+            GemvParams p = base_gemv(w.o, H, c.o_k);
+            p.x = c.attn_d + (size_t)c.att_rep_idx * c.o_k;
+            p.logits = c.ybuf; p.part_val = c.part_val; p.part_idx = c.part_idx;
+            launch_gemv<Epi::Logits>(L, p, c.num_sms);                 // fp32 partial output
+        }
+        tp_all_reduce(c, L, c.ybuf, c.ysum, (size_t)H);
+        {
+            GemvParams p = base_gemv(w.gate_up, 2 * I, H);
+            p.prologue = kProRmsNorm;
+            p.x = RA; p.addend = c.ysum; p.resid_out = RB;
+            p.norm_w = w.post_norm; p.eps = d.rms_eps; p.y = c.act_d;
+            launch_gemv<Epi::SwiGlu>(L, p, c.num_sms);
+        }
+        {
+            GemvParams p = base_gemv(w.down, H, I);
+            p.x = c.act_d;
+            p.logits = c.ybuf; p.part_val = c.part_val; p.part_idx = c.part_idx;
+            launch_gemv<Epi::Logits>(L, p, c.num_sms);
+        }
+        tp_all_reduce(c, L, c.ybuf, c.ysum, (size_t)H);
+    }
+    {
+        GemvParams p = base_gemv(c.lm_head, c.vocab_l, H);
+        p.prologue = kProRmsNorm;
+        p.x = RB; p.addend = c.ysum; p.resid_out = RA;
+        p.norm_w = c.final_norm; p.eps = d.rms_eps;
+        p.logits = c.logits_l; p.part_val = c.part_val; p.part_idx = c.part_idx;
+        launch_gemv<Epi::Logits>(L, p, c.num_sms);
+    }
+    tp_all_gather(c, L, c.logits_l, c.logits, (size_t)c.vocab_l);
+    launch_sample_only(c, L, /*n_part=*/0, /*advance=*/1);
+}
+
 void qwen_decode_step(efm_b200_ctx& c, KvSlot& slot, Launcher& L) {
+    if (c.tp_size > 1) {
+        qwen_decode_step_tp(c, slot, L);
+        return;
+    }
     if (c.mega && L.trace == nullptr) {      // per-kernel tracing needs the phase-per-launch form
         qwen_decode_step_mega(c, slot, L);
         return;
@@ -162,7 +259,7 @@ void qwen_decode_step(efm_b200_ctx& c, KvSlot& slot, Launcher& L) {
             launch_decode_attention(L, a, D);
         }
         {
-            GemvParams p = base_gemv(w.o, H, QD);
+            GemvParams p = base_gemv(w.o, H, c.o_k);
             p.x = c.attn_d;
             p.residual = c.resid_d;
             launch_gemv<Epi::Residual>(L, p, c.num_sms);
@@ -205,11 +302,11 @@ static EncodeTiledFn encode_tiled_fn() {
 
 // bf16 row-major [rows, cols] tensor, box = 64 columns x 128 rows, 128-byte swizzle, zero fill
 // outside the tensor.
-static bool make_tile_map(CUtensorMap* map, const void* ptr, int rows, int cols) {
+static bool make_tile_map(CUtensorMap* map, const void* ptr, int rows, int cols, int row_stride) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (fn == nullptr) return false;
     const cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    const cuuint64_t gstride[1] = {(cuuint64_t)cols * 2};
+    const cuuint64_t gstride[1] = {(cuuint64_t)row_stride * 2};
     const cuuint32_t box[2] = {(cuuint32_t)tc::BK, (cuuint32_t)tc::BM};
     const cuuint32_t estride[2] = {1, 1};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), gdim, gstride, box, estride,
@@ -225,7 +322,7 @@ static void launch_gemm(Launcher& L, const GemmParams& p, int* error_word = null
         attr_set = true;
     }
     CUtensorMap ma, mb;
-    if (!make_tile_map(&ma, p.A, p.M, p.K) || !make_tile_map(&mb, p.B, p.N, p.K)) {
+    if (!make_tile_map(&ma, p.A, p.M, p.K, p.lda > 0 ? p.lda : p.K) || !make_tile_map(&mb, p.B, p.N, p.K, p.K)) {
         if (L.err == cudaSuccess) L.err = cudaErrorInvalidValue;
         return;
     }
@@ -270,9 +367,15 @@ void qwen_prefill_chunk(efm_b200_ctx& c, KvSlot& slot, int S, int kv_offset, int
                  (const int32_t*)c.pos3, S, d.q_heads, d.kv_heads, D, kv_offset, d.use_mrope, d.mrope_section[0],
                  d.mrope_section[0] + d.mrope_section[1]);
         launch_prefill_attention(L, c.qbuf, slot.k[l], slot.v[l], c.attn, S, kv_offset, d.q_heads, d.kv_heads, D);
-        {
+        if (c.tp_size == 1) {
             GemmParams g{c.attn, w.o, nullptr, c.resid, nullptr, S, H, QD};
             launch_gemm<GemmEpi::Residual>(L, g, &c.state->error);
+        } else {      // row-parallel: this rank's input columns, fp32 partial, all-reduce, then the residual add
+            GemmParams g{c.attn + (size_t)c.att_rep_idx * c.o_k, w.o, nullptr, nullptr, c.ybuf, S, H, c.o_k, QD};
+            launch_gemm<GemmEpi::F32>(L, g, &c.state->error);
+            tp_all_reduce(c, L, c.ybuf, c.ysum, (size_t)S * H);
+            L.launch(add_rows_kernel, dim3(std::min<size_t>(((size_t)S * H / 2 + 255) / 256, (size_t)c.num_sms * 8)), dim3(256), 0,
+                     c.resid, (const float*)c.ysum, (size_t)S * H / 2);
         }
         L.launch(rmsnorm_rows_kernel, dim3(S), dim3(256), 0, (const __nv_bfloat16*)c.resid,
                  (const __nv_bfloat16*)w.post_norm, c.norm, H, d.rms_eps);
@@ -285,9 +388,15 @@ void qwen_prefill_chunk(efm_b200_ctx& c, KvSlot& slot, int S, int kv_offset, int
             const int grid = (int)std::min<size_t>((total + 255) / 256, (size_t)c.num_sms * 8);
             L.launch(swiglu_rows_kernel, dim3(grid), dim3(256), 0, (const float*)c.gu, c.act, S, I);
         }
-        {
+        if (c.tp_size == 1) {
             GemmParams g{c.act, w.down, nullptr, c.resid, nullptr, S, H, I};
             launch_gemm<GemmEpi::Residual>(L, g, &c.state->error);
+        } else {
+            GemmParams g{c.act, w.down, nullptr, nullptr, c.ybuf, S, H, I};
+            launch_gemm<GemmEpi::F32>(L, g, &c.state->error);
+            tp_all_reduce(c, L, c.ybuf, c.ysum, (size_t)S * H);
+            L.launch(add_rows_kernel, dim3(std::min<size_t>(((size_t)S * H / 2 + 255) / 256, (size_t)c.num_sms * 8)), dim3(256), 0,
+                     c.resid, (const float*)c.ysum, (size_t)S * H / 2);
         }
     }
     if (sample_last) launch_lm_head_and_sample(c, L, c.resid + (size_t)(S - 1) * H, /*advance=*/0);

@@ -17,9 +17,21 @@
 #include <cuda.h>
 
 #include "common.cuh"
-#include "gemm_mma.cuh"      // GemmParams / GemmEpi
 
 namespace efm {
+
+enum class GemmEpi : int { Bf16Bias = 0, Residual = 1, F32 = 2 };
+
+struct GemmParams {
+    const __nv_bfloat16* A;   // [M, K] (row stride lda)
+    const __nv_bfloat16* B;   // [N, K]
+    const __nv_bfloat16* bias;
+    __nv_bfloat16* C;         // Bf16Bias: out; Residual: in/out
+    float* Cf;                // F32
+    int M, N, K;
+    int lda = 0;              // row stride of A in elements (0: K)
+};
+
 namespace tc {
 
 constexpr int BM = 128, BN = 128, BK = 64, STAGES = 6, UMMA_K = 16;

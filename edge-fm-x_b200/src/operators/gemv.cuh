@@ -39,7 +39,9 @@ struct GemvParams {
     float eps;
     const __nv_bfloat16* embed_table;
     int vocab;
-    __nv_bfloat16* resid_out; // EmbedRmsNorm: block 0 stores the gathered row here
+    __nv_bfloat16* resid_out; // EmbedRmsNorm / addend: block 0 stores the (updated) residual row here
+    const float* addend;      // norm prologues, tensor parallel: x = bf16(x + bf16(addend)) first (summed partial
+                              // output of the previous row-parallel linear); resid_out must differ from x
     DecodeState* state;
     // epilogue
     __nv_bfloat16* y;         // Plain: [N]; SwiGlu: [N/2]
@@ -228,10 +230,19 @@ __device__ __forceinline__ void gemv_run(const GemvParams& p, const GemvSched& s
             if (!zero) v = from_table ? ld_cached(src + (size_t)c * 8) : ld_cg(src + (size_t)c * 8);
             float f[8];
             unpack8(v, f);
+            if (p.addend != nullptr) {
+                const float4 a0 = __ldcg(reinterpret_cast<const float4*>(p.addend + (size_t)c * 8));
+                const float4 a1 = __ldcg(reinterpret_cast<const float4*>(p.addend + (size_t)c * 8 + 4));
+                v.x = pack_bf16(f[0] + round_bf16(a0.x), f[1] + round_bf16(a0.y));
+                v.y = pack_bf16(f[2] + round_bf16(a0.z), f[3] + round_bf16(a0.w));
+                v.z = pack_bf16(f[4] + round_bf16(a1.x), f[5] + round_bf16(a1.y));
+                v.w = pack_bf16(f[6] + round_bf16(a1.z), f[7] + round_bf16(a1.w));
+                unpack8(v, f);
+            }
 #pragma unroll
             for (int j = 0; j < 8; ++j) ss = fmaf(f[j], f[j], ss);
             reinterpret_cast<uint4*>(xs)[c] = v;
-            if (from_table && blockIdx.x == 0) reinterpret_cast<uint4*>(p.resid_out)[c] = v;
+            if ((from_table || p.addend != nullptr) && blockIdx.x == 0) reinterpret_cast<uint4*>(p.resid_out)[c] = v;
         }
         ss = warp_sum(ss);
         if (lane == 0) misc[warp] = ss;

@@ -120,6 +120,17 @@ __global__ void __launch_bounds__(256) swiglu_rows_kernel(const float* __restric
     }
 }
 
+// Tensor parallel prefill: resid = bf16(resid + bf16(sum)), `sum` being the all-reduced fp32 output
+// of a row-parallel linear (same rounding points as the single-GPU residual epilogue).
+__global__ void __launch_bounds__(256) add_rows_kernel(__nv_bfloat16* __restrict__ resid, const float* __restrict__ sum,
+                                                       size_t n_pairs) {
+    for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n_pairs; i += (size_t)gridDim.x * 256) {
+        const uint32_t old = reinterpret_cast<const uint32_t*>(resid)[i];
+        const float2 s = reinterpret_cast<const float2*>(sum)[i];
+        reinterpret_cast<uint32_t*>(resid)[i] = pack_bf16(bf16lo(old) + round_bf16(s.x), bf16hi(old) + round_bf16(s.y));
+    }
+}
+
 // Causal GQA prefill attention on CUDA cores: one warp per (query, q head); the warp is four
 // independent 8-lane streams, stream j walking keys j, j+4, ... with its own online-softmax
 // state; the four states merge at the end.  Queries sit at cache rows kv_offset + s and see rows

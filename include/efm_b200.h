@@ -90,6 +90,14 @@ EFM_API efm_status efm_b200_destroy(efm_b200_ctx* ctx);
 EFM_API const char* efm_b200_last_error(const efm_b200_ctx* ctx);
 EFM_API const char* efm_b200_version(void);
 
+/* ---- tensor parallel (no counterpart in the reference, which is single-GPU) ------------------ */
+/* One context per rank / GPU.  Rank 0 draws a 128-byte communicator id, the host code carries it to
+ * the other ranks (any transport), every rank then calls tp_init before its first prefill.  Heads
+ * and MLP columns are sharded inside set_weight (callers always pass whole tensors); row-parallel
+ * outputs are summed with an NCCL all-reduce on the context stream (captured in the decode graph). */
+EFM_API efm_status efm_b200_tp_unique_id(void* out128);
+EFM_API efm_status efm_b200_tp_init(efm_b200_ctx* ctx, const void* id128);
+
 /* ---- weights --------------------------------------------------------------------------- */
 /* Replaces WeightLoader::load_weights_from_file + per-layer load_weights
  * (src/utils/device/weight_loader.cpp:80-171, src/layers/linear.cu:1691-1717,1926-1943).

@@ -39,6 +39,8 @@ SIGNATURES = {
     "efm_b200_destroy": (I32, [P]),
     "efm_b200_last_error": (C.c_char_p, [P]),
     "efm_b200_version": (C.c_char_p, []),
+    "efm_b200_tp_unique_id": (I32, [P]),
+    "efm_b200_tp_init": (I32, [P, P]),
     "efm_b200_set_weight": (I32, [P, C.c_char_p, P, C.POINTER(C.c_int64), I32, I32, I32]),
     "efm_b200_finalize_weights": (I32, [P]),
     "efm_b200_alloc_kv_slot": (I32, [P, I32, I32]),
@@ -91,7 +93,7 @@ def _i32_array(values):
 class Backend:
     """Thin object wrapper over one efm_b200_ctx."""
 
-    def __init__(self, cfg, *, max_prefill_tokens=256, max_response_tokens=512, device_id=0):
+    def __init__(self, cfg, *, max_prefill_tokens=256, max_response_tokens=512, device_id=0, tp_rank=0, tp_size=1):
         self.L = lib()
         self.cfg = cfg
         d = ModelDesc()
@@ -105,7 +107,7 @@ class Backend:
             d.mrope_section[:] = cfg.mrope_section
         d.max_prefill_tokens, d.max_response_tokens = max_prefill_tokens, max_response_tokens
         self.ctx = P()
-        st = self.L.efm_b200_create(C.byref(d), device_id, 0, 1, C.byref(self.ctx))
+        st = self.L.efm_b200_create(C.byref(d), device_id, tp_rank, tp_size, C.byref(self.ctx))
         if st != EFM_OK:
             raise BackendError(f"create failed ({st}): {self.L.efm_b200_last_error(None).decode()}")
 
@@ -123,6 +125,10 @@ class Backend:
             self.close()
         except Exception:
             pass
+
+    def tp_init(self, id_bytes):
+        buf = C.create_string_buffer(bytes(id_bytes), 128)
+        self.check(self.L.efm_b200_tp_init(self.ctx, buf), "tp_init")
 
     def load_weights(self, weights):
         """weights: dict name -> torch bf16 tensor (CPU or CUDA)."""
@@ -239,3 +245,11 @@ def generate(be: Backend, slot, prompt, max_new_tokens, *, prefix_len=0, embeds=
                 if collect_logits:
                     logits.append(be.read_logits())
     return be.read_tokens(0, max_new_tokens), logits
+
+
+def tp_unique_id():
+    buf = C.create_string_buffer(128)
+    st = lib().efm_b200_tp_unique_id(buf)
+    if st != EFM_OK:
+        raise BackendError(f"tp_unique_id failed ({st}): {lib().efm_b200_last_error(None).decode()}")
+    return bytes(buf.raw)

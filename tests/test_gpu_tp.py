@@ -1,0 +1,85 @@
+"""GPU (needs >= 2 devices): the CUDA backend with tensor parallelism over NCCL against the
+single-GPU backend and the oracle.  Ranks run as child processes, one GPU each, NVLS off."""
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+import cabi
+import tp_worker
+from oracle import qwen_text, synth
+
+pytestmark = pytest.mark.gpu
+
+
+def free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def run_ranks(fn, world, args, timeout=150):
+    """Child processes with a hard limit: a rank that does not finish is terminated (by pid) and the test fails."""
+    ctx = mp.get_context("spawn")
+    procs = [ctx.Process(target=fn, args=(r,) + args) for r in range(world)]
+    for p in procs:
+        p.start()
+    ok = True
+    for p in procs:
+        p.join(timeout)
+        if p.is_alive():
+            p.terminate()
+            p.join(10)
+            ok = False
+        elif p.exitcode != 0:
+            ok = False
+    assert ok, "a tensor-parallel rank failed or did not finish in time"
+
+
+CASES = [
+    (2, dict(num_layers=2, hidden=256, q_heads=4, kv_heads=2, intermediate=512, vocab=1200, tied=False)),
+    (2, dict(num_layers=2, hidden=512, q_heads=4, kv_heads=2, intermediate=256, vocab=2000, tied=True,
+             mrope_section=[16, 24, 24], model_type="qwen2_5_vl")),
+    (4, dict(num_layers=2, hidden=512, q_heads=8, kv_heads=2, intermediate=512, vocab=1600, tied=False)),   # paired ranks
+]
+
+
+@pytest.mark.parametrize("world,kw", CASES)
+@pytest.mark.parametrize("use_graph", [True, False])
+def test_tensor_parallel_generate(tmp_path, world, kw, use_graph):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    steps, n_prompt, seed = 12, 21, 3
+    run_ranks(tp_worker.gpu_rank, world, (world, free_port(), kw, seed, n_prompt, steps, str(tmp_path), use_graph))
+    cfg = synth.tiny_config(**kw)
+    w = synth.make_weights(cfg, seed=seed)
+    prompt = synth.make_token_ids(n_prompt, seed=seed, vocab=cfg.vocab)
+    pos = torch.arange(n_prompt).repeat(3, 1) if cfg.mrope_section is not None else None
+    got = [torch.load(tmp_path / f"rank{r}.pt") for r in range(world)]
+    for g in got[1:]:
+        assert g["tokens"] == got[0]["tokens"] and g["free"] == got[0]["free"]
+    assert got[0]["free"] == got[0]["tokens"]
+    toks = got[0]["tokens"]
+    oe = qwen_text.QwenTextOracle(cfg, w, "exact_fp32")
+    ref = qwen_text.generate(oe, prompt, steps, forced=toks, position_ids=pos, mrope_last_pos=[n_prompt - 1] * 3)
+    ob = qwen_text.QwenTextOracle(cfg, w, "bf16_points")
+    refb = qwen_text.generate(ob, prompt, steps, forced=toks, position_ids=pos, mrope_last_pos=[n_prompt - 1] * 3)
+    logits = got[0]["logits"].numpy()
+    for s in range(steps):
+        e = ref.logits[s].numpy()
+        assert np.abs(logits[s] - e).max() / np.abs(e).max() < 2e-2
+        if toks[s] != refb.tokens[s]:
+            assert refb.margins[s] <= 2 * np.abs(logits[s] - refb.logits[s].numpy()).max()
+    # and equal to the single-GPU backend up to near-ties
+    be = cabi.Backend(cfg)
+    be.load_weights(w)
+    be.alloc_slot(0, 256)
+    be.set_sampling(0.0, 1.0, 0)
+    one, l1 = cabi.generate(be, 0, prompt, steps, pos3=None if pos is None else pos.tolist(), forced=toks, collect_logits=True)
+    for s in range(steps):
+        assert np.abs(logits[s] - l1[s]).max() / np.abs(l1[s]).max() < 1e-2
+    be.close()

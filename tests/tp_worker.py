@@ -1,0 +1,61 @@
+"""Worker processes for the tensor-parallel tests (spawned by test_tp_*.py; not collected)."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+for p in (ROOT, os.path.join(ROOT, "tests")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+from oracle import qwen_text, synth, tp as tp_oracle  # noqa: E402
+
+
+def cpu_rank(rank, world, port, cfg_kw, seed, n_prompt, steps, out_dir):
+    """gloo rank: tensor-parallel oracle vs nothing (rank 0 writes its logits / ids)."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.set_num_threads(2)
+    cfg = synth.tiny_config(**cfg_kw)
+    w = synth.make_weights(cfg, seed=seed)
+    prompt = synth.make_token_ids(n_prompt, seed=seed, vocab=cfg.vocab)
+    o = tp_oracle.TpOracle(cfg, w, rank, world, "exact_fp32")
+    logits, toks = [], []
+    lg = o.forward(prompt)
+    for s in range(steps):
+        logits.append(lg.clone())
+        toks.append(qwen_text.greedy(lg))
+        if s + 1 < steps:
+            lg = o.forward([toks[-1]])
+    torch.save({"tokens": toks, "logits": torch.stack(logits)}, os.path.join(out_dir, f"rank{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def gpu_rank(rank, world, port, cfg_kw, seed, n_prompt, steps, out_dir, use_graph):
+    """One GPU per rank: the CUDA backend with tp_size = world, NCCL between the ranks."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import cabi
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)      # host plumbing for the 128-byte id
+    cfg = synth.tiny_config(**cfg_kw)
+    w = synth.make_weights(cfg, seed=seed)
+    prompt = synth.make_token_ids(n_prompt, seed=seed, vocab=cfg.vocab)
+    box = [cabi.tp_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(box, src=0)
+    be = cabi.Backend(cfg, device_id=rank, tp_rank=rank, tp_size=world)
+    be.tp_init(box[0])
+    be.load_weights(w)
+    be.alloc_slot(0, 256)
+    be.set_sampling(0.0, 1.0, 0)
+    pos3 = None
+    if cfg.mrope_section is not None:
+        pos3 = [list(range(n_prompt))] * 3
+    toks, logits = cabi.generate(be, 0, prompt, steps, pos3=pos3, use_graph=use_graph, collect_logits=True)
+    free, _ = cabi.generate(be, 0, prompt, steps, pos3=pos3, use_graph=use_graph)
+    torch.save({"tokens": toks, "free": free, "logits": torch.from_numpy(__import__("numpy").stack(logits))}, os.path.join(out_dir, f"rank{rank}.pt"))
+    dist.barrier()
+    be.close()
+    dist.destroy_process_group()

@@ -161,10 +161,130 @@ def cpu_baseline(cfg_id, budget_s=25.0):
                       f"{len(ids)})"}
 
 
+def run_tp(args, rank, world, local_rank):
+    """Config 3 (7B-class) on several GPUs: ONE request, tensor parallel over all ranks (strong scaling).
+    Weights are drawn on the device with a seeded generator (identical on every rank); each rank keeps
+    its shard.  e2e here is the C-ABI call sequence with host token ids in and host ids out."""
+    import torch
+    import torch.distributed as dist
+    import cabi
+    from oracle import synth
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(local_rank)
+
+    class _Solo:                       # world == 1: no process group
+        class ReduceOp:
+            MAX = None
+
+        @staticmethod
+        def barrier():
+            pass
+
+        @staticmethod
+        def all_reduce(t, op=None):
+            pass
+
+        @staticmethod
+        def destroy_process_group():
+            pass
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    else:
+        dist = _Solo
+    cfg, prefix, ids, gen_tokens, temp, top_p = workload(args.config)
+    if args.tokens:
+        gen_tokens = args.tokens
+    max_tokens = len(ids) + gen_tokens + 8
+    pos = position_ids(cfg, len(ids))
+    t_setup = time.perf_counter()
+    be = cabi.Backend(cfg, max_prefill_tokens=min(2048, max_tokens), max_response_tokens=gen_tokens + 8,
+                      device_id=local_rank, tp_rank=rank, tp_size=world)
+    if world > 1:
+        box = [cabi.tp_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        be.tp_init(box[0])
+    g = torch.Generator(device="cuda")
+    g.manual_seed(0)
+    for name, shape, kind in synth.weight_names(cfg):       # one tensor at a time: the whole model never sits twice in HBM
+        t = torch.randn(shape, generator=g, device="cuda", dtype=torch.float32) * 0.02
+        if kind == "n":
+            t += 1.0
+        be.load_weights_partial({name: t.to(torch.bfloat16)})
+        del t
+    be.finalize()
+    be.alloc_slot(0, max_tokens)
+    be.set_sampling(temp, top_p, 0)
+    be.capture_decode(0)
+    be.synchronize()
+    setup_s = time.perf_counter() - t_setup
+    mp = None if pos is None else [len(ids)] * 3
+
+    def one_request():
+        be.event_record(0)
+        be.prefill(0, ids, kv_offset=0, pos3=pos, sample=True)
+        be.event_record(1)
+        be.decode_begin(0, len(ids), mp, 1)
+        be.decode_steps(gen_tokens - 1, True)
+        be.event_record(2)
+        toks = be.read_tokens(0, gen_tokens)              # host ids out (one D2H + sync)
+        return be.elapsed_ms(0, 1), be.elapsed_ms(1, 2), toks
+
+    for _ in range(args.warmup):
+        one_request()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    launches0 = be.launch_count()
+    dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    pre_ms = dec_ms = 0.0
+    for _ in range(args.steps):
+        a, b, tokens = one_request()
+        pre_ms += a
+        dec_ms += b
+    dist.barrier()
+    torch.cuda.synchronize()
+    wall_s = time.perf_counter() - t0
+    clocks = sampler.stop()
+    launches = be.launch_count() - launches0
+    local = torch.tensor([dec_ms, pre_ms, wall_s], dtype=torch.float64, device="cuda")
+    dist.all_reduce(local, op=dist.ReduceOp.MAX)
+    dec_ms, pre_ms, wall_s = [float(x) for x in local.tolist()]
+    dec_steps = args.steps * (gen_tokens - 1)
+    step_ms = dec_ms / dec_steps
+    step_bytes = be.decode_step_bytes(len(ids) + gen_tokens // 2)          # this rank's share
+    peak, peak_kind = peaks()
+    achieved = step_bytes / (step_ms * 1e-3) / 1e9
+    if rank == 0:
+        line = {"metric": METRIC, "value": dec_steps / (dec_ms / 1e3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": (pre_ms + dec_ms) / args.steps, "higher_is_better": True,
+                "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                "config": {"workload": f"{NAMES[args.config]}: {len(ids)}-token prompt, {gen_tokens} generated tokens, batch 1, "
+                                       f"temperature {temp}, top_p {top_p}",
+                           "parallelism": "single GPU" if world == 1 else f"tp{world} (heads + MLP columns + vocab rows; NCCL all-reduce in the decode graph)",
+                           "l2_policy": "weights streamed per decode step exceed L2 (%.2f GB per GPU vs 126 MB)" % (step_bytes / 1e9),
+                           "cuda_graph": True},
+                "decode_ms_per_token": step_ms, "prefill_ms": pre_ms / args.steps, "ttft_ms": pre_ms / args.steps,
+                "wall_s": wall_s, "setup_s": setup_s,
+                "e2e": {"value": args.steps * gen_tokens / wall_s, "unit": UNIT, "h2d_bytes_per_step": 4 * len(ids) * (4 if pos else 1),
+                        "d2h_bytes_per_step": 4 * gen_tokens + 32, "api": "efm_b200_prefill / decode_steps / read_tokens (C ABI, host buffers)"},
+                "gpu_launches": launches, "clocks": clocks,
+                "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                             "traffic": None, "peak_kind": peak_kind, "launch": "one decode step on one rank",
+                             "bytes_per_launch": step_bytes, "us_per_launch": step_ms * 1e3},
+                "tokens_head": tokens[:8]}
+        print(json.dumps(line), flush=True)
+    be.close()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def run_ours(args, rank, world, local_rank):
     import torch
     import cabi
     from oracle import synth
+    if args.config == 3:      # 7B-class: tensor parallel over all ranks (one rank: the plain single-GPU path, device-drawn weights)
+        return run_tp(args, rank, world, local_rank)
     torch.cuda.set_device(local_rank)
     dist = None
     if world > 1:

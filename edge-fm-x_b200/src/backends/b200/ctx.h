@@ -72,7 +72,7 @@ struct efm_b200_ctx {
     int max_s = 0;
     int32_t* ids = nullptr;               // [max_s]
     int32_t* pos3 = nullptr;              // [3 * max_s]
-    __nv_bfloat16* resid = nullptr;       // [max_s, H]
+    float* resid = nullptr;               // [max_s, H] residual stream, fp32
     __nv_bfloat16* norm = nullptr;        // [max_s, H]
     __nv_bfloat16* qkv = nullptr;         // [max_s, (q+2kv)*D]
     __nv_bfloat16* qbuf = nullptr;        // [max_s, q*D]
@@ -81,8 +81,8 @@ struct efm_b200_ctx {
     __nv_bfloat16* act = nullptr;         // [max_s, I]
     __nv_bfloat16* custom_embeds = nullptr;
     size_t custom_embeds_cap = 0;
-    __nv_bfloat16* resid_d = nullptr;     // decode residual stream [H]
-    __nv_bfloat16* resid_d2 = nullptr;    // second copy (tensor parallel: the add-and-norm prologue ping-pongs)
+    float* resid_d = nullptr;             // decode residual stream [H], fp32
+    float* resid_d2 = nullptr;            // second copy (tensor parallel: the add-and-norm prologue ping-pongs)
     __nv_bfloat16* q_d = nullptr;         // [q*D]
     __nv_bfloat16* attn_d = nullptr;      // [q*D]
     __nv_bfloat16* act_d = nullptr;       // [I]

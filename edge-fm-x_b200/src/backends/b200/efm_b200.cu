@@ -61,7 +61,11 @@ efm_status require_b200(efm_b200_ctx* c, int device_id) {
     if (major != 10) return fail(c, EFM_ERR_CUDA, "device is not sm_100 (this library carries sm_100a code only)");
     EFM_CK(c, cudaSetDevice(device_id));
     EFM_CK(c, configure_decode_attention());
-    EFM_CK(c, configure_gemv(96 * 1024));
+    {
+        int optin = 0;
+        EFM_CK(c, cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device_id));
+        EFM_CK(c, configure_gemv(optin - 2048));        // leave room for the kernels' static shared memory
+    }
     return EFM_OK;
 }
 
@@ -667,8 +671,10 @@ efm_status efm_b200_decode_step_bytes(efm_b200_ctx* c, int32_t kv_len, int64_t* 
     if (c == nullptr || bytes == nullptr) return fail(c, EFM_ERR_INVALID_ARGUMENT, "null argument");
     const efm_model_desc& d = c->d;
     const int64_t H = d.hidden, D = d.head_dim, q = d.q_heads, kv = d.kv_heads, I = d.intermediate, V = d.vocab, L = d.num_layers;
-    const int64_t per_layer = (q + 2 * kv) * D * H + (q + 2 * kv) * D + q * D * H + 3 * I * H + 2 * H;
-    const int64_t w = 2 * (L * per_layer + H + V * H) + 2 * H;      // + final norm, lm_head matrix, one embedding row
+    // what THIS rank streams: its head shard, its o_proj columns, its MLP columns, its lm_head rows
+    const int64_t per_layer = (q + 2 * kv) * D * H + (q + 2 * kv) * D + (int64_t)c->o_k * H + 3 * I * H + 2 * H;
+    const int64_t w = 2 * (L * per_layer + H + (int64_t)c->vocab_l * H) + 2 * H;      // + final norm, lm_head rows, one embedding row
+    (void)V;
     *bytes = w + L * 2 * (int64_t)kv_len * kv * D * 2;
     return EFM_OK;
 }
@@ -701,8 +707,8 @@ efm_status efm_b200_op_gemv(const void* w, const void* x, const void* norm_w, fl
     GemvParams p{};
     p.W = (const __nv_bfloat16*)w; p.N = n; p.K = k; p.n_items = n / 2;
     p.prologue = norm_w != nullptr ? kProRmsNorm : kProPlain;
-    p.x = (const __nv_bfloat16*)x; p.norm_w = (const __nv_bfloat16*)norm_w; p.eps = eps;
-    p.y = (__nv_bfloat16*)y_bf16; p.residual = (__nv_bfloat16*)residual;
+    p.x = (const __nv_bfloat16*)x; p.xr = (const float*)x; p.norm_w = (const __nv_bfloat16*)norm_w; p.eps = eps;
+    p.y = (__nv_bfloat16*)y_bf16; p.residual = (float*)residual;
     Launcher L; L.pdl = false;
     if (residual != nullptr) launch_gemv<Epi::Residual>(L, p, sms); else launch_gemv<Epi::Plain>(L, p, sms);
     return op_finish(L);

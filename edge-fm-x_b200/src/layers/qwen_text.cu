@@ -31,11 +31,11 @@ static void launch_sample_only(efm_b200_ctx& c, Launcher& L, int n_part, int adv
 
 void launch_sample(Launcher& L, const SampleParams& p) { L.launch(sample_kernel, dim3(1), dim3(1024), 0, p); }
 
-void launch_lm_head_and_sample(efm_b200_ctx& c, Launcher& L, const __nv_bfloat16* resid_row, int advance) {
+void launch_lm_head_and_sample(efm_b200_ctx& c, Launcher& L, const float* resid_row, int advance) {
     const efm_model_desc& d = c.d;
     GemvParams p = base_gemv(c.lm_head, c.vocab_l, d.hidden);      // this rank's rows (all of them without TP)
     p.prologue = kProRmsNorm;
-    p.x = resid_row;
+    p.xr = resid_row;
     p.norm_w = c.final_norm;
     p.eps = d.rms_eps;
     p.logits = c.tp_size > 1 ? c.logits_l : c.logits;
@@ -143,14 +143,14 @@ static void tp_all_gather(efm_b200_ctx& c, Launcher& L, const float* send, float
 static void qwen_decode_step_tp(efm_b200_ctx& c, KvSlot& slot, Launcher& L) {
     const efm_model_desc& d = c.d;
     const int H = d.hidden, D = d.head_dim, QD = d.q_heads * D, KVD = d.kv_heads * D, I = d.intermediate;
-    __nv_bfloat16* RA = c.resid_d;
-    __nv_bfloat16* RB = c.resid_d2;
+    float* RA = c.resid_d;
+    float* RB = c.resid_d2;
     for (int l = 0; l < d.num_layers; ++l) {
         const LayerWeights& w = c.layers[l];
         {
             GemvParams p = base_gemv(w.qkv, QD + 2 * KVD, H);
             p.prologue = l == 0 ? kProEmbedRmsNorm : kProRmsNorm;
-            p.x = RB;                        // l > 0: residual after the previous layer's attention add
+            p.xr = RB;                       // l > 0: residual after the previous layer's attention add
             p.addend = l == 0 ? nullptr : c.ysum;
             p.resid_out = RA;
             p.norm_w = w.in_norm; p.eps = d.rms_eps; p.embed_table = c.embed; p.vocab = d.vocab; p.state = c.state;
@@ -178,7 +178,7 @@ static void qwen_decode_step_tp(efm_b200_ctx& c, KvSlot& slot, Launcher& L) {
         {
             GemvParams p = base_gemv(w.gate_up, 2 * I, H);
             p.prologue = kProRmsNorm;
-            p.x = RA; p.addend = c.ysum; p.resid_out = RB;
+            p.xr = RA; p.addend = c.ysum; p.resid_out = RB;
             p.norm_w = w.post_norm; p.eps = d.rms_eps; p.y = c.act_d;
             launch_gemv<Epi::SwiGlu>(L, p, c.num_sms);
         }
@@ -193,7 +193,7 @@ static void qwen_decode_step_tp(efm_b200_ctx& c, KvSlot& slot, Launcher& L) {
     {
         GemvParams p = base_gemv(c.lm_head, c.vocab_l, H);
         p.prologue = kProRmsNorm;
-        p.x = RB; p.addend = c.ysum; p.resid_out = RA;
+        p.xr = RB; p.addend = c.ysum; p.resid_out = RA;
         p.norm_w = c.final_norm; p.eps = d.rms_eps;
         p.logits = c.logits_l; p.part_val = c.part_val; p.part_idx = c.part_idx;
         launch_gemv<Epi::Logits>(L, p, c.num_sms);
@@ -218,7 +218,7 @@ void qwen_decode_step(efm_b200_ctx& c, KvSlot& slot, Launcher& L) {
         {
             GemvParams p = base_gemv(w.qkv, QD + 2 * KVD, H);
             p.prologue = l == 0 ? kProEmbedRmsNorm : kProRmsNorm;
-            p.x = c.resid_d;
+            p.xr = c.resid_d;
             p.norm_w = w.in_norm;
             p.eps = d.rms_eps;
             p.embed_table = c.embed;
@@ -267,7 +267,7 @@ void qwen_decode_step(efm_b200_ctx& c, KvSlot& slot, Launcher& L) {
         {
             GemvParams p = base_gemv(w.gate_up, 2 * I, H);
             p.prologue = kProRmsNorm;
-            p.x = c.resid_d;
+            p.xr = c.resid_d;
             p.norm_w = w.post_norm;
             p.eps = d.rms_eps;
             p.y = c.act_d;
@@ -356,7 +356,7 @@ void qwen_prefill_chunk(efm_b200_ctx& c, KvSlot& slot, int S, int kv_offset, int
              (const __nv_bfloat16*)(n_custom > 0 ? c.custom_embeds : nullptr), c.resid, d.vocab, H, embed_token_id, n_custom);
     for (int l = 0; l < d.num_layers; ++l) {
         const LayerWeights& w = c.layers[l];
-        L.launch(rmsnorm_rows_kernel, dim3(S), dim3(256), 0, (const __nv_bfloat16*)c.resid,
+        L.launch(rmsnorm_rows_kernel, dim3(S), dim3(256), 0, (const float*)c.resid,
                  (const __nv_bfloat16*)w.in_norm, c.norm, H, d.rms_eps);
         {
             GemmParams g{c.norm, w.qkv, w.qkv_bias, c.qkv, nullptr, S, QD + 2 * KVD, H};
@@ -368,7 +368,7 @@ void qwen_prefill_chunk(efm_b200_ctx& c, KvSlot& slot, int S, int kv_offset, int
                  d.mrope_section[0] + d.mrope_section[1]);
         launch_prefill_attention(L, c.qbuf, slot.k[l], slot.v[l], c.attn, S, kv_offset, d.q_heads, d.kv_heads, D);
         if (c.tp_size == 1) {
-            GemmParams g{c.attn, w.o, nullptr, c.resid, nullptr, S, H, QD};
+            GemmParams g{c.attn, w.o, nullptr, nullptr, c.resid, S, H, QD};
             launch_gemm<GemmEpi::Residual>(L, g, &c.state->error);
         } else {      // row-parallel: this rank's input columns, fp32 partial, all-reduce, then the residual add
             GemmParams g{c.attn + (size_t)c.att_rep_idx * c.o_k, w.o, nullptr, nullptr, c.ybuf, S, H, c.o_k, QD};
@@ -377,7 +377,7 @@ void qwen_prefill_chunk(efm_b200_ctx& c, KvSlot& slot, int S, int kv_offset, int
             L.launch(add_rows_kernel, dim3(std::min<size_t>(((size_t)S * H / 2 + 255) / 256, (size_t)c.num_sms * 8)), dim3(256), 0,
                      c.resid, (const float*)c.ysum, (size_t)S * H / 2);
         }
-        L.launch(rmsnorm_rows_kernel, dim3(S), dim3(256), 0, (const __nv_bfloat16*)c.resid,
+        L.launch(rmsnorm_rows_kernel, dim3(S), dim3(256), 0, (const float*)c.resid,
                  (const __nv_bfloat16*)w.post_norm, c.norm, H, d.rms_eps);
         {
             GemmParams g{c.norm, w.gate_up, nullptr, nullptr, c.gu, S, 2 * I, H};
@@ -389,7 +389,7 @@ void qwen_prefill_chunk(efm_b200_ctx& c, KvSlot& slot, int S, int kv_offset, int
             L.launch(swiglu_rows_kernel, dim3(grid), dim3(256), 0, (const float*)c.gu, c.act, S, I);
         }
         if (c.tp_size == 1) {
-            GemmParams g{c.act, w.down, nullptr, c.resid, nullptr, S, H, I};
+            GemmParams g{c.act, w.down, nullptr, nullptr, c.resid, S, H, I};
             launch_gemm<GemmEpi::Residual>(L, g, &c.state->error);
         } else {
             GemmParams g{c.act, w.down, nullptr, nullptr, c.ybuf, S, H, I};

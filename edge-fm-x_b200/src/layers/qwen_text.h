@@ -14,7 +14,7 @@ void qwen_decode_step(efm_b200_ctx& c, KvSlot& slot, Launcher& L);
 void qwen_prefill_chunk(efm_b200_ctx& c, KvSlot& slot, int S, int kv_offset, int n_custom, int embed_token_id,
                         bool sample_last, Launcher& L);
 // Final norm + lm_head + sampler on one residual row.
-void launch_lm_head_and_sample(efm_b200_ctx& c, Launcher& L, const __nv_bfloat16* resid_row, int advance);
+void launch_lm_head_and_sample(efm_b200_ctx& c, Launcher& L, const float* resid_row, int advance);
 // Single operators (used by the per-operator C entry points).
 void launch_gemm_bf16(Launcher& L, const GemmParams& p);
 void launch_sample(Launcher& L, const SampleParams& p);

@@ -33,7 +33,8 @@ struct MegaParams {
     float eps;
     int ks_qkv, ks_o, ks_gu, ks_down, ks_lm;     // warps sharing one row pair, per phase
     const __nv_bfloat16 *embed, *final_norm, *lm_head;
-    __nv_bfloat16 *resid, *q, *attn, *act;
+    float* resid;                      // residual stream [H] fp32
+    __nv_bfloat16 *q, *attn, *act;
     float* logits;
     float* part_val;
     int* part_idx;
@@ -123,7 +124,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const Mega
         GemvParams g{};
         g.W = W.qkv; g.N = P.QD + 2 * P.KVD; g.K = P.H; g.n_items = g.N / 2;
         g.prologue = l == 0 ? kProEmbedRmsNorm : kProRmsNorm;
-        g.x = P.resid; g.norm_w = W.in_norm; g.eps = P.eps;
+        g.xr = P.resid; g.norm_w = W.in_norm; g.eps = P.eps;
         g.embed_table = P.embed; g.vocab = P.vocab; g.resid_out = P.resid; g.state = P.state;
         g.bias = W.qkv_bias; g.q_out = P.q; g.k_cache = W.k_cache; g.v_cache = W.v_cache;
         g.inv_freq = P.inv_freq; g.q_heads = P.q_heads; g.kv_heads = P.kv_heads; g.head_dim = D;
@@ -167,7 +168,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const Mega
         gemv_run<Epi::Residual>(go, sc, regs, mega_smem, xbytes, best_v, best_i);
         GemvParams gg{};
         gg.W = W.gate_up; gg.N = 2 * P.I; gg.K = P.H; gg.n_items = P.I; gg.prologue = kProRmsNorm;
-        gg.x = P.resid; gg.norm_w = W.post_norm; gg.eps = P.eps; gg.y = P.act;
+        gg.xr = P.resid; gg.norm_w = W.post_norm; gg.eps = P.eps; gg.y = P.act;
         mega_barrier_arrive(bar);
         sc = gemv_sched(gg, P.ks_gu, cta, nblk);
         gemv_prefetch<Epi::SwiGlu>(gg, sc, regs, mega_smem, xbytes);
@@ -191,7 +192,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const Mega
         } else {
             GemvParams g{};
             g.W = P.lm_head; g.N = P.V; g.K = P.H; g.n_items = P.V / 2; g.prologue = kProRmsNorm;
-            g.x = P.resid; g.norm_w = P.final_norm; g.eps = P.eps;
+            g.xr = P.resid; g.norm_w = P.final_norm; g.eps = P.eps;
             sc = gemv_sched(g, P.ks_lm, cta, nblk);
             gemv_prefetch<Epi::Logits>(g, sc, regs, mega_smem, xbytes);
         }
@@ -206,7 +207,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const Mega
     {
         GemvParams g{};
         g.W = P.lm_head; g.N = P.V; g.K = P.H; g.n_items = P.V / 2; g.prologue = kProRmsNorm;
-        g.x = P.resid; g.norm_w = P.final_norm; g.eps = P.eps;
+        g.xr = P.resid; g.norm_w = P.final_norm; g.eps = P.eps;
         g.logits = P.logits; g.part_val = P.part_val; g.part_idx = P.part_idx;
         gemv_run<Epi::Logits>(g, sc, regs, mega_smem, xbytes, best_v, best_i);
         gemv_publish_best(g, best_v, best_i, bv, bi);

@@ -9,7 +9,7 @@
 //   warp 1      allocates 128 TMEM columns; one lane issues tcgen05.mma (M 128, N 128, K 16, four
 //               per stage) and tcgen05.commit, which releases the stage to the producer;
 //   warps 2-5   epilogue: tcgen05.ld the accumulator (row = TMEM lane, 32 columns at a time) and
-//               write bf16 (+bias) | residual add | fp32.
+//               write bf16 (+bias) | fp32 residual add | fp32.
 // Rows past M and columns past N are zero-filled by TMA on load and masked on store.
 // Every mbarrier wait is bounded; a wait that gives up raises *error, the block frees its TMEM and
 // returns.  Bound: tensor pipe (2 M N K flops).
@@ -26,8 +26,8 @@ struct GemmParams {
     const __nv_bfloat16* A;   // [M, K] (row stride lda)
     const __nv_bfloat16* B;   // [N, K]
     const __nv_bfloat16* bias;
-    __nv_bfloat16* C;         // Bf16Bias: out; Residual: in/out
-    float* Cf;                // F32
+    __nv_bfloat16* C;         // Bf16Bias: out
+    float* Cf;                // F32: out; Residual: in/out (fp32 residual stream)
     int M, N, K;
     int lda = 0;              // row stride of A in elements (0: K)
 };
@@ -214,23 +214,17 @@ __global__ void __launch_bounds__(tc::kThreads) gemm_tc_kernel(const __grid_cons
                         } else {
                             for (int j = 0; j < nv; j += 2) *reinterpret_cast<uint32_t*>(p.C + off + j) = pack_bf16(v[j], v[j + 1]);
                         }
-                    } else {
+                    } else {      // residual stream in fp32: Cf += acc
                         if (wide) {
 #pragma unroll
-                            for (int j = 0; j < 32; j += 8) {
-                                const uint4 o = *reinterpret_cast<const uint4*>(p.C + off + j);
-                                uint4 w;
-                                w.x = pack_bf16(bf16lo(o.x) + round_bf16(v[j]), bf16hi(o.x) + round_bf16(v[j + 1]));
-                                w.y = pack_bf16(bf16lo(o.y) + round_bf16(v[j + 2]), bf16hi(o.y) + round_bf16(v[j + 3]));
-                                w.z = pack_bf16(bf16lo(o.z) + round_bf16(v[j + 4]), bf16hi(o.z) + round_bf16(v[j + 5]));
-                                w.w = pack_bf16(bf16lo(o.w) + round_bf16(v[j + 6]), bf16hi(o.w) + round_bf16(v[j + 7]));
-                                *reinterpret_cast<uint4*>(p.C + off + j) = w;
+                            for (int j = 0; j < 32; j += 4) {
+                                const float4 o = *reinterpret_cast<const float4*>(p.Cf + off + j);
+                                *reinterpret_cast<float4*>(p.Cf + off + j) = make_float4(o.x + v[j], o.y + v[j + 1], o.z + v[j + 2], o.w + v[j + 3]);
                             }
                         } else {
                             for (int j = 0; j < nv; j += 2) {
-                                const uint32_t old = *reinterpret_cast<const uint32_t*>(p.C + off + j);
-                                *reinterpret_cast<uint32_t*>(p.C + off + j) =
-                                    pack_bf16(bf16lo(old) + round_bf16(v[j]), bf16hi(old) + round_bf16(v[j + 1]));
+                                const float2 o = *reinterpret_cast<const float2*>(p.Cf + off + j);
+                                *reinterpret_cast<float2*>(p.Cf + off + j) = make_float2(o.x + v[j], o.y + v[j + 1]);
                             }
                         }
                     }

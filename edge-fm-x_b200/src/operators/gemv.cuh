@@ -2,11 +2,13 @@
 // fused in so that one launch replaces a chain of the reference's kernels:
 //
 //   prologue  Plain            x is read as is                      (o_proj, down_proj)
-//             RmsNorm          x = bf16(rmsnorm(residual) * w)      (K2/K3 + K4 of the reference:
+//             RmsNorm          x = bf16(rmsnorm(residual) * w), residual stream in fp32
+//                                                                   (K2/K3 + K4 of the reference:
 //                                                                    src/operators/norm_op.cu:20-106)
 //             EmbedRmsNorm     residual = embed_table[token] first  (src/layers/embed_head.cu:22-61)
 //   epilogue  Plain            y = bf16(W x)
-//             Residual         r = bf16(r + bf16(W x))              (fused add of norm_op.cu:64-106)
+//             Residual         r += W x, r kept in fp32             (fused add of norm_op.cu:64-106; the
+//                              reference stores r in bf16, which costs ~2x in logit error on deep stacks)
 //             QkvRope          + bias, rotate-half RoPE / M-RoPE on q and k, append k, v to the
 //                              cache row kv_len-1                    (linear_impl.cu:90-106,
 //                              decode_runtime_kernels.cu:67-225)
@@ -34,18 +36,19 @@ struct GemvParams {
     int N, K, n_items;        // n_items = N / 2 (every epilogue consumes rows in pairs)
     // prologue
     int prologue;
-    const __nv_bfloat16* x;   // Plain: [K]; RmsNorm: residual stream [K]
+    const __nv_bfloat16* x;   // Plain: activations [K] bf16
+    const float* xr;          // norm prologues: residual stream [K] fp32
     const __nv_bfloat16* norm_w;
     float eps;
     const __nv_bfloat16* embed_table;
     int vocab;
-    __nv_bfloat16* resid_out; // EmbedRmsNorm / addend: block 0 stores the (updated) residual row here
-    const float* addend;      // norm prologues, tensor parallel: x = bf16(x + bf16(addend)) first (summed partial
-                              // output of the previous row-parallel linear); resid_out must differ from x
+    float* resid_out;         // EmbedRmsNorm / addend: block 0 stores the (updated) residual row here
+    const float* addend;      // norm prologues, tensor parallel: x = x + addend first (summed partial output of
+                              // the previous row-parallel linear); resid_out must differ from xr
     DecodeState* state;
     // epilogue
     __nv_bfloat16* y;         // Plain: [N]; SwiGlu: [N/2]
-    __nv_bfloat16* residual;  // Residual: [N] in/out
+    float* residual;          // Residual: [N] fp32 in/out
     const __nv_bfloat16* bias;
     __nv_bfloat16* q_out;     // QkvRope
     __nv_bfloat16* k_cache;
@@ -86,9 +89,8 @@ __device__ __forceinline__ void item_epilogue(const GemvParams& p, int item, flo
         p.y[item * 2 + 1] = __float2bfloat16_rn(a1);
     } else if constexpr (EPI == Epi::Residual) {
         // L2 load: inside the persistent decode kernel another block wrote this value
-        const uint32_t old = __ldcg(reinterpret_cast<const unsigned int*>(p.residual + item * 2));
-        *reinterpret_cast<uint32_t*>(p.residual + item * 2) =
-            pack_bf16(bf16lo(old) + round_bf16(a0), bf16hi(old) + round_bf16(a1));
+        const float2 old = __ldcg(reinterpret_cast<const float2*>(p.residual + item * 2));
+        *reinterpret_cast<float2*>(p.residual + item * 2) = make_float2(old.x + a0, old.y + a1);
     } else if constexpr (EPI == Epi::SwiGlu) {
         const float s = a0 / (1.0f + expf(-a0));
         p.y[item] = __float2bfloat16_rn(s * a1);
@@ -195,7 +197,7 @@ __device__ __forceinline__ void gemv_prefetch(const GemvParams& p, const GemvSch
 }
 
 // Stage activations (with the fused norm), stream the rows, reduce, epilogue.
-// smem: [xs: xbytes][norm weight: xbytes][red: 2 x 16 x 2 floats][misc: 16 floats]
+// smem: [xs: xbytes][norm weight: xbytes][red: 2 x 16 x 2 floats][misc: 16 floats][residual row: K floats]
 template <Epi EPI>
 __device__ __forceinline__ void gemv_run(const GemvParams& p, const GemvSched& sc, GemvRegs& r, unsigned char* smem,
                                          const unsigned int xbytes, float& best_v, int& best_i) {
@@ -207,42 +209,48 @@ __device__ __forceinline__ void gemv_run(const GemvParams& p, const GemvSched& s
     const int nch = sc.nch;
 
     // residual pair of the first item, fetched under the weight stream
-    uint32_t old_first = 0u;
+    float2 old_first = make_float2(0.f, 0.f);
     if constexpr (EPI == Epi::Residual) {
         if (sc.wk == 0 && lane == 0 && sc.total > 0)
-            old_first = __ldcg(reinterpret_cast<const unsigned int*>(p.residual + sc.ig0 * 2));
+            old_first = __ldcg(reinterpret_cast<const float2*>(p.residual + sc.ig0 * 2));
     }
     // ---- activations (L2 loads: another block may have produced them) ------------------------
     if (p.prologue == kProPlain) {
         for (int c = tid; c < nch; c += kGemvThreads) reinterpret_cast<uint4*>(xs)[c] = ld_cg(p.x + (size_t)c * 8);
     } else {
-        const __nv_bfloat16* src = p.x;
+        // residual stream in fp32 (or the embedding row); staged as fp32 until the scale is known
+        const __nv_bfloat16* table_row = nullptr;
         bool zero = false, from_table = false;
         if (p.prologue == kProEmbedRmsNorm) {
             const int tok = p.state->token;
             zero = tok < 0 || tok >= p.vocab;
-            src = p.embed_table + (size_t)(zero ? 0 : tok) * p.K;
+            table_row = p.embed_table + (size_t)(zero ? 0 : tok) * p.K;
             from_table = true;
         }
+        float* xf32 = reinterpret_cast<float*>(smem + 2 * xbytes + (2 * kGemvWarps * 2 + 16) * sizeof(float));   // [K]
         float ss = 0.f;
         for (int c = tid; c < nch; c += kGemvThreads) {
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (!zero) v = from_table ? ld_cached(src + (size_t)c * 8) : ld_cg(src + (size_t)c * 8);
             float f[8];
-            unpack8(v, f);
+            if (from_table) {
+                unpack8(zero ? make_uint4(0, 0, 0, 0) : ld_cached(table_row + (size_t)c * 8), f);
+            } else {
+                const float4 lo = __ldcg(reinterpret_cast<const float4*>(p.xr + (size_t)c * 8));
+                const float4 hi = __ldcg(reinterpret_cast<const float4*>(p.xr + (size_t)c * 8 + 4));
+                f[0] = lo.x; f[1] = lo.y; f[2] = lo.z; f[3] = lo.w; f[4] = hi.x; f[5] = hi.y; f[6] = hi.z; f[7] = hi.w;
+            }
             if (p.addend != nullptr) {
                 const float4 a0 = __ldcg(reinterpret_cast<const float4*>(p.addend + (size_t)c * 8));
                 const float4 a1 = __ldcg(reinterpret_cast<const float4*>(p.addend + (size_t)c * 8 + 4));
-                v.x = pack_bf16(f[0] + round_bf16(a0.x), f[1] + round_bf16(a0.y));
-                v.y = pack_bf16(f[2] + round_bf16(a0.z), f[3] + round_bf16(a0.w));
-                v.z = pack_bf16(f[4] + round_bf16(a1.x), f[5] + round_bf16(a1.y));
-                v.w = pack_bf16(f[6] + round_bf16(a1.z), f[7] + round_bf16(a1.w));
-                unpack8(v, f);
+                f[0] += a0.x; f[1] += a0.y; f[2] += a0.z; f[3] += a0.w; f[4] += a1.x; f[5] += a1.y; f[6] += a1.z; f[7] += a1.w;
             }
 #pragma unroll
             for (int j = 0; j < 8; ++j) ss = fmaf(f[j], f[j], ss);
-            reinterpret_cast<uint4*>(xs)[c] = v;
-            if ((from_table || p.addend != nullptr) && blockIdx.x == 0) reinterpret_cast<uint4*>(p.resid_out)[c] = v;
+            reinterpret_cast<float4*>(xf32)[2 * c] = make_float4(f[0], f[1], f[2], f[3]);
+            reinterpret_cast<float4*>(xf32)[2 * c + 1] = make_float4(f[4], f[5], f[6], f[7]);
+            if ((from_table || p.addend != nullptr) && blockIdx.x == 0) {
+                reinterpret_cast<float4*>(p.resid_out)[2 * c] = make_float4(f[0], f[1], f[2], f[3]);
+                reinterpret_cast<float4*>(p.resid_out)[2 * c + 1] = make_float4(f[4], f[5], f[6], f[7]);
+            }
         }
         ss = warp_sum(ss);
         if (lane == 0) misc[warp] = ss;
@@ -252,14 +260,14 @@ __device__ __forceinline__ void gemv_run(const GemvParams& p, const GemvSched& s
         for (int w = 0; w < kGemvWarps; ++w) tot += misc[w];
         const float inv = 1.0f / sqrtf(tot / (float)p.K + p.eps);
         for (int c = tid; c < nch; c += kGemvThreads) {       // same thread, same chunks as above
-            float f[8], w[8];
-            unpack8(reinterpret_cast<const uint4*>(xs)[c], f);
+            const float4 lo = reinterpret_cast<const float4*>(xf32)[2 * c], hi = reinterpret_cast<const float4*>(xf32)[2 * c + 1];
+            float w[8];
             unpack8(gs[c], w);
             uint4 o;
-            o.x = pack_bf16(f[0] * inv * w[0], f[1] * inv * w[1]);
-            o.y = pack_bf16(f[2] * inv * w[2], f[3] * inv * w[3]);
-            o.z = pack_bf16(f[4] * inv * w[4], f[5] * inv * w[5]);
-            o.w = pack_bf16(f[6] * inv * w[6], f[7] * inv * w[7]);
+            o.x = pack_bf16(lo.x * inv * w[0], lo.y * inv * w[1]);
+            o.y = pack_bf16(lo.z * inv * w[2], lo.w * inv * w[3]);
+            o.z = pack_bf16(hi.x * inv * w[4], hi.y * inv * w[5]);
+            o.w = pack_bf16(hi.z * inv * w[6], hi.w * inv * w[7]);
             reinterpret_cast<uint4*>(xs)[c] = o;
         }
     }
@@ -299,9 +307,8 @@ __device__ __forceinline__ void gemv_run(const GemvParams& p, const GemvSched& s
         }
         if (sc.wk == 0 && lane == 0) {
             if constexpr (EPI == Epi::Residual) {
-                const uint32_t old = j == 0 ? old_first : __ldcg(reinterpret_cast<const unsigned int*>(p.residual + ig * 2));
-                *reinterpret_cast<uint32_t*>(p.residual + ig * 2) =
-                    pack_bf16(bf16lo(old) + round_bf16(t0), bf16hi(old) + round_bf16(t1));
+                const float2 old = j == 0 ? old_first : __ldcg(reinterpret_cast<const float2*>(p.residual + ig * 2));
+                *reinterpret_cast<float2*>(p.residual + ig * 2) = make_float2(old.x + t0, old.y + t1);
             } else {
                 item_epilogue<EPI>(p, ig, t0, t1, best_v, best_i);
             }
@@ -354,8 +361,8 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
     if constexpr (EPI == Epi::Logits) gemv_publish_best(p, best_v, best_i, bv, bi);
 }
 
-inline size_t gemv_smem_bytes(int K) {
-    return 2 * (((size_t)K * 2 + 15) & ~(size_t)15) + (size_t)(2 * kGemvWarps * 2 + 16) * sizeof(float);
+inline size_t gemv_smem_bytes(int K) {      // xs | norm weight | red + misc | fp32 staging of the residual row
+    return 2 * (((size_t)K * 2 + 15) & ~(size_t)15) + (size_t)(2 * kGemvWarps * 2 + 16) * sizeof(float) + (size_t)K * sizeof(float);
 }
 
 }  // namespace efm

@@ -14,7 +14,7 @@ namespace efm {
 __global__ void __launch_bounds__(128) embed_rows_kernel(const int32_t* __restrict__ ids,
                                                          const __nv_bfloat16* __restrict__ table,
                                                          const __nv_bfloat16* __restrict__ custom,
-                                                         __nv_bfloat16* __restrict__ out, int vocab, int hidden,
+                                                         float* __restrict__ out, int vocab, int hidden,
                                                          int embed_token_id, int n_custom) {
     const int t = blockIdx.x;
     const int id = ids[t];
@@ -23,24 +23,28 @@ __global__ void __launch_bounds__(128) embed_rows_kernel(const int32_t* __restri
         src = custom + (size_t)(id - embed_token_id) * hidden;
     else if (id >= 0 && id < vocab)
         src = table + (size_t)id * hidden;
-    uint4* dst = reinterpret_cast<uint4*>(out + (size_t)t * hidden);
-    for (int c = threadIdx.x; c < hidden / 8; c += blockDim.x)
-        dst[c] = src != nullptr ? ld_cached(src + (size_t)c * 8) : make_uint4(0, 0, 0, 0);
+    float4* dst = reinterpret_cast<float4*>(out + (size_t)t * hidden);      // residual stream: fp32
+    for (int c = threadIdx.x; c < hidden / 8; c += blockDim.x) {
+        float f[8];
+        unpack8(src != nullptr ? ld_cached(src + (size_t)c * 8) : make_uint4(0, 0, 0, 0), f);
+        dst[2 * c] = make_float4(f[0], f[1], f[2], f[3]);
+        dst[2 * c + 1] = make_float4(f[4], f[5], f[6], f[7]);
+    }
 }
 
-// y[s,:] = bf16(x[s,:] * rsqrt(mean(x^2) + eps) * w), fp32 inside (reference: FlashInfer RMSNorm
+// y[s,:] = bf16(x[s,:] * rsqrt(mean(x^2) + eps) * w), x = fp32 residual stream, fp32 inside (reference: FlashInfer RMSNorm
 // through src/operators/norm_op.cu:20-62; formula pinned by tests/operators/test_norm_sampler.py:62-64).
-__global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const __nv_bfloat16* __restrict__ x,
+__global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float* __restrict__ x,
                                                            const __nv_bfloat16* __restrict__ w,
                                                            __nv_bfloat16* __restrict__ y, int hidden, float eps) {
     __shared__ float part[8];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const __nv_bfloat16* xr = x + (size_t)blockIdx.x * hidden;
+    const float* xr = x + (size_t)blockIdx.x * hidden;
     const int nch = hidden >> 3;
     float ss = 0.f;
     for (int c = tid; c < nch; c += 256) {
-        float f[8];
-        unpack8(ld_cached(xr + (size_t)c * 8), f);
+        const float4 lo = reinterpret_cast<const float4*>(xr)[2 * c], hi = reinterpret_cast<const float4*>(xr)[2 * c + 1];
+        const float f[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
 #pragma unroll
         for (int j = 0; j < 8; ++j) ss = fmaf(f[j], f[j], ss);
     }
@@ -53,8 +57,9 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const __nv_bfloat16* 
     const float inv = 1.0f / sqrtf(tot / (float)hidden + eps);
     uint4* yr = reinterpret_cast<uint4*>(y + (size_t)blockIdx.x * hidden);
     for (int c = tid; c < nch; c += 256) {
-        float f[8], g[8];
-        unpack8(ld_cached(xr + (size_t)c * 8), f);
+        const float4 lo = reinterpret_cast<const float4*>(xr)[2 * c], hi = reinterpret_cast<const float4*>(xr)[2 * c + 1];
+        const float f[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+        float g[8];
         unpack8(ld_cached(w + (size_t)c * 8), g);
         uint4 o;
         o.x = pack_bf16(f[0] * inv * g[0], f[1] * inv * g[1]);
@@ -120,14 +125,13 @@ __global__ void __launch_bounds__(256) swiglu_rows_kernel(const float* __restric
     }
 }
 
-// Tensor parallel prefill: resid = bf16(resid + bf16(sum)), `sum` being the all-reduced fp32 output
-// of a row-parallel linear (same rounding points as the single-GPU residual epilogue).
-__global__ void __launch_bounds__(256) add_rows_kernel(__nv_bfloat16* __restrict__ resid, const float* __restrict__ sum,
+// Tensor parallel prefill: resid += sum, `sum` being the all-reduced fp32 output of a row-parallel linear.
+__global__ void __launch_bounds__(256) add_rows_kernel(float* __restrict__ resid, const float* __restrict__ sum,
                                                        size_t n_pairs) {
     for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n_pairs; i += (size_t)gridDim.x * 256) {
-        const uint32_t old = reinterpret_cast<const uint32_t*>(resid)[i];
+        const float2 old = reinterpret_cast<const float2*>(resid)[i];
         const float2 s = reinterpret_cast<const float2*>(sum)[i];
-        reinterpret_cast<uint32_t*>(resid)[i] = pack_bf16(bf16lo(old) + round_bf16(s.x), bf16hi(old) + round_bf16(s.y));
+        reinterpret_cast<float2*>(resid)[i] = make_float2(old.x + s.x, old.y + s.y);
     }
 }
 

@@ -102,7 +102,8 @@ EFM_API efm_status efm_b200_tp_init(efm_b200_ctx* ctx, const void* id128);
 /* Replaces WeightLoader::load_weights_from_file + per-layer load_weights
  * (src/utils/device/weight_loader.cpp:80-171, src/layers/linear.cu:1691-1717,1926-1943).
  * hf_name: e.g. "model.layers.3.self_attn.q_proj.weight"; data is row-major [out,in] bf16.
- * Unknown names are ignored (returns EFM_OK), like the reference's name filter. */
+ * Unknown names are ignored (returns EFM_OK), like the reference's name filter.  A device-resident
+ * source (EFM_MEM_DEVICE) is read on the context's own stream: whatever produced it must have finished. */
 EFM_API efm_status efm_b200_set_weight(efm_b200_ctx* ctx, const char* hf_name, const void* data,
                                        const int64_t* shape, int32_t ndim, int32_t dtype, int32_t mem_kind);
 /* Checks that every tensor arrived; after this call weights are immutable. */
@@ -172,8 +173,9 @@ EFM_API efm_status efm_b200_decode_step_bytes(efm_b200_ctx* ctx, int32_t kv_len,
 
 /* ---- single operators on caller-provided DEVICE buffers (parity tests per kernel; the
  * reference exposes the same granularity through its debug bindings, pybind_debug.cpp) ----- */
-/* y[n] = W[n,:] . x   (+ optional rmsnorm prologue when norm_w != NULL; + optional residual
- * epilogue r[n] = bf16(r[n] + bf16(y[n])) when residual != NULL, else y_bf16[n] written).
+/* y[n] = W[n,:] . x.  x is bf16 [k]; with norm_w != NULL it is instead the fp32 residual stream and
+ * x_used = bf16(rmsnorm(x) * norm_w).  With residual != NULL (fp32 [n]) the result is accumulated:
+ * residual[n] += y[n]; else y_bf16[n] is written.
  * LinearLayer decode GEMV (src/operators/linear_impl.cu:457-469). */
 EFM_API efm_status efm_b200_op_gemv(const void* w, const void* x, const void* norm_w, float eps,
                                     void* y_bf16, void* residual, int32_t n, int32_t k);

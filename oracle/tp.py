@@ -11,7 +11,7 @@ checked on CPU with gloo ranks against the unpartitioned oracle:
 * MLP: gate/up rows and down columns in tp equal parts;
 * lm_head: vocabulary rows in tp equal parts, logits all-gathered;
 * embedding and norms replicated; o_proj / down outputs are summed in fp32 across ranks, then the
-  residual add rounds exactly as on one GPU: r = bf16(r + bf16(sum)).
+  residual add happens in fp32 exactly as on one GPU: r += sum.
 """
 from __future__ import annotations
 
@@ -100,10 +100,10 @@ class TpOracle:
             s = s.masked_fill(~mask[None], float("-inf"))
             attn = r(torch.einsum("hst,thd->shd", torch.softmax(s, dim=-1), V).reshape(S, q_l * D))
             mine = attn[:, lay["rep"] * lay["o_k"]:(lay["rep"] + 1) * lay["o_k"]]
-            R = r(R + r(self._sum(mine @ w["wo"].T)))
+            R = R + self._sum(mine @ w["wo"].T)
             n2 = r(rmsnorm(R, w["post_norm"], c.rms_eps))
             act = r(silu(n2 @ w["wg"].T) * (n2 @ w["wu"].T))
-            R = r(R + r(self._sum(act @ w["wd"].T)))
+            R = R + self._sum(act @ w["wd"].T)
         hn = r(rmsnorm(R[-1:], self.final_norm, c.rms_eps))
         local = (hn @ self.lm_head.T)[0].contiguous()
         if self.tp == 1:

@@ -136,8 +136,26 @@ class Backend:
             t = t.contiguous()
             shape = (C.c_int64 * t.dim())(*t.shape)
             mem = EFM_MEM_DEVICE if t.is_cuda else EFM_MEM_HOST
+            if t.is_cuda:        # the backend copies on its own stream: the producer's work must be complete
+                import torch
+                torch.cuda.current_stream(t.device).synchronize()
             self.check(self.L.efm_b200_set_weight(self.ctx, name.encode(), P(t.data_ptr()), shape, t.dim(),
                                                   EFM_BF16, mem), "set_weight " + name)
+        self.check(self.L.efm_b200_finalize_weights(self.ctx), "finalize_weights")
+
+    def load_weights_partial(self, weights):
+        """set_weight only (call finalize() after the last batch)."""
+        for name, t in weights.items():
+            t = t.contiguous()
+            shape = (C.c_int64 * t.dim())(*t.shape)
+            mem = EFM_MEM_DEVICE if t.is_cuda else EFM_MEM_HOST
+            if t.is_cuda:
+                import torch
+                torch.cuda.current_stream(t.device).synchronize()
+            self.check(self.L.efm_b200_set_weight(self.ctx, name.encode(), P(t.data_ptr()), shape, t.dim(),
+                                                  EFM_BF16, mem), "set_weight " + name)
+
+    def finalize(self):
         self.check(self.L.efm_b200_finalize_weights(self.ctx), "finalize_weights")
 
     def alloc_slot(self, slot, max_tokens):
@@ -152,6 +170,9 @@ class Backend:
         ep, ne, em = None, 0, EFM_MEM_HOST
         if embeds is not None:
             embeds = embeds.contiguous()
+            if embeds.is_cuda:
+                import torch
+                torch.cuda.current_stream(embeds.device).synchronize()
             ep, ne = P(embeds.data_ptr()), embeds.shape[0]
             em = EFM_MEM_DEVICE if embeds.is_cuda else EFM_MEM_HOST
         pp = None

@@ -77,7 +77,6 @@ struct efm_b200_ctx {
     __nv_bfloat16* qkv = nullptr;         // [max_s, (q+2kv)*D]
     __nv_bfloat16* qbuf = nullptr;        // [max_s, q*D]
     __nv_bfloat16* attn = nullptr;        // [max_s, q*D]
-    float* gu = nullptr;                  // [max_s, 2I] fp32
     __nv_bfloat16* act = nullptr;         // [max_s, I]
     __nv_bfloat16* custom_embeds = nullptr;
     size_t custom_embeds_cap = 0;

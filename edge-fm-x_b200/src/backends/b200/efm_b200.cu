@@ -201,7 +201,6 @@ efm_status efm_b200_create(const efm_model_desc* desc, int32_t device_id, int32_
     EFM_TRY(dev_alloc(c, &c->qkv, S * (QD + 2 * KVD)));
     EFM_TRY(dev_alloc(c, &c->qbuf, S * QD));
     EFM_TRY(dev_alloc(c, &c->attn, S * QD));
-    EFM_TRY(dev_alloc(c, &c->gu, S * 2 * I));
     EFM_TRY(dev_alloc(c, &c->act, S * I));
     EFM_TRY(dev_alloc(c, &c->resid_d, H));
     EFM_TRY(dev_alloc(c, &c->resid_d2, H));

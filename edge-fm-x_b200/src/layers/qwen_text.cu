@@ -7,6 +7,7 @@
 // and norm + lm_head + block argmax | sampler + state advance at the end of the step.
 #include "qwen_text.h"
 
+#include "../operators/attention_mma.cuh"
 #include "../operators/gemm_tc.cuh"
 #include "../operators/prefill.cuh"
 #include "../operators/sample.cuh"
@@ -335,15 +336,54 @@ static void launch_gemm(Launcher& L, const GemmParams& p, int* error_word = null
 
 void launch_gemm_bf16(Launcher& L, const GemmParams& p) { launch_gemm<GemmEpi::Bf16Bias>(L, p); }
 
-void launch_prefill_attention(Launcher& L, const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v,
-                              __nv_bfloat16* out, int S, int kv_offset, int q_heads, int kv_heads, int D) {
-    const dim3 grid((S + 3) / 4, q_heads), block(128);
-    const float scale = 1.0f / sqrtf((float)D);
+void launch_rmsnorm_rows(Launcher& L, const float* x, const __nv_bfloat16* w, __nv_bfloat16* y, int rows, int hidden, float eps) {
     const bool pdl = L.pdl;
     L.pdl = false;
-    if (D == 128) L.launch(prefill_attention_kernel<128>, grid, block, 0, q, k, v, out, S, kv_offset, q_heads, kv_heads, scale);
-    else L.launch(prefill_attention_kernel<64>, grid, block, 0, q, k, v, out, S, kv_offset, q_heads, kv_heads, scale);
+    L.launch(rmsnorm_rows_kernel, dim3(rows), dim3(256), 0, x, w, y, hidden, eps);
     L.pdl = pdl;
+}
+
+void launch_gemm_epi(Launcher& L, GemmEpi epi, const GemmParams& p, int* error_word) {
+    switch (epi) {
+        case GemmEpi::Bf16Bias: launch_gemm<GemmEpi::Bf16Bias>(L, p, error_word); break;
+        case GemmEpi::Residual: launch_gemm<GemmEpi::Residual>(L, p, error_word); break;
+        case GemmEpi::F32: launch_gemm<GemmEpi::F32>(L, p, error_word); break;
+        case GemmEpi::Bf16Gelu: launch_gemm<GemmEpi::Bf16Gelu>(L, p, error_word); break;
+        case GemmEpi::SwiGlu: launch_gemm<GemmEpi::SwiGlu>(L, p, error_word); break;
+    }
+}
+
+template <int D>
+static void launch_seg_attention_d(Launcher& L, const SegAttnParams& p) {
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaFuncSetAttribute(seg_attention_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sa::smem_bytes<D>());
+        attr_set = true;
+    }
+    const dim3 grid((p.S + sa::BQ - 1) / sa::BQ, p.q_heads), block(sa::kThreads);
+    const bool pdl = L.pdl;
+    L.pdl = false;
+    L.launch(seg_attention_kernel<D>, grid, block, sa::smem_bytes<D>(), p);
+    L.pdl = pdl;
+}
+
+void launch_seg_attention(Launcher& L, const SegAttnParams& p, int D) {
+    if (p.S <= 0) return;
+    if (D == 128) launch_seg_attention_d<128>(L, p);
+    else if (D == 80) launch_seg_attention_d<80>(L, p);
+    else if (D == 64) launch_seg_attention_d<64>(L, p);
+    else if (L.err == cudaSuccess) L.err = cudaErrorInvalidValue;
+}
+
+// Causal GQA attention of a prefill chunk: queries at cache rows [kv_offset, kv_offset + S).
+void launch_prefill_attention(Launcher& L, const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v,
+                              __nv_bfloat16* out, int S, int kv_offset, int q_heads, int kv_heads, int D) {
+    SegAttnParams p{};
+    p.q = q; p.k = k; p.v = v; p.out = out;
+    p.q_stride = q_heads * D; p.kv_stride = kv_heads * D; p.out_stride = q_heads * D;
+    p.S = S; p.kv_offset = kv_offset; p.q_heads = q_heads; p.kv_heads = kv_heads;
+    p.scale = 1.0f / sqrtf((float)D);
+    launch_seg_attention(L, p, D);
 }
 
 void qwen_prefill_chunk(efm_b200_ctx& c, KvSlot& slot, int S, int kv_offset, int n_custom, int embed_token_id,
@@ -379,14 +419,9 @@ void qwen_prefill_chunk(efm_b200_ctx& c, KvSlot& slot, int S, int kv_offset, int
         }
         L.launch(rmsnorm_rows_kernel, dim3(S), dim3(256), 0, (const float*)c.resid,
                  (const __nv_bfloat16*)w.post_norm, c.norm, H, d.rms_eps);
-        {
-            GemmParams g{c.norm, w.gate_up, nullptr, nullptr, c.gu, S, 2 * I, H};
-            launch_gemm<GemmEpi::F32>(L, g, &c.state->error);
-        }
-        {
-            const size_t total = (size_t)S * I;
-            const int grid = (int)std::min<size_t>((total + 255) / 256, (size_t)c.num_sms * 8);
-            L.launch(swiglu_rows_kernel, dim3(grid), dim3(256), 0, (const float*)c.gu, c.act, S, I);
+        {     // gate|up with silu(gate) * up in the epilogue
+            GemmParams g{c.norm, w.gate_up, nullptr, c.act, nullptr, S, 2 * I, H};
+            launch_gemm<GemmEpi::SwiGlu>(L, g, &c.state->error);
         }
         if (c.tp_size == 1) {
             GemmParams g{c.act, w.down, nullptr, nullptr, c.resid, S, H, I};

@@ -6,6 +6,8 @@ namespace efm {
 struct Launcher;
 struct GemmParams;
 struct SampleParams;
+struct SegAttnParams;
+enum class GemmEpi : int;
 
 // One decode step: reads the device state (token, kv_len, positions), appends K/V at row
 // kv_len-1, samples, advances the state.  All launches go through L (graph-capturable).
@@ -17,7 +19,14 @@ void qwen_prefill_chunk(efm_b200_ctx& c, KvSlot& slot, int S, int kv_offset, int
 void launch_lm_head_and_sample(efm_b200_ctx& c, Launcher& L, const float* resid_row, int advance);
 // Single operators (used by the per-operator C entry points).
 void launch_gemm_bf16(Launcher& L, const GemmParams& p);
+// C = A . B^T on the tensor cores with the named epilogue; error_word (device int, may be null) is
+// raised when a bounded pipeline wait gives up.
+void launch_gemm_epi(Launcher& L, GemmEpi epi, const GemmParams& p, int* error_word);
+// Attention with per-query key ranges (or the causal prefill rule when p.lo is null).
+void launch_seg_attention(Launcher& L, const SegAttnParams& p, int D);
 void launch_sample(Launcher& L, const SampleParams& p);
+// y[r,:] = bf16(rmsnorm(x[r,:]) * w) over `rows` fp32 rows.
+void launch_rmsnorm_rows(Launcher& L, const float* x, const __nv_bfloat16* w, __nv_bfloat16* y, int rows, int hidden, float eps);
 void launch_prefill_attention(Launcher& L, const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v,
                               __nv_bfloat16* out, int S, int kv_offset, int q_heads, int kv_heads, int D);
 }  // namespace efm

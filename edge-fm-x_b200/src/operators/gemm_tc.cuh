@@ -9,7 +9,7 @@
 //   warp 1      allocates 128 TMEM columns; one lane issues tcgen05.mma (M 128, N 128, K 16, four
 //               per stage) and tcgen05.commit, which releases the stage to the producer;
 //   warps 2-5   epilogue: tcgen05.ld the accumulator (row = TMEM lane, 32 columns at a time) and
-//               write bf16 (+bias) | fp32 residual add | fp32.
+//               write bf16 (+bias, optionally erf-GELU) | fp32 residual add | fp32 | silu(gate)*up in bf16.
 // Rows past M and columns past N are zero-filled by TMA on load and masked on store.
 // Every mbarrier wait is bounded; a wait that gives up raises *error, the block frees its TMEM and
 // returns.  Bound: tensor pipe (2 M N K flops).
@@ -20,13 +20,13 @@
 
 namespace efm {
 
-enum class GemmEpi : int { Bf16Bias = 0, Residual = 1, F32 = 2 };
+enum class GemmEpi : int { Bf16Bias = 0, Residual = 1, F32 = 2, Bf16Gelu = 3, SwiGlu = 4 };
 
 struct GemmParams {
     const __nv_bfloat16* A;   // [M, K] (row stride lda)
     const __nv_bfloat16* B;   // [N, K]
     const __nv_bfloat16* bias;
-    __nv_bfloat16* C;         // Bf16Bias: out
+    __nv_bfloat16* C;         // Bf16Bias / Bf16Gelu: out [M, N]; SwiGlu: out [M, N/2]
     float* Cf;                // F32: out; Residual: in/out (fp32 residual stream)
     int M, N, K;
     int lda = 0;              // row stride of A in elements (0: K)
@@ -179,6 +179,34 @@ __global__ void __launch_bounds__(tc::kThreads) gemm_tc_kernel(const __grid_cons
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const int m = m0 + q * 32 + lane;
         if (ok && *abort_s == 0) {
+            if constexpr (EPI == GemmEpi::SwiGlu) {
+                // fused gate|up weight: columns [n0, n0+64) are gate rows, [n0+64, n0+128) the up rows of the
+                // same 64 intermediate channels; out[m, n0/2 + j] = silu(gate_j) * up_j
+#pragma unroll 1
+                for (int c0 = 0; c0 < 64; c0 += 32) {
+                    uint32_t rg[32], ru[32];
+                    tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, rg);
+                    tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(64 + c0), ru);
+                    const int n = n0 + c0;                          // gate column in the fused output
+                    if (m < p.M && n0 + 128 <= p.N) {
+                        const size_t off = (size_t)m * (p.N >> 1) + (n0 >> 1) + c0;
+                        uint32_t o[16];
+#pragma unroll
+                        for (int j = 0; j < 32; j += 2) {
+                            float g0 = __uint_as_float(rg[j]), g1 = __uint_as_float(rg[j + 1]);
+                            float u0 = __uint_as_float(ru[j]), u1 = __uint_as_float(ru[j + 1]);
+                            if (p.bias != nullptr) {
+                                g0 += __bfloat162float(p.bias[n + j]);      g1 += __bfloat162float(p.bias[n + j + 1]);
+                                u0 += __bfloat162float(p.bias[n + 64 + j]); u1 += __bfloat162float(p.bias[n + 64 + j + 1]);
+                            }
+                            o[j >> 1] = pack_bf16(g0 / (1.0f + __expf(-g0)) * u0, g1 / (1.0f + __expf(-g1)) * u1);
+                        }
+#pragma unroll
+                        for (int j = 0; j < 16; j += 4)
+                            *reinterpret_cast<uint4*>(p.C + off + 2 * j) = make_uint4(o[j], o[j + 1], o[j + 2], o[j + 3]);
+                    }
+                }
+            } else {
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 uint32_t r[32];
@@ -190,11 +218,13 @@ __global__ void __launch_bounds__(tc::kThreads) gemm_tc_kernel(const __grid_cons
                     float v[32];
 #pragma unroll
                     for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-                    if constexpr (EPI == GemmEpi::Bf16Bias) {
-                        if (p.bias != nullptr) {
+                    if (p.bias != nullptr) {
 #pragma unroll
-                            for (int j = 0; j < 32; ++j) if (j < nv) v[j] += __bfloat162float(p.bias[n + j]);
-                        }
+                        for (int j = 0; j < 32; ++j) if (j < nv) v[j] += __bfloat162float(p.bias[n + j]);
+                    }
+                    if constexpr (EPI == GemmEpi::Bf16Gelu) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = 0.5f * v[j] * (1.0f + erff(v[j] * 0.70710678118654752f));
                     }
                     const bool wide = nv == 32 && (p.N & 7) == 0;  // 16-byte aligned row segments
                     if constexpr (EPI == GemmEpi::F32) {
@@ -203,18 +233,20 @@ __global__ void __launch_bounds__(tc::kThreads) gemm_tc_kernel(const __grid_cons
                             for (int j = 0; j < 32; j += 4)
                                 *reinterpret_cast<float4*>(p.Cf + off + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
                         } else {
-                            for (int j = 0; j < nv; j += 2) *reinterpret_cast<float2*>(p.Cf + off + j) = make_float2(v[j], v[j + 1]);
+#pragma unroll
+                            for (int j = 0; j < 32; j += 2) if (j < nv) *reinterpret_cast<float2*>(p.Cf + off + j) = make_float2(v[j], v[j + 1]);
                         }
-                    } else if constexpr (EPI == GemmEpi::Bf16Bias) {
+                    } else if constexpr (EPI == GemmEpi::Bf16Bias || EPI == GemmEpi::Bf16Gelu) {
                         if (wide) {
 #pragma unroll
                             for (int j = 0; j < 32; j += 8)
                                 *reinterpret_cast<uint4*>(p.C + off + j) = make_uint4(pack_bf16(v[j], v[j + 1]), pack_bf16(v[j + 2], v[j + 3]),
                                                                                        pack_bf16(v[j + 4], v[j + 5]), pack_bf16(v[j + 6], v[j + 7]));
                         } else {
-                            for (int j = 0; j < nv; j += 2) *reinterpret_cast<uint32_t*>(p.C + off + j) = pack_bf16(v[j], v[j + 1]);
+#pragma unroll
+                            for (int j = 0; j < 32; j += 2) if (j < nv) *reinterpret_cast<uint32_t*>(p.C + off + j) = pack_bf16(v[j], v[j + 1]);
                         }
-                    } else {      // residual stream in fp32: Cf += acc
+                    } else {      // residual stream in fp32: Cf += acc (+ bias)
                         if (wide) {
 #pragma unroll
                             for (int j = 0; j < 32; j += 4) {
@@ -222,13 +254,15 @@ __global__ void __launch_bounds__(tc::kThreads) gemm_tc_kernel(const __grid_cons
                                 *reinterpret_cast<float4*>(p.Cf + off + j) = make_float4(o.x + v[j], o.y + v[j + 1], o.z + v[j + 2], o.w + v[j + 3]);
                             }
                         } else {
-                            for (int j = 0; j < nv; j += 2) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 2) if (j < nv) {
                                 const float2 o = *reinterpret_cast<const float2*>(p.Cf + off + j);
                                 *reinterpret_cast<float2*>(p.Cf + off + j) = make_float2(o.x + v[j], o.y + v[j + 1]);
                             }
                         }
                     }
                 }
+            }
             }
         }
     }

@@ -110,21 +110,6 @@ __global__ void rope_scatter_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_
     }
 }
 
-// act[s, j] = bf16(silu(gate) * up) from the fp32 fused projection [S, 2I] whose columns come in
-// blocks of 64 gate values followed by the 64 matching up values
-// (reference: act_and_mul, src/operators/activation_op.cu:35-76).
-__global__ void __launch_bounds__(256) swiglu_rows_kernel(const float* __restrict__ gu,
-                                                          __nv_bfloat16* __restrict__ act, int S, int I) {
-    const size_t total = (size_t)S * I;
-    for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (size_t)gridDim.x * 256) {
-        const size_t s = i / I;
-        const int j = (int)(i - s * I);
-        const float* row = gu + s * 2 * (size_t)I + ((j >> 6) << 7) + (j & 63);
-        const float g = row[0], u = row[64];
-        act[i] = __float2bfloat16_rn(g / (1.0f + expf(-g)) * u);
-    }
-}
-
 // Tensor parallel prefill: resid += sum, `sum` being the all-reduced fp32 output of a row-parallel linear.
 __global__ void __launch_bounds__(256) add_rows_kernel(float* __restrict__ resid, const float* __restrict__ sum,
                                                        size_t n_pairs) {
@@ -132,105 +117,6 @@ __global__ void __launch_bounds__(256) add_rows_kernel(float* __restrict__ resid
         const float2 old = reinterpret_cast<const float2*>(resid)[i];
         const float2 s = reinterpret_cast<const float2*>(sum)[i];
         reinterpret_cast<float2*>(resid)[i] = make_float2(old.x + s.x, old.y + s.y);
-    }
-}
-
-// Causal GQA prefill attention on CUDA cores: one warp per (query, q head); the warp is four
-// independent 8-lane streams, stream j walking keys j, j+4, ... with its own online-softmax
-// state; the four states merge at the end.  Queries sit at cache rows kv_offset + s and see rows
-// [0, kv_offset + s] (reference: prefill attention with the q offset, qwen2_5.cpp:812-814;
-// FlashInfer SinglePrefillWithKVCache through src/operators/attention_op.cu:1221-1343).
-// Grid (ceil(S/4), q_heads), 128 threads.
-template <int D>
-__global__ void __launch_bounds__(128) prefill_attention_kernel(const __nv_bfloat16* __restrict__ q,
-                                                                const __nv_bfloat16* __restrict__ k_cache,
-                                                                const __nv_bfloat16* __restrict__ v_cache,
-                                                                __nv_bfloat16* __restrict__ out, int S,
-                                                                int kv_offset, int q_heads, int kv_heads,
-                                                                float scale) {
-    constexpr int E = D / 8;                 // channels per lane
-    constexpr int NV = E / 8;                // uint4 per lane and row
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int s = blockIdx.x * 4 + warp, h = blockIdx.y;
-    if (s >= S) return;
-    const int kvh = h / (q_heads / kv_heads);
-    const int stream = lane >> 3, part = lane & 7;
-    const size_t row_stride = (size_t)kv_heads * D;
-    float qf[E];
-    {
-        const __nv_bfloat16* qr = q + ((size_t)s * q_heads + h) * D + part * E;
-#pragma unroll
-        for (int j = 0; j < NV; ++j) {
-            float t[8];
-            unpack8(ld_cached(qr + j * 8), t);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) qf[j * 8 + e] = t[e] * scale;
-        }
-    }
-    float m = -INFINITY, l = 0.f, o[E];
-#pragma unroll
-    for (int e = 0; e < E; ++e) o[e] = 0.f;
-    const int n_keys = kv_offset + s + 1;
-    const int n_iter = (n_keys + 3) >> 2;    // every lane runs the same trip count (shuffles inside)
-    for (int it = 0; it < n_iter; ++it) {
-        const int t = it * 4 + stream;
-        const bool valid = t < n_keys;
-        const size_t off = (size_t)(valid ? t : 0) * row_stride + (size_t)kvh * D + part * E;
-        uint4 kv[NV], vv[NV];
-#pragma unroll
-        for (int j = 0; j < NV; ++j) { kv[j] = ld_cached(k_cache + off + j * 8); vv[j] = ld_cached(v_cache + off + j * 8); }
-        float dot = 0.f;
-#pragma unroll
-        for (int j = 0; j < NV; ++j) {
-            float kf[8];
-            unpack8(kv[j], kf);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) dot = fmaf(kf[e], qf[j * 8 + e], dot);
-        }
-        dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-        dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-        dot += __shfl_xor_sync(0xffffffffu, dot, 4);
-        if (valid) {
-            const float mn = fmaxf(m, dot);
-            const float corr = expf(m - mn), pj = expf(dot - mn);
-            l = l * corr + pj;
-#pragma unroll
-            for (int j = 0; j < NV; ++j) {
-                float vf[8];
-                unpack8(vv[j], vf);
-#pragma unroll
-                for (int e = 0; e < 8; ++e) o[j * 8 + e] = fmaf(pj, vf[e], o[j * 8 + e] * corr);
-            }
-            m = mn;
-        }
-    }
-    // merge the four streams (lanes with equal `part`)
-#pragma unroll
-    for (int sh = 8; sh < 32; sh <<= 1) {
-        const float mo = __shfl_xor_sync(0xffffffffu, m, sh);
-        const float lo = __shfl_xor_sync(0xffffffffu, l, sh);
-        const float mn = fmaxf(m, mo);
-        const float ca = mn == -INFINITY ? 0.f : expf(m - mn), cb = mn == -INFINITY ? 0.f : expf(mo - mn);
-        l = l * ca + lo * cb;
-#pragma unroll
-        for (int e = 0; e < E; ++e) {
-            const float oo = __shfl_xor_sync(0xffffffffu, o[e], sh);
-            o[e] = o[e] * ca + oo * cb;
-        }
-        m = mn;
-    }
-    if (stream == 0) {
-        const float inv = l > 0.f ? 1.0f / l : 0.f;
-        __nv_bfloat16* dst = out + ((size_t)s * q_heads + h) * D + part * E;
-#pragma unroll
-        for (int j = 0; j < NV; ++j) {
-            uint4 v;
-            v.x = pack_bf16(o[j * 8 + 0] * inv, o[j * 8 + 1] * inv);
-            v.y = pack_bf16(o[j * 8 + 2] * inv, o[j * 8 + 3] * inv);
-            v.z = pack_bf16(o[j * 8 + 4] * inv, o[j * 8 + 5] * inv);
-            v.w = pack_bf16(o[j * 8 + 6] * inv, o[j * 8 + 7] * inv);
-            reinterpret_cast<uint4*>(dst)[j] = v;
-        }
     }
 }
 

@@ -217,6 +217,62 @@ EFM_API efm_status efm_b200_op_prefill_attention(const void* q, const void* k_ca
 EFM_API efm_status efm_b200_op_sample(const float* logits, int32_t vocab, const efm_sampling* s,
                                       uint32_t rng_step, int32_t* token_out);
 
+/* Softmax attention where query row i sees the key rows [lo[i], hi[i]) (device int32 [s]); the
+ * bidirectional windowed / full attention of the vision tower.  q, k, v are rows of `stride`
+ * elements with head h at column h*D (q, k, v may be three column ranges of one fused qkv
+ * buffer); out: [s, heads*D] bf16.  head_dim 64, 80 or 128.  No counterpart in the reference. */
+EFM_API efm_status efm_b200_op_segment_attention(const void* q, const void* k, const void* v, void* out_bf16,
+                                                 const int32_t* lo, const int32_t* hi, int32_t s,
+                                                 int32_t heads, int32_t head_dim, int32_t stride);
+
+/* ---- Qwen2.5-VL vision encoder ------------------------------------------------------------
+ * The reference has no vision tower: callers run one elsewhere and pass its output through
+ * Request.embedding (examples/qwen2.5-vl-3b-instruct/generate.py:3, embed_head.cu:63-132).
+ * These entry points produce exactly that tensor on the device, on the stream of the text
+ * context they were created from, so that encode -> efm_b200_prefill(embeds, EFM_MEM_DEVICE)
+ * needs no copy and no host synchronisation.  Algorithm: the published Qwen2.5-VL encoder
+ * (patch embedding, window-major token order, 2-D rotary, windowed / full bidirectional
+ * attention, SiLU-gated MLP, 2x2 merger). */
+typedef struct efm_vit_desc {
+    int32_t struct_size;          /* = sizeof(efm_vit_desc) */
+    int32_t depth;
+    int32_t hidden;               /* heads * head_dim */
+    int32_t heads;                /* head_dim 64, 80 or 128 */
+    int32_t intermediate;         /* any multiple of 4 (zero-padded to 64 inside) */
+    int32_t out_hidden;           /* width of the produced embeddings = LLM hidden */
+    int32_t patch;                /* 14 */
+    int32_t temporal_patch;       /* 2 */
+    int32_t in_channels;          /* 3 */
+    int32_t merge;                /* 2: merge x merge patches per produced token */
+    int32_t window;               /* 112 (pixels) */
+    int32_t n_fullatt;            /* number of layers with full attention, <= 8 */
+    int32_t fullatt[8];           /* their indices */
+    float rms_eps;
+    float rope_theta;
+    int32_t max_patches;          /* capacity of one encode call */
+} efm_vit_desc;
+
+typedef struct efm_b200_vit efm_b200_vit;
+
+/* The encoder lives on ctx's device and stream and reports errors through
+ * efm_b200_last_error(ctx); destroy it before ctx. */
+EFM_API efm_status efm_b200_vit_create(efm_b200_ctx* ctx, const efm_vit_desc* desc, efm_b200_vit** out);
+EFM_API efm_status efm_b200_vit_destroy(efm_b200_vit* vit);
+/* HF tensor names "visual.*" (patch_embed.proj, blocks.N.{norm1,norm2,attn.qkv,attn.proj,
+ * mlp.gate_proj,mlp.up_proj,mlp.down_proj}, merger.{ln_q,mlp.0,mlp.2}); bf16, whole tensors. */
+EFM_API efm_status efm_b200_vit_set_weight(efm_b200_vit* vit, const char* hf_name, const void* data,
+                                           const int64_t* shape, int32_t ndim, int32_t dtype,
+                                           int32_t mem_kind);
+EFM_API efm_status efm_b200_vit_finalize_weights(efm_b200_vit* vit);
+/* pixels: bf16 [n_patches, in_channels*temporal_patch*patch*patch] in the image processor's row
+ * order (every merge*merge consecutive rows are one block), host or device per pixels_mem.
+ * grid_thw: host int32 [n_grids, 3] patch grids (frames, rows, columns); n_patches = sum t*h*w.
+ * out: bf16 [n_patches / merge^2, out_hidden], host or device per out_mem, in the original
+ * (row-major merged-grid) order.  Asynchronous on the context's stream when out is on the device. */
+EFM_API efm_status efm_b200_vit_encode(efm_b200_vit* vit, const void* pixels, int32_t pixels_mem,
+                                       const int32_t* grid_thw, int32_t n_grids, void* out,
+                                       int32_t out_mem);
+
 #ifdef __cplusplus
 }
 #endif

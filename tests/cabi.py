@@ -27,6 +27,14 @@ class ModelDesc(C.Structure):
                 ("max_response_tokens", C.c_int32)]
 
 
+class VitDesc(C.Structure):
+    _fields_ = [("struct_size", C.c_int32), ("depth", C.c_int32), ("hidden", C.c_int32), ("heads", C.c_int32),
+                ("intermediate", C.c_int32), ("out_hidden", C.c_int32), ("patch", C.c_int32),
+                ("temporal_patch", C.c_int32), ("in_channels", C.c_int32), ("merge", C.c_int32),
+                ("window", C.c_int32), ("n_fullatt", C.c_int32), ("fullatt", C.c_int32 * 8),
+                ("rms_eps", C.c_float), ("rope_theta", C.c_float), ("max_patches", C.c_int32)]
+
+
 class Sampling(C.Structure):
     _fields_ = [("temperature", C.c_float), ("top_p", C.c_float), ("top_k", C.c_int32),
                 ("reserved", C.c_uint32), ("seed", C.c_uint64)]
@@ -65,6 +73,12 @@ SIGNATURES = {
     "efm_b200_op_decode_attention_noalloc": (I32, [P, P, P, P, I32, I32, I32, I32, I32]),
     "efm_b200_op_prefill_attention": (I32, [P, P, P, P, I32, I32, I32, I32, I32]),
     "efm_b200_op_sample": (I32, [C.POINTER(C.c_float), I32, C.POINTER(Sampling), C.c_uint32, C.POINTER(I32)]),
+    "efm_b200_op_segment_attention": (I32, [P, P, P, P, P, P, I32, I32, I32, I32]),
+    "efm_b200_vit_create": (I32, [P, C.POINTER(VitDesc), C.POINTER(P)]),
+    "efm_b200_vit_destroy": (I32, [P]),
+    "efm_b200_vit_set_weight": (I32, [P, C.c_char_p, P, C.POINTER(C.c_int64), I32, I32, I32]),
+    "efm_b200_vit_finalize_weights": (I32, [P]),
+    "efm_b200_vit_encode": (I32, [P, P, I32, C.POINTER(I32), I32, P, I32]),
 }
 
 _lib = None
@@ -238,6 +252,50 @@ class Backend:
         p, mt = P(), I32()
         self.check(self.L.efm_b200_kv_layer_ptr(self.ctx, slot, layer, C.byref(p), C.byref(mt)), "kv_layer_ptr")
         return p.value, mt.value
+
+
+class VitEncoder:
+    """Vision encoder bound to a Backend's device and stream (efm_b200_vit_*)."""
+
+    def __init__(self, be: Backend, vcfg, max_patches):
+        self.be, self.L, self.cfg = be, be.L, vcfg
+        d = VitDesc()
+        d.struct_size = C.sizeof(VitDesc)
+        d.depth, d.hidden, d.heads, d.intermediate = vcfg.depth, vcfg.hidden, vcfg.heads, vcfg.intermediate
+        d.out_hidden, d.patch, d.temporal_patch, d.in_channels = vcfg.out_hidden, vcfg.patch, vcfg.temporal_patch, vcfg.in_channels
+        d.merge, d.window, d.n_fullatt = vcfg.merge, vcfg.window, len(vcfg.fullatt)
+        d.fullatt[:len(vcfg.fullatt)] = list(vcfg.fullatt)
+        d.rms_eps, d.rope_theta, d.max_patches = vcfg.rms_eps, vcfg.rope_theta, max_patches
+        self.h = P()
+        be.check(self.L.efm_b200_vit_create(be.ctx, C.byref(d), C.byref(self.h)), "vit_create")
+
+    def close(self):
+        if self.h:
+            self.L.efm_b200_vit_destroy(self.h)
+            self.h = P()
+
+    def load_weights(self, weights):
+        for name, t in weights.items():
+            t = t.contiguous()
+            shape = (C.c_int64 * t.dim())(*t.shape)
+            if t.is_cuda:
+                import torch
+                torch.cuda.current_stream(t.device).synchronize()
+            self.be.check(self.L.efm_b200_vit_set_weight(self.h, name.encode(), P(t.data_ptr()), shape, t.dim(), EFM_BF16,
+                                                         EFM_MEM_DEVICE if t.is_cuda else EFM_MEM_HOST), "vit_set_weight " + name)
+        self.be.check(self.L.efm_b200_vit_finalize_weights(self.h), "vit_finalize_weights")
+
+    def encode(self, pixels, grids, out):
+        """pixels, out: torch bf16 tensors (CPU or CUDA); grids: list of (t, h, w)."""
+        pixels = pixels.contiguous()
+        if pixels.is_cuda or out.is_cuda:
+            import torch
+            torch.cuda.current_stream().synchronize()
+        flat = _i32_array([v for g in grids for v in g])
+        self.be.check(self.L.efm_b200_vit_encode(self.h, P(pixels.data_ptr()), EFM_MEM_DEVICE if pixels.is_cuda else EFM_MEM_HOST,
+                                                 flat, len(grids), P(out.data_ptr()),
+                                                 EFM_MEM_DEVICE if out.is_cuda else EFM_MEM_HOST), "vit_encode")
+        return out
 
 
 def generate(be: Backend, slot, prompt, max_new_tokens, *, prefix_len=0, embeds=None, embed_token_id=-1, pos3=None,

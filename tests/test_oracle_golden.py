@@ -132,3 +132,32 @@ def test_synthetic_checkpoint_roundtrip(tmp_path):
     assert set(back) == set(w) and all(torch.equal(back[k], w[k]) for k in w)
     w2 = synth.make_weights(cfg, seed=0)
     assert all(torch.equal(w[k], w2[k]) for k in w)      # seeded: identical on every machine
+
+
+# ---- vision tower: pinned to transformers' Qwen2_5_VisionTransformerPretrainedModel ---------------------
+@pytest.mark.parametrize("case", ["one_window", "ragged", "frames_and_image"])
+def test_vit_oracle_reproduces_hf_outputs(case):
+    from oracle import qwen_vit
+    z = np.load(os.path.join(os.path.dirname(__file__), "golden", "qwen_vit_tiny.npz"))
+    cfg = qwen_vit.VitConfig(**eval(str(z["cfg"])))
+    w = qwen_vit.make_weights(cfg, seed=int(z["seed"]))
+    grids = [tuple(g) for g in z[case + "_grids"].tolist()]
+    px = qwen_vit.make_pixels(cfg, grids, seed=int(z["seed"]))
+    want = z[case + "_out"]
+    got = qwen_vit.VitOracle(cfg, w, "exact_fp32").forward(px, grids).numpy()
+    assert np.abs(got - want).max() < 2e-5
+    got_b = qwen_vit.VitOracle(cfg, w, "bf16_points").forward(px, grids).numpy()
+    assert np.abs(got_b - want).max() < 1e-2             # bf16 rounding points only
+
+
+def test_vit_plan_windows_of_the_benchmark_images():
+    from oracle import qwen_vit
+    cfg = qwen_vit.CONFIGS[2]
+    p = qwen_vit.make_plan(cfg, [qwen_vit.GRIDS[2]])      # 448x448: 16 windows of 64 patches
+    lens = np.diff(p.cu_window)
+    assert len(lens) == 16 and set(lens) == {64} and sorted(p.order) == list(range(256))
+    p = qwen_vit.make_plan(cfg, [qwen_vit.GRIDS[3]])      # 1288x728: 92x52 patches, 84 windows
+    lens = np.diff(p.cu_window)
+    assert len(lens) == 84 and set(lens) == {64, 32, 16} and lens.sum() == 4784
+    assert sorted(p.order) == list(range(1196)) and p.cu_full == [0, 4784]
+    assert max(p.pos_h) == 51 and max(p.pos_w) == 91

@@ -137,6 +137,60 @@ def run_reference(args, rank):
     print(json.dumps(line), flush=True)
 
 
+def vlm_request(cfg_id, cfg):
+    """Image-first multimodal prompt of configurations 2 / 3: the image's merged tokens (ids >= vocab select rows of
+    the injected embeddings), then text.  M-RoPE positions: image t = 0, h = merged row, w = merged column; text
+    continues from max(rows, columns) on all three axes."""
+    from oracle import qwen_vit, synth
+    vcfg = qwen_vit.CONFIGS[cfg_id]
+    t, h, w = qwen_vit.GRIDS[cfg_id]
+    hm, wm = h // vcfg.merge, w // vcfg.merge
+    n_img = t * hm * wm
+    n_text = synth.WORKLOADS[cfg_id][1] - n_img
+    ids = [cfg.vocab + k for k in range(n_img)] + synth.make_token_ids(n_text, seed=0)
+    start = max(hm, wm)
+    text_pos = [start + i for i in range(n_text)]
+    pos = [[0] * n_img + text_pos,
+           [r for r in range(hm) for _ in range(wm)] * t + text_pos,
+           [c for _ in range(hm) for c in range(wm)] * t + text_pos]
+    return {"vcfg": vcfg, "grids": [(t, h, w)], "ids": ids, "pos": pos, "n_img": n_img, "embed_id": cfg.vocab,
+            "last": start + n_text - 1}
+
+
+def vit_flops(vcfg, grids):
+    """Algorithmic flops of one encode: 2 m n k per GEMM, 4 D per (query, visible key, head)."""
+    from oracle import qwen_vit
+    plan = qwen_vit.make_plan(vcfg, grids)
+    n = plan.cu_full[-1]
+    H, I, M = vcfg.hidden, vcfg.intermediate, vcfg.hidden * vcfg.merge ** 2
+    win = sum((b - a) ** 2 for a, b in zip(plan.cu_window[:-1], plan.cu_window[1:]))
+    full = sum((b - a) ** 2 for a, b in zip(plan.cu_full[:-1], plan.cu_full[1:]))
+    per_layer = 2 * n * (3 * H * H + H * H + 3 * H * I)
+    att = 4 * H * (win * (vcfg.depth - len(vcfg.fullatt)) + full * len(vcfg.fullatt))
+    return 2 * n * vcfg.patch_dim * H + vcfg.depth * per_layer + att + 2 * (n // vcfg.merge ** 2) * (M * M + M * vcfg.out_hidden)
+
+
+def prefill_flops(cfg, s, prefix):
+    H, I = cfg.hidden, cfg.intermediate
+    qd, kvd = cfg.q_heads * cfg.head_dim, cfg.kv_heads * cfg.head_dim
+    lin = 2 * s * (H * (qd + 2 * kvd) + qd * H + 3 * H * I)
+    att = 4 * qd * sum(prefix + i + 1 for i in range(s))
+    return cfg.num_layers * (lin + att) + 2 * cfg.vocab * H
+
+
+def tensor_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        return float(json.load(open(path))["bf16_tflops"]), "measured"
+    return 1590.0, "fallback"
+
+
+def tensor_report(flops, ms):
+    peak, kind = tensor_peak()
+    tf = flops / (ms * 1e-3) / 1e12
+    return {"ms": ms, "tflop": flops / 1e12, "tflops": tf, "frac_of_bf16_peak": tf / peak, "peak": peak, "peak_kind": kind}
+
+
 # --------------------------------------------------------------------------------------------------
 def cpu_baseline(cfg_id, budget_s=25.0):
     import torch
@@ -194,8 +248,10 @@ def run_tp(args, rank, world, local_rank):
     cfg, prefix, ids, gen_tokens, temp, top_p = workload(args.config)
     if args.tokens:
         gen_tokens = args.tokens
+    from oracle import qwen_vit
+    vlm = vlm_request(args.config, cfg)
+    ids, pos = vlm["ids"], vlm["pos"]
     max_tokens = len(ids) + gen_tokens + 8
-    pos = position_ids(cfg, len(ids))
     t_setup = time.perf_counter()
     be = cabi.Backend(cfg, max_prefill_tokens=min(2048, max_tokens), max_response_tokens=gen_tokens + 8,
                       device_id=local_rank, tp_rank=rank, tp_size=world)
@@ -215,19 +271,29 @@ def run_tp(args, rank, world, local_rank):
     be.alloc_slot(0, max_tokens)
     be.set_sampling(temp, top_p, 0)
     be.capture_decode(0)
+    # vision encoder: replicated on every rank (its windows are not sharded), weights drawn on the device
+    n_patches = sum(t * h * w for t, h, w in vlm["grids"])
+    enc = cabi.VitEncoder(be, vlm["vcfg"], max_patches=n_patches)
+    enc.load_weights(qwen_vit.make_weights(vlm["vcfg"], seed=0, device="cuda"))
+    pixels = qwen_vit.make_pixels(vlm["vcfg"], vlm["grids"], seed=0)
+    pixels_host = pixels.pin_memory()
+    pixels_dev = pixels.cuda()
+    embeds = torch.zeros(vlm["n_img"], cfg.hidden, dtype=torch.bfloat16, device="cuda")
     be.synchronize()
     setup_s = time.perf_counter() - t_setup
-    mp = None if pos is None else [len(ids)] * 3
+    mp = [vlm["last"] + 1] * 3
 
-    def one_request():
+    def one_request(host_pixels=False):
         be.event_record(0)
-        be.prefill(0, ids, kv_offset=0, pos3=pos, sample=True)
+        enc.encode(pixels_host if host_pixels else pixels_dev, vlm["grids"], embeds)
+        be.event_record(3)
+        be.prefill(0, ids, kv_offset=0, embeds=embeds, embed_token_id=vlm["embed_id"], pos3=pos, sample=True)
         be.event_record(1)
         be.decode_begin(0, len(ids), mp, 1)
         be.decode_steps(gen_tokens - 1, True)
         be.event_record(2)
         toks = be.read_tokens(0, gen_tokens)              # host ids out (one D2H + sync)
-        return be.elapsed_ms(0, 1), be.elapsed_ms(1, 2), toks
+        return be.elapsed_ms(3, 1), be.elapsed_ms(1, 2), toks, be.elapsed_ms(0, 3)
 
     for _ in range(args.warmup):
         one_request()
@@ -237,19 +303,26 @@ def run_tp(args, rank, world, local_rank):
     dist.barrier()
     torch.cuda.synchronize()
     t0 = time.perf_counter()
-    pre_ms = dec_ms = 0.0
+    pre_ms = dec_ms = vit_ms = 0.0
     for _ in range(args.steps):
-        a, b, tokens = one_request()
+        a, b, tokens, v = one_request()
         pre_ms += a
         dec_ms += b
+        vit_ms += v
+    dist.barrier()
+    torch.cuda.synchronize()
+    launches = be.launch_count() - launches0
+    # end to end: host pixels and host ids in (H2D inside), host ids out
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        one_request(host_pixels=True)
     dist.barrier()
     torch.cuda.synchronize()
     wall_s = time.perf_counter() - t0
     clocks = sampler.stop()
-    launches = be.launch_count() - launches0
-    local = torch.tensor([dec_ms, pre_ms, wall_s], dtype=torch.float64, device="cuda")
+    local = torch.tensor([dec_ms, pre_ms, wall_s, vit_ms], dtype=torch.float64, device="cuda")
     dist.all_reduce(local, op=dist.ReduceOp.MAX)
-    dec_ms, pre_ms, wall_s = [float(x) for x in local.tolist()]
+    dec_ms, pre_ms, wall_s, vit_ms = [float(x) for x in local.tolist()]
     dec_steps = args.steps * (gen_tokens - 1)
     step_ms = dec_ms / dec_steps
     step_bytes = be.decode_step_bytes(len(ids) + gen_tokens // 2)          # this rank's share
@@ -259,21 +332,28 @@ def run_tp(args, rank, world, local_rank):
         line = {"metric": METRIC, "value": dec_steps / (dec_ms / 1e3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": (pre_ms + dec_ms) / args.steps, "higher_is_better": True,
                 "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-                "config": {"workload": f"{NAMES[args.config]}: {len(ids)}-token prompt, {gen_tokens} generated tokens, batch 1, "
-                                       f"temperature {temp}, top_p {top_p}",
+                "config": {"workload": f"{NAMES[args.config]}: 1288x728 image ({n_patches} patches -> {vlm['n_img']} tokens through the vision "
+                                       f"encoder) + {len(ids) - vlm['n_img']} text tokens = {len(ids)}-token prompt, {gen_tokens} generated "
+                                       f"tokens, batch 1, temperature {temp}, top_p {top_p}",
                            "parallelism": "single GPU" if world == 1 else f"tp{world} (heads + MLP columns + vocab rows; NCCL all-reduce in the decode graph)",
                            "l2_policy": "weights streamed per decode step exceed L2 (%.2f GB per GPU vs 126 MB)" % (step_bytes / 1e9),
                            "cuda_graph": True},
-                "decode_ms_per_token": step_ms, "prefill_ms": pre_ms / args.steps, "ttft_ms": pre_ms / args.steps,
+                "decode_ms_per_token": step_ms, "prefill_ms": pre_ms / args.steps, "vit_ms": vit_ms / args.steps,
+                "ttft_ms": (pre_ms + vit_ms) / args.steps,
+                "prefill": tensor_report(prefill_flops(synth.CONFIGS[args.config], len(ids), 0) / world, pre_ms / args.steps),
+                "vit": tensor_report(vit_flops(vlm["vcfg"], vlm["grids"]), vit_ms / args.steps),
                 "wall_s": wall_s, "setup_s": setup_s,
-                "e2e": {"value": args.steps * gen_tokens / wall_s, "unit": UNIT, "h2d_bytes_per_step": 4 * len(ids) * (4 if pos else 1),
-                        "d2h_bytes_per_step": 4 * gen_tokens + 32, "api": "efm_b200_prefill / decode_steps / read_tokens (C ABI, host buffers)"},
+                "e2e": {"value": args.steps * gen_tokens / wall_s, "unit": UNIT,
+                        "h2d_bytes_per_step": 16 * len(ids) + pixels.numel() * 2,
+                        "d2h_bytes_per_step": 4 * gen_tokens + 32,
+                        "api": "efm_b200_vit_encode / prefill / decode_steps / read_tokens (C ABI, host buffers)"},
                 "gpu_launches": launches, "clocks": clocks,
                 "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                              "traffic": None, "peak_kind": peak_kind, "launch": "one decode step on one rank",
                              "bytes_per_launch": step_bytes, "us_per_launch": step_ms * 1e3},
                 "tokens_head": tokens[:8]}
         print(json.dumps(line), flush=True)
+    enc.close()
     be.close()
     dist.barrier()
     dist.destroy_process_group()
@@ -294,9 +374,12 @@ def run_ours(args, rank, world, local_rank):
     cfg, prefix, ids, gen_tokens, temp, top_p = workload(args.config)
     if args.tokens:
         gen_tokens = args.tokens
+    vlm = vlm_request(args.config, cfg) if cfg.mrope_section is not None else None
+    if vlm is not None:
+        ids = vlm["ids"]
     prompt_n = len(ids) - len(prefix)
     max_tokens = len(ids) + gen_tokens + 8
-    pos = position_ids(cfg, len(ids))
+    pos = vlm["pos"] if vlm is not None else None
 
     t_setup = time.perf_counter()
     w = synth.make_weights(cfg, seed=0)
@@ -307,6 +390,15 @@ def run_ours(args, rank, world, local_rank):
     if prefix:
         be.prefill(0, prefix, kv_offset=0, pos3=None if pos is None else [r[:len(prefix)] for r in pos], sample=False)
     be.capture_decode(0)
+    enc = None
+    if vlm is not None:
+        from oracle import qwen_vit
+        n_patches = sum(t * h * w for t, h, w in vlm["grids"])
+        enc = cabi.VitEncoder(be, vlm["vcfg"], max_patches=n_patches)
+        enc.load_weights(qwen_vit.make_weights(vlm["vcfg"], seed=0, device="cuda"))
+        pixels = qwen_vit.make_pixels(vlm["vcfg"], vlm["grids"], seed=0)
+        pixels_host, pixels_dev = pixels.pin_memory(), pixels.cuda()
+        embeds = torch.zeros(vlm["n_img"], cfg.hidden, dtype=torch.bfloat16, device="cuda")
     be.synchronize()
 
     # public API engine for the end-to-end leg (weights travel through a safetensors checkpoint)
@@ -324,17 +416,23 @@ def run_ours(args, rank, world, local_rank):
 
     suffix = ids[len(prefix):]
     pos_suffix = None if pos is None else [r[len(prefix):] for r in pos]
-    mp = None if pos is None else [len(ids)] * 3
+    mp = None if vlm is None else [vlm["last"] + 1] * 3
 
     def one_request():
         be.event_record(0)
-        be.prefill(0, suffix, kv_offset=len(prefix), pos3=pos_suffix, sample=True)
+        if enc is not None:
+            enc.encode(pixels_dev, vlm["grids"], embeds)
+        be.event_record(3)
+        if enc is not None:
+            be.prefill(0, suffix, kv_offset=len(prefix), embeds=embeds, embed_token_id=vlm["embed_id"], pos3=pos_suffix, sample=True)
+        else:
+            be.prefill(0, suffix, kv_offset=len(prefix), pos3=pos_suffix, sample=True)
         be.event_record(1)
         be.decode_begin(0, len(ids), mp, 1)
         be.decode_steps(gen_tokens - 1, True)
         be.event_record(2)
         be.synchronize()
-        return be.elapsed_ms(0, 1), be.elapsed_ms(1, 2)
+        return be.elapsed_ms(3, 1), be.elapsed_ms(1, 2), be.elapsed_ms(0, 3)
 
     def barrier():
         if dist is not None:
@@ -348,11 +446,12 @@ def run_ours(args, rank, world, local_rank):
     launches0 = be.launch_count()
     barrier()
     t0 = time.perf_counter()
-    pre_ms, dec_ms = 0.0, 0.0
+    pre_ms, dec_ms, vit_ms = 0.0, 0.0, 0.0
     for _ in range(args.steps):
-        a, b = one_request()
+        a, b, v = one_request()
         pre_ms += a
         dec_ms += b
+        vit_ms += v
     barrier()
     wall_s = time.perf_counter() - t0
     launches = be.launch_count() - launches0
@@ -360,14 +459,16 @@ def run_ours(args, rank, world, local_rank):
 
     # end to end through the public API: host ids in, host ids out
     def e2e_request():
-        if pos is None:
+        if vlm is None:
             req = edge_fm.Request(0, ids)
-        else:
+        else:       # host pixels -> vision encoder (C ABI) -> embeddings stay on the device -> public generate()
+            enc.encode(pixels_host, vlm["grids"], embeds)
+            be.synchronize()
             pt = torch.tensor(pos, dtype=torch.int32)
-            dummy = torch.zeros(1, cfg.hidden, dtype=torch.bfloat16)
-            req = edge_fm.Request(0, ids, edge_fm.Tensor(dummy.data_ptr(), [1, cfg.hidden], edge_fm.DType.BFloat16, edge_fm.Device.CPU),
-                                  cfg.vocab + 100,
-                                  edge_fm.Tensor(pt.data_ptr(), [3, len(ids)], edge_fm.DType.Int32, edge_fm.Device.CPU), mp and [m - 1 for m in mp])
+            req = edge_fm.Request(0, ids, edge_fm.Tensor(embeds.data_ptr(), [vlm["n_img"], cfg.hidden], edge_fm.DType.BFloat16,
+                                                         edge_fm.Device.GPU, local_rank),
+                                  vlm["embed_id"],
+                                  edge_fm.Tensor(pt.data_ptr(), [3, len(ids)], edge_fm.DType.Int32, edge_fm.Device.CPU), [vlm["last"]] * 3)
         req.set_ignore_stop_tokens(True)
         return list(engine.generate(req).token_ids())
     for _ in range(max(1, args.warmup // 2)):
@@ -387,10 +488,10 @@ def run_ours(args, rank, world, local_rank):
     step_bytes = be.decode_step_bytes(len(ids) + gen_tokens // 2)
 
     dec_steps = args.steps * (gen_tokens - 1)
-    local = torch.tensor([dec_ms, pre_ms, wall_s, e2e_s], dtype=torch.float64, device="cuda")
+    local = torch.tensor([dec_ms, pre_ms, wall_s, e2e_s, vit_ms], dtype=torch.float64, device="cuda")
     if dist is not None:
         dist.all_reduce(local, op=dist.ReduceOp.MAX)
-    dec_ms_max, pre_ms_max, wall_max, e2e_max = [float(x) for x in local.tolist()]
+    dec_ms_max, pre_ms_max, wall_max, e2e_max, vit_ms_max = [float(x) for x in local.tolist()]
     value = world * dec_steps / (dec_ms_max / 1e3)
     e2e_value = world * args.steps * gen_tokens / e2e_max
     step_ms = dec_ms_max / dec_steps
@@ -419,20 +520,30 @@ def run_ours(args, rank, world, local_rank):
                        "l2_policy": "weights streamed per decode step exceed L2 (%.2f GB vs 126 MB)" % (step_bytes / 1e9),
                        "cuda_graph": True},
             "decode_ms_per_token": step_ms, "prefill_ms": pre_ms_max / args.steps,
-            "ttft_ms": pre_ms_max / args.steps, "wall_s": wall_max, "setup_s": setup_s,
-            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 4 * prompt_n + (12 * len(ids) if pos else 0),
+            "ttft_ms": (pre_ms_max + vit_ms_max) / args.steps, "wall_s": wall_max, "setup_s": setup_s,
+            "prefill": tensor_report(prefill_flops(cfg, prompt_n, len(prefix)), pre_ms_max / args.steps),
+            "e2e": {"value": e2e_value, "unit": UNIT,
+                    "h2d_bytes_per_step": 4 * prompt_n + (12 * len(ids) + pixels.numel() * 2 if vlm is not None else 0),
                     "d2h_bytes_per_step": 4 * gen_tokens + 32, "api": "edge_fm.EdgeFM.generate",
                     "engine_decode_tok_s": m.get("decode_tokens_per_second"), "engine_prefill_ms": m.get("prefill_ms")},
             "gpu_launches": launches,
             "clocks": clocks,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "peak_kind": peak_kind, "launch": "one decode step (CUDA graph of %d kernels)" % (5 * L + 2),
+                         "traffic": None, "peak_kind": peak_kind, "launch": "one decode step (CUDA graph of %d kernel nodes: 5 per layer + lm_head + sampler)" % (5 * L + 2),
                          "bytes_per_launch": step_bytes, "us_per_launch": step_ms * 1e3, "kernels": kernels},
             "tokens_head": tokens[:8], "e2e_tokens_equal": e2e_tokens == tokens,
         }
+        if vlm is not None:
+            line["vit_ms"] = vit_ms_max / args.steps
+            line["vit"] = tensor_report(vit_flops(vlm["vcfg"], vlm["grids"]), vit_ms_max / args.steps)
+            line["config"]["workload"] = (f"{NAMES[args.config]}: 448x448 image ({n_patches} patches -> {vlm['n_img']} tokens through the "
+                                          f"vision encoder) + {prompt_n - vlm['n_img']} text tokens, {gen_tokens} generated tokens, batch 1, "
+                                          f"temperature {temp}, top_p {top_p}")
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline(args.config)
         print(json.dumps(line), flush=True)
+    if enc is not None:
+        enc.close()
     be.close()
     del engine
     if dist is not None:

@@ -53,6 +53,7 @@ struct efm_b200_vit {
     __nv_bfloat16 *pixels = nullptr, *xn = nullptr, *qkv = nullptr, *attn = nullptr, *act = nullptr, *h1 = nullptr,
                   *mo = nullptr, *out_dev = nullptr;
     float *pe = nullptr, *resid = nullptr;
+    float2* rope_tab = nullptr;          // [N, D/2] (cos, sin)
     int32_t* plan = nullptr;             // order [N/unit] | pos_h | pos_w | lo_win | hi_win | lo_full | hi_full, [N] each
     std::vector<void*> allocations;
 };
@@ -192,6 +193,7 @@ efm_status efm_b200_vit_create(efm_b200_ctx* c, const efm_vit_desc* desc, efm_b2
     VTRY(valloc(v, &v->mo, NM * d.out_hidden));
     VTRY(valloc(v, &v->out_dev, NM * d.out_hidden));
     VTRY(valloc(v, &v->plan, NM + 6 * N));
+    VTRY(valloc(v, &v->rope_tab, N * (size_t)(D / 2)));
 #undef VTRY
     *out = v;
     return EFM_OK;
@@ -356,6 +358,8 @@ efm_status efm_b200_vit_encode(efm_b200_vit* v, const void* pixels, int32_t pixe
         L.launch(vit_gather_blocks_f32_kernel, dim3(std::min(NM, c->num_sms * 8)), dim3(256), 0, (const float*)v->pe, v->resid,
                  (const int32_t*)order, NM, v->unit, H);
     }
+    L.launch(vit_rope_table_kernel, dim3((N * (D / 2) + 127) / 128), dim3(128), 0, v->rope_tab, (const int32_t*)pos_h,
+             (const int32_t*)pos_w, N, D, d.rope_theta);
     for (int l = 0; l < d.depth; ++l) {
         const VitBlock& b = v->blocks[l];
         bool full = false;
@@ -365,7 +369,7 @@ efm_status efm_b200_vit_encode(efm_b200_vit* v, const void* pixels, int32_t pixe
             GemmParams g{v->xn, b.qkv_w, b.qkv_b, v->qkv, nullptr, N, 3 * H, H};
             launch_gemm_epi(L, GemmEpi::Bf16Bias, g, err);
         }
-        L.launch(vit_rope2d_kernel, dim3(N), dim3(256), 0, v->qkv, (const int32_t*)pos_h, (const int32_t*)pos_w, d.heads, D, d.rope_theta);
+        L.launch(vit_rope2d_kernel, dim3(N), dim3(256), 0, v->qkv, (const float2*)v->rope_tab, d.heads, D);
         {
             SegAttnParams a{};
             a.q = v->qkv; a.k = v->qkv + H; a.v = v->qkv + 2 * H; a.out = v->attn;

@@ -8,7 +8,8 @@
 //               a 128 x 64 A tile and a 128 x 64 B tile per stage into a 6-stage ring;
 //   warp 1      allocates 128 TMEM columns; one lane issues tcgen05.mma (M 128, N 128, K 16, four
 //               per stage) and tcgen05.commit, which releases the stage to the producer;
-//   warps 2-5   epilogue: tcgen05.ld the accumulator (row = TMEM lane, 32 columns at a time) and
+//   warps 2-5   epilogue: tcgen05.ld the accumulator (row = TMEM lane, 32 columns at a time), stage it in
+//               shared memory so that global rows are written as contiguous segments, and
 //               write bf16 (+bias, optionally erf-GELU) | fp32 residual add | fp32 | silu(gate)*up in bf16.
 // Rows past M and columns past N are zero-filled by TMA on load and masked on store.
 // Every mbarrier wait is bounded; a wait that gives up raises *error, the block frees its TMEM and
@@ -172,13 +173,18 @@ __global__ void __launch_bounds__(tc::kThreads) gemm_tc_kernel(const __grid_cons
             umma_commit(done_bar);                                   // accumulator complete
         }
     } else {
-        // epilogue warps 2..5: TMEM lane group = warp % 4
+        // epilogue warps 2..5: TMEM lane group = warp % 4.  Phase 1: each lane owns one accumulator row; bias and
+        // activation are applied and the row goes to a padded fp32 staging tile in shared memory (the operand ring
+        // is idle once the last MMA has completed).  Phase 2: the warp walks its 32 rows with the lanes across the
+        // columns, so that every global access is one contiguous row segment.
         const int q = warp & 3;
         const bool ok = mbar_wait(done_bar, 0u, abort_s);
         if (!ok) *abort_s = 1;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const int m = m0 + q * 32 + lane;
+        constexpr int LD = BN + 4;                                   // staging row stride in floats
+        float* stage = reinterpret_cast<float*>(base_ptr) + (size_t)q * 32 * LD;
         if (ok && *abort_s == 0) {
+            constexpr int OUT_COLS = EPI == GemmEpi::SwiGlu ? BN / 2 : BN;
             if constexpr (EPI == GemmEpi::SwiGlu) {
                 // fused gate|up weight: columns [n0, n0+64) are gate rows, [n0+64, n0+128) the up rows of the
                 // same 64 intermediate channels; out[m, n0/2 + j] = silu(gate_j) * up_j
@@ -187,82 +193,76 @@ __global__ void __launch_bounds__(tc::kThreads) gemm_tc_kernel(const __grid_cons
                     uint32_t rg[32], ru[32];
                     tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, rg);
                     tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(64 + c0), ru);
-                    const int n = n0 + c0;                          // gate column in the fused output
-                    if (m < p.M && n0 + 128 <= p.N) {
-                        const size_t off = (size_t)m * (p.N >> 1) + (n0 >> 1) + c0;
-                        uint32_t o[16];
+                    const int n = n0 + c0;
+                    const bool in = n0 + 128 <= p.N;
 #pragma unroll
-                        for (int j = 0; j < 32; j += 2) {
-                            float g0 = __uint_as_float(rg[j]), g1 = __uint_as_float(rg[j + 1]);
-                            float u0 = __uint_as_float(ru[j]), u1 = __uint_as_float(ru[j + 1]);
-                            if (p.bias != nullptr) {
-                                g0 += __bfloat162float(p.bias[n + j]);      g1 += __bfloat162float(p.bias[n + j + 1]);
-                                u0 += __bfloat162float(p.bias[n + 64 + j]); u1 += __bfloat162float(p.bias[n + 64 + j + 1]);
+                    for (int j = 0; j < 32; j += 4) {
+                        float o[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            float g = __uint_as_float(rg[j + e]), u = __uint_as_float(ru[j + e]);
+                            if (p.bias != nullptr && in) {
+                                g += __bfloat162float(p.bias[n + j + e]);
+                                u += __bfloat162float(p.bias[n + 64 + j + e]);
                             }
-                            o[j >> 1] = pack_bf16(g0 / (1.0f + __expf(-g0)) * u0, g1 / (1.0f + __expf(-g1)) * u1);
+                            o[e] = g / (1.0f + __expf(-g)) * u;
                         }
-#pragma unroll
-                        for (int j = 0; j < 16; j += 4)
-                            *reinterpret_cast<uint4*>(p.C + off + 2 * j) = make_uint4(o[j], o[j + 1], o[j + 2], o[j + 3]);
+                        *reinterpret_cast<float4*>(stage + lane * LD + c0 + j) = make_float4(o[0], o[1], o[2], o[3]);
                     }
                 }
             } else {
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                uint32_t r[32];
-                tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
-                const int n = n0 + c0;
-                if (m < p.M && n < p.N) {
-                    const size_t off = (size_t)m * p.N + n;
-                    const int nv = min(32, p.N - n);               // N is even
-                    float v[32];
+                for (int c0 = 0; c0 < BN; c0 += 32) {
+                    uint32_t r[32];
+                    tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
+                    const int n = n0 + c0;
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-                    if (p.bias != nullptr) {
+                    for (int j = 0; j < 32; j += 4) {
+                        float o[4];
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) if (j < nv) v[j] += __bfloat162float(p.bias[n + j]);
-                    }
-                    if constexpr (EPI == GemmEpi::Bf16Gelu) {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) v[j] = 0.5f * v[j] * (1.0f + erff(v[j] * 0.70710678118654752f));
-                    }
-                    const bool wide = nv == 32 && (p.N & 7) == 0;  // 16-byte aligned row segments
-                    if constexpr (EPI == GemmEpi::F32) {
-                        if (wide) {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 4)
-                                *reinterpret_cast<float4*>(p.Cf + off + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 2) if (j < nv) *reinterpret_cast<float2*>(p.Cf + off + j) = make_float2(v[j], v[j + 1]);
+                        for (int e = 0; e < 4; ++e) {
+                            o[e] = __uint_as_float(r[j + e]);
+                            if (p.bias != nullptr && n + j + e < p.N) o[e] += __bfloat162float(p.bias[n + j + e]);
+                            if constexpr (EPI == GemmEpi::Bf16Gelu) o[e] = 0.5f * o[e] * (1.0f + erff(o[e] * 0.70710678118654752f));
                         }
-                    } else if constexpr (EPI == GemmEpi::Bf16Bias || EPI == GemmEpi::Bf16Gelu) {
-                        if (wide) {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 8)
-                                *reinterpret_cast<uint4*>(p.C + off + j) = make_uint4(pack_bf16(v[j], v[j + 1]), pack_bf16(v[j + 2], v[j + 3]),
-                                                                                       pack_bf16(v[j + 4], v[j + 5]), pack_bf16(v[j + 6], v[j + 7]));
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 2) if (j < nv) *reinterpret_cast<uint32_t*>(p.C + off + j) = pack_bf16(v[j], v[j + 1]);
-                        }
-                    } else {      // residual stream in fp32: Cf += acc (+ bias)
-                        if (wide) {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 4) {
-                                const float4 o = *reinterpret_cast<const float4*>(p.Cf + off + j);
-                                *reinterpret_cast<float4*>(p.Cf + off + j) = make_float4(o.x + v[j], o.y + v[j + 1], o.z + v[j + 2], o.w + v[j + 3]);
-                            }
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 2) if (j < nv) {
-                                const float2 o = *reinterpret_cast<const float2*>(p.Cf + off + j);
-                                *reinterpret_cast<float2*>(p.Cf + off + j) = make_float2(o.x + v[j], o.y + v[j + 1]);
-                            }
-                        }
+                        *reinterpret_cast<float4*>(stage + lane * LD + c0 + j) = make_float4(o[0], o[1], o[2], o[3]);
                     }
                 }
             }
+            __syncwarp();
+            const int ldc = EPI == GemmEpi::SwiGlu ? (p.N >> 1) : p.N;         // output row length
+            const int nc0 = EPI == GemmEpi::SwiGlu ? (n0 >> 1) : n0;           // first output column of the tile
+            const bool vec = (ldc & 3) == 0;
+            constexpr int LANES_PER_ROW = OUT_COLS / 4;                        // 32 (one row per pass) or 16 (two rows)
+            constexpr int ROWS_PER_PASS = 32 / LANES_PER_ROW;
+            const int cl = (lane % LANES_PER_ROW) * 4;
+#pragma unroll 4
+            for (int r0 = 0; r0 < 32; r0 += ROWS_PER_PASS) {
+                const int r = r0 + lane / LANES_PER_ROW;
+                const int m = m0 + q * 32 + r;
+                const int n = nc0 + cl;
+                if (m >= p.M || n >= ldc) continue;
+                const float4 v = *reinterpret_cast<const float4*>(stage + r * LD + cl);
+                const size_t off = (size_t)m * ldc + n;
+                if (vec && n + 3 < ldc) {
+                    if constexpr (EPI == GemmEpi::F32) {
+                        *reinterpret_cast<float4*>(p.Cf + off) = v;
+                    } else if constexpr (EPI == GemmEpi::Residual) {
+                        const float4 o = *reinterpret_cast<const float4*>(p.Cf + off);
+                        *reinterpret_cast<float4*>(p.Cf + off) = make_float4(o.x + v.x, o.y + v.y, o.z + v.z, o.w + v.w);
+                    } else {
+                        *reinterpret_cast<uint2*>(p.C + off) = make_uint2(pack_bf16(v.x, v.y), pack_bf16(v.z, v.w));
+                    }
+                } else {
+                    const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        if (n + i >= ldc) break;
+                        if constexpr (EPI == GemmEpi::F32) p.Cf[off + i] = e[i];
+                        else if constexpr (EPI == GemmEpi::Residual) p.Cf[off + i] += e[i];
+                        else p.C[off + i] = __float2bfloat16_rn(e[i]);
+                    }
+                }
             }
         }
     }

@@ -31,28 +31,41 @@ __global__ void __launch_bounds__(128) vit_scatter_rows_bf16_kernel(const __nv_b
     }
 }
 
-// In-place rotary embedding of the q and k parts of qkv [N, 3 * heads * D] (q | k | v along the row).
-// The D/2 rotation angles of a patch are D/4 from its row index and D/4 from its column index, both
-// with inv_freq[i] = theta^(-2 i / (D/2)); element d pairs with d + D/2 (rotate-half).  fp32 math,
-// one rounding to bf16.  One block per patch; thread = (q|k, head, pair).
-__global__ void __launch_bounds__(256) vit_rope2d_kernel(__nv_bfloat16* __restrict__ qkv, const int32_t* __restrict__ pos_h,
-                                                        const int32_t* __restrict__ pos_w, int heads, int D, float theta) {
-    const int n = blockIdx.x;
+// cos/sin table of the 2-D rotary embedding, one row of D/2 (cos, sin) pairs per patch: the first D/4
+// angles come from the patch's row index, the next D/4 from its column index, both with
+// inv_freq[i] = theta^(-2 i / (D/2)).  Computed once per encode call.
+__global__ void __launch_bounds__(128) vit_rope_table_kernel(float2* __restrict__ table, const int32_t* __restrict__ pos_h,
+                                                            const int32_t* __restrict__ pos_w, int n_patches, int D, float theta) {
     const int half = D / 2, quarter = D / 4;
-    const float ph = (float)pos_h[n], pw = (float)pos_w[n];
+    const int i = blockIdx.x * 128 + threadIdx.x;
+    if (i >= n_patches * half) return;
+    const int n = i / half, pair = i - n * half;
+    const int f = pair < quarter ? pair : pair - quarter;
+    const float inv = 1.0f / powf(theta, (float)(2 * f) / (float)half);
+    const float ang = (float)(pair < quarter ? pos_h[n] : pos_w[n]) * inv;
+    float sn, cs;
+    sincosf(ang, &sn, &cs);
+    table[i] = make_float2(cs, sn);
+}
+
+// In-place rotary embedding of the q and k parts of qkv [N, 3 * heads * D] (q | k | v along the row):
+// element d pairs with d + D/2 (rotate-half); fp32 math, one rounding to bf16.  One block per patch;
+// each thread rotates two adjacent pairs of one head (32-bit accesses).
+__global__ void __launch_bounds__(256) vit_rope2d_kernel(__nv_bfloat16* __restrict__ qkv, const float2* __restrict__ table,
+                                                        int heads, int D) {
+    const int n = blockIdx.x;
+    const int half = D / 2, hp = half / 2;                   // hp: 2-pair groups per head
     __nv_bfloat16* row = qkv + (size_t)n * 3 * heads * D;
-    const int total = 2 * heads * half;
+    const float2* tab = table + (size_t)n * half;
+    const int total = 2 * heads * hp;
     for (int i = threadIdx.x; i < total; i += 256) {
-        const int pair = i % half, hh = i / half;            // hh in [0, 2*heads): q heads then k heads
-        const int f = pair < quarter ? pair : pair - quarter;
-        const float inv = 1.0f / powf(theta, (float)(2 * f) / (float)half);
-        const float ang = (pair < quarter ? ph : pw) * inv;
-        float sn, cs;
-        sincosf(ang, &sn, &cs);
-        __nv_bfloat16* x = row + (size_t)hh * D;
-        const float a = __bfloat162float(x[pair]), b = __bfloat162float(x[pair + half]);
-        x[pair] = __float2bfloat16_rn(a * cs - b * sn);
-        x[pair + half] = __float2bfloat16_rn(b * cs + a * sn);
+        const int hh = i / hp, pair = (i - hh * hp) * 2;     // hh in [0, 2*heads): q heads then k heads
+        __nv_bfloat162* lo = reinterpret_cast<__nv_bfloat162*>(row + (size_t)hh * D + pair);
+        __nv_bfloat162* hi = reinterpret_cast<__nv_bfloat162*>(row + (size_t)hh * D + pair + half);
+        const float2 a = __bfloat1622float2(*lo), b = __bfloat1622float2(*hi);
+        const float2 t0 = tab[pair], t1 = tab[pair + 1];
+        *lo = __floats2bfloat162_rn(a.x * t0.x - b.x * t0.y, a.y * t1.x - b.y * t1.y);
+        *hi = __floats2bfloat162_rn(b.x * t0.x + a.x * t0.y, b.y * t1.x + a.y * t1.y);
     }
 }
 

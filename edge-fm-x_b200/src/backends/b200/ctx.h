@@ -33,7 +33,7 @@ struct KvSlot {
     std::vector<__nv_bfloat16*> v;
     cudaGraphExec_t graph = nullptr;      // decode step captured against this slot's pointers
     int graph_nodes = 0;
-    int n_splits = 1, chunk_cap = 1;
+    int n_splits = 1, chunk_cap = 1, attn_cluster = 0;
     void* mega_layers = nullptr;          // device array of per-layer pointers for the persistent decode kernel
 };
 

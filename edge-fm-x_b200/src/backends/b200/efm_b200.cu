@@ -398,6 +398,7 @@ efm_status efm_b200_alloc_kv_slot(efm_b200_ctx* c, int32_t slot, int32_t max_tok
     const AttnPlan plan = plan_decode_attention(max_tokens, c->d.kv_heads, c->num_sms);
     s.n_splits = plan.n_splits;
     s.chunk_cap = plan.chunk_cap;
+    s.attn_cluster = plan.cluster;
     {
         std::vector<MegaLayer> ml(c->d.num_layers);
         for (int l = 0; l < c->d.num_layers; ++l) {
@@ -743,7 +744,7 @@ efm_status efm_b200_op_decode_attention(const void* q, const void* k_cache, cons
         a.q = (const __nv_bfloat16*)q; a.k_cache = (const __nv_bfloat16*)k_cache; a.v_cache = (const __nv_bfloat16*)v_cache;
         a.out = (__nv_bfloat16*)out_bf16; a.state = nullptr; a.kv_len_static = kv_len;
         a.q_heads = q_heads; a.kv_heads = kv_heads; a.group = q_heads / kv_heads;
-        a.n_splits = plan.n_splits; a.chunk_cap = plan.chunk_cap; a.max_tokens = max_tokens;
+        a.n_splits = plan.n_splits; a.chunk_cap = plan.chunk_cap; a.max_tokens = max_tokens; a.cluster = plan.cluster;
         a.scale = 1.0f / sqrtf((float)head_dim);
         a.part_o = part_o; a.part_ml = part_ml; a.counters = counters;
         Launcher L; L.pdl = false;
@@ -805,7 +806,7 @@ efm_status efm_b200_op_decode_attention_noalloc(const void* q, const void* k_cac
     a.q = (const __nv_bfloat16*)q; a.k_cache = (const __nv_bfloat16*)k_cache; a.v_cache = (const __nv_bfloat16*)v_cache;
     a.out = (__nv_bfloat16*)out_bf16; a.state = nullptr; a.kv_len_static = kv_len;
     a.q_heads = q_heads; a.kv_heads = kv_heads; a.group = q_heads / kv_heads;
-    a.n_splits = plan.n_splits; a.chunk_cap = plan.chunk_cap; a.max_tokens = max_tokens;
+    a.n_splits = plan.n_splits; a.chunk_cap = plan.chunk_cap; a.max_tokens = max_tokens; a.cluster = plan.cluster;
     a.scale = 1.0f / sqrtf((float)head_dim);
     a.part_o = scratch; a.part_ml = scratch + kNoAllocPartO; a.counters = tickets;
     Launcher L; L.pdl = false;

@@ -19,6 +19,7 @@ struct Launcher {
     cudaStream_t stream = nullptr;
     bool pdl = true;                 // programmatic stream serialization between consecutive kernels
     bool cooperative = false;        // next launch only: all blocks co-resident (they wait on each other)
+    int cluster_x = 0;               // next launch only: thread-block cluster of this many blocks along x
     int64_t* counter = nullptr;
     cudaError_t err = cudaSuccess;   // first failure sticks
     std::vector<cudaEvent_t>* trace = nullptr;   // when set: one event recorded after every launch
@@ -32,17 +33,25 @@ struct Launcher {
         cfg.blockDim = block;
         cfg.dynamicSmemBytes = smem;
         cfg.stream = stream;
-        cudaLaunchAttribute attr[1];
+        cudaLaunchAttribute attr[2];
+        int na = 0;
         if (cooperative) {
-            attr[0].id = cudaLaunchAttributeCooperative;
-            attr[0].val.cooperative = 1;
-        } else {
-            attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-            attr[0].val.programmaticStreamSerializationAllowed = 1;
+            attr[na].id = cudaLaunchAttributeCooperative;
+            attr[na++].val.cooperative = 1;
+        } else if (pdl) {
+            attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[na++].val.programmaticStreamSerializationAllowed = 1;
         }
-        cfg.attrs = (pdl || cooperative) ? attr : nullptr;
-        cfg.numAttrs = (pdl || cooperative) ? 1 : 0;
+        if (cluster_x > 1) {
+            attr[na].id = cudaLaunchAttributeClusterDimension;
+            attr[na].val.clusterDim.x = (unsigned)cluster_x;
+            attr[na].val.clusterDim.y = 1;
+            attr[na++].val.clusterDim.z = 1;
+        }
+        cfg.attrs = na > 0 ? attr : nullptr;
+        cfg.numAttrs = na;
         cooperative = false;
+        cluster_x = 0;
         err = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
         if (counter != nullptr) ++*counter;
         if (trace != nullptr && err == cudaSuccess) {
@@ -91,26 +100,79 @@ inline cudaError_t configure_decode_mega(int max_smem_optin) {
     return cudaFuncSetAttribute(decode_mega_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem_optin);
 }
 
-struct AttnPlan { int n_splits, chunk_cap; };
-inline AttnPlan plan_decode_attention(int max_tokens, int kv_heads, int num_sms) {
-    int n = (max_tokens + kAttnTile - 1) / kAttnTile;
-    n = std::min(n, std::max(1, num_sms / std::max(1, kv_heads)));
-    n = std::max(1, std::min(n, kMaxSplits));
-    return AttnPlan{n, (max_tokens + n - 1) / n};
+struct AttnPlan { int n_splits, chunk_cap, cluster; };
+
+// Largest cluster the decode attention kernel can run with on this device (16, 8 or 0 = cluster form
+// unavailable / switched off with EFM_B200_ATTN_CLUSTER=0); set by configure_decode_attention().
+inline int& decode_attention_max_cluster() {
+    static int v = 0;
+    return v;
 }
 
-// Opt-in shared-memory sizes; called once per device at set-up, never inside a stream capture.
-inline cudaError_t configure_decode_attention() {
-    cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)decode_attention_smem_bytes(128, 0));
+inline AttnPlan plan_decode_attention(int max_tokens, int kv_heads, int num_sms) {
+    int n = (max_tokens + kAttnTile - 1) / kAttnTile;
+    const int maxc = decode_attention_max_cluster();
+    if (maxc > 1 && n <= 2 * maxc) {          // at most two tiles per block: one cluster per kv head
+        int cs = 1;
+        while (cs < n && cs < maxc) cs <<= 1;
+        return AttnPlan{cs, (max_tokens + cs - 1) / cs, cs};
+    }
+    n = std::min(n, std::max(1, num_sms / std::max(1, kv_heads)));
+    n = std::max(1, std::min(n, kMaxSplits));
+    return AttnPlan{n, (max_tokens + n - 1) / n, 0};
+}
+
+template <int D>
+inline cudaError_t configure_decode_attention_d(int& max_cluster) {
+    const int smem = (int)decode_attention_smem_bytes(D, 0);
+    cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
-    return cudaFuncSetAttribute(decode_attention_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                (int)decode_attention_smem_bytes(64, 0));
+    e = cudaFuncSetAttribute(decode_attention_cluster_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    const bool wide = cudaFuncSetAttribute(decode_attention_cluster_kernel<D>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
+    for (int cs = wide ? 16 : 8; cs >= 2; cs >>= 1) {       // the widest cluster the device can place
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(cs, 1, 1);
+        cfg.blockDim = dim3(kAttnThreads);
+        cfg.dynamicSmemBytes = smem;
+        cudaLaunchAttribute at;
+        at.id = cudaLaunchAttributeClusterDimension;
+        at.val.clusterDim.x = (unsigned)cs;
+        at.val.clusterDim.y = at.val.clusterDim.z = 1;
+        cfg.attrs = &at;
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, decode_attention_cluster_kernel<D>, &cfg) == cudaSuccess && n >= 1) {
+            max_cluster = std::min(max_cluster, cs);
+            return cudaSuccess;
+        }
+    }
+    (void)cudaGetLastError();
+    max_cluster = 0;
+    return cudaSuccess;
+}
+
+// Opt-in shared-memory sizes and the cluster width; called once per device at set-up, never inside a
+// stream capture.
+inline cudaError_t configure_decode_attention() {
+    int maxc = 16;
+    cudaError_t e = configure_decode_attention_d<128>(maxc);
+    if (e == cudaSuccess) e = configure_decode_attention_d<64>(maxc);
+    const char* env = std::getenv("EFM_B200_ATTN_CLUSTER");
+    if (env != nullptr && env[0] == '0') maxc = 0;
+    decode_attention_max_cluster() = maxc;
+    return e;
 }
 
 inline void launch_decode_attention(Launcher& L, const DecodeAttnParams& p, int head_dim) {
     const size_t smem = decode_attention_smem_bytes(head_dim, p.chunk_cap);
     const dim3 grid(p.n_splits, p.kv_heads), block(kAttnThreads);
+    if (p.cluster > 1) {
+        L.cluster_x = p.cluster;
+        if (head_dim == 128) L.launch(decode_attention_cluster_kernel<128>, grid, block, smem, p);
+        else L.launch(decode_attention_cluster_kernel<64>, grid, block, smem, p);
+        return;
+    }
     if (head_dim == 128) L.launch(decode_attention_kernel<128>, grid, block, smem, p);
     else L.launch(decode_attention_kernel<64>, grid, block, smem, p);
 }

@@ -11,6 +11,8 @@
 //   3. o += P.V from shared memory, 4 channels per thread, folded over the row groups;
 //   4. (m, l, o) go to scratch; the last block to finish for a kv head (atomic ticket, nobody
 //      spins) computes the merge weights once and folds all chunks with independent loads.
+//   4c. cluster form (short contexts, at most 16 chunks): the chunks of a kv head are the blocks of one
+//      thread-block cluster and exchange (m, l, o) through distributed shared memory instead.
 // The kernel is latency-bound (about 1 MB of KV per layer): 16 warps per block keep the
 // dependent-issue latency covered and the instruction count per warp small.
 // Bound: HBM (2 * kv_len * kv_heads * D * 2 bytes per layer); in practice latency.
@@ -37,6 +39,7 @@ struct DecodeAttnParams {
     float* part_o;                 // [q_heads][n_splits][D]
     float* part_ml;                // [q_heads][n_splits][2]
     unsigned int* counters;        // [kv_heads], zero between launches
+    int cluster;                   // > 1: the n_splits blocks of a kv head form one thread-block cluster (n_splits == cluster)
 };
 
 template <int D>
@@ -50,12 +53,13 @@ struct DecodeAttnSmem {
     float run_m[kMaxGroup], run_l[kMaxGroup], new_m[kMaxGroup];
     float mw[kMaxGroup][kMaxSplits];                        // merge weights
     __nv_bfloat16 v[kAttnTile][D];
+    float fin[kMaxGroup][D];                                // cluster form: this block's un-normalised output
     unsigned int ticket;
 };
 
 // One (chunk, kv head) work item, executed by all 512 threads of the block.  Every load of data
 // another block may have written in this step (q, the newest cache row, the partials) bypasses L1.
-template <int D>
+template <int D, bool CLUSTER = false>
 __device__ __forceinline__ void decode_attention_body(const DecodeAttnParams& p, const int split, const int kvh,
                                                       unsigned char* attn_smem) {
     constexpr int NT = kAttnThreads, NW = kAttnWarps;
@@ -96,18 +100,22 @@ __device__ __forceinline__ void decode_attention_body(const DecodeAttnParams& p,
     }
     if (tid < kMaxGroup) { sm.run_m[tid] = -INFINITY; sm.run_l[tid] = 0.f; }
 
-    for (int t0 = 0; t0 < n; t0 += kAttnTile) {
-        const int nt = min(kAttnTile, n - t0);
-        const bool valid = tok < nt;
-        // ---- 1. K and V slices in flight together ---------------------------------------------
-        uint4 kq[QV], vq[QV];
-        if (valid) {
+    // ---- 1. K and V slices in flight together; the next tile's are issued as soon as this tile's
+    //         registers are free, so that they fly during the softmax and P.V of the current tile
+    uint4 kq[QV], vq[QV];
+    auto issue_tile = [&](int t0) {
+        if (t0 < n && tok < min(kAttnTile, n - t0)) {
             const size_t off = (size_t)(start + t0 + tok) * row_stride + (size_t)kvh * D + part * DP;
 #pragma unroll
             for (int j = 0; j < QV; ++j) kq[j] = ld_cg(p.k_cache + off + j * 8);
 #pragma unroll
             for (int j = 0; j < QV; ++j) vq[j] = ld_cg(p.v_cache + off + j * 8);
         }
+    };
+    issue_tile(0);
+    for (int t0 = 0; t0 < n; t0 += kAttnTile) {
+        const int nt = min(kAttnTile, n - t0);
+        const bool valid = tok < nt;
         __syncthreads();      // q staged (first tile) / previous tile's p and v fully consumed
         // ---- 2. scores ------------------------------------------------------------------------
         float s[kMaxGroup];
@@ -134,6 +142,7 @@ __device__ __forceinline__ void decode_attention_body(const DecodeAttnParams& p,
             for (int j = 0; j < QV; ++j)
                 *reinterpret_cast<uint4*>(&sm.v[tok][part * DP + j * 8]) = vq[j];
         }
+        issue_tile(t0 + kAttnTile);
 #pragma unroll
         for (int g = 0; g < kMaxGroup; ++g) {
             s[g] += __shfl_xor_sync(0xffffffffu, s[g], 1);
@@ -215,6 +224,53 @@ __device__ __forceinline__ void decode_attention_body(const DecodeAttnParams& p,
     }
     __syncthreads();
 
+    if constexpr (CLUSTER) {
+        // ---- 4c. the blocks of the cluster exchange (m, l, o) through distributed shared memory: no
+        //          scratch in global memory, no ticket, one remote round trip
+        for (int i = tid; i < G * D; i += NT) {
+            const int g = i / D, d = i - g * D;
+            float o = 0.f;
+#pragma unroll
+            for (int w = 0; w < NW; ++w) o += sm.ored[w][g][d];
+            sm.fin[g][d] = o;
+        }
+        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+        const int CS = p.cluster;
+        const uint32_t a_fin = (uint32_t)__cvta_generic_to_shared(&sm.fin[0][0]);
+        const uint32_t a_m = (uint32_t)__cvta_generic_to_shared(&sm.run_m[0]);
+        const uint32_t a_l = (uint32_t)__cvta_generic_to_shared(&sm.run_l[0]);
+        for (int i = split + CS * tid; i < G * D; i += CS * NT) {      // this block's share of the outputs
+            const int g = i / D;
+            float mr[16], lr[16], orr[16];
+#pragma unroll
+            for (int r = 0; r < 16; ++r) {
+                mr[r] = -INFINITY; lr[r] = 0.f; orr[r] = 0.f;
+                if (r < CS) {
+                    uint32_t ra;
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(a_m + 4u * g), "r"(r));
+                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(mr[r]) : "r"(ra) : "memory");
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(a_l + 4u * g), "r"(r));
+                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(lr[r]) : "r"(ra) : "memory");
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(a_fin + 4u * i), "r"(r));
+                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(orr[r]) : "r"(ra) : "memory");
+                }
+            }
+            float M = -INFINITY;
+#pragma unroll
+            for (int r = 0; r < 16; ++r) M = fmaxf(M, mr[r]);
+            float Lsum = 0.f, o = 0.f;
+#pragma unroll
+            for (int r = 0; r < 16; ++r) {
+                const float w = lr[r] > 0.f ? expf(mr[r] - M) : 0.f;
+                Lsum = fmaf(lr[r], w, Lsum);
+                o = fmaf(orr[r], w, o);
+            }
+            p.out[(size_t)(kvh * G) * D + i] = __float2bfloat16_rn(Lsum > 0.f ? o / Lsum : 0.f);
+        }
+        // nobody leaves while a neighbour may still read its shared memory
+        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+        return;
+    }
     // ---- 4. publish the partial, merge if last -------------------------------------------------
     for (int i = tid; i < G * D; i += NT) {
         const int g = i / D, d = i - g * D;
@@ -289,6 +345,15 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(const De
     pdl_launch_dependents();
     pdl_wait();
     decode_attention_body<D>(p, blockIdx.x, blockIdx.y, attn_smem_raw);
+}
+
+// Cluster form: grid (cluster, kv_heads) with cluster dimension (cluster, 1, 1).
+template <int D>
+__global__ void __launch_bounds__(kAttnThreads) decode_attention_cluster_kernel(const DecodeAttnParams p) {
+    extern __shared__ __align__(16) unsigned char attn_smem_raw[];
+    pdl_launch_dependents();
+    pdl_wait();
+    decode_attention_body<D, true>(p, blockIdx.x, blockIdx.y, attn_smem_raw);
 }
 
 inline size_t decode_attention_smem_bytes(int D, int /*chunk_cap*/) {

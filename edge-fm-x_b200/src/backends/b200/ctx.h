@@ -92,6 +92,8 @@ struct efm_b200_ctx {
     float* attn_part_o = nullptr;         // decode attention scratch
     float* attn_part_ml = nullptr;
     unsigned int* attn_counters = nullptr;
+    float* gemm_ws = nullptr;             // split-K workspace of the prefill / vision GEMMs (fp32 partial tiles)
+    size_t gemm_ws_floats = 0;
     efm::DecodeState* state = nullptr;
     int32_t* tokens_out = nullptr;        // [max_response_tokens]
 

@@ -74,6 +74,9 @@ Launcher make_launcher(efm_b200_ctx* c) {
     L.stream = c->stream;
     L.pdl = c->pdl;
     L.counter = &c->launches;
+    L.gemm_ws = c->gemm_ws;
+    L.gemm_ws_floats = c->gemm_ws_floats;
+    L.num_sms = c->num_sms;
     return L;
 }
 
@@ -223,6 +226,8 @@ efm_status efm_b200_create(const efm_model_desc* desc, int32_t device_id, int32_
         if (need > (size_t)optin) c->mega = false;       // does not fit: phase-per-launch form
         else EFM_TRY(configure_decode_mega((int)need));
     }
+    c->gemm_ws_floats = (size_t)c->num_sms * 128 * 128;      // splits x tiles never exceeds the SM count
+    EFM_TRY(dev_alloc(c, &c->gemm_ws, c->gemm_ws_floats, false));
     EFM_TRY(dev_alloc(c, &c->state, 1));
     EFM_TRY(dev_alloc(c, &c->tokens_out, (size_t)d.max_response_tokens));
     EFM_TRY(cudaStreamSynchronize(c->stream));
@@ -721,8 +726,18 @@ efm_status efm_b200_op_gemm(const void* x, const void* w, const void* bias, void
         return fail(nullptr, EFM_ERR_INVALID_ARGUMENT, "op_gemm: bad arguments (n even, k % 32 == 0)");
     GemmParams g{(const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)bias, (__nv_bfloat16*)y_bf16, nullptr, m, n, k};
     Launcher L; L.pdl = false;
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
+    L.num_sms = sms;
+    L.gemm_ws_floats = (size_t)sms * 128 * 128;          // lets skinny products take the split-K path, as inside a context
+    if (cudaMalloc(&L.gemm_ws, L.gemm_ws_floats * sizeof(float)) != cudaSuccess) {
+        (void)cudaGetLastError();
+        L.gemm_ws = nullptr;
+    }
     launch_gemm_bf16(L, g);
-    return op_finish(L);
+    const efm_status out = op_finish(L);
+    if (L.gemm_ws != nullptr) cudaFree(L.gemm_ws);
+    return out;
 }
 
 efm_status efm_b200_op_decode_attention(const void* q, const void* k_cache, const void* v_cache, void* out_bf16,

@@ -348,6 +348,9 @@ efm_status efm_b200_vit_encode(efm_b200_vit* v, const void* pixels, int32_t pixe
     L.stream = st;
     L.pdl = false;
     L.counter = &c->launches;
+    L.gemm_ws = c->gemm_ws;
+    L.gemm_ws_floats = c->gemm_ws_floats;
+    L.num_sms = c->num_sms;
     int* err = &c->state->error;
     const int H = d.hidden, D = v->head_dim, Ip = v->ipad;
     auto norm_rows = [&](const __nv_bfloat16* w) { launch_rmsnorm_rows(L, v->resid, w, v->xn, N, H, d.rms_eps); };

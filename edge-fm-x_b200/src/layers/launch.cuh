@@ -20,6 +20,9 @@ struct Launcher {
     bool pdl = true;                 // programmatic stream serialization between consecutive kernels
     bool cooperative = false;        // next launch only: all blocks co-resident (they wait on each other)
     int cluster_x = 0;               // next launch only: thread-block cluster of this many blocks along x
+    float* gemm_ws = nullptr;        // split-K workspace of the owning context (nullptr: GEMMs never split)
+    size_t gemm_ws_floats = 0;
+    int num_sms = 148;
     int64_t* counter = nullptr;
     cudaError_t err = cudaSuccess;   // first failure sticks
     std::vector<cudaEvent_t>* trace = nullptr;   // when set: one event recorded after every launch

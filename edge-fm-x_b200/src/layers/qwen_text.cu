@@ -328,9 +328,35 @@ static void launch_gemm(Launcher& L, const GemmParams& p, int* error_word = null
         if (L.err == cudaSuccess) L.err = cudaErrorInvalidValue;
         return;
     }
-    const dim3 grid((p.N + tc::BN - 1) / tc::BN, (p.M + tc::BM - 1) / tc::BM), block(tc::kThreads);
+    dim3 grid((p.N + tc::BN - 1) / tc::BN, (p.M + tc::BM - 1) / tc::BM), block(tc::kThreads);
     const bool pdl = L.pdl;
     L.pdl = false;     // prefill kernels do not use the dependent-launch protocol
+    // Few output tiles and a long K: split K over grid.z so that the whole GPU works, fp32 partials to the
+    // workspace, then a fixed-order sum with the epilogue.
+    if constexpr (EPI == GemmEpi::Bf16Bias || EPI == GemmEpi::Residual || EPI == GemmEpi::F32) {
+        const int tiles = (int)(grid.x * grid.y), KB = (p.K + tc::BK - 1) / tc::BK;
+        int splits = std::min(L.num_sms / std::max(1, tiles), KB / 4);
+        if (L.gemm_ws != nullptr && splits >= 2 && (p.N & 3) == 0 && (size_t)splits * p.M * p.N <= L.gemm_ws_floats) {
+            const int per = (KB + splits - 1) / splits;
+            splits = (KB + per - 1) / per;                 // no empty split
+            GemmParams q = p;
+            q.kb_per_split = per;
+            q.Cf = L.gemm_ws;
+            q.bias = nullptr;
+            grid.z = (unsigned)splits;
+            static bool attr_f32 = false;
+            if (!attr_f32) {
+                cudaFuncSetAttribute(gemm_tc_kernel<GemmEpi::F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc::SMEM_BYTES);
+                attr_f32 = true;
+            }
+            L.launch(gemm_tc_kernel<GemmEpi::F32>, grid, block, tc::SMEM_BYTES, ma, mb, q, error_word);
+            const size_t total4 = (size_t)p.M * p.N / 4;
+            const int fin = (int)std::min<size_t>((total4 + 255) / 256, (size_t)L.num_sms * 4);
+            L.launch(gemm_splitk_finish_kernel<EPI>, dim3(fin), dim3(256), 0, (const float*)L.gemm_ws, splits, p);
+            L.pdl = pdl;
+            return;
+        }
+    }
     L.launch(gemm_tc_kernel<EPI>, grid, block, tc::SMEM_BYTES, ma, mb, p, error_word);
     L.pdl = pdl;
 }

@@ -31,6 +31,8 @@ struct GemmParams {
     float* Cf;                // F32: out; Residual: in/out (fp32 residual stream)
     int M, N, K;
     int lda = 0;              // row stride of A in elements (0: K)
+    int kb_per_split = 0;     // split-K: block z covers 64-wide k-blocks [z * kb_per_split, (z+1) * kb_per_split) and
+                              // writes its raw fp32 partial tile to Cf + z * M * N (F32 epilogue, no bias); 0: no split
 };
 
 namespace tc {
@@ -129,7 +131,9 @@ __global__ void __launch_bounds__(tc::kThreads) gemm_tc_kernel(const __grid_cons
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
-    const int KB = (p.K + BK - 1) / BK;
+    const int KB_all = (p.K + BK - 1) / BK;
+    const int kb0 = p.kb_per_split > 0 ? (int)blockIdx.z * p.kb_per_split : 0;
+    const int KB = p.kb_per_split > 0 ? min(KB_all, kb0 + p.kb_per_split) : KB_all;     // this block walks [kb0, KB)
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
@@ -148,9 +152,9 @@ __global__ void __launch_bounds__(tc::kThreads) gemm_tc_kernel(const __grid_cons
 
     if (warp == 0) {
         if (lane == 0) {
-            for (int kb = 0; kb < KB; ++kb) {
-                const int s = kb % STAGES;
-                const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
+            for (int kb = kb0; kb < KB; ++kb) {
+                const int s = (kb - kb0) % STAGES;
+                const uint32_t ph = (uint32_t)((kb - kb0) / STAGES) & 1u;
                 if (!mbar_wait(empty0 + 8 * s, ph ^ 1u, abort_s)) { *abort_s = 1; break; }
                 mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
                 tma_load_2d(base + s * STAGE_BYTES, &map_a, kb * BK, m0, full0 + 8 * s);
@@ -159,15 +163,15 @@ __global__ void __launch_bounds__(tc::kThreads) gemm_tc_kernel(const __grid_cons
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            for (int kb = 0; kb < KB; ++kb) {
-                const int s = kb % STAGES;
-                const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
+            for (int kb = kb0; kb < KB; ++kb) {
+                const int s = (kb - kb0) % STAGES;
+                const uint32_t ph = (uint32_t)((kb - kb0) / STAGES) & 1u;
                 if (!mbar_wait(full0 + 8 * s, ph, abort_s)) { *abort_s = 1; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint64_t da = umma_desc(base + s * STAGE_BYTES), db = umma_desc(base + s * STAGE_BYTES + A_BYTES);
 #pragma unroll
                 for (int k = 0; k < BK / UMMA_K; ++k)               // 32 bytes further along K inside the swizzle atom
-                    umma(tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), (kb | k) != 0 ? 1u : 0u);
+                    umma(tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), ((kb - kb0) | k) != 0 ? 1u : 0u);
                 umma_commit(empty0 + 8 * s);                         // stage free once these MMAs have read it
             }
             umma_commit(done_bar);                                   // accumulator complete
@@ -233,6 +237,7 @@ __global__ void __launch_bounds__(tc::kThreads) gemm_tc_kernel(const __grid_cons
             const int ldc = EPI == GemmEpi::SwiGlu ? (p.N >> 1) : p.N;         // output row length
             const int nc0 = EPI == GemmEpi::SwiGlu ? (n0 >> 1) : n0;           // first output column of the tile
             const bool vec = (ldc & 3) == 0;
+            const size_t split_off = p.kb_per_split > 0 ? (size_t)blockIdx.z * (size_t)p.M * (size_t)p.N : 0;
             constexpr int LANES_PER_ROW = OUT_COLS / 4;                        // 32 (one row per pass) or 16 (two rows)
             constexpr int ROWS_PER_PASS = 32 / LANES_PER_ROW;
             const int cl = (lane % LANES_PER_ROW) * 4;
@@ -246,7 +251,7 @@ __global__ void __launch_bounds__(tc::kThreads) gemm_tc_kernel(const __grid_cons
                 const size_t off = (size_t)m * ldc + n;
                 if (vec && n + 3 < ldc) {
                     if constexpr (EPI == GemmEpi::F32) {
-                        *reinterpret_cast<float4*>(p.Cf + off) = v;
+                        *reinterpret_cast<float4*>(p.Cf + split_off + off) = v;
                     } else if constexpr (EPI == GemmEpi::Residual) {
                         const float4 o = *reinterpret_cast<const float4*>(p.Cf + off);
                         *reinterpret_cast<float4*>(p.Cf + off) = make_float4(o.x + v.x, o.y + v.y, o.z + v.z, o.w + v.w);
@@ -258,7 +263,7 @@ __global__ void __launch_bounds__(tc::kThreads) gemm_tc_kernel(const __grid_cons
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         if (n + i >= ldc) break;
-                        if constexpr (EPI == GemmEpi::F32) p.Cf[off + i] = e[i];
+                        if constexpr (EPI == GemmEpi::F32) p.Cf[split_off + off + i] = e[i];
                         else if constexpr (EPI == GemmEpi::Residual) p.Cf[off + i] += e[i];
                         else p.C[off + i] = __float2bfloat16_rn(e[i]);
                     }
@@ -272,6 +277,34 @@ __global__ void __launch_bounds__(tc::kThreads) gemm_tc_kernel(const __grid_cons
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// Second half of a split-K product: out = epilogue(sum over splits, in split order, of the fp32
+// partial tiles) -- the order is fixed, so the result does not depend on which block finished first.
+template <GemmEpi EPI>
+__global__ void __launch_bounds__(256) gemm_splitk_finish_kernel(const float* __restrict__ ws, int splits, const GemmParams p) {
+    const size_t total4 = (size_t)p.M * p.N / 4;           // N % 4 == 0 (checked by the launcher)
+    const size_t plane = (size_t)p.M * p.N;
+    for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < total4; i += (size_t)gridDim.x * 256) {
+        float4 a = *reinterpret_cast<const float4*>(ws + i * 4);
+        for (int z = 1; z < splits; ++z) {
+            const float4 b = *reinterpret_cast<const float4*>(ws + (size_t)z * plane + i * 4);
+            a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+        }
+        const int n = (int)((i * 4) % (size_t)p.N);
+        if (p.bias != nullptr) {
+            a.x += __bfloat162float(p.bias[n]); a.y += __bfloat162float(p.bias[n + 1]);
+            a.z += __bfloat162float(p.bias[n + 2]); a.w += __bfloat162float(p.bias[n + 3]);
+        }
+        if constexpr (EPI == GemmEpi::F32) {
+            *reinterpret_cast<float4*>(p.Cf + i * 4) = a;
+        } else if constexpr (EPI == GemmEpi::Residual) {
+            const float4 o = *reinterpret_cast<const float4*>(p.Cf + i * 4);
+            *reinterpret_cast<float4*>(p.Cf + i * 4) = make_float4(o.x + a.x, o.y + a.y, o.z + a.z, o.w + a.w);
+        } else {
+            *reinterpret_cast<uint2*>(p.C + i * 4) = make_uint2(pack_bf16(a.x, a.y), pack_bf16(a.z, a.w));
+        }
     }
 }
 

@@ -28,6 +28,9 @@ for p in (ROOT, os.path.join(ROOT, "tests"), os.path.join(ROOT, "edge-fm-x_b200"
         sys.path.insert(0, p)
 
 METRIC, UNIT = "decode_tokens_per_second_batch1", "tok/s"
+# DRAM bytes (read + write) of the four per-layer GEMV launches of one decode step, from the ncu capture
+# summarised in profiles/decode_gemv_qwen1p5b_ncu.md (config 1 only; other configs were not captured).
+NCU_LAYER_GEMV_DRAM_BYTES = {1: 6.33984e6 + 4.758528e6 + 55.090432e6 + 77.824e3 + 27.579904e6}
 NAMES = {0: "qwen2.5-0.5b", 1: "qwen2.5-1.5b", 2: "qwen2.5-vl-3b-llm", 3: "qwen2.5-vl-7b-llm"}
 
 
@@ -509,6 +512,10 @@ def run_ours(args, rank, world, local_rank):
         if k in kbytes:
             kernels[k]["gbs"] = round(kbytes[k] / (us * 1e-6) / 1e9, 1)
             kernels[k]["frac"] = round(kbytes[k] / (us * 1e-6) / 1e9 / peak, 3)
+    traffic = None
+    if args.config in NCU_LAYER_GEMV_DRAM_BYTES:       # measured for the layer GEMVs, algorithmic for the rest of the step
+        layer_alg = sum(v for k, v in kbytes.items() if k != "lm_head")
+        traffic = step_bytes + L * (NCU_LAYER_GEMV_DRAM_BYTES[args.config] - layer_alg)
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -529,7 +536,8 @@ def run_ours(args, rank, world, local_rank):
             "gpu_launches": launches,
             "clocks": clocks,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "peak_kind": peak_kind, "launch": "one decode step (CUDA graph of %d kernel nodes: 5 per layer + lm_head + sampler)" % (5 * L + 2),
+                         "traffic": traffic, "traffic_source": "ncu dram__bytes_read+write of the per-layer GEMV launches (profiles/decode_gemv_qwen1p5b_ncu.md) + algorithmic bytes of lm_head, attention and vectors" if traffic else None,
+                         "peak_kind": peak_kind, "launch": "one decode step (CUDA graph of %d kernel nodes: 5 per layer + lm_head + sampler)" % (5 * L + 2),
                          "bytes_per_launch": step_bytes, "us_per_launch": step_ms * 1e3, "kernels": kernels},
             "tokens_head": tokens[:8], "e2e_tokens_equal": e2e_tokens == tokens,
         }

@@ -226,7 +226,7 @@ efm_status efm_b200_create(const efm_model_desc* desc, int32_t device_id, int32_
         if (need > (size_t)optin) c->mega = false;       // does not fit: phase-per-launch form
         else EFM_TRY(configure_decode_mega((int)need));
     }
-    c->gemm_ws_floats = (size_t)c->num_sms * 128 * 128;      // splits x tiles never exceeds the SM count
+    c->gemm_ws_floats = (size_t)c->num_sms * 128 * 256;      // splits x tiles never exceeds the SM count
     EFM_TRY(dev_alloc(c, &c->gemm_ws, c->gemm_ws_floats, false));
     EFM_TRY(dev_alloc(c, &c->state, 1));
     EFM_TRY(dev_alloc(c, &c->tokens_out, (size_t)d.max_response_tokens));
@@ -729,7 +729,7 @@ efm_status efm_b200_op_gemm(const void* x, const void* w, const void* bias, void
     int sms = 148;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
     L.num_sms = sms;
-    L.gemm_ws_floats = (size_t)sms * 128 * 128;          // lets skinny products take the split-K path, as inside a context
+    L.gemm_ws_floats = (size_t)sms * 128 * 256;          // lets skinny products take the split-K path, as inside a context
     if (cudaMalloc(&L.gemm_ws, L.gemm_ws_floats * sizeof(float)) != cudaSuccess) {
         (void)cudaGetLastError();
         L.gemm_ws = nullptr;

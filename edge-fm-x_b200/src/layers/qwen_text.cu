@@ -302,14 +302,14 @@ static EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-// bf16 row-major [rows, cols] tensor, box = 64 columns x 128 rows, 128-byte swizzle, zero fill
+// bf16 row-major [rows, cols] tensor, box = 64 columns x box_rows rows, 128-byte swizzle, zero fill
 // outside the tensor.
-static bool make_tile_map(CUtensorMap* map, const void* ptr, int rows, int cols, int row_stride) {
+static bool make_tile_map(CUtensorMap* map, const void* ptr, int rows, int cols, int row_stride, int box_rows) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (fn == nullptr) return false;
     const cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     const cuuint64_t gstride[1] = {(cuuint64_t)row_stride * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)tc::BK, (cuuint32_t)tc::BM};
+    const cuuint32_t box[2] = {(cuuint32_t)tc::BK, (cuuint32_t)box_rows};
     const cuuint32_t estride[2] = {1, 1};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), gdim, gstride, box, estride,
               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -324,17 +324,18 @@ static void launch_gemm(Launcher& L, const GemmParams& p, int* error_word = null
         attr_set = true;
     }
     CUtensorMap ma, mb;
-    if (!make_tile_map(&ma, p.A, p.M, p.K, p.lda > 0 ? p.lda : p.K) || !make_tile_map(&mb, p.B, p.N, p.K, p.K)) {
+    if (!make_tile_map(&ma, p.A, p.M, p.K, p.lda > 0 ? p.lda : p.K, tc::BM) || !make_tile_map(&mb, p.B, p.N, p.K, p.K, tc::BN)) {
         if (L.err == cudaSuccess) L.err = cudaErrorInvalidValue;
         return;
     }
-    dim3 grid((p.N + tc::BN - 1) / tc::BN, (p.M + tc::BM - 1) / tc::BM), block(tc::kThreads);
+    const int tiles = ((p.N + tc::BN - 1) / tc::BN) * ((p.M + tc::BM - 1) / tc::BM);
+    const dim3 block(tc::kThreads);
     const bool pdl = L.pdl;
     L.pdl = false;     // prefill kernels do not use the dependent-launch protocol
-    // Few output tiles and a long K: split K over grid.z so that the whole GPU works, fp32 partials to the
-    // workspace, then a fixed-order sum with the epilogue.
+    // Few output tiles and a long K: split K so that the whole GPU works, fp32 partials to the workspace, then
+    // a fixed-order sum with the epilogue.
     if constexpr (EPI == GemmEpi::Bf16Bias || EPI == GemmEpi::Residual || EPI == GemmEpi::F32) {
-        const int tiles = (int)(grid.x * grid.y), KB = (p.K + tc::BK - 1) / tc::BK;
+        const int KB = (p.K + tc::BK - 1) / tc::BK;
         int splits = std::min(L.num_sms / std::max(1, tiles), KB / 4);
         if (L.gemm_ws != nullptr && splits >= 2 && (p.N & 3) == 0 && (size_t)splits * p.M * p.N <= L.gemm_ws_floats) {
             const int per = (KB + splits - 1) / splits;
@@ -343,13 +344,12 @@ static void launch_gemm(Launcher& L, const GemmParams& p, int* error_word = null
             q.kb_per_split = per;
             q.Cf = L.gemm_ws;
             q.bias = nullptr;
-            grid.z = (unsigned)splits;
             static bool attr_f32 = false;
             if (!attr_f32) {
                 cudaFuncSetAttribute(gemm_tc_kernel<GemmEpi::F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc::SMEM_BYTES);
                 attr_f32 = true;
             }
-            L.launch(gemm_tc_kernel<GemmEpi::F32>, grid, block, tc::SMEM_BYTES, ma, mb, q, error_word);
+            L.launch(gemm_tc_kernel<GemmEpi::F32>, dim3(std::min(L.num_sms, tiles * splits)), block, tc::SMEM_BYTES, ma, mb, q, error_word);
             const size_t total4 = (size_t)p.M * p.N / 4;
             const int fin = (int)std::min<size_t>((total4 + 255) / 256, (size_t)L.num_sms * 4);
             L.launch(gemm_splitk_finish_kernel<EPI>, dim3(fin), dim3(256), 0, (const float*)L.gemm_ws, splits, p);
@@ -357,7 +357,7 @@ static void launch_gemm(Launcher& L, const GemmParams& p, int* error_word = null
             return;
         }
     }
-    L.launch(gemm_tc_kernel<EPI>, grid, block, tc::SMEM_BYTES, ma, mb, p, error_word);
+    L.launch(gemm_tc_kernel<EPI>, dim3(std::min(L.num_sms, tiles)), block, tc::SMEM_BYTES, ma, mb, p, error_word);
     L.pdl = pdl;
 }
 

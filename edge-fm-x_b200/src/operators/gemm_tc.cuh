@@ -3,17 +3,19 @@
 // (reference: cublasLtMatmul / CUTLASS sm80 prefill linears, src/operators/linear_impl.cu:457-469,482-706;
 //  the reference has no sm_100 kernel.)
 //
-// One 128 x 128 output tile per block, 192 threads:
+// Persistent blocks (one per SM, 192 threads) walk the 128 x 256 output tiles (and K splits) round-robin:
 //   warp 0      one lane issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle, no multicast) of
-//               a 128 x 64 A tile and a 128 x 64 B tile per stage into a 6-stage ring;
-//   warp 1      allocates 128 TMEM columns; one lane issues tcgen05.mma (M 128, N 128, K 16, four
-//               per stage) and tcgen05.commit, which releases the stage to the producer;
-//   warps 2-5   epilogue: tcgen05.ld the accumulator (row = TMEM lane, 32 columns at a time), stage it in
-//               shared memory so that global rows are written as contiguous segments, and
-//               write bf16 (+bias, optionally erf-GELU) | fp32 residual add | fp32 | silu(gate)*up in bf16.
+//               a 128 x 64 A tile and a 256 x 64 B tile per stage into a 4-stage ring;
+//   warp 1      owns all 512 TMEM columns = two 128 x 256 fp32 accumulators; one lane issues tcgen05.mma
+//               (M 128, N 256, K 16, four per stage) and tcgen05.commit, which releases the stage to the
+//               producer, and after the last k-block of a tile marks the accumulator complete;
+//   warps 2-5   epilogue of tile j while the MMA warp already fills the other accumulator with tile j+1:
+//               tcgen05.ld (row = TMEM lane, 32 columns at a time), bias / activation, staging through
+//               shared memory so that global rows are written as contiguous 128-byte segments:
+//               bf16 (+bias, optionally erf-GELU) | fp32 residual add | fp32 | silu(gate)*up in bf16.
 // Rows past M and columns past N are zero-filled by TMA on load and masked on store.
-// Every mbarrier wait is bounded; a wait that gives up raises *error, the block frees its TMEM and
-// returns.  Bound: tensor pipe (2 M N K flops).
+// Every mbarrier wait is bounded; a wait that gives up raises *error, all roles leave their loops, the
+// block frees its TMEM and returns.  Bound: tensor pipe (2 M N K flops).
 #pragma once
 #include <cuda.h>
 
@@ -31,18 +33,19 @@ struct GemmParams {
     float* Cf;                // F32: out; Residual: in/out (fp32 residual stream)
     int M, N, K;
     int lda = 0;              // row stride of A in elements (0: K)
-    int kb_per_split = 0;     // split-K: block z covers 64-wide k-blocks [z * kb_per_split, (z+1) * kb_per_split) and
+    int kb_per_split = 0;     // split-K: split z covers 64-wide k-blocks [z * kb_per_split, (z+1) * kb_per_split) and
                               // writes its raw fp32 partial tile to Cf + z * M * N (F32 epilogue, no bias); 0: no split
 };
 
 namespace tc {
 
-constexpr int BM = 128, BN = 128, BK = 64, STAGES = 6, UMMA_K = 16;
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4, UMMA_K = 16;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int kThreads = 192;
-constexpr int TMEM_COLS = 128;
+constexpr int TMEM_COLS = 512;                             // two accumulators of BN columns
+constexpr int STAGING_BYTES = 4 * 32 * 36 * 4;             // per epilogue warp: 32 rows x (32 + 4) floats
 constexpr int kWaitLimit = 1 << 20;                        // try_wait polls before giving up
-constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + STAGING_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -84,7 +87,7 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
     d |= (uint64_t)2 << 61;                               // SWIZZLE_128B
     return d;
 }
-// kind::f16, A = B = bf16, D = fp32, both operands K-major, M = 128, N = 128.
+// kind::f16, A = B = bf16, D = fp32, both operands K-major, M = 128, N = BN.
 constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 
 __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
@@ -122,22 +125,24 @@ __global__ void __launch_bounds__(tc::kThreads) gemm_tc_kernel(const __grid_cons
     const uint32_t raw = smem_u32(gemm_tc_smem);
     const uint32_t base = (raw + 1023u) & ~1023u;                     // swizzle atoms need 1024-byte alignment
     unsigned char* base_ptr = gemm_tc_smem + (base - raw);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(base_ptr + (size_t)STAGES * STAGE_BYTES);
-    const uint32_t full0 = base + STAGES * STAGE_BYTES;               // full[s]  = full0 + 8 s
-    const uint32_t empty0 = full0 + 8 * STAGES;                       // empty[s] = empty0 + 8 s
-    const uint32_t done_bar = empty0 + 8 * STAGES;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
+    float* stage_all = reinterpret_cast<float*>(base_ptr + (size_t)STAGES * STAGE_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(base_ptr + (size_t)STAGES * STAGE_BYTES + STAGING_BYTES);
+    const uint32_t full0 = base + STAGES * STAGE_BYTES + STAGING_BYTES;   // full[s]  = full0 + 8 s
+    const uint32_t empty0 = full0 + 8 * STAGES;                           // empty[s] = empty0 + 8 s
+    const uint32_t accf0 = empty0 + 8 * STAGES;                           // accumulator a complete
+    const uint32_t acce0 = accf0 + 16;                                    // accumulator a drained
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
     volatile int* abort_s = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
     const int KB_all = (p.K + BK - 1) / BK;
-    const int kb0 = p.kb_per_split > 0 ? (int)blockIdx.z * p.kb_per_split : 0;
-    const int KB = p.kb_per_split > 0 ? min(KB_all, kb0 + p.kb_per_split) : KB_all;     // this block walks [kb0, KB)
+    const int splits = p.kb_per_split > 0 ? (KB_all + p.kb_per_split - 1) / p.kb_per_split : 1;
+    const int n_items = tiles_m * tiles_n * splits;                   // item = (split, n tile, m tile), m fastest
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
-        mbar_init(done_bar, 1);
+        for (int a = 0; a < 2; ++a) { mbar_init(accf0 + 8 * a, 1); mbar_init(acce0 + 8 * a, 4); }
         *abort_s = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -150,125 +155,153 @@ __global__ void __launch_bounds__(tc::kThreads) gemm_tc_kernel(const __grid_cons
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = *tmem_slot;
 
+    auto item_coords = [&](int item, int& m0, int& n0, int& kb0, int& kb1, int& z) {
+        const int mt = item % tiles_m, rest = item / tiles_m;
+        const int nt = rest % tiles_n;
+        z = rest / tiles_n;
+        m0 = mt * BM;
+        n0 = nt * BN;
+        kb0 = p.kb_per_split > 0 ? z * p.kb_per_split : 0;
+        kb1 = p.kb_per_split > 0 ? min(KB_all, kb0 + p.kb_per_split) : KB_all;
+    };
+
     if (warp == 0) {
         if (lane == 0) {
-            for (int kb = kb0; kb < KB; ++kb) {
-                const int s = (kb - kb0) % STAGES;
-                const uint32_t ph = (uint32_t)((kb - kb0) / STAGES) & 1u;
-                if (!mbar_wait(empty0 + 8 * s, ph ^ 1u, abort_s)) { *abort_s = 1; break; }
-                mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
-                tma_load_2d(base + s * STAGE_BYTES, &map_a, kb * BK, m0, full0 + 8 * s);
-                tma_load_2d(base + s * STAGE_BYTES + A_BYTES, &map_b, kb * BK, n0, full0 + 8 * s);
+            uint32_t it = 0;
+            for (int item = blockIdx.x; item < n_items && *abort_s == 0; item += gridDim.x) {
+                int m0, n0, kb0, kb1, z;
+                item_coords(item, m0, n0, kb0, kb1, z);
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1u;
+                    if (!mbar_wait(empty0 + 8 * s, ph ^ 1u, abort_s)) { *abort_s = 1; break; }
+                    mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+                    tma_load_2d(base + s * STAGE_BYTES, &map_a, kb * BK, m0, full0 + 8 * s);
+                    tma_load_2d(base + s * STAGE_BYTES + A_BYTES, &map_b, kb * BK, n0, full0 + 8 * s);
+                }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            for (int kb = kb0; kb < KB; ++kb) {
-                const int s = (kb - kb0) % STAGES;
-                const uint32_t ph = (uint32_t)((kb - kb0) / STAGES) & 1u;
-                if (!mbar_wait(full0 + 8 * s, ph, abort_s)) { *abort_s = 1; break; }
+            uint32_t it = 0;
+            int j = 0;
+            for (int item = blockIdx.x; item < n_items && *abort_s == 0; item += gridDim.x, ++j) {
+                int m0, n0, kb0, kb1, z;
+                item_coords(item, m0, n0, kb0, kb1, z);
+                const int a = j & 1;
+                const uint32_t use = (uint32_t)(j >> 1) & 1u;
+                if (!mbar_wait(acce0 + 8 * a, use ^ 1u, abort_s)) { *abort_s = 1; break; }     // epilogue drained this buffer
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint64_t da = umma_desc(base + s * STAGE_BYTES), db = umma_desc(base + s * STAGE_BYTES + A_BYTES);
+                const uint32_t acc = tmem + (uint32_t)(a * BN);
+                bool ok = true;
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1u;
+                    if (!mbar_wait(full0 + 8 * s, ph, abort_s)) { *abort_s = 1; ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint64_t da = umma_desc(base + s * STAGE_BYTES), db = umma_desc(base + s * STAGE_BYTES + A_BYTES);
 #pragma unroll
-                for (int k = 0; k < BK / UMMA_K; ++k)               // 32 bytes further along K inside the swizzle atom
-                    umma(tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), ((kb - kb0) | k) != 0 ? 1u : 0u);
-                umma_commit(empty0 + 8 * s);                         // stage free once these MMAs have read it
+                    for (int k = 0; k < BK / UMMA_K; ++k)               // 32 bytes further along K inside the swizzle atom
+                        umma(acc, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), ((kb - kb0) | k) != 0 ? 1u : 0u);
+                    umma_commit(empty0 + 8 * s);                         // stage free once these MMAs have read it
+                }
+                if (!ok) break;
+                umma_commit(accf0 + 8 * a);                              // accumulator complete
             }
-            umma_commit(done_bar);                                   // accumulator complete
         }
     } else {
-        // epilogue warps 2..5: TMEM lane group = warp % 4.  Phase 1: each lane owns one accumulator row; bias and
-        // activation are applied and the row goes to a padded fp32 staging tile in shared memory (the operand ring
-        // is idle once the last MMA has completed).  Phase 2: the warp walks its 32 rows with the lanes across the
-        // columns, so that every global access is one contiguous row segment.
+        // Epilogue warps 2..5: TMEM lane group = warp % 4.  Per 32-column chunk: each lane owns one accumulator row
+        // (tcgen05.ld), applies bias / activation and parks the row in a padded staging tile; then the warp
+        // writes the chunk out four rows per instruction, eight lanes of 16 bytes per row.
         const int q = warp & 3;
-        const bool ok = mbar_wait(done_bar, 0u, abort_s);
-        if (!ok) *abort_s = 1;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        constexpr int LD = BN + 4;                                   // staging row stride in floats
-        float* stage = reinterpret_cast<float*>(base_ptr) + (size_t)q * 32 * LD;
-        if (ok && *abort_s == 0) {
+        constexpr int LD = 36;
+        float* stage = stage_all + (size_t)q * 32 * LD;
+        int j = 0;
+        for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++j) {
+            int m0, n0, kb0, kb1, z;
+            item_coords(item, m0, n0, kb0, kb1, z);
+            const int a = j & 1;
+            const uint32_t use = (uint32_t)(j >> 1) & 1u;
+            if (!mbar_wait(accf0 + 8 * a, use, abort_s)) { *abort_s = 1; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t acc = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * BN);
             constexpr int OUT_COLS = EPI == GemmEpi::SwiGlu ? BN / 2 : BN;
-            if constexpr (EPI == GemmEpi::SwiGlu) {
-                // fused gate|up weight: columns [n0, n0+64) are gate rows, [n0+64, n0+128) the up rows of the
-                // same 64 intermediate channels; out[m, n0/2 + j] = silu(gate_j) * up_j
-#pragma unroll 1
-                for (int c0 = 0; c0 < 64; c0 += 32) {
-                    uint32_t rg[32], ru[32];
-                    tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, rg);
-                    tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(64 + c0), ru);
-                    const int n = n0 + c0;
-                    const bool in = n0 + 128 <= p.N;
-#pragma unroll
-                    for (int j = 0; j < 32; j += 4) {
-                        float o[4];
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            float g = __uint_as_float(rg[j + e]), u = __uint_as_float(ru[j + e]);
-                            if (p.bias != nullptr && in) {
-                                g += __bfloat162float(p.bias[n + j + e]);
-                                u += __bfloat162float(p.bias[n + 64 + j + e]);
-                            }
-                            o[e] = g / (1.0f + __expf(-g)) * u;
-                        }
-                        *reinterpret_cast<float4*>(stage + lane * LD + c0 + j) = make_float4(o[0], o[1], o[2], o[3]);
-                    }
-                }
-            } else {
-#pragma unroll 1
-                for (int c0 = 0; c0 < BN; c0 += 32) {
-                    uint32_t r[32];
-                    tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
-                    const int n = n0 + c0;
-#pragma unroll
-                    for (int j = 0; j < 32; j += 4) {
-                        float o[4];
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            o[e] = __uint_as_float(r[j + e]);
-                            if (p.bias != nullptr && n + j + e < p.N) o[e] += __bfloat162float(p.bias[n + j + e]);
-                            if constexpr (EPI == GemmEpi::Bf16Gelu) o[e] = 0.5f * o[e] * (1.0f + erff(o[e] * 0.70710678118654752f));
-                        }
-                        *reinterpret_cast<float4*>(stage + lane * LD + c0 + j) = make_float4(o[0], o[1], o[2], o[3]);
-                    }
-                }
-            }
-            __syncwarp();
             const int ldc = EPI == GemmEpi::SwiGlu ? (p.N >> 1) : p.N;         // output row length
             const int nc0 = EPI == GemmEpi::SwiGlu ? (n0 >> 1) : n0;           // first output column of the tile
             const bool vec = (ldc & 3) == 0;
-            const size_t split_off = p.kb_per_split > 0 ? (size_t)blockIdx.z * (size_t)p.M * (size_t)p.N : 0;
-            constexpr int LANES_PER_ROW = OUT_COLS / 4;                        // 32 (one row per pass) or 16 (two rows)
-            constexpr int ROWS_PER_PASS = 32 / LANES_PER_ROW;
-            const int cl = (lane % LANES_PER_ROW) * 4;
-#pragma unroll 4
-            for (int r0 = 0; r0 < 32; r0 += ROWS_PER_PASS) {
-                const int r = r0 + lane / LANES_PER_ROW;
-                const int m = m0 + q * 32 + r;
-                const int n = nc0 + cl;
-                if (m >= p.M || n >= ldc) continue;
-                const float4 v = *reinterpret_cast<const float4*>(stage + r * LD + cl);
-                const size_t off = (size_t)m * ldc + n;
-                if (vec && n + 3 < ldc) {
-                    if constexpr (EPI == GemmEpi::F32) {
-                        *reinterpret_cast<float4*>(p.Cf + split_off + off) = v;
-                    } else if constexpr (EPI == GemmEpi::Residual) {
-                        const float4 o = *reinterpret_cast<const float4*>(p.Cf + off);
-                        *reinterpret_cast<float4*>(p.Cf + off) = make_float4(o.x + v.x, o.y + v.y, o.z + v.z, o.w + v.w);
-                    } else {
-                        *reinterpret_cast<uint2*>(p.C + off) = make_uint2(pack_bf16(v.x, v.y), pack_bf16(v.z, v.w));
+            const size_t split_off = p.kb_per_split > 0 ? (size_t)z * (size_t)p.M * (size_t)p.N : 0;
+#pragma unroll 1
+            for (int c0 = 0; c0 < OUT_COLS; c0 += 32) {
+                if (nc0 + c0 >= ldc && c0 > 0) break;                          // whole chunk outside the matrix
+                float o[32];
+                if constexpr (EPI == GemmEpi::SwiGlu) {
+                    // fused gate|up weight: in every 128 columns the first 64 are gate rows and the last 64 the up
+                    // rows of the same channels; out[m, n/2 + j] = silu(gate_j) * up_j
+                    const int blk = c0 >> 6, cc = c0 & 63;
+                    uint32_t rg[32], ru[32];
+                    tmem_ld32(acc + (uint32_t)(blk * 128 + cc), rg);
+                    tmem_ld32(acc + (uint32_t)(blk * 128 + 64 + cc), ru);
+                    const int n = n0 + blk * 128 + cc;                        // gate column in the fused output
+                    const bool in = n0 + blk * 128 + 128 <= p.N;
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) {
+                        float g = __uint_as_float(rg[e]), u = __uint_as_float(ru[e]);
+                        if (p.bias != nullptr && in) {
+                            g += __bfloat162float(p.bias[n + e]);
+                            u += __bfloat162float(p.bias[n + 64 + e]);
+                        }
+                        o[e] = g / (1.0f + __expf(-g)) * u;
                     }
                 } else {
-                    const float e[4] = {v.x, v.y, v.z, v.w};
+                    uint32_t r[32];
+                    tmem_ld32(acc + (uint32_t)c0, r);
+                    const int n = n0 + c0;
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        if (n + i >= ldc) break;
-                        if constexpr (EPI == GemmEpi::F32) p.Cf[split_off + off + i] = e[i];
-                        else if constexpr (EPI == GemmEpi::Residual) p.Cf[off + i] += e[i];
-                        else p.C[off + i] = __float2bfloat16_rn(e[i]);
+                    for (int e = 0; e < 32; ++e) {
+                        o[e] = __uint_as_float(r[e]);
+                        if (p.bias != nullptr && n + e < p.N) o[e] += __bfloat162float(p.bias[n + e]);
+                        if constexpr (EPI == GemmEpi::Bf16Gelu) o[e] = 0.5f * o[e] * (1.0f + erff(o[e] * 0.70710678118654752f));
+                    }
+                }
+                __syncwarp();                                                  // previous chunk fully written out
+#pragma unroll
+                for (int e = 0; e < 32; e += 4)
+                    *reinterpret_cast<float4*>(stage + lane * LD + e) = make_float4(o[e], o[e + 1], o[e + 2], o[e + 3]);
+                __syncwarp();
+                const int cl = (lane & 7) * 4;
+#pragma unroll
+                for (int r0 = 0; r0 < 32; r0 += 4) {
+                    const int r = r0 + (lane >> 3);
+                    const int m = m0 + q * 32 + r;
+                    const int n = nc0 + c0 + cl;
+                    if (m >= p.M || n >= ldc) continue;
+                    const float4 v = *reinterpret_cast<const float4*>(stage + r * LD + cl);
+                    const size_t off = (size_t)m * ldc + n;
+                    if (vec && n + 3 < ldc) {
+                        if constexpr (EPI == GemmEpi::F32) {
+                            *reinterpret_cast<float4*>(p.Cf + split_off + off) = v;
+                        } else if constexpr (EPI == GemmEpi::Residual) {
+                            const float4 old = *reinterpret_cast<const float4*>(p.Cf + off);
+                            *reinterpret_cast<float4*>(p.Cf + off) = make_float4(old.x + v.x, old.y + v.y, old.z + v.z, old.w + v.w);
+                        } else {
+                            *reinterpret_cast<uint2*>(p.C + off) = make_uint2(pack_bf16(v.x, v.y), pack_bf16(v.z, v.w));
+                        }
+                    } else {
+                        const float e4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            if (n + i >= ldc) break;
+                            if constexpr (EPI == GemmEpi::F32) p.Cf[split_off + off + i] = e4[i];
+                            else if constexpr (EPI == GemmEpi::Residual) p.Cf[off + i] += e4[i];
+                            else p.C[off + i] = __float2bfloat16_rn(e4[i]);
+                        }
                     }
                 }
             }
+            // every tcgen05.ld of this accumulator has completed: hand the buffer back to the MMA warp
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acce0 + 8 * a) : "memory");
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");

@@ -85,4 +85,4 @@ def test_config1_full_size_properties():
     a, b = outs["phase_per_launch"], outs["persistent"]
     assert a[0][0] == b[0][0]
     assert rel(a[1][0], b[1][0]) < 1e-6                     # prefill: identical kernels
-    assert rel(a[1][1], b[1][1]) < 2e-3
+    assert rel(a[1][1], b[1][1]) < 1e-2                     # bf16 rounding points amplify the fp32 merge difference

@@ -233,6 +233,19 @@ __global__ void __launch_bounds__(tc::kThreads) gemm_tc_kernel(const __grid_cons
 #pragma unroll 1
             for (int c0 = 0; c0 < OUT_COLS; c0 += 32) {
                 if (nc0 + c0 >= ldc && c0 > 0) break;                          // whole chunk outside the matrix
+                const int cl = (lane & 7) * 4;
+                // residual epilogue: all eight old values of the chunk are requested up front, before the accumulator is
+                // read and long before the first store (the
+                // compiler may not move a load of Cf above a store to Cf by itself), one round trip per chunk
+                float4 prev[8];
+                if constexpr (EPI == GemmEpi::Residual) {
+#pragma unroll
+                    for (int r0 = 0; r0 < 32; r0 += 4) {
+                        const int m = m0 + q * 32 + r0 + (lane >> 3), n = nc0 + c0 + cl;
+                        prev[r0 >> 2] = (vec && m < p.M && n + 3 < ldc) ? __ldcg(reinterpret_cast<const float4*>(p.Cf + (size_t)m * ldc + n))
+                                                                     : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+                }
                 float o[32];
                 if constexpr (EPI == GemmEpi::SwiGlu) {
                     // fused gate|up weight: in every 128 columns the first 64 are gate rows and the last 64 the up
@@ -268,7 +281,6 @@ __global__ void __launch_bounds__(tc::kThreads) gemm_tc_kernel(const __grid_cons
                 for (int e = 0; e < 32; e += 4)
                     *reinterpret_cast<float4*>(stage + lane * LD + e) = make_float4(o[e], o[e + 1], o[e + 2], o[e + 3]);
                 __syncwarp();
-                const int cl = (lane & 7) * 4;
 #pragma unroll
                 for (int r0 = 0; r0 < 32; r0 += 4) {
                     const int r = r0 + (lane >> 3);
@@ -281,7 +293,7 @@ __global__ void __launch_bounds__(tc::kThreads) gemm_tc_kernel(const __grid_cons
                         if constexpr (EPI == GemmEpi::F32) {
                             *reinterpret_cast<float4*>(p.Cf + split_off + off) = v;
                         } else if constexpr (EPI == GemmEpi::Residual) {
-                            const float4 old = *reinterpret_cast<const float4*>(p.Cf + off);
+                            const float4 old = prev[r0 >> 2];
                             *reinterpret_cast<float4*>(p.Cf + off) = make_float4(old.x + v.x, old.y + v.y, old.z + v.z, old.w + v.w);
                         } else {
                             *reinterpret_cast<uint2*>(p.C + off) = make_uint2(pack_bf16(v.x, v.y), pack_bf16(v.z, v.w));

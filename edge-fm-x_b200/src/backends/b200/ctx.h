@@ -37,6 +37,17 @@ struct KvSlot {
     void* mega_layers = nullptr;          // device array of per-layer pointers for the persistent decode kernel
 };
 
+// Scratch of the INT8 prefill attention (operators/sage_attention.cuh).
+struct SageScratch {
+    int8_t* q8 = nullptr;      // [q_rows, q_heads*D]
+    int8_t* k8 = nullptr;      // [kv_rows, kv_heads*D]
+    void* vh = nullptr;        // fp16 [kv_rows, kv_heads*D]
+    float* sq = nullptr;       // [q_rows/128 + 1, q_heads]
+    float* sk = nullptr;       // [kv_rows/128 + 1, kv_heads]
+    float* kmean = nullptr;    // [kv_heads, D]
+    int q_rows = 0, kv_rows = 0;
+};
+
 }  // namespace efm
 
 struct efm_b200_ctx {
@@ -92,6 +103,8 @@ struct efm_b200_ctx {
     float* attn_part_o = nullptr;         // decode attention scratch
     float* attn_part_ml = nullptr;
     unsigned int* attn_counters = nullptr;
+    int prefill_attention_kind = 0;       // 0: bf16 flash attention, 1: INT8 Q.K^T / fp16 P.V
+    efm::SageScratch sage;
     float* gemm_ws = nullptr;             // split-K workspace of the prefill / vision GEMMs (fp32 partial tiles)
     size_t gemm_ws_floats = 0;
     efm::DecodeState* state = nullptr;

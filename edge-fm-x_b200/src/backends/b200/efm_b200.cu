@@ -243,6 +243,7 @@ efm_status efm_b200_destroy(efm_b200_ctx* c) {
     for (auto& kv : c->slots)      // graphs that hold collective nodes go before their communicator
         if (kv.second.graph != nullptr) cudaGraphExecDestroy(kv.second.graph);
     if (c->nccl_comm != nullptr && nccl_api().ok) nccl_api().comm_destroy(c->nccl_comm);
+    if (c->sage.q8 != nullptr) { cudaFree(c->sage.q8); cudaFree(c->sage.k8); cudaFree(c->sage.vh); cudaFree(c->sage.sq); cudaFree(c->sage.sk); cudaFree(c->sage.kmean); }
     for (void* p : c->allocations) cudaFree(p);
     for (auto& ev : c->events)
         if (ev != nullptr) cudaEventDestroy(ev);
@@ -738,6 +739,65 @@ efm_status efm_b200_op_gemm(const void* x, const void* w, const void* bias, void
     const efm_status out = op_finish(L);
     if (L.gemm_ws != nullptr) cudaFree(L.gemm_ws);
     return out;
+}
+
+namespace {
+// INT8 attention scratch for up to q_rows queries and kv_rows keys (one scale per 128-token block and head);
+// plain cudaMalloc, caller frees with free_sage.
+cudaError_t alloc_sage(SageScratch& sc, int q_rows, int kv_rows, int q_heads, int kv_heads, int D) {
+    cudaError_t e = cudaMalloc(&sc.q8, (size_t)q_rows * q_heads * D);
+    if (e == cudaSuccess) e = cudaMalloc(&sc.k8, (size_t)kv_rows * kv_heads * D);
+    if (e == cudaSuccess) e = cudaMalloc(&sc.vh, (size_t)kv_rows * kv_heads * D * 2);
+    if (e == cudaSuccess) e = cudaMalloc(&sc.sq, (size_t)(q_rows / 128 + 1) * q_heads * sizeof(float));
+    if (e == cudaSuccess) e = cudaMalloc(&sc.sk, (size_t)(kv_rows / 128 + 1) * kv_heads * sizeof(float));
+    if (e == cudaSuccess) e = cudaMalloc(&sc.kmean, (size_t)kv_heads * D * sizeof(float));
+    sc.q_rows = q_rows;
+    sc.kv_rows = kv_rows;
+    return e;
+}
+void free_sage(SageScratch& sc) {
+    cudaFree(sc.q8); cudaFree(sc.k8); cudaFree(sc.vh); cudaFree(sc.sq); cudaFree(sc.sk); cudaFree(sc.kmean);
+    sc = SageScratch{};
+}
+}  // namespace
+
+efm_status efm_b200_set_prefill_attention(efm_b200_ctx* c, int32_t kind) {
+    if (c == nullptr) return fail(c, EFM_ERR_INVALID_ARGUMENT, "null argument");
+    if (kind != 0 && kind != 1) return fail(c, EFM_ERR_INVALID_ARGUMENT, "prefill attention kind must be 0 (bf16) or 1 (int8)");
+    if (kind == 1) {
+        int rows = 0;
+        for (auto& kv : c->slots) rows = std::max(rows, kv.second.max_tokens);
+        if (rows == 0) return fail(c, EFM_ERR_STATE, "allocate the KV slots before selecting the INT8 prefill attention");
+        if (c->d.head_dim != 64 && c->d.head_dim != 128) return fail(c, EFM_ERR_UNSUPPORTED, "INT8 prefill attention: head_dim 64 or 128");
+        EFM_CK(c, cudaSetDevice(c->device));
+        if (rows > c->sage.kv_rows) {
+            EFM_CK(c, cudaStreamSynchronize(c->stream));
+            free_sage(c->sage);
+            cudaError_t e = alloc_sage(c->sage, c->max_s, rows, c->d.q_heads, c->d.kv_heads, c->d.head_dim);
+            if (e != cudaSuccess) { free_sage(c->sage); return cuda_fail(c, e, "INT8 attention scratch"); }
+        }
+    }
+    c->prefill_attention_kind = kind;
+    return EFM_OK;
+}
+
+efm_status efm_b200_op_sage_prefill_attention(const void* q, const void* k_cache, const void* v_cache, void* out_bf16,
+                                              int32_t s, int32_t kv_offset, int32_t q_heads, int32_t kv_heads, int32_t head_dim) {
+    efm_status st = op_prepare(nullptr);
+    if (st != EFM_OK) return st;
+    if (q == nullptr || k_cache == nullptr || v_cache == nullptr || out_bf16 == nullptr || s <= 0 || kv_offset < 0 || q_heads <= 0 ||
+        kv_heads <= 0 || q_heads % kv_heads != 0)
+        return fail(nullptr, EFM_ERR_INVALID_ARGUMENT, "op_sage_prefill_attention: bad arguments");
+    if (head_dim != 64 && head_dim != 128) return fail(nullptr, EFM_ERR_UNSUPPORTED, "op_sage_prefill_attention: head_dim 64 or 128");
+    SageScratch sc;
+    cudaError_t e = alloc_sage(sc, s, kv_offset + s, q_heads, kv_heads, head_dim);
+    if (e != cudaSuccess) { free_sage(sc); return cuda_fail(nullptr, e, "INT8 attention scratch"); }
+    Launcher L; L.pdl = false;
+    launch_sage_prefill_attention(L, sc, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
+                                  (__nv_bfloat16*)out_bf16, s, kv_offset, q_heads, kv_heads, head_dim);
+    st = op_finish(L);
+    free_sage(sc);
+    return st;
 }
 
 efm_status efm_b200_op_decode_attention(const void* q, const void* k_cache, const void* v_cache, void* out_bf16,

@@ -122,6 +122,7 @@ json::Value EngineConfig::prefill_model_config() const {
 std::string EngineConfig::runtime_device() const { return section("runtime").get_string("device", "cuda"); }
 int32_t EngineConfig::runtime_device_id() const { return (int32_t)section("runtime").get_int("device_id", 0); }
 bool EngineConfig::use_cuda_graph() const { return section("runtime").get_bool("use_cuda_graph", false); }
+std::string EngineConfig::prefill_attention() const { return section("runtime").get_string("prefill_attention", "bf16"); }
 int32_t EngineConfig::tensor_parallel() const { return (int32_t)section("runtime").get_int("tensor_parallel", 1); }
 bool EngineConfig::lm_head_top1_enabled() const {
     const json::Value rt = section("runtime");

@@ -168,6 +168,9 @@ StandardEngine::StandardEngine(const EngineConfig& config) : config_(config) {
         s.top_k = config_.sampling_top_k();
         s.seed = config_.sampling_seed();
         check(efm_b200_set_sampling(ctx_, &s), "sampling configuration");
+        const std::string pa = config_.prefill_attention();
+        if (pa == "int8") check(efm_b200_set_prefill_attention(ctx_, 1), "prefill attention selection");
+        else if (pa != "bf16") throw ConfigurationError("runtime.prefill_attention must be \"bf16\" or \"int8\", got " + pa);
     } catch (...) {
         efm_b200_destroy(ctx_);
         ctx_ = nullptr;

@@ -8,6 +8,7 @@
 #include "qwen_text.h"
 
 #include "../operators/attention_mma.cuh"
+#include "../operators/sage_attention.cuh"
 #include "../operators/gemm_tc.cuh"
 #include "../operators/prefill.cuh"
 #include "../operators/sample.cuh"
@@ -413,6 +414,43 @@ void launch_prefill_attention(Launcher& L, const __nv_bfloat16* q, const __nv_bf
     launch_seg_attention(L, p, D);
 }
 
+template <int D>
+static void launch_sage_d(Launcher& L, const SageAttnParams& p) {
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaFuncSetAttribute(sage_attention_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sg::smem_bytes<D>());
+        attr_set = true;
+    }
+    L.launch(sage_attention_kernel<D>, dim3((p.S + sa::BQ - 1) / sa::BQ, p.q_heads), dim3(sa::kThreads), sg::smem_bytes<D>(), p);
+}
+
+void launch_sage_prefill_attention(Launcher& L, const SageScratch& sc, const __nv_bfloat16* q, const __nv_bfloat16* k,
+                                   const __nv_bfloat16* v, __nv_bfloat16* out, int S, int kv_offset, int q_heads,
+                                   int kv_heads, int D) {
+    const int T = kv_offset + S;
+    if (S <= 0) return;
+    if ((D != 128 && D != 64) || S > sc.q_rows || T > sc.kv_rows) {
+        if (L.err == cudaSuccess) L.err = cudaErrorInvalidValue;
+        return;
+    }
+    const bool pdl = L.pdl;
+    L.pdl = false;
+    const int kvw = kv_heads * D, qw = q_heads * D;
+    L.launch(sage_kmean_kernel, dim3(kv_heads), dim3(256), 0, k, kvw, T, D, sc.kmean);
+    L.launch(sage_quant_kernel, dim3((T + kSageBlock - 1) / kSageBlock, kv_heads), dim3(kSageBlock), 0, k, kvw, T, kv_heads, D,
+             (const float*)sc.kmean, sc.k8, sc.sk);
+    L.launch(sage_quant_kernel, dim3((S + kSageBlock - 1) / kSageBlock, q_heads), dim3(kSageBlock), 0, q, qw, S, q_heads, D,
+             (const float*)nullptr, sc.q8, sc.sq);
+    L.launch(sage_to_half_kernel, dim3(std::min(((size_t)T * kvw / 2 + 255) / 256, (size_t)L.num_sms * 8)), dim3(256), 0, v, kvw, T,
+             kvw, static_cast<__half*>(sc.vh));
+    SageAttnParams p{};
+    p.q = sc.q8; p.k = sc.k8; p.v = static_cast<const __half*>(sc.vh); p.sq = sc.sq; p.sk = sc.sk; p.out = out;
+    p.S = S; p.kv_offset = kv_offset; p.q_heads = q_heads; p.kv_heads = kv_heads;
+    p.scale = 1.0f / sqrtf((float)D);
+    if (D == 128) launch_sage_d<128>(L, p); else launch_sage_d<64>(L, p);
+    L.pdl = pdl;
+}
+
 void qwen_prefill_chunk(efm_b200_ctx& c, KvSlot& slot, int S, int kv_offset, int n_custom, int embed_token_id,
                         bool sample_last, Launcher& L) {
     const efm_model_desc& d = c.d;
@@ -433,7 +471,10 @@ void qwen_prefill_chunk(efm_b200_ctx& c, KvSlot& slot, int S, int kv_offset, int
                  (const __nv_bfloat16*)c.qkv, c.qbuf, slot.k[l], slot.v[l], (const float*)c.inv_freq,
                  (const int32_t*)c.pos3, S, d.q_heads, d.kv_heads, D, kv_offset, d.use_mrope, d.mrope_section[0],
                  d.mrope_section[0] + d.mrope_section[1]);
-        launch_prefill_attention(L, c.qbuf, slot.k[l], slot.v[l], c.attn, S, kv_offset, d.q_heads, d.kv_heads, D);
+        if (c.prefill_attention_kind == 1)
+            launch_sage_prefill_attention(L, c.sage, c.qbuf, slot.k[l], slot.v[l], c.attn, S, kv_offset, d.q_heads, d.kv_heads, D);
+        else
+            launch_prefill_attention(L, c.qbuf, slot.k[l], slot.v[l], c.attn, S, kv_offset, d.q_heads, d.kv_heads, D);
         if (c.tp_size == 1) {
             GemmParams g{c.attn, w.o, nullptr, nullptr, c.resid, S, H, QD};
             launch_gemm<GemmEpi::Residual>(L, g, &c.state->error);

@@ -24,6 +24,11 @@ void launch_gemm_bf16(Launcher& L, const GemmParams& p);
 void launch_gemm_epi(Launcher& L, GemmEpi epi, const GemmParams& p, int* error_word);
 // Attention with per-query key ranges (or the causal prefill rule when p.lo is null).
 void launch_seg_attention(Launcher& L, const SegAttnParams& p, int D);
+// INT8 prefill attention (sage_attention.cuh): pre-pass (key mean, INT8 Q / centred K + scales, fp16 V) into
+// `sc`, then the attention kernel.  q: [S, q_heads*D] rotated queries; k/v: cache rows [0, kv_offset + S).
+void launch_sage_prefill_attention(Launcher& L, const SageScratch& sc, const __nv_bfloat16* q, const __nv_bfloat16* k,
+                                   const __nv_bfloat16* v, __nv_bfloat16* out, int S, int kv_offset, int q_heads,
+                                   int kv_heads, int D);
 void launch_sample(Launcher& L, const SampleParams& p);
 // y[r,:] = bf16(rmsnorm(x[r,:]) * w) over `rows` fp32 rows.
 void launch_rmsnorm_rows(Launcher& L, const float* x, const __nv_bfloat16* w, __nv_bfloat16* y, int rows, int hidden, float eps);

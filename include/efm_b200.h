@@ -136,6 +136,11 @@ EFM_API efm_status efm_b200_prefill(efm_b200_ctx* ctx, int32_t slot, const int32
                                     int32_t n_embeds, int32_t embed_token_id, int32_t embeds_mem,
                                     const int32_t* pos_ids3, int32_t sample);
 
+/* Which attention kernel efm_b200_prefill uses: 0 = bf16 flash attention (default), 1 = the INT8 scheme of
+ * efm_b200_op_sage_prefill_attention.  Allocates the INT8 scratch for the largest KV slot allocated so far;
+ * call it after efm_b200_alloc_kv_slot.  Decode is unaffected. */
+EFM_API efm_status efm_b200_set_prefill_attention(efm_b200_ctx* ctx, int32_t kind);
+
 /* Replaces prepare_decode_tensors / DecodeRuntimeStateLayout (standard_engine.cpp:128-150,
  * 1479-1572): binds the slot and sets the device state {kv_len, positions, step}.  kv_len =
  * tokens resident before the first decode step; mrope_pos = position of the first decoded
@@ -212,6 +217,13 @@ EFM_API efm_status efm_b200_op_decode_attention_noalloc(const void* q, const voi
 EFM_API efm_status efm_b200_op_prefill_attention(const void* q, const void* k_cache, const void* v_cache,
                                                  void* out_bf16, int32_t s, int32_t kv_offset,
                                                  int32_t q_heads, int32_t kv_heads, int32_t head_dim);
+/* INT8 ("SageAttention"-style) causal prefill attention, same arguments and layout as
+ * efm_b200_op_prefill_attention; head_dim 64 or 128.  Keys are centred per kv head, Q and K quantised per
+ * 128-token block and head (scale = max|x|/127), S from an exact int32 dot product, softmax in fp32, P and V in
+ * fp16.  No source for it exists in the reference tree (README.md:23,456 mention it only). */
+EFM_API efm_status efm_b200_op_sage_prefill_attention(const void* q, const void* k_cache, const void* v_cache,
+                                                      void* out_bf16, int32_t s, int32_t kv_offset,
+                                                      int32_t q_heads, int32_t kv_heads, int32_t head_dim);
 /* Sampler on fp32 logits [vocab] -> one int32 (device).  SamplerLayer::forward
  * (src/layers/sampler.cu:146-299). */
 EFM_API efm_status efm_b200_op_sample(const float* logits, int32_t vocab, const efm_sampling* s,

@@ -72,6 +72,8 @@ SIGNATURES = {
     "efm_b200_op_decode_attention": (I32, [P, P, P, P, I32, I32, I32, I32, I32]),
     "efm_b200_op_decode_attention_noalloc": (I32, [P, P, P, P, I32, I32, I32, I32, I32]),
     "efm_b200_op_prefill_attention": (I32, [P, P, P, P, I32, I32, I32, I32, I32]),
+    "efm_b200_op_sage_prefill_attention": (I32, [P, P, P, P, I32, I32, I32, I32, I32]),
+    "efm_b200_set_prefill_attention": (I32, [P, I32]),
     "efm_b200_op_sample": (I32, [C.POINTER(C.c_float), I32, C.POINTER(Sampling), C.c_uint32, C.POINTER(I32)]),
     "efm_b200_op_segment_attention": (I32, [P, P, P, P, P, P, I32, I32, I32, I32]),
     "efm_b200_vit_create": (I32, [P, C.POINTER(VitDesc), C.POINTER(P)]),
@@ -200,6 +202,9 @@ class Backend:
     def decode_begin(self, slot, kv_len, mrope_pos=None, step=1):
         mp = _i32_array(mrope_pos) if mrope_pos is not None else None
         self.check(self.L.efm_b200_decode_begin(self.ctx, slot, kv_len, mp, step), "decode_begin")
+
+    def set_prefill_attention(self, kind):
+        self.check(self.L.efm_b200_set_prefill_attention(self.ctx, int(kind)), "set_prefill_attention")
 
     def set_token(self, tok):
         self.check(self.L.efm_b200_set_token(self.ctx, int(tok)), "set_token")

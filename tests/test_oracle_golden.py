@@ -161,3 +161,25 @@ def test_vit_plan_windows_of_the_benchmark_images():
     assert len(lens) == 84 and set(lens) == {64, 32, 16} and lens.sum() == 4784
     assert sorted(p.order) == list(range(1196)) and p.cu_full == [0, 4784]
     assert max(p.pos_h) == 51 and max(p.pos_w) == 91
+
+
+# ---- INT8 prefill attention: properties of the CPU statement (no reference vectors exist for it) -------------
+def test_sage_statement_properties():
+    from oracle import sage
+    g = torch.Generator().manual_seed(11)
+    S, off, qh, kvh, D = 150, 40, 4, 2, 128
+    q = torch.randn(S, qh, D, generator=g).to(torch.bfloat16)
+    k = (torch.randn(off + S, kvh, D, generator=g) + 2.0).to(torch.bfloat16)      # large common offset
+    v = torch.randn(off + S, kvh, D, generator=g).to(torch.bfloat16)
+    exact = sage.exact_prefill_attention(q, k, v, off)
+    got = sage.sage_prefill_attention(q, k, v, off)
+    assert (got - exact).abs().max() < 5e-2 * exact.abs().max()
+    # quantisation: |x - q * scale| <= scale / 2, scale = max|x| / 127 per 128-token block and head
+    x = torch.randn(300, 3, 64, generator=g)
+    qi, sc = sage.quantize_blocks(x)
+    assert qi.abs().max() == 127 and sc.shape == (3, 3)
+    err = (x - qi.float() * sc[torch.arange(300) // 128][:, :, None]).abs()
+    assert (err <= sc[torch.arange(300) // 128][:, :, None] * 0.5 + 1e-7).all()
+    # the first query sees exactly keys [0, off]: row 0 equals plain softmax attention over them to INT8 accuracy
+    one = sage.sage_prefill_attention(q[:1], k[:off + 1], v[:off + 1], off)
+    assert (one - exact[:1]).abs().max() < 5e-2 * exact.abs().max()

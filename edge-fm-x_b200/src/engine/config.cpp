@@ -70,6 +70,10 @@ std::string EngineConfig::normalize_model_name(const std::string& raw) {
 
 EngineConfig::EngineConfig(const std::string& config_path) {
     config_ = json::parse(kDefaults);
+    {
+        const size_t slash = config_path.find_last_of('/');
+        config_dir_ = slash == std::string::npos ? std::string(".") : (slash == 0 ? std::string("/") : config_path.substr(0, slash));
+    }
     const json::Value user = load_json(config_path, "configuration file");
     if (!user.is_object()) throw ConfigurationError("configuration file must hold a JSON object");
     for (const auto& kv : user.obj) config_.set(kv.first, kv.second);     // shallow: sections replace wholesale

@@ -22,6 +22,8 @@ public:
     explicit EngineConfig(const std::string& config_path);
 
     const json::Value& root() const { return config_; }
+    const std::string& config_dir() const { return config_dir_; }   // directory of the engine JSON
+    json::Value compact_vocab() const { return section("compact_vocab"); }
     std::string model_name() const;               // as written
     std::string resolved_model_name() const;      // "qwen2_5" | "qwen2_5_vl" (throws otherwise)
     std::string prefill_model_path() const;
@@ -51,6 +53,7 @@ public:
 private:
     json::Value section(const std::string& name) const;
     json::Value config_;
+    std::string config_dir_;
 };
 
 }  // namespace edge_fm

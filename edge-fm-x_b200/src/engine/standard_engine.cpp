@@ -168,6 +168,7 @@ StandardEngine::StandardEngine(const EngineConfig& config) : config_(config) {
         s.top_k = config_.sampling_top_k();
         s.seed = config_.sampling_seed();
         check(efm_b200_set_sampling(ctx_, &s), "sampling configuration");
+        compact_ = CompactVocab(config_);
         const std::string pa = config_.prefill_attention();
         if (pa == "int8") check(efm_b200_set_prefill_attention(ctx_, 1), "prefill attention selection");
         else if (pa != "bf16") throw ConfigurationError("runtime.prefill_attention must be \"bf16\" or \"int8\", got " + pa);
@@ -193,7 +194,8 @@ void StandardEngine::warmup() {
                 for (int r = 0; r < 3; ++r)
                     for (int32_t i = 0; i < n; ++i) pos[(size_t)r * n + i] = i;
             }
-            check(efm_b200_prefill(ctx_, slot.request_id, slot.prefix_token_ids.data(), n, 0, nullptr, 0, -1, EFM_MEM_HOST,
+            const std::vector<int32_t> prefix_ids = compact_.remap_required_token_ids(slot.prefix_token_ids, "kvcache prefix_token_ids");
+            check(efm_b200_prefill(ctx_, slot.request_id, prefix_ids.data(), n, 0, nullptr, 0, -1, EFM_MEM_HOST,
                                    use_mrope_ ? pos.data() : nullptr, 0),
                   "prefix prefill");
         }
@@ -215,6 +217,14 @@ Response StandardEngine::generate(const Request& request) {
         for (int32_t id : config_.stop_token_ids()) stop.insert(id);
         for (int32_t id : request.stop_token_ids()) stop.insert(id);
     }
+
+    // compact vocabulary: the model runs on compact ids, callers keep tokenizer ids (identity when disabled)
+    const std::vector<int32_t> model_ids = compact_.remap_token_ids(request.token_ids(), "request token_ids");
+    if (compact_.enabled() && !request.ignore_stop_tokens())
+        (void)compact_.remap_token_ids(request.stop_token_ids(), "request stop_token_ids");      // a pruned stop id is an error
+    const int32_t model_embed_token_id = request.has_embedding()
+        ? compact_.remap_embed_token_id(request.embed_token_id(), request.embedding().shape().empty() ? -1 : request.embedding().shape()[0])
+        : request.embed_token_id();
 
     // ---- request tensors -> what the backend takes --------------------------------------
     const void* embeds = nullptr;
@@ -270,8 +280,8 @@ Response StandardEngine::generate(const Request& request) {
     // ---- prefill ----------------------------------------------------------------------------
     const double t_prep = now_ms();
     check(efm_b200_event_record(ctx_, 0), "event");
-    check(efm_b200_prefill(ctx_, ctx.request_id, request.token_ids().data() + ctx.prefix_size, ctx.prefill_tokens,
-                           ctx.prefix_size, embeds, n_embeds, request.embed_token_id(), embeds_mem,
+    check(efm_b200_prefill(ctx_, ctx.request_id, model_ids.data() + ctx.prefix_size, ctx.prefill_tokens,
+                           ctx.prefix_size, embeds, n_embeds, model_embed_token_id, embeds_mem,
                            use_mrope_ ? pos.data() : nullptr, 1),
           "prefill");
     check(efm_b200_event_record(ctx_, 1), "event");
@@ -295,6 +305,7 @@ Response StandardEngine::generate(const Request& request) {
     check(efm_b200_read_tokens(ctx_, host_tokens.data(), 0, ctx.generated_tokens), "reading response tokens");
     const double t_copy_end = now_ms();
     const int32_t executed = ctx.generated_tokens;
+    if (compact_.enabled()) host_tokens = compact_.restore_token_ids(host_tokens, "response token_ids");   // stop ids are tokenizer ids
     const double t_stop = now_ms();
     if (!stop.empty())
         for (size_t i = 0; i < host_tokens.size(); ++i)

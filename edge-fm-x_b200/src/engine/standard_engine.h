@@ -10,6 +10,7 @@
 #include <unordered_map>
 #include <vector>
 
+#include "compact_vocab.h"
 #include "config.h"
 #include "kv_manager.h"
 #include "scheduler.h"
@@ -42,6 +43,7 @@ private:
     bool use_graph_ = false;
     std::shared_ptr<KVManager> kv_manager_;
     std::unique_ptr<Scheduler> scheduler_;
+    CompactVocab compact_;                // identity unless compact_vocab.enabled
     std::unordered_map<std::string, double> metrics_;
 };
 

@@ -312,6 +312,22 @@ efm_status efm_b200_vit_finalize_weights(efm_b200_vit* v) {
 
 extern "C" {
 
+efm_status efm_b200_vit_plan(const efm_vit_desc* desc, const int32_t* grid_thw, int32_t n_grids, int32_t* order, int32_t* pos_h,
+                             int32_t* pos_w, int32_t* win_lo, int32_t* win_hi, int32_t* full_lo, int32_t* full_hi) {
+    if (desc == nullptr || grid_thw == nullptr || n_grids <= 0 || desc->struct_size != (int32_t)sizeof(efm_vit_desc) ||
+        desc->merge <= 0 || desc->patch <= 0)
+        return EFM_ERR_INVALID_ARGUMENT;
+    Plan P;
+    std::string why;
+    if (!build_plan(*desc, grid_thw, n_grids, P, why)) return EFM_ERR_INVALID_ARGUMENT;
+    auto put = [](int32_t* dst, const std::vector<int32_t>& src) {
+        if (dst != nullptr) std::memcpy(dst, src.data(), src.size() * sizeof(int32_t));
+    };
+    put(order, P.order); put(pos_h, P.pos_h); put(pos_w, P.pos_w);
+    put(win_lo, P.lo_win); put(win_hi, P.hi_win); put(full_lo, P.lo_full); put(full_hi, P.hi_full);
+    return EFM_OK;
+}
+
 efm_status efm_b200_vit_encode(efm_b200_vit* v, const void* pixels, int32_t pixels_mem, const int32_t* grid_thw,
                                int32_t n_grids, void* out, int32_t out_mem) {
     if (v == nullptr || pixels == nullptr || grid_thw == nullptr || out == nullptr || n_grids <= 0)

@@ -281,6 +281,16 @@ EFM_API efm_status efm_b200_vit_finalize_weights(efm_b200_vit* vit);
  * grid_thw: host int32 [n_grids, 3] patch grids (frames, rows, columns); n_patches = sum t*h*w.
  * out: bf16 [n_patches / merge^2, out_hidden], host or device per out_mem, in the original
  * (row-major merged-grid) order.  Asynchronous on the context's stream when out is on the device. */
+/* Host-only (no GPU needed): the plan efm_b200_vit_encode derives from the patch grids.  For n_patches =
+ * sum t*h*w and n_merged = n_patches / merge^2 it fills (any pointer may be NULL):
+ *   order[n_merged]   window-major order: position i holds merged token order[i] of the row-major input;
+ *   pos_h/pos_w[n_patches]  patch row / column (inside its frame) of the patch at each permuted position;
+ *   win_lo/win_hi[n_patches]  attention range of each permuted position in the windowed layers;
+ *   full_lo/full_hi[n_patches] the same for the full-attention layers (the patch's frame).
+ * Returns EFM_ERR_INVALID_ARGUMENT for grids that are not positive multiples of the merge size. */
+EFM_API efm_status efm_b200_vit_plan(const efm_vit_desc* desc, const int32_t* grid_thw, int32_t n_grids,
+                                     int32_t* order, int32_t* pos_h, int32_t* pos_w, int32_t* win_lo,
+                                     int32_t* win_hi, int32_t* full_lo, int32_t* full_hi);
 EFM_API efm_status efm_b200_vit_encode(efm_b200_vit* vit, const void* pixels, int32_t pixels_mem,
                                        const int32_t* grid_thw, int32_t n_grids, void* out,
                                        int32_t out_mem);

@@ -80,6 +80,7 @@ SIGNATURES = {
     "efm_b200_vit_destroy": (I32, [P]),
     "efm_b200_vit_set_weight": (I32, [P, C.c_char_p, P, C.POINTER(C.c_int64), I32, I32, I32]),
     "efm_b200_vit_finalize_weights": (I32, [P]),
+    "efm_b200_vit_plan": (I32, [C.POINTER(VitDesc), C.POINTER(I32), I32] + [C.POINTER(I32)] * 7),
     "efm_b200_vit_encode": (I32, [P, P, I32, C.POINTER(I32), I32, P, I32]),
 }
 
@@ -259,18 +260,36 @@ class Backend:
         return p.value, mt.value
 
 
+def vit_desc(vcfg, max_patches):
+    d = VitDesc()
+    d.struct_size = C.sizeof(VitDesc)
+    d.depth, d.hidden, d.heads, d.intermediate = vcfg.depth, vcfg.hidden, vcfg.heads, vcfg.intermediate
+    d.out_hidden, d.patch, d.temporal_patch, d.in_channels = vcfg.out_hidden, vcfg.patch, vcfg.temporal_patch, vcfg.in_channels
+    d.merge, d.window, d.n_fullatt = vcfg.merge, vcfg.window, len(vcfg.fullatt)
+    d.fullatt[:len(vcfg.fullatt)] = list(vcfg.fullatt)
+    d.rms_eps, d.rope_theta, d.max_patches = vcfg.rms_eps, vcfg.rope_theta, max_patches
+    return d
+
+
+def vit_plan(vcfg, grids):
+    """Host-only plan of the vision encoder (efm_b200_vit_plan) as python lists, or None when the grids are refused."""
+    n = sum(t * h * w for t, h, w in grids)
+    nm = n // (vcfg.merge * vcfg.merge)
+    d = vit_desc(vcfg, max(n, vcfg.merge * vcfg.merge))
+    bufs = [(I32 * max(nm, 1))()] + [(I32 * max(n, 1))() for _ in range(6)]
+    st = lib().efm_b200_vit_plan(C.byref(d), _i32_array([v for g in grids for v in g]), len(grids), *bufs)
+    if st != EFM_OK:
+        return None
+    names = ("order", "pos_h", "pos_w", "win_lo", "win_hi", "full_lo", "full_hi")
+    return {k: list(b[:nm if k == "order" else n]) for k, b in zip(names, bufs)}
+
+
 class VitEncoder:
     """Vision encoder bound to a Backend's device and stream (efm_b200_vit_*)."""
 
     def __init__(self, be: Backend, vcfg, max_patches):
         self.be, self.L, self.cfg = be, be.L, vcfg
-        d = VitDesc()
-        d.struct_size = C.sizeof(VitDesc)
-        d.depth, d.hidden, d.heads, d.intermediate = vcfg.depth, vcfg.hidden, vcfg.heads, vcfg.intermediate
-        d.out_hidden, d.patch, d.temporal_patch, d.in_channels = vcfg.out_hidden, vcfg.patch, vcfg.temporal_patch, vcfg.in_channels
-        d.merge, d.window, d.n_fullatt = vcfg.merge, vcfg.window, len(vcfg.fullatt)
-        d.fullatt[:len(vcfg.fullatt)] = list(vcfg.fullatt)
-        d.rms_eps, d.rope_theta, d.max_patches = vcfg.rms_eps, vcfg.rope_theta, max_patches
+        d = vit_desc(vcfg, max_patches)
         self.h = P()
         be.check(self.L.efm_b200_vit_create(be.ctx, C.byref(d), C.byref(self.h)), "vit_create")
 

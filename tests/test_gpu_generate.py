@@ -268,3 +268,70 @@ def test_edge_fm_module_configuration_errors(tmp_path, built):
     ok_cfg = synth.write_engine_config(str(tmp_path / "trunc.json"), model_dir)
     with pytest.raises(RuntimeError, match="truncated|outside"):
         edge_fm.EdgeFM(ok_cfg)
+
+
+def test_edge_fm_compact_vocab_and_int8_prefill_through_the_public_api(tmp_path, built):
+    """Non-identity compact vocabulary: requests and responses stay in tokenizer ids while the model runs on a
+    pre-pruned checkpoint (the reference's test_generate_compact_vocab_non_identity_remaps_request_response_and_stop).
+    The same engine also runs with runtime.prefill_attention = "int8"."""
+    import json
+    import edge_fm
+    full = synth.tiny_config(num_layers=2, hidden=256, q_heads=4, kv_heads=2, intermediate=256, vocab=1500)
+    w_full = synth.make_weights(full, seed=4)
+    g = torch.Generator().manual_seed(9)
+    keep = torch.randperm(full.vocab, generator=g)[:900].sort().values            # new -> old, increasing
+    old_to_new = torch.full((full.vocab,), -1, dtype=torch.int64)
+    old_to_new[keep] = torch.arange(keep.numel())
+    pruned = synth.tiny_config(num_layers=2, hidden=256, q_heads=4, kv_heads=2, intermediate=256, vocab=int(keep.numel()))
+    w = dict(w_full)
+    w["model.embed_tokens.weight"] = w_full["model.embed_tokens.weight"][keep].contiguous()
+    model_dir = synth.write_checkpoint(str(tmp_path / "model"), pruned, w)
+    prompt_new = synth.make_token_ids(24, seed=3, vocab=pruned.vocab)
+    prompt_old = [int(keep[i]) for i in prompt_new]
+    (tmp_path / "map.json").write_text(json.dumps(dict(
+        format="edgefm.compact_vocab.v1", original_vocab_size=full.vocab, compact_vocab_size=pruned.vocab,
+        old_to_new=old_to_new.tolist(), new_to_old=keep.tolist(), special_token_ids=[int(keep[0])])))
+
+    # what the model itself produces on compact ids, straight through the C ABI
+    be = cabi.Backend(pruned, max_prefill_tokens=64, max_response_tokens=16)
+    be.load_weights(w)
+    be.alloc_slot(0, 64)
+    be.set_sampling(0.0, 1.0, 0)
+    compact_tokens, _ = cabi.generate(be, 0, prompt_new, 12)
+    be.close()
+
+    for attention in ("bf16", "int8"):
+        path = synth.write_engine_config(str(tmp_path / f"engine_{attention}.json"), model_dir, max_tokens=64, max_new_tokens=12)
+        cfg = json.load(open(path))
+        cfg["compact_vocab"] = {"enabled": True, "mapping_path": "map.json", "reject_unknown_input_ids": True}
+        cfg["runtime"]["prefill_attention"] = attention
+        json.dump(cfg, open(path, "w"))
+        eng = edge_fm.EdgeFM(path)
+        req = edge_fm.Request(0, prompt_old)
+        req.set_ignore_stop_tokens(True)
+        got = list(eng.generate(req).token_ids())
+        if attention == "bf16":
+            assert got == [int(keep[t]) for t in compact_tokens]             # restored to tokenizer ids
+        else:
+            assert got[0] == int(keep[compact_tokens[0]]) and all(int(old_to_new[t]) >= 0 for t in got)
+        # a stop id given in tokenizer ids cuts the restored response
+        rs = edge_fm.Request(0, prompt_old)
+        rs.set_stop_token_ids([got[2]])
+        assert list(eng.generate(rs).token_ids()) == got[:got.index(got[2]) + 1]
+        # a pruned id in the request (or as a request stop id) is refused, not remapped
+        pruned_id = int((old_to_new < 0).nonzero()[0])
+        with pytest.raises(ValueError, match="compact_vocab"):
+            eng.generate(edge_fm.Request(0, prompt_old[:5] + [pruned_id]))
+        bad_stop = edge_fm.Request(0, prompt_old)
+        bad_stop.set_stop_token_ids([pruned_id])
+        with pytest.raises(ValueError, match="compact_vocab"):
+            eng.generate(bad_stop)
+        del eng
+    # an unpruned checkpoint behind an enabled mapping is a configuration error
+    other = synth.write_checkpoint(str(tmp_path / "full"), full, w_full)
+    path = synth.write_engine_config(str(tmp_path / "engine_bad.json"), other, max_tokens=64)
+    cfg = json.load(open(path))
+    cfg["compact_vocab"] = {"enabled": True, "mapping_path": "map.json"}
+    json.dump(cfg, open(path, "w"))
+    with pytest.raises(Exception, match="pre-pruned"):
+        edge_fm.EdgeFM(path)

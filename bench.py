@@ -569,7 +569,11 @@ def main():
     ap.add_argument("--tokens", type=int, default=0, help="override the number of generated tokens")
     ap.add_argument("--ref-context", type=int, default=256, help="context length of the CPU arm's bounded sample")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--prefill-attention", default="auto", choices=["auto", "bf16", "int8"],
+                    help="auto: int8 for config 3 (as the benchmark specifies), bf16 otherwise")
     args = ap.parse_args()
+    if args.prefill_attention == "auto":
+        args.prefill_attention = "int8" if args.config == 3 else "bf16"
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else max(args.warmup, 1)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -218,8 +218,21 @@ def make_weights(cfg: VitConfig, seed: int = 0, device: str = "cpu", prefix: str
     return out
 
 
+def image_mean_std():
+    """Per-channel normalisation constants of the Qwen2-VL image processor, read from transformers at run time."""
+    from transformers.image_utils import OPENAI_CLIP_MEAN, OPENAI_CLIP_STD
+    return list(OPENAI_CLIP_MEAN), list(OPENAI_CLIP_STD)
+
+
 def make_pixels(cfg: VitConfig, grids: Sequence[Tuple[int, int, int]], seed: int = 0, device: str = "cpu") -> torch.Tensor:
-    """Normalised-image stand-in: N(0, 1) values in the processor's patch-row layout, bf16."""
+    """Synthetic images as the benchmark describes them: RGB uniform in [0, 1], mean/std normalised, already in the
+    processor's patch-row layout [n_patches, C*T*P*P] (channel-major inside a row), bf16."""
     n = sum(t * h * w for t, h, w in grids)
     g = torch.Generator(device=device).manual_seed(seed + 7919)
-    return torch.randn(n, cfg.patch_dim, generator=g, device=device).to(torch.bfloat16)
+    px = torch.rand(n, cfg.in_channels, cfg.temporal_patch * cfg.patch * cfg.patch, generator=g, device=device)
+    mean, std = image_mean_std()
+    if len(mean) == cfg.in_channels:
+        m = torch.tensor(mean, device=device)[None, :, None]
+        s = torch.tensor(std, device=device)[None, :, None]
+        px = (px - m) / s
+    return px.reshape(n, cfg.patch_dim).to(torch.bfloat16)

@@ -286,6 +286,10 @@ def test_edge_fm_compact_vocab_and_int8_prefill_through_the_public_api(tmp_path,
     w = dict(w_full)
     w["model.embed_tokens.weight"] = w_full["model.embed_tokens.weight"][keep].contiguous()
     model_dir = synth.write_checkpoint(str(tmp_path / "model"), pruned, w)
+    hf = json.load(open(os.path.join(model_dir, "config.json")))
+    hf["eos_token_id"] = int(keep[1])                      # tokenizer id space, and kept
+    hf.pop("bos_token_id", None)
+    json.dump(hf, open(os.path.join(model_dir, "config.json"), "w"))
     prompt_new = synth.make_token_ids(24, seed=3, vocab=pruned.vocab)
     prompt_old = [int(keep[i]) for i in prompt_new]
     (tmp_path / "map.json").write_text(json.dumps(dict(
@@ -329,6 +333,9 @@ def test_edge_fm_compact_vocab_and_int8_prefill_through_the_public_api(tmp_path,
         del eng
     # an unpruned checkpoint behind an enabled mapping is a configuration error
     other = synth.write_checkpoint(str(tmp_path / "full"), full, w_full)
+    hf = json.load(open(os.path.join(other, "config.json")))
+    hf["eos_token_id"] = int(keep[1])
+    json.dump(hf, open(os.path.join(other, "config.json"), "w"))
     path = synth.write_engine_config(str(tmp_path / "engine_bad.json"), other, max_tokens=64)
     cfg = json.load(open(path))
     cfg["compact_vocab"] = {"enabled": True, "mapping_path": "map.json"}

@@ -272,6 +272,8 @@ def run_tp(args, rank, world, local_rank):
         del t
     be.finalize()
     be.alloc_slot(0, max_tokens)
+    if args.prefill_attention == "int8":        # the benchmark's configuration 3 prefills with the INT8 attention scheme
+        be.set_prefill_attention(1)
     be.set_sampling(temp, top_p, 0)
     be.capture_decode(0)
     # vision encoder: replicated on every rank (its windows are not sharded), weights drawn on the device
@@ -339,6 +341,7 @@ def run_tp(args, rank, world, local_rank):
                                        f"encoder) + {len(ids) - vlm['n_img']} text tokens = {len(ids)}-token prompt, {gen_tokens} generated "
                                        f"tokens, batch 1, temperature {temp}, top_p {top_p}",
                            "parallelism": "single GPU" if world == 1 else f"tp{world} (heads + MLP columns + vocab rows; NCCL all-reduce in the decode graph)",
+                           "prefill_attention": args.prefill_attention,
                            "l2_policy": "weights streamed per decode step exceed L2 (%.2f GB per GPU vs 126 MB)" % (step_bytes / 1e9),
                            "cuda_graph": True},
                 "decode_ms_per_token": step_ms, "prefill_ms": pre_ms / args.steps, "vit_ms": vit_ms / args.steps,

@@ -44,7 +44,7 @@ struct SageScratch {
     void* vh = nullptr;        // fp16 [kv_rows, kv_heads*D]
     float* sq = nullptr;       // [q_rows/128 + 1, q_heads]
     float* sk = nullptr;       // [kv_rows/128 + 1, kv_heads]
-    float* kmean = nullptr;    // [kv_heads, D]
+    float* kmean = nullptr;    // partial key sums [kv_rows/128 + 1, kv_heads, D]
     int q_rows = 0, kv_rows = 0;
 };
 

@@ -750,7 +750,7 @@ cudaError_t alloc_sage(SageScratch& sc, int q_rows, int kv_rows, int q_heads, in
     if (e == cudaSuccess) e = cudaMalloc(&sc.vh, (size_t)kv_rows * kv_heads * D * 2);
     if (e == cudaSuccess) e = cudaMalloc(&sc.sq, (size_t)(q_rows / 128 + 1) * q_heads * sizeof(float));
     if (e == cudaSuccess) e = cudaMalloc(&sc.sk, (size_t)(kv_rows / 128 + 1) * kv_heads * sizeof(float));
-    if (e == cudaSuccess) e = cudaMalloc(&sc.kmean, (size_t)kv_heads * D * sizeof(float));
+    if (e == cudaSuccess) e = cudaMalloc(&sc.kmean, (size_t)(kv_rows / 128 + 1) * kv_heads * D * sizeof(float));
     sc.q_rows = q_rows;
     sc.kv_rows = kv_rows;
     return e;

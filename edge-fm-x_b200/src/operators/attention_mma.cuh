@@ -5,7 +5,7 @@
 //  in the reference and follows the published Qwen2.5-VL encoder.)
 //
 // Each query row i sees the key rows [lo[i], hi[i]).  Without lo/hi the rule is the causal one of
-// prefill: [0, kv_offset + i + 1).  One block = 64 consecutive queries of one head, 4 warps x 16
+// prefill: [0, kv_offset + i + 1).  One block = 64 or 128 consecutive queries of one head, 4 or 8 warps x 16
 // rows; keys and values stream through shared memory in tiles of 64 rows (cp.async, two buffers);
 // per tile S = Q K^T (fragments from ldmatrix), online softmax in registers, O += P V (V fragments
 // from ldmatrix.trans).  Rows of 16-byte chunks are padded by 16 bytes so that ldmatrix is
@@ -28,9 +28,11 @@ struct SegAttnParams {
 };
 
 namespace sa {
-constexpr int BQ = 64, BKV = 64, kThreads = 128;
+constexpr int BKV = 64;                                   // key rows per tile
+// NW warps per block = 16 * NW query rows (NW 4: short sequences, more blocks; NW 8: long ones, K/V tiles shared
+// by twice as many queries and twice the warps per SM)
 template <int D> constexpr int row_bytes() { return (D + 8) * 2; }
-template <int D> constexpr size_t smem_bytes() { return (size_t)5 * BQ * row_bytes<D>(); }
+template <int D, int NW> constexpr size_t smem_bytes() { return (size_t)(16 * NW + 4 * BKV) * row_bytes<D>(); }
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
@@ -52,13 +54,13 @@ __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], 
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// 64 rows x D bf16 from global (row stride in elements) into padded shared rows; rows outside
+// ROWS rows x D bf16 from global (row stride in elements) into padded shared rows; rows outside
 // [row_begin, row_end) are zero filled.
-template <int D>
+template <int D, int ROWS, int THREADS>
 __device__ __forceinline__ void load_tile(uint32_t smem, const __nv_bfloat16* base, int stride, int row0, int row_begin,
                                           int row_end) {
     constexpr int CH = D / 8;
-    for (int idx = threadIdx.x; idx < 64 * CH; idx += kThreads) {
+    for (int idx = threadIdx.x; idx < ROWS * CH; idx += THREADS) {
         const int r = idx / CH, ch = idx - r * CH;
         const int row = row0 + r;
         const bool in = row >= row_begin && row < row_end;
@@ -68,9 +70,10 @@ __device__ __forceinline__ void load_tile(uint32_t smem, const __nv_bfloat16* ba
 }
 }  // namespace sa
 
-template <int D>
-__global__ void __launch_bounds__(sa::kThreads) seg_attention_kernel(const SegAttnParams p) {
+template <int D, int NW>
+__global__ void __launch_bounds__(NW * 32) seg_attention_kernel(const SegAttnParams p) {
     using namespace sa;
+    constexpr int BQ = 16 * NW, kThreads = 32 * NW;
     constexpr int RB = row_bytes<D>();
     constexpr int KS = D / 16;           // k-steps of Q K^T
     constexpr int DT = D / 8;            // 8-wide output tiles
@@ -104,10 +107,10 @@ __global__ void __launch_bounds__(sa::kThreads) seg_attention_kernel(const SegAt
     if (i0 < p.S) { lo0 = p.lo != nullptr ? p.lo[i0] : 0; hi0 = p.hi != nullptr ? p.hi[i0] : p.kv_offset + i0 + 1; }
     if (i1 < p.S) { lo1 = p.lo != nullptr ? p.lo[i1] : 0; hi1 = p.hi != nullptr ? p.hi[i1] : p.kv_offset + i1 + 1; }
 
-    load_tile<D>(sq, p.q + (size_t)h * D, p.q_stride, q0, 0, p.S);
+    load_tile<D, BQ, kThreads>(sq, p.q + (size_t)h * D, p.q_stride, q0, 0, p.S);
     if (ntiles > 0) {
-        load_tile<D>(sk0, kbase, p.kv_stride, kbegin, kbegin, kend);
-        load_tile<D>(sv0, vbase, p.kv_stride, kbegin, kbegin, kend);
+        load_tile<D, BKV, kThreads>(sk0, kbase, p.kv_stride, kbegin, kbegin, kend);
+        load_tile<D, BKV, kThreads>(sv0, vbase, p.kv_stride, kbegin, kbegin, kend);
     }
     cp_async_commit();
 
@@ -122,8 +125,8 @@ __global__ void __launch_bounds__(sa::kThreads) seg_attention_kernel(const SegAt
         const int buf = it & 1;
         if (it + 1 < ntiles) {
             const int row0 = kbegin + (it + 1) * BKV;
-            load_tile<D>(sk0 + (buf ^ 1) * BKV * RB, kbase, p.kv_stride, row0, kbegin, kend);
-            load_tile<D>(sv0 + (buf ^ 1) * BKV * RB, vbase, p.kv_stride, row0, kbegin, kend);
+            load_tile<D, BKV, kThreads>(sk0 + (buf ^ 1) * BKV * RB, kbase, p.kv_stride, row0, kbegin, kend);
+            load_tile<D, BKV, kThreads>(sv0 + (buf ^ 1) * BKV * RB, vbase, p.kv_stride, row0, kbegin, kend);
         }
         cp_async_commit();
         cp_async_wait<1>();

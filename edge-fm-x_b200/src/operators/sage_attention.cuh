@@ -4,7 +4,7 @@
 //  scale = max|x| / 127, S = (Qi8 . Ki8^T) sq sk / sqrt(D) from an exact int32 dot product, fp32 online
 //  softmax, P in fp16, P . V in fp16 with fp32 accumulation.)
 //
-// Pre-pass (HBM-bound, a few microseconds): key mean per kv head; Q and centred K to INT8 + scales; V to fp16.
+// Pre-pass (HBM-bound, a few microseconds): per-block key sums; Q and centred K to INT8 + scales; V to fp16.
 // Main kernel: same tiling as seg_attention_kernel (64 queries x 64-key tiles, cp.async double buffer,
 // ldmatrix fragments) with mma.sync m16n8k32 s8 for Q.K^T and m16n8k16 f16 for P.V.  Causal rule only:
 // query i sees keys [0, kv_offset + i].  Bound: tensor pipe.
@@ -18,49 +18,83 @@ namespace efm {
 
 constexpr int kSageBlock = 128;      // tokens per quantisation block
 
-// mean over tokens of k[t, h, :] (bf16 rows of `stride` elements).  One block per kv head, 256 threads.
-__global__ void __launch_bounds__(256) sage_kmean_kernel(const __nv_bfloat16* __restrict__ k, int stride, int T, int D,
-                                                        float* __restrict__ mean) {
-    __shared__ float part[256];
-    const int h = blockIdx.x, c = threadIdx.x % D, tg = threadIdx.x / D, ng = 256 / D;
-    float s = 0.f;
-    if (tg < ng)
-        for (int t = tg; t < T; t += ng) s += __bfloat162float(k[(size_t)t * stride + (size_t)h * D + c]);
-    part[threadIdx.x] = s;
+// Partial sums for the key mean: block (b, h) adds up the rows of quantisation block b of kv head h,
+// part[b][h][:] (fp32).  The consumer adds the partials in block order, so the mean is deterministic.
+// 512 threads: warp w takes rows w, w + 16, ... (eight independent loads per lane), lane l the channels 4l .. 4l+3.
+__global__ void __launch_bounds__(512) sage_ksum_kernel(const __nv_bfloat16* __restrict__ k, int stride, int T, int heads, int D,
+                                                       float* __restrict__ part) {
+    __shared__ float red[16][kSageBlock];
+    const int b = blockIdx.x, h = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t0 = b * kSageBlock;
+    float a[4] = {0.f, 0.f, 0.f, 0.f};
+    if (lane * 4 < D) {
+        uint2 w[kSageBlock / 16];
+#pragma unroll
+        for (int i = 0; i < kSageBlock / 16; ++i) {
+            const int t = t0 + warp + 16 * i;
+            w[i] = t < T ? *reinterpret_cast<const uint2*>(k + (size_t)t * stride + (size_t)h * D + lane * 4) : make_uint2(0u, 0u);
+        }
+#pragma unroll
+        for (int i = 0; i < kSageBlock / 16; ++i) {
+            a[0] += bf16lo(w[i].x); a[1] += bf16hi(w[i].x); a[2] += bf16lo(w[i].y); a[3] += bf16hi(w[i].y);
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) red[warp][lane * 4 + e] = a[e];
+    }
     __syncthreads();
-    if (threadIdx.x < D) {
-        float a = 0.f;
-        for (int g = 0; g < ng; ++g) a += part[g * D + threadIdx.x];
-        mean[h * D + threadIdx.x] = a / (float)T;
+    if ((int)threadIdx.x < D) {
+        float sum = 0.f;
+#pragma unroll
+        for (int w2 = 0; w2 < 16; ++w2) sum += red[w2][threadIdx.x];
+        part[((size_t)b * heads + h) * D + threadIdx.x] = sum;
     }
 }
 
-// One block = one quantisation block (128 tokens) of one head; thread t owns token row t.
-// out: int8 [T, heads, D]; scales: [ceil(T/128), heads].  mean may be null.
-__global__ void __launch_bounds__(kSageBlock) sage_quant_kernel(const __nv_bfloat16* __restrict__ x, int stride, int T,
-                                                               int heads, int D, const float* __restrict__ mean,
-                                                               int8_t* __restrict__ out, float* __restrict__ scales) {
-    __shared__ float wmax[kSageBlock / 32];
+// One block = one quantisation block (128 tokens) of one head, 512 threads: four threads per token row, each
+// holding a quarter of the row in registers (max, then quantise, no second read).
+// out: int8 [T, heads, D]; scales: [ceil(T/128), heads].  ksum (may be null): the partial key sums of
+// sage_ksum_kernel, [n_part][heads][D]; the row mean (sum of the partials in order, divided by T) is subtracted.
+template <int D>
+__global__ void __launch_bounds__(512) sage_quant_kernel(const __nv_bfloat16* __restrict__ x, int stride, int T, int heads,
+                                                        const float* __restrict__ ksum, int n_part, int8_t* __restrict__ out,
+                                                        float* __restrict__ scales) {
+    constexpr int Q = D / 4;                              // elements per thread (32 or 16)
+    __shared__ float wmax[16];
     __shared__ float s_scale;
-    const int b = blockIdx.x, h = blockIdx.y, t = b * kSageBlock + threadIdx.x;
-    const __nv_bfloat16* row = x + (size_t)t * stride + (size_t)h * D;
-    const float* mu = mean != nullptr ? mean + h * D : nullptr;
+    __shared__ float s_mean[D];
+    const int b = blockIdx.x, h = blockIdx.y, r = threadIdx.x >> 2, part = threadIdx.x & 3;
+    const int t = b * kSageBlock + r;
+    if (ksum != nullptr && (int)threadIdx.x < D) {
+        float a = 0.f;
+        for (int i = 0; i < n_part; ++i) a += ksum[((size_t)i * heads + h) * D + threadIdx.x];
+        s_mean[threadIdx.x] = a / (float)T;
+    }
+    __syncthreads();
+    float v[Q];
     float amax = 0.f;
     if (t < T) {
-        for (int d = 0; d < D; d += 8) {
-            const uint4 w = *reinterpret_cast<const uint4*>(row + d);
+        const __nv_bfloat16* src = x + (size_t)t * stride + (size_t)h * D + part * Q;
+#pragma unroll
+        for (int j = 0; j < Q / 8; ++j) {
+            const uint4 w = *reinterpret_cast<const uint4*>(src + j * 8);
             float f[8];
             unpack8(w, f);
 #pragma unroll
-            for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(mu != nullptr ? f[e] - mu[d + e] : f[e]));
+            for (int e = 0; e < 8; ++e) {
+                v[j * 8 + e] = ksum != nullptr ? f[e] - s_mean[part * Q + j * 8 + e] : f[e];
+                amax = fmaxf(amax, fabsf(v[j * 8 + e]));
+            }
         }
+    } else {
+#pragma unroll
+        for (int e = 0; e < Q; ++e) v[e] = 0.f;
     }
     amax = warp_max(amax);
     if ((threadIdx.x & 31) == 0) wmax[threadIdx.x >> 5] = amax;
     __syncthreads();
     if (threadIdx.x == 0) {
         float m = 0.f;
-        for (int w = 0; w < kSageBlock / 32; ++w) m = fmaxf(m, wmax[w]);
+        for (int w = 0; w < 16; ++w) m = fmaxf(m, wmax[w]);
         const float sc = m > 0.f ? m / 127.0f : 1.0f;
         s_scale = sc;
         scales[b * heads + h] = sc;
@@ -68,27 +102,21 @@ __global__ void __launch_bounds__(kSageBlock) sage_quant_kernel(const __nv_bfloa
     __syncthreads();
     if (t >= T) return;
     const float sc = s_scale;
-    int8_t* dst = out + ((size_t)t * heads + h) * D;
-    for (int d = 0; d < D; d += 16) {
+    int8_t* dst = out + ((size_t)t * heads + h) * D + part * Q;
+#pragma unroll
+    for (int j = 0; j < Q / 16; ++j) {
         uint32_t packed[4];
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-            const uint4 w = *reinterpret_cast<const uint4*>(row + d + half * 8);
-            float f[8];
-            unpack8(w, f);
+        for (int w = 0; w < 4; ++w) {
+            uint32_t word = 0;
 #pragma unroll
-            for (int e = 0; e < 8; e += 4) {
-                uint32_t word = 0;
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float v = mu != nullptr ? f[e + i] - mu[d + half * 8 + e + i] : f[e + i];
-                    const int qv = (int)fminf(fmaxf(rintf(v / sc), -127.f), 127.f);
-                    word |= (uint32_t)(qv & 0xff) << (8 * i);
-                }
-                packed[half * 2 + e / 4] = word;
+            for (int i = 0; i < 4; ++i) {
+                const int qv = (int)fminf(fmaxf(rintf(v[j * 16 + w * 4 + i] / sc), -127.f), 127.f);
+                word |= (uint32_t)(qv & 0xff) << (8 * i);
             }
+            packed[w] = word;
         }
-        *reinterpret_cast<uint4*>(dst + d) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        *reinterpret_cast<uint4*>(dst + j * 16) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
     }
 }
 
@@ -118,6 +146,7 @@ namespace sg {
 using namespace sa;
 template <int D> constexpr int q_row() { return D + 16; }            // int8 rows, 16 bytes of padding
 template <int D> constexpr int v_row() { return (D + 8) * 2; }       // fp16 rows
+constexpr int BQ = 64, kThreads = 128;                                 // 4 warps x 16 query rows
 template <int D> constexpr size_t smem_bytes() { return (size_t)BQ * q_row<D>() * 3 + (size_t)BKV * v_row<D>() * 2; }
 
 __device__ __forceinline__ void mma_s8(int (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
@@ -149,7 +178,7 @@ __device__ __forceinline__ void load_rows(uint32_t smem, const unsigned char* ba
 }  // namespace sg
 
 template <int D>
-__global__ void __launch_bounds__(sa::kThreads) sage_attention_kernel(const SageAttnParams p) {
+__global__ void __launch_bounds__(sg::kThreads) sage_attention_kernel(const SageAttnParams p) {
     using namespace sg;
     constexpr int QR = q_row<D>(), VR = v_row<D>();
     constexpr int KS = D / 32;           // int8 k-steps of Q K^T

@@ -272,6 +272,12 @@ def run_tp(args, rank, world, local_rank):
         del t
     be.finalize()
     be.alloc_slot(0, max_tokens)
+    fused = world > 1 and args.tp_exchange == "peer"
+    if fused:        # the decode step's all-reduces inside the GEMVs, over peer memory (CUDA IPC handles via the host)
+        handles = [None] * world
+        dist.all_gather_object(handles, be.tp_peer_export())
+        be.tp_peer_import(handles)
+        dist.barrier()
     if args.prefill_attention == "int8":        # the benchmark's configuration 3 prefills with the INT8 attention scheme
         be.set_prefill_attention(1)
     be.set_sampling(temp, top_p, 0)
@@ -340,7 +346,8 @@ def run_tp(args, rank, world, local_rank):
                 "config": {"workload": f"{NAMES[args.config]}: 1288x728 image ({n_patches} patches -> {vlm['n_img']} tokens through the vision "
                                        f"encoder) + {len(ids) - vlm['n_img']} text tokens = {len(ids)}-token prompt, {gen_tokens} generated "
                                        f"tokens, batch 1, temperature {temp}, top_p {top_p}",
-                           "parallelism": "single GPU" if world == 1 else f"tp{world} (heads + MLP columns + vocab rows; NCCL all-reduce in the decode graph)",
+                           "parallelism": "single GPU" if world == 1 else f"tp{world} (heads + MLP columns + vocab rows; decode all-reduce: " +
+                                          ("fused into the GEMVs over peer memory" if fused else "NCCL in the decode graph") + ")",
                            "prefill_attention": args.prefill_attention,
                            "l2_policy": "weights streamed per decode step exceed L2 (%.2f GB per GPU vs 126 MB)" % (step_bytes / 1e9),
                            "cuda_graph": True},
@@ -572,6 +579,8 @@ def main():
     ap.add_argument("--tokens", type=int, default=0, help="override the number of generated tokens")
     ap.add_argument("--ref-context", type=int, default=256, help="context length of the CPU arm's bounded sample")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--tp-exchange", default="peer", choices=["peer", "nccl"],
+                    help="config 3 on several GPUs: how the decode step sums the row-parallel partials")
     ap.add_argument("--prefill-attention", default="auto", choices=["auto", "bf16", "int8"],
                     help="auto: int8 for config 3 (as the benchmark specifies), bf16 otherwise")
     args = ap.parse_args()

@@ -177,6 +177,7 @@ efm_status efm_b200_create(const efm_model_desc* desc, int32_t device_id, int32_
         EFM_TRY(dev_alloc(c, &c->ybuf, S * H));
         EFM_TRY(dev_alloc(c, &c->ysum, S * H));
         EFM_TRY(dev_alloc(c, &c->logits_l, (size_t)c->vocab_l));
+        EFM_TRY(dev_alloc(c, &c->tp_xchg, 256 + (size_t)2 * tp_size * H * sizeof(float)));     // zeroed: flags, epoch, ticket
     }
     EFM_TRY(dev_alloc(c, &c->final_norm, H));
     c->layers.resize(d.num_layers);
@@ -242,6 +243,8 @@ efm_status efm_b200_destroy(efm_b200_ctx* c) {
     if (c->stream != nullptr) cudaStreamSynchronize(c->stream);
     for (auto& kv : c->slots)      // graphs that hold collective nodes go before their communicator
         if (kv.second.graph != nullptr) cudaGraphExecDestroy(kv.second.graph);
+    for (int r = 0; r < 8; ++r)
+        if (c->peers_ready && r != c->tp_rank && c->peer_base[r] != nullptr) cudaIpcCloseMemHandle(c->peer_base[r]);
     if (c->nccl_comm != nullptr && nccl_api().ok) nccl_api().comm_destroy(c->nccl_comm);
     if (c->sage.q8 != nullptr) { cudaFree(c->sage.q8); cudaFree(c->sage.k8); cudaFree(c->sage.vh); cudaFree(c->sage.sq); cudaFree(c->sage.sk); cudaFree(c->sage.kmean); }
     for (void* p : c->allocations) cudaFree(p);
@@ -270,6 +273,43 @@ efm_status efm_b200_tp_init(efm_b200_ctx* c, const void* id128) {
     EFM_CK(c, cudaSetDevice(c->device));
     const int r = api.comm_init_rank(&c->nccl_comm, c->tp_size, id128, c->tp_rank);
     if (r != 0) { c->nccl_comm = nullptr; return fail(c, EFM_ERR_CUDA, std::string("ncclCommInitRank: ") + api.error_string(r)); }
+    return EFM_OK;
+}
+
+efm_status efm_b200_tp_peer_export(efm_b200_ctx* c, void* handle64) {
+    if (c == nullptr || handle64 == nullptr) return fail(c, EFM_ERR_INVALID_ARGUMENT, "null argument");
+    if (c->tp_size == 1 || c->tp_xchg == nullptr) return fail(c, EFM_ERR_STATE, "peer exchange needs tp_size > 1");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+    EFM_CK(c, cudaSetDevice(c->device));
+    EFM_CK(c, cudaStreamSynchronize(c->stream));            // the buffer's zero fill has landed
+    cudaIpcMemHandle_t h;
+    EFM_CK(c, cudaIpcGetMemHandle(&h, c->tp_xchg));
+    std::memcpy(handle64, &h, 64);
+    return EFM_OK;
+}
+
+efm_status efm_b200_tp_peer_import(efm_b200_ctx* c, const void* handles, int32_t n_handles) {
+    if (c == nullptr || handles == nullptr) return fail(c, EFM_ERR_INVALID_ARGUMENT, "null argument");
+    if (c->tp_size == 1 || c->tp_xchg == nullptr) return fail(c, EFM_ERR_STATE, "peer exchange needs tp_size > 1");
+    if (n_handles != c->tp_size || c->tp_size > 8) return fail(c, EFM_ERR_INVALID_ARGUMENT, "one handle per rank, at most 8 ranks");
+    if (c->peers_ready) return fail(c, EFM_ERR_STATE, "peer buffers are already imported");
+    EFM_CK(c, cudaSetDevice(c->device));
+    for (int r = 0; r < c->tp_size; ++r) {
+        if (r == c->tp_rank) { c->peer_base[r] = c->tp_xchg; continue; }
+        cudaIpcMemHandle_t h;
+        std::memcpy(&h, static_cast<const char*>(handles) + (size_t)r * 64, 64);
+        void* p = nullptr;
+        cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) {
+            for (int q = 0; q < r; ++q)
+                if (q != c->tp_rank && c->peer_base[q] != nullptr) { cudaIpcCloseMemHandle(c->peer_base[q]); c->peer_base[q] = nullptr; }
+            return cuda_fail(c, e, "cudaIpcOpenMemHandle (peer exchange buffer)");
+        }
+        c->peer_base[r] = static_cast<char*>(p);
+    }
+    for (auto& kv : c->slots)       // decode graphs captured with the NCCL form are rebuilt on next use
+        if (kv.second.graph != nullptr) { cudaGraphExecDestroy(kv.second.graph); kv.second.graph = nullptr; }
+    c->peers_ready = true;
     return EFM_OK;
 }
 

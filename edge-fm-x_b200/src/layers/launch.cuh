@@ -94,6 +94,7 @@ inline cudaError_t configure_gemv(int max_smem_optin) {
     if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_kernel<Epi::QkvRope>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem_optin);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_kernel<Epi::SwiGlu>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem_optin);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_kernel<Epi::Logits>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem_optin);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_kernel<Epi::Peers>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem_optin);
     return e;
 }
 

@@ -138,6 +138,25 @@ static void tp_all_gather(efm_b200_ctx& c, Launcher& L, const float* send, float
     else if (L.counter != nullptr) ++*L.counter;
 }
 
+// Exchange buffer layout (ctx.h): flags [2][8] u32 at 0, epoch at 64, ticket at 68, receive buffer [2][tp][H] fp32 at 256.
+static void peers_producer(const efm_b200_ctx& c, GemvParams& p, int parity) {
+    const size_t H = (size_t)c.d.hidden;
+    p.n_peers = c.tp_size;
+    for (int r = 0; r < c.tp_size; ++r) {
+        p.peer_out[r] = reinterpret_cast<float*>(c.peer_base[r] + 256) + ((size_t)parity * c.tp_size + c.tp_rank) * H;
+        p.peer_flag[r] = reinterpret_cast<unsigned int*>(c.peer_base[r]) + parity * 8 + c.tp_rank;
+    }
+    p.epoch = reinterpret_cast<unsigned int*>(c.tp_xchg + 64);
+    p.ticket = reinterpret_cast<unsigned int*>(c.tp_xchg + 68);
+}
+static void peers_consumer(const efm_b200_ctx& c, GemvParams& p, int parity) {
+    p.addend_parts = reinterpret_cast<const float*>(c.tp_xchg + 256) + (size_t)parity * c.tp_size * c.d.hidden;
+    p.wait_flags = reinterpret_cast<const unsigned int*>(c.tp_xchg) + parity * 8;
+    p.n_parts = c.tp_size;
+    p.epoch = reinterpret_cast<unsigned int*>(c.tp_xchg + 64);
+    p.error = &c.state->error;
+}
+
 // Tensor-parallel decode step: column-parallel QKV / gate-up, row-parallel o_proj / down with an
 // all-reduce of the fp32 partial [H]; the residual add moves into the next kernel's norm prologue
 // (x = bf16(x + bf16(sum)), ping-ponging between two residual buffers so no block re-reads a row that
@@ -147,13 +166,14 @@ static void qwen_decode_step_tp(efm_b200_ctx& c, KvSlot& slot, Launcher& L) {
     const int H = d.hidden, D = d.head_dim, QD = d.q_heads * D, KVD = d.kv_heads * D, I = d.intermediate;
     float* RA = c.resid_d;
     float* RB = c.resid_d2;
+    const bool fused = c.peers_ready;        // exchange inside the GEMVs over peer memory instead of ncclAllReduce
     for (int l = 0; l < d.num_layers; ++l) {
         const LayerWeights& w = c.layers[l];
         {
             GemvParams p = base_gemv(w.qkv, QD + 2 * KVD, H);
             p.prologue = l == 0 ? kProEmbedRmsNorm : kProRmsNorm;
             p.xr = RB;                       // l > 0: residual after the previous layer's attention add
-            p.addend = l == 0 ? nullptr : c.ysum;
+            if (l > 0) { if (fused) peers_consumer(c, p, 1); else p.addend = c.ysum; }
             p.resid_out = RA;
             p.norm_w = w.in_norm; p.eps = d.rms_eps; p.embed_table = c.embed; p.vocab = d.vocab; p.state = c.state;
             p.bias = w.qkv_bias; p.q_out = c.q_d; p.k_cache = slot.k[l]; p.v_cache = slot.v[l]; p.inv_freq = c.inv_freq;
@@ -173,29 +193,41 @@ static void qwen_decode_step_tp(efm_b200_ctx& c, KvSlot& slot, Launcher& L) {
         {
             GemvParams p = base_gemv(w.o, H, c.o_k);
             p.x = c.attn_d + (size_t)c.att_rep_idx * c.o_k;
-            p.logits = c.ybuf; p.part_val = c.part_val; p.part_idx = c.part_idx;
-            launch_gemv<Epi::Logits>(L, p, c.num_sms);                 // fp32 partial output
+            if (fused) {
+                peers_producer(c, p, 0);
+                launch_gemv<Epi::Peers>(L, p, c.num_sms);              // fp32 partial straight into every rank's buffer
+            } else {
+                p.logits = c.ybuf; p.part_val = c.part_val; p.part_idx = c.part_idx;
+                launch_gemv<Epi::Logits>(L, p, c.num_sms);             // fp32 partial output
+            }
         }
-        tp_all_reduce(c, L, c.ybuf, c.ysum, (size_t)H);
+        if (!fused) tp_all_reduce(c, L, c.ybuf, c.ysum, (size_t)H);
         {
             GemvParams p = base_gemv(w.gate_up, 2 * I, H);
             p.prologue = kProRmsNorm;
-            p.xr = RA; p.addend = c.ysum; p.resid_out = RB;
+            p.xr = RA; p.resid_out = RB;
+            if (fused) peers_consumer(c, p, 0); else p.addend = c.ysum;
             p.norm_w = w.post_norm; p.eps = d.rms_eps; p.y = c.act_d;
             launch_gemv<Epi::SwiGlu>(L, p, c.num_sms);
         }
         {
             GemvParams p = base_gemv(w.down, H, I);
             p.x = c.act_d;
-            p.logits = c.ybuf; p.part_val = c.part_val; p.part_idx = c.part_idx;
-            launch_gemv<Epi::Logits>(L, p, c.num_sms);
+            if (fused) {
+                peers_producer(c, p, 1);
+                launch_gemv<Epi::Peers>(L, p, c.num_sms);
+            } else {
+                p.logits = c.ybuf; p.part_val = c.part_val; p.part_idx = c.part_idx;
+                launch_gemv<Epi::Logits>(L, p, c.num_sms);
+            }
         }
-        tp_all_reduce(c, L, c.ybuf, c.ysum, (size_t)H);
+        if (!fused) tp_all_reduce(c, L, c.ybuf, c.ysum, (size_t)H);
     }
     {
         GemvParams p = base_gemv(c.lm_head, c.vocab_l, H);
         p.prologue = kProRmsNorm;
-        p.xr = RB; p.addend = c.ysum; p.resid_out = RA;
+        p.xr = RB; p.resid_out = RA;
+        if (fused) peers_consumer(c, p, 1); else p.addend = c.ysum;
         p.norm_w = c.final_norm; p.eps = d.rms_eps;
         p.logits = c.logits_l; p.part_val = c.part_val; p.part_idx = c.part_idx;
         launch_gemv<Epi::Logits>(L, p, c.num_sms);

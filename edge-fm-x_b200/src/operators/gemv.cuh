@@ -28,7 +28,9 @@
 
 namespace efm {
 
-enum class Epi : int { Plain = 0, Residual = 1, QkvRope = 2, SwiGlu = 3, Logits = 4 };
+enum class Epi : int { Plain = 0, Residual = 1, QkvRope = 2, SwiGlu = 3, Logits = 4, Peers = 5 };
+constexpr int kMaxPeers = 8;
+constexpr int kPeerSpinLimit = 1 << 22;      // flag polls before a wait gives up (a few milliseconds)
 enum : int { kProPlain = 0, kProRmsNorm = 1, kProEmbedRmsNorm = 2 };
 
 struct GemvParams {
@@ -58,7 +60,30 @@ struct GemvParams {
     float* logits;            // Logits
     float* part_val;
     int* part_idx;
+    // Peers (tensor parallel, row-parallel linear fused with its exchange): every output pair is stored into
+    // this rank's row of EVERY rank's receive buffer (peer memory over NVLink, own buffer included); the last
+    // block to finish bumps the local epoch and publishes it in this rank's flag word on every rank.
+    float* peer_out[kMaxPeers];
+    unsigned int* peer_flag[kMaxPeers];
+    int n_peers;
+    unsigned int* epoch;      // local: number of exchanges completed by this rank
+    unsigned int* ticket;     // local: block ticket, zero between launches
+    // consumer side (norm prologues): wait until every rank's flag reached the local epoch, then
+    // x = x + sum over ranks, in rank order, of parts[r][:]
+    const float* addend_parts;            // local receive buffer [n_parts][K]
+    const unsigned int* wait_flags;       // local flags [n_parts]
+    int n_parts;
+    int* error;               // raised (3) when a wait gives up
 };
+
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 
 __device__ __forceinline__ void group_barrier(int id, int nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
@@ -94,6 +119,10 @@ __device__ __forceinline__ void item_epilogue(const GemvParams& p, int item, flo
     } else if constexpr (EPI == Epi::SwiGlu) {
         const float s = a0 / (1.0f + expf(-a0));
         p.y[item] = __float2bfloat16_rn(s * a1);
+    } else if constexpr (EPI == Epi::Peers) {
+#pragma unroll
+        for (int r = 0; r < kMaxPeers; ++r)
+            if (r < p.n_peers) *reinterpret_cast<float2*>(p.peer_out[r] + item * 2) = make_float2(a0, a1);
     } else if constexpr (EPI == Epi::Logits) {
         *reinterpret_cast<float2*>(p.logits + item * 2) = make_float2(a0, a1);
         if (a0 > best_v) { best_v = a0; best_i = item * 2; }          // ascending ids: strict > keeps
@@ -228,6 +257,19 @@ __device__ __forceinline__ void gemv_run(const GemvParams& p, const GemvSched& s
             from_table = true;
         }
         float* xf32 = reinterpret_cast<float*>(smem + 2 * xbytes + (2 * kGemvWarps * 2 + 16) * sizeof(float));   // [K]
+        if (p.addend_parts != nullptr) {
+            // every rank's partial of the previous row-parallel linear must have landed in the local buffer: its
+            // flag carries the exchange count, ours was bumped by the producing kernel of this GPU
+            if (tid < p.n_parts) {
+                const unsigned int want = __ldcg(p.epoch);
+                int spins = 0;
+                while ((int)(ld_acquire_sys(p.wait_flags + tid) - want) < 0) {
+                    if (++spins > kPeerSpinLimit) { if (p.error != nullptr) atomicExch(p.error, 3); break; }
+                    if ((spins & 63) == 0) __nanosleep(64);
+                }
+            }
+            __syncthreads();
+        }
         float ss = 0.f;
         for (int c = tid; c < nch; c += kGemvThreads) {
             float f[8];
@@ -243,11 +285,22 @@ __device__ __forceinline__ void gemv_run(const GemvParams& p, const GemvSched& s
                 const float4 a1 = __ldcg(reinterpret_cast<const float4*>(p.addend + (size_t)c * 8 + 4));
                 f[0] += a0.x; f[1] += a0.y; f[2] += a0.z; f[3] += a0.w; f[4] += a1.x; f[5] += a1.y; f[6] += a1.z; f[7] += a1.w;
             }
+            if (p.addend_parts != nullptr) {       // (p0 + p1 + ...) + x: the partials first, in rank order, as an all-reduce would
+                float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                for (int r = 0; r < p.n_parts; ++r) {
+                    const float* part = p.addend_parts + (size_t)r * p.K + (size_t)c * 8;
+                    const float4 a0 = __ldcg(reinterpret_cast<const float4*>(part));
+                    const float4 a1 = __ldcg(reinterpret_cast<const float4*>(part + 4));
+                    a[0] += a0.x; a[1] += a0.y; a[2] += a0.z; a[3] += a0.w; a[4] += a1.x; a[5] += a1.y; a[6] += a1.z; a[7] += a1.w;
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) f[j] += a[j];
+            }
 #pragma unroll
             for (int j = 0; j < 8; ++j) ss = fmaf(f[j], f[j], ss);
             reinterpret_cast<float4*>(xf32)[2 * c] = make_float4(f[0], f[1], f[2], f[3]);
             reinterpret_cast<float4*>(xf32)[2 * c + 1] = make_float4(f[4], f[5], f[6], f[7]);
-            if ((from_table || p.addend != nullptr) && blockIdx.x == 0) {
+            if ((from_table || p.addend != nullptr || p.addend_parts != nullptr) && blockIdx.x == 0) {
                 reinterpret_cast<float4*>(p.resid_out)[2 * c] = make_float4(f[0], f[1], f[2], f[3]);
                 reinterpret_cast<float4*>(p.resid_out)[2 * c + 1] = make_float4(f[4], f[5], f[6], f[7]);
             }
@@ -359,6 +412,22 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
     pdl_wait();
     gemv_run<EPI>(p, sc, regs, gemv_smem, xbytes, best_v, best_i);
     if constexpr (EPI == Epi::Logits) gemv_publish_best(p, best_v, best_i, bv, bi);
+    if constexpr (EPI == Epi::Peers) {
+        // all of this block's remote stores are ordered before its ticket; the block that draws the last ticket
+        // therefore publishes after every store of the grid
+        __threadfence_system();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const unsigned int t = atomicAdd(p.ticket, 1u);
+            if (t == gridDim.x - 1) {
+                *p.ticket = 0u;
+                const unsigned int e = *p.epoch + 1u;
+                *p.epoch = e;
+                __threadfence_system();
+                for (int r = 0; r < p.n_peers; ++r) st_release_sys(p.peer_flag[r], e);
+            }
+        }
+    }
 }
 
 inline size_t gemv_smem_bytes(int K) {      // xs | norm weight | red + misc | fp32 staging of the residual row

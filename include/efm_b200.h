@@ -98,6 +98,16 @@ EFM_API const char* efm_b200_version(void);
 EFM_API efm_status efm_b200_tp_unique_id(void* out128);
 EFM_API efm_status efm_b200_tp_init(efm_b200_ctx* ctx, const void* id128);
 
+/* Optional: fuse the two all-reduces per layer of the DECODE step into the GEMV kernels.  Every rank exports a
+ * 64-byte handle of its exchange buffer (CUDA IPC), the host gathers the tp_size handles in rank order and
+ * hands the whole array to every rank.  After import — and a host-side barrier across the ranks, so that
+ * nobody decodes before everybody imported — each row-parallel GEMV stores its fp32 partial straight into
+ * every peer's buffer over NVLink and publishes a step counter; the next kernel's prologue waits (bounded,
+ * EFM_ERR_DEVICE_WAIT on expiry) for all counters and adds the partials in rank order.  Without these two calls
+ * the decode step uses ncclAllReduce.  Prefill and the logits all-gather stay on NCCL either way. */
+EFM_API efm_status efm_b200_tp_peer_export(efm_b200_ctx* ctx, void* handle64);
+EFM_API efm_status efm_b200_tp_peer_import(efm_b200_ctx* ctx, const void* handles, int32_t n_handles);
+
 /* ---- weights --------------------------------------------------------------------------- */
 /* Replaces WeightLoader::load_weights_from_file + per-layer load_weights
  * (src/utils/device/weight_loader.cpp:80-171, src/layers/linear.cu:1691-1717,1926-1943).

@@ -49,6 +49,8 @@ SIGNATURES = {
     "efm_b200_version": (C.c_char_p, []),
     "efm_b200_tp_unique_id": (I32, [P]),
     "efm_b200_tp_init": (I32, [P, P]),
+    "efm_b200_tp_peer_export": (I32, [P, P]),
+    "efm_b200_tp_peer_import": (I32, [P, P, I32]),
     "efm_b200_set_weight": (I32, [P, C.c_char_p, P, C.POINTER(C.c_int64), I32, I32, I32]),
     "efm_b200_finalize_weights": (I32, [P]),
     "efm_b200_alloc_kv_slot": (I32, [P, I32, I32]),
@@ -146,6 +148,16 @@ class Backend:
     def tp_init(self, id_bytes):
         buf = C.create_string_buffer(bytes(id_bytes), 128)
         self.check(self.L.efm_b200_tp_init(self.ctx, buf), "tp_init")
+
+    def tp_peer_export(self):
+        buf = C.create_string_buffer(64)
+        self.check(self.L.efm_b200_tp_peer_export(self.ctx, buf), "tp_peer_export")
+        return bytes(buf.raw)
+
+    def tp_peer_import(self, handles):
+        """handles: list of the 64-byte exports of all ranks, in rank order."""
+        blob = C.create_string_buffer(b"".join(handles), 64 * len(handles))
+        self.check(self.L.efm_b200_tp_peer_import(self.ctx, blob, len(handles)), "tp_peer_import")
 
     def load_weights(self, weights):
         """weights: dict name -> torch bf16 tensor (CPU or CUDA)."""

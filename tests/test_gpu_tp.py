@@ -49,12 +49,13 @@ CASES = [
 
 
 @pytest.mark.parametrize("world,kw", CASES)
-@pytest.mark.parametrize("use_graph", [True, False])
-def test_tensor_parallel_generate(tmp_path, world, kw, use_graph):
+@pytest.mark.parametrize("use_graph,fused", [(True, False), (False, False), (True, True), (False, True)])
+def test_tensor_parallel_generate(tmp_path, world, kw, use_graph, fused):
+    """fused: the decode step's all-reduces run inside the GEMV kernels over peer memory instead of NCCL."""
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     steps, n_prompt, seed = 12, 21, 3
-    run_ranks(tp_worker.gpu_rank, world, (world, free_port(), kw, seed, n_prompt, steps, str(tmp_path), use_graph))
+    run_ranks(tp_worker.gpu_rank, world, (world, free_port(), kw, seed, n_prompt, steps, str(tmp_path), use_graph, fused))
     cfg = synth.tiny_config(**kw)
     w = synth.make_weights(cfg, seed=seed)
     prompt = synth.make_token_ids(n_prompt, seed=seed, vocab=cfg.vocab)

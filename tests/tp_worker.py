@@ -34,7 +34,7 @@ def cpu_rank(rank, world, port, cfg_kw, seed, n_prompt, steps, out_dir):
     dist.destroy_process_group()
 
 
-def gpu_rank(rank, world, port, cfg_kw, seed, n_prompt, steps, out_dir, use_graph):
+def gpu_rank(rank, world, port, cfg_kw, seed, n_prompt, steps, out_dir, use_graph, fused=False):
     """One GPU per rank: the CUDA backend with tp_size = world, NCCL between the ranks."""
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     import cabi
@@ -50,6 +50,11 @@ def gpu_rank(rank, world, port, cfg_kw, seed, n_prompt, steps, out_dir, use_grap
     be.load_weights(w)
     be.alloc_slot(0, 256)
     be.set_sampling(0.0, 1.0, 0)
+    if fused:        # decode all-reduces inside the GEMVs over peer memory: exchange the IPC handles, then a barrier
+        handles = [None] * world
+        dist.all_gather_object(handles, be.tp_peer_export())
+        be.tp_peer_import(handles)
+        dist.barrier()
     pos3 = None
     if cfg.mrope_section is not None:
         pos3 = [list(range(n_prompt))] * 3

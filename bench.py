@@ -337,6 +337,12 @@ def run_tp(args, rank, world, local_rank):
     dec_steps = args.steps * (gen_tokens - 1)
     step_ms = dec_ms / dec_steps
     step_bytes = be.decode_step_bytes(len(ids) + gen_tokens // 2)          # this rank's share
+    breakdown = None
+    if world == 1 or fused:      # per-kernel device time of a few un-overlapped steps (every rank takes part)
+        be.decode_begin(0, len(ids), mp, 1)
+        bd = be.decode_breakdown(4)
+        Lc = synth.CONFIGS[args.config].num_layers
+        breakdown = {k: round(v / (4 * (Lc if k not in ("lm_head", "sampler") else 1)) * 1e3, 2) for k, v in bd.items()}
     peak, peak_kind = peaks()
     achieved = step_bytes / (step_ms * 1e-3) / 1e9
     if rank == 0:
@@ -365,6 +371,8 @@ def run_tp(args, rank, world, local_rank):
                              "traffic": None, "peak_kind": peak_kind, "launch": "one decode step on one rank",
                              "bytes_per_launch": step_bytes, "us_per_launch": step_ms * 1e3},
                 "tokens_head": tokens[:8]}
+        if breakdown is not None:
+            line["roofline"]["kernel_us_unoverlapped"] = breakdown
         print(json.dumps(line), flush=True)
     enc.close()
     be.close()

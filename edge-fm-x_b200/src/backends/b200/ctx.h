@@ -60,8 +60,8 @@ struct efm_b200_ctx {
     int vocab_l = 0, vocab_off = 0;       // lm_head rows of this rank
     void* nccl_comm = nullptr;
     // Peer exchange of the decode step (row-parallel GEMV fused with its all-reduce): one allocation per rank,
-    // [flags: 2 x 8 u32 | epoch | ticket | pad to 256 B | receive buffer: 2 x tp x H fp32], mapped into every
-    // other rank with CUDA IPC.  peer_base[r] is rank r's allocation as seen from here (own: tp_xchg).
+    // [exchange count at byte 64 | block ticket at 68 | receive buffer at 256: 2 x tp x H words {fp32, count}],
+    // mapped into every other rank with CUDA IPC.  peer_base[r] is rank r's allocation as seen from here.
     char* tp_xchg = nullptr;
     char* peer_base[8] = {};
     bool peers_ready = false;

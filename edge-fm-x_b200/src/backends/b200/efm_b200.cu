@@ -177,7 +177,7 @@ efm_status efm_b200_create(const efm_model_desc* desc, int32_t device_id, int32_
         EFM_TRY(dev_alloc(c, &c->ybuf, S * H));
         EFM_TRY(dev_alloc(c, &c->ysum, S * H));
         EFM_TRY(dev_alloc(c, &c->logits_l, (size_t)c->vocab_l));
-        EFM_TRY(dev_alloc(c, &c->tp_xchg, 256 + (size_t)2 * tp_size * H * sizeof(float)));     // zeroed: flags, epoch, ticket
+        EFM_TRY(dev_alloc(c, &c->tp_xchg, 256 + (size_t)2 * tp_size * H * 8));     // zeroed: count, ticket, {value, count} words
     }
     EFM_TRY(dev_alloc(c, &c->final_norm, H));
     c->layers.resize(d.num_layers);

@@ -138,20 +138,17 @@ static void tp_all_gather(efm_b200_ctx& c, Launcher& L, const float* send, float
     else if (L.counter != nullptr) ++*L.counter;
 }
 
-// Exchange buffer layout (ctx.h): flags [2][8] u32 at 0, epoch at 64, ticket at 68, receive buffer [2][tp][H] fp32 at 256.
+// Exchange buffer layout (ctx.h): count at byte 64, ticket at 68, receive buffer [2][tp][H] of {fp32, count} at 256.
 static void peers_producer(const efm_b200_ctx& c, GemvParams& p, int parity) {
     const size_t H = (size_t)c.d.hidden;
     p.n_peers = c.tp_size;
-    for (int r = 0; r < c.tp_size; ++r) {
-        p.peer_out[r] = reinterpret_cast<float*>(c.peer_base[r] + 256) + ((size_t)parity * c.tp_size + c.tp_rank) * H;
-        p.peer_flag[r] = reinterpret_cast<unsigned int*>(c.peer_base[r]) + parity * 8 + c.tp_rank;
-    }
+    for (int r = 0; r < c.tp_size; ++r)
+        p.peer_out[r] = reinterpret_cast<uint2*>(c.peer_base[r] + 256) + ((size_t)parity * c.tp_size + c.tp_rank) * H;
     p.epoch = reinterpret_cast<unsigned int*>(c.tp_xchg + 64);
     p.ticket = reinterpret_cast<unsigned int*>(c.tp_xchg + 68);
 }
 static void peers_consumer(const efm_b200_ctx& c, GemvParams& p, int parity) {
-    p.addend_parts = reinterpret_cast<const float*>(c.tp_xchg + 256) + (size_t)parity * c.tp_size * c.d.hidden;
-    p.wait_flags = reinterpret_cast<const unsigned int*>(c.tp_xchg) + parity * 8;
+    p.addend_parts = reinterpret_cast<const uint2*>(c.tp_xchg + 256) + (size_t)parity * c.tp_size * c.d.hidden;
     p.n_parts = c.tp_size;
     p.epoch = reinterpret_cast<unsigned int*>(c.tp_xchg + 64);
     p.error = &c.state->error;

@@ -60,29 +60,26 @@ struct GemvParams {
     float* logits;            // Logits
     float* part_val;
     int* part_idx;
-    // Peers (tensor parallel, row-parallel linear fused with its exchange): every output pair is stored into
-    // this rank's row of EVERY rank's receive buffer (peer memory over NVLink, own buffer included); the last
-    // block to finish bumps the local epoch and publishes it in this rank's flag word on every rank.
-    float* peer_out[kMaxPeers];
-    unsigned int* peer_flag[kMaxPeers];
+    // Peers (tensor parallel, row-parallel linear fused with its exchange): every output value travels as one
+    // 8-byte word {fp32 value, exchange count} stored into this rank's row of EVERY rank's receive buffer (peer
+    // memory over NVLink, own buffer included).  Value and count arrive together, so there is no fence and no
+    // separate flag; the last block to finish bumps the local count (local atomics only).
+    uint2* peer_out[kMaxPeers];
     int n_peers;
     unsigned int* epoch;      // local: number of exchanges completed by this rank
     unsigned int* ticket;     // local: block ticket, zero between launches
-    // consumer side (norm prologues): wait until every rank's flag reached the local epoch, then
-    // x = x + sum over ranks, in rank order, of parts[r][:]
-    const float* addend_parts;            // local receive buffer [n_parts][K]
-    const unsigned int* wait_flags;       // local flags [n_parts]
+    // consumer side (norm prologues): x = x + sum over ranks, in rank order, of parts[r][:], every word being
+    // re-read (bounded) until it carries the local count
+    const uint2* addend_parts;            // local receive buffer [n_parts][K] of {value, count}
     int n_parts;
     int* error;               // raised (3) when a wait gives up
 };
 
-__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
-    unsigned int v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+// 16 bytes = two {value, count} words, read past every cache that a peer's store does not update
+__device__ __forceinline__ uint4 ld_peer_words(const uint2* p) {
+    uint4 v;
+    asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
     return v;
-}
-__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
 __device__ __forceinline__ void group_barrier(int id, int nthreads) {
@@ -120,9 +117,11 @@ __device__ __forceinline__ void item_epilogue(const GemvParams& p, int item, flo
         const float s = a0 / (1.0f + expf(-a0));
         p.y[item] = __float2bfloat16_rn(s * a1);
     } else if constexpr (EPI == Epi::Peers) {
+        const unsigned int e = (unsigned int)best_i;           // exchange count of this launch (see gemv_kernel)
+        const uint4 w = make_uint4(__float_as_uint(a0), e, __float_as_uint(a1), e);
 #pragma unroll
         for (int r = 0; r < kMaxPeers; ++r)
-            if (r < p.n_peers) *reinterpret_cast<float2*>(p.peer_out[r] + item * 2) = make_float2(a0, a1);
+            if (r < p.n_peers) *reinterpret_cast<uint4*>(p.peer_out[r] + item * 2) = w;
     } else if constexpr (EPI == Epi::Logits) {
         *reinterpret_cast<float2*>(p.logits + item * 2) = make_float2(a0, a1);
         if (a0 > best_v) { best_v = a0; best_i = item * 2; }          // ascending ids: strict > keeps
@@ -257,19 +256,7 @@ __device__ __forceinline__ void gemv_run(const GemvParams& p, const GemvSched& s
             from_table = true;
         }
         float* xf32 = reinterpret_cast<float*>(smem + 2 * xbytes + (2 * kGemvWarps * 2 + 16) * sizeof(float));   // [K]
-        if (p.addend_parts != nullptr) {
-            // every rank's partial of the previous row-parallel linear must have landed in the local buffer: its
-            // flag carries the exchange count, ours was bumped by the producing kernel of this GPU
-            if (tid < p.n_parts) {
-                const unsigned int want = __ldcg(p.epoch);
-                int spins = 0;
-                while ((int)(ld_acquire_sys(p.wait_flags + tid) - want) < 0) {
-                    if (++spins > kPeerSpinLimit) { if (p.error != nullptr) atomicExch(p.error, 3); break; }
-                    if ((spins & 63) == 0) __nanosleep(64);
-                }
-            }
-            __syncthreads();
-        }
+        const unsigned int want = p.addend_parts != nullptr ? __ldcg(p.epoch) : 0u;   // bumped by this GPU's producing kernel
         float ss = 0.f;
         for (int c = tid; c < nch; c += kGemvThreads) {
             float f[8];
@@ -288,10 +275,21 @@ __device__ __forceinline__ void gemv_run(const GemvParams& p, const GemvSched& s
             if (p.addend_parts != nullptr) {       // (p0 + p1 + ...) + x: the partials first, in rank order, as an all-reduce would
                 float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
                 for (int r = 0; r < p.n_parts; ++r) {
-                    const float* part = p.addend_parts + (size_t)r * p.K + (size_t)c * 8;
-                    const float4 a0 = __ldcg(reinterpret_cast<const float4*>(part));
-                    const float4 a1 = __ldcg(reinterpret_cast<const float4*>(part + 4));
-                    a[0] += a0.x; a[1] += a0.y; a[2] += a0.z; a[3] += a0.w; a[4] += a1.x; a[5] += a1.y; a[6] += a1.z; a[7] += a1.w;
+                    const uint2* part = p.addend_parts + (size_t)r * p.K + (size_t)c * 8;
+                    uint4 w[4];
+                    int spins = 0;
+                    for (;;) {                     // until all eight words carry this exchange's count
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) w[j] = ld_peer_words(part + 2 * j);
+                        bool ok = true;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) ok = ok && w[j].y == want && w[j].w == want;
+                        if (ok) break;
+                        if (++spins > kPeerSpinLimit) { if (p.error != nullptr) atomicExch(p.error, 3); break; }
+                        if ((spins & 15) == 0) __nanosleep(32);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) { a[2 * j] += __uint_as_float(w[j].x); a[2 * j + 1] += __uint_as_float(w[j].z); }
                 }
 #pragma unroll
                 for (int j = 0; j < 8; ++j) f[j] += a[j];
@@ -410,21 +408,17 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
     const GemvSched sc = gemv_sched(p, ks, blockIdx.x, gridDim.x);
     gemv_prefetch<EPI>(p, sc, regs, gemv_smem, xbytes);
     pdl_wait();
+    if constexpr (EPI == Epi::Peers) best_i = (int)(__ldcg(p.epoch) + 1u);      // this launch's exchange count rides in best_i
     gemv_run<EPI>(p, sc, regs, gemv_smem, xbytes, best_v, best_i);
     if constexpr (EPI == Epi::Logits) gemv_publish_best(p, best_v, best_i, bv, bi);
     if constexpr (EPI == Epi::Peers) {
-        // all of this block's remote stores are ordered before its ticket; the block that draws the last ticket
-        // therefore publishes after every store of the grid
-        __threadfence_system();
+        // every block has read the count by now; the one that draws the last ticket advances it for the consumer
         __syncthreads();
         if (threadIdx.x == 0) {
             const unsigned int t = atomicAdd(p.ticket, 1u);
             if (t == gridDim.x - 1) {
                 *p.ticket = 0u;
-                const unsigned int e = *p.epoch + 1u;
-                *p.epoch = e;
-                __threadfence_system();
-                for (int r = 0; r < p.n_peers; ++r) st_release_sys(p.peer_flag[r], e);
+                *p.epoch = (unsigned int)best_i;
             }
         }
     }

@@ -102,8 +102,9 @@ EFM_API efm_status efm_b200_tp_init(efm_b200_ctx* ctx, const void* id128);
  * 64-byte handle of its exchange buffer (CUDA IPC), the host gathers the tp_size handles in rank order and
  * hands the whole array to every rank.  After import — and a host-side barrier across the ranks, so that
  * nobody decodes before everybody imported — each row-parallel GEMV stores its fp32 partial straight into
- * every peer's buffer over NVLink and publishes a step counter; the next kernel's prologue waits (bounded,
- * EFM_ERR_DEVICE_WAIT on expiry) for all counters and adds the partials in rank order.  Without these two calls
+ * every peer's buffer over NVLink as 8-byte {value, exchange count} words; the next kernel's prologue re-reads
+ * (bounded, EFM_ERR_DEVICE_WAIT on expiry) until every word carries the current count and adds the partials in
+ * rank order.  Without these two calls
  * the decode step uses ncclAllReduce.  Prefill and the logits all-gather stay on NCCL either way. */
 EFM_API efm_status efm_b200_tp_peer_export(efm_b200_ctx* ctx, void* handle64);
 EFM_API efm_status efm_b200_tp_peer_import(efm_b200_ctx* ctx, const void* handles, int32_t n_handles);

@@ -17,6 +17,10 @@ struct NcclApi {
     int (*comm_destroy)(void* comm) = nullptr;
     int (*all_reduce_f32_sum)(const void* send, void* recv, size_t count, void* comm, cudaStream_t stream) = nullptr;
     int (*all_gather_f32)(const void* send, void* recv, size_t count, void* comm, cudaStream_t stream) = nullptr;
+    // all-gather with a different byte count per rank: rank r's `send` (counts[r] bytes) lands at recv_base +
+    // offsets[r] on every rank (grouped ncclBroadcast calls)
+    int (*all_gather_v_bytes)(const void* send, void* recv_base, const size_t* offsets, const size_t* counts, int nranks,
+                              void* comm, cudaStream_t stream) = nullptr;
     const char* (*error_string)(int) = nullptr;
 };
 

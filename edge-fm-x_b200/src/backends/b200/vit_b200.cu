@@ -21,6 +21,7 @@
 #include "../../operators/gemm_tc.cuh"
 #include "../../operators/vit.cuh"
 #include "ctx.h"
+#include "nccl_glue.h"
 
 using namespace efm;
 
@@ -55,6 +56,8 @@ struct efm_b200_vit {
     float *pe = nullptr, *resid = nullptr;
     float2* rope_tab = nullptr;          // [N, D/2] (cos, sin)
     int32_t* plan = nullptr;             // order [N/unit] | pos_h | pos_w | lo_win | hi_win | lo_full | hi_full, [N] each
+    __nv_bfloat16* qkv_all = nullptr;    // tensor parallel: q|k|v rows of every rank, full-attention layers [N, 3H]
+    __nv_bfloat16* mo_all = nullptr;     // tensor parallel: merged tokens of every rank [N/unit, out]
     std::vector<void*> allocations;
 };
 
@@ -342,15 +345,46 @@ efm_status efm_b200_vit_encode(efm_b200_vit* v, const void* pixels, int32_t pixe
     if (N > d.max_patches) return vfail(v, EFM_ERR_INVALID_ARGUMENT, "more patches than max_patches");
     VIT_CK(v, cudaSetDevice(c->device));
     cudaStream_t st = c->stream;
+    const int H = d.hidden, D = v->head_dim, Ip = v->ipad;
 
-    // plan and pixels to the device
+    // Tensor parallel: the permuted rows are cut at window boundaries into one contiguous share per rank.  The
+    // windowed layers then run on the local rows alone; the full-attention layers all-gather the q|k|v rows, and
+    // the merged tokens are all-gathered once at the end (every rank ends with the whole output).
+    int tp = c->tp_size > 1 && c->nccl_comm != nullptr && std::getenv("EFM_B200_VIT_REPLICATED") == nullptr ? c->tp_size : 1;
+    std::vector<int> cut(1, 0);
+    if (tp > 1) {
+        std::vector<int> bounds;                                   // first row of every window, then N
+        for (int i = 0; i < N; ++i)
+            if (P.lo_win[i] == i) bounds.push_back(i);
+        bounds.push_back(N);
+        if ((int)bounds.size() - 1 < tp) tp = 1;                   // fewer windows than ranks: everybody encodes everything
+        for (int r = 1; r < tp; ++r) {                             // the window boundary nearest to an even split
+            const long long target = (long long)N * r / tp;
+            int best = cut.back();
+            for (int bnd : bounds)
+                if (bnd >= cut.back() && std::llabs(bnd - target) < std::llabs(best - target)) best = bnd;
+            cut.push_back(best);
+        }
+    }
+    cut.push_back(N);
+    const int rank = tp > 1 ? c->tp_rank : 0;
+    const int r0 = cut[rank], n = cut[rank + 1] - r0, nm = n / v->unit;       // this rank's rows
+    if (tp > 1 && v->qkv_all == nullptr) {
+        VIT_CK(v, valloc(v, &v->qkv_all, (size_t)d.max_patches * 3 * H));
+        VIT_CK(v, valloc(v, &v->mo_all, (size_t)(d.max_patches / v->unit) * d.out_hidden));
+    }
+
+    // plan and pixels to the device; the windowed ranges are made relative to the local rows
+    std::vector<int32_t> lw(P.lo_win.begin() + r0, P.lo_win.begin() + r0 + n), hw(P.hi_win.begin() + r0, P.hi_win.begin() + r0 + n);
+    for (int i = 0; i < n; ++i) { lw[i] -= r0; hw[i] -= r0; }
     int32_t* order = v->plan;
     int32_t* pos_h = order + NM;
     int32_t *pos_w = pos_h + N, *lo_win = pos_w + N, *hi_win = lo_win + N, *lo_full = hi_win + N, *hi_full = lo_full + N;
-    const std::vector<int32_t>* host[7] = {&P.order, &P.pos_h, &P.pos_w, &P.lo_win, &P.hi_win, &P.lo_full, &P.hi_full};
+    const std::vector<int32_t>* host[7] = {&P.order, &P.pos_h, &P.pos_w, &lw, &hw, &P.lo_full, &P.hi_full};
     int32_t* dev[7] = {order, pos_h, pos_w, lo_win, hi_win, lo_full, hi_full};
     for (int i = 0; i < 7; ++i)
-        VIT_CK(v, cudaMemcpyAsync(dev[i], host[i]->data(), host[i]->size() * 4, cudaMemcpyHostToDevice, st));
+        if (!host[i]->empty())
+            VIT_CK(v, cudaMemcpyAsync(dev[i], host[i]->data(), host[i]->size() * 4, cudaMemcpyHostToDevice, st));
     const __nv_bfloat16* px = static_cast<const __nv_bfloat16*>(pixels);
     if (pixels_mem == EFM_MEM_HOST) {
         VIT_CK(v, cudaMemcpyAsync(v->pixels, pixels, (size_t)N * v->patch_dim * 2, cudaMemcpyHostToDevice, st));
@@ -368,58 +402,77 @@ efm_status efm_b200_vit_encode(efm_b200_vit* v, const void* pixels, int32_t pixe
     L.gemm_ws_floats = c->gemm_ws_floats;
     L.num_sms = c->num_sms;
     int* err = &c->state->error;
-    const int H = d.hidden, D = v->head_dim, Ip = v->ipad;
-    auto norm_rows = [&](const __nv_bfloat16* w) { launch_rmsnorm_rows(L, v->resid, w, v->xn, N, H, d.rms_eps); };
+    auto norm_rows = [&](const __nv_bfloat16* w) { if (n > 0) launch_rmsnorm_rows(L, v->resid, w, v->xn, n, H, d.rms_eps); };
+    auto gather_v = [&](const void* send, void* recv, size_t row_bytes, int per) {      // rows cut[r]/per .. cut[r+1]/per of every rank
+        size_t off[8], cnt[8];
+        for (int r = 0; r < tp; ++r) { off[r] = (size_t)(cut[r] / per) * row_bytes; cnt[r] = (size_t)((cut[r + 1] - cut[r]) / per) * row_bytes; }
+        if (L.err != cudaSuccess) return;
+        const NcclApi& api = nccl_api();
+        if (!api.ok || api.all_gather_v_bytes(send, recv, off, cnt, tp, c->nccl_comm, st) != 0) L.err = cudaErrorUnknown;
+        else ++c->launches;
+    };
 
-    {   // patch embedding, then window-major order
+    {   // patch embedding (all rows: 1 % of the flops), then this rank's rows in window-major order
         GemmParams g{px, v->patch_w, nullptr, nullptr, v->pe, N, H, v->patch_dim};
         launch_gemm_epi(L, GemmEpi::F32, g, err);
-        L.launch(vit_gather_blocks_f32_kernel, dim3(std::min(NM, c->num_sms * 8)), dim3(256), 0, (const float*)v->pe, v->resid,
-                 (const int32_t*)order, NM, v->unit, H);
+        if (nm > 0)
+            L.launch(vit_gather_blocks_f32_kernel, dim3(std::min(nm, c->num_sms * 8)), dim3(256), 0, (const float*)v->pe, v->resid,
+                     (const int32_t*)(order + r0 / v->unit), nm, v->unit, H);
     }
-    L.launch(vit_rope_table_kernel, dim3((N * (D / 2) + 127) / 128), dim3(128), 0, v->rope_tab, (const int32_t*)pos_h,
-             (const int32_t*)pos_w, N, D, d.rope_theta);
+    if (n > 0)
+        L.launch(vit_rope_table_kernel, dim3((n * (D / 2) + 127) / 128), dim3(128), 0, v->rope_tab, (const int32_t*)(pos_h + r0),
+                 (const int32_t*)(pos_w + r0), n, D, d.rope_theta);
     for (int l = 0; l < d.depth; ++l) {
         const VitBlock& b = v->blocks[l];
         bool full = false;
         for (int i = 0; i < d.n_fullatt; ++i) full = full || d.fullatt[i] == l;
         norm_rows(b.norm1);
-        {
-            GemmParams g{v->xn, b.qkv_w, b.qkv_b, v->qkv, nullptr, N, 3 * H, H};
+        if (n > 0) {
+            GemmParams g{v->xn, b.qkv_w, b.qkv_b, v->qkv, nullptr, n, 3 * H, H};
             launch_gemm_epi(L, GemmEpi::Bf16Bias, g, err);
+            L.launch(vit_rope2d_kernel, dim3(n), dim3(256), 0, v->qkv, (const float2*)v->rope_tab, d.heads, D);
         }
-        L.launch(vit_rope2d_kernel, dim3(N), dim3(256), 0, v->qkv, (const float2*)v->rope_tab, d.heads, D);
-        {
+        const __nv_bfloat16* kv_rows = v->qkv;
+        if (full && tp > 1) {
+            gather_v(v->qkv, v->qkv_all, (size_t)3 * H * 2, 1);
+            kv_rows = v->qkv_all;
+        }
+        if (n > 0) {
             SegAttnParams a{};
-            a.q = v->qkv; a.k = v->qkv + H; a.v = v->qkv + 2 * H; a.out = v->attn;
-            a.lo = full ? lo_full : lo_win; a.hi = full ? hi_full : hi_win;
+            a.q = v->qkv; a.k = kv_rows + H; a.v = kv_rows + 2 * H; a.out = v->attn;
+            // windowed ranges are relative to the local rows; full ranges index the gathered (global) rows
+            a.lo = full ? lo_full + (tp > 1 ? r0 : 0) : lo_win;
+            a.hi = full ? hi_full + (tp > 1 ? r0 : 0) : hi_win;
             a.q_stride = a.kv_stride = 3 * H; a.out_stride = H;
-            a.S = N; a.kv_offset = 0; a.q_heads = a.kv_heads = d.heads;
+            a.S = n; a.kv_offset = 0; a.q_heads = a.kv_heads = d.heads;
             a.scale = 1.0f / sqrtf((float)D);
             launch_seg_attention(L, a, D);
-        }
-        {
-            GemmParams g{v->attn, b.proj_w, b.proj_b, nullptr, v->resid, N, H, H};
+            GemmParams g{v->attn, b.proj_w, b.proj_b, nullptr, v->resid, n, H, H};
             launch_gemm_epi(L, GemmEpi::Residual, g, err);
         }
         norm_rows(b.norm2);
-        {
-            GemmParams g{v->xn, b.gate_up_w, b.gate_up_b, v->act, nullptr, N, 2 * Ip, H};
+        if (n > 0) {
+            GemmParams g{v->xn, b.gate_up_w, b.gate_up_b, v->act, nullptr, n, 2 * Ip, H};
             launch_gemm_epi(L, GemmEpi::SwiGlu, g, err);
-        }
-        {
-            GemmParams g{v->act, b.down_w, b.down_b, nullptr, v->resid, N, H, Ip};
-            launch_gemm_epi(L, GemmEpi::Residual, g, err);
+            GemmParams g2{v->act, b.down_w, b.down_b, nullptr, v->resid, n, H, Ip};
+            launch_gemm_epi(L, GemmEpi::Residual, g2, err);
         }
     }
     {   // merger: norm, 4 rows -> one, MLP with exact GELU, back to the original token order
         norm_rows(v->ln_q);
-        GemmParams g0{v->xn, v->m0_w, v->m0_b, v->h1, nullptr, NM, v->merged, v->merged};
-        launch_gemm_epi(L, GemmEpi::Bf16Gelu, g0, err);
-        GemmParams g1{v->h1, v->m2_w, v->m2_b, v->mo, nullptr, NM, d.out_hidden, v->merged};
-        launch_gemm_epi(L, GemmEpi::Bf16Bias, g1, err);
+        if (nm > 0) {
+            GemmParams g0{v->xn, v->m0_w, v->m0_b, v->h1, nullptr, nm, v->merged, v->merged};
+            launch_gemm_epi(L, GemmEpi::Bf16Gelu, g0, err);
+            GemmParams g1{v->h1, v->m2_w, v->m2_b, v->mo, nullptr, nm, d.out_hidden, v->merged};
+            launch_gemm_epi(L, GemmEpi::Bf16Bias, g1, err);
+        }
+        const __nv_bfloat16* merged = v->mo;
+        if (tp > 1) {
+            gather_v(v->mo, v->mo_all, (size_t)d.out_hidden * 2, v->unit);
+            merged = v->mo_all;
+        }
         __nv_bfloat16* dst = out_mem == EFM_MEM_DEVICE ? static_cast<__nv_bfloat16*>(out) : v->out_dev;
-        L.launch(vit_scatter_rows_bf16_kernel, dim3(std::min(NM, c->num_sms * 8)), dim3(128), 0, (const __nv_bfloat16*)v->mo, dst,
+        L.launch(vit_scatter_rows_bf16_kernel, dim3(std::min(NM, c->num_sms * 8)), dim3(128), 0, merged, dst,
                  (const int32_t*)order, NM, d.out_hidden);
     }
     if (L.err != cudaSuccess) return vfail(v, EFM_ERR_CUDA, std::string("vision encoder launch: ") + cudaGetErrorString(L.err));

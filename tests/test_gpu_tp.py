@@ -84,3 +84,25 @@ def test_tensor_parallel_generate(tmp_path, world, kw, use_graph, fused):
     for s in range(steps):
         assert np.abs(logits[s] - l1[s]).max() / np.abs(l1[s]).max() < 1e-2
     be.close()
+
+
+@pytest.mark.parametrize("world,grids", [(2, [(1, 16, 24)]), (2, [(2, 12, 6), (1, 4, 18)]), (2, [(1, 8, 8)]), (4, [(1, 20, 28)])])
+def test_vision_encoder_windows_sharded_over_ranks(tmp_path, world, grids):
+    """Windowed layers run on each rank's own windows, full-attention layers all-gather q|k|v, the merged tokens are
+    all-gathered at the end: every rank must hold the single-GPU result.  One 8x8 grid has a single window, fewer
+    than ranks, and falls back to replication."""
+    from oracle import qwen_vit
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    vit_kw = dict(depth=4, hidden=160, heads=2, intermediate=344, out_hidden=96, fullatt=(1, 3))
+    seed = 5
+    run_ranks(tp_worker.gpu_vit_rank, world, (world, free_port(), vit_kw, grids, seed, str(tmp_path)))
+    got = [torch.load(tmp_path / f"vit_rank{r}.pt") for r in range(world)]
+    for g in got[1:]:
+        assert torch.equal(g, got[0])
+    vcfg = qwen_vit.VitConfig(**vit_kw)
+    w = qwen_vit.make_weights(vcfg, seed=seed)
+    px = qwen_vit.make_pixels(vcfg, grids, seed=seed)
+    want = qwen_vit.VitOracle(vcfg, w, "bf16_points").forward(px, grids)
+    scale = want.abs().max().item()
+    assert (got[0] - want).abs().max().item() <= 0.02 * scale

@@ -64,3 +64,31 @@ def gpu_rank(rank, world, port, cfg_kw, seed, n_prompt, steps, out_dir, use_grap
     dist.barrier()
     be.close()
     dist.destroy_process_group()
+
+
+def gpu_vit_rank(rank, world, port, vit_kw, grids, seed, out_dir):
+    """Vision encoder with its windows sharded over the tensor-parallel ranks (every rank returns the whole output)."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import cabi
+    from oracle import qwen_vit
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    cfg = synth.tiny_config(num_layers=1, hidden=256, q_heads=4, kv_heads=2, intermediate=256, vocab=1000)
+    box = [cabi.tp_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(box, src=0)
+    be = cabi.Backend(cfg, device_id=rank, tp_rank=rank, tp_size=world)
+    be.tp_init(box[0])
+    vcfg = qwen_vit.VitConfig(**vit_kw)
+    w = qwen_vit.make_weights(vcfg, seed=seed)
+    px = qwen_vit.make_pixels(vcfg, grids, seed=seed)
+    enc = cabi.VitEncoder(be, vcfg, max_patches=px.shape[0])
+    enc.load_weights(w)
+    out = torch.zeros(px.shape[0] // 4, vcfg.out_hidden, dtype=torch.bfloat16, device="cuda")
+    for _ in range(2):                      # twice: buffers and collectives are reusable
+        enc.encode(px.cuda(), grids, out)
+        be.synchronize()
+    torch.save(out.float().cpu(), os.path.join(out_dir, f"vit_rank{rank}.pt"))
+    dist.barrier()
+    enc.close()
+    be.close()
+    dist.destroy_process_group()

@@ -1,5 +1,7 @@
 #include "config.h"
 
+#include <cstdlib>
+
 #include <edge-fm/core.h>
 #include <sys/stat.h>
 
@@ -126,6 +128,19 @@ json::Value EngineConfig::prefill_model_config() const {
 std::string EngineConfig::runtime_device() const { return section("runtime").get_string("device", "cuda"); }
 int32_t EngineConfig::runtime_device_id() const { return (int32_t)section("runtime").get_int("device_id", 0); }
 bool EngineConfig::use_cuda_graph() const { return section("runtime").get_bool("use_cuda_graph", false); }
+std::string EngineConfig::tp_rendezvous() const {
+    const std::string v = section("runtime").get_string("tp_rendezvous", "");
+    if (!v.empty()) return v;
+    const char* e = std::getenv("EFM_TP_RENDEZVOUS");
+    return e != nullptr ? std::string(e) : std::string();
+}
+int32_t EngineConfig::tp_rank() const {
+    for (const char* name : {"EFM_TP_RANK", "RANK"}) {
+        const char* e = std::getenv(name);
+        if (e != nullptr && e[0] != 0) return (int32_t)std::atoi(e);
+    }
+    return 0;
+}
 std::string EngineConfig::prefill_attention() const { return section("runtime").get_string("prefill_attention", "bf16"); }
 int32_t EngineConfig::tensor_parallel() const { return (int32_t)section("runtime").get_int("tensor_parallel", 1); }
 bool EngineConfig::lm_head_top1_enabled() const {

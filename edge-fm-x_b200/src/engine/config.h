@@ -34,6 +34,8 @@ public:
     int32_t runtime_device_id() const;
     bool use_cuda_graph() const;
     int32_t tensor_parallel() const;              // runtime.tensor_parallel (new key, default 1)
+    std::string tp_rendezvous() const;            // runtime.tp_rendezvous (new key) or $EFM_TP_RENDEZVOUS: fresh shared directory
+    int32_t tp_rank() const;                      // $EFM_TP_RANK, else $RANK, else 0
     std::string prefill_attention() const;        // runtime.prefill_attention (new key): "bf16" (default) | "int8"
     bool lm_head_top1_enabled() const;            // accepted; the fused argmax is always on here
     std::string kvcache_dtype() const;

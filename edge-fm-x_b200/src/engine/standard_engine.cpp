@@ -1,5 +1,7 @@
 #include "standard_engine.h"
 
+#include "tp_rendezvous.h"
+
 #include <cuda_runtime.h>
 #include <efm_b200.h>
 
@@ -130,8 +132,19 @@ StandardEngine::StandardEngine(const EngineConfig& config) : config_(config) {
     d.max_prefill_tokens = std::min(max_tokens, 2048);
     d.max_response_tokens = config_.sampling_max_new_tokens() + 1;
 
-    if (config_.tensor_parallel() != 1) throw ConfigurationError("runtime.tensor_parallel > 1 is not available in this build");
-    efm_status st = efm_b200_create(&d, device_id_, 0, 1, &ctx_);
+    // Tensor parallel: one process per GPU, every process builds the same engine and issues the same requests.
+    // Rank from the environment, device = $LOCAL_RANK (else runtime.device_id + rank), host exchange through files.
+    const int32_t tp = config_.tensor_parallel();
+    if (tp < 1 || tp > 8) throw ConfigurationError("runtime.tensor_parallel must be between 1 and 8");
+    const int32_t tp_rank = tp > 1 ? config_.tp_rank() : 0;
+    std::unique_ptr<TpRendezvous> meet;
+    if (tp > 1) {
+        if (tp_rank < 0 || tp_rank >= tp) throw ConfigurationError("tensor parallel rank (EFM_TP_RANK / RANK) must be in [0, runtime.tensor_parallel)");
+        const char* local = std::getenv("LOCAL_RANK");
+        device_id_ = local != nullptr && local[0] != 0 ? std::atoi(local) : device_id_ + tp_rank;
+        meet.reset(new TpRendezvous(config_.tp_rendezvous(), tp_rank, tp));
+    }
+    efm_status st = efm_b200_create(&d, device_id_, tp_rank, tp, &ctx_);
     if (st != EFM_OK) {
         const std::string msg = std::string("backend creation failed: ") + efm_b200_last_error(nullptr);
         if (st == EFM_ERR_OUT_OF_MEMORY) throw OutOfMemoryError(msg);
@@ -139,6 +152,13 @@ StandardEngine::StandardEngine(const EngineConfig& config) : config_(config) {
         throw DeviceError(msg);
     }
     try {
+        if (tp > 1) {
+            std::vector<char> id(128, 0);
+            if (tp_rank == 0) check(efm_b200_tp_unique_id(id.data()), "communicator id");
+            id = meet->broadcast_from_root("nccl_id", id);
+            if (id.size() != 128) throw ConfigurationError("tensor parallel rendezvous: malformed communicator id");
+            check(efm_b200_tp_init(ctx_, id.data()), "communicator initialisation");
+        }
         for (const auto& m : maps) {
             for (const SafeTensorEntry& e : m->entries()) {
                 std::string name = e.name;
@@ -160,6 +180,18 @@ StandardEngine::StandardEngine(const EngineConfig& config) : config_(config) {
         geo.dtype = DType::BFloat16;
         kv_manager_ = std::make_shared<KVManager>(reqs, geo, attn, device_id_, std::make_shared<BackendKVAllocator>(ctx_));
         scheduler_.reset(new Scheduler(kv_manager_, config_.sampling_max_new_tokens()));
+        if (tp > 1) {      // decode all-reduces inside the GEMVs over peer memory: exchange the buffer handles, then a barrier
+            std::vector<char> mine(64, 0);
+            check(efm_b200_tp_peer_export(ctx_, mine.data()), "peer buffer export");
+            const std::vector<std::vector<char>> all = meet->all_gather("peer", mine);
+            std::vector<char> flat;
+            for (const auto& h : all) {
+                if (h.size() != 64) throw ConfigurationError("tensor parallel rendezvous: malformed peer handle");
+                flat.insert(flat.end(), h.begin(), h.end());
+            }
+            check(efm_b200_tp_peer_import(ctx_, flat.data(), tp), "peer buffer import");
+            meet->barrier("ready");
+        }
 
         efm_sampling s;
         std::memset(&s, 0, sizeof(s));

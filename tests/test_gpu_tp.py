@@ -106,3 +106,35 @@ def test_vision_encoder_windows_sharded_over_ranks(tmp_path, world, grids):
     want = qwen_vit.VitOracle(vcfg, w, "bf16_points").forward(px, grids)
     scale = want.abs().max().item()
     assert (got[0] - want).abs().max().item() <= 0.02 * scale
+
+
+def test_public_api_tensor_parallel_engine(tmp_path):
+    """runtime.tensor_parallel = 2 in the engine JSON: two processes, one GPU each, meet through a directory and
+    return the tokens of the single-GPU engine."""
+    import json
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    cfg = synth.tiny_config(num_layers=2, hidden=256, q_heads=4, kv_heads=2, intermediate=512, vocab=1500)
+    w = synth.make_weights(cfg, seed=6)
+    model_dir = synth.write_checkpoint(str(tmp_path / "model"), cfg, w)
+    prefix = synth.make_token_ids(10, seed=1, vocab=cfg.vocab)
+    prompt = prefix + synth.make_token_ids(15, seed=2, vocab=cfg.vocab)
+    path = synth.write_engine_config(str(tmp_path / "engine.json"), model_dir, prefix_ids=prefix, max_tokens=64, max_new_tokens=10)
+    ej = json.load(open(path))
+    ej["runtime"]["tensor_parallel"] = 2
+    ej["runtime"]["tp_rendezvous"] = str(tmp_path / "meet")
+    json.dump(ej, open(path, "w"))
+    run_ranks(tp_worker.gpu_engine_rank, 2, (2, path, prompt, str(tmp_path)))
+    got = [torch.load(tmp_path / f"engine_rank{r}.pt") for r in range(2)]
+    assert got[0]["tokens"] == got[1]["tokens"] == got[0]["again"] and len(got[0]["tokens"]) == 10
+    assert got[0]["metrics"]["generated_tokens_total"] == 10
+    be = cabi.Backend(cfg)
+    be.load_weights(w)
+    be.alloc_slot(0, 64)
+    be.set_sampling(0.0, 1.0, 0)
+    single, lg = cabi.generate(be, 0, prompt, 10, collect_logits=True)
+    be.close()
+    mism = [s for s in range(10) if single[s] != got[0]["tokens"][s]]
+    if mism:       # only a near-tie may part the two: compare up to the first difference, which must be a small margin
+        top2 = np.sort(lg[mism[0]])[-2:]
+        assert top2[1] - top2[0] < 2e-2 * np.abs(lg[mism[0]]).max()

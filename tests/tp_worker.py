@@ -92,3 +92,21 @@ def gpu_vit_rank(rank, world, port, vit_kw, grids, seed, out_dir):
     enc.close()
     be.close()
     dist.destroy_process_group()
+
+
+def gpu_engine_rank(rank, world, engine_json, prompt, out_dir):
+    """Public API on several GPUs: every rank builds edge_fm.EdgeFM from the same JSON (runtime.tensor_parallel = world)
+    and issues the same request; the ranks meet through the rendezvous directory named in the JSON."""
+    os.environ.update(EFM_TP_RANK=str(rank), LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0")
+    import cabi
+    if cabi.PY_DIR not in sys.path:
+        sys.path.insert(0, cabi.PY_DIR)
+    import edge_fm
+    eng = edge_fm.EdgeFM(engine_json)
+    outs = []
+    for _ in range(2):
+        req = edge_fm.Request(0, prompt)
+        req.set_ignore_stop_tokens(True)
+        outs.append(list(eng.generate(req).token_ids()))
+    torch.save({"tokens": outs[0], "again": outs[1], "metrics": dict(eng.last_generate_metrics())}, os.path.join(out_dir, f"engine_rank{rank}.pt"))
+    del eng

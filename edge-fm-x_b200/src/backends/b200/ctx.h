@@ -63,6 +63,8 @@ struct efm_b200_ctx {
     // [exchange count at byte 64 | block ticket at 68 | receive buffer at 256: 2 x tp x H words {fp32, count}],
     // mapped into every other rank with CUDA IPC.  peer_base[r] is rank r's allocation as seen from here.
     char* tp_xchg = nullptr;
+    size_t tp_prefill_off = 0;            // byte offset of the prefill slots [2][tp][max_s * H] fp32 (flags [2][8] at byte 128,
+                                          // prefill exchange count at 192, ticket at 196)
     char* peer_base[8] = {};
     bool peers_ready = false;
     float* ybuf = nullptr;                // [max_s, H] fp32 partial outputs of row-parallel linears

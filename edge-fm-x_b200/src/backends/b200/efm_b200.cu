@@ -177,7 +177,9 @@ efm_status efm_b200_create(const efm_model_desc* desc, int32_t device_id, int32_
         EFM_TRY(dev_alloc(c, &c->ybuf, S * H));
         EFM_TRY(dev_alloc(c, &c->ysum, S * H));
         EFM_TRY(dev_alloc(c, &c->logits_l, (size_t)c->vocab_l));
-        EFM_TRY(dev_alloc(c, &c->tp_xchg, 256 + (size_t)2 * tp_size * H * 8));     // zeroed: count, ticket, {value, count} words
+        // zeroed: header (counts, tickets, prefill flags) | decode {value, count} words | prefill fp32 slots
+        c->tp_prefill_off = 256 + (((size_t)2 * tp_size * H * 8 + 255) & ~(size_t)255);
+        EFM_TRY(dev_alloc(c, &c->tp_xchg, c->tp_prefill_off + (size_t)2 * tp_size * S * H * sizeof(float)));
     }
     EFM_TRY(dev_alloc(c, &c->final_norm, H));
     c->layers.resize(d.num_layers);

@@ -154,6 +154,36 @@ static void peers_consumer(const efm_b200_ctx& c, GemvParams& p, int parity) {
     p.error = &c.state->error;
 }
 
+// Tensor-parallel prefill: sum of the row-parallel partial c.ybuf [S, H] over the ranks, added to the residual.
+// With imported peer buffers: push the partial into every rank's slot, then wait for all ranks' flags and add the
+// slots in rank order; otherwise ncclAllReduce + add.
+static void tp_prefill_sum(efm_b200_ctx& c, Launcher& L, int S, int parity) {
+    const size_t H = (size_t)c.d.hidden, n = (size_t)S * H;
+    const int grid = (int)std::min<size_t>((n / 4 + 255) / 256, (size_t)c.num_sms * 8);
+    if (!c.peers_ready) {
+        tp_all_reduce(c, L, c.ybuf, c.ysum, n);
+        L.launch(add_rows_kernel, dim3(std::min<size_t>((n / 2 + 255) / 256, (size_t)c.num_sms * 8)), dim3(256), 0, c.resid,
+                 (const float*)c.ysum, n / 2);
+        return;
+    }
+    const size_t slot = (size_t)c.max_s * H;                                   // floats per (parity, rank) slot
+    PeerPushParams pp{};
+    pp.src = reinterpret_cast<const float4*>(c.ybuf);
+    pp.n_peers = c.tp_size;
+    pp.n4 = n / 4;
+    for (int r = 0; r < c.tp_size; ++r) {
+        pp.dst[r] = reinterpret_cast<float4*>(reinterpret_cast<float*>(c.peer_base[r] + c.tp_prefill_off) + ((size_t)parity * c.tp_size + c.tp_rank) * slot);
+        pp.flag[r] = reinterpret_cast<unsigned int*>(c.peer_base[r] + 128) + parity * 8 + c.tp_rank;
+    }
+    pp.epoch = reinterpret_cast<unsigned int*>(c.tp_xchg + 192);
+    pp.ticket = reinterpret_cast<unsigned int*>(c.tp_xchg + 196);
+    L.launch(peer_push_rows_kernel, dim3(grid), dim3(256), 0, pp);
+    L.launch(peer_add_rows_kernel, dim3(grid), dim3(256), 0, reinterpret_cast<float4*>(c.resid),
+             reinterpret_cast<const float4*>(reinterpret_cast<const float*>(c.tp_xchg + c.tp_prefill_off) + (size_t)parity * c.tp_size * slot),
+             reinterpret_cast<const unsigned int*>(c.tp_xchg + 128) + parity * 8, c.tp_size, n / 4, slot / 4,
+             (const unsigned int*)reinterpret_cast<unsigned int*>(c.tp_xchg + 192), &c.state->error);
+}
+
 // Tensor-parallel decode step: column-parallel QKV / gate-up, row-parallel o_proj / down with an
 // all-reduce of the fp32 partial [H]; the residual add moves into the next kernel's norm prologue
 // (x = bf16(x + bf16(sum)), ping-ponging between two residual buffers so no block re-reads a row that
@@ -522,9 +552,7 @@ void qwen_prefill_chunk(efm_b200_ctx& c, KvSlot& slot, int S, int kv_offset, int
         } else {      // row-parallel: this rank's input columns, fp32 partial, all-reduce, then the residual add
             GemmParams g{c.attn + (size_t)c.att_rep_idx * c.o_k, w.o, nullptr, nullptr, c.ybuf, S, H, c.o_k, QD};
             launch_gemm<GemmEpi::F32>(L, g, &c.state->error);
-            tp_all_reduce(c, L, c.ybuf, c.ysum, (size_t)S * H);
-            L.launch(add_rows_kernel, dim3(std::min<size_t>(((size_t)S * H / 2 + 255) / 256, (size_t)c.num_sms * 8)), dim3(256), 0,
-                     c.resid, (const float*)c.ysum, (size_t)S * H / 2);
+            tp_prefill_sum(c, L, S, 0);
         }
         L.launch(rmsnorm_rows_kernel, dim3(S), dim3(256), 0, (const float*)c.resid,
                  (const __nv_bfloat16*)w.post_norm, c.norm, H, d.rms_eps);
@@ -538,9 +566,7 @@ void qwen_prefill_chunk(efm_b200_ctx& c, KvSlot& slot, int S, int kv_offset, int
         } else {
             GemmParams g{c.act, w.down, nullptr, nullptr, c.ybuf, S, H, I};
             launch_gemm<GemmEpi::F32>(L, g, &c.state->error);
-            tp_all_reduce(c, L, c.ybuf, c.ysum, (size_t)S * H);
-            L.launch(add_rows_kernel, dim3(std::min<size_t>(((size_t)S * H / 2 + 255) / 256, (size_t)c.num_sms * 8)), dim3(256), 0,
-                     c.resid, (const float*)c.ysum, (size_t)S * H / 2);
+            tp_prefill_sum(c, L, S, 1);
         }
     }
     if (sample_last) launch_lm_head_and_sample(c, L, c.resid + (size_t)(S - 1) * H, /*advance=*/0);

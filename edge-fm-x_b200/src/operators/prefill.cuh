@@ -120,4 +120,65 @@ __global__ void __launch_bounds__(256) add_rows_kernel(float* __restrict__ resid
     }
 }
 
+// Tensor parallel prefill over peer memory, producer side: this rank's fp32 partial [n4 float4] is copied into its
+// slot of every rank's receive buffer (P2P stores over NVLink, own buffer included).  Every block orders its stores
+// with a system-scope fence and draws a ticket; the block that draws the last one advances the local exchange
+// count and publishes it in this rank's flag word on every rank.
+struct PeerPushParams {
+    const float4* src;
+    float4* dst[8];              // this rank's slot in rank r's buffer
+    unsigned int* flag[8];       // this rank's flag word on rank r
+    int n_peers;
+    size_t n4;
+    unsigned int* epoch;         // local: prefill exchanges completed
+    unsigned int* ticket;        // local, zero between launches
+};
+__global__ void __launch_bounds__(256) peer_push_rows_kernel(const PeerPushParams p) {
+    for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < p.n4; i += (size_t)gridDim.x * 256) {
+        const float4 v = p.src[i];
+        for (int r = 0; r < p.n_peers; ++r) p.dst[r][i] = v;
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned int t = atomicAdd(p.ticket, 1u);
+        if (t == gridDim.x - 1) {
+            *p.ticket = 0u;
+            const unsigned int e = *p.epoch + 1u;
+            *p.epoch = e;
+            __threadfence_system();
+            for (int r = 0; r < p.n_peers; ++r)
+                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.flag[r]), "r"(e) : "memory");
+        }
+    }
+}
+
+// Consumer side: wait (bounded; *error = 3 on expiry) until every rank's flag reached the local exchange count, then
+// resid += (part[0] + part[1] + ...) in rank order.  parts: n_parts slots of slot4 float4 each, n4 of them used.
+__global__ void __launch_bounds__(256) peer_add_rows_kernel(float4* __restrict__ resid, const float4* __restrict__ parts,
+                                                            const unsigned int* __restrict__ flags, int n_parts, size_t n4,
+                                                            size_t slot4, const unsigned int* __restrict__ epoch, int* error) {
+    if ((int)threadIdx.x < n_parts) {
+        const unsigned int want = __ldcg(epoch);
+        int spins = 0;
+        for (;;) {
+            unsigned int v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + threadIdx.x) : "memory");
+            if ((int)(v - want) >= 0) break;
+            if (++spins > (1 << 22)) { if (error != nullptr) atomicExch(error, 3); break; }
+            if ((spins & 63) == 0) __nanosleep(64);
+        }
+    }
+    __syncthreads();
+    for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n4; i += (size_t)gridDim.x * 256) {
+        float4 a = __ldcg(parts + i);
+        for (int r = 1; r < n_parts; ++r) {
+            const float4 b = __ldcg(parts + (size_t)r * slot4 + i);
+            a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+        }
+        const float4 o = resid[i];
+        resid[i] = make_float4(o.x + a.x, o.y + a.y, o.z + a.z, o.w + a.w);
+    }
+}
+
 }  // namespace efm

@@ -105,7 +105,8 @@ EFM_API efm_status efm_b200_tp_init(efm_b200_ctx* ctx, const void* id128);
  * every peer's buffer over NVLink as 8-byte {value, exchange count} words; the next kernel's prologue re-reads
  * (bounded, EFM_ERR_DEVICE_WAIT on expiry) until every word carries the current count and adds the partials in
  * rank order.  Without these two calls
- * the decode step uses ncclAllReduce.  Prefill and the logits all-gather stay on NCCL either way. */
+ * the decode step uses ncclAllReduce.  Prefill exchanges its [S, hidden] partials through the same peer buffers
+ * (copy + published count + ordered add) once they are imported; the logits all-gather stays on NCCL. */
 EFM_API efm_status efm_b200_tp_peer_export(efm_b200_ctx* ctx, void* handle64);
 EFM_API efm_status efm_b200_tp_peer_import(efm_b200_ctx* ctx, const void* handles, int32_t n_handles);
 

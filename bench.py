@@ -29,7 +29,7 @@ for p in (ROOT, os.path.join(ROOT, "tests"), os.path.join(ROOT, "edge-fm-x_b200"
 
 METRIC, UNIT = "decode_tokens_per_second_batch1", "tok/s"
 # DRAM bytes (read + write) of the four per-layer GEMV launches of one decode step, from the ncu capture
-# summarised in profiles/decode_gemv_qwen1p5b_ncu.md (config 1 only; other configs were not captured).
+# summarised under profiles/ (config 1 only; other configs were not captured).
 NCU_LAYER_GEMV_DRAM_BYTES = {1: 6.33984e6 + 4.758528e6 + 55.090432e6 + 77.824e3 + 27.579904e6}
 NAMES = {0: "qwen2.5-0.5b", 1: "qwen2.5-1.5b", 2: "qwen2.5-vl-3b-llm", 3: "qwen2.5-vl-7b-llm"}
 
@@ -554,7 +554,7 @@ def run_ours(args, rank, world, local_rank):
             "gpu_launches": launches,
             "clocks": clocks,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": traffic, "traffic_source": "ncu dram__bytes_read+write of the per-layer GEMV launches (profiles/decode_gemv_qwen1p5b_ncu.md) + algorithmic bytes of lm_head, attention and vectors" if traffic else None,
+                         "traffic": traffic, "traffic_source": "ncu dram__bytes_read+write of the per-layer GEMV launches (summary under profiles/) + algorithmic bytes of lm_head, attention and vectors" if traffic else None,
                          "peak_kind": peak_kind, "launch": "one decode step (CUDA graph of %d kernel nodes: 5 per layer + lm_head + sampler)" % (5 * L + 2),
                          "bytes_per_launch": step_bytes, "us_per_launch": step_ms * 1e3, "kernels": kernels},
             "tokens_head": tokens[:8], "e2e_tokens_equal": e2e_tokens == tokens,

@@ -212,7 +212,7 @@ static void qwen_decode_step_tp(efm_b200_ctx& c, KvSlot& slot, Launcher& L) {
             DecodeAttnParams a{};
             a.q = c.q_d; a.k_cache = slot.k[l]; a.v_cache = slot.v[l]; a.out = c.attn_d; a.state = c.state;
             a.q_heads = d.q_heads; a.kv_heads = d.kv_heads; a.group = d.q_heads / d.kv_heads;
-            a.n_splits = slot.n_splits; a.chunk_cap = slot.chunk_cap; a.max_tokens = slot.max_tokens; a.cluster = slot.attn_cluster;
+            a.n_splits = slot.n_splits; a.chunk_cap = slot.chunk_cap; a.max_tokens = slot.max_tokens; a.cluster = slot.attn_cluster; a.early = l > 0 ? 1 : 0;
             a.scale = 1.0f / sqrtf((float)D);
             a.part_o = c.attn_part_o; a.part_ml = c.attn_part_ml; a.counters = c.attn_counters;
             launch_decode_attention(L, a, D);
@@ -313,6 +313,7 @@ void qwen_decode_step(efm_b200_ctx& c, KvSlot& slot, Launcher& L) {
             a.n_splits = slot.n_splits;
             a.chunk_cap = slot.chunk_cap;
             a.cluster = slot.attn_cluster;
+            a.early = l > 0 ? 1 : 0;       // layer 0 follows the sampler's state update: wait first
             a.max_tokens = slot.max_tokens;
             a.scale = 1.0f / sqrtf((float)D);
             a.part_o = c.attn_part_o;

@@ -40,6 +40,8 @@ struct DecodeAttnParams {
     float* part_ml;                // [q_heads][n_splits][2]
     unsigned int* counters;        // [kv_heads], zero between launches
     int cluster;                   // > 1: the n_splits blocks of a kv head form one thread-block cluster (n_splits == cluster)
+    int early;                     // 1: kv_len and every cache row but the newest may be read before the dependency wait
+                                   //    (they were written in earlier steps; only q and row kv_len-1 come from the launch before)
 };
 
 template <int D>
@@ -59,7 +61,7 @@ struct DecodeAttnSmem {
 
 // One (chunk, kv head) work item, executed by all 512 threads of the block.  Every load of data
 // another block may have written in this step (q, the newest cache row, the partials) bypasses L1.
-template <int D, bool CLUSTER = false>
+template <int D, bool CLUSTER = false, bool WAIT_INSIDE = false>
 __device__ __forceinline__ void decode_attention_body(const DecodeAttnParams& p, const int split, const int kvh,
                                                       unsigned char* attn_smem) {
     constexpr int NT = kAttnThreads, NW = kAttnWarps;
@@ -72,6 +74,10 @@ __device__ __forceinline__ void decode_attention_body(const DecodeAttnParams& p,
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = p.group;
 
+    // WAIT_INSIDE: this body holds the kernel's dependency wait.  With p.early the old cache rows of the first tile
+    // are requested before it, so that their DRAM latency runs under the tail of the preceding launch.
+    const bool early = WAIT_INSIDE && p.early != 0;
+    if (WAIT_INSIDE && !early) pdl_wait();
     int kv_len = p.state != nullptr ? (int)p.state->kv_len : p.kv_len_static;
     if (kv_len > p.max_tokens) {
         if (p.state != nullptr) p.state->error = 2;
@@ -92,19 +98,13 @@ __device__ __forceinline__ void decode_attention_body(const DecodeAttnParams& p,
 #pragma unroll
         for (int e = 0; e < 4; ++e) acc[g][e] = 0.f;
 
-    for (int i = tid * 2; i < G * D; i += NT * 2) {              // q: two channels per load
-        const int g = i / D, d = i - g * D;
-        const uint32_t two = __ldcg(reinterpret_cast<const unsigned int*>(p.q + (size_t)(kvh * G) * D + i));
-        sm.q[g][d / DP][d % DP] = bf16lo(two);
-        sm.q[g][(d + 1) / DP][(d + 1) % DP] = bf16hi(two);
-    }
     if (tid < kMaxGroup) { sm.run_m[tid] = -INFINITY; sm.run_l[tid] = 0.f; }
 
     // ---- 1. K and V slices in flight together; the next tile's are issued as soon as this tile's
     //         registers are free, so that they fly during the softmax and P.V of the current tile
     uint4 kq[QV], vq[QV];
-    auto issue_tile = [&](int t0) {
-        if (t0 < n && tok < min(kAttnTile, n - t0)) {
+    auto issue_tile = [&](int t0, int skip_row) {
+        if (t0 < n && tok < min(kAttnTile, n - t0) && start + t0 + tok != skip_row) {
             const size_t off = (size_t)(start + t0 + tok) * row_stride + (size_t)kvh * D + part * DP;
 #pragma unroll
             for (int j = 0; j < QV; ++j) kq[j] = ld_cg(p.k_cache + off + j * 8);
@@ -112,7 +112,21 @@ __device__ __forceinline__ void decode_attention_body(const DecodeAttnParams& p,
             for (int j = 0; j < QV; ++j) vq[j] = ld_cg(p.v_cache + off + j * 8);
         }
     };
-    issue_tile(0);
+    if (early) {
+        issue_tile(0, kv_len - 1);       // everything but the row the preceding launch appends
+        pdl_wait();
+    }
+    for (int i = tid * 2; i < G * D; i += NT * 2) {              // q: two channels per load
+        const int g = i / D, d = i - g * D;
+        const uint32_t two = __ldcg(reinterpret_cast<const unsigned int*>(p.q + (size_t)(kvh * G) * D + i));
+        sm.q[g][d / DP][d % DP] = bf16lo(two);
+        sm.q[g][(d + 1) / DP][(d + 1) % DP] = bf16hi(two);
+    }
+    if (early) {
+        if (0 < n && tok < min(kAttnTile, n) && start + tok == kv_len - 1) issue_tile(0, -1);
+    } else {
+        issue_tile(0, -1);
+    }
     for (int t0 = 0; t0 < n; t0 += kAttnTile) {
         const int nt = min(kAttnTile, n - t0);
         const bool valid = tok < nt;
@@ -142,7 +156,7 @@ __device__ __forceinline__ void decode_attention_body(const DecodeAttnParams& p,
             for (int j = 0; j < QV; ++j)
                 *reinterpret_cast<uint4*>(&sm.v[tok][part * DP + j * 8]) = vq[j];
         }
-        issue_tile(t0 + kAttnTile);
+        issue_tile(t0 + kAttnTile, -1);
 #pragma unroll
         for (int g = 0; g < kMaxGroup; ++g) {
             s[g] += __shfl_xor_sync(0xffffffffu, s[g], 1);
@@ -343,8 +357,7 @@ template <int D>
 __global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(const DecodeAttnParams p) {
     extern __shared__ __align__(16) unsigned char attn_smem_raw[];
     pdl_launch_dependents();
-    pdl_wait();
-    decode_attention_body<D>(p, blockIdx.x, blockIdx.y, attn_smem_raw);
+    decode_attention_body<D, false, true>(p, blockIdx.x, blockIdx.y, attn_smem_raw);
 }
 
 // Cluster form: grid (cluster, kv_heads) with cluster dimension (cluster, 1, 1).
@@ -352,8 +365,7 @@ template <int D>
 __global__ void __launch_bounds__(kAttnThreads) decode_attention_cluster_kernel(const DecodeAttnParams p) {
     extern __shared__ __align__(16) unsigned char attn_smem_raw[];
     pdl_launch_dependents();
-    pdl_wait();
-    decode_attention_body<D, true>(p, blockIdx.x, blockIdx.y, attn_smem_raw);
+    decode_attention_body<D, true, true>(p, blockIdx.x, blockIdx.y, attn_smem_raw);
 }
 
 inline size_t decode_attention_smem_bytes(int D, int /*chunk_cap*/) {

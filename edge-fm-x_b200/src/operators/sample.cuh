@@ -166,7 +166,9 @@ __global__ void __launch_bounds__(1024) sample_kernel(const SampleParams p) {
         const int seg_lo = min(p.vocab, warp * seg), seg_hi = min(p.vocab, seg_lo + seg);
         const bool vec_ok = (p.vocab & 3) == 0;
 
-        // pass 0: integer weights (four 128-id strides per trip so that the loads overlap)
+        // pass 0: integer weights (four 128-id strides per trip so that the loads overlap); their sum is the
+        // candidate mass of round 0 (every token is a candidate then), which saves that round's first scan
+        unsigned long long mass0 = 0ull;
         for (int base0 = seg_lo + lane * 4; base0 < seg_hi; base0 += 512) {
             float lg[4][4];
 #pragma unroll
@@ -188,6 +190,7 @@ __global__ void __launch_bounds__(1024) sample_kernel(const SampleParams p) {
                 for (int e = 0; e < 4; ++e) {
                     const float s = expf((lg[u][e] - M) * inv_t) * 2147483648.0f;
                     w4[e] = s >= 2147483648.0f ? 0x7fffffffu : (unsigned int)s;   // NaN -> 0
+                    if (base + e < seg_hi) mass0 += w4[e];
                 }
                 if (vec_ok) { if (base < seg_hi) *reinterpret_cast<uint4*>(p.wbuf + base) = make_uint4(w4[0], w4[1], w4[2], w4[3]); }
                 else {
@@ -205,8 +208,8 @@ __global__ void __launch_bounds__(1024) sample_kernel(const SampleParams p) {
 #pragma unroll 1
         for (uint32_t round = 0; round < 32u && !accepted; ++round) {
             // (a) candidate mass per segment
-            unsigned long long mass = 0ull;
-            for (int base0 = seg_lo + lane * 4; base0 < seg_hi; base0 += 512) {
+            unsigned long long mass = round == 0 ? mass0 : 0ull;
+            for (int base0 = seg_lo + lane * 4; round > 0 && base0 < seg_hi; base0 += 512) {
                 unsigned int w4[4][4];
                 load_weights16(p.wbuf, base0, seg_hi, vec_ok, w4);
 #pragma unroll

@@ -61,6 +61,7 @@ efm_status require_b200(efm_b200_ctx* c, int device_id) {
     if (major != 10) return fail(c, EFM_ERR_CUDA, "device is not sm_100 (this library carries sm_100a code only)");
     EFM_CK(c, cudaSetDevice(device_id));
     EFM_CK(c, configure_decode_attention());
+    EFM_CK(c, configure_sampler());
     {
         int optin = 0;
         EFM_CK(c, cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device_id));
@@ -216,7 +217,7 @@ efm_status efm_b200_create(const efm_model_desc* desc, int32_t device_id, int32_
     EFM_TRY(dev_alloc(c, &c->logits, V));
     EFM_TRY(dev_alloc(c, &c->part_val, 2 * (size_t)c->num_sms + 8));
     EFM_TRY(dev_alloc(c, &c->part_idx, 2 * (size_t)c->num_sms + 8));
-    EFM_TRY(dev_alloc(c, &c->wbuf, V));
+    EFM_TRY(dev_alloc(c, &c->wbuf, sample_scratch_words((int)V)));
     EFM_TRY(dev_alloc(c, &c->attn_part_o, (size_t)dl.q_heads * 64 * D));
     EFM_TRY(dev_alloc(c, &c->attn_part_ml, (size_t)dl.q_heads * 64 * 2));
     EFM_TRY(dev_alloc(c, &c->attn_counters, (size_t)dl.kv_heads));
@@ -950,12 +951,12 @@ efm_status efm_b200_op_sample(const float* logits, int32_t vocab, const efm_samp
     if (logits == nullptr || s == nullptr || token_out == nullptr || vocab <= 0)
         return fail(nullptr, EFM_ERR_INVALID_ARGUMENT, "op_sample: bad arguments");
     uint32_t* wbuf = nullptr;
-    cudaError_t e = cudaMalloc(&wbuf, (size_t)vocab * 4);
+    cudaError_t e = cudaMalloc(&wbuf, sample_scratch_words(vocab) * 4);
     if (e != cudaSuccess) return cuda_fail(nullptr, e, "op_sample scratch");
     SampleParams p{};
     p.logits = logits; p.vocab = vocab; p.n_part = 0;
     p.temperature = s->temperature; p.top_p = s->top_p; p.seed = s->seed; p.rng_step = rng_step;
-    p.state = nullptr; p.token_single = token_out; p.wbuf = wbuf;
+    p.state = nullptr; p.token_single = token_out; p.wbuf = wbuf; p.xchg = sample_xchg(wbuf, vocab);
     Launcher L; L.pdl = false;
     launch_sample(L, p);
     st = op_finish(L);

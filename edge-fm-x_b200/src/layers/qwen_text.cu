@@ -31,7 +31,44 @@ static void tp_all_reduce(efm_b200_ctx& c, Launcher& L, const float* send, float
 static void tp_all_gather(efm_b200_ctx& c, Launcher& L, const float* send, float* recv, size_t count);
 static void launch_sample_only(efm_b200_ctx& c, Launcher& L, int n_part, int advance);
 
-void launch_sample(Launcher& L, const SampleParams& p) { L.launch(sample_kernel, dim3(1), dim3(1024), 0, p); }
+// Widest cluster the sampler can run with on this device: 16, 8, ... or 1 (single block; also with
+// EFM_B200_SAMPLER_CLUSTER=1).  Found once, outside any stream capture.
+static int g_sampler_cluster = -1;
+
+cudaError_t configure_sampler() {
+    if (g_sampler_cluster >= 0) return cudaSuccess;
+    int best = 1;
+    const bool wide = cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
+    for (int cs = wide ? 16 : 8; cs >= 2; cs >>= 1) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(cs, 1, 1);
+        cfg.blockDim = dim3(1024);
+        cudaLaunchAttribute at;
+        at.id = cudaLaunchAttributeClusterDimension;
+        at.val.clusterDim.x = (unsigned)cs;
+        at.val.clusterDim.y = at.val.clusterDim.z = 1;
+        cfg.attrs = &at;
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, sample_kernel, &cfg) == cudaSuccess && n >= 1) { best = cs; break; }
+    }
+    (void)cudaGetLastError();
+    if (const char* env = std::getenv("EFM_B200_SAMPLER_CLUSTER")) {
+        const int v = std::atoi(env);
+        if (v >= 1) { int cs = 1; while (cs * 2 <= v && cs * 2 <= best) cs *= 2; best = cs; }
+    }
+    g_sampler_cluster = best;
+    return cudaSuccess;
+}
+
+// Greedy decoding needs one block (the arg-max of the logits pass's partial maxima); top-p sampling
+// spreads its passes over the vocabulary across one cluster.
+void launch_sample(Launcher& L, const SampleParams& p) {
+    if (g_sampler_cluster < 0) (void)configure_sampler();
+    const int cs = (p.temperature >= 1e-6f && p.xchg != nullptr) ? g_sampler_cluster : 1;
+    L.cluster_x = cs;
+    L.launch(sample_kernel, dim3(cs), dim3(1024), 0, p);
+}
 
 void launch_lm_head_and_sample(efm_b200_ctx& c, Launcher& L, const float* resid_row, int advance) {
     const efm_model_desc& d = c.d;
@@ -66,6 +103,7 @@ void launch_lm_head_and_sample(efm_b200_ctx& c, Launcher& L, const float* resid_
     s.max_response = d.max_response_tokens;
     s.advance = advance;
     s.wbuf = c.wbuf;
+    s.xchg = sample_xchg(c.wbuf, d.vocab);
     launch_sample(L, s);
 }
 
@@ -85,6 +123,7 @@ static void launch_sample_only(efm_b200_ctx& c, Launcher& L, int n_part, int adv
     s.max_response = d.max_response_tokens;
     s.advance = advance;
     s.wbuf = c.wbuf;
+    s.xchg = sample_xchg(c.wbuf, d.vocab);
     launch_sample(L, s);
 }
 

@@ -30,6 +30,7 @@ void launch_sage_prefill_attention(Launcher& L, const SageScratch& sc, const __n
                                    const __nv_bfloat16* v, __nv_bfloat16* out, int S, int kv_offset, int q_heads,
                                    int kv_heads, int D);
 void launch_sample(Launcher& L, const SampleParams& p);
+cudaError_t configure_sampler();      // once per device at set-up, never inside a stream capture
 // y[r,:] = bf16(rmsnorm(x[r,:]) * w) over `rows` fp32 rows.
 void launch_rmsnorm_rows(Launcher& L, const float* x, const __nv_bfloat16* w, __nv_bfloat16* y, int rows, int hidden, float eps);
 void launch_prefill_attention(Launcher& L, const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v,

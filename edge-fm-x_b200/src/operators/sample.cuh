@@ -41,7 +41,15 @@ struct SampleParams {
     int32_t* token_single;   // optional single output
     int advance;             // 1: move kv_len / positions / step on to the next decode step
     uint32_t* wbuf;          // [vocab] scratch: integer weights
+    unsigned long long* xchg;  // [1040] scratch of the multi-block form: segment masses [512] | masses before the pick [512] | pick
 };
+
+// Sampler scratch is one allocation of sample_scratch_words(vocab) 32-bit words: the integer weights,
+// then (16-byte aligned) the exchange area of the multi-block form.
+inline size_t sample_scratch_words(int vocab) { return (size_t)((vocab + 3) & ~3) + 2 * 1040; }
+inline unsigned long long* sample_xchg(uint32_t* wbuf, int vocab) {
+    return reinterpret_cast<unsigned long long*>(wbuf + ((vocab + 3) & ~3));
+}
 
 #ifndef EFM_DECLARATIONS_ONLY   // kernel bodies are compiled in exactly one translation unit
 __device__ __forceinline__ uint32_t philox4x32_10_first(uint32_t c0, uint32_t c1, uint32_t k0, uint32_t k1) {
@@ -105,11 +113,11 @@ __device__ __forceinline__ void load_weights16(const uint32_t* wbuf, int base0, 
 __global__ void __launch_bounds__(1024) sample_kernel(const SampleParams p) {
     constexpr int NT = 1024;
     __shared__ unsigned long long scan_tmp[33];
-    __shared__ unsigned long long seg_mass[32];
     __shared__ float rv[32];
     __shared__ int ri[32];
-    __shared__ unsigned int sel_w;
-    __shared__ int sel_id;
+    __shared__ unsigned long long cta_tot[16];
+    __shared__ unsigned long long s_before_seg;
+    __shared__ int s_ow;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     pdl_launch_dependents();
@@ -153,18 +161,39 @@ __global__ void __launch_bounds__(1024) sample_kernel(const SampleParams p) {
     const float M = rv[0];
     int token = ri[0];
     if (token < 0 || token >= p.vocab) token = p.vocab - 1;     // all-NaN / empty guard
-    if (tid == 0) { sel_id = token; sel_w = 0u; }
 
     if (p.temperature >= 1e-6f) {
         const float inv_t = 1.0f / p.temperature;
         double top_p = (double)p.top_p;
         top_p = top_p > 1.0 ? 1.0 : (top_p < 1e-9 ? 1e-9 : top_p);
         const uint32_t step = p.state != nullptr ? (uint32_t)p.state->step : p.rng_step;
-        // Each warp owns one contiguous id segment (a multiple of 128 ids) and walks it 128 ids at a
-        // time, 4 consecutive ids per lane: every pass over the vocabulary is coalesced.
-        const int seg = ((p.vocab + 32 * 128 - 1) / (32 * 128)) * 128;
-        const int seg_lo = min(p.vocab, warp * seg), seg_hi = min(p.vocab, seg_lo + seg);
+        // The blocks of the launch form one thread-block cluster (1 block: the same code with trivial barriers).
+        // Each warp of each block owns one contiguous id segment (a multiple of 128 ids) and walks it 128 ids at a
+        // time, 4 consecutive ids per lane: every pass over the vocabulary is coalesced.  All masses are exact
+        // integers, so the pick does not depend on how many blocks share the work.
+        const int ncta = (int)gridDim.x, cta = (int)blockIdx.x;
+        const int nseg = 32 * ncta;
+        const int seg = ((p.vocab + nseg * 128 - 1) / (nseg * 128)) * 128;
+        const int gs = cta * 32 + warp;
+        const int seg_lo = min(p.vocab, gs * seg), seg_hi = min(p.vocab, seg_lo + seg);
         const bool vec_ok = (p.vocab & 3) == 0;
+        unsigned long long* xseg = p.xchg;
+        unsigned long long* xbefore = p.xchg + 512;
+        unsigned int* xsel = reinterpret_cast<unsigned int*>(p.xchg + 1024);
+        auto cluster_sync = [&]() {
+            if (ncta > 1) asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+            else __syncthreads();
+        };
+        // sum over all segments of an exchanged array: warp c adds block c's 32 values -> cta_tot[c]
+        auto block_totals = [&](const unsigned long long* arr) {
+            if (warp < ncta) {
+                unsigned long long v = __ldcg(arr + warp * 32 + lane);
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                if (lane == 0) cta_tot[warp] = v;
+            }
+            __syncthreads();
+        };
 
         // pass 0: integer weights (four 128-id strides per trip so that the loads overlap); their sum is the
         // candidate mass of round 0 (every token is a candidate then), which saves that round's first scan
@@ -223,47 +252,66 @@ __global__ void __launch_bounds__(1024) sample_kernel(const SampleParams p) {
             }
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) mass += __shfl_xor_sync(0xffffffffu, mass, o);
-            if (lane == 0) seg_mass[warp] = mass;
-            __syncthreads();
-            // (b) owner segment of r
+            if (lane == 0) xseg[gs] = mass;
+            cluster_sync();
+            // (b) owner segment of r: first the owning block, then the segment inside it
+            block_totals(xseg);
             unsigned long long Wc = 0ull;
-            for (int w = 0; w < 32; ++w) Wc += seg_mass[w];
+            for (int c = 0; c < ncta; ++c) Wc += cta_tot[c];
             if (round == 0) target = (double)Wc * top_p;
             if (Wc == 0ull) break;
             const uint32_t x = philox4x32_10_first(step, round, (uint32_t)(p.seed & 0xffffffffull),
                                                    (uint32_t)(p.seed >> 32));
             const unsigned long long r =
                 __double2ull_rd(__dmul_rn(__dmul_rn((double)x, (double)Wc), 2.3283064365386963e-10));
-            int ow = 0;
-            unsigned long long before_seg = 0ull;
-            for (int w = 0; w < 32; ++w) {
-                if (r >= before_seg + seg_mass[w]) before_seg += seg_mass[w]; else { ow = w; break; }
+            int oc = 0;
+            unsigned long long before_cta = 0ull;
+            for (int c = 0; c < ncta; ++c) {
+                if (r >= before_cta + cta_tot[c]) before_cta += cta_tot[c]; else { oc = c; break; }
             }
+            if (warp == 0) {
+                const unsigned long long v = __ldcg(xseg + oc * 32 + lane);
+                unsigned long long incl = v;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const unsigned long long u = __shfl_up_sync(0xffffffffu, incl, o);
+                    if (lane >= o) incl += u;
+                }
+                const unsigned long long rr = r - before_cta, excl = incl - v;
+                if (lane == 0) { s_ow = oc * 32; s_before_seg = before_cta; }
+                __syncwarp();
+                if (excl <= rr && rr < incl) { s_ow = oc * 32 + lane; s_before_seg = before_cta + excl; }
+            }
+            __syncthreads();
+            const int ow = s_ow;
+            const unsigned long long before_seg = s_before_seg;
             // (c) inside the owner segment: a few consecutive ids per thread, exact block scan
-            const int olo = min(p.vocab, ow * seg), ohi = min(p.vocab, olo + seg);
-            const int per = (ohi - olo + NT - 1) / NT;
-            const int lo = min(ohi, olo + tid * per), hi = min(ohi, lo + per);
-            unsigned long long m2 = 0ull;
-            for (int i = lo; i < hi; ++i) {
-                const unsigned int w = p.wbuf[i];
-                if (piv_id < 0 || w > piv_w || (w == piv_w && i < piv_id)) m2 += w;
-            }
-            unsigned long long tot2;
-            const unsigned long long incl = block_scan_u64(m2, scan_tmp, &tot2) + before_seg;
-            const unsigned long long excl = incl - m2;
-            if (excl <= r && r < incl) {
-                unsigned long long run = excl;
+            if (cta == ow / 32) {            // the block that wrote the owner segment's weights
+                const int olo = min(p.vocab, ow * seg), ohi = min(p.vocab, olo + seg);
+                const int per = (ohi - olo + NT - 1) / NT;
+                const int lo = min(ohi, olo + tid * per), hi = min(ohi, lo + per);
+                unsigned long long m2 = 0ull;
                 for (int i = lo; i < hi; ++i) {
                     const unsigned int w = p.wbuf[i];
-                    if (piv_id < 0 || w > piv_w || (w == piv_w && i < piv_id)) {
-                        run += w;
-                        if (run > r) { sel_id = i; sel_w = w; break; }
+                    if (piv_id < 0 || w > piv_w || (w == piv_w && i < piv_id)) m2 += w;
+                }
+                unsigned long long tot2;
+                const unsigned long long incl = block_scan_u64(m2, scan_tmp, &tot2) + before_seg;
+                const unsigned long long excl = incl - m2;
+                if (excl <= r && r < incl) {
+                    unsigned long long run = excl;
+                    for (int i = lo; i < hi; ++i) {
+                        const unsigned int w = p.wbuf[i];
+                        if (piv_id < 0 || w > piv_w || (w == piv_w && i < piv_id)) {
+                            run += w;
+                            if (run > r) { xsel[0] = (unsigned int)i; xsel[1] = w; break; }
+                        }
                     }
                 }
             }
-            __syncthreads();
-            const int j = sel_id;
-            const unsigned int wj = sel_w;
+            cluster_sync();
+            const int j = (int)__ldcg(xsel);
+            const unsigned int wj = __ldcg(xsel + 1);
             // (d) mass strictly before j in (w desc, id asc) order
             unsigned long long before = 0ull;
             for (int base0 = seg_lo + lane * 4; base0 < seg_hi; base0 += 512) {
@@ -277,18 +325,18 @@ __global__ void __launch_bounds__(1024) sample_kernel(const SampleParams p) {
             }
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) before += __shfl_xor_sync(0xffffffffu, before, o);
-            __syncthreads();                       // seg_mass of step (a) fully consumed
-            if (lane == 0) seg_mass[warp] = before;
-            __syncthreads();
+            if (lane == 0) xbefore[gs] = before;
+            cluster_sync();
+            block_totals(xbefore);
             unsigned long long E = 0ull;
-            for (int w = 0; w < 32; ++w) E += seg_mass[w];
+            for (int c = 0; c < ncta; ++c) E += cta_tot[c];
             if ((double)E < target) { accepted = true; token = j; }
             else { piv_w = wj; piv_id = j; }
             __syncthreads();
         }
     }
 
-    if (tid == 0) {
+    if (tid == 0 && blockIdx.x == 0) {
         if (p.token_single != nullptr) *p.token_single = token;
         if (p.state != nullptr) {
             const int step = p.state->step;

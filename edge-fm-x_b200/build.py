@@ -26,7 +26,7 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", 
               "-Xcompiler", "-fPIC,-fvisibility=hidden", "--expt-relaxed-constexpr", "-Xptxas", "-v"]
 CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-Wall", "-Wextra", "-Wno-unused-parameter"]
 
-BACKEND_CU = ["src/backends/b200/efm_b200.cu", "src/layers/qwen_text.cu", "src/backends/b200/vit_b200.cu",
+BACKEND_CU = ["src/backends/b200/efm_b200.cu", "src/layers/qwen_text.cu", "src/backends/b200/vit_b200.cu", "src/backends/b200/vla_b200.cu",
               "src/backends/b200/nccl_glue.cpp"]
 ENGINE_CPP = sorted(glob.glob(os.path.join(HERE, "src", "engine", "*.cpp"))) + \
     [os.path.join(HERE, "src", "edge-fm.cpp"), os.path.join(HERE, "src", "tensor.cpp")]

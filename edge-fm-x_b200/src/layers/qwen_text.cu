@@ -476,6 +476,7 @@ void launch_gemm_epi(Launcher& L, GemmEpi epi, const GemmParams& p, int* error_w
         case GemmEpi::Residual: launch_gemm<GemmEpi::Residual>(L, p, error_word); break;
         case GemmEpi::F32: launch_gemm<GemmEpi::F32>(L, p, error_word); break;
         case GemmEpi::Bf16Gelu: launch_gemm<GemmEpi::Bf16Gelu>(L, p, error_word); break;
+        case GemmEpi::Bf16GeluTanh: launch_gemm<GemmEpi::Bf16GeluTanh>(L, p, error_word); break;
         case GemmEpi::SwiGlu: launch_gemm<GemmEpi::SwiGlu>(L, p, error_word); break;
     }
 }

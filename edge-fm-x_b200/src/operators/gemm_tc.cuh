@@ -23,13 +23,13 @@
 
 namespace efm {
 
-enum class GemmEpi : int { Bf16Bias = 0, Residual = 1, F32 = 2, Bf16Gelu = 3, SwiGlu = 4 };
+enum class GemmEpi : int { Bf16Bias = 0, Residual = 1, F32 = 2, Bf16Gelu = 3, SwiGlu = 4, Bf16GeluTanh = 5 };
 
 struct GemmParams {
     const __nv_bfloat16* A;   // [M, K] (row stride lda)
     const __nv_bfloat16* B;   // [N, K]
     const __nv_bfloat16* bias;
-    __nv_bfloat16* C;         // Bf16Bias / Bf16Gelu: out [M, N]; SwiGlu: out [M, N/2]
+    __nv_bfloat16* C;         // Bf16Bias / Bf16Gelu / Bf16GeluTanh: out [M, N]; SwiGlu: out [M, N/2]
     float* Cf;                // F32: out; Residual: in/out (fp32 residual stream)
     int M, N, K;
     int lda = 0;              // row stride of A in elements (0: K)
@@ -274,6 +274,8 @@ __global__ void __launch_bounds__(tc::kThreads) gemm_tc_kernel(const __grid_cons
                         o[e] = __uint_as_float(r[e]);
                         if (p.bias != nullptr && n + e < p.N) o[e] += __bfloat162float(p.bias[n + e]);
                         if constexpr (EPI == GemmEpi::Bf16Gelu) o[e] = 0.5f * o[e] * (1.0f + erff(o[e] * 0.70710678118654752f));
+                        if constexpr (EPI == GemmEpi::Bf16GeluTanh)
+                            o[e] = 0.5f * o[e] * (1.0f + tanhf(0.7978845608028654f * (o[e] + 0.044715f * o[e] * o[e] * o[e])));
                     }
                 }
                 __syncwarp();                                                  // previous chunk fully written out

@@ -307,6 +307,53 @@ EFM_API efm_status efm_b200_vit_encode(efm_b200_vit* vit, const void* pixels, in
                                        const int32_t* grid_thw, int32_t n_grids, void* out,
                                        int32_t out_mem);
 
+/* ---- SmolVLA-shaped action chunk ----------------------------------------------------------
+ * The reference describes this model (doc/smolvla_architecture.md) but ships no code for it; its
+ * closest entry point is the trajectory planner's Euler loop
+ * (src/engine/tasks/trajectory_planner/trajectory_planner_engine.cpp:298-318, edge-fm.h:49-75 plan()).
+ * One call = one action chunk: SigLIP-style vision tower + pixel-shuffle connector on n_images square
+ * images, Llama-style backbone over [image tokens | prompt | state], action expert with alternating
+ * self / cross attention over the backbone's KV rows, `steps` flow-matching Euler steps from `noise`.
+ * The object owns its device buffers and stream; it needs no text context. */
+typedef struct efm_vla_desc {
+    int32_t struct_size;          /* = sizeof(efm_vla_desc) */
+    int32_t image_size, patch, vit_layers, vit_hidden, vit_heads, vit_mlp;   /* vit_hidden = vit_heads * 64 */
+    int32_t shuffle, n_images;    /* pixel-shuffle factor; (image_size / patch) % shuffle == 0 */
+    int32_t hidden, layers, q_heads, kv_heads, head_dim, mlp;  /* backbone; head_dim 64; layers even; the expert has the same heads and depth */
+    int32_t vocab, lang_tokens;
+    int32_t expert_hidden, expert_mlp;
+    int32_t state_dim, action_dim, chunk, steps;
+    float rope_theta, rms_eps, ln_eps;
+} efm_vla_desc;
+
+typedef struct efm_b200_vla efm_b200_vla;
+
+EFM_API efm_status efm_b200_vla_create(const efm_vla_desc* desc, int32_t device, efm_b200_vla** out);
+EFM_API efm_status efm_b200_vla_destroy(efm_b200_vla* vla);
+EFM_API const char* efm_b200_vla_last_error(const efm_b200_vla* vla);
+/* bf16 tensors by name: vit.patch.{weight,bias}, vit.pos, vit.N.{ln1,ln2,q,k,v,o,fc1,fc2}.{weight,bias},
+ * vit.post_ln.{weight,bias}, connector.weight, embed, state_proj.{weight,bias},
+ * vlm.N.{norm1,norm2} and vlm.N.{q,k,v,o,gate,up,down}.weight, the same under expert.N. (k / v of the odd,
+ * cross-attention layers are [kv_dim, kv_dim]), expert.norm, action_in / time_in / time_out /
+ * action_out .{weight,bias}.  Linear weights are [out, in] row-major as in the checkpoint. */
+EFM_API efm_status efm_b200_vla_set_weight(efm_b200_vla* vla, const char* name, const void* data,
+                                           const int64_t* shape, int32_t ndim, int32_t dtype, int32_t mem_kind);
+EFM_API efm_status efm_b200_vla_finalize_weights(efm_b200_vla* vla);
+/* images fp32 [n_images, 3, image_size, image_size] (already normalised), lang_ids int32 [lang_tokens],
+ * state fp32 [state_dim], noise fp32 [chunk, action_dim]; actions_out fp32 [chunk, action_dim].  All five
+ * on the host or all on the device per mem_kind; a NULL input keeps what the previous call uploaded.
+ * Synchronous: returns when actions_out is written.  The first call launches kernel by kernel, later
+ * calls replay one captured graph. */
+EFM_API efm_status efm_b200_vla_chunk(efm_b200_vla* vla, const float* images, const int32_t* lang_ids,
+                                      const float* state, const float* noise, int32_t mem_kind,
+                                      float* actions_out);
+/* One chunk on the inputs already resident from an earlier efm_b200_vla_chunk call, enqueued on the
+ * object's stream without synchronising (for device-side timing); the stream for events. */
+EFM_API efm_status efm_b200_vla_enqueue(efm_b200_vla* vla);
+EFM_API efm_status efm_b200_vla_stream(efm_b200_vla* vla, void** stream_out);
+/* kernels launched so far / per chunk (graph replays count their kernel nodes) */
+EFM_API efm_status efm_b200_vla_launch_count(const efm_b200_vla* vla, int64_t* total, int64_t* per_chunk);
+
 #ifdef __cplusplus
 }
 #endif

@@ -35,6 +35,13 @@ class VitDesc(C.Structure):
                 ("rms_eps", C.c_float), ("rope_theta", C.c_float), ("max_patches", C.c_int32)]
 
 
+class VlaDesc(C.Structure):
+    _fields_ = [("struct_size", C.c_int32)] + [(n, C.c_int32) for n in (
+        "image_size", "patch", "vit_layers", "vit_hidden", "vit_heads", "vit_mlp", "shuffle", "n_images", "hidden", "layers",
+        "q_heads", "kv_heads", "head_dim", "mlp", "vocab", "lang_tokens", "expert_hidden", "expert_mlp", "state_dim",
+        "action_dim", "chunk", "steps")] + [("rope_theta", C.c_float), ("rms_eps", C.c_float), ("ln_eps", C.c_float)]
+
+
 class Sampling(C.Structure):
     _fields_ = [("temperature", C.c_float), ("top_p", C.c_float), ("top_k", C.c_int32),
                 ("reserved", C.c_uint32), ("seed", C.c_uint64)]
@@ -84,6 +91,15 @@ SIGNATURES = {
     "efm_b200_vit_finalize_weights": (I32, [P]),
     "efm_b200_vit_plan": (I32, [C.POINTER(VitDesc), C.POINTER(I32), I32] + [C.POINTER(I32)] * 7),
     "efm_b200_vit_encode": (I32, [P, P, I32, C.POINTER(I32), I32, P, I32]),
+    "efm_b200_vla_create": (I32, [C.POINTER(VlaDesc), I32, C.POINTER(P)]),
+    "efm_b200_vla_destroy": (I32, [P]),
+    "efm_b200_vla_last_error": (C.c_char_p, [P]),
+    "efm_b200_vla_set_weight": (I32, [P, C.c_char_p, P, C.POINTER(C.c_int64), I32, I32, I32]),
+    "efm_b200_vla_finalize_weights": (I32, [P]),
+    "efm_b200_vla_chunk": (I32, [P, P, P, P, P, I32, P]),
+    "efm_b200_vla_enqueue": (I32, [P]),
+    "efm_b200_vla_stream": (I32, [P, C.POINTER(P)]),
+    "efm_b200_vla_launch_count": (I32, [P, C.POINTER(C.c_int64), C.POINTER(C.c_int64)]),
 }
 
 _lib = None
@@ -332,6 +348,68 @@ class VitEncoder:
                                                  flat, len(grids), P(out.data_ptr()),
                                                  EFM_MEM_DEVICE if out.is_cuda else EFM_MEM_HOST), "vit_encode")
         return out
+
+
+def vla_desc(cfg):
+    """efm_vla_desc from an oracle.smolvla.VlaConfig-like object."""
+    d = VlaDesc()
+    d.struct_size = C.sizeof(VlaDesc)
+    for name, _ in VlaDesc._fields_[1:]:
+        setattr(d, name, getattr(cfg, name))
+    return d
+
+
+class VlaPolicy:
+    """Action-chunk model behind efm_b200_vla_* (owns its device buffers and stream)."""
+
+    def __init__(self, cfg, device=0):
+        self.L, self.cfg = lib(), cfg
+        d = vla_desc(cfg)
+        self.h = P()
+        st = self.L.efm_b200_vla_create(C.byref(d), device, C.byref(self.h))
+        if st != 0:
+            raise RuntimeError(f"vla_create failed with status {st}")
+
+    def check(self, st, what):
+        if st != 0:
+            raise RuntimeError(f"{what}: status {st}: {self.L.efm_b200_vla_last_error(self.h).decode()}")
+
+    def close(self):
+        if self.h:
+            self.L.efm_b200_vla_destroy(self.h)
+            self.h = P()
+
+    def load_weights(self, weights):
+        for name, t in weights.items():
+            t = t.contiguous()
+            shape = (C.c_int64 * t.dim())(*t.shape)
+            self.check(self.L.efm_b200_vla_set_weight(self.h, name.encode(), P(t.data_ptr()), shape, t.dim(), EFM_BF16,
+                                                      EFM_MEM_DEVICE if t.is_cuda else EFM_MEM_HOST), "vla_set_weight " + name)
+        self.check(self.L.efm_b200_vla_finalize_weights(self.h), "vla_finalize_weights")
+
+    def chunk(self, images, ids, state, noise):
+        """Host tensors in (fp32 / int32), host fp32 [chunk, action_dim] out."""
+        import torch
+        c = self.cfg
+        images, state, noise = (t.to(torch.float32).contiguous() for t in (images, state, noise))
+        ids = ids.to(torch.int32).contiguous()
+        out = torch.empty(c.chunk, c.action_dim, dtype=torch.float32)
+        self.check(self.L.efm_b200_vla_chunk(self.h, P(images.data_ptr()), P(ids.data_ptr()), P(state.data_ptr()),
+                                             P(noise.data_ptr()), EFM_MEM_HOST, P(out.data_ptr())), "vla_chunk")
+        return out
+
+    def enqueue(self):
+        self.check(self.L.efm_b200_vla_enqueue(self.h), "vla_enqueue")
+
+    def stream(self):
+        s = P()
+        self.check(self.L.efm_b200_vla_stream(self.h, C.byref(s)), "vla_stream")
+        return s.value
+
+    def launch_count(self):
+        a, b = C.c_int64(), C.c_int64()
+        self.check(self.L.efm_b200_vla_launch_count(self.h, C.byref(a), C.byref(b)), "vla_launch_count")
+        return a.value, b.value
 
 
 def generate(be: Backend, slot, prompt, max_new_tokens, *, prefix_len=0, embeds=None, embed_token_id=-1, pos3=None,

@@ -87,6 +87,8 @@ struct efm_b200_vla {
     int64_t launches = 0, launches_per_chunk = 0;
     int runs = 0;
     cudaGraphExec_t graph = nullptr;
+    cudaEvent_t phase_ev[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};   // set while efm_b200_vla_phase_ms runs
+    bool mark_phases = false;
 };
 
 namespace {
@@ -395,6 +397,8 @@ void vla_forward(efm_b200_vla* v, Launcher& L) {
         launch_seg_attention(L, a, D);
     };
 
+    auto mark = [&](int i) { if (v->mark_phases && L.err == cudaSuccess) L.err = cudaEventRecord(v->phase_ev[i], L.stream); };
+    mark(0);
     // ---- vision tower ----
     L.launch(vla_patch_rows_kernel, dim3(NV), dim3(256), 0, (const float*)v->images, v->rows, d.image_size, d.patch);
     L.launch(vla_tile_rows_kernel, dim3(NV), dim3(256), 0, (const __nv_bfloat16*)v->pos, v->v_resid, v->patches, Hv);
@@ -415,6 +419,7 @@ void vla_forward(efm_b200_vla* v, Launcher& L) {
     L.launch(vla_pixel_shuffle_kernel, dim3(n_img_tok), dim3(256), 0, (const __nv_bfloat16*)v->v_xn, v->shuf, v->side, d.shuffle, Hv);
     gemm(GemmEpi::F32, v->shuf, 0, v->conn_w, nullptr, nullptr, v->resid, n_img_tok, H, SH);
 
+    mark(1);
     // ---- prefix through the backbone ----
     L.launch(vla_prefix_rows_kernel, dim3(P), dim3(256), 0, v->resid, (const __nv_bfloat16*)v->embed, (const int32_t*)v->ids,
              (const float*)v->state, (const __nv_bfloat16*)v->state_w, (const __nv_bfloat16*)v->state_b, n_img_tok, d.lang_tokens, H,
@@ -431,6 +436,7 @@ void vla_forward(efm_b200_vla* v, Launcher& L) {
         gemm(GemmEpi::Residual, v->act, 0, b.down_w, nullptr, nullptr, v->resid, P, H, d.mlp);
     }
 
+    mark(2);
     // ---- bridge: what the expert reads of the prefix, once per chunk ----
     for (int l = 0; l < d.layers; ++l) {
         LlamaLayer& e = v->expert[l];
@@ -445,6 +451,7 @@ void vla_forward(efm_b200_vla* v, Launcher& L) {
         }
     }
 
+    mark(3);
     // ---- denoising loop ----
     if (L.err == cudaSuccess) L.err = cudaMemcpyAsync(v->x_t, v->noise, (size_t)n * d.action_dim * 4, cudaMemcpyDeviceToDevice, L.stream);
     const float dt = -1.0f / (float)d.steps;
@@ -482,6 +489,7 @@ void vla_forward(efm_b200_vla* v, Launcher& L) {
         L.launch(vla_bf16_to_f32_kernel, dim3((n * He + 255) / 256), dim3(256), 0, (const __nv_bfloat16*)v->e_xn, v->hf, n * He);
         small(0, v->hf, He, v->aout_w, v->aout_b, v->x_t, d.action_dim, n, d.action_dim, He, dt);
     }
+    mark(4);
 }
 
 // Runs one chunk on the inputs resident on the device: eagerly the first time (which also sets every
@@ -560,6 +568,29 @@ efm_status efm_b200_vla_enqueue(efm_b200_vla* v) {
     if (!v->finalized) return vla_fail(v, EFM_ERR_STATE, "weights are not finalized");
     VLA_CK(v, cudaSetDevice(v->device));
     return vla_run(v);
+}
+
+efm_status efm_b200_vla_phase_ms(efm_b200_vla* v, float* ms4) {
+    if (v == nullptr || ms4 == nullptr) return EFM_ERR_INVALID_ARGUMENT;
+    if (!v->finalized || v->runs == 0) return vla_fail(v, EFM_ERR_STATE, "run a chunk first");
+    VLA_CK(v, cudaSetDevice(v->device));
+    for (cudaEvent_t& e : v->phase_ev) VLA_CK(v, cudaEventCreate(&e));
+    Launcher L;
+    L.stream = v->stream;
+    L.pdl = false;
+    L.gemm_ws = v->gemm_ws;
+    L.gemm_ws_floats = v->gemm_ws_floats;
+    L.num_sms = v->num_sms;
+    v->mark_phases = true;
+    vla_forward(v, L);                 // kernel by kernel, not the graph
+    v->mark_phases = false;
+    cudaError_t e = L.err != cudaSuccess ? L.err : cudaStreamSynchronize(v->stream);
+    if (e == cudaSuccess)
+        for (int i = 0; i < 4 && e == cudaSuccess; ++i) e = cudaEventElapsedTime(&ms4[i], v->phase_ev[i], v->phase_ev[i + 1]);
+    for (cudaEvent_t& ev : v->phase_ev) { cudaEventDestroy(ev); ev = nullptr; }
+    if (e != cudaSuccess) return vla_fail(v, EFM_ERR_CUDA, std::string("phase timing: ") + cudaGetErrorString(e));
+    v->launches += v->launches_per_chunk;
+    return EFM_OK;
 }
 
 efm_status efm_b200_vla_launch_count(const efm_b200_vla* v, int64_t* total, int64_t* per_chunk) {

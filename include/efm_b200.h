@@ -351,6 +351,9 @@ EFM_API efm_status efm_b200_vla_chunk(efm_b200_vla* vla, const float* images, co
  * object's stream without synchronising (for device-side timing); the stream for events. */
 EFM_API efm_status efm_b200_vla_enqueue(efm_b200_vla* vla);
 EFM_API efm_status efm_b200_vla_stream(efm_b200_vla* vla, void** stream_out);
+/* Device time of the four phases of one chunk (vision, prefix, bridge, denoise), launched kernel by kernel on
+ * the resident inputs with events in between: ms4[4].  A profiling aid; the graph replay is faster. */
+EFM_API efm_status efm_b200_vla_phase_ms(efm_b200_vla* vla, float* ms4);
 /* kernels launched so far / per chunk (graph replays count their kernel nodes) */
 EFM_API efm_status efm_b200_vla_launch_count(const efm_b200_vla* vla, int64_t* total, int64_t* per_chunk);
 

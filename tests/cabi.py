@@ -99,6 +99,7 @@ SIGNATURES = {
     "efm_b200_vla_chunk": (I32, [P, P, P, P, P, I32, P]),
     "efm_b200_vla_enqueue": (I32, [P]),
     "efm_b200_vla_stream": (I32, [P, C.POINTER(P)]),
+    "efm_b200_vla_phase_ms": (I32, [P, C.POINTER(C.c_float)]),
     "efm_b200_vla_launch_count": (I32, [P, C.POINTER(C.c_int64), C.POINTER(C.c_int64)]),
 }
 
@@ -405,6 +406,11 @@ class VlaPolicy:
         s = P()
         self.check(self.L.efm_b200_vla_stream(self.h, C.byref(s)), "vla_stream")
         return s.value
+
+    def phase_ms(self):
+        ms = (C.c_float * 4)()
+        self.check(self.L.efm_b200_vla_phase_ms(self.h, ms), "vla_phase_ms")
+        return dict(zip(("vision", "prefix", "bridge", "denoise"), [float(x) for x in ms]))
 
     def launch_count(self):
         a, b = C.c_int64(), C.c_int64()

@@ -86,3 +86,15 @@ def test_missing_weight_and_bad_shape_are_reported():
             pol.load_weights({"nope": torch.zeros(3, dtype=torch.bfloat16)})
     finally:
         pol.close()
+
+
+def test_benchmark_size_chunk_equals_oracle():
+    # the configuration the chunks/s number is quoted on (3 x 512 px, 241-token prefix, 10 steps x 50 actions)
+    cfg = smolvla.VlaConfig()
+    w, inp, first, second, third, launches = _run(cfg, seed=0)
+    with torch.no_grad():
+        want = smolvla.VlaOracle(cfg, w, mode="bf16_points").chunk(*inp)
+    err = (first - want).abs().max().item()
+    assert err < TOL, err
+    assert torch.equal(first, third)
+    assert cfg.prefix == 241 and tuple(first.shape) == (50, 32)

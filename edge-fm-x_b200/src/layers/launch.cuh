@@ -18,6 +18,7 @@ namespace efm {
 struct Launcher {
     cudaStream_t stream = nullptr;
     bool pdl = true;                 // programmatic stream serialization between consecutive kernels
+    bool pdl_rows = false;           // keep `pdl` for the row / attention kernels of the prefill family too (they open with the wait)
     bool cooperative = false;        // next launch only: all blocks co-resident (they wait on each other)
     int cluster_x = 0;               // next launch only: thread-block cluster of this many blocks along x
     float* gemm_ws = nullptr;        // split-K workspace of the owning context (nullptr: GEMMs never split)

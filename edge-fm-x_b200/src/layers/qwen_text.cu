@@ -465,7 +465,7 @@ void launch_gemm_bf16(Launcher& L, const GemmParams& p) { launch_gemm<GemmEpi::B
 
 void launch_rmsnorm_rows(Launcher& L, const float* x, const __nv_bfloat16* w, __nv_bfloat16* y, int rows, int hidden, float eps) {
     const bool pdl = L.pdl;
-    L.pdl = false;
+    L.pdl = pdl && L.pdl_rows;
     L.launch(rmsnorm_rows_kernel, dim3(rows), dim3(256), 0, x, w, y, hidden, eps);
     L.pdl = pdl;
 }
@@ -490,7 +490,7 @@ static void launch_seg_attention_dn(Launcher& L, const SegAttnParams& p) {
     }
     const dim3 grid((p.S + 16 * NW - 1) / (16 * NW), p.q_heads), block(32 * NW);
     const bool pdl = L.pdl;
-    L.pdl = false;
+    L.pdl = pdl && L.pdl_rows;
     L.launch(seg_attention_kernel<D, NW>, grid, block, sa::smem_bytes<D, NW>(), p);
     L.pdl = pdl;
 }

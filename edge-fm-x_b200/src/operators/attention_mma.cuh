@@ -73,6 +73,8 @@ __device__ __forceinline__ void load_tile(uint32_t smem, const __nv_bfloat16* ba
 template <int D, int NW>
 __global__ void __launch_bounds__(NW * 32) seg_attention_kernel(const SegAttnParams p) {
     using namespace sa;
+    pdl_launch_dependents();
+    pdl_wait();            // no-ops unless launched with programmatic stream serialization
     constexpr int BQ = 16 * NW, kThreads = 32 * NW;
     constexpr int RB = row_bytes<D>();
     constexpr int KS = D / 16;           // k-steps of Q K^T

@@ -269,13 +269,18 @@ __global__ void __launch_bounds__(tc::kThreads) gemm_tc_kernel(const __grid_cons
                     uint32_t r[32];
                     tmem_ld32(acc + (uint32_t)c0, r);
                     const int n = n0 + c0;
+                    // one bias element per lane, handed round by shuffles (32 broadcast loads per thread otherwise)
+                    const float bias_l = (p.bias != nullptr && n + lane < p.N) ? __bfloat162float(p.bias[n + lane]) : 0.f;
 #pragma unroll
                     for (int e = 0; e < 32; ++e) {
-                        o[e] = __uint_as_float(r[e]);
-                        if (p.bias != nullptr && n + e < p.N) o[e] += __bfloat162float(p.bias[n + e]);
+                        o[e] = __uint_as_float(r[e]) + __shfl_sync(0xffffffffu, bias_l, e);
                         if constexpr (EPI == GemmEpi::Bf16Gelu) o[e] = 0.5f * o[e] * (1.0f + erff(o[e] * 0.70710678118654752f));
                         if constexpr (EPI == GemmEpi::Bf16GeluTanh)
-                            o[e] = 0.5f * o[e] * (1.0f + tanhf(0.7978845608028654f * (o[e] + 0.044715f * o[e] * o[e] * o[e])));
+                        {
+                            float th;           // hardware tanh (relative error ~2^-11, below the bf16 rounding of the result)
+                            asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(0.7978845608028654f * (o[e] + 0.044715f * o[e] * o[e] * o[e])));
+                            o[e] = 0.5f * o[e] * (1.0f + th);
+                        }
                     }
                 }
                 __syncwarp();                                                  // previous chunk fully written out

@@ -39,6 +39,8 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float* __restri
                                                            __nv_bfloat16* __restrict__ y, int hidden, float eps) {
     __shared__ float part[8];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    pdl_launch_dependents();
+    pdl_wait();            // no-ops unless launched with programmatic stream serialization
     const float* xr = x + (size_t)blockIdx.x * hidden;
     const int nch = hidden >> 3;
     float ss = 0.f;

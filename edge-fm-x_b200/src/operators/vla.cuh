@@ -1,6 +1,8 @@
 // Row kernels of the SmolVLA-shaped action chunk around its GEMMs and attention: patch rows of the
 // camera images, LayerNorm, pixel shuffle, prefix assembly, rotate-half RoPE with K/V scatter, the
-// small fp32 linears of the flow-matching head and the Euler update.  The reference ships no code
+// small fp32 linears of the flow-matching head and the Euler update.  Every kernel opens with the
+// dependent-launch pair (release the next launch, then wait for the previous kernel's writes), so the chunk
+// can be launched with programmatic stream serialization; without that attribute both are no-ops.  The reference ships no code
 // for this model (only doc/smolvla_architecture.md); the arithmetic follows that description and
 // the public SmolVLM vision tower.  All are HBM- or latency-bound elementwise / row passes.
 #pragma once
@@ -12,6 +14,8 @@ namespace efm {
 // row as in the convolution weight.  One block per patch row.
 __global__ void __launch_bounds__(256) vla_patch_rows_kernel(const float* __restrict__ images, __nv_bfloat16* __restrict__ rows,
                                                             int S, int p) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int side = S / p, patch = blockIdx.x % (side * side), img = blockIdx.x / (side * side);
     const int pr = patch / side, pc = patch % side, pd = 3 * p * p;
     const float* im = images + (size_t)img * 3 * S * S;
@@ -26,6 +30,8 @@ __global__ void __launch_bounds__(256) vla_patch_rows_kernel(const float* __rest
 // value of the residual stream (the patch GEMM then adds onto it).
 __global__ void __launch_bounds__(256) vla_tile_rows_kernel(const __nv_bfloat16* __restrict__ src, float* __restrict__ dst,
                                                            int period, int width) {
+    pdl_launch_dependents();
+    pdl_wait();
     const __nv_bfloat16* s = src + (size_t)(blockIdx.x % period) * width;
     float* d = dst + (size_t)blockIdx.x * width;
     for (int i = threadIdx.x; i < width; i += 256) d[i] = __bfloat162float(s[i]);
@@ -36,6 +42,8 @@ __global__ void __launch_bounds__(256) vla_tile_rows_kernel(const __nv_bfloat16*
 __global__ void __launch_bounds__(256) layernorm_rows_kernel(const float* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                                                             const __nv_bfloat16* __restrict__ b, __nv_bfloat16* __restrict__ y,
                                                             int width, float eps) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float red[8];
     __shared__ float stat[2];
     const float* xr = x + (size_t)blockIdx.x * width;
@@ -69,6 +77,8 @@ __global__ void __launch_bounds__(256) layernorm_rows_kernel(const float* __rest
 // One block per output token; d % 8 == 0.
 __global__ void __launch_bounds__(256) vla_pixel_shuffle_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out,
                                                                int side, int s, int d) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int ts = side / s, per = ts * ts;
     const int img = blockIdx.x / per, tok = blockIdx.x % per, R = tok / ts, C = tok % ts;
     const int d8 = d / 8;
@@ -87,6 +97,8 @@ __global__ void __launch_bounds__(256) vla_prefix_rows_kernel(float* __restrict_
                                                              const int32_t* __restrict__ ids, const float* __restrict__ state,
                                                              const __nv_bfloat16* __restrict__ sw, const __nv_bfloat16* __restrict__ sb,
                                                              int n_img_tok, int n_lang, int H, int state_dim, int vocab) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.x;
     float* row = resid + (size_t)r * H;
     const float sc = sqrtf((float)H);
@@ -113,6 +125,8 @@ __global__ void __launch_bounds__(256) vla_prefix_rows_kernel(float* __restrict_
 __global__ void __launch_bounds__(256) vla_rope_rows_kernel(__nv_bfloat16* __restrict__ qkv, int row_stride, int q_heads, int kv_heads,
                                                            int D, int pos0, float theta, __nv_bfloat16* __restrict__ kv_out,
                                                            int kv_out_stride, int kv_row0) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.x, half = D / 2;
     __nv_bfloat16* row = qkv + (size_t)r * row_stride;
     const float pos = (float)(pos0 + r);
@@ -142,6 +156,8 @@ __global__ void __launch_bounds__(256) vla_rope_rows_kernel(__nv_bfloat16* __res
 // dst rows [0, rows) of width w (stride dst_stride) = src rows (stride src_stride); w % 8 == 0, bf16.
 __global__ void __launch_bounds__(128) vla_copy_rows_kernel(const __nv_bfloat16* __restrict__ src, int src_stride,
                                                            __nv_bfloat16* __restrict__ dst, int dst_stride, int w) {
+    pdl_launch_dependents();
+    pdl_wait();
     const uint4* s = reinterpret_cast<const uint4*>(src + (size_t)blockIdx.x * src_stride);
     uint4* d = reinterpret_cast<uint4*>(dst + (size_t)blockIdx.x * dst_stride);
     for (int i = threadIdx.x; i < w / 8; i += 128) d[i] = s[i];
@@ -155,6 +171,8 @@ template <int ACT>
 __global__ void __launch_bounds__(256) vla_small_linear_kernel(const float* __restrict__ x, int ldx, const __nv_bfloat16* __restrict__ W,
                                                               const __nv_bfloat16* __restrict__ b, float* __restrict__ y, int ldy,
                                                               int M, int N, int K, float euler) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const int o = blockIdx.x * 8 + (threadIdx.x >> 5);
     if (o >= M * N) return;
@@ -175,12 +193,16 @@ __global__ void __launch_bounds__(256) vla_small_linear_kernel(const float* __re
 // cat[m, off + i] = emb[i] for every row m: the time embedding of this step beside the action embedding.
 __global__ void __launch_bounds__(256) vla_fill_time_kernel(float* __restrict__ cat, int ld, int off, const float* __restrict__ emb,
                                                            int width) {
+    pdl_launch_dependents();
+    pdl_wait();
     float* d = cat + (size_t)blockIdx.x * ld + off;
     for (int i = threadIdx.x; i < width; i += 256) d[i] = emb[i];
 }
 
 // y (fp32 rows) = float(x) of bf16 rows -- the final expert norm output for the fp32 output projection.
 __global__ void __launch_bounds__(256) vla_bf16_to_f32_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ y, int n) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int i = blockIdx.x * 256 + threadIdx.x;
     if (i < n) y[i] = __bfloat162float(x[i]);
 }

@@ -1,7 +1,8 @@
 // The engine facade.  Source-compatible with the reference's include/edge-fm/edge-fm.h:10-111.
-// Only the token-generation path is implemented behind it; the planner / stage entry points
-// exist so that callers link, and throw ConfigurationError exactly as the reference's base
-// Engine does when the configured task does not provide them (src/engine/engine.cpp:551-564).
+// Behind it: the token-generation path (generate) and, for task = trajectory_planning, the
+// action-chunk policy (plan).  The stage entry points exist so that callers link, and throw
+// ConfigurationError exactly as the reference's base Engine does when the configured task does
+// not provide them (src/engine/engine.cpp:551-564).
 #pragma once
 #include <edge-fm/core.h>
 
@@ -22,6 +23,8 @@ public:
     // slot's capacity; stop tokens cut the returned ids on the host afterwards.
     Response generate(const Request& request) const;
 
+    // task = trajectory_planning: host tensors "images" f32 [n, 3, S, S], "lang_tokens" i32, "state" f32 and optionally
+    // the planner's state tensor (default "current_actions", f32 [chunk, action_dim]) -> {"trajectory": f32 [chunk, action_dim]}.
     TensorMap plan(int32_t request_id, const TensorRefMap& inputs) const;
     TensorMap run_stage(int32_t request_id, const std::string& stage_name, const TensorRefMap& inputs) const;
     TensorMap prefill(int32_t request_id, const TensorRefMap& inputs) const;

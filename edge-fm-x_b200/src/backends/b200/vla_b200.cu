@@ -1,7 +1,7 @@
 // SmolVLA-shaped action chunk behind the C ABI (efm_b200_vla_*): three camera images, a prompt and a
 // robot state in, one [chunk, action_dim] action chunk out.  The reference ships no code for this
 // model, only its description (doc/smolvla_architecture.md); its flow-matching loop follows the same
-// Euler plumbing as src/engine/tasks/trajectory_planner/trajectory_planner_engine.cpp:70-78,298-318.
+// Euler plumbing as src/engine/tasks/trajectory_planning/trajectory_planner_engine.cpp:70-78,298-318.
 //
 // Phases of one chunk, all on one stream and (from the second call on) replayed as one CUDA graph:
 //   vision   patch rows -> patch GEMM onto the position table -> vit_layers x [LayerNorm, q|k|v GEMM,

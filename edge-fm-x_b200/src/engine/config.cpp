@@ -82,8 +82,8 @@ EngineConfig::EngineConfig(const std::string& config_path) {
 
     std::string task = config_.get_string("task", "");
     std::transform(task.begin(), task.end(), task.begin(), [](unsigned char c) { return (char)std::tolower(c); });
-    if (!task.empty() && task != "token_generation")
-        throw ConfigurationError("Unsupported task in engine config: " + task + " (this build provides token_generation only)");
+    if (!task.empty() && task != "token_generation" && task != "trajectory_planning")
+        throw ConfigurationError("Unsupported task in engine config: " + task + " (this build provides token_generation and trajectory_planning)");
     const std::string path = prefill_model_path();
     if (path.empty()) throw ConfigurationError("prefill_model_path is required in configuration");
     validate_model_path(path, "prefill_model_path");
@@ -106,6 +106,11 @@ json::Value EngineConfig::section(const std::string& name) const {
     return *v;
 }
 
+std::string EngineConfig::task() const {
+    std::string t = config_.get_string("task", "token_generation");
+    std::transform(t.begin(), t.end(), t.begin(), [](unsigned char c) { return (char)std::tolower(c); });
+    return t.empty() ? std::string("token_generation") : t;
+}
 std::string EngineConfig::model_name() const { return config_.get_string("model_name", ""); }
 std::string EngineConfig::prefill_model_path() const { return config_.get_string("prefill_model_path", ""); }
 std::string EngineConfig::decode_model_path() const { return config_.get_string("decode_model_path", ""); }

@@ -24,6 +24,7 @@ public:
     const json::Value& root() const { return config_; }
     const std::string& config_dir() const { return config_dir_; }   // directory of the engine JSON
     json::Value compact_vocab() const { return section("compact_vocab"); }
+    std::string task() const;                     // "token_generation" (default) | "trajectory_planning"
     std::string model_name() const;               // as written
     std::string resolved_model_name() const;      // "qwen2_5" | "qwen2_5_vl" (throws otherwise)
     std::string prefill_model_path() const;

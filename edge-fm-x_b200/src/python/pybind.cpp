@@ -43,6 +43,23 @@ py::capsule tensor_to_capsule(const Tensor& t) {
     });
 }
 
+// dict[str, Tensor] -> pointers into the Python-owned tensors (alive for the duration of the call), and back:
+// the conversions of the reference's planner bindings (src/python/pybind_debug.cpp:108-130,1672-1679).
+TensorRefMap tensor_ref_map_from_py_dict(const py::dict& dict) {
+    TensorRefMap out;
+    for (auto item : dict) {
+        const std::string key = py::cast<std::string>(item.first);
+        out[key] = &py::cast<const Tensor&>(item.second);
+    }
+    return out;
+}
+
+py::dict tensor_map_to_py_dict(TensorMap&& map) {
+    py::dict out;
+    for (auto& kv : map) out[py::str(kv.first)] = py::cast(new Tensor(std::move(kv.second)), py::return_value_policy::take_ownership);
+    return out;
+}
+
 }  // namespace
 
 PYBIND11_MODULE(edge_fm, m) {
@@ -120,6 +137,18 @@ PYBIND11_MODULE(edge_fm, m) {
     py::class_<EdgeFM>(m, "EdgeFM")
         .def(py::init<const std::string&>(), py::arg("config_path"))
         .def("generate", &EdgeFM::generate, py::arg("request"), py::call_guard<py::gil_scoped_release>())
+        .def("plan",
+             [](const EdgeFM& self, int32_t request_id, const py::dict& inputs) {
+                 TensorRefMap refs = tensor_ref_map_from_py_dict(inputs);
+                 TensorMap result;
+                 {
+                     py::gil_scoped_release release;
+                     result = self.plan(request_id, refs);
+                 }
+                 return tensor_map_to_py_dict(std::move(result));
+             },
+             py::arg("request_id"), py::arg("inputs"))
+        .def("last_plan_metrics", &EdgeFM::last_plan_metrics)
         .def("last_generate_metrics", &EdgeFM::last_generate_metrics)
         .def("tune", &EdgeFM::tune);
 }

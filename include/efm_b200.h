@@ -310,7 +310,7 @@ EFM_API efm_status efm_b200_vit_encode(efm_b200_vit* vit, const void* pixels, in
 /* ---- SmolVLA-shaped action chunk ----------------------------------------------------------
  * The reference describes this model (doc/smolvla_architecture.md) but ships no code for it; its
  * closest entry point is the trajectory planner's Euler loop
- * (src/engine/tasks/trajectory_planner/trajectory_planner_engine.cpp:298-318, edge-fm.h:49-75 plan()).
+ * (src/engine/tasks/trajectory_planning/trajectory_planner_engine.cpp:298-318, edge-fm.h:49-75 plan()).
  * One call = one action chunk: SigLIP-style vision tower + pixel-shuffle connector on n_images square
  * images, Llama-style backbone over [image tokens | prompt | state], action expert with alternating
  * self / cross attention over the backbone's KV rows, `steps` flow-matching Euler steps from `noise`.

@@ -5,7 +5,7 @@ The reference project ships no code for this model, only a description:
 doc/smolvla_architecture.md (vision tower and connector :155-259, Llama backbone :264-409, action
 expert :411-517, flow-matching head and suffix embedding :519-617, mask rule :619-656, the two
 inference phases :776-1150).  The timestep plumbing follows the reference's Euler loop
-(src/engine/tasks/trajectory_planner/trajectory_planner_engine.cpp:70-78,298-318).
+(src/engine/tasks/trajectory_planning/trajectory_planner_engine.cpp:70-78,298-318).
 
 Pinning: the vision tower and the connector (pixel shuffle + projection) are checked against
 transformers.models.smolvlm.modeling_smolvlm (SmolVLMVisionTransformer, SmolVLMConnector) through

@@ -107,9 +107,12 @@ json::Value EngineConfig::section(const std::string& name) const {
 }
 
 std::string EngineConfig::task() const {
-    std::string t = config_.get_string("task", "token_generation");
+    std::string t = config_.get_string("task", "");
     std::transform(t.begin(), t.end(), t.begin(), [](unsigned char c) { return (char)std::tolower(c); });
-    return t.empty() ? std::string("token_generation") : t;
+    if (!t.empty()) return t;
+    // no task written: a policy model name implies the planner task, as in the reference
+    // (tests/engine/test_planner_policy_api.py, "model name without task infers trajectory planning")
+    return normalize_model_name(model_name()) == "smolvla" ? std::string("trajectory_planning") : std::string("token_generation");
 }
 std::string EngineConfig::model_name() const { return config_.get_string("model_name", ""); }
 std::string EngineConfig::prefill_model_path() const { return config_.get_string("prefill_model_path", ""); }

@@ -85,20 +85,30 @@ __global__ void __launch_bounds__(kSkinnyThreads) skinny_gemm_kernel(const Skinn
                 const int k0 = (c0 + i * GROUP) << 5;
                 w[i] = (k0 + 8 * t + 8 <= p.K) ? ld_stream16(wrow + k0) : make_uint4(0u, 0u, 0u, 0u);   // also false past the last chunk
             }
+            // two chunks at a time: all sixteen activation vectors are requested before the first MMA needs one, so a
+            // batch costs two memory round trips instead of one per m-tile (rows >= M and k >= K read as zeros)
 #pragma unroll
-            for (int i = 0; i < BATCH; ++i) {
-                const int k0 = (c0 + i * GROUP) << 5;
-                if (k0 >= p.K) break;
-                const bool kin = k0 + 8 * t + 8 <= p.K;
+            for (int i = 0; i < BATCH; i += 2) {
+                if (((c0 + i * GROUP) << 5) >= p.K) break;
+                uint4 xa[2][4], xb[2][4];
 #pragma unroll
-                for (int mt = 0; mt < 4; ++mt) {
-                    const int r0 = 16 * mt + g, r1 = r0 + 8;
-                    if (16 * mt >= p.M) break;
-                    const uint4 xa = (kin && r0 < p.M) ? __ldg(reinterpret_cast<const uint4*>(xcol + (size_t)r0 * p.ldx + k0)) : make_uint4(0u, 0u, 0u, 0u);
-                    const uint4 xb = (kin && r1 < p.M) ? __ldg(reinterpret_cast<const uint4*>(xcol + (size_t)r1 * p.ldx + k0)) : make_uint4(0u, 0u, 0u, 0u);
-                    mma_bf16_16816(acc[mt], xa.x, xb.x, xa.y, xb.y, w[i].x, w[i].y);
-                    mma_bf16_16816(acc[mt], xa.z, xb.z, xa.w, xb.w, w[i].z, w[i].w);
+                for (int u = 0; u < 2; ++u) {
+                    const int k0 = (c0 + (i + u) * GROUP) << 5;
+                    const bool kin = k0 + 8 * t + 8 <= p.K;
+#pragma unroll
+                    for (int mt = 0; mt < 4; ++mt) {
+                        const int r0 = 16 * mt + g, r1 = r0 + 8;
+                        xa[u][mt] = (kin && r0 < p.M) ? __ldg(reinterpret_cast<const uint4*>(xcol + (size_t)r0 * p.ldx + k0)) : make_uint4(0u, 0u, 0u, 0u);
+                        xb[u][mt] = (kin && r1 < p.M) ? __ldg(reinterpret_cast<const uint4*>(xcol + (size_t)r1 * p.ldx + k0)) : make_uint4(0u, 0u, 0u, 0u);
+                    }
                 }
+#pragma unroll
+                for (int u = 0; u < 2; ++u)
+#pragma unroll
+                    for (int mt = 0; mt < 4; ++mt) {
+                        mma_bf16_16816(acc[mt], xa[u][mt].x, xb[u][mt].x, xa[u][mt].y, xb[u][mt].y, w[i + u].x, w[i + u].y);
+                        mma_bf16_16816(acc[mt], xa[u][mt].z, xb[u][mt].z, xa[u][mt].w, xb[u][mt].w, w[i + u].z, w[i + u].w);
+                    }
             }
         }
     }

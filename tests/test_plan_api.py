@@ -50,6 +50,14 @@ def test_unsupported_planner_settings_are_configuration_errors(tmp_path):
         d.mkdir()
         with pytest.raises(ValueError):
             edge_fm.EdgeFM(_write_policy(d, cfg, None, planner))
+    d = tmp_path / "inferred"           # no task key: the policy model name selects the planner task
+    d.mkdir()
+    path = _write_policy(d, cfg, None, {"type": "candidate_scoring"})
+    doc = json.loads(open(path).read())
+    del doc["task"]
+    open(path, "w").write(json.dumps(doc))
+    with pytest.raises(ValueError, match="planner.type"):
+        edge_fm.EdgeFM(path)
     d = tmp_path / "task"
     d.mkdir()
     with pytest.raises(ValueError, match="Unsupported task"):

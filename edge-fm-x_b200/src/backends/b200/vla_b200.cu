@@ -372,6 +372,19 @@ efm_status efm_b200_vla_finalize_weights(efm_b200_vla* v) {
     if (v == nullptr) return EFM_ERR_INVALID_ARGUMENT;
     for (const auto& kv : v->slots)
         if (!kv.second.seen) return vla_fail(v, EFM_ERR_STATE, "missing tensor: " + kv.first);
+    if (v->finalized) return EFM_OK;
+    if (v->d.chunk <= 64) {      // the expert's products run on the skinny kernel: fold its RMSNorm weights into them
+        VLA_CK(v, cudaSetDevice(v->device));
+        const size_t He = (size_t)v->d.expert_hidden;
+        for (int l = 0; l < v->d.layers; ++l) {
+            LlamaLayer& e = v->expert[l];
+            const size_t qrows = (size_t)(l % 2 == 0 ? v->QD + 2 * v->KD : v->QD), grows = 2 * (size_t)v->d.expert_mlp;
+            fold_norm_weight_kernel<<<(unsigned)std::min<size_t>((qrows * He + 255) / 256, 1184), 256, 0, v->stream>>>(e.qkv_w, e.norm1, qrows, (int)He);
+            fold_norm_weight_kernel<<<(unsigned)std::min<size_t>((grows * He + 255) / 256, 1184), 256, 0, v->stream>>>(e.gate_up_w, e.norm2, grows, (int)He);
+        }
+        VLA_CK(v, cudaGetLastError());
+        VLA_CK(v, cudaStreamSynchronize(v->stream));
+    }
     v->finalized = true;
     return EFM_OK;
 }
@@ -463,17 +476,19 @@ void vla_forward(efm_b200_vla* v, Launcher& L) {
     // ---- denoising loop ----
     const float dt = -1.0f / (float)d.steps;
     auto small = [&](int act, const float* x, int ldx, const __nv_bfloat16* W, const __nv_bfloat16* bias, float* y, int ldy, int M, int N,
-                     int K, float euler) {
+                     int K, float euler, __nv_bfloat16* y16 = nullptr) {
         const dim3 grid((M * N + 7) / 8), block(256);
-        if (act == 1) L.launch(vla_small_linear_kernel<1>, grid, block, 0, x, ldx, W, bias, y, ldy, M, N, K, euler);
-        else L.launch(vla_small_linear_kernel<0>, grid, block, 0, x, ldx, W, bias, y, ldy, M, N, K, euler);
+        if (act == 1) L.launch(vla_small_linear_kernel<1>, grid, block, 0, x, ldx, W, bias, y, ldy, M, N, K, euler, y16);
+        else L.launch(vla_small_linear_kernel<0>, grid, block, 0, x, ldx, W, bias, y, ldy, M, N, K, euler, y16);
     };
     // the expert's products: at most 64 rows -> weights streamed once on mma.sync tiles; more rows -> the tcgen05 GEMM
     const bool skinny = n <= 64;
     auto egemm = [&](GemmEpi epi, const __nv_bfloat16* A, const __nv_bfloat16* B, __nv_bfloat16* C, float* Cf, int N, int K) {
         if (!skinny) { gemm(epi, A, 0, B, nullptr, C, Cf, n, N, K); return; }
         SkinnyParams sp{A, B, C, Cf, n, N, K, K};
-        if (epi == GemmEpi::SwiGlu) L.launch(skinny_gemm_kernel<SkinnyEpi::SwiGlu, 2>, dim3(N / 16), dim3(kSkinnyThreads), 0, sp);
+        sp.eps = d.rms_eps;
+        if (epi == GemmEpi::Residual) sp.x16_out = v->e_xn;      // bf16 copy of the new residual for the NORM product that follows
+        if (epi == GemmEpi::SwiGlu) L.launch(skinny_gemm_kernel<SkinnyEpi::SwiGlu, 2, true>, dim3(N / 16), dim3(kSkinnyThreads), 0, sp);
         else if (epi == GemmEpi::Residual) L.launch(skinny_gemm_kernel<SkinnyEpi::Residual, 1>, dim3(N / 8), dim3(kSkinnyThreads), 0, sp);
         else L.launch(skinny_gemm_kernel<SkinnyEpi::Bf16, 1>, dim3(N / 8), dim3(kSkinnyThreads), 0, sp);
     };
@@ -485,16 +500,18 @@ void vla_forward(efm_b200_vla* v, Launcher& L) {
         small(0, v->x_t, d.action_dim, v->ain_w, v->ain_b, v->cat, 2 * He, n, He, d.action_dim, 0.f);
         L.launch(vla_fill_time_kernel, dim3(n), dim3(256), 0, v->cat, 2 * He, He, (const float*)(v->time_tab + (size_t)s * He), He);
         small(1, v->cat, 2 * He, v->tin_w, v->tin_b, v->h1, He, n, He, 2 * He, 0.f);
-        small(0, v->h1, He, v->tout_w, v->tout_b, v->e_resid, He, n, He, He, 0.f);
+        small(0, v->h1, He, v->tout_w, v->tout_b, v->e_resid, He, n, He, He, 0.f, skinny ? v->e_xn : nullptr);
         for (int l = 0; l < d.layers; ++l) {
             LlamaLayer& e = v->expert[l];
-            launch_rmsnorm_rows(L, v->e_resid, e.norm1, v->e_xn, n, He, d.rms_eps);
-            if (skinny) {          // projection, RoPE and the K / V scatter in one kernel
+            // skinny path: both RMSNorms are folded into the products that follow them (weights folded at load time,
+            // e_xn = bf16 copy of the un-normalised residual written by the kernel that produced it)
+            if (!skinny) launch_rmsnorm_rows(L, v->e_resid, e.norm1, v->e_xn, n, He, d.rms_eps);
+            if (skinny) {          // norm, projection, RoPE and the K / V scatter in one kernel
                 const bool self = l % 2 == 0;
                 SkinnyParams sp{v->e_xn, e.qkv_w, v->e_qkv, nullptr, n, self ? QKV : QD, He, He};
                 sp.q_heads = d.q_heads; sp.kv_heads = self ? d.kv_heads : 0; sp.pos0 = self ? P : 0; sp.theta = d.rope_theta;
-                sp.kv_out = self ? e.kv : nullptr; sp.kv_stride = 2 * KD; sp.kv_row0 = P;
-                L.launch(skinny_gemm_kernel<SkinnyEpi::QkvRope, 2>, dim3(sp.N / 16), dim3(kSkinnyThreads), 0, sp);
+                sp.kv_out = self ? e.kv : nullptr; sp.kv_stride = 2 * KD; sp.kv_row0 = P; sp.eps = d.rms_eps;
+                L.launch(skinny_gemm_kernel<SkinnyEpi::QkvRope, 2, true>, dim3(sp.N / 16), dim3(kSkinnyThreads), 0, sp);
                 if (self) attend(v->e_qkv, QKV, e.kv, e.kv + KD, 2 * KD, v->e_attn, n, d.q_heads, d.kv_heads, v->s_lo, v->s_hi);
                 else attend(v->e_qkv, QD, e.kv, e.kv + KD, 2 * KD, v->e_attn, n, d.q_heads, d.kv_heads, v->s_lo, v->c_hi);
             } else if (l % 2 == 0) {
@@ -509,7 +526,7 @@ void vla_forward(efm_b200_vla* v, Launcher& L) {
                 attend(v->e_qkv, QD, e.kv, e.kv + KD, 2 * KD, v->e_attn, n, d.q_heads, d.kv_heads, v->s_lo, v->c_hi);
             }
             egemm(GemmEpi::Residual, v->e_attn, e.o_w, nullptr, v->e_resid, He, QD);
-            launch_rmsnorm_rows(L, v->e_resid, e.norm2, v->e_xn, n, He, d.rms_eps);
+            if (!skinny) launch_rmsnorm_rows(L, v->e_resid, e.norm2, v->e_xn, n, He, d.rms_eps);
             egemm(GemmEpi::SwiGlu, v->e_xn, e.gate_up_w, v->e_act, nullptr, 2 * d.expert_mlp, He);
             egemm(GemmEpi::Residual, v->e_act, e.down_w, nullptr, v->e_resid, He, d.expert_mlp);
         }

@@ -7,6 +7,9 @@
 // Work split: an 8-column tile of the output per group of warps (8 warps / TILES tiles per block); the
 // warps of a group take the 32-wide k-chunks round-robin and their partial 64 x 8 tiles are summed in
 // shared memory in warp order (fixed order: results do not depend on timing).
+// RMSNorm in front of a product costs nothing extra (NORM variants): the norm weight is folded into W when the
+// weights are loaded, the rows' sums of squares fall out of the activation vectors the warps load anyway, and the
+// 1 / rms factor is applied to the finished 64 x 8 tile.
 // k-permutation: inside a 32-wide chunk lane t (= lane % 4) owns the 8 consecutive k values 8t .. 8t+7 of
 // its row, for both operands, and feeds them to two k16 MMA steps; a dot product does not care in which
 // order k is visited as long as both operands agree.
@@ -23,6 +26,12 @@ struct SkinnyParams {
     __nv_bfloat16* C;         // Bf16: [M, N]; SwiGlu: [M, N / 2] = silu(gate) * up, W rows interleaved 64 gate | 64 up
     float* Cf;                // Residual: [M, N] fp32, accumulated into
     int M, N, K, ldx;
+    // NORM variants: x holds the bf16 copy of the un-normalised residual rows and W already carries the RMSNorm weight
+    // (W'[n][k] = W[n][k] * w[k]); the kernel sums x^2 per row on the way and scales its results by
+    // rsqrt(mean(x^2) + eps):  rmsnorm(x) . W^T  =  inv_rms(row) * (x . W'^T)
+    float eps = 0.f;
+    // Residual: when set, the new residual value is also stored as bf16 here ([M, N]) for the next NORM product
+    __nv_bfloat16* x16_out = nullptr;
     // QkvRope (head_dim 64): columns are q heads | k heads | v heads; q and k get the rotate-half RoPE at position
     // pos0 + row (inverse frequencies theta^(-2i/64)) on the bf16-rounded projections; q goes to C [M, N] in place
     // of its columns, rotated k and v of row r to kv_out row kv_row0 + r ([.., kv_stride]: k | v) when kv_out is set
@@ -46,13 +55,22 @@ __device__ __forceinline__ uint4 ld_stream16(const void* p) {
 
 constexpr int kSkinnyThreads = 256;
 
+// W[n][k] *= w[k] (bf16, one rounding): folds an RMSNorm weight into the product that follows the norm.
+__global__ void __launch_bounds__(256) fold_norm_weight_kernel(__nv_bfloat16* __restrict__ W, const __nv_bfloat16* __restrict__ w, size_t rows,
+                                                              int K) {
+    const size_t total = rows * (size_t)K;
+    for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (size_t)gridDim.x * 256)
+        W[i] = __float2bfloat16_rn(__bfloat162float(W[i]) * __bfloat162float(w[i % (size_t)K]));
+}
+
 // TILES: 8-column tiles per block (1 or 2; SwiGlu needs 2: a gate tile and its up tile; QkvRope needs 2: a tile and
 // the tile 32 columns further in the same head).
-template <SkinnyEpi EPI, int TILES>
+template <SkinnyEpi EPI, int TILES, bool NORM = false>
 __global__ void __launch_bounds__(kSkinnyThreads) skinny_gemm_kernel(const SkinnyParams p) {
     constexpr int GROUP = 8 / TILES;                       // warps per tile
     constexpr int BATCH = 4;                               // weight vectors requested ahead per warp
     __shared__ float red[8][64][8];
+    __shared__ float ssq[NORM ? 8 : 1][64];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
     pdl_launch_dependents();
     pdl_wait();            // no-ops unless launched with programmatic stream serialization
@@ -73,6 +91,20 @@ __global__ void __launch_bounds__(kSkinnyThreads) skinny_gemm_kernel(const Skinn
     for (int mt = 0; mt < 4; ++mt)
 #pragma unroll
         for (int e = 0; e < 4; ++e) acc[mt][e] = 0.f;
+    float ss[4][2];                                         // NORM: sum of squares of rows 16 mt + g (+ 8) over this lane's k
+#pragma unroll
+    for (int mt = 0; mt < 4; ++mt) ss[mt][0] = ss[mt][1] = 0.f;
+    auto sq8 = [](const uint4& v) {
+        float a = 0.f;
+        const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float lo = __uint_as_float(u[e] << 16), hi = __uint_as_float(u[e] & 0xffff0000u);
+            a = fmaf(lo, lo, a);
+            a = fmaf(hi, hi, a);
+        }
+        return a;
+    };
 
     if (tile_ok) {
         const int nchunks = (p.K + 31) >> 5;
@@ -102,6 +134,12 @@ __global__ void __launch_bounds__(kSkinnyThreads) skinny_gemm_kernel(const Skinn
                         xb[u][mt] = (kin && r1 < p.M) ? __ldg(reinterpret_cast<const uint4*>(xcol + (size_t)r1 * p.ldx + k0)) : make_uint4(0u, 0u, 0u, 0u);
                     }
                 }
+                if (NORM) {
+#pragma unroll
+                    for (int u = 0; u < 2; ++u)
+#pragma unroll
+                        for (int mt = 0; mt < 4; ++mt) { ss[mt][0] += sq8(xa[u][mt]); ss[mt][1] += sq8(xb[u][mt]); }
+                }
 #pragma unroll
                 for (int u = 0; u < 2; ++u)
 #pragma unroll
@@ -118,6 +156,17 @@ __global__ void __launch_bounds__(kSkinnyThreads) skinny_gemm_kernel(const Skinn
         *reinterpret_cast<float2*>(&red[warp][16 * mt + g][2 * t]) = make_float2(acc[mt][0], acc[mt][1]);
         *reinterpret_cast<float2*>(&red[warp][16 * mt + g + 8][2 * t]) = make_float2(acc[mt][2], acc[mt][3]);
     }
+    if (NORM) {          // lanes t = 0..3 of a row hold disjoint k: add them, one value per (warp, row)
+#pragma unroll
+        for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                float v = ss[mt][h];
+                v += __shfl_xor_sync(0xffffffffu, v, 1);
+                v += __shfl_xor_sync(0xffffffffu, v, 2);
+                if (t == 0) ssq[NORM ? warp : 0][16 * mt + g + 8 * h] = v;
+            }
+    }
     __syncthreads();
     // 64 x 8 outputs per tile, 4 consecutive columns per thread
     const int idx = tid & 127, row = idx >> 1, c4 = (idx & 1) * 4;
@@ -130,6 +179,13 @@ __global__ void __launch_bounds__(kSkinnyThreads) skinny_gemm_kernel(const Skinn
         }
     };
     if (row >= p.M) return;
+    float inv = 1.0f;
+    if (NORM) {          // the warps of tile group 0 cover every k exactly once
+        float tot = 0.f;
+#pragma unroll
+        for (int wv = 0; wv < GROUP; ++wv) tot += ssq[NORM ? wv : 0][row];
+        inv = rsqrtf(tot / (float)p.K + p.eps);
+    }
     if (EPI == SkinnyEpi::SwiGlu) {
         if (tid >= 128) return;
         const int blk = blockIdx.x >> 3, j0 = (blockIdx.x & 7) * 8;
@@ -139,7 +195,7 @@ __global__ void __launch_bounds__(kSkinnyThreads) skinny_gemm_kernel(const Skinn
         tile_sum(1, up);
         float o[4];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) o[e] = gt[e] / (1.0f + __expf(-gt[e])) * up[e];
+        for (int e = 0; e < 4; ++e) { const float gv = gt[e] * inv, uv = up[e] * inv; o[e] = gv / (1.0f + __expf(-gv)) * uv; }
         __nv_bfloat16* dst = p.C + (size_t)row * (p.N >> 1) + blk * 64 + j0 + c4;
         *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]));
     } else if (EPI == SkinnyEpi::QkvRope) {
@@ -153,7 +209,7 @@ __global__ void __launch_bounds__(kSkinnyThreads) skinny_gemm_kernel(const Skinn
         float o1[4], o2[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-            const float a = __bfloat162float(__float2bfloat16_rn(x1[e])), b = __bfloat162float(__float2bfloat16_rn(x2[e]));
+            const float a = __bfloat162float(__float2bfloat16_rn(x1[e] * inv)), b = __bfloat162float(__float2bfloat16_rn(x2[e] * inv));
             if (rotate) {
                 float sn, cs;
                 sincosf((float)(p.pos0 + row) * powf(p.theta, -(float)(2 * (f0 + e)) / 64.0f), &sn, &cs);
@@ -179,7 +235,10 @@ __global__ void __launch_bounds__(kSkinnyThreads) skinny_gemm_kernel(const Skinn
         if (EPI == SkinnyEpi::Residual) {
             float4* dst = reinterpret_cast<float4*>(p.Cf + (size_t)row * p.N + n);
             const float4 old = *dst;
-            *dst = make_float4(old.x + s[0], old.y + s[1], old.z + s[2], old.w + s[3]);
+            const float4 nv = make_float4(old.x + s[0], old.y + s[1], old.z + s[2], old.w + s[3]);
+            *dst = nv;
+            if (p.x16_out != nullptr)
+                *reinterpret_cast<uint2*>(p.x16_out + (size_t)row * p.N + n) = make_uint2(pack_bf16(nv.x, nv.y), pack_bf16(nv.z, nv.w));
         } else {
             *reinterpret_cast<uint2*>(p.C + (size_t)row * p.N + n) = make_uint2(pack_bf16(s[0], s[1]), pack_bf16(s[2], s[3]));
         }

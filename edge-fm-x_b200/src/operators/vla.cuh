@@ -166,11 +166,11 @@ __global__ void __launch_bounds__(128) vla_copy_rows_kernel(const __nv_bfloat16*
 // Small fp32 linear of the flow-matching head: y[m, n] = act(sum_k x[m, k] * W[n, k] + b[n]) with bf16 weights,
 // fp32 input (row stride ldx) and fp32 output (row stride ldy, column offset applied by the caller).
 // One warp per output element; ACT 0: none, 1: SiLU.  With `euler` != 0 the result is not stored but
-// applied as y[m, n] += euler * value (the flow-matching update x += dt * v).
+// applied as y[m, n] += euler * value (the flow-matching update x += dt * v).  y16 (optional): bf16 copy of the result.
 template <int ACT>
 __global__ void __launch_bounds__(256) vla_small_linear_kernel(const float* __restrict__ x, int ldx, const __nv_bfloat16* __restrict__ W,
                                                               const __nv_bfloat16* __restrict__ b, float* __restrict__ y, int ldy,
-                                                              int M, int N, int K, float euler) {
+                                                              int M, int N, int K, float euler, __nv_bfloat16* __restrict__ y16) {
     pdl_launch_dependents();
     pdl_wait();
     const int lane = threadIdx.x & 31;
@@ -188,6 +188,7 @@ __global__ void __launch_bounds__(256) vla_small_linear_kernel(const float* __re
     if (ACT == 1) a = a / (1.0f + __expf(-a));
     if (euler != 0.f) y[(size_t)m * ldy + n] += euler * a;
     else y[(size_t)m * ldy + n] = a;
+    if (y16 != nullptr) y16[(size_t)m * N + n] = __float2bfloat16_rn(a);      // bf16 copy [M, N] for a NORM product
 }
 
 // cat[m, off + i] = emb[i] for every row m: the time embedding of this step beside the action embedding.

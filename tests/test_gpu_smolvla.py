@@ -98,3 +98,15 @@ def test_benchmark_size_chunk_equals_oracle():
     assert err < TOL, err
     assert torch.equal(first, third)
     assert cfg.prefix == 241 and tuple(first.shape) == (50, 32)
+
+
+def test_chunk_wider_than_64_rows_takes_the_tensor_core_products():
+    # more than 64 action rows: the expert's products go through the tcgen05 GEMM with separate norm / rope kernels
+    cfg = smolvla.VlaConfig(image_size=128, patch=16, vit_layers=1, vit_hidden=128, vit_heads=2, vit_mlp=256, shuffle=4,
+                            n_images=1, hidden=192, layers=2, q_heads=3, kv_heads=1, head_dim=64, mlp=256, vocab=300,
+                            lang_tokens=6, expert_hidden=128, expert_mlp=256, chunk=70, steps=3)
+    w, inp, first, second, third, _ = _run(cfg, seed=26)
+    want = smolvla.VlaOracle(cfg, w, mode="bf16_points").chunk(*inp)
+    err = (first - want).abs().max().item()
+    assert err < TOL, err
+    assert torch.equal(first, third)

@@ -512,8 +512,11 @@ void vla_forward(efm_b200_vla* v, Launcher& L) {
                 sp.q_heads = d.q_heads; sp.kv_heads = self ? d.kv_heads : 0; sp.pos0 = self ? P : 0; sp.theta = d.rope_theta;
                 sp.kv_out = self ? e.kv : nullptr; sp.kv_stride = 2 * KD; sp.kv_row0 = P; sp.eps = d.rms_eps;
                 L.launch(skinny_gemm_kernel<SkinnyEpi::QkvRope, 2, true>, dim3(sp.N / 16), dim3(kSkinnyThreads), 0, sp);
-                if (self) attend(v->e_qkv, QKV, e.kv, e.kv + KD, 2 * KD, v->e_attn, n, d.q_heads, d.kv_heads, v->s_lo, v->s_hi);
-                else attend(v->e_qkv, QD, e.kv, e.kv + KD, 2 * KD, v->e_attn, n, d.q_heads, d.kv_heads, v->s_lo, v->c_hi);
+                SegAttnParams a{};
+                a.q = v->e_qkv; a.k = e.kv; a.v = e.kv + KD; a.out = v->e_attn; a.lo = v->s_lo; a.hi = self ? v->s_hi : v->c_hi;
+                a.q_stride = self ? QKV : QD; a.kv_stride = 2 * KD; a.out_stride = QD;
+                a.S = n; a.kv_offset = 0; a.q_heads = d.q_heads; a.kv_heads = d.kv_heads; a.scale = scale;
+                launch_seg_attention_short(L, a, D, self ? P + n : P);
             } else if (l % 2 == 0) {
                 egemm(GemmEpi::Bf16Bias, v->e_xn, e.qkv_w, v->e_qkv, nullptr, QKV, He);
                 L.launch(vla_rope_rows_kernel, dim3(n), dim3(256), 0, v->e_qkv, QKV, d.q_heads, d.kv_heads, D, P, d.rope_theta, e.kv,

@@ -502,6 +502,23 @@ static void launch_seg_attention_d(Launcher& L, const SegAttnParams& p) {
     launch_seg_attention_dn<D, 4>(L, p);
 }
 
+void launch_seg_attention(Launcher& L, const SegAttnParams& p, int D);
+// Head dim 64, at most 64 queries and at most 320 keys per block (the action expert's attention): every key of the
+// block is requested at once.  Anything else goes to the streaming kernel.
+void launch_seg_attention_short(Launcher& L, const SegAttnParams& p, int D, int max_keys) {
+    constexpr int PRE = 5;
+    if (D != 64 || p.S <= 0 || p.S > 64 || max_keys > PRE * sa::BKV) { launch_seg_attention(L, p, D); return; }
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaFuncSetAttribute(seg_attention_kernel<64, 4, PRE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sa::smem_bytes<64, 4, PRE>());
+        attr_set = true;
+    }
+    const bool pdl = L.pdl;
+    L.pdl = pdl && L.pdl_rows;
+    L.launch(seg_attention_kernel<64, 4, PRE>, dim3(1, p.q_heads), dim3(128), sa::smem_bytes<64, 4, PRE>(), p);
+    L.pdl = pdl;
+}
+
 void launch_seg_attention(Launcher& L, const SegAttnParams& p, int D) {
     if (p.S <= 0) return;
     if (D == 128) launch_seg_attention_d<128>(L, p);

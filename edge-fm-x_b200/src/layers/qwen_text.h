@@ -24,6 +24,8 @@ void launch_gemm_bf16(Launcher& L, const GemmParams& p);
 void launch_gemm_epi(Launcher& L, GemmEpi epi, const GemmParams& p, int* error_word);
 // Attention with per-query key ranges (or the causal prefill rule when p.lo is null).
 void launch_seg_attention(Launcher& L, const SegAttnParams& p, int D);
+// Same result; picks the all-keys-resident variant when D == 64, S <= 64 and max_keys (largest hi) <= 320.
+void launch_seg_attention_short(Launcher& L, const SegAttnParams& p, int D, int max_keys);
 // INT8 prefill attention (sage_attention.cuh): pre-pass (key mean, INT8 Q / centred K + scales, fp16 V) into
 // `sc`, then the attention kernel.  q: [S, q_heads*D] rotated queries; k/v: cache rows [0, kv_offset + S).
 void launch_sage_prefill_attention(Launcher& L, const SageScratch& sc, const __nv_bfloat16* q, const __nv_bfloat16* k,

@@ -32,7 +32,9 @@ constexpr int BKV = 64;                                   // key rows per tile
 // NW warps per block = 16 * NW query rows (NW 4: short sequences, more blocks; NW 8: long ones, K/V tiles shared
 // by twice as many queries and twice the warps per SM)
 template <int D> constexpr int row_bytes() { return (D + 8) * 2; }
-template <int D, int NW> constexpr size_t smem_bytes() { return (size_t)(16 * NW + 4 * BKV) * row_bytes<D>(); }
+// PRE = 0: two K / V tile buffers, the next tile streamed in behind the current one.  PRE > 0: room for PRE tiles; all of
+// a block's keys are requested at once and the tile loop never waits on memory again (short key ranges, latency-bound).
+template <int D, int NW, int PRE = 0> constexpr size_t smem_bytes() { return (size_t)(16 * NW + 2 * (PRE > 0 ? PRE : 2) * BKV) * row_bytes<D>(); }
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
@@ -70,7 +72,7 @@ __device__ __forceinline__ void load_tile(uint32_t smem, const __nv_bfloat16* ba
 }
 }  // namespace sa
 
-template <int D, int NW>
+template <int D, int NW, int PRE = 0>
 __global__ void __launch_bounds__(NW * 32) seg_attention_kernel(const SegAttnParams p) {
     using namespace sa;
     pdl_launch_dependents();
@@ -82,7 +84,8 @@ __global__ void __launch_bounds__(NW * 32) seg_attention_kernel(const SegAttnPar
     extern __shared__ __align__(16) unsigned char seg_attn_smem[];
     __shared__ int s_range[2];
     const uint32_t sq = (uint32_t)__cvta_generic_to_shared(seg_attn_smem);
-    const uint32_t sk0 = sq + BQ * RB, sv0 = sk0 + 2 * BKV * RB;
+    constexpr int NBUF = PRE > 0 ? PRE : 2;
+    const uint32_t sk0 = sq + BQ * RB, sv0 = sk0 + NBUF * BKV * RB;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int q0 = blockIdx.x * BQ, h = blockIdx.y;
@@ -101,7 +104,8 @@ __global__ void __launch_bounds__(NW * 32) seg_attention_kernel(const SegAttnPar
     }
     __syncthreads();
     const int kbegin = s_range[0], kend = s_range[1];
-    const int ntiles = kend > kbegin ? (kend - kbegin + BKV - 1) / BKV : 0;
+    int ntiles = kend > kbegin ? (kend - kbegin + BKV - 1) / BKV : 0;
+    if (PRE > 0 && ntiles > PRE) ntiles = PRE;       // never past the buffers; the launcher only picks PRE for ranges that fit
 
     // per-thread rows: r0 = warp*16 + g, r1 = r0 + 8
     const int i0 = q0 + warp * 16 + g, i1 = i0 + 8;
@@ -110,7 +114,12 @@ __global__ void __launch_bounds__(NW * 32) seg_attention_kernel(const SegAttnPar
     if (i1 < p.S) { lo1 = p.lo != nullptr ? p.lo[i1] : 0; hi1 = p.hi != nullptr ? p.hi[i1] : p.kv_offset + i1 + 1; }
 
     load_tile<D, BQ, kThreads>(sq, p.q + (size_t)h * D, p.q_stride, q0, 0, p.S);
-    if (ntiles > 0) {
+    if (PRE > 0) {
+        for (int tl = 0; tl < ntiles; ++tl) {
+            load_tile<D, BKV, kThreads>(sk0 + tl * BKV * RB, kbase, p.kv_stride, kbegin + tl * BKV, kbegin, kend);
+            load_tile<D, BKV, kThreads>(sv0 + tl * BKV * RB, vbase, p.kv_stride, kbegin + tl * BKV, kbegin, kend);
+        }
+    } else if (ntiles > 0) {
         load_tile<D, BKV, kThreads>(sk0, kbase, p.kv_stride, kbegin, kbegin, kend);
         load_tile<D, BKV, kThreads>(sv0, vbase, p.kv_stride, kbegin, kbegin, kend);
     }
@@ -124,15 +133,19 @@ __global__ void __launch_bounds__(NW * 32) seg_attention_kernel(const SegAttnPar
     const float sl2 = p.scale * 1.4426950408889634f;
 
     for (int it = 0; it < ntiles; ++it) {
-        const int buf = it & 1;
-        if (it + 1 < ntiles) {
-            const int row0 = kbegin + (it + 1) * BKV;
-            load_tile<D, BKV, kThreads>(sk0 + (buf ^ 1) * BKV * RB, kbase, p.kv_stride, row0, kbegin, kend);
-            load_tile<D, BKV, kThreads>(sv0 + (buf ^ 1) * BKV * RB, vbase, p.kv_stride, row0, kbegin, kend);
+        const int buf = PRE > 0 ? it : (it & 1);
+        if (PRE > 0) {
+            if (it == 0) { cp_async_wait<0>(); __syncthreads(); }
+        } else {
+            if (it + 1 < ntiles) {
+                const int row0 = kbegin + (it + 1) * BKV;
+                load_tile<D, BKV, kThreads>(sk0 + (buf ^ 1) * BKV * RB, kbase, p.kv_stride, row0, kbegin, kend);
+                load_tile<D, BKV, kThreads>(sv0 + (buf ^ 1) * BKV * RB, vbase, p.kv_stride, row0, kbegin, kend);
+            }
+            cp_async_commit();
+            cp_async_wait<1>();
+            __syncthreads();
         }
-        cp_async_commit();
-        cp_async_wait<1>();
-        __syncthreads();
         if (it == 0) {
 #pragma unroll
             for (int ks = 0; ks < KS; ++ks)
@@ -204,7 +217,7 @@ __global__ void __launch_bounds__(NW * 32) seg_attention_kernel(const SegAttnPar
                 mma16816(o[2 * dp + 1], a, b[2], b[3]);
             }
         }
-        __syncthreads();          // the next iteration overwrites the other buffer, read one iteration ago
+        if (PRE == 0) __syncthreads();          // the next iteration overwrites the other buffer, read one iteration ago
     }
     cp_async_wait<0>();
 

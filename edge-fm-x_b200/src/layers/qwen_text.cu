@@ -434,10 +434,11 @@ static void launch_gemm(Launcher& L, const GemmParams& p, int* error_word = null
     L.pdl = false;     // prefill kernels do not use the dependent-launch protocol
     // Few output tiles and a long K: split K so that the whole GPU works, fp32 partials to the workspace, then
     // a fixed-order sum with the epilogue.
-    if constexpr (EPI == GemmEpi::Bf16Bias || EPI == GemmEpi::Residual || EPI == GemmEpi::F32) {
+    if constexpr (EPI == GemmEpi::Bf16Bias || EPI == GemmEpi::Residual || EPI == GemmEpi::F32 || EPI == GemmEpi::SwiGlu) {
         const int KB = (p.K + tc::BK - 1) / tc::BK;
         int splits = std::min(L.num_sms / std::max(1, tiles), KB / 4);
-        if (L.gemm_ws != nullptr && splits >= 2 && (p.N & 3) == 0 && (size_t)splits * p.M * p.N <= L.gemm_ws_floats) {
+        if (L.gemm_ws != nullptr && splits >= 2 && (p.N & 3) == 0 && (EPI != GemmEpi::SwiGlu || (p.N & 127) == 0) &&
+            (size_t)splits * p.M * p.N <= L.gemm_ws_floats) {
             const int per = (KB + splits - 1) / splits;
             splits = (KB + per - 1) / per;                 // no empty split
             GemmParams q = p;
@@ -450,7 +451,7 @@ static void launch_gemm(Launcher& L, const GemmParams& p, int* error_word = null
                 attr_f32 = true;
             }
             L.launch(gemm_tc_kernel<GemmEpi::F32>, dim3(std::min(L.num_sms, tiles * splits)), block, tc::SMEM_BYTES, ma, mb, q, error_word);
-            const size_t total4 = (size_t)p.M * p.N / 4;
+            const size_t total4 = (size_t)p.M * p.N / (EPI == GemmEpi::SwiGlu ? 8 : 4);
             const int fin = (int)std::min<size_t>((total4 + 255) / 256, (size_t)L.num_sms * 4);
             L.launch(gemm_splitk_finish_kernel<EPI>, dim3(fin), dim3(256), 0, (const float*)L.gemm_ws, splits, p);
             L.pdl = pdl;

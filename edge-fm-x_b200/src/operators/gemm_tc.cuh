@@ -336,8 +336,34 @@ __global__ void __launch_bounds__(tc::kThreads) gemm_tc_kernel(const __grid_cons
 // partial tiles) -- the order is fixed, so the result does not depend on which block finished first.
 template <GemmEpi EPI>
 __global__ void __launch_bounds__(256) gemm_splitk_finish_kernel(const float* __restrict__ ws, int splits, const GemmParams p) {
-    const size_t total4 = (size_t)p.M * p.N / 4;           // N % 4 == 0 (checked by the launcher)
     const size_t plane = (size_t)p.M * p.N;
+    if constexpr (EPI == GemmEpi::SwiGlu) {
+        // fused gate|up partials [M, N] (64 gate columns, 64 up columns, ...) -> out [M, N / 2] = silu(gate) * up
+        const int half = p.N >> 1;
+        const size_t out4 = (size_t)p.M * half / 4;        // N % 128 == 0 (checked by the launcher)
+        for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < out4; i += (size_t)gridDim.x * 256) {
+            const size_t m = (i * 4) / (size_t)half;
+            const int j = (int)((i * 4) % (size_t)half), blk = j >> 6, jj = j & 63;
+            const size_t goff = m * p.N + (size_t)blk * 128 + jj, uoff = goff + 64;
+            float4 g = *reinterpret_cast<const float4*>(ws + goff), u = *reinterpret_cast<const float4*>(ws + uoff);
+            for (int z = 1; z < splits; ++z) {
+                const float4 g2 = *reinterpret_cast<const float4*>(ws + (size_t)z * plane + goff);
+                const float4 u2 = *reinterpret_cast<const float4*>(ws + (size_t)z * plane + uoff);
+                g.x += g2.x; g.y += g2.y; g.z += g2.z; g.w += g2.w;
+                u.x += u2.x; u.y += u2.y; u.z += u2.z; u.w += u2.w;
+            }
+            if (p.bias != nullptr) {
+                const __nv_bfloat16* bg = p.bias + blk * 128 + jj;
+                g.x += __bfloat162float(bg[0]); g.y += __bfloat162float(bg[1]); g.z += __bfloat162float(bg[2]); g.w += __bfloat162float(bg[3]);
+                u.x += __bfloat162float(bg[64]); u.y += __bfloat162float(bg[65]); u.z += __bfloat162float(bg[66]); u.w += __bfloat162float(bg[67]);
+            }
+            const float o0 = g.x / (1.0f + __expf(-g.x)) * u.x, o1 = g.y / (1.0f + __expf(-g.y)) * u.y;
+            const float o2 = g.z / (1.0f + __expf(-g.z)) * u.z, o3 = g.w / (1.0f + __expf(-g.w)) * u.w;
+            *reinterpret_cast<uint2*>(p.C + m * half + j) = make_uint2(pack_bf16(o0, o1), pack_bf16(o2, o3));
+        }
+        return;
+    }
+    const size_t total4 = (size_t)p.M * p.N / 4;           // N % 4 == 0 (checked by the launcher)
     for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < total4; i += (size_t)gridDim.x * 256) {
         float4 a = *reinterpret_cast<const float4*>(ws + i * 4);
         for (int z = 1; z < splits; ++z) {

@@ -416,6 +416,12 @@ static bool make_tile_map(CUtensorMap* map, const void* ptr, int rows, int cols,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// fewest 64-wide k-blocks a split may get (EFM_B200_GEMM_MIN_KB overrides, for measurements)
+static int min_kb_per_split() {
+    static int v = [] { const char* e = std::getenv("EFM_B200_GEMM_MIN_KB"); const int x = e != nullptr ? std::atoi(e) : 0; return x >= 1 ? x : 4; }();
+    return v;
+}
+
 template <GemmEpi EPI>
 static void launch_gemm(Launcher& L, const GemmParams& p, int* error_word = nullptr) {
     static bool attr_set = false;
@@ -436,7 +442,7 @@ static void launch_gemm(Launcher& L, const GemmParams& p, int* error_word = null
     // a fixed-order sum with the epilogue.
     if constexpr (EPI == GemmEpi::Bf16Bias || EPI == GemmEpi::Residual || EPI == GemmEpi::F32 || EPI == GemmEpi::SwiGlu) {
         const int KB = (p.K + tc::BK - 1) / tc::BK;
-        int splits = std::min(L.num_sms / std::max(1, tiles), KB / 4);
+        int splits = std::min(L.num_sms / std::max(1, tiles), KB / min_kb_per_split());
         if (L.gemm_ws != nullptr && splits >= 2 && (p.N & 3) == 0 && (EPI != GemmEpi::SwiGlu || (p.N & 127) == 0) &&
             (size_t)splits * p.M * p.N <= L.gemm_ws_floats) {
             const int per = (KB + splits - 1) / splits;

@@ -82,7 +82,7 @@ struct efm_b200_vla {
     __nv_bfloat16 *xn = nullptr, *attn = nullptr, *act = nullptr;
     // expert activations
     float *e_resid = nullptr, *cat = nullptr, *h1 = nullptr, *hf = nullptr;
-    __nv_bfloat16 *e_xn = nullptr, *e_qkv = nullptr, *e_attn = nullptr, *e_act = nullptr;
+    __nv_bfloat16 *e_xn = nullptr, *e_qkv = nullptr, *e_attn = nullptr, *e_act = nullptr, *cat16 = nullptr, *h16 = nullptr;
     float* gemm_ws = nullptr;
     size_t gemm_ws_floats = 0;
     int* err_word = nullptr;
@@ -299,6 +299,8 @@ efm_status efm_b200_vla_create(const efm_vla_desc* desc, int32_t device, efm_b20
     VTRY(vla_alloc(v, &v->h1, (size_t)(n * He)));
     VTRY(vla_alloc(v, &v->hf, (size_t)(n * He)));
     VTRY(vla_alloc(v, &v->e_xn, (size_t)(n * He)));
+    VTRY(vla_alloc(v, &v->cat16, (size_t)(n * 2 * He)));
+    VTRY(vla_alloc(v, &v->h16, (size_t)(n * He)));
     VTRY(vla_alloc(v, &v->e_qkv, (size_t)(n * (QD + 2 * KD))));
     VTRY(vla_alloc(v, &v->e_attn, (size_t)(n * QD)));
     VTRY(vla_alloc(v, &v->e_act, (size_t)(n * d.expert_mlp)));
@@ -476,10 +478,10 @@ void vla_forward(efm_b200_vla* v, Launcher& L) {
     // ---- denoising loop ----
     const float dt = -1.0f / (float)d.steps;
     auto small = [&](int act, const float* x, int ldx, const __nv_bfloat16* W, const __nv_bfloat16* bias, float* y, int ldy, int M, int N,
-                     int K, float euler, __nv_bfloat16* y16 = nullptr) {
+                     int K, float euler, __nv_bfloat16* y16 = nullptr, int ldy16 = 0) {
         const dim3 grid((M * N + 7) / 8), block(256);
-        if (act == 1) L.launch(vla_small_linear_kernel<1>, grid, block, 0, x, ldx, W, bias, y, ldy, M, N, K, euler, y16);
-        else L.launch(vla_small_linear_kernel<0>, grid, block, 0, x, ldx, W, bias, y, ldy, M, N, K, euler, y16);
+        if (act == 1) L.launch(vla_small_linear_kernel<1>, grid, block, 0, x, ldx, W, bias, y, ldy, M, N, K, euler, y16, ldy16 > 0 ? ldy16 : N);
+        else L.launch(vla_small_linear_kernel<0>, grid, block, 0, x, ldx, W, bias, y, ldy, M, N, K, euler, y16, ldy16 > 0 ? ldy16 : N);
     };
     // the expert's products: at most 64 rows -> weights streamed once on mma.sync tiles; more rows -> the tcgen05 GEMM
     const bool skinny = n <= 64;
@@ -497,10 +499,22 @@ void vla_forward(efm_b200_vla* v, Launcher& L) {
     L.pdl = skinny && v->use_pdl;
     L.pdl_rows = L.pdl;
     for (int s = 0; s < d.steps; ++s) {
-        small(0, v->x_t, d.action_dim, v->ain_w, v->ain_b, v->cat, 2 * He, n, He, d.action_dim, 0.f);
-        L.launch(vla_fill_time_kernel, dim3(n), dim3(256), 0, v->cat, 2 * He, He, (const float*)(v->time_tab + (size_t)s * He), He);
-        small(1, v->cat, 2 * He, v->tin_w, v->tin_b, v->h1, He, n, He, 2 * He, 0.f);
-        small(0, v->h1, He, v->tout_w, v->tout_b, v->e_resid, He, n, He, He, 0.f, skinny ? v->e_xn : nullptr);
+        if (skinny) {      // the two wider linears of the suffix embedding on the weight-streaming kernel, bf16 activations
+            small(0, v->x_t, d.action_dim, v->ain_w, v->ain_b, v->cat, 2 * He, n, He, d.action_dim, 0.f, v->cat16, 2 * He);
+            L.launch(vla_fill_time_kernel, dim3(n), dim3(256), 0, v->cat, 2 * He, He, (const float*)(v->time_tab + (size_t)s * He), He, v->cat16);
+            SkinnyParams t1{v->cat16, v->tin_w, v->h16, nullptr, n, He, 2 * He, 2 * He};
+            t1.bias = v->tin_b; t1.act = 1;
+            L.launch(skinny_gemm_kernel<SkinnyEpi::Bf16, 1>, dim3(He / 8), dim3(kSkinnyThreads), 0, t1);
+            SkinnyParams t2{v->h16, v->tout_w, nullptr, v->e_resid, n, He, He, He};
+            t2.bias = v->tout_b; t2.assign = 1; t2.x16_out = v->e_xn;
+            L.launch(skinny_gemm_kernel<SkinnyEpi::Residual, 1>, dim3(He / 8), dim3(kSkinnyThreads), 0, t2);
+        } else {
+            small(0, v->x_t, d.action_dim, v->ain_w, v->ain_b, v->cat, 2 * He, n, He, d.action_dim, 0.f);
+            L.launch(vla_fill_time_kernel, dim3(n), dim3(256), 0, v->cat, 2 * He, He, (const float*)(v->time_tab + (size_t)s * He), He,
+                     (__nv_bfloat16*)nullptr);
+            small(1, v->cat, 2 * He, v->tin_w, v->tin_b, v->h1, He, n, He, 2 * He, 0.f);
+            small(0, v->h1, He, v->tout_w, v->tout_b, v->e_resid, He, n, He, He, 0.f);
+        }
         for (int l = 0; l < d.layers; ++l) {
             LlamaLayer& e = v->expert[l];
             // skinny path: both RMSNorms are folded into the products that follow them (weights folded at load time,

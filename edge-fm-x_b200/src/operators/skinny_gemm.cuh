@@ -32,6 +32,10 @@ struct SkinnyParams {
     float eps = 0.f;
     // Residual: when set, the new residual value is also stored as bf16 here ([M, N]) for the next NORM product
     __nv_bfloat16* x16_out = nullptr;
+    // Bf16 and Residual: bias[N] added to the sum (nullptr: none); Bf16: act 1 = SiLU; Residual: assign 1 = the fp32
+    // destination is overwritten (sum + bias) instead of accumulated into
+    const __nv_bfloat16* bias = nullptr;
+    int act = 0, assign = 0;
     // QkvRope (head_dim 64): columns are q heads | k heads | v heads; q and k get the rotate-half RoPE at position
     // pos0 + row (inverse frequencies theta^(-2i/64)) on the bf16-rounded projections; q goes to C [M, N] in place
     // of its columns, rotated k and v of row r to kv_out row kv_row0 + r ([.., kv_stride]: k | v) when kv_out is set
@@ -232,9 +236,17 @@ __global__ void __launch_bounds__(kSkinnyThreads) skinny_gemm_kernel(const Skinn
         if (n >= p.N) return;
         float s[4];
         tile_sum(tl, s);
+        if (p.bias != nullptr) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) s[e] += __bfloat162float(p.bias[n + e]);
+        }
+        if (EPI == SkinnyEpi::Bf16 && p.act == 1) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) s[e] = s[e] / (1.0f + __expf(-s[e]));
+        }
         if (EPI == SkinnyEpi::Residual) {
             float4* dst = reinterpret_cast<float4*>(p.Cf + (size_t)row * p.N + n);
-            const float4 old = *dst;
+            const float4 old = p.assign ? make_float4(0.f, 0.f, 0.f, 0.f) : *dst;
             const float4 nv = make_float4(old.x + s[0], old.y + s[1], old.z + s[2], old.w + s[3]);
             *dst = nv;
             if (p.x16_out != nullptr)

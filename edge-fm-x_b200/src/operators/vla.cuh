@@ -170,7 +170,7 @@ __global__ void __launch_bounds__(128) vla_copy_rows_kernel(const __nv_bfloat16*
 template <int ACT>
 __global__ void __launch_bounds__(256) vla_small_linear_kernel(const float* __restrict__ x, int ldx, const __nv_bfloat16* __restrict__ W,
                                                               const __nv_bfloat16* __restrict__ b, float* __restrict__ y, int ldy,
-                                                              int M, int N, int K, float euler, __nv_bfloat16* __restrict__ y16) {
+                                                              int M, int N, int K, float euler, __nv_bfloat16* __restrict__ y16, int ldy16) {
     pdl_launch_dependents();
     pdl_wait();
     const int lane = threadIdx.x & 31;
@@ -188,16 +188,20 @@ __global__ void __launch_bounds__(256) vla_small_linear_kernel(const float* __re
     if (ACT == 1) a = a / (1.0f + __expf(-a));
     if (euler != 0.f) y[(size_t)m * ldy + n] += euler * a;
     else y[(size_t)m * ldy + n] = a;
-    if (y16 != nullptr) y16[(size_t)m * N + n] = __float2bfloat16_rn(a);      // bf16 copy [M, N] for a NORM product
+    if (y16 != nullptr) y16[(size_t)m * ldy16 + n] = __float2bfloat16_rn(a);  // bf16 copy (row stride ldy16) for a skinny product
 }
 
 // cat[m, off + i] = emb[i] for every row m: the time embedding of this step beside the action embedding.
 __global__ void __launch_bounds__(256) vla_fill_time_kernel(float* __restrict__ cat, int ld, int off, const float* __restrict__ emb,
-                                                           int width) {
+                                                           int width, __nv_bfloat16* __restrict__ cat16) {
     pdl_launch_dependents();
     pdl_wait();
     float* d = cat + (size_t)blockIdx.x * ld + off;
     for (int i = threadIdx.x; i < width; i += 256) d[i] = emb[i];
+    if (cat16 != nullptr) {                 // bf16 copy with the same layout
+        __nv_bfloat16* d16 = cat16 + (size_t)blockIdx.x * ld + off;
+        for (int i = threadIdx.x; i < width; i += 256) d16[i] = __float2bfloat16_rn(emb[i]);
+    }
 }
 
 // y (fp32 rows) = float(x) of bf16 rows -- the final expert norm output for the fp32 output projection.

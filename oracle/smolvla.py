@@ -269,9 +269,9 @@ class VlaOracle:
         c, r, w = self.c, self.r, self.w
         n, P, He = c.chunk, c.prefix, c.expert_hidden
         a_emb = x_t @ w["action_in.weight"].T + w["action_in.bias"]
-        cat = torch.cat([a_emb, time_embedding(t, He)[None, :].expand(n, He)], dim=1)
+        cat = r(torch.cat([a_emb, time_embedding(t, He)[None, :].expand(n, He)], dim=1))
         h = cat @ w["time_in.weight"].T + w["time_in.bias"]
-        x = (h * torch.sigmoid(h)) @ w["time_out.weight"].T + w["time_out.bias"]
+        x = r(h * torch.sigmoid(h)) @ w["time_out.weight"].T + w["time_out.bias"]
         vis_self = torch.cat([torch.ones(n, P, dtype=torch.bool), torch.tril(torch.ones(n, n, dtype=torch.bool))], dim=1)
         vis_cross = torch.ones(n, P, dtype=torch.bool)
         for l in range(c.layers):

@@ -422,23 +422,26 @@ void vla_forward(efm_b200_vla* v, Launcher& L) {
     mark(0);
     // the action state starts as the noise (copied here, far ahead of the loop that launches with programmatic edges)
     if (L.err == cudaSuccess) L.err = cudaMemcpyAsync(v->x_t, v->noise, (size_t)n * d.action_dim * 4, cudaMemcpyDeviceToDevice, L.stream);
+    auto layernorm = [&](const __nv_bfloat16* w, const __nv_bfloat16* b) {       // v_resid -> v_xn
+        if (Hv <= 1024 && Hv % 4 == 0)
+            L.launch(layernorm_rows_warp_kernel, dim3((NV + 7) / 8), dim3(256), 0, (const float*)v->v_resid, w, b, v->v_xn, NV, Hv, d.ln_eps);
+        else
+            L.launch(layernorm_rows_kernel, dim3(NV), dim3(256), 0, (const float*)v->v_resid, w, b, v->v_xn, Hv, d.ln_eps);
+    };
     // ---- vision tower ----
     L.launch(vla_patch_rows_kernel, dim3(NV), dim3(256), 0, (const float*)v->images, v->rows, d.image_size, d.patch);
     L.launch(vla_tile_rows_kernel, dim3(NV), dim3(256), 0, (const __nv_bfloat16*)v->pos, v->v_resid, v->patches, Hv);
     gemm(GemmEpi::Residual, v->rows, 0, v->patch_w, v->patch_b, nullptr, v->v_resid, NV, Hv, v->pd);
     for (const VitLayer& b : v->vit) {
-        L.launch(layernorm_rows_kernel, dim3(NV), dim3(256), 0, (const float*)v->v_resid, (const __nv_bfloat16*)b.ln1_w,
-                 (const __nv_bfloat16*)b.ln1_b, v->v_xn, Hv, d.ln_eps);
+        layernorm(b.ln1_w, b.ln1_b);
         gemm(GemmEpi::Bf16Bias, v->v_xn, 0, b.qkv_w, b.qkv_b, v->v_qkv, nullptr, NV, 3 * Hv, Hv);
         attend(v->v_qkv, 3 * Hv, v->v_qkv + Hv, v->v_qkv + 2 * Hv, 3 * Hv, v->v_attn, NV, d.vit_heads, d.vit_heads, v->v_lo, v->v_hi);
         gemm(GemmEpi::Residual, v->v_attn, 0, b.o_w, b.o_b, nullptr, v->v_resid, NV, Hv, Hv);
-        L.launch(layernorm_rows_kernel, dim3(NV), dim3(256), 0, (const float*)v->v_resid, (const __nv_bfloat16*)b.ln2_w,
-                 (const __nv_bfloat16*)b.ln2_b, v->v_xn, Hv, d.ln_eps);
+        layernorm(b.ln2_w, b.ln2_b);
         gemm(GemmEpi::Bf16GeluTanh, v->v_xn, 0, b.fc1_w, b.fc1_b, v->v_act, nullptr, NV, d.vit_mlp, Hv);
         gemm(GemmEpi::Residual, v->v_act, 0, b.fc2_w, b.fc2_b, nullptr, v->v_resid, NV, Hv, d.vit_mlp);
     }
-    L.launch(layernorm_rows_kernel, dim3(NV), dim3(256), 0, (const float*)v->v_resid, (const __nv_bfloat16*)v->post_w,
-             (const __nv_bfloat16*)v->post_b, v->v_xn, Hv, d.ln_eps);
+    layernorm(v->post_w, v->post_b);
     L.launch(vla_pixel_shuffle_kernel, dim3(n_img_tok), dim3(256), 0, (const __nv_bfloat16*)v->v_xn, v->shuf, v->side, d.shuffle, Hv);
     gemm(GemmEpi::F32, v->shuf, 0, v->conn_w, nullptr, nullptr, v->resid, n_img_tok, H, SH);
 

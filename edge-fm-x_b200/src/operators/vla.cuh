@@ -72,6 +72,55 @@ __global__ void __launch_bounds__(256) layernorm_rows_kernel(const float* __rest
         yr[i] = __float2bfloat16_rn((xr[i] - mu) * rs * __bfloat162float(w[i]) + __bfloat162float(b[i]));
 }
 
+// The same LayerNorm with one warp per row and the row held in registers (width <= 1024, width % 4 == 0): one read of
+// x, no block barriers.  Eight rows per 256-thread block.
+__global__ void __launch_bounds__(256) layernorm_rows_warp_kernel(const float* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                                                                 const __nv_bfloat16* __restrict__ b, __nv_bfloat16* __restrict__ y,
+                                                                 int rows, int width, float eps) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31, row = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)row * width);
+    const int n4 = width >> 2;
+    float4 v[8];
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int c = lane + 32 * i;
+        v[i] = c < n4 ? xr[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+        s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    const float mu = s / (float)width;
+    float q = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        if (lane + 32 * i < n4) {
+            const float a = v[i].x - mu, bb = v[i].y - mu, c = v[i].z - mu, d = v[i].w - mu;
+            q += (a * a + bb * bb) + (c * c + d * d);
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) q += __shfl_xor_sync(0xffffffffu, q, o);
+    const float rs = rsqrtf(q / (float)width + eps);
+    uint2* yr = reinterpret_cast<uint2*>(y + (size_t)row * width);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int c = lane + 32 * i;
+        if (c < n4) {
+            const uint2 wv = *reinterpret_cast<const uint2*>(w + 4 * c), bv = *reinterpret_cast<const uint2*>(b + 4 * c);
+            const float w0 = __uint_as_float(wv.x << 16), w1 = __uint_as_float(wv.x & 0xffff0000u);
+            const float w2 = __uint_as_float(wv.y << 16), w3 = __uint_as_float(wv.y & 0xffff0000u);
+            const float b0 = __uint_as_float(bv.x << 16), b1 = __uint_as_float(bv.x & 0xffff0000u);
+            const float b2 = __uint_as_float(bv.y << 16), b3 = __uint_as_float(bv.y & 0xffff0000u);
+            yr[c] = make_uint2(pack_bf16((v[i].x - mu) * rs * w0 + b0, (v[i].y - mu) * rs * w1 + b1),
+                               pack_bf16((v[i].z - mu) * rs * w2 + b2, (v[i].w - mu) * rs * w3 + b3));
+        }
+    }
+}
+
 // Pixel shuffle by factor s of every image: x [n_img * side * side, d] -> out [n_img * (side/s)^2, s*s*d];
 // output token (R, C), channel (ry * s + cx) * d + e  <-  patch (R*s + ry, C*s + cx), channel e.
 // One block per output token; d % 8 == 0.

@@ -69,12 +69,13 @@ __global__ void __launch_bounds__(256) fold_norm_weight_kernel(__nv_bfloat16* __
 
 // TILES: 8-column tiles per block (1 or 2; SwiGlu needs 2: a gate tile and its up tile; QkvRope needs 2: a tile and
 // the tile 32 columns further in the same head).
-template <SkinnyEpi EPI, int TILES, bool NORM = false>
-__global__ void __launch_bounds__(kSkinnyThreads) skinny_gemm_kernel(const SkinnyParams p) {
-    constexpr int GROUP = 8 / TILES;                       // warps per tile
+// NWARPS: warps per block (8, or 16 for long K so that a warp's share of the k-chunks fits one batch of requests).
+template <SkinnyEpi EPI, int TILES, bool NORM = false, int NWARPS = 8>
+__global__ void __launch_bounds__(NWARPS * 32) skinny_gemm_kernel(const SkinnyParams p) {
+    constexpr int GROUP = NWARPS / TILES;                  // warps per tile
     constexpr int BATCH = 4;                               // weight vectors requested ahead per warp
-    __shared__ float red[8][64][8];
-    __shared__ float ssq[NORM ? 8 : 1][64];
+    __shared__ float red[NWARPS][64][8];
+    __shared__ float ssq[NORM ? NWARPS : 1][64];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
     pdl_launch_dependents();
     pdl_wait();            // no-ops unless launched with programmatic stream serialization

@@ -63,8 +63,14 @@ struct efm_b200_ctx {
     // [exchange count at byte 64 | block ticket at 68 | receive buffer at 256: 2 x tp x H words {fp32, count}],
     // mapped into every other rank with CUDA IPC.  peer_base[r] is rank r's allocation as seen from here.
     char* tp_xchg = nullptr;
-    size_t tp_prefill_off = 0;            // byte offset of the prefill slots [2][tp][max_s * H] fp32 (flags [2][8] at byte 128,
-                                          // prefill exchange count at 192, ticket at 196)
+    // prefill exchange (reduce-scatter + all-gather over peer stores): exchange count at byte 96, ticket at 100,
+    // scatter flags [2][8] at 128, gather flags [2][8] at 192; receive slots [2][tp][tp_slot_floats] fp32 at
+    // tp_prefill_off (one slot = the rows one rank owns: ceil(max_s / tp) x H), gather buffers [2][max_s x H] at tp_gather_off
+    size_t tp_prefill_off = 0, tp_gather_off = 0, tp_slot_floats = 0;
+    double tp_timeout_s = 300.0;          // host-side limit of a synchronising call on a tensor-parallel context
+    unsigned long long peer_wait_ns = 0;  // total wait budget of one kernel on its peers (0 = built-in default)
+    int* error_host = nullptr;            // mapped host mirror of DecodeState.error, written by a kernel that gave up a
+                                          // wait, polled by decode_steps between graph launches (same address on both sides)
     char* peer_base[8] = {};
     bool peers_ready = false;
     float* ybuf = nullptr;                // [max_s, H] fp32 partial outputs of row-parallel linears

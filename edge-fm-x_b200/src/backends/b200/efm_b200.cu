@@ -2,7 +2,9 @@
 // ingestion (fusing q|k|v and interleaving gate/up as the kernels expect), KV slots, the
 // prefill and decode entry points with CUDA-graph capture of the decode step, and the
 // single-operator entry points used by the parity tests.
+#include <atomic>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <cmath>
 #include <new>
@@ -79,6 +81,23 @@ Launcher make_launcher(efm_b200_ctx* c) {
     L.gemm_ws_floats = c->gemm_ws_floats;
     L.num_sms = c->num_sms;
     return L;
+}
+
+// Stream synchronisation of a context.  Tensor-parallel contexts do not block inside the driver: they poll the stream
+// and NCCL's asynchronous error state, and give up after tp_timeout_s (the communicator is then aborted and gone).
+int stream_ready(void* stream) { return cudaStreamQuery(static_cast<cudaStream_t>(stream)) != cudaErrorNotReady; }
+efm_status ctx_sync(efm_b200_ctx* c) {
+    if (c->tp_size > 1 && c->nccl_comm != nullptr) {
+        std::string what;
+        const int r = tp_host_wait(c->nccl_comm, stream_ready, c->stream, c->tp_timeout_s, &what);
+        if (r != 0) {
+            c->nccl_comm = nullptr;       // aborted
+            return fail(c, r == 2 ? EFM_ERR_DEVICE_WAIT : EFM_ERR_CUDA, what);
+        }
+    }
+    cudaError_t e = cudaStreamSynchronize(c->stream);
+    if (e != cudaSuccess) return cuda_fail(c, e, "cudaStreamSynchronize");
+    return EFM_OK;
 }
 
 enum : uint32_t { kQw = 1, kQb = 2, kKw = 4, kKb = 8, kVw = 16, kVb = 32, kO = 64, kGate = 128, kUp = 256,
@@ -178,9 +197,21 @@ efm_status efm_b200_create(const efm_model_desc* desc, int32_t device_id, int32_
         EFM_TRY(dev_alloc(c, &c->ybuf, S * H));
         EFM_TRY(dev_alloc(c, &c->ysum, S * H));
         EFM_TRY(dev_alloc(c, &c->logits_l, (size_t)c->vocab_l));
-        // zeroed: header (counts, tickets, prefill flags) | decode {value, count} words | prefill fp32 slots
+        // zeroed: header (counts, tickets, prefill flags) | decode {value, count} words | prefill receive slots | gather buffers
         c->tp_prefill_off = 256 + (((size_t)2 * tp_size * H * 8 + 255) & ~(size_t)255);
-        EFM_TRY(dev_alloc(c, &c->tp_xchg, c->tp_prefill_off + (size_t)2 * tp_size * S * H * sizeof(float)));
+        c->tp_slot_floats = ((S + tp_size - 1) / tp_size) * H;
+        c->tp_gather_off = c->tp_prefill_off + (((size_t)2 * tp_size * c->tp_slot_floats * sizeof(float) + 255) & ~(size_t)255);
+        EFM_TRY(dev_alloc(c, &c->tp_xchg, c->tp_gather_off + (size_t)2 * S * H * sizeof(float)));
+        EFM_TRY(cudaHostAlloc(reinterpret_cast<void**>(&c->error_host), sizeof(int), cudaHostAllocMapped));
+        *c->error_host = 0;
+        if (const char* ms = std::getenv("EFM_B200_PEER_WAIT_MS")) {
+            const long v = std::atol(ms);
+            if (v > 0) c->peer_wait_ns = (unsigned long long)v * 1000000ull;
+        }
+        if (const char* ts = std::getenv("EFM_B200_TP_TIMEOUT_S")) {
+            const double v = std::atof(ts);
+            if (v > 0) c->tp_timeout_s = v;
+        }
     }
     EFM_TRY(dev_alloc(c, &c->final_norm, H));
     c->layers.resize(d.num_layers);
@@ -254,6 +285,7 @@ efm_status efm_b200_destroy(efm_b200_ctx* c) {
     for (auto& ev : c->events)
         if (ev != nullptr) cudaEventDestroy(ev);
     if (c->stream != nullptr) cudaStreamDestroy(c->stream);
+    if (c->error_host != nullptr) cudaFreeHost(c->error_host);
     delete c;
     return EFM_OK;
 }
@@ -274,9 +306,32 @@ efm_status efm_b200_tp_init(efm_b200_ctx* c, const void* id128) {
     const NcclApi& api = nccl_api();
     if (!api.ok) return fail(c, EFM_ERR_UNSUPPORTED, api.error);
     EFM_CK(c, cudaSetDevice(c->device));
+    // In-switch (NVLS) collectives bind this rank's buffers to an NVLink multicast object; a rank that dies while bound
+    // can fault its peers' GPUs.  Off unless the caller's environment already decided.
+    setenv("NCCL_NVLS_ENABLE", "0", 0);
     const int r = api.comm_init_rank(&c->nccl_comm, c->tp_size, id128, c->tp_rank);
     if (r != 0) { c->nccl_comm = nullptr; return fail(c, EFM_ERR_CUDA, std::string("ncclCommInitRank: ") + api.error_string(r)); }
     return EFM_OK;
+}
+
+efm_status efm_b200_tp_set_wait_limit(efm_b200_ctx* c, int64_t device_wait_us, double host_timeout_s) {
+    if (c == nullptr) return fail(c, EFM_ERR_INVALID_ARGUMENT, "null context");
+    if (device_wait_us < 0 || host_timeout_s < 0) return fail(c, EFM_ERR_INVALID_ARGUMENT, "limits must be >= 0 (0 keeps the current value)");
+    bool changed = false;
+    if (device_wait_us > 0) { changed = c->peer_wait_ns != (unsigned long long)device_wait_us * 1000ull; c->peer_wait_ns = (unsigned long long)device_wait_us * 1000ull; }
+    if (host_timeout_s > 0) c->tp_timeout_s = host_timeout_s;
+    if (changed)     // the device limit is a kernel argument baked into the captured step
+        for (auto& kv : c->slots)
+            if (kv.second.graph != nullptr) { cudaGraphExecDestroy(kv.second.graph); kv.second.graph = nullptr; }
+    return EFM_OK;
+}
+
+efm_status efm_b200_tp_host_wait(void* nccl_comm, int (*ready)(void*), void* arg, double timeout_s) {
+    if (ready == nullptr || !(timeout_s >= 0)) return fail(nullptr, EFM_ERR_INVALID_ARGUMENT, "tp_host_wait: bad arguments");
+    std::string what;
+    const int r = tp_host_wait(nccl_comm, ready, arg, timeout_s, &what);
+    if (r == 0) return EFM_OK;
+    return fail(nullptr, r == 2 ? EFM_ERR_DEVICE_WAIT : EFM_ERR_CUDA, what);
 }
 
 efm_status efm_b200_tp_peer_export(efm_b200_ctx* c, void* handle64) {
@@ -547,6 +602,7 @@ efm_status efm_b200_decode_begin(efm_b200_ctx* c, int32_t slot, int32_t kv_len, 
     static_assert(offsetof(DecodeState, kv_len) == 4 && sizeof(tail) == 24, "DecodeState layout");
     EFM_CK(c, cudaMemcpyAsync(reinterpret_cast<char*>(c->state) + 4, &tail, sizeof(tail), cudaMemcpyHostToDevice, c->stream));
     EFM_CK(c, cudaMemsetAsync(c->mega_barrier, 0, 4 * sizeof(unsigned int), c->stream));   // barrier counters, abort flag
+    if (c->error_host != nullptr) *reinterpret_cast<volatile int*>(c->error_host) = 0;
     c->bound_slot = slot;
     return EFM_OK;
 }
@@ -599,6 +655,10 @@ efm_status efm_b200_decode_steps(efm_b200_ctx* c, int32_t n_steps, int32_t use_g
     const efm_status st = ensure_graph(c, s);
     if (st != EFM_OK) return st;
     for (int i = 0; i < n_steps; ++i) {
+        // a kernel of an earlier step gave up waiting for a peer: queue nothing more behind it
+        if (c->error_host != nullptr && *reinterpret_cast<volatile int*>(c->error_host) != 0)
+            return fail(c, EFM_ERR_DEVICE_WAIT, "a tensor-parallel peer did not answer within the wait limit; decode stopped after " +
+                                                    std::to_string(i) + " queued steps");
         EFM_CK(c, cudaGraphLaunch(s.graph, c->stream));
         c->launches += s.graph_nodes;
     }
@@ -608,9 +668,10 @@ efm_status efm_b200_decode_steps(efm_b200_ctx* c, int32_t n_steps, int32_t use_g
 static efm_status check_device_state(efm_b200_ctx* c) {
     DecodeState st{};
     EFM_CK(c, cudaMemcpyAsync(&st, c->state, sizeof(st), cudaMemcpyDeviceToHost, c->stream));
-    EFM_CK(c, cudaStreamSynchronize(c->stream));
+    { const efm_status s = ctx_sync(c); if (s != EFM_OK) return s; }
     if (st.error != 0) {
         int zero = 0;
+        if (c->error_host != nullptr) *reinterpret_cast<volatile int*>(c->error_host) = 0;
         cudaMemcpyAsync(&c->state->error, &zero, 4, cudaMemcpyHostToDevice, c->stream);
         return fail(c, EFM_ERR_DEVICE_WAIT, "a kernel refused an out-of-range cache row or abandoned a bounded wait (device status " + std::to_string(st.error) + ")");
     }
@@ -630,14 +691,12 @@ efm_status efm_b200_read_logits(efm_b200_ctx* c, float* host_out, int32_t n) {
     if (n < 0 || n > c->d.vocab) return fail(c, EFM_ERR_INVALID_ARGUMENT, "n exceeds vocab");
     EFM_CK(c, cudaSetDevice(c->device));
     EFM_CK(c, cudaMemcpyAsync(host_out, c->logits, (size_t)n * 4, cudaMemcpyDeviceToHost, c->stream));
-    EFM_CK(c, cudaStreamSynchronize(c->stream));
-    return EFM_OK;
+    return ctx_sync(c);
 }
 
 efm_status efm_b200_synchronize(efm_b200_ctx* c) {
     if (c == nullptr) return fail(c, EFM_ERR_INVALID_ARGUMENT, "null context");
-    EFM_CK(c, cudaStreamSynchronize(c->stream));
-    return EFM_OK;
+    return ctx_sync(c);
 }
 
 efm_status efm_b200_event_record(efm_b200_ctx* c, int32_t idx) {
@@ -761,6 +820,39 @@ efm_status efm_b200_op_gemv(const void* w, const void* x, const void* norm_w, fl
     Launcher L; L.pdl = false;
     if (residual != nullptr) launch_gemv<Epi::Residual>(L, p, sms); else launch_gemv<Epi::Plain>(L, p, sms);
     return op_finish(L);
+}
+
+efm_status efm_b200_op_gemv_peer_consume(const void* w, const void* resid_f32, const void* norm_w, float eps, const void* parts,
+                                         int32_t n_parts, uint32_t want_count, int64_t wait_limit_us, void* y_bf16,
+                                         void* resid_out_f32, int32_t n, int32_t k) {
+    int sms = 148;
+    efm_status st = op_prepare(&sms);
+    if (st != EFM_OK) return st;
+    if (w == nullptr || resid_f32 == nullptr || norm_w == nullptr || parts == nullptr || y_bf16 == nullptr || resid_out_f32 == nullptr ||
+        resid_out_f32 == resid_f32 || n_parts < 1 || n_parts > kMaxPeers || want_count == 0 || wait_limit_us <= 0 || n <= 0 || n % 2 ||
+        k <= 0 || k % 8)
+        return fail(nullptr, EFM_ERR_INVALID_ARGUMENT, "op_gemv_peer_consume: bad arguments");
+    int* error = nullptr;
+    cudaError_t e = cudaMalloc(&error, sizeof(int));
+    if (e == cudaSuccess) e = cudaMemset(error, 0, sizeof(int));
+    if (e != cudaSuccess) { cudaFree(error); return cuda_fail(nullptr, e, "op_gemv_peer_consume scratch"); }
+    GemvParams p{};
+    p.W = (const __nv_bfloat16*)w; p.N = n; p.K = k; p.n_items = n / 2;
+    p.prologue = kProRmsNorm;
+    p.xr = (const float*)resid_f32; p.norm_w = (const __nv_bfloat16*)norm_w; p.eps = eps;
+    p.resid_out = (float*)resid_out_f32;
+    p.addend_parts = (const uint2*)parts; p.n_parts = n_parts; p.want_override = want_count;
+    p.error = error; p.wait_ns = (unsigned long long)wait_limit_us * 1000ull;
+    p.y = (__nv_bfloat16*)y_bf16;
+    Launcher L; L.pdl = false;
+    launch_gemv<Epi::Plain>(L, p, sms);
+    st = op_finish(L);
+    int raised = 0;
+    if (st == EFM_OK && cudaMemcpy(&raised, error, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) st = fail(nullptr, EFM_ERR_CUDA, "reading the status word");
+    cudaFree(error);
+    if (st == EFM_OK && raised != 0)
+        return fail(nullptr, EFM_ERR_DEVICE_WAIT, "the wait for the peers' words ran out (device status " + std::to_string(raised) + ")");
+    return st;
 }
 
 efm_status efm_b200_op_gemm(const void* x, const void* w, const void* bias, void* y_bf16, int32_t m, int32_t n, int32_t k) {
@@ -889,7 +981,7 @@ constexpr size_t kNoAllocPartMl = (size_t)kNoAllocMaxQHeads * kMaxSplits * 2;
 constexpr size_t kNoAllocWords = kNoAllocPartO + kNoAllocPartMl + kNoAllocMaxKvHeads;     // ~1.06 MB
 static __device__ __align__(256) float g_noalloc_scratch[kNoAllocWords];
 constexpr int kNoAllocMaxDevices = 64;
-float* g_noalloc_ptr[kNoAllocMaxDevices] = {};
+std::atomic<float*> g_noalloc_ptr[kNoAllocMaxDevices];     // zero-initialised; filled once per device, any thread
 }  // namespace
 
 efm_status efm_b200_op_decode_attention_noalloc(const void* q, const void* k_cache, const void* v_cache, void* out_bf16,
@@ -904,18 +996,19 @@ efm_status efm_b200_op_decode_attention_noalloc(const void* q, const void* k_cac
     if (q_heads * head_dim > kNoAllocMaxQD || kv_heads > kNoAllocMaxKvHeads || q_heads > kNoAllocMaxQHeads)
         return fail(nullptr, EFM_ERR_UNSUPPORTED,
                     "op_decode_attention_noalloc: shape exceeds the built-in scratch (q_heads * head_dim <= 4096, "
-                    "kv_heads <= 16); use efm_b200_op_decode_attention");
+                    "q_heads <= 64, kv_heads <= 16); use efm_b200_op_decode_attention");
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return cuda_fail(nullptr, e, "cudaGetDevice");
     if (dev < 0 || dev >= kNoAllocMaxDevices) return fail(nullptr, EFM_ERR_UNSUPPORTED, "device index above 63");
-    if (g_noalloc_ptr[dev] == nullptr) {      // once per device, with that device current
+    float* scratch = g_noalloc_ptr[dev].load(std::memory_order_acquire);
+    if (scratch == nullptr) {      // once per device, with that device current (two threads racing here store the same address)
         float* ptr = nullptr;
         e = cudaGetSymbolAddress((void**)&ptr, g_noalloc_scratch);
         if (e != cudaSuccess || ptr == nullptr) return cuda_fail(nullptr, e, "cudaGetSymbolAddress(scratch)");
-        g_noalloc_ptr[dev] = ptr;
+        g_noalloc_ptr[dev].store(ptr, std::memory_order_release);
+        scratch = ptr;
     }
-    float* scratch = g_noalloc_ptr[dev];
     unsigned int* tickets = reinterpret_cast<unsigned int*>(scratch + kNoAllocPartO + kNoAllocPartMl);
     const AttnPlan plan = plan_decode_attention(max_tokens, kv_heads, sms);
     e = cudaMemsetAsync(tickets, 0, kNoAllocMaxKvHeads * sizeof(unsigned int), nullptr);

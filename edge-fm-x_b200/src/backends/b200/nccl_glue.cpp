@@ -3,8 +3,10 @@
 #include <dlfcn.h>
 #include <nccl.h>
 
+#include <chrono>
 #include <cstdlib>
 #include <cstring>
+#include <thread>
 
 namespace efm {
 
@@ -18,6 +20,8 @@ decltype(&ncclGetErrorString) p_err = nullptr;
 decltype(&ncclBroadcast) p_bcast = nullptr;
 decltype(&ncclGroupStart) p_group_start = nullptr;
 decltype(&ncclGroupEnd) p_group_end = nullptr;
+decltype(&ncclCommGetAsyncError) p_async = nullptr;
+decltype(&ncclCommAbort) p_abort = nullptr;
 
 int get_unique_id(void* id128) {
     ncclUniqueId id;
@@ -34,6 +38,13 @@ int comm_init_rank(void** comm, int nranks, const void* id128, int rank) {
     return (int)r;
 }
 int comm_destroy(void* comm) { return (int)p_destroy(static_cast<ncclComm_t>(comm)); }
+int comm_async_error(void* comm, int* async_result) {
+    ncclResult_t st = ncclSuccess;
+    const ncclResult_t r = p_async(static_cast<ncclComm_t>(comm), &st);
+    *async_result = (int)st;
+    return (int)r;
+}
+int comm_abort(void* comm) { return (int)p_abort(static_cast<ncclComm_t>(comm)); }
 int all_reduce_f32_sum(const void* send, void* recv, size_t count, void* comm, cudaStream_t stream) {
     return (int)p_all_reduce(send, recv, count, ncclFloat32, ncclSum, static_cast<ncclComm_t>(comm), stream);
 }
@@ -74,13 +85,18 @@ const NcclApi& nccl_api() {
         p_bcast = reinterpret_cast<decltype(p_bcast)>(dlsym(h, "ncclBroadcast"));
         p_group_start = reinterpret_cast<decltype(p_group_start)>(dlsym(h, "ncclGroupStart"));
         p_group_end = reinterpret_cast<decltype(p_group_end)>(dlsym(h, "ncclGroupEnd"));
-        if (!p_get_id || !p_init || !p_destroy || !p_all_reduce || !p_all_gather || !p_err || !p_bcast || !p_group_start || !p_group_end) {
+        p_async = reinterpret_cast<decltype(p_async)>(dlsym(h, "ncclCommGetAsyncError"));
+        p_abort = reinterpret_cast<decltype(p_abort)>(dlsym(h, "ncclCommAbort"));
+        if (!p_get_id || !p_init || !p_destroy || !p_all_reduce || !p_all_gather || !p_err || !p_bcast || !p_group_start || !p_group_end || !p_async ||
+            !p_abort) {
             a.error = "libnccl.so.2 lacks an expected symbol";
             return a;
         }
         a.get_unique_id = get_unique_id;
         a.comm_init_rank = comm_init_rank;
         a.comm_destroy = comm_destroy;
+        a.comm_async_error = comm_async_error;
+        a.comm_abort = comm_abort;
         a.all_reduce_f32_sum = all_reduce_f32_sum;
         a.all_gather_f32 = all_gather_f32;
         a.all_gather_v_bytes = all_gather_v_bytes;
@@ -89,6 +105,33 @@ const NcclApi& nccl_api() {
         return a;
     }();
     return api;
+}
+
+// Host-side wait of a tensor-parallel context: `ready` about once per millisecond, NCCL's asynchronous error state
+// in between, a hard limit on the whole wait.  0 = ready, 1 = NCCL reported an error, 2 = timed out; in both failure
+// cases the communicator has been aborted, so that collectives stuck on a lost rank leave the GPU.
+int tp_host_wait(void* comm, int (*ready)(void*), void* arg, double timeout_s, std::string* what) {
+    const NcclApi& api = nccl_api();
+    const auto t0 = std::chrono::steady_clock::now();
+    for (;;) {
+        if (ready(arg) != 0) return 0;
+        if (comm != nullptr && api.ok) {
+            int async = 0;
+            const int r = api.comm_async_error(comm, &async);
+            if (r != 0 || async != 0) {
+                if (what != nullptr) *what = std::string("NCCL reported an asynchronous error: ") + api.error_string(r != 0 ? r : async);
+                api.comm_abort(comm);
+                return 1;
+            }
+        }
+        const double waited = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+        if (waited > timeout_s) {
+            if (what != nullptr) *what = "tensor-parallel wait timed out after " + std::to_string(timeout_s) + " s (a rank is lost or out of step)";
+            if (comm != nullptr && api.ok) api.comm_abort(comm);
+            return 2;
+        }
+        std::this_thread::sleep_for(std::chrono::microseconds(waited < 0.05 ? 50 : 1000));
+    }
 }
 
 }  // namespace efm

@@ -15,6 +15,8 @@ struct NcclApi {
     int (*get_unique_id)(void* id128) = nullptr;
     int (*comm_init_rank)(void** comm, int nranks, const void* id128, int rank) = nullptr;   // wrapper, see .cpp
     int (*comm_destroy)(void* comm) = nullptr;
+    int (*comm_async_error)(void* comm, int* async_result) = nullptr;   // ncclCommGetAsyncError
+    int (*comm_abort)(void* comm) = nullptr;                            // ncclCommAbort
     int (*all_reduce_f32_sum)(const void* send, void* recv, size_t count, void* comm, cudaStream_t stream) = nullptr;
     int (*all_gather_f32)(const void* send, void* recv, size_t count, void* comm, cudaStream_t stream) = nullptr;
     // all-gather with a different byte count per rank: rank r's `send` (counts[r] bytes) lands at recv_base +
@@ -25,5 +27,9 @@ struct NcclApi {
 };
 
 const NcclApi& nccl_api();
+
+// Polls ready(arg) (non-zero = done) and the communicator's asynchronous error state until done, error or timeout.
+// Returns 0 ready / 1 NCCL error / 2 timeout; on 1 and 2 the communicator was aborted and *what says why.
+int tp_host_wait(void* comm, int (*ready)(void*), void* arg, double timeout_s, std::string* what);
 
 }  // namespace efm

@@ -14,6 +14,23 @@
 
 namespace edge_fm {
 
+namespace {
+// bytes per element of the safetensors dtype names; 0 = unknown (such a tensor is kept, its size is not checked)
+size_t dtype_bytes(const std::string& d) {
+    if (d == "F64" || d == "I64" || d == "U64") return 8;
+    if (d == "F32" || d == "I32" || d == "U32") return 4;
+    if (d == "BF16" || d == "F16" || d == "I16" || d == "U16") return 2;
+    if (d == "I8" || d == "U8" || d == "BOOL" || d == "F8_E4M3" || d == "F8_E5M2") return 1;
+    return 0;
+}
+// unmaps when the constructor leaves by exception (the destructor does not run then)
+struct MapGuard {
+    void* map;
+    size_t size;
+    ~MapGuard() { if (map != nullptr) munmap(map, size); }
+};
+}  // namespace
+
 SafeTensorsFile::SafeTensorsFile(const std::string& path) {
     const int fd = ::open(path.c_str(), O_RDONLY);
     if (fd < 0) throw ModelNotLoadedError("Cannot open weights file: " + path);
@@ -29,6 +46,7 @@ SafeTensorsFile::SafeTensorsFile(const std::string& path) {
         map_ = nullptr;
         throw ModelNotLoadedError("mmap failed for: " + path);
     }
+    MapGuard guard{map_, size_};
     const unsigned char* base = static_cast<const unsigned char*>(map_);
     uint64_t header_len = 0;
     for (int i = 7; i >= 0; --i) header_len = (header_len << 8) | base[i];     // little-endian u64
@@ -57,8 +75,19 @@ SafeTensorsFile::SafeTensorsFile(const std::string& path) {
             throw ModelNotLoadedError("Tensor '" + kv.first + "' points outside the file (truncated checkpoint?): " + path);
         e.data = base + data_start + b;
         e.nbytes = en - b;
+        // the loader copies shape-derived byte counts: a record whose byte range disagrees with its shape would be
+        // read past its end
+        size_t want = dtype_bytes(e.dtype);
+        for (const int64_t d : e.shape) {
+            if (d < 0) throw ModelNotLoadedError("Tensor '" + kv.first + "' has a negative dimension in " + path);
+            want *= (size_t)d;
+        }
+        if (dtype_bytes(e.dtype) != 0 && want != e.nbytes)
+            throw ModelNotLoadedError("Tensor '" + kv.first + "' spans " + std::to_string(e.nbytes) + " bytes but its shape and dtype need " +
+                                      std::to_string(want) + " (malformed or mis-sharded checkpoint): " + path);
         entries_.push_back(std::move(e));
     }
+    guard.map = nullptr;      // construction succeeded: the destructor owns the mapping
 }
 
 SafeTensorsFile::~SafeTensorsFile() {

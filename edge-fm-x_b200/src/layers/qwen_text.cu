@@ -191,36 +191,56 @@ static void peers_consumer(const efm_b200_ctx& c, GemvParams& p, int parity) {
     p.n_parts = c.tp_size;
     p.epoch = reinterpret_cast<unsigned int*>(c.tp_xchg + 64);
     p.error = &c.state->error;
+    p.error_host = c.error_host;
+    p.wait_ns = c.peer_wait_ns;
 }
 
 // Tensor-parallel prefill: sum of the row-parallel partial c.ybuf [S, H] over the ranks, added to the residual.
-// With imported peer buffers: push the partial into every rank's slot, then wait for all ranks' flags and add the
-// slots in rank order; otherwise ncclAllReduce + add.
+// With imported peer buffers: reduce-scatter + all-gather over peer stores (operators/prefill.cuh); otherwise
+// ncclAllReduce + add.  Header words of the exchange allocation (ctx.h): prefill exchange count at byte 96, ticket at
+// 100, scatter flags [2][8] at 128, gather flags [2][8] at 192.
 static void tp_prefill_sum(efm_b200_ctx& c, Launcher& L, int S, int parity) {
     const size_t H = (size_t)c.d.hidden, n = (size_t)S * H;
-    const int grid = (int)std::min<size_t>((n / 4 + 255) / 256, (size_t)c.num_sms * 8);
     if (!c.peers_ready) {
         tp_all_reduce(c, L, c.ybuf, c.ysum, n);
         L.launch(add_rows_kernel, dim3(std::min<size_t>((n / 2 + 255) / 256, (size_t)c.num_sms * 8)), dim3(256), 0, c.resid,
                  (const float*)c.ysum, n / 2);
         return;
     }
-    const size_t slot = (size_t)c.max_s * H;                                   // floats per (parity, rank) slot
-    PeerPushParams pp{};
-    pp.src = reinterpret_cast<const float4*>(c.ybuf);
-    pp.n_peers = c.tp_size;
-    pp.n4 = n / 4;
-    for (int r = 0; r < c.tp_size; ++r) {
-        pp.dst[r] = reinterpret_cast<float4*>(reinterpret_cast<float*>(c.peer_base[r] + c.tp_prefill_off) + ((size_t)parity * c.tp_size + c.tp_rank) * slot);
-        pp.flag[r] = reinterpret_cast<unsigned int*>(c.peer_base[r] + 128) + parity * 8 + c.tp_rank;
+    const int tp = c.tp_size;
+    const size_t slot = c.tp_slot_floats;                                    // floats per (parity, rank) receive slot
+    PeerXchgParams pp{};
+    pp.src = c.ybuf;
+    pp.n_peers = tp;
+    pp.rank = c.tp_rank;
+    pp.S = S;
+    pp.H = (int)H;
+    pp.rows_per = (S + tp - 1) / tp;
+    pp.slot_floats = slot;
+    pp.epoch = reinterpret_cast<unsigned int*>(c.tp_xchg + 96);
+    pp.ticket = reinterpret_cast<unsigned int*>(c.tp_xchg + 100);
+    pp.error = &c.state->error;
+    pp.error_host = c.error_host;
+    pp.wait_ns = c.peer_wait_ns;
+    pp.recv_local = reinterpret_cast<const float*>(c.tp_xchg + c.tp_prefill_off) + (size_t)parity * tp * slot;
+    pp.gather_local = reinterpret_cast<const float*>(c.tp_xchg + c.tp_gather_off) + (size_t)parity * c.max_s * H;
+    pp.resid = c.resid;
+    for (int r = 0; r < tp; ++r) {
+        pp.recv[r] = reinterpret_cast<float*>(c.peer_base[r] + c.tp_prefill_off) + ((size_t)parity * tp + c.tp_rank) * slot;
+        pp.gather[r] = reinterpret_cast<float*>(c.peer_base[r] + c.tp_gather_off) + (size_t)parity * c.max_s * H;
     }
-    pp.epoch = reinterpret_cast<unsigned int*>(c.tp_xchg + 192);
-    pp.ticket = reinterpret_cast<unsigned int*>(c.tp_xchg + 196);
-    L.launch(peer_push_rows_kernel, dim3(grid), dim3(256), 0, pp);
-    L.launch(peer_add_rows_kernel, dim3(grid), dim3(256), 0, reinterpret_cast<float4*>(c.resid),
-             reinterpret_cast<const float4*>(reinterpret_cast<const float*>(c.tp_xchg + c.tp_prefill_off) + (size_t)parity * c.tp_size * slot),
-             reinterpret_cast<const unsigned int*>(c.tp_xchg + 128) + parity * 8, c.tp_size, n / 4, slot / 4,
-             (const unsigned int*)reinterpret_cast<unsigned int*>(c.tp_xchg + 192), &c.state->error);
+    const int grid_all = (int)std::min<size_t>((n / 4 + 255) / 256, (size_t)c.num_sms * 8);
+    const int grid_own = (int)std::min<size_t>(((size_t)pp.rows_per * H / 4 + 255) / 256, (size_t)c.num_sms * 8);
+    // 1. scatter (publishes this rank's scatter flag on every rank)
+    for (int r = 0; r < tp; ++r) pp.flag[r] = reinterpret_cast<unsigned int*>(c.peer_base[r] + 128) + parity * 8 + c.tp_rank;
+    L.launch(peer_scatter_rows_kernel, dim3(grid_all), dim3(256), 0, pp);
+    // 2. reduce own rows, store them into every rank's gather buffer (waits for the scatter flags, publishes gather flags)
+    pp.flags_local = reinterpret_cast<const unsigned int*>(c.tp_xchg + 128) + parity * 8;
+    for (int r = 0; r < tp; ++r) pp.flag[r] = reinterpret_cast<unsigned int*>(c.peer_base[r] + 192) + parity * 8 + c.tp_rank;
+    L.launch(peer_reduce_gather_kernel, dim3(std::max(1, grid_own)), dim3(256), 0, pp);
+    // 3. resid += gathered sum (waits for the gather flags)
+    pp.flags_local = reinterpret_cast<const unsigned int*>(c.tp_xchg + 192) + parity * 8;
+    L.launch(peer_add_gathered_kernel, dim3(grid_all), dim3(256), 0, pp);
 }
 
 // Tensor-parallel decode step: column-parallel QKV / gate-up, row-parallel o_proj / down with an

@@ -81,4 +81,47 @@ __device__ __forceinline__ float warp_max(float v) {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// ---- bounded waits on words another GPU writes -------------------------------------------
+// Longest a kernel waits for its peers' words, in total over all of its waits (nanoseconds on %globaltimer).  Ranks
+// of one request run in lock step, so a healthy wait lasts microseconds; the limit only has to outlast host jitter
+// between the ranks' launches.  A context overrides it (efm_b200_tp_set_wait_limit).
+constexpr unsigned long long kPeerWaitDefaultNs = 2000ull * 1000ull * 1000ull;
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ int ld_error_word(const int* p) {
+    int v;
+    asm volatile("ld.volatile.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Wait budget shared by all waits of one thread in one kernel.  `dead` once the budget ran out here, or once any
+// thread of any kernel raised the error word: from then on nothing waits any more (the step's result is void and
+// the host reads the status), so a lost peer costs one budget, not one per kernel.
+struct PeerWait {
+    bool dead;
+    unsigned long long deadline;      // 0 until the first poll that had to wait
+};
+__device__ __forceinline__ PeerWait peer_wait_begin(const int* error) {
+    PeerWait w;
+    w.dead = error != nullptr && ld_error_word(error) != 0;
+    w.deadline = 0ull;
+    return w;
+}
+// Called every few failed polls; true = stop waiting.
+__device__ __forceinline__ bool peer_wait_expired(PeerWait& w, int* error, volatile int* error_host, unsigned long long budget_ns) {
+    const unsigned long long now = globaltimer_ns();
+    if (w.deadline == 0ull) { w.deadline = now + (budget_ns != 0ull ? budget_ns : kPeerWaitDefaultNs); return false; }
+    const bool raised = error != nullptr && ld_error_word(error) != 0;
+    if (now > w.deadline || raised) {
+        if (!raised && error != nullptr) atomicExch(error, 3);
+        if (error_host != nullptr) *error_host = 3;
+        w.dead = true;
+        return true;
+    }
+    return false;
+}
+
 }  // namespace efm

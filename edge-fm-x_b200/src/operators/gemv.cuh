@@ -30,7 +30,6 @@ namespace efm {
 
 enum class Epi : int { Plain = 0, Residual = 1, QkvRope = 2, SwiGlu = 3, Logits = 4, Peers = 5 };
 constexpr int kMaxPeers = 8;
-constexpr int kPeerSpinLimit = 1 << 22;      // flag polls before a wait gives up (a few milliseconds)
 enum : int { kProPlain = 0, kProRmsNorm = 1, kProEmbedRmsNorm = 2 };
 
 struct GemvParams {
@@ -73,15 +72,24 @@ struct GemvParams {
     const uint2* addend_parts;            // local receive buffer [n_parts][K] of {value, count}
     int n_parts;
     int* error;               // raised (3) when a wait gives up
+    volatile int* error_host; // optional mirror of `error` in mapped host memory (the host stops queueing steps)
+    unsigned long long wait_ns;   // total wait budget of one kernel; 0 = kPeerWaitDefaultNs
+    unsigned int want_override;   // != 0: wait for this count instead of *epoch (single-GPU test of the wait)
 };
 
-// 16 bytes = two {value, count} words, read past every cache that a peer's store does not update
-__device__ __forceinline__ uint4 ld_peer_words(const uint2* p) {
-    uint4 v;
-    asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
-    return v;
+// One {value, count} word is ONE 64-bit element (value in the low half), so that value and count are read and
+// written together by the memory model's own rule (a 64-bit access is single-copy atomic), not by the accident
+// of how a 16-byte store travels.  Two words per access; relaxed, system scope: the consumer needs no ordering
+// between words, only each word whole.
+__device__ __forceinline__ void ld_peer_words(const uint2* p, unsigned long long& w0, unsigned long long& w1) {
+    asm volatile("ld.relaxed.sys.global.v2.b64 {%0,%1}, [%2];" : "=l"(w0), "=l"(w1) : "l"(p) : "memory");
 }
-
+__device__ __forceinline__ void st_peer_words(uint2* p, unsigned long long w0, unsigned long long w1) {
+    asm volatile("st.relaxed.sys.global.v2.b64 [%0], {%1,%2};" ::"l"(p), "l"(w0), "l"(w1) : "memory");
+}
+__device__ __forceinline__ unsigned long long peer_word(float v, unsigned int count) {
+    return (unsigned long long)__float_as_uint(v) | ((unsigned long long)count << 32);
+}
 __device__ __forceinline__ void group_barrier(int id, int nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
@@ -118,10 +126,10 @@ __device__ __forceinline__ void item_epilogue(const GemvParams& p, int item, flo
         p.y[item] = __float2bfloat16_rn(s * a1);
     } else if constexpr (EPI == Epi::Peers) {
         const unsigned int e = (unsigned int)best_i;           // exchange count of this launch (see gemv_kernel)
-        const uint4 w = make_uint4(__float_as_uint(a0), e, __float_as_uint(a1), e);
+        const unsigned long long w0 = peer_word(a0, e), w1 = peer_word(a1, e);
 #pragma unroll
         for (int r = 0; r < kMaxPeers; ++r)
-            if (r < p.n_peers) *reinterpret_cast<uint4*>(p.peer_out[r] + item * 2) = w;
+            if (r < p.n_peers) st_peer_words(p.peer_out[r] + item * 2, w0, w1);
     } else if constexpr (EPI == Epi::Logits) {
         *reinterpret_cast<float2*>(p.logits + item * 2) = make_float2(a0, a1);
         if (a0 > best_v) { best_v = a0; best_i = item * 2; }          // ascending ids: strict > keeps
@@ -256,7 +264,9 @@ __device__ __forceinline__ void gemv_run(const GemvParams& p, const GemvSched& s
             from_table = true;
         }
         float* xf32 = reinterpret_cast<float*>(smem + 2 * xbytes + (2 * kGemvWarps * 2 + 16) * sizeof(float));   // [K]
-        const unsigned int want = p.addend_parts != nullptr ? __ldcg(p.epoch) : 0u;   // bumped by this GPU's producing kernel
+        // count to wait for: bumped by this GPU's producing kernel
+        const unsigned int want = p.addend_parts == nullptr ? 0u : (p.want_override != 0u ? p.want_override : __ldcg(p.epoch));
+        PeerWait pw = peer_wait_begin(p.addend_parts != nullptr ? p.error : nullptr);
         float ss = 0.f;
         for (int c = tid; c < nch; c += kGemvThreads) {
             float f[8];
@@ -276,20 +286,22 @@ __device__ __forceinline__ void gemv_run(const GemvParams& p, const GemvSched& s
                 float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
                 for (int r = 0; r < p.n_parts; ++r) {
                     const uint2* part = p.addend_parts + (size_t)r * p.K + (size_t)c * 8;
-                    uint4 w[4];
+                    unsigned long long w[8];
                     int spins = 0;
                     for (;;) {                     // until all eight words carry this exchange's count
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) w[j] = ld_peer_words(part + 2 * j);
+                        for (int j = 0; j < 4; ++j) ld_peer_words(part + 2 * j, w[2 * j], w[2 * j + 1]);
                         bool ok = true;
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) ok = ok && w[j].y == want && w[j].w == want;
-                        if (ok) break;
-                        if (++spins > kPeerSpinLimit) { if (p.error != nullptr) atomicExch(p.error, 3); break; }
-                        if ((spins & 15) == 0) __nanosleep(32);
+                        for (int j = 0; j < 8; ++j) ok = ok && (unsigned int)(w[j] >> 32) == want;
+                        if (ok || pw.dead) break;
+                        if ((++spins & 15) == 0) {
+                            if (peer_wait_expired(pw, p.error, p.error_host, p.wait_ns)) break;
+                            __nanosleep(32);
+                        }
                     }
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) { a[2 * j] += __uint_as_float(w[j].x); a[2 * j + 1] += __uint_as_float(w[j].z); }
+                    for (int j = 0; j < 8; ++j) a[j] += __uint_as_float((unsigned int)w[j]);
                 }
 #pragma unroll
                 for (int j = 0; j < 8; ++j) f[j] += a[j];

@@ -122,32 +122,45 @@ __global__ void __launch_bounds__(256) add_rows_kernel(float* __restrict__ resid
     }
 }
 
-// Tensor parallel prefill over peer memory, producer side: this rank's fp32 partial [n4 float4] is copied into its
-// slot of every rank's receive buffer (P2P stores over NVLink, own buffer included).  Every block orders its stores
-// with a system-scope fence and draws a ticket; the block that draws the last one advances the local exchange
-// count and publishes it in this rank's flag word on every rank.
-struct PeerPushParams {
-    const float4* src;
-    float4* dst[8];              // this rank's slot in rank r's buffer
-    unsigned int* flag[8];       // this rank's flag word on rank r
-    int n_peers;
-    size_t n4;
-    unsigned int* epoch;         // local: prefill exchanges completed
+// ---- tensor parallel prefill over peer memory: reduce-scatter + all-gather of a row-parallel partial ------------
+// Every rank holds an fp32 partial [S, H] of a row-parallel linear and needs resid += sum over ranks.  Rank j owns
+// the rows [j * rows_per, (j + 1) * rows_per) of the sum:
+//   1. scatter: each rank stores slice j of its partial into its slot of rank j's receive buffer (peer stores over
+//      NVLink; (tp - 1) / tp of one copy leaves the GPU instead of tp - 1 whole copies);
+//   2. reduce + gather: the owner adds the tp slots in rank order and stores the summed rows into every rank's gather
+//      buffer;
+//   3. add: resid += gather buffer.
+// A step is complete for its readers when the writer's flag word on the reader carries the exchange count: every
+// block orders its stores with a system-scope fence and draws a ticket, the block that draws the last one publishes.
+// Two buffers used alternately (o_proj, down): a rank can be at most one exchange ahead of a peer.  Every wait is
+// bounded (PeerWait) and raises *error = 3.
+struct PeerXchgParams {
+    const float* src;            // 1: this rank's partial [S, H]
+    float* recv[8];              // 1: this rank's slot in rank r's receive buffer [rows_per, H]
+    const float* recv_local;     // 2: local receive buffer, tp slots of slot_floats each
+    float* gather[8];            // 2: rank r's gather buffer [S, H]
+    const float* gather_local;   // 3
+    float* resid;                // 3
+    unsigned int* flag[8];       // 1, 2: this rank's flag word on rank r (scatter flags in 1, gather flags in 2)
+    const unsigned int* flags_local;   // 2, 3: the flag words the ranks publish here
+    int n_peers, rank, S, H, rows_per;
+    size_t slot_floats;
+    unsigned int* epoch;         // local exchange count: advanced by step 1, read by steps 2 and 3
     unsigned int* ticket;        // local, zero between launches
+    int* error;
+    volatile int* error_host;
+    unsigned long long wait_ns;
 };
-__global__ void __launch_bounds__(256) peer_push_rows_kernel(const PeerPushParams p) {
-    for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < p.n4; i += (size_t)gridDim.x * 256) {
-        const float4 v = p.src[i];
-        for (int r = 0; r < p.n_peers; ++r) p.dst[r][i] = v;
-    }
+
+__device__ __forceinline__ void peer_publish(const PeerXchgParams& p, const bool advance) {
     __threadfence_system();
     __syncthreads();
     if (threadIdx.x == 0) {
         const unsigned int t = atomicAdd(p.ticket, 1u);
         if (t == gridDim.x - 1) {
             *p.ticket = 0u;
-            const unsigned int e = *p.epoch + 1u;
-            *p.epoch = e;
+            unsigned int e = *reinterpret_cast<volatile unsigned int*>(p.epoch);
+            if (advance) { e += 1u; *p.epoch = e; }
             __threadfence_system();
             for (int r = 0; r < p.n_peers; ++r)
                 asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.flag[r]), "r"(e) : "memory");
@@ -155,31 +168,58 @@ __global__ void __launch_bounds__(256) peer_push_rows_kernel(const PeerPushParam
     }
 }
 
-// Consumer side: wait (bounded; *error = 3 on expiry) until every rank's flag reached the local exchange count, then
-// resid += (part[0] + part[1] + ...) in rank order.  parts: n_parts slots of slot4 float4 each, n4 of them used.
-__global__ void __launch_bounds__(256) peer_add_rows_kernel(float4* __restrict__ resid, const float4* __restrict__ parts,
-                                                            const unsigned int* __restrict__ flags, int n_parts, size_t n4,
-                                                            size_t slot4, const unsigned int* __restrict__ epoch, int* error) {
-    if ((int)threadIdx.x < n_parts) {
-        const unsigned int want = __ldcg(epoch);
+// All ranks' flags have reached the local exchange count (or the wait budget ran out).
+__device__ __forceinline__ void peer_await(const PeerXchgParams& p) {
+    if ((int)threadIdx.x < p.n_peers) {
+        const unsigned int want = __ldcg(p.epoch);
+        PeerWait pw = peer_wait_begin(p.error);
         int spins = 0;
         for (;;) {
             unsigned int v;
-            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + threadIdx.x) : "memory");
-            if ((int)(v - want) >= 0) break;
-            if (++spins > (1 << 22)) { if (error != nullptr) atomicExch(error, 3); break; }
-            if ((spins & 63) == 0) __nanosleep(64);
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.flags_local + threadIdx.x) : "memory");
+            if ((int)(v - want) >= 0 || pw.dead) break;
+            if ((++spins & 15) == 0) {
+                if (peer_wait_expired(pw, p.error, p.error_host, p.wait_ns)) break;
+                __nanosleep(64);
+            }
         }
     }
     __syncthreads();
+}
+
+__global__ void __launch_bounds__(256) peer_scatter_rows_kernel(const PeerXchgParams p) {
+    const size_t row4 = (size_t)p.H / 4, n4 = (size_t)p.S * row4, per4 = (size_t)p.rows_per * row4;
     for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n4; i += (size_t)gridDim.x * 256) {
-        float4 a = __ldcg(parts + i);
-        for (int r = 1; r < n_parts; ++r) {
-            const float4 b = __ldcg(parts + (size_t)r * slot4 + i);
+        const int owner = (int)(i / per4);
+        reinterpret_cast<float4*>(p.recv[owner])[i - (size_t)owner * per4] = reinterpret_cast<const float4*>(p.src)[i];
+    }
+    peer_publish(p, /*advance=*/true);
+}
+
+__global__ void __launch_bounds__(256) peer_reduce_gather_kernel(const PeerXchgParams p) {
+    peer_await(p);
+    const size_t row4 = (size_t)p.H / 4, per4 = (size_t)p.rows_per * row4, first4 = (size_t)p.rank * per4;
+    const size_t total4 = (size_t)p.S * row4;
+    const size_t mine4 = first4 >= total4 ? 0 : (total4 - first4 < per4 ? total4 - first4 : per4);
+    const size_t slot4 = p.slot_floats / 4;
+    for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < mine4; i += (size_t)gridDim.x * 256) {
+        float4 a = __ldcg(reinterpret_cast<const float4*>(p.recv_local) + i);
+        for (int r = 1; r < p.n_peers; ++r) {
+            const float4 b = __ldcg(reinterpret_cast<const float4*>(p.recv_local) + (size_t)r * slot4 + i);
             a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
         }
-        const float4 o = resid[i];
-        resid[i] = make_float4(o.x + a.x, o.y + a.y, o.z + a.z, o.w + a.w);
+        for (int r = 0; r < p.n_peers; ++r) reinterpret_cast<float4*>(p.gather[r])[first4 + i] = a;
+    }
+    peer_publish(p, /*advance=*/false);
+}
+
+__global__ void __launch_bounds__(256) peer_add_gathered_kernel(const PeerXchgParams p) {
+    peer_await(p);
+    const size_t n4 = (size_t)p.S * p.H / 4;
+    for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n4; i += (size_t)gridDim.x * 256) {
+        const float4 a = __ldcg(reinterpret_cast<const float4*>(p.gather_local) + i);
+        const float4 o = reinterpret_cast<const float4*>(p.resid)[i];
+        reinterpret_cast<float4*>(p.resid)[i] = make_float4(o.x + a.x, o.y + a.y, o.z + a.z, o.w + a.w);
     }
 }
 

@@ -110,6 +110,22 @@ EFM_API efm_status efm_b200_tp_init(efm_b200_ctx* ctx, const void* id128);
 EFM_API efm_status efm_b200_tp_peer_export(efm_b200_ctx* ctx, void* handle64);
 EFM_API efm_status efm_b200_tp_peer_import(efm_b200_ctx* ctx, const void* handles, int32_t n_handles);
 
+/* Failure detection (the reference, being single-GPU, only surfaces CUDA errors at the final stream sync:
+ * src/utils/device/cuda_utils.h:27-33).  Two limits, 0 keeps the current value:
+ *   device_wait_us  longest a kernel waits, in total, for its peers' words / flags before it raises the device status
+ *                   (EFM_ERR_DEVICE_WAIT from read_tokens; later kernels see the status and do not wait again, and
+ *                   decode_steps stops queueing).  Default 2 s, or $EFM_B200_PEER_WAIT_MS.  Re-captures decode graphs.
+ *   host_timeout_s  limit of every synchronising call (read_tokens, read_logits, synchronize) on a tensor-parallel
+ *                   context; while it waits the call polls ncclCommGetAsyncError.  On an NCCL error (EFM_ERR_CUDA) or on
+ *                   expiry (EFM_ERR_DEVICE_WAIT) the communicator is aborted and the context is only good for destroy.
+ *                   Default 300 s, or $EFM_B200_TP_TIMEOUT_S. */
+EFM_API efm_status efm_b200_tp_set_wait_limit(efm_b200_ctx* ctx, int64_t device_wait_us, double host_timeout_s);
+/* The host-side wait itself, for engines that wait on their own streams by the same rule: polls ready(arg) (non-zero =
+ * done) about once per millisecond and the communicator's asynchronous error state in between.  nccl_comm may be NULL
+ * (timeout only).  EFM_OK / EFM_ERR_CUDA (NCCL error; communicator aborted) / EFM_ERR_DEVICE_WAIT (timeout; aborted).
+ * Needs no GPU by itself. */
+EFM_API efm_status efm_b200_tp_host_wait(void* nccl_comm, int (*ready)(void*), void* arg, double timeout_s);
+
 /* ---- weights --------------------------------------------------------------------------- */
 /* Replaces WeightLoader::load_weights_from_file + per-layer load_weights
  * (src/utils/device/weight_loader.cpp:80-171, src/layers/linear.cu:1691-1717,1926-1943).
@@ -196,6 +212,15 @@ EFM_API efm_status efm_b200_decode_step_bytes(efm_b200_ctx* ctx, int32_t kv_len,
  * LinearLayer decode GEMV (src/operators/linear_impl.cu:457-469). */
 EFM_API efm_status efm_b200_op_gemv(const void* w, const void* x, const void* norm_w, float eps,
                                     void* y_bf16, void* residual, int32_t n, int32_t k);
+/* Consumer side of the tensor-parallel decode exchange on ONE GPU (no counterpart in the reference): the norm-prologue
+ * GEMV whose input is resid + parts[0] + parts[1] + ... (rank order), parts being device [n_parts][k] 8-byte words
+ * {fp32 value, count}.  Every word is re-read until it carries want_count, for at most wait_limit_us microseconds in
+ * total; then y = W . bf16(rmsnorm(x) * norm_w) -> bf16 [n] and resid_out = x (fp32 [k], must differ from resid).
+ * Returns EFM_ERR_DEVICE_WAIT when the wait ran out (outputs undefined; the device stays usable). */
+EFM_API efm_status efm_b200_op_gemv_peer_consume(const void* w, const void* resid_f32, const void* norm_w, float eps,
+                                                 const void* parts, int32_t n_parts, uint32_t want_count,
+                                                 int64_t wait_limit_us, void* y_bf16, void* resid_out_f32, int32_t n,
+                                                 int32_t k);
 /* Y[m,n] = X[m,k] . W[n,k]^T (+bias[n]) -> bf16 (prefill linear; linear_impl.cu:457-469,482-706). */
 EFM_API efm_status efm_b200_op_gemm(const void* x, const void* w, const void* bias, void* y_bf16,
                                     int32_t m, int32_t n, int32_t k);
@@ -214,13 +239,15 @@ EFM_API efm_status efm_b200_op_decode_attention(const void* q, const void* k_cac
  * in a fixed array that is part of the library image: about 1 MB on every GPU that loads the
  * library, held until the process exits.  It calls no cudaMalloc / cudaFree and no allocating
  * library routine.
- * Limits: q_heads * head_dim <= 4096 and kv_heads <= 16; larger shapes are refused with
- * EFM_ERR_UNSUPPORTED (use efm_b200_op_decode_attention for those).
+ * Limits: q_heads * head_dim <= 4096, q_heads <= 64, kv_heads <= 16 and q_heads / kv_heads <= 8;
+ * larger shapes are refused with EFM_ERR_UNSUPPORTED (use efm_b200_op_decode_attention for those).
  * The first call on each device looks up the device address of that array (with that device
- * current) and caches it; make that first call before starting any stream capture.
+ * current) and caches it; the cache may be filled from several host threads at once.  The call
+ * sets kernel attributes, runs on the default stream and synchronises it before returning, so it
+ * must not be issued while a stream capture is active on the calling thread.
  * All calls share the one array and it keeps whatever the previous call left in it (the tickets
  * are re-zeroed at the start of every call): two calls whose kernels overlap on the GPU race on
- * it, so issue them one after the other.  Runs on the default stream and returns when done. */
+ * it, so issue them one after the other (one host thread per device at a time). */
 EFM_API efm_status efm_b200_op_decode_attention_noalloc(const void* q, const void* k_cache, const void* v_cache,
                                                         void* out_bf16, int32_t q_heads, int32_t kv_heads,
                                                         int32_t head_dim, int32_t kv_len, int32_t max_tokens);

@@ -58,6 +58,8 @@ SIGNATURES = {
     "efm_b200_tp_init": (I32, [P, P]),
     "efm_b200_tp_peer_export": (I32, [P, P]),
     "efm_b200_tp_peer_import": (I32, [P, P, I32]),
+    "efm_b200_tp_set_wait_limit": (I32, [P, C.c_int64, C.c_double]),
+    "efm_b200_tp_host_wait": (I32, [P, C.CFUNCTYPE(C.c_int, P), P, C.c_double]),
     "efm_b200_set_weight": (I32, [P, C.c_char_p, P, C.POINTER(C.c_int64), I32, I32, I32]),
     "efm_b200_finalize_weights": (I32, [P]),
     "efm_b200_alloc_kv_slot": (I32, [P, I32, I32]),
@@ -77,6 +79,7 @@ SIGNATURES = {
     "efm_b200_decode_breakdown": (I32, [P, I32, C.POINTER(C.c_float)]),
     "efm_b200_decode_step_bytes": (I32, [P, I32, C.POINTER(C.c_int64)]),
     "efm_b200_op_gemv": (I32, [P, P, P, C.c_float, P, P, I32, I32]),
+    "efm_b200_op_gemv_peer_consume": (I32, [P, P, P, C.c_float, P, I32, C.c_uint32, C.c_int64, P, P, I32, I32]),
     "efm_b200_op_gemm": (I32, [P, P, P, P, I32, I32, I32]),
     "efm_b200_op_decode_attention": (I32, [P, P, P, P, I32, I32, I32, I32, I32]),
     "efm_b200_op_decode_attention_noalloc": (I32, [P, P, P, P, I32, I32, I32, I32, I32]),

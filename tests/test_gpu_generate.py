@@ -268,6 +268,17 @@ def test_edge_fm_module_configuration_errors(tmp_path, built):
     ok_cfg = synth.write_engine_config(str(tmp_path / "trunc.json"), model_dir)
     with pytest.raises(RuntimeError, match="truncated|outside"):
         edge_fm.EdgeFM(ok_cfg)
+    # a record whose byte range disagrees with its shape (mis-sharded header) is refused, not read past its end
+    import json
+    import struct
+    n = struct.unpack("<Q", data[:8])[0]
+    header = json.loads(data[8:8 + n])
+    name = next(k for k in header if k.endswith("q_proj.weight"))
+    header[name]["shape"][0] *= 2
+    hb = json.dumps(header).encode()
+    open(st, "wb").write(struct.pack("<Q", len(hb)) + hb + data[8 + n:])
+    with pytest.raises(RuntimeError, match="shape and dtype need"):
+        edge_fm.EdgeFM(ok_cfg)
 
 
 def test_edge_fm_compact_vocab_and_int8_prefill_through_the_public_api(tmp_path, built):

@@ -162,3 +162,59 @@ def test_sampler_ties_at_the_nucleus_edge():
         assert got == want
         seen.add(got)
     assert max(seen) < 32
+
+
+def peer_words(vals, count):
+    """[n_parts, k] fp32 -> the exchange's 8-byte words {fp32 value (low half), count (high half)}."""
+    w = torch.empty(vals.shape + (2,), dtype=torch.int32, device="cuda")
+    w[..., 0] = vals.view(torch.int32)
+    w[..., 1] = count
+    return w.contiguous()
+
+
+@pytest.mark.parametrize("n,k,parts", [(512, 896, 2), (1024, 3584, 8)])
+def test_peer_consumer_sums_the_partials_in_rank_order(n, k, parts):
+    """Consumer side of the tensor-parallel decode exchange on one GPU: x = resid + p0 + p1 + ..., then norm + GEMV."""
+    L = cabi.lib()
+    g = torch.Generator(device="cuda").manual_seed(21)
+    w, nw = bf16(n, k, scale=0.02, seed=22), (1 + 0.02 * torch.randn(k, device="cuda", generator=g)).to(torch.bfloat16)
+    resid = torch.randn(k, device="cuda", generator=g)
+    vals = torch.randn(parts, k, device="cuda", generator=g)
+    words = peer_words(vals, 7)
+    y = torch.zeros(n, device="cuda", dtype=torch.bfloat16)
+    rout = torch.zeros(k, device="cuda")
+    ok(L.efm_b200_op_gemv_peer_consume(P(w), P(resid), P(nw), 1e-6, P(words), parts, 7, 200_000, P(y), P(rout), n, k))
+    acc = torch.zeros(k, device="cuda")
+    for r in range(parts):
+        acc = acc + vals[r]
+    x = resid + acc
+    assert torch.equal(rout, x)                       # same order of additions: bit-identical
+    xn = (x * torch.rsqrt(x.pow(2).mean() + 1e-6) * nw.float()).to(torch.bfloat16)
+    ref = (w.double() @ xn.double()).float()
+    assert torch.allclose(y.float(), ref, atol=3e-3, rtol=2e-2)
+
+
+def test_peer_wait_runs_out_and_the_device_stays_usable():
+    """Failure detection without a fault: one word of one partial never receives the awaited count (as if its rank
+    were lost).  The kernel's wait is bounded in TIME and in total, so the call must come back promptly with
+    EFM_ERR_DEVICE_WAIT, and the next call on the same device must work."""
+    import time
+    L = cabi.lib()
+    n, k, parts = 512, 1536, 4
+    g = torch.Generator(device="cuda").manual_seed(23)
+    w, nw = bf16(n, k, scale=0.02, seed=24), torch.ones(k, device="cuda", dtype=torch.bfloat16)
+    resid = torch.randn(k, device="cuda", generator=g)
+    vals = torch.randn(parts, k, device="cuda", generator=g)
+    words = peer_words(vals, 5)
+    words[2, 100, 1] = 4                              # rank 2 is one exchange behind on one value, forever
+    y = torch.zeros(n, device="cuda", dtype=torch.bfloat16)
+    rout = torch.zeros(k, device="cuda")
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    st = L.efm_b200_op_gemv_peer_consume(P(w), P(resid), P(nw), 1e-6, P(words), parts, 5, 20_000, P(y), P(rout), n, k)
+    waited = time.perf_counter() - t0
+    assert st == 6 and b"ran out" in L.efm_b200_last_error(None)          # EFM_ERR_DEVICE_WAIT
+    assert waited < 2.0, waited                       # 20 ms budget for the whole kernel, not per wait
+    words[2, 100, 1] = 5                              # the word arrives: same call succeeds, device still usable
+    ok(L.efm_b200_op_gemv_peer_consume(P(w), P(resid), P(nw), 1e-6, P(words), parts, 5, 20_000, P(y), P(rout), n, k))
+    assert torch.equal(rout, resid + ((vals[0] + vals[1]) + vals[2]) + vals[3])

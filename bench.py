@@ -2,20 +2,22 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config 0..4]
 
-Workload (default --config 1, the configuration the decode tok/s metric is quoted on):
-Qwen2.5-1.5B-shaped random bf16 model, 512-token fixed prefix resident in the KV slot, 256-token
-prompt, 256 generated tokens at batch 1 with temperature 0.7 / top-p 0.9 / seed 0.  One "step" is
-one request: prefill of the prompt over the prefix + sample + 255 decode steps.
-  value  decode tok/s from CUDA events around the decode phase (inputs resident on the device);
-  e2e    tokens/s of edge_fm.EdgeFM.generate() with host token ids in and host ids out;
-  N > 1  independent replicas, one process per GPU (the path has no data-parallel exchange).
-Prints exactly one JSON line on rank 0.
+Without --config the workload is configuration 3, the one the benchmark partitions: a Qwen2.5-VL-7B-shaped
+random bf16 model, one 1288x728 image (4784 patches -> 1196 tokens through the vision encoder) + 128 text
+tokens, INT8 prefill attention, 256 generated tokens at batch 1.  One "step" is one request: encode + prefill +
+sample + 255 decode steps.  N = 1 runs it on one GPU; N > 1 (one process per GPU under torch.distributed.run)
+runs the SAME request tensor parallel over the N ranks (heads + MLP columns + vocabulary rows; strong scaling).
+  value  decode tok/s from CUDA events on the context stream around the decode phase (inputs resident);
+  e2e    tokens/s of edge_fm.EdgeFM.generate() with host pixels / ids in and host ids out;
+  per_config (N = 1 only)  a short pass over configurations 0, 1, 2 and 4 on the same GPU.
+--config k runs configuration k alone (0-2 and 4: replicas when N > 1).  Prints exactly one JSON line on rank 0.
 """
 from __future__ import annotations
 
 import argparse
 import json
 import os
+import shutil
 import subprocess
 import sys
 import tempfile
@@ -28,10 +30,11 @@ for p in (ROOT, os.path.join(ROOT, "tests"), os.path.join(ROOT, "edge-fm-x_b200"
         sys.path.insert(0, p)
 
 METRIC, UNIT = "decode_tokens_per_second_batch1", "tok/s"
-# DRAM bytes (read + write) of the four per-layer GEMV launches of one decode step, from the ncu capture
-# summarised under profiles/ (config 1 only; other configs were not captured).
+# DRAM bytes (read + write) of the four per-layer GEMV launches of one decode step: constants taken from one ncu
+# capture per configuration (summaries under profiles/), not re-measured by this script.
 NCU_LAYER_GEMV_DRAM_BYTES = {1: 6.33984e6 + 4.758528e6 + 55.090432e6 + 77.824e3 + 27.579904e6}
 NAMES = {0: "qwen2.5-0.5b", 1: "qwen2.5-1.5b", 2: "qwen2.5-vl-3b-llm", 3: "qwen2.5-vl-7b-llm"}
+HEADLINE = 3
 
 
 def peaks():
@@ -90,74 +93,9 @@ def workload(cfg_id):
     return cfg, ids[:prefix_n], ids, steps, temp, top_p
 
 
-def position_ids(cfg, n):
-    if cfg.mrope_section is None:
-        return None
-    return [list(range(n)) for _ in range(3)]
-
-
-# --------------------------------------------------------------------------------------------------
-def run_reference(args, rank):
-    """The reference has no CPU implementation of this path (it throws without CUDA), so this arm
-    times the CPU restatement (oracle, exact_fp32) on the host cores.  One step = a bounded sample:
-    `sample_tokens` decode steps at the workload's context length."""
-    if rank != 0:
-        return
-    import torch
-    from oracle import qwen_text, synth
-    cfg, prefix, ids, steps, temp, top_p = workload(args.config)
-    cores = os.cpu_count() or 1
-    torch.set_num_threads(cores)
-    w = synth.make_weights(cfg, seed=0)
-    o = qwen_text.QwenTextOracle(cfg, w, "exact_fp32")
-    pos = position_ids(cfg, len(ids))
-    ctx = min(len(ids), args.ref_context)
-    with torch.no_grad():
-        o.forward(ids[:ctx], position_ids=None if pos is None else torch.tensor(pos)[:, :ctx])
-        sample_tokens = 2
-        tok = ids[-1]
-
-        def one_step():
-            n0 = o.kv_len
-            for i in range(sample_tokens):
-                p3 = None if pos is None else torch.full((3, 1), n0 + i)
-                o.forward([tok], position_ids=p3)
-            o.truncate(n0)
-        for _ in range(args.warmup):
-            one_step()
-        t0 = time.perf_counter()
-        for _ in range(args.steps):
-            one_step()
-        dt = time.perf_counter() - t0
-    value = args.steps * sample_tokens / dt
-    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"{NAMES[args.config]} decode at context {ctx} (CPU restatement of the reference path)"},
-            "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
-                             "sample": f"{sample_tokens} decode steps per bench step at context {ctx}, fp32 torch-CPU"},
-            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-    print(json.dumps(line), flush=True)
-
-
 def vlm_request(cfg_id, cfg):
-    """Image-first multimodal prompt of configurations 2 / 3: the image's merged tokens (ids >= vocab select rows of
-    the injected embeddings), then text.  M-RoPE positions: image t = 0, h = merged row, w = merged column; text
-    continues from max(rows, columns) on all three axes."""
-    from oracle import qwen_vit, synth
-    vcfg = qwen_vit.CONFIGS[cfg_id]
-    t, h, w = qwen_vit.GRIDS[cfg_id]
-    hm, wm = h // vcfg.merge, w // vcfg.merge
-    n_img = t * hm * wm
-    n_text = synth.WORKLOADS[cfg_id][1] - n_img
-    ids = [cfg.vocab + k for k in range(n_img)] + synth.make_token_ids(n_text, seed=0)
-    start = max(hm, wm)
-    text_pos = [start + i for i in range(n_text)]
-    pos = [[0] * n_img + text_pos,
-           [r for r in range(hm) for _ in range(wm)] * t + text_pos,
-           [c for _ in range(hm) for c in range(wm)] * t + text_pos]
-    return {"vcfg": vcfg, "grids": [(t, h, w)], "ids": ids, "pos": pos, "n_img": n_img, "embed_id": cfg.vocab,
-            "last": start + n_text - 1}
+    from oracle import synth
+    return synth.vlm_request(cfg_id)
 
 
 def vit_flops(vcfg, grids):
@@ -194,56 +132,157 @@ def tensor_report(flops, ms):
     return {"ms": ms, "tflop": flops / 1e12, "tflops": tf, "frac_of_bf16_peak": tf / peak, "peak": peak, "peak_kind": kind}
 
 
+def scratch_dir(rank, need_gb):
+    """A fresh directory for a synthetic checkpoint: memory-backed when it has the room, else the default temp dir."""
+    base = None
+    try:
+        st = os.statvfs("/dev/shm")
+        if st.f_bavail * st.f_frsize > (need_gb + 4) * 2 ** 30:
+            base = "/dev/shm"
+    except OSError:
+        pass
+    return tempfile.mkdtemp(prefix=f"efm_bench_{rank}_", dir=base)
+
+
 # --------------------------------------------------------------------------------------------------
-def cpu_baseline(cfg_id, budget_s=25.0):
+# CPU arm: the reference has no CPU implementation of this path (it throws without CUDA) and cannot be built here,
+# so both `--impl reference` and the cpu_baseline object time the fp32 torch-CPU restatement on the host cores.
+class CpuDecode:
+    """The restatement positioned at the workload's REAL context: the prompt is prefilled once (outside any timed
+    region; image rows are seeded noise of the embeddings' scale, since decode time does not depend on their
+    values), then decode steps are timed and the cache rolled back."""
+
+    def __init__(self, cfg_id, weights=None):
+        import torch
+        from oracle import qwen_text, synth
+        self.torch = torch
+        self.cfg = cfg = synth.CONFIGS[cfg_id]
+        self.cores = os.cpu_count() or 1
+        torch.set_num_threads(self.cores)
+        w = weights if weights is not None else synth.make_weights(cfg, seed=0)
+        self.o = qwen_text.QwenTextOracle(cfg, w, "exact_fp32")
+        del w
+        if cfg.mrope_section is not None:
+            vlm = vlm_request(cfg_id, cfg)
+            ids, pos = vlm["ids"], torch.tensor(vlm["pos"])
+            g = torch.Generator().manual_seed(0)
+            embeds = torch.randn(vlm["n_img"], cfg.hidden, generator=g) * 0.02
+            self.first_pos = vlm["last"] + 1
+        else:
+            _, _, ids, _, _, _ = workload(cfg_id)
+            pos, embeds, self.first_pos = None, None, None
+        self.ctx = len(ids)
+        self.tok = ids[-1]
+        t0 = time.perf_counter()
+        with torch.no_grad():
+            self.o.forward(ids, embeds=embeds, embed_token_id=cfg.vocab if embeds is not None else -1, position_ids=pos)
+        self.prefill_s = time.perf_counter() - t0
+
+    def decode(self, n):
+        torch, o = self.torch, self.o
+        n0 = o.kv_len
+        with torch.no_grad():
+            for i in range(n):
+                p3 = None if self.first_pos is None else torch.full((3, 1), self.first_pos + i)
+                o.forward([self.tok], position_ids=p3)
+        o.truncate(n0)
+
+
+def run_reference(args, rank):
+    """One bench step = a bounded sample: `sample_tokens` decode steps at the workload's full context."""
+    if rank != 0:
+        return
+    cpu = CpuDecode(args.config)
+    sample_tokens = 1 if args.config == 3 else 2
+    for _ in range(args.warmup):
+        cpu.decode(sample_tokens)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu.decode(sample_tokens)
+    dt = time.perf_counter() - t0
+    value = args.steps * sample_tokens / dt
+    sample = (f"{sample_tokens} decode step(s) per bench step at context {cpu.ctx} (the workload's own), fp32 torch-CPU restatement; "
+              f"prompt prefilled once outside the timed region ({cpu.prefill_s:.1f} s)")
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
+            "scaling": "strong" if args.config == 3 else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"{NAMES[args.config]} decode at context {cpu.ctx} (CPU restatement of the reference path; the reference "
+                                   "itself has no CPU implementation of token generation)"},
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": cpu.cores, "kind": "port", "sample": sample,
+                             "prefill_s": cpu.prefill_s},
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def cpu_baseline(cfg_id, weights=None, budget_s=20.0):
+    cpu = CpuDecode(cfg_id, weights)
+    cpu.decode(1)
+    n, t0 = 0, time.perf_counter()
+    while n < 64 and (n < 8 or time.perf_counter() - t0 < budget_s):
+        cpu.decode(1)
+        n += 1
+    dt = time.perf_counter() - t0
+    return {"value": n / dt, "unit": UNIT, "cores": cpu.cores, "kind": "port", "prefill_s": cpu.prefill_s,
+            "sample": f"{n} decode steps at context {cpu.ctx} (the workload's own), fp32 torch-CPU restatement, all host threads"}
+
+
+# --------------------------------------------------------------------------------------------------
+class _Solo:
+    """torch.distributed stand-in for a single process."""
+    class ReduceOp:
+        MAX = None
+
+    @staticmethod
+    def barrier():
+        pass
+
+    @staticmethod
+    def all_reduce(t, op=None):
+        pass
+
+    @staticmethod
+    def broadcast_object_list(box, src=0):
+        pass
+
+    @staticmethod
+    def all_gather_object(out, obj):
+        out[0] = obj
+
+    @staticmethod
+    def destroy_process_group():
+        pass
+
+
+def draw_weights_on_device(cfg, be, keep_host):
+    """Seeded weights drawn tensor by tensor on the GPU (identical on every rank: same generator, same order), handed
+    to the backend from device memory; rank 0 may keep host copies for the checkpoint the public-API engine loads."""
     import torch
-    from oracle import qwen_text, synth
-    cfg, prefix, ids, steps, temp, top_p = workload(cfg_id)
-    cores = os.cpu_count() or 1
-    torch.set_num_threads(cores)
-    w = synth.make_weights(cfg, seed=0)
-    o = qwen_text.QwenTextOracle(cfg, w, "exact_fp32")
-    ctx = min(len(ids), 256)                      # bounded: a 256-token context instead of the full one
-    pos = position_ids(cfg, len(ids))
-    with torch.no_grad():
-        o.forward(ids[:ctx], position_ids=None if pos is None else torch.tensor(pos)[:, :ctx])
-        o.forward([ids[-1]], position_ids=None if pos is None else torch.full((3, 1), ctx))
-        n, t0 = 0, time.perf_counter()
-        while n < 64 and time.perf_counter() - t0 < budget_s / 2:
-            o.forward([ids[-1]], position_ids=None if pos is None else torch.full((3, 1), ctx + 1 + n))
-            n += 1
-        dt = time.perf_counter() - t0
-    return {"value": n / dt, "unit": UNIT, "cores": cores, "kind": "port",
-            "sample": f"{n} decode steps at context {ctx} (fp32 torch-CPU restatement; the full workload runs at context "
-                      f"{len(ids)})"}
+    from oracle import synth
+    g = torch.Generator(device="cuda")
+    g.manual_seed(0)
+    host = {}
+    for name, shape, kind in synth.weight_names(cfg):       # one tensor at a time: the whole model never sits twice in HBM
+        t = torch.randn(shape, generator=g, device="cuda", dtype=torch.float32) * 0.02
+        if kind == "n":
+            t += 1.0
+        t = t.to(torch.bfloat16)
+        be.load_weights_partial({name: t})
+        if keep_host:
+            host[name] = t.cpu()
+        del t
+    be.finalize()
+    return host
 
 
 def run_tp(args, rank, world, local_rank):
-    """Config 3 (7B-class) on several GPUs: ONE request, tensor parallel over all ranks (strong scaling).
-    Weights are drawn on the device with a seeded generator (identical on every rank); each rank keeps
-    its shard.  e2e here is the C-ABI call sequence with host token ids in and host ids out."""
+    """Config 3 (7B-class): ONE request, tensor parallel over all ranks (strong scaling); one rank = the plain
+    single-GPU path."""
     import torch
     import torch.distributed as dist
     import cabi
-    from oracle import synth
+    from oracle import qwen_vit, synth
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     torch.cuda.set_device(local_rank)
-
-    class _Solo:                       # world == 1: no process group
-        class ReduceOp:
-            MAX = None
-
-        @staticmethod
-        def barrier():
-            pass
-
-        @staticmethod
-        def all_reduce(t, op=None):
-            pass
-
-        @staticmethod
-        def destroy_process_group():
-            pass
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     else:
@@ -251,10 +290,11 @@ def run_tp(args, rank, world, local_rank):
     cfg, prefix, ids, gen_tokens, temp, top_p = workload(args.config)
     if args.tokens:
         gen_tokens = args.tokens
-    from oracle import qwen_vit
     vlm = vlm_request(args.config, cfg)
     ids, pos = vlm["ids"], vlm["pos"]
     max_tokens = len(ids) + gen_tokens + 8
+    want_e2e = not args.no_e2e
+    want_cpu = world == 1 and not args.no_cpu
     t_setup = time.perf_counter()
     be = cabi.Backend(cfg, max_prefill_tokens=min(2048, max_tokens), max_response_tokens=gen_tokens + 8,
                       device_id=local_rank, tp_rank=rank, tp_size=world)
@@ -262,15 +302,7 @@ def run_tp(args, rank, world, local_rank):
         box = [cabi.tp_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(box, src=0)
         be.tp_init(box[0])
-    g = torch.Generator(device="cuda")
-    g.manual_seed(0)
-    for name, shape, kind in synth.weight_names(cfg):       # one tensor at a time: the whole model never sits twice in HBM
-        t = torch.randn(shape, generator=g, device="cuda", dtype=torch.float32) * 0.02
-        if kind == "n":
-            t += 1.0
-        be.load_weights_partial({name: t.to(torch.bfloat16)})
-        del t
-    be.finalize()
+    host_w = draw_weights_on_device(cfg, be, keep_host=rank == 0 and (want_e2e or want_cpu))
     be.alloc_slot(0, max_tokens)
     fused = world > 1 and args.tp_exchange == "peer"
     if fused:        # the decode step's all-reduces inside the GEMVs, over peer memory (CUDA IPC handles via the host)
@@ -282,7 +314,7 @@ def run_tp(args, rank, world, local_rank):
         be.set_prefill_attention(1)
     be.set_sampling(temp, top_p, 0)
     be.capture_decode(0)
-    # vision encoder: replicated on every rank (its windows are not sharded), weights drawn on the device
+    # vision encoder on the text context's stream; its windows are sharded over the ranks
     n_patches = sum(t * h * w for t, h, w in vlm["grids"])
     enc = cabi.VitEncoder(be, vlm["vcfg"], max_patches=n_patches)
     enc.load_weights(qwen_vit.make_weights(vlm["vcfg"], seed=0, device="cuda"))
@@ -291,12 +323,41 @@ def run_tp(args, rank, world, local_rank):
     pixels_dev = pixels.cuda()
     embeds = torch.zeros(vlm["n_img"], cfg.hidden, dtype=torch.bfloat16, device="cuda")
     be.synchronize()
+
+    # public-API engine for the end-to-end leg: every rank builds edge_fm.EdgeFM from the same JSON
+    engine, tmp = None, None
+    if want_e2e:
+        import edge_fm
+        box = [scratch_dir(rank, 16) if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        tmp = box[0]
+        model_dir = os.path.join(tmp, "model")
+        if rank == 0:
+            synth.write_checkpoint(model_dir, cfg, host_w)
+            eng_path = synth.write_engine_config(os.path.join(tmp, "engine.json"), model_dir, model_name="Qwen2.5-VL", prefix_ids=[],
+                                                 max_tokens=max_tokens, max_new_tokens=gen_tokens, temperature=temp, top_p=top_p,
+                                                 seed=0, use_cuda_graph=True, device_id=local_rank)
+            ej = json.load(open(eng_path))
+            ej["runtime"]["prefill_attention"] = args.prefill_attention
+            if world > 1:
+                ej["runtime"]["tensor_parallel"] = world
+                ej["runtime"]["tp_rendezvous"] = os.path.join(tmp, "meet")
+            json.dump(ej, open(eng_path, "w"))
+        dist.barrier()
+        os.environ["EFM_TP_RANK"] = str(rank)
+        os.environ["LOCAL_RANK"] = str(local_rank)
+        engine = edge_fm.EdgeFM(os.path.join(tmp, "engine.json"))
+        dist.barrier()
+        if rank == 0:
+            os.remove(os.path.join(model_dir, "model.safetensors"))
+    if not want_cpu:
+        host_w = None
     setup_s = time.perf_counter() - t_setup
     mp = [vlm["last"] + 1] * 3
 
-    def one_request(host_pixels=False):
+    def one_request():
         be.event_record(0)
-        enc.encode(pixels_host if host_pixels else pixels_dev, vlm["grids"], embeds)
+        enc.encode(pixels_dev, vlm["grids"], embeds)
         be.event_record(3)
         be.prefill(0, ids, kv_offset=0, embeds=embeds, embed_token_id=vlm["embed_id"], pos3=pos, sample=True)
         be.event_record(1)
@@ -306,6 +367,18 @@ def run_tp(args, rank, world, local_rank):
         toks = be.read_tokens(0, gen_tokens)              # host ids out (one D2H + sync)
         return be.elapsed_ms(3, 1), be.elapsed_ms(1, 2), toks, be.elapsed_ms(0, 3)
 
+    pt = torch.tensor(pos, dtype=torch.int32)
+
+    def e2e_request():       # host pixels -> vision encoder (C ABI) -> embeddings stay on the device -> public generate()
+        enc.encode(pixels_host, vlm["grids"], embeds)
+        be.synchronize()
+        req = edge_fm.Request(0, ids, edge_fm.Tensor(embeds.data_ptr(), [vlm["n_img"], cfg.hidden], edge_fm.DType.BFloat16,
+                                                     edge_fm.Device.GPU, local_rank),
+                              vlm["embed_id"], edge_fm.Tensor(pt.data_ptr(), [3, len(ids)], edge_fm.DType.Int32, edge_fm.Device.CPU),
+                              [vlm["last"]] * 3)
+        req.set_ignore_stop_tokens(True)
+        return list(engine.generate(req).token_ids())
+
     for _ in range(args.warmup):
         one_request()
     sampler = ClockSampler(local_rank)
@@ -313,7 +386,6 @@ def run_tp(args, rank, world, local_rank):
     launches0 = be.launch_count()
     dist.barrier()
     torch.cuda.synchronize()
-    t0 = time.perf_counter()
     pre_ms = dec_ms = vit_ms = 0.0
     for _ in range(args.steps):
         a, b, tokens, v = one_request()
@@ -323,17 +395,23 @@ def run_tp(args, rank, world, local_rank):
     dist.barrier()
     torch.cuda.synchronize()
     launches = be.launch_count() - launches0
-    # end to end: host pixels and host ids in (H2D inside), host ids out
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        one_request(host_pixels=True)
-    dist.barrier()
-    torch.cuda.synchronize()
-    wall_s = time.perf_counter() - t0
+    wall_s, e2e_tokens, m = None, None, {}
+    if engine is not None:
+        for _ in range(max(1, min(2, args.warmup))):
+            e2e_tokens = e2e_request()
+        dist.barrier()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            e2e_tokens = e2e_request()
+        dist.barrier()
+        torch.cuda.synchronize()
+        wall_s = time.perf_counter() - t0
+        m = engine.last_generate_metrics()
     clocks = sampler.stop()
-    local = torch.tensor([dec_ms, pre_ms, wall_s, vit_ms], dtype=torch.float64, device="cuda")
+    local = torch.tensor([dec_ms, pre_ms, wall_s or 0.0, vit_ms], dtype=torch.float64, device="cuda")
     dist.all_reduce(local, op=dist.ReduceOp.MAX)
-    dec_ms, pre_ms, wall_s, vit_ms = [float(x) for x in local.tolist()]
+    dec_ms, pre_ms, wall_max, vit_ms = [float(x) for x in local.tolist()]
     dec_steps = args.steps * (gen_tokens - 1)
     step_ms = dec_ms / dec_steps
     step_bytes = be.decode_step_bytes(len(ids) + gen_tokens // 2)          # this rank's share
@@ -341,61 +419,70 @@ def run_tp(args, rank, world, local_rank):
     if world == 1 or fused:      # per-kernel device time of a few un-overlapped steps (every rank takes part)
         be.decode_begin(0, len(ids), mp, 1)
         bd = be.decode_breakdown(4)
-        Lc = synth.CONFIGS[args.config].num_layers
+        Lc = cfg.num_layers
         breakdown = {k: round(v / (4 * (Lc if k not in ("lm_head", "sampler") else 1)) * 1e3, 2) for k, v in bd.items()}
     peak, peak_kind = peaks()
     achieved = step_bytes / (step_ms * 1e-3) / 1e9
+    line = None
     if rank == 0:
         line = {"metric": METRIC, "value": dec_steps / (dec_ms / 1e3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
-                "warmup": args.warmup, "ms_per_step": (pre_ms + dec_ms) / args.steps, "higher_is_better": True,
+                "warmup": args.warmup, "ms_per_step": (vit_ms + pre_ms + dec_ms) / args.steps, "higher_is_better": True,
                 "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
                 "config": {"workload": f"{NAMES[args.config]}: 1288x728 image ({n_patches} patches -> {vlm['n_img']} tokens through the vision "
                                        f"encoder) + {len(ids) - vlm['n_img']} text tokens = {len(ids)}-token prompt, {gen_tokens} generated "
                                        f"tokens, batch 1, temperature {temp}, top_p {top_p}",
                            "parallelism": "single GPU" if world == 1 else f"tp{world} (heads + MLP columns + vocab rows; decode all-reduce: " +
-                                          ("fused into the GEMVs over peer memory" if fused else "NCCL in the decode graph") + ")",
+                                          ("fused into the GEMVs over peer memory" if fused else "NCCL in the decode graph") +
+                                          "; prefill: reduce-scatter + all-gather over peer stores; vision windows sharded)",
                            "prefill_attention": args.prefill_attention,
                            "l2_policy": "weights streamed per decode step exceed L2 (%.2f GB per GPU vs 126 MB)" % (step_bytes / 1e9),
                            "cuda_graph": True},
                 "decode_ms_per_token": step_ms, "prefill_ms": pre_ms / args.steps, "vit_ms": vit_ms / args.steps,
                 "ttft_ms": (pre_ms + vit_ms) / args.steps,
-                "prefill": tensor_report(prefill_flops(synth.CONFIGS[args.config], len(ids), 0) / world, pre_ms / args.steps),
-                "vit": tensor_report(vit_flops(vlm["vcfg"], vlm["grids"]), vit_ms / args.steps),
-                "wall_s": wall_s, "setup_s": setup_s,
-                "e2e": {"value": args.steps * gen_tokens / wall_s, "unit": UNIT,
-                        "h2d_bytes_per_step": 16 * len(ids) + pixels.numel() * 2,
-                        "d2h_bytes_per_step": 4 * gen_tokens + 32,
-                        "api": "efm_b200_vit_encode / prefill / decode_steps / read_tokens (C ABI, host buffers)"},
+                "prefill": tensor_report(prefill_flops(cfg, len(ids), 0) / world, pre_ms / args.steps),
+                "vit": tensor_report(vit_flops(vlm["vcfg"], vlm["grids"]) / world, vit_ms / args.steps),
+                "setup_s": setup_s,
                 "gpu_launches": launches, "clocks": clocks,
                 "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                             "traffic": None, "peak_kind": peak_kind, "launch": "one decode step on one rank",
-                             "bytes_per_launch": step_bytes, "us_per_launch": step_ms * 1e3},
+                             "traffic": None, "peak_kind": peak_kind,
+                             "launch": "one decode step on one rank (CUDA graph: 5 kernels per layer + lm_head + logits gather + sampler)",
+                             "bytes_per_launch": step_bytes, "us_per_launch": step_ms * 1e3,
+                             "frac_of_nominal_8tbs": achieved / 8000.0},
                 "tokens_head": tokens[:8]}
+        if wall_s is not None:
+            line["wall_s"] = wall_max
+            line["e2e"] = {"value": args.steps * gen_tokens / wall_max, "unit": UNIT,
+                           "h2d_bytes_per_step": 16 * len(ids) + pixels.numel() * 2, "d2h_bytes_per_step": 4 * gen_tokens + 32,
+                           "api": "efm_b200_vit_encode (host pixels) -> edge_fm.EdgeFM.generate (host ids in / out)" +
+                                  ("" if world == 1 else f", runtime.tensor_parallel = {world}"),
+                           "engine_decode_tok_s": m.get("decode_tokens_per_second"), "engine_prefill_ms": m.get("prefill_ms")}
+            line["e2e_tokens_equal"] = e2e_tokens == tokens
         if breakdown is not None:
             line["roofline"]["kernel_us_unoverlapped"] = breakdown
-        print(json.dumps(line), flush=True)
     enc.close()
     be.close()
+    engine = None
     dist.barrier()
-    dist.destroy_process_group()
+    if rank == 0 and tmp is not None:
+        shutil.rmtree(tmp, ignore_errors=True)
+    if world > 1:
+        dist.destroy_process_group()
+    if rank == 0 and want_cpu:
+        torch.cuda.empty_cache()
+        line["cpu_baseline"] = cpu_baseline(args.config, host_w)
+    return line
 
 
-def run_ours(args, rank, world, local_rank):
+def run_text(args, cfg_id, rank, world, local_rank, *, steps, warmup, want_cpu, dist=None):
+    """Configurations 0-2 on one GPU (world > 1: independent replicas, one per rank)."""
     import torch
     import cabi
     from oracle import synth
-    if args.config == 3:      # 7B-class: tensor parallel over all ranks (one rank: the plain single-GPU path, device-drawn weights)
-        return run_tp(args, rank, world, local_rank)
     torch.cuda.set_device(local_rank)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist_mod
-        dist = dist_mod
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    cfg, prefix, ids, gen_tokens, temp, top_p = workload(args.config)
+    cfg, prefix, ids, gen_tokens, temp, top_p = workload(cfg_id)
     if args.tokens:
         gen_tokens = args.tokens
-    vlm = vlm_request(args.config, cfg) if cfg.mrope_section is not None else None
+    vlm = vlm_request(cfg_id, cfg) if cfg.mrope_section is not None else None
     if vlm is not None:
         ids = vlm["ids"]
     prompt_n = len(ids) - len(prefix)
@@ -403,7 +490,7 @@ def run_ours(args, rank, world, local_rank):
     pos = vlm["pos"] if vlm is not None else None
 
     t_setup = time.perf_counter()
-    w = synth.make_weights(cfg, seed=0)
+    w = synth.make_weights(cfg, seed=0, device="cuda")
     be = cabi.Backend(cfg, max_prefill_tokens=min(2048, max_tokens), max_response_tokens=gen_tokens + 8, device_id=local_rank)
     be.load_weights(w)
     be.alloc_slot(0, max_tokens)
@@ -414,7 +501,7 @@ def run_ours(args, rank, world, local_rank):
     enc = None
     if vlm is not None:
         from oracle import qwen_vit
-        n_patches = sum(t * h * w for t, h, w in vlm["grids"])
+        n_patches = sum(t * h * w_ for t, h, w_ in vlm["grids"])
         enc = cabi.VitEncoder(be, vlm["vcfg"], max_patches=n_patches)
         enc.load_weights(qwen_vit.make_weights(vlm["vcfg"], seed=0, device="cuda"))
         pixels = qwen_vit.make_pixels(vlm["vcfg"], vlm["grids"], seed=0)
@@ -423,16 +510,19 @@ def run_ours(args, rank, world, local_rank):
     be.synchronize()
 
     # public API engine for the end-to-end leg (weights travel through a safetensors checkpoint)
-    import edge_fm
-    tmp = tempfile.mkdtemp(prefix=f"efm_bench_{rank}_")
-    model_dir = synth.write_checkpoint(os.path.join(tmp, "model"), cfg, w)
-    name = "Qwen2.5-VL" if cfg.mrope_section is not None else "Qwen2.5"
-    eng_cfg = synth.write_engine_config(os.path.join(tmp, "engine.json"), model_dir, model_name=name, prefix_ids=prefix,
-                                        max_tokens=max_tokens, max_new_tokens=gen_tokens, temperature=temp, top_p=top_p,
-                                        seed=0, use_cuda_graph=True, device_id=local_rank)
+    engine, tmp = None, None
+    if not args.no_e2e:
+        import edge_fm
+        tmp = scratch_dir(rank, 8)
+        model_dir = synth.write_checkpoint(os.path.join(tmp, "model"), cfg, w)
+        name = "Qwen2.5-VL" if cfg.mrope_section is not None else "Qwen2.5"
+        eng_cfg = synth.write_engine_config(os.path.join(tmp, "engine.json"), model_dir, model_name=name, prefix_ids=prefix,
+                                            max_tokens=max_tokens, max_new_tokens=gen_tokens, temperature=temp, top_p=top_p,
+                                            seed=0, use_cuda_graph=True, device_id=local_rank)
+        engine = edge_fm.EdgeFM(eng_cfg)
+        shutil.rmtree(tmp, ignore_errors=True)
+    host_w = {k: v.cpu() for k, v in w.items()} if want_cpu else None
     del w
-    engine = edge_fm.EdgeFM(eng_cfg)
-    os.remove(os.path.join(model_dir, "model.safetensors"))
     setup_s = time.perf_counter() - t_setup
 
     suffix = ids[len(prefix):]
@@ -460,7 +550,7 @@ def run_ours(args, rank, world, local_rank):
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(args.warmup):
+    for _ in range(warmup):
         one_request()
     sampler = ClockSampler(local_rank)
     sampler.start()
@@ -468,7 +558,7 @@ def run_ours(args, rank, world, local_rank):
     barrier()
     t0 = time.perf_counter()
     pre_ms, dec_ms, vit_ms = 0.0, 0.0, 0.0
-    for _ in range(args.steps):
+    for _ in range(steps):
         a, b, v = one_request()
         pre_ms += a
         dec_ms += b
@@ -492,29 +582,30 @@ def run_ours(args, rank, world, local_rank):
                                   edge_fm.Tensor(pt.data_ptr(), [3, len(ids)], edge_fm.DType.Int32, edge_fm.Device.CPU), [vlm["last"]] * 3)
         req.set_ignore_stop_tokens(True)
         return list(engine.generate(req).token_ids())
-    for _ in range(max(1, args.warmup // 2)):
-        e2e_tokens = e2e_request()
-    barrier()
-    t1 = time.perf_counter()
-    for _ in range(args.steps):
-        e2e_tokens = e2e_request()
-    barrier()
-    e2e_s = time.perf_counter() - t1
+    e2e_s, e2e_tokens, m = None, None, {}
+    if engine is not None:
+        for _ in range(max(1, warmup // 2)):
+            e2e_tokens = e2e_request()
+        barrier()
+        t1 = time.perf_counter()
+        for _ in range(steps):
+            e2e_tokens = e2e_request()
+        barrier()
+        e2e_s = time.perf_counter() - t1
+        m = engine.last_generate_metrics()
     clocks = sampler.stop()
-    m = engine.last_generate_metrics()
 
     # per-kernel device time of a few un-overlapped steps (after the timed region)
     be.decode_begin(0, len(ids), mp, 1)
     breakdown = be.decode_breakdown(4)
     step_bytes = be.decode_step_bytes(len(ids) + gen_tokens // 2)
 
-    dec_steps = args.steps * (gen_tokens - 1)
-    local = torch.tensor([dec_ms, pre_ms, wall_s, e2e_s, vit_ms], dtype=torch.float64, device="cuda")
+    dec_steps = steps * (gen_tokens - 1)
+    local = torch.tensor([dec_ms, pre_ms, wall_s, e2e_s or 0.0, vit_ms], dtype=torch.float64, device="cuda")
     if dist is not None:
         dist.all_reduce(local, op=dist.ReduceOp.MAX)
     dec_ms_max, pre_ms_max, wall_max, e2e_max, vit_ms_max = [float(x) for x in local.tolist()]
     value = world * dec_steps / (dec_ms_max / 1e3)
-    e2e_value = world * args.steps * gen_tokens / e2e_max
     step_ms = dec_ms_max / dec_steps
     peak, peak_kind = peaks()
     achieved = step_bytes / (step_ms * 1e-3) / 1e9
@@ -531,50 +622,55 @@ def run_ours(args, rank, world, local_rank):
             kernels[k]["gbs"] = round(kbytes[k] / (us * 1e-6) / 1e9, 1)
             kernels[k]["frac"] = round(kbytes[k] / (us * 1e-6) / 1e9 / peak, 3)
     traffic = None
-    if args.config in NCU_LAYER_GEMV_DRAM_BYTES:       # measured for the layer GEMVs, algorithmic for the rest of the step
+    if cfg_id in NCU_LAYER_GEMV_DRAM_BYTES:       # measured for the layer GEMVs, algorithmic for the rest of the step
         layer_alg = sum(v for k, v in kbytes.items() if k != "lm_head")
-        traffic = step_bytes + L * (NCU_LAYER_GEMV_DRAM_BYTES[args.config] - layer_alg)
+        traffic = step_bytes + L * (NCU_LAYER_GEMV_DRAM_BYTES[cfg_id] - layer_alg)
+    line = None
     if rank == 0:
         line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": (pre_ms_max + dec_ms_max) / args.steps, "higher_is_better": True, "scaling": "weak",
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
+            "ms_per_step": (vit_ms_max + pre_ms_max + dec_ms_max) / steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"{NAMES[args.config]}: {len(prefix)}-token resident prefix + {prompt_n}-token prompt, "
+            "config": {"workload": f"{NAMES[cfg_id]}: {len(prefix)}-token resident prefix + {prompt_n}-token prompt, "
                                    f"{gen_tokens} generated tokens, batch 1, temperature {temp}, top_p {top_p}",
                        "parallelism": "single GPU" if world == 1 else f"{world} independent replicas",
                        "l2_policy": "weights streamed per decode step exceed L2 (%.2f GB vs 126 MB)" % (step_bytes / 1e9),
                        "cuda_graph": True},
-            "decode_ms_per_token": step_ms, "prefill_ms": pre_ms_max / args.steps,
-            "ttft_ms": (pre_ms_max + vit_ms_max) / args.steps, "wall_s": wall_max, "setup_s": setup_s,
-            "prefill": tensor_report(prefill_flops(cfg, prompt_n, len(prefix)), pre_ms_max / args.steps),
-            "e2e": {"value": e2e_value, "unit": UNIT,
-                    "h2d_bytes_per_step": 4 * prompt_n + (12 * len(ids) + pixels.numel() * 2 if vlm is not None else 0),
-                    "d2h_bytes_per_step": 4 * gen_tokens + 32, "api": "edge_fm.EdgeFM.generate",
-                    "engine_decode_tok_s": m.get("decode_tokens_per_second"), "engine_prefill_ms": m.get("prefill_ms")},
+            "decode_ms_per_token": step_ms, "prefill_ms": pre_ms_max / steps,
+            "ttft_ms": (pre_ms_max + vit_ms_max) / steps, "wall_s": wall_max, "setup_s": setup_s,
+            "prefill": tensor_report(prefill_flops(cfg, prompt_n, len(prefix)), pre_ms_max / steps),
             "gpu_launches": launches,
             "clocks": clocks,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": traffic, "traffic_source": "ncu dram__bytes_read+write of the per-layer GEMV launches (summary under profiles/) + algorithmic bytes of lm_head, attention and vectors" if traffic else None,
-                         "peak_kind": peak_kind, "launch": "one decode step (CUDA graph of %d kernel nodes: 5 per layer + lm_head + sampler)" % (5 * L + 2),
-                         "bytes_per_launch": step_bytes, "us_per_launch": step_ms * 1e3, "kernels": kernels},
-            "tokens_head": tokens[:8], "e2e_tokens_equal": e2e_tokens == tokens,
+                         "traffic": traffic,
+                         "traffic_source": "constants from one ncu capture (dram__bytes_read+write of the per-layer GEMV launches, summary "
+                                           "under profiles/) + algorithmic bytes of lm_head, attention and vectors" if traffic else None,
+                         "peak_kind": peak_kind,
+                         "launch": "one decode step (CUDA graph of %d kernel nodes: 5 per layer + lm_head + sampler)" % (5 * L + 2),
+                         "bytes_per_launch": step_bytes, "us_per_launch": step_ms * 1e3, "frac_of_nominal_8tbs": achieved / 8000.0,
+                         "kernels": kernels},
+            "tokens_head": tokens[:8],
         }
+        if e2e_s is not None:
+            line["e2e"] = {"value": world * steps * gen_tokens / e2e_max, "unit": UNIT,
+                           "h2d_bytes_per_step": 4 * prompt_n + (12 * len(ids) + pixels.numel() * 2 if vlm is not None else 0),
+                           "d2h_bytes_per_step": 4 * gen_tokens + 32, "api": "edge_fm.EdgeFM.generate",
+                           "engine_decode_tok_s": m.get("decode_tokens_per_second"), "engine_prefill_ms": m.get("prefill_ms")}
+            line["e2e_tokens_equal"] = e2e_tokens == tokens
         if vlm is not None:
-            line["vit_ms"] = vit_ms_max / args.steps
-            line["vit"] = tensor_report(vit_flops(vlm["vcfg"], vlm["grids"]), vit_ms_max / args.steps)
-            line["config"]["workload"] = (f"{NAMES[args.config]}: 448x448 image ({n_patches} patches -> {vlm['n_img']} tokens through the "
+            line["vit_ms"] = vit_ms_max / steps
+            line["vit"] = tensor_report(vit_flops(vlm["vcfg"], vlm["grids"]), vit_ms_max / steps)
+            line["config"]["workload"] = (f"{NAMES[cfg_id]}: 448x448 image ({n_patches} patches -> {vlm['n_img']} tokens through the "
                                           f"vision encoder) + {prompt_n - vlm['n_img']} text tokens, {gen_tokens} generated tokens, batch 1, "
                                           f"temperature {temp}, top_p {top_p}")
-        if world == 1 and not args.no_cpu:
-            line["cpu_baseline"] = cpu_baseline(args.config)
-        print(json.dumps(line), flush=True)
     if enc is not None:
         enc.close()
     be.close()
-    del engine
-    if dist is not None:
-        dist.barrier()
-        dist.destroy_process_group()
+    engine = None
+    if rank == 0 and want_cpu:
+        torch.cuda.empty_cache()
+        line["cpu_baseline"] = cpu_baseline(cfg_id, host_w)
+    return line
 
 
 # --------------------------------------------------------------------------------------------------
@@ -635,15 +731,11 @@ def run_vla_reference(args, rank):
                       "e2e": {"value": v, "unit": VLA_UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}), flush=True)
 
 
-def run_vla(args, rank, world, local_rank):
+def run_vla(args, rank, world, local_rank, *, steps, warmup, want_cpu, dist=None):
     import torch
-    import torch.distributed as dist
     import cabi
     from oracle import smolvla          # synthetic weights / inputs (generators only) and the CPU baseline leg
     torch.cuda.set_device(local_rank)
-    if world > 1:
-        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     c = smolvla.VlaConfig()
     t_setup = time.perf_counter()
     w = smolvla.make_weights(c, seed=0)
@@ -652,7 +744,7 @@ def run_vla(args, rank, world, local_rank):
     pol.load_weights(w)
     host = [t.contiguous().pin_memory() for t in (inp[0].float(), inp[1].int(), inp[2].float(), inp[3].float())]
     first = pol.chunk(*host)
-    for _ in range(max(args.warmup, 3)):
+    for _ in range(max(warmup, 3)):
         last = pol.chunk(*host)
     assert torch.equal(first, last), "graph replay differs from the kernel-by-kernel run"
     setup_s = time.perf_counter() - t_setup
@@ -661,42 +753,43 @@ def run_vla(args, rank, world, local_rank):
     sampler = ClockSampler(local_rank)
     sampler.start()
     launches0 = pol.launch_count()[0]
-    if world > 1:
+    if dist is not None:
         dist.barrier()
     torch.cuda.synchronize()
     e0.record(stream)
-    for _ in range(args.steps):
+    for _ in range(steps):
         pol.enqueue()                                  # inputs resident on the device
     e1.record(stream)
     stream.synchronize()
-    if world > 1:
+    if dist is not None:
         dist.barrier()
     torch.cuda.synchronize()
     dev_ms = e0.elapsed_time(e1)
     launches = pol.launch_count()[0] - launches0
     t0 = time.perf_counter()
-    for _ in range(args.steps):
+    for _ in range(steps):
         out = pol.chunk(*host)                         # host buffers in, host actions out
     wall_s = time.perf_counter() - t0
     clocks = sampler.stop()
     pol.phase_ms()
     phases = pol.phase_ms()
-    if world > 1:
+    if dist is not None:
         t = torch.tensor([dev_ms, wall_s], dtype=torch.float64, device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dev_ms, wall_s = [float(x) for x in t.tolist()]
     fl = vla_flops(c)
     total = sum(fl.values())
-    ms = dev_ms / args.steps
+    ms = dev_ms / steps
     peak_tf, kind = tensor_peak()
     achieved = total / (ms * 1e-3) / 1e12
+    line = None
     if rank == 0:
-        line = {"metric": VLA_METRIC, "value": world * args.steps / (dev_ms / 1e3), "unit": VLA_UNIT, "n_gpus": world, "steps": args.steps,
-                "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        line = {"metric": VLA_METRIC, "value": world * steps / (dev_ms / 1e3), "unit": VLA_UNIT, "n_gpus": world, "steps": steps,
+                "warmup": max(warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
                 "dtype": "bf16", "data": "synthetic",
                 "config": dict(vla_config_dict(c), parallelism="single GPU" if world == 1 else f"{world} independent replicas"),
                 "wall_s": wall_s, "setup_s": setup_s,
-                "e2e": {"value": world * args.steps / wall_s, "unit": VLA_UNIT,
+                "e2e": {"value": world * steps / wall_s, "unit": VLA_UNIT,
                         "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in host),
                         "d2h_bytes_per_step": out.numel() * 4, "api": "efm_b200_vla_chunk (C ABI, host buffers)"},
                 "gpu_launches": launches, "clocks": clocks,
@@ -708,15 +801,33 @@ def run_vla(args, rank, world, local_rank):
                 "actions_head": [round(float(x), 4) for x in out[0, :4]]}
         line["roofline"]["phase_ms_kernel_by_kernel"] = {k: round(x, 3) for k, x in phases.items()}
         line["roofline"]["vision"] = tensor_report(fl["vision"], phases["vision"])
-        if not args.no_cpu:
+        if want_cpu:
             v, cores = vla_cpu_chunks_per_s(c, w, smolvla.make_inputs(c, seed=0), 2)
             line["cpu_baseline"] = {"value": v, "unit": VLA_UNIT, "cores": cores, "kind": "port",
                                     "sample": "2 full chunks (fp32 torch-CPU restatement)"}
-        print(json.dumps(line), flush=True)
     pol.close()
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+    return line
+
+
+def summarise(line):
+    """The per-configuration entry of the headline line."""
+    if line is None:
+        return None
+    if line["metric"] == VLA_METRIC:
+        return {"metric": VLA_METRIC, "value": line["value"], "unit": VLA_UNIT, "ms_per_chunk": line["ms_per_step"],
+                "e2e": line["e2e"]["value"], "tensor_frac_whole_chunk": line["roofline"]["frac"],
+                "vision_ms": line["roofline"]["vision"]["ms"], "vision_frac_of_bf16_peak": line["roofline"]["vision"]["frac_of_bf16_peak"],
+                "phase_ms_kernel_by_kernel": line["roofline"]["phase_ms_kernel_by_kernel"], "workload": line["config"]["workload"]}
+    out = {"metric": METRIC, "value": line["value"], "unit": UNIT, "decode_ms_per_token": line["decode_ms_per_token"],
+           "hbm_frac": line["roofline"]["frac"], "hbm_frac_of_nominal_8tbs": line["roofline"]["frac_of_nominal_8tbs"],
+           "prefill_ms": line["prefill_ms"], "prefill_frac_of_bf16_peak": line["prefill"]["frac_of_bf16_peak"],
+           "ttft_ms": line["ttft_ms"], "e2e": line.get("e2e", {}).get("value"), "e2e_tokens_equal": line.get("e2e_tokens_equal"),
+           "kernel_us": {k: v["us_per_launch"] for k, v in line["roofline"]["kernels"].items()},
+           "steps": line["steps"], "workload": line["config"]["workload"]}
+    if "vit" in line:
+        out["vit_ms"] = line["vit_ms"]
+        out["vit_frac_of_bf16_peak"] = line["vit"]["frac_of_bf16_peak"]
+    return out
 
 
 def main():
@@ -725,31 +836,63 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--config", type=int, default=1, choices=[0, 1, 2, 3, 4])
+    ap.add_argument("--config", type=int, default=None, choices=[0, 1, 2, 3, 4],
+                    help="run one configuration alone; default: configuration 3 (tensor parallel over the ranks) plus, on one GPU, "
+                         "a short pass over the other four")
     ap.add_argument("--tokens", type=int, default=0, help="override the number of generated tokens")
-    ap.add_argument("--ref-context", type=int, default=256, help="context length of the CPU arm's bounded sample")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the public-API end-to-end leg (profiling runs)")
+    ap.add_argument("--no-per-config", action="store_true", help="headline run without the pass over configurations 0, 1, 2, 4")
     ap.add_argument("--tp-exchange", default="peer", choices=["peer", "nccl"],
                     help="config 3 on several GPUs: how the decode step sums the row-parallel partials")
     ap.add_argument("--prefill-attention", default="auto", choices=["auto", "bf16", "int8"],
                     help="auto: int8 for config 3 (as the benchmark specifies), bf16 otherwise")
     args = ap.parse_args()
+    headline = args.config is None
+    if headline:
+        args.config = HEADLINE
     if args.prefill_attention == "auto":
         args.prefill_attention = "int8" if args.config == 3 else "bf16"
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else max(args.warmup, 1)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if args.config == 4:
-        if args.impl == "reference":
+    if args.impl == "reference":
+        if args.config == 4:
             run_vla_reference(args, rank)
         else:
-            run_vla(args, rank, world, local_rank)
+            run_reference(args, rank)
         return
-    if args.impl == "reference":
-        run_reference(args, rank)
+    if args.config == 3:
+        line = run_tp(args, rank, world, local_rank)
+        if headline and world == 1 and not args.no_per_config:
+            per = {}
+            for c in (0, 1, 2):
+                per[str(c)] = summarise(run_text(args, c, 0, 1, local_rank, steps=2, warmup=3, want_cpu=False))
+            per["4"] = summarise(run_vla(args, 0, 1, local_rank, steps=5, warmup=3, want_cpu=False))
+            line["per_config"] = per
+        if rank == 0:
+            print(json.dumps(line), flush=True)
         return
-    run_ours(args, rank, world, local_rank)
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist_mod
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        torch.cuda.set_device(local_rank)
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    if args.config == 4:
+        line = run_vla(args, rank, world, local_rank, steps=args.steps, warmup=args.warmup,
+                       want_cpu=world == 1 and not args.no_cpu, dist=dist)
+    else:
+        line = run_text(args, args.config, rank, world, local_rank, steps=args.steps, warmup=args.warmup,
+                        want_cpu=world == 1 and not args.no_cpu, dist=dist)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":

@@ -88,6 +88,27 @@ def make_token_ids(n: int, seed: int = 0, vocab: Optional[int] = None) -> List[i
     return torch.randint(0, hi, (n,), generator=g).tolist()
 
 
+def vlm_request(cfg_id: int) -> dict:
+    """Image-first multimodal prompt of configurations 2 / 3: the image's merged tokens (ids >= vocab select rows of
+    the injected embeddings), then text.  M-RoPE positions: image t = 0, h = merged row, w = merged column; text
+    continues from max(rows, columns) on all three axes."""
+    from . import qwen_vit
+    cfg = CONFIGS[cfg_id]
+    vcfg = qwen_vit.CONFIGS[cfg_id]
+    t, h, w = qwen_vit.GRIDS[cfg_id]
+    hm, wm = h // vcfg.merge, w // vcfg.merge
+    n_img = t * hm * wm
+    n_text = WORKLOADS[cfg_id][1] - n_img
+    ids = [cfg.vocab + k for k in range(n_img)] + make_token_ids(n_text, seed=0)
+    start = max(hm, wm)
+    text_pos = [start + i for i in range(n_text)]
+    pos = [[0] * n_img + text_pos,
+           [r for r in range(hm) for _ in range(wm)] * t + text_pos,
+           [c for _ in range(hm) for c in range(wm)] * t + text_pos]
+    return {"vcfg": vcfg, "grids": [(t, h, w)], "ids": ids, "pos": pos, "n_img": n_img, "embed_id": cfg.vocab,
+            "last": start + n_text - 1}
+
+
 def write_checkpoint(dirname: str, cfg: QwenConfig, weights: Dict[str, torch.Tensor]) -> str:
     from safetensors.torch import save_file
     os.makedirs(dirname, exist_ok=True)

@@ -3,9 +3,11 @@
 Config 0 (Qwen2.5-0.5B shape, 128-token resident prefix + 64-token prompt) is small enough for the CPU
 oracle to finish in seconds, so it is checked against it directly: greedy ids for the first 32 steps
 (bf16_points oracle, teacher-forced; a differing id must be a tie within the observed logit error) and
-logits within 2e-2 relative of the exact fp32 oracle.  Config 1 (1.5B shape, the benchmarked workload) is
-checked through size-independent properties: captured graph == plain launches == persistent kernel,
-resident prefix == full prefill, run-to-run determinism of the seeded top-p sampler."""
+logits within 2e-2 relative of the exact fp32 oracle.  Config 1 (1.5B shape, top-p) and the config 2 text tower
+(3B shape, M-RoPE, injected embeddings) get the same teacher-forced 32-step comparison at their own sizes; config 1
+is also checked through size-independent properties: captured graph == plain launches == persistent kernel,
+resident prefix == full prefill, run-to-run determinism of the seeded top-p sampler.  Every comparison prints its
+worst logit error and the number of tie-limited steps (run pytest with -s to see them)."""
 import os
 
 import numpy as np
@@ -49,6 +51,7 @@ def test_config0_full_size_against_the_oracle():
         if toks[s] != rb.tokens[s]:
             assert rb.margins[s] <= 2 * np.abs(logits[s] - rb.logits[s].numpy()).max(), f"step {s}"
             ties += 1
+    print(f"config 0: worst relative logit error {worst:.2e}, tie-limited steps {ties} of {steps}")
     assert worst < 2e-2, worst
     assert ties <= 3
     be.close()
@@ -86,3 +89,74 @@ def test_config1_full_size_properties():
     assert a[0][0] == b[0][0]
     assert rel(a[1][0], b[1][0]) < 1e-6                     # prefill: identical kernels
     assert rel(a[1][1], b[1][1]) < 1e-2                     # bf16 rounding points amplify the fp32 merge difference
+
+
+def teacher_forced_check(cfg, w, be, ids, steps, *, prefix_n=0, embeds=None, embed_id=-1, pos=None, last_pos=None, sampler=None,
+                         modes=("bf16_points", "exact_fp32")):
+    """The CUDA path generates `steps` tokens (one launch sequence per step, logits read back); the oracle is fed the
+    CUDA path's own tokens.  Returns (worst relative logit error against exact_fp32, number of steps whose id differs
+    from the bf16_points oracle's); a differing id must sit inside twice the observed logit error (a tie)."""
+    toks, logits = cabi.generate(be, 0, ids, steps, prefix_len=prefix_n, embeds=embeds, embed_token_id=embed_id, pos3=pos,
+                                 mrope_last_pos=last_pos, collect_logits=True)
+    torch.set_num_threads(os.cpu_count() or 8)
+    pt = None if pos is None else torch.tensor(pos)
+    e32 = None if embeds is None else embeds.float().cpu()
+    worst, ties = 0.0, 0
+    for mode in modes:
+        o = qwen_text.QwenTextOracle(cfg, w, mode)
+        r = qwen_text.generate(o, ids, steps, forced=toks, embeds=e32, embed_token_id=embed_id, position_ids=pt,
+                               mrope_last_pos=last_pos, sampler=sampler)
+        del o
+        for s in range(steps):
+            ref = r.logits[s].numpy()
+            if mode == "exact_fp32":
+                worst = max(worst, rel(logits[s], ref))
+            if mode == modes[0] and sampler is None and toks[s] != r.tokens[s]:
+                assert r.margins[s] <= 2 * np.abs(logits[s] - ref).max(), f"step {s}: {toks[s]} vs {r.tokens[s]}, margin {r.margins[s]}"
+                ties += 1
+    return toks, logits, worst, ties
+
+
+def test_config1_full_size_against_the_oracle():
+    """The benchmarked top-p workload at its own size (1.5B shape, 512-token resident prefix + 256-token prompt, T 0.7 /
+    top-p 0.9): logits of 32 teacher-forced steps within 2e-2 of the exact fp32 oracle, and every sampled id equal to
+    the CPU statement of the sampling rule applied to the SAME (CUDA) logits with the same seed and step."""
+    from oracle import sampling
+    cfg = synth.CONFIGS[1]
+    prefix_n, prompt_n, _, temp, top_p = synth.WORKLOADS[1]
+    w = synth.make_weights(cfg, seed=0)
+    ids = synth.make_token_ids(prefix_n + prompt_n, seed=0)
+    steps = 32
+    be = cabi.Backend(cfg, max_prefill_tokens=1024, max_response_tokens=64)
+    be.load_weights(w)
+    be.alloc_slot(0, prefix_n + prompt_n + 64)
+    be.set_sampling(temp, top_p, 0)
+    be.prefill(0, ids[:prefix_n], kv_offset=0, sample=False)
+    pick = sampling.make_sampler(temp, top_p, 0)
+    toks, logits, worst, _ = teacher_forced_check(cfg, w, be, ids, steps, prefix_n=prefix_n, sampler=pick, modes=("exact_fp32",))
+    be.close()
+    print(f"config 1: worst relative logit error {worst:.2e} over {steps} teacher-forced steps")
+    assert worst < 2e-2, worst
+    for s in range(steps):
+        assert toks[s] == sampling.sample_top_p(logits[s], temp, top_p, 0, s), f"step {s}"
+
+
+def test_config2_text_tower_full_size_against_the_oracle():
+    """Qwen2.5-VL-3B text tower at its own size: 256 injected embedding rows (seeded noise in place of the vision
+    encoder's output, whose parity is tests/test_gpu_vit.py) + 64 text ids with the benchmark's M-RoPE positions."""
+    cfg = synth.CONFIGS[2]
+    vlm = synth.vlm_request(2)
+    w = synth.make_weights(cfg, seed=0)
+    g = torch.Generator().manual_seed(5)
+    embeds = (torch.randn(vlm["n_img"], cfg.hidden, generator=g) * 0.02).to(torch.bfloat16)
+    steps = 32
+    be = cabi.Backend(cfg, max_prefill_tokens=512, max_response_tokens=64)
+    be.load_weights(w)
+    be.alloc_slot(0, len(vlm["ids"]) + 64)
+    be.set_sampling(0.0, 1.0, 0)
+    _, _, worst, ties = teacher_forced_check(cfg, w, be, vlm["ids"], steps, embeds=embeds.cuda(), embed_id=vlm["embed_id"],
+                                             pos=vlm["pos"], last_pos=[vlm["last"]] * 3)
+    be.close()
+    print(f"config 2 text tower: worst relative logit error {worst:.2e}, tie-limited steps {ties} of {steps}")
+    assert worst < 2e-2, worst
+    assert ties <= 3

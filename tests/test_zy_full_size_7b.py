@@ -1,0 +1,73 @@
+"""GPU: configuration 3's text tower (Qwen2.5-VL-7B shape) at its own size against the fp32 CPU oracle.
+
+The oracle holds 7.6 B parameters in fp32 (30 GB of host memory) and needs about a minute per prefill on a
+16-core host, so this file keeps to 8 teacher-forced steps and one oracle mode (exact_fp32: logits within 2e-2
+relative; a differing greedy id must sit inside twice the observed logit error).  Both prefill attention kernels are
+checked: the bf16 one and the INT8 scheme the benchmark uses.  Skipped when the host has less than 72 GB free.
+Collected late so that its cost comes after every other test file but the allocation-free entry point's."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import cabi
+from oracle import qwen_text, synth
+
+pytestmark = pytest.mark.gpu
+
+
+def host_free_gb():
+    try:
+        import psutil
+        return psutil.virtual_memory().available / 2 ** 30
+    except Exception:
+        return 0.0
+
+
+def test_config3_text_tower_full_size_against_the_oracle():
+    if host_free_gb() < 72:
+        pytest.skip("the fp32 oracle of the 7B shape needs about 50 GB of host memory")
+    cfg = synth.CONFIGS[3]
+    vlm = synth.vlm_request(3)
+    ids, pos, last = vlm["ids"], vlm["pos"], [vlm["last"]] * 3
+    torch.set_num_threads(os.cpu_count() or 8)
+    w = synth.make_weights(cfg, seed=0)
+    g = torch.Generator().manual_seed(5)
+    embeds = (torch.randn(vlm["n_img"], cfg.hidden, generator=g) * 0.02).to(torch.bfloat16)
+    steps = 8
+    be = cabi.Backend(cfg, max_prefill_tokens=2048, max_response_tokens=16)
+    for name, t in w.items():
+        be.load_weights_partial({name: t})
+    be.finalize()
+    be.alloc_slot(0, len(ids) + 16)
+    be.set_sampling(0.0, 1.0, 0)
+    runs = {}
+    for kind in (0, 1):                                  # bf16 flash attention, then INT8 Q.K^T / fp16 P.V
+        be.set_prefill_attention(kind)
+        runs[kind] = cabi.generate(be, 0, ids, steps, embeds=embeds.cuda(), embed_token_id=vlm["embed_id"], pos3=pos,
+                                   mrope_last_pos=last, collect_logits=True)
+    be.close()
+    o = qwen_text.QwenTextOracle(cfg, w, "exact_fp32")
+    del w
+    pt, e32 = torch.tensor(pos), embeds.float()
+    with torch.no_grad():
+        first = o.forward(ids, embeds=e32, embed_token_id=vlm["embed_id"], position_ids=pt)
+    n0 = o.kv_len
+    for kind, (toks, logits) in runs.items():
+        o.truncate(n0)
+        worst, ties, lg = 0.0, 0, first
+        with torch.no_grad():
+            for s in range(steps):
+                ref = lg.numpy()
+                err = np.abs(logits[s] - ref).max()
+                worst = max(worst, float(err / np.abs(ref).max()))
+                if toks[s] != qwen_text.greedy(lg):
+                    assert qwen_text.top2_margin(lg) <= 2 * err, f"kind {kind} step {s}"
+                    ties += 1
+                if s + 1 < steps:
+                    lg = o.forward([toks[s]], position_ids=torch.full((3, 1), last[0] + 1 + s))
+        print(f"config 3 text tower, prefill attention {'int8' if kind else 'bf16'}: worst relative logit error {worst:.2e}, "
+              f"tie-limited steps {ties} of {steps}")
+        assert worst < 2e-2, (kind, worst)
+        assert ties <= 2

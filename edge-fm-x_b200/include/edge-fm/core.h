@@ -39,6 +39,10 @@ enum class DType { Float32, Float16, BFloat16, Int32, Int64, UInt8, Int8 };
 // Who releases a Tensor's buffer, and how.  Says nothing about who allocated or copied it:
 // Tensor::view never frees, Tensor::adopt frees a buffer it was handed, Tensor::clone_from
 // frees the buffer it allocated.
+// Which of a model's two passes (and weight sets) a call refers to; the reference keeps this enum next to its Engine
+// (src/engine/engine.h:16) and exposes it from the Python module.
+enum class ModelStage { Prefill, Decode };
+
 enum class MemoryOwnership {
     ViewExternal,    // never freed by the Tensor
     OwnCpuMalloc,    // std::free

@@ -1,6 +1,7 @@
 // edge_fm::EdgeFM facade: configuration -> engine -> warmup; generate() forwards.
 // Reference: src/edge-fm.cpp:12-22 (the constructor runs warmup) and the base Engine's
-// refusal of stage / planner calls the configured task does not provide (src/engine/engine.cpp:551-564).
+// refusal of planner calls the configured task does not provide (src/engine/engine.cpp:551-564); the stage calls
+// (run_stage / prefill / decode) are served by the token-generation engine.
 // task = trajectory_planning builds the action-chunk engine instead and serves plan().
 #include <edge-fm/edge-fm.h>
 
@@ -36,15 +37,13 @@ TensorMap EdgeFM::plan(int32_t request_id, const TensorRefMap& inputs) const {
     if (!impl_->planner) throw ConfigurationError("plan() is not supported by the active engine (task=token_generation)");
     return impl_->planner->plan(request_id, inputs);
 }
-TensorMap EdgeFM::run_stage(int32_t, const std::string& stage_name, const TensorRefMap&) const {
-    throw ConfigurationError("run_stage('" + stage_name + "') is not supported by the active engine (task=token_generation)");
+TensorMap EdgeFM::run_stage(int32_t request_id, const std::string& stage_name, const TensorRefMap& inputs) const {
+    if (!impl_->engine) throw ConfigurationError("run_stage('" + stage_name + "') is not supported by the active engine (task=trajectory_planning): use plan()");
+    return impl_->engine->run_stage(request_id, stage_name, inputs);
 }
-TensorMap EdgeFM::prefill(int32_t, const TensorRefMap&) const {
-    throw ConfigurationError("prefill() stage API is not supported by the active engine; use generate()");
-}
-TensorMap EdgeFM::decode(int32_t, const TensorRefMap&) const {
-    throw ConfigurationError("decode() stage API is not supported by the active engine; use generate()");
-}
+// compatibility wrappers, as the reference's base Engine defines them (src/engine/engine.cpp:542-548)
+TensorMap EdgeFM::prefill(int32_t request_id, const TensorRefMap& inputs) const { return run_stage(request_id, "prefill", inputs); }
+TensorMap EdgeFM::decode(int32_t request_id, const TensorRefMap& inputs) const { return run_stage(request_id, "decode", inputs); }
 
 std::unordered_map<std::string, double> EdgeFM::last_generate_metrics() const {
     if (!impl_->engine) return {};
@@ -54,7 +53,10 @@ std::unordered_map<std::string, double> EdgeFM::last_plan_metrics() const {
     if (!impl_->planner) return {};
     return impl_->planner->last_plan_metrics();
 }
-std::unordered_map<std::string, double> EdgeFM::last_stage_metrics() const { return {}; }
+std::unordered_map<std::string, double> EdgeFM::last_stage_metrics() const {
+    if (!impl_->engine) return {};
+    return impl_->engine->last_stage_metrics();
+}
 
 void EdgeFM::tune() {}
 

@@ -7,6 +7,7 @@
 
 #include <algorithm>
 #include <chrono>
+#include <cstdlib>
 #include <cstring>
 #include <unordered_set>
 
@@ -107,6 +108,7 @@ StandardEngine::StandardEngine(const EngineConfig& config) : config_(config) {
     }
     use_mrope_ = d.use_mrope != 0;
     hidden_ = d.hidden;
+    vocab_ = d.vocab;
     if (model == "qwen2_5" && use_mrope_) throw ConfigurationError("model_name Qwen2.5 with an mrope checkpoint: use Qwen2.5-VL");
 
     // tied lm_head <=> the checkpoint carries no lm_head.weight (reference: src/layers/linear.cu:2244-2248)
@@ -236,6 +238,165 @@ void StandardEngine::warmup() {
     check(efm_b200_synchronize(ctx_), "warmup");
 }
 
+void StandardEngine::build_positions(const Request& request, const Context& ctx, std::vector<int32_t>* pos_out, int32_t last_pos[3]) const {
+    if (!use_mrope_) return;
+    std::vector<int32_t>& pos = *pos_out;
+    const int32_t S = ctx.seq_len, P = ctx.prefix_size, n = ctx.prefill_tokens;
+    pos.resize(3 * (size_t)n);
+    int32_t global_max = 0;
+    if (request.has_position_ids()) {
+        const Tensor& t = request.position_ids();
+        if (t.shape().size() != 2 || t.shape()[0] != 3 || t.shape()[1] != S)
+            throw InvalidRequestError("position_ids must have shape [3, seq_len]");
+        if (t.dtype() != DType::Int32 && t.dtype() != DType::Int64) throw InvalidRequestError("position_ids must be int32 or int64");
+        const size_t esz = get_dtype_size(t.dtype());
+        std::vector<char> host(3 * (size_t)S * esz);
+        if (std::get<0>(t.device()) == Device::GPU) {
+            if (cudaMemcpy(host.data(), t.data_ptr(), host.size(), cudaMemcpyDeviceToHost) != cudaSuccess)
+                throw DeviceError("copying position_ids to the host failed");
+        } else {
+            std::memcpy(host.data(), t.data_ptr(), host.size());
+        }
+        for (int r = 0; r < 3; ++r)
+            for (int32_t i = 0; i < S; ++i) {
+                int64_t v;
+                if (esz == 4) { int32_t x; std::memcpy(&x, host.data() + ((size_t)r * S + i) * 4, 4); v = x; }
+                else std::memcpy(&v, host.data() + ((size_t)r * S + i) * 8, 8);
+                global_max = std::max<int32_t>(global_max, (int32_t)v);
+                if (i >= P) pos[(size_t)r * n + (i - P)] = (int32_t)v;
+            }
+    } else {
+        for (int r = 0; r < 3; ++r)
+            for (int32_t i = 0; i < n; ++i) pos[(size_t)r * n + i] = P + i;
+        global_max = S - 1;
+    }
+    // decode positions start one past the last prefill position on every axis
+    // (reference: Qwen2_5::prepare_decode_position_ids, qwen2_5.cpp:932-955)
+    for (int r = 0; r < 3; ++r)
+        last_pos[r] = request.has_mrope_last_pos() && request.mrope_last_pos().size() >= 3 ? request.mrope_last_pos()[r] : global_max;
+}
+
+namespace {
+// small integer tensor (int32 / int64, host or device) -> host int32 values
+std::vector<int32_t> read_int_tensor(const Tensor& t, const char* what) {
+    if (t.dtype() != DType::Int32 && t.dtype() != DType::Int64) throw InvalidRequestError(std::string(what) + " must be int32 or int64");
+    size_t n = 1;
+    for (int64_t d : t.shape()) n *= (size_t)std::max<int64_t>(d, 0);
+    const size_t esz = get_dtype_size(t.dtype());
+    std::vector<char> host(n * esz);
+    if (n == 0) return {};
+    if (std::get<0>(t.device()) == Device::GPU) {
+        if (cudaMemcpy(host.data(), t.data_ptr(), host.size(), cudaMemcpyDeviceToHost) != cudaSuccess)
+            throw DeviceError(std::string("copying ") + what + " to the host failed");
+    } else {
+        std::memcpy(host.data(), t.data_ptr(), host.size());
+    }
+    std::vector<int32_t> out(n);
+    for (size_t i = 0; i < n; ++i) {
+        if (esz == 4) std::memcpy(&out[i], host.data() + i * 4, 4);
+        else { int64_t v; std::memcpy(&v, host.data() + i * 8, 8); out[i] = (int32_t)v; }
+    }
+    return out;
+}
+const Tensor* find_input(const TensorRefMap& inputs, const char* name) {
+    auto it = inputs.find(name);
+    return it != inputs.end() && it->second != nullptr && !it->second->empty() ? it->second : nullptr;
+}
+}  // namespace
+
+TensorMap StandardEngine::stage_outputs(int32_t response_index) {
+    TensorMap out;
+    void* lbuf = std::malloc((size_t)vocab_ * sizeof(float));
+    void* tbuf = std::malloc(sizeof(int32_t));
+    if (lbuf == nullptr || tbuf == nullptr) { std::free(lbuf); std::free(tbuf); throw OutOfMemoryError("stage outputs"); }
+    Tensor logits = Tensor::adopt(lbuf, {1, (int64_t)vocab_}, DType::Float32, Device::CPU, 0, MemoryOwnership::OwnCpuMalloc);
+    Tensor token = Tensor::adopt(tbuf, {1}, DType::Int32, Device::CPU, 0, MemoryOwnership::OwnCpuMalloc);
+    check(efm_b200_read_logits(ctx_, static_cast<float*>(logits.data_ptr()), vocab_), "reading logits");
+    check(efm_b200_read_tokens(ctx_, static_cast<int32_t*>(token.data_ptr()), response_index, 1), "reading the sampled token");
+    if (compact_.enabled()) {
+        std::vector<int32_t> one(1, *static_cast<int32_t*>(token.data_ptr()));
+        one = compact_.restore_token_ids(one, "stage next_token");
+        *static_cast<int32_t*>(token.data_ptr()) = one[0];
+    }
+    out.emplace("logits", std::move(logits));
+    out.emplace("next_token", std::move(token));
+    return out;
+}
+
+TensorMap StandardEngine::run_stage(int32_t request_id, const std::string& stage_name, const TensorRefMap& inputs) {
+    const double t0 = now_ms();
+    stage_metrics_.clear();
+    if (stage_name == "prefill") {
+        const Tensor* ids_t = find_input(inputs, "token_ids");
+        if (ids_t == nullptr) throw InvalidRequestError("prefill stage needs token_ids");
+        const std::vector<int32_t> ids = read_int_tensor(*ids_t, "token_ids");
+        const Tensor* emb = find_input(inputs, "embedding");
+        const Tensor* pid = find_input(inputs, "position_ids");
+        const Tensor* eid = find_input(inputs, "embed_token_id");
+        const Tensor* mlp = find_input(inputs, "mrope_last_pos");
+        const int32_t embed_token_id = eid != nullptr ? read_int_tensor(*eid, "embed_token_id").at(0) : -1;
+        std::unique_ptr<Request> req;
+        if (emb != nullptr && pid != nullptr && mlp != nullptr)
+            req.reset(new Request(request_id, ids, *emb, embed_token_id, *pid, read_int_tensor(*mlp, "mrope_last_pos")));
+        else if (emb != nullptr && pid != nullptr) req.reset(new Request(request_id, ids, *emb, embed_token_id, *pid));
+        else if (emb != nullptr) req.reset(new Request(request_id, ids, *emb, embed_token_id));
+        else req.reset(new Request(request_id, ids));
+        const Request& request = *req;
+        Context ctx = scheduler_->create_context(request);
+        if (ctx.prefill_tokens <= 0) throw InvalidRequestError("prefill stage: nothing beyond the resident prefix");
+        const std::vector<int32_t> model_ids = compact_.remap_token_ids(request.token_ids(), "stage token_ids");
+        const void* embeds = nullptr;
+        int32_t n_embeds = 0, embeds_mem = EFM_MEM_HOST, model_embed_id = request.embed_token_id();
+        if (request.has_embedding()) {
+            const Tensor& e = request.embedding();
+            if (e.dtype() != DType::BFloat16 || e.shape().size() != 2 || e.shape()[1] != hidden_)
+                throw InvalidRequestError("embedding must be bf16 [N, hidden_size]");
+            if (request.embed_token_id() < 0) throw InvalidRequestError("embedding given without embed_token_id");
+            embeds = e.data_ptr();
+            n_embeds = (int32_t)e.shape()[0];
+            embeds_mem = std::get<0>(e.device()) == Device::GPU ? EFM_MEM_DEVICE : EFM_MEM_HOST;
+            model_embed_id = compact_.remap_embed_token_id(request.embed_token_id(), n_embeds);
+        }
+        std::vector<int32_t> pos;
+        int32_t last_pos[3] = {0, 0, 0};
+        if (use_mrope_ && !request.has_position_ids() && pid != nullptr) throw InvalidRequestError("position_ids need an embedding tensor in this API");
+        build_positions(request, ctx, &pos, last_pos);
+        check(efm_b200_prefill(ctx_, ctx.request_id, model_ids.data() + ctx.prefix_size, ctx.prefill_tokens, ctx.prefix_size, embeds,
+                               n_embeds, model_embed_id, embeds_mem, use_mrope_ ? pos.data() : nullptr, 1),
+              "prefill stage");
+        StageState& st = stage_state_[request_id];
+        st.kv_len = ctx.seq_len;
+        for (int r = 0; r < 3; ++r) st.next_pos[r] = last_pos[r] + 1;
+        st.primed = true;
+        TensorMap out = stage_outputs(0);
+        stage_metrics_ = {{"stage_ms", now_ms() - t0}, {"kv_len", (double)st.kv_len}, {"stage_tokens", (double)ctx.prefill_tokens}};
+        return out;
+    }
+    if (stage_name == "decode") {
+        auto it = stage_state_.find(request_id);
+        if (it == stage_state_.end() || !it->second.primed) throw InvalidRequestError("decode stage before a prefill stage for request_id " + std::to_string(request_id));
+        StageState& st = it->second;
+        const KVSlotStatus* slot = kv_manager_->find_slot(request_id);
+        if (slot == nullptr || st.kv_len + 1 > slot->max_tokens)
+            throw InvalidRequestError("decode stage: the KV slot of request_id " + std::to_string(request_id) + " is full");
+        // every call binds the slot afresh and writes its sample to response position 1
+        check(efm_b200_decode_begin(ctx_, request_id, st.kv_len, st.next_pos, 1), "decode stage setup");
+        if (const Tensor* ids_t = find_input(inputs, "token_ids")) {
+            std::vector<int32_t> feed = read_int_tensor(*ids_t, "token_ids");
+            if (feed.size() != 1) throw InvalidRequestError("decode stage takes exactly one token");
+            feed = compact_.remap_token_ids(feed, "stage token_ids");
+            check(efm_b200_set_token(ctx_, feed[0]), "decode stage token");
+        }
+        check(efm_b200_decode_steps(ctx_, 1, use_graph_ ? 1 : 0), "decode stage");
+        st.kv_len += 1;
+        for (int r = 0; r < 3; ++r) st.next_pos[r] += 1;
+        TensorMap out = stage_outputs(1);
+        stage_metrics_ = {{"stage_ms", now_ms() - t0}, {"kv_len", (double)st.kv_len}, {"stage_tokens", 1.0}};
+        return out;
+    }
+    throw ConfigurationError("run_stage('" + stage_name + "'): the token-generation engine serves the stages \"prefill\" and \"decode\"");
+}
+
 Response StandardEngine::generate(const Request& request) {
     metrics_.clear();
     Response response;
@@ -273,41 +434,7 @@ Response StandardEngine::generate(const Request& request) {
     }
     std::vector<int32_t> pos;          // [3, prefill_tokens]
     int32_t last_pos[3] = {0, 0, 0};
-    if (use_mrope_) {
-        const int32_t S = ctx.seq_len, P = ctx.prefix_size, n = ctx.prefill_tokens;
-        pos.resize(3 * (size_t)n);
-        int32_t global_max = 0;
-        if (request.has_position_ids()) {
-            const Tensor& t = request.position_ids();
-            if (t.shape().size() != 2 || t.shape()[0] != 3 || t.shape()[1] != S)
-                throw InvalidRequestError("position_ids must have shape [3, seq_len]");
-            if (t.dtype() != DType::Int32 && t.dtype() != DType::Int64) throw InvalidRequestError("position_ids must be int32 or int64");
-            const size_t esz = get_dtype_size(t.dtype());
-            std::vector<char> host(3 * (size_t)S * esz);
-            if (std::get<0>(t.device()) == Device::GPU) {
-                if (cudaMemcpy(host.data(), t.data_ptr(), host.size(), cudaMemcpyDeviceToHost) != cudaSuccess)
-                    throw DeviceError("copying position_ids to the host failed");
-            } else {
-                std::memcpy(host.data(), t.data_ptr(), host.size());
-            }
-            for (int r = 0; r < 3; ++r)
-                for (int32_t i = 0; i < S; ++i) {
-                    int64_t v;
-                    if (esz == 4) { int32_t x; std::memcpy(&x, host.data() + ((size_t)r * S + i) * 4, 4); v = x; }
-                    else std::memcpy(&v, host.data() + ((size_t)r * S + i) * 8, 8);
-                    global_max = std::max<int32_t>(global_max, (int32_t)v);
-                    if (i >= P) pos[(size_t)r * n + (i - P)] = (int32_t)v;
-                }
-        } else {
-            for (int r = 0; r < 3; ++r)
-                for (int32_t i = 0; i < n; ++i) pos[(size_t)r * n + i] = P + i;
-            global_max = S - 1;
-        }
-        // decode positions start one past the last prefill position on every axis
-        // (reference: Qwen2_5::prepare_decode_position_ids, qwen2_5.cpp:932-955)
-        for (int r = 0; r < 3; ++r)
-            last_pos[r] = request.has_mrope_last_pos() && request.mrope_last_pos().size() >= 3 ? request.mrope_last_pos()[r] : global_max;
-    }
+    build_positions(request, ctx, &pos, last_pos);
 
     // ---- prefill ----------------------------------------------------------------------------
     const double t_prep = now_ms();

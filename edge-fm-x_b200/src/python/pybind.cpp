@@ -90,6 +90,9 @@ PYBIND11_MODULE(edge_fm, m) {
         .value("Float32", DType::Float32).value("Float16", DType::Float16).value("BFloat16", DType::BFloat16)
         .value("Int32", DType::Int32).value("Int64", DType::Int64).value("UInt8", DType::UInt8).value("Int8", DType::Int8)
         .export_values();
+    // which of a model's two weight sets / passes a call refers to (reference: src/engine/engine.h:16, bound at
+    // src/python/pybind_debug.cpp:349-351)
+    py::enum_<ModelStage>(m, "ModelStage").value("Prefill", ModelStage::Prefill).value("Decode", ModelStage::Decode);
     py::enum_<MemoryOwnership>(m, "MemoryOwnership")
         .value("ViewExternal", MemoryOwnership::ViewExternal).value("OwnCpuMalloc", MemoryOwnership::OwnCpuMalloc)
         .value("OwnCudaMalloc", MemoryOwnership::OwnCudaMalloc).value("OwnCudaPool", MemoryOwnership::OwnCudaPool);
@@ -148,6 +151,40 @@ PYBIND11_MODULE(edge_fm, m) {
                  return tensor_map_to_py_dict(std::move(result));
              },
              py::arg("request_id"), py::arg("inputs"))
+        .def("run_stage",
+             [](const EdgeFM& self, int32_t request_id, const std::string& stage, const py::dict& inputs) {
+                 TensorRefMap refs = tensor_ref_map_from_py_dict(inputs);
+                 TensorMap result;
+                 {
+                     py::gil_scoped_release release;
+                     result = self.run_stage(request_id, stage, refs);
+                 }
+                 return tensor_map_to_py_dict(std::move(result));
+             },
+             py::arg("request_id"), py::arg("stage_name"), py::arg("inputs"))
+        .def("prefill",
+             [](const EdgeFM& self, int32_t request_id, const py::dict& inputs) {
+                 TensorRefMap refs = tensor_ref_map_from_py_dict(inputs);
+                 TensorMap result;
+                 {
+                     py::gil_scoped_release release;
+                     result = self.prefill(request_id, refs);
+                 }
+                 return tensor_map_to_py_dict(std::move(result));
+             },
+             py::arg("request_id"), py::arg("inputs"))
+        .def("decode",
+             [](const EdgeFM& self, int32_t request_id, const py::dict& inputs) {
+                 TensorRefMap refs = tensor_ref_map_from_py_dict(inputs);
+                 TensorMap result;
+                 {
+                     py::gil_scoped_release release;
+                     result = self.decode(request_id, refs);
+                 }
+                 return tensor_map_to_py_dict(std::move(result));
+             },
+             py::arg("request_id"), py::arg("inputs"))
+        .def("last_stage_metrics", &EdgeFM::last_stage_metrics)
         .def("last_plan_metrics", &EdgeFM::last_plan_metrics)
         .def("last_generate_metrics", &EdgeFM::last_generate_metrics)
         .def("tune", &EdgeFM::tune);

@@ -353,3 +353,69 @@ def test_edge_fm_compact_vocab_and_int8_prefill_through_the_public_api(tmp_path,
     json.dump(cfg, open(path, "w"))
     with pytest.raises(Exception, match="pre-pruned"):
         edge_fm.EdgeFM(path)
+
+
+def test_edge_fm_stage_api_prefill_and_decode(tmp_path, built):
+    """Tensor-in / tensor-out stage calls (EdgeFM.prefill / decode / run_stage): the prefill stage over a request whose
+    prefix is resident returns the logits and the first token generate() returns; decode stages, one token each, walk
+    the same greedy sequence and accept a fed token; both kinds of M-RoPE input travel as tensors."""
+    import edge_fm
+    for kw in (dict(), dict(mrope_section=[8, 12, 12], model_type="qwen2_5_vl")):
+        cfg = synth.tiny_config(num_layers=2, hidden=256, q_heads=4, kv_heads=2, intermediate=256, vocab=1500, **kw)
+        tag = "vl" if kw else "text"
+        w = synth.make_weights(cfg, seed=11)
+        model_dir = synth.write_checkpoint(str(tmp_path / f"model_{tag}"), cfg, w)
+        prefix = synth.make_token_ids(9, seed=3, vocab=cfg.vocab) if not kw else []
+        prompt = prefix + synth.make_token_ids(14, seed=4, vocab=cfg.vocab)
+        path = synth.write_engine_config(str(tmp_path / f"engine_{tag}.json"), model_dir, model_name="Qwen2.5-VL" if kw else "Qwen2.5",
+                                         prefix_ids=prefix, max_tokens=64, max_new_tokens=8)
+        eng = edge_fm.EdgeFM(path)
+        ids_t = torch.tensor(prompt, dtype=torch.int32)
+        inputs = {"token_ids": edge_fm.Tensor(ids_t.data_ptr(), [len(prompt)], edge_fm.DType.Int32, edge_fm.Device.CPU)}
+        if kw:
+            emb = (torch.randn(3, cfg.hidden) * 0.02).to(torch.bfloat16)
+            ids_v = [cfg.vocab, cfg.vocab + 1, cfg.vocab + 2] + prompt
+            pos = torch.tensor([[0, 0, 0] + list(range(2, 2 + len(prompt))), [0, 0, 1] + list(range(2, 2 + len(prompt))),
+                                [0, 1, 0] + list(range(2, 2 + len(prompt)))], dtype=torch.int32)
+            req = edge_fm.Request(0, ids_v, edge_fm.Tensor(emb.data_ptr(), [3, cfg.hidden], edge_fm.DType.BFloat16, edge_fm.Device.CPU),
+                                  cfg.vocab, edge_fm.Tensor(pos.data_ptr(), [3, len(ids_v)], edge_fm.DType.Int32, edge_fm.Device.CPU))
+            ids_t = torch.tensor(ids_v, dtype=torch.int64)                 # int64 ids are accepted too
+            eid = torch.tensor([cfg.vocab], dtype=torch.int32)
+            inputs = {"token_ids": edge_fm.Tensor(ids_t.data_ptr(), [1, len(ids_v)], edge_fm.DType.Int64, edge_fm.Device.CPU),
+                      "embedding": edge_fm.Tensor(emb.data_ptr(), [3, cfg.hidden], edge_fm.DType.BFloat16, edge_fm.Device.CPU),
+                      "embed_token_id": edge_fm.Tensor(eid.data_ptr(), [1], edge_fm.DType.Int32, edge_fm.Device.CPU),
+                      "position_ids": edge_fm.Tensor(pos.data_ptr(), [3, len(ids_v)], edge_fm.DType.Int32, edge_fm.Device.CPU)}
+        else:
+            req = edge_fm.Request(0, prompt)
+        req.set_ignore_stop_tokens(True)
+        want = list(eng.generate(req).token_ids())
+        assert len(want) == 8
+
+        def unpack(out):
+            lg = torch.from_dlpack(out["logits"].to_dlpack()).clone()
+            tk = int(torch.from_dlpack(out["next_token"].to_dlpack())[0])
+            assert lg.shape == (1, cfg.vocab) and lg.dtype == torch.float32
+            assert int(lg.argmax()) == tk
+            return lg, tk
+
+        _, t0 = unpack(eng.prefill(0, inputs))
+        got = [t0]
+        assert eng.last_stage_metrics()["kv_len"] == len(ids_t.flatten())
+        for _ in range(7):
+            _, t = unpack(eng.decode(0, {}))
+            got.append(t)
+        assert got == want
+        # the same walk with every token fed explicitly (run_stage by name), restarting from the prefill stage
+        _, t0 = unpack(eng.run_stage(0, "prefill", inputs))
+        again = [t0]
+        for s in range(7):
+            feed = torch.tensor([want[s]], dtype=torch.int32)
+            _, t = unpack(eng.run_stage(0, "decode", {"token_ids": edge_fm.Tensor(feed.data_ptr(), [1], edge_fm.DType.Int32, edge_fm.Device.CPU)}))
+            again.append(t)
+        assert again == want
+        with pytest.raises(ValueError, match="prefill"):
+            eng.run_stage(0, "context", {})
+        with pytest.raises(ValueError, match="before a prefill"):
+            eng.decode(1, {}) if False else edge_fm.EdgeFM.decode(eng, 7, {})
+        assert edge_fm.ModelStage.Prefill != edge_fm.ModelStage.Decode
+        del eng

@@ -50,6 +50,24 @@ struct SageScratch {
 
 }  // namespace efm
 
+namespace efm {
+// One captured prefill pass: the launch sequence of a single chunk with every shape-dependent argument baked in.
+// Valid for exactly the (slot, rows, cache offset, injected-embedding, sampling, attention-kind) combination it
+// was captured with; the per-request inputs (ids, positions, embeddings, state) live in stable buffers that are
+// refreshed by copies issued before the launch.
+struct PrefillGraph {
+    int slot = 0, rows = 0, kv_offset = 0, n_embeds = 0, embed_token_id = 0, sample = 0, attention_kind = 0;
+    const void* embeds_buf = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    int nodes = 0;
+    uint64_t last_use = 0;
+    bool same_key(const PrefillGraph& o) const {
+        return slot == o.slot && rows == o.rows && kv_offset == o.kv_offset && n_embeds == o.n_embeds && embed_token_id == o.embed_token_id &&
+               sample == o.sample && attention_kind == o.attention_kind && embeds_buf == o.embeds_buf;
+    }
+};
+}  // namespace efm
+
 struct efm_b200_ctx {
     efm_model_desc d{};                   // geometry as THIS RANK sees it (heads / MLP columns already sharded)
     efm_model_desc full{};                // geometry of the whole model (weight slicing)
@@ -127,6 +145,12 @@ struct efm_b200_ctx {
     efm_sampling sampling{0.f, 1.f, 1, 0, 0};
     std::map<int, efm::KvSlot> slots;
     int bound_slot = -1;
+    // prefill CUDA graphs (short prompts are launch-bound): a shape is launched kernel by kernel the first time it is
+    // seen, captured the second time, replayed afterwards; at most kMaxPrefillGraphs shapes are kept (least recently used out)
+    bool prefill_graphs = false;
+    std::vector<efm::PrefillGraph> prefill_cache;     // exec == nullptr: seen once, not captured yet
+    uint64_t prefill_clock = 0;
+    int64_t prefill_graph_replays = 0;
     int64_t launches = 0;
     cudaEvent_t events[16] = {};
     std::vector<void*> allocations;

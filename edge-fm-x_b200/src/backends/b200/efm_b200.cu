@@ -100,6 +100,13 @@ efm_status ctx_sync(efm_b200_ctx* c) {
     return EFM_OK;
 }
 
+constexpr size_t kMaxPrefillGraphs = 8;
+void drop_prefill_graphs(efm_b200_ctx* c) {
+    for (auto& g : c->prefill_cache)
+        if (g.exec != nullptr) cudaGraphExecDestroy(g.exec);
+    c->prefill_cache.clear();
+}
+
 enum : uint32_t { kQw = 1, kQb = 2, kKw = 4, kKb = 8, kVw = 16, kVb = 32, kO = 64, kGate = 128, kUp = 256,
                   kDown = 512, kInNorm = 1024, kPostNorm = 2048 };
 constexpr uint32_t kRequired = kQw | kKw | kVw | kO | kGate | kUp | kDown | kInNorm | kPostNorm;
@@ -277,6 +284,7 @@ efm_status efm_b200_destroy(efm_b200_ctx* c) {
     if (c->stream != nullptr) cudaStreamSynchronize(c->stream);
     for (auto& kv : c->slots)      // graphs that hold collective nodes go before their communicator
         if (kv.second.graph != nullptr) cudaGraphExecDestroy(kv.second.graph);
+    drop_prefill_graphs(c);
     for (int r = 0; r < 8; ++r)
         if (c->peers_ready && r != c->tp_rank && c->peer_base[r] != nullptr) cudaIpcCloseMemHandle(c->peer_base[r]);
     if (c->nccl_comm != nullptr && nccl_api().ok) nccl_api().comm_destroy(c->nccl_comm);
@@ -367,6 +375,7 @@ efm_status efm_b200_tp_peer_import(efm_b200_ctx* c, const void* handles, int32_t
     }
     for (auto& kv : c->slots)       // decode graphs captured with the NCCL form are rebuilt on next use
         if (kv.second.graph != nullptr) { cudaGraphExecDestroy(kv.second.graph); kv.second.graph = nullptr; }
+    drop_prefill_graphs(c);
     c->peers_ready = true;
     return EFM_OK;
 }
@@ -534,9 +543,27 @@ efm_status efm_b200_set_sampling(efm_b200_ctx* c, const efm_sampling* s) {
     if (!(s->temperature >= 0.f)) return fail(c, EFM_ERR_INVALID_ARGUMENT, "temperature must be >= 0");
     const bool changed = std::memcmp(&c->sampling, s, sizeof(*s)) != 0;
     c->sampling = *s;
-    if (changed)     // sampling parameters are baked into the captured step
+    if (changed) {   // sampling parameters are baked into the captured step
         for (auto& kv : c->slots)
             if (kv.second.graph != nullptr) { cudaGraphExecDestroy(kv.second.graph); kv.second.graph = nullptr; }
+        drop_prefill_graphs(c);
+    }
+    return EFM_OK;
+}
+
+efm_status efm_b200_set_prefill_graph(efm_b200_ctx* c, int32_t enable) {
+    if (c == nullptr) return fail(c, EFM_ERR_INVALID_ARGUMENT, "null context");
+    c->prefill_graphs = enable != 0;
+    if (!c->prefill_graphs) drop_prefill_graphs(c);
+    return EFM_OK;
+}
+
+efm_status efm_b200_prefill_graph_stats(efm_b200_ctx* c, int32_t* captured, int64_t* replays) {
+    if (c == nullptr) return fail(c, EFM_ERR_INVALID_ARGUMENT, "null context");
+    int n = 0;
+    for (const auto& g : c->prefill_cache) n += g.exec != nullptr ? 1 : 0;
+    if (captured != nullptr) *captured = n;
+    if (replays != nullptr) *replays = c->prefill_graph_replays;
     return EFM_OK;
 }
 
@@ -573,6 +600,52 @@ efm_status efm_b200_prefill(efm_b200_ctx* c, int32_t slot, const int32_t* token_
         EFM_CK(c, cudaMemcpyAsync(c->state, &st, sizeof(st), cudaMemcpyHostToDevice, c->stream));
     }
     Launcher L = make_launcher(c);
+    // ---- one chunk, graphs on: replay (or capture) the launch sequence of this shape ------------------------------
+    if (c->prefill_graphs && n_tokens <= c->max_s) {
+        const int S = n_tokens;
+        EFM_CK(c, cudaMemcpyAsync(c->ids, token_ids, (size_t)S * 4, cudaMemcpyHostToDevice, c->stream));
+        if (pos_ids3 != nullptr) EFM_CK(c, cudaMemcpyAsync(c->pos3, pos_ids3, (size_t)3 * S * 4, cudaMemcpyHostToDevice, c->stream));
+        PrefillGraph key;
+        key.slot = slot; key.rows = S; key.kv_offset = kv_offset; key.n_embeds = n_embeds; key.embed_token_id = embed_token_id;
+        key.sample = sample != 0; key.attention_kind = c->prefill_attention_kind; key.embeds_buf = n_embeds > 0 ? c->custom_embeds : nullptr;
+        PrefillGraph* hit = nullptr;
+        for (auto& g : c->prefill_cache)
+            if (g.same_key(key)) { hit = &g; break; }
+        if (hit != nullptr && hit->exec == nullptr) {          // second sighting: capture
+            cudaGraph_t g = nullptr;
+            const int64_t before = c->launches;
+            EFM_CK(c, cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
+            qwen_prefill_chunk(*c, s, S, kv_offset, n_embeds, embed_token_id, sample != 0, L);
+            cudaError_t e = cudaStreamEndCapture(c->stream, &g);
+            hit->nodes = (int)(c->launches - before);
+            c->launches = before;
+            if (L.err != cudaSuccess) { if (g) cudaGraphDestroy(g); return cuda_fail(c, L.err, "prefill capture launch"); }
+            if (e != cudaSuccess) return cuda_fail(c, e, "cudaStreamEndCapture (prefill)");
+            e = cudaGraphInstantiate(&hit->exec, g, 0);
+            cudaGraphDestroy(g);
+            if (e != cudaSuccess) { hit->exec = nullptr; return cuda_fail(c, e, "cudaGraphInstantiate (prefill)"); }
+        }
+        if (hit != nullptr) {
+            hit->last_use = ++c->prefill_clock;
+            EFM_CK(c, cudaGraphLaunch(hit->exec, c->stream));
+            c->launches += hit->nodes;
+            ++c->prefill_graph_replays;
+            return EFM_OK;
+        }
+        // first sighting: remember the shape (evicting the least recently used one), run kernel by kernel below
+        if (c->prefill_cache.size() >= kMaxPrefillGraphs) {
+            size_t victim = 0;
+            for (size_t i = 1; i < c->prefill_cache.size(); ++i)
+                if (c->prefill_cache[i].last_use < c->prefill_cache[victim].last_use) victim = i;
+            if (c->prefill_cache[victim].exec != nullptr) cudaGraphExecDestroy(c->prefill_cache[victim].exec);
+            c->prefill_cache.erase(c->prefill_cache.begin() + (long)victim);
+        }
+        key.last_use = ++c->prefill_clock;
+        c->prefill_cache.push_back(key);
+        qwen_prefill_chunk(*c, s, S, kv_offset, n_embeds, embed_token_id, sample != 0, L);
+        if (L.err != cudaSuccess) return cuda_fail(c, L.err, "prefill launch");
+        return EFM_OK;
+    }
     for (int off = 0; off < n_tokens; off += c->max_s) {
         const int S = std::min(c->max_s, n_tokens - off);
         EFM_CK(c, cudaMemcpyAsync(c->ids, token_ids + off, (size_t)S * 4, cudaMemcpyHostToDevice, c->stream));
@@ -912,6 +985,7 @@ efm_status efm_b200_set_prefill_attention(efm_b200_ctx* c, int32_t kind) {
             if (e != cudaSuccess) { free_sage(c->sage); return cuda_fail(c, e, "INT8 attention scratch"); }
         }
     }
+    if (c->prefill_attention_kind != kind) drop_prefill_graphs(c);     // the INT8 scratch may have moved as well
     c->prefill_attention_kind = kind;
     return EFM_OK;
 }

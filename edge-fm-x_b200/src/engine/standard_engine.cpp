@@ -202,6 +202,9 @@ StandardEngine::StandardEngine(const EngineConfig& config) : config_(config) {
         s.top_k = config_.sampling_top_k();
         s.seed = config_.sampling_seed();
         check(efm_b200_set_sampling(ctx_, &s), "sampling configuration");
+        // short prompts are launch-bound: one captured graph per (request id, prompt length), as the reference does
+        // (standard_engine.cpp:568-770)
+        check(efm_b200_set_prefill_graph(ctx_, use_graph_ ? 1 : 0), "prefill graph selection");
         compact_ = CompactVocab(config_);
         const std::string pa = config_.prefill_attention();
         if (pa == "int8") check(efm_b200_set_prefill_attention(ctx_, 1), "prefill attention selection");

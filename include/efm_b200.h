@@ -164,6 +164,16 @@ EFM_API efm_status efm_b200_prefill(efm_b200_ctx* ctx, int32_t slot, const int32
                                     int32_t n_embeds, int32_t embed_token_id, int32_t embeds_mem,
                                     const int32_t* pos_ids3, int32_t sample);
 
+/* Prefill CUDA graphs for short prompts (try_run_prefill_cuda_graph, standard_engine.cpp:568-770: one graph per
+ * request id and sequence length, token ids refreshed before each replay).  When enabled, a prefill that fits one chunk
+ * (n_tokens <= max_prefill_tokens) is launched kernel by kernel the first time its shape (slot, n_tokens, kv_offset,
+ * injected-embedding count / id, sample flag, attention kind) is seen, captured the second time and replayed afterwards;
+ * ids, positions, embeddings and the state words are copied into stable device buffers before each launch.  At most 8
+ * shapes are kept (least recently used out).  Off by default; the engine turns it on with runtime.use_cuda_graph. */
+EFM_API efm_status efm_b200_set_prefill_graph(efm_b200_ctx* ctx, int32_t enable);
+/* Graphs currently held and replays so far (either pointer may be NULL). */
+EFM_API efm_status efm_b200_prefill_graph_stats(efm_b200_ctx* ctx, int32_t* captured, int64_t* replays);
+
 /* Which attention kernel efm_b200_prefill uses: 0 = bf16 flash attention (default), 1 = the INT8 scheme of
  * efm_b200_op_sage_prefill_attention.  Allocates the INT8 scratch for the largest KV slot allocated so far;
  * call it after efm_b200_alloc_kv_slot.  Decode is unaffected. */

@@ -66,6 +66,8 @@ SIGNATURES = {
     "efm_b200_kv_layer_ptr": (I32, [P, I32, I32, C.POINTER(P), C.POINTER(I32)]),
     "efm_b200_set_sampling": (I32, [P, C.POINTER(Sampling)]),
     "efm_b200_prefill": (I32, [P, I32, C.POINTER(I32), I32, I32, P, I32, I32, I32, C.POINTER(I32), I32]),
+    "efm_b200_set_prefill_graph": (I32, [P, I32]),
+    "efm_b200_prefill_graph_stats": (I32, [P, C.POINTER(I32), C.POINTER(C.c_int64)]),
     "efm_b200_decode_begin": (I32, [P, I32, I32, C.POINTER(I32), I32]),
     "efm_b200_set_token": (I32, [P, I32]),
     "efm_b200_decode_steps": (I32, [P, I32, I32]),
@@ -235,6 +237,14 @@ class Backend:
     def decode_begin(self, slot, kv_len, mrope_pos=None, step=1):
         mp = _i32_array(mrope_pos) if mrope_pos is not None else None
         self.check(self.L.efm_b200_decode_begin(self.ctx, slot, kv_len, mp, step), "decode_begin")
+
+    def set_prefill_graph(self, enable):
+        self.check(self.L.efm_b200_set_prefill_graph(self.ctx, 1 if enable else 0), "set_prefill_graph")
+
+    def prefill_graph_stats(self):
+        n, r = I32(), C.c_int64()
+        self.check(self.L.efm_b200_prefill_graph_stats(self.ctx, C.byref(n), C.byref(r)), "prefill_graph_stats")
+        return n.value, r.value
 
     def set_prefill_attention(self, kind):
         self.check(self.L.efm_b200_set_prefill_attention(self.ctx, int(kind)), "set_prefill_attention")

@@ -419,3 +419,51 @@ def test_edge_fm_stage_api_prefill_and_decode(tmp_path, built):
             eng.decode(1, {}) if False else edge_fm.EdgeFM.decode(eng, 7, {})
         assert edge_fm.ModelStage.Prefill != edge_fm.ModelStage.Decode
         del eng
+
+
+def test_prefill_cuda_graph_buckets():
+    """Prefill graphs: the first prefill of a shape runs kernel by kernel, the second is captured, later ones replay;
+    every form must return the tokens and logits of the plain launch sequence, for fresh token ids each time, with and
+    without a resident prefix, with injected embeddings, and after the sampling parameters change."""
+    cfg = synth.tiny_config(num_layers=3, hidden=256, q_heads=4, kv_heads=2, intermediate=512, vocab=1500,
+                            mrope_section=[8, 12, 12], model_type="qwen2_5_vl")
+    w = synth.make_weights(cfg, seed=8)
+    plain, graph = cabi.Backend(cfg), cabi.Backend(cfg)
+    for be in (plain, graph):
+        be.load_weights(w)
+        be.alloc_slot(0, 128)
+        be.alloc_slot(1, 128)
+        be.set_sampling(0.0, 1.0, 0)
+    graph.set_prefill_graph(True)
+    prefix = synth.make_token_ids(12, seed=1, vocab=cfg.vocab)
+    for be in (plain, graph):
+        be.prefill(1, prefix, kv_offset=0, pos3=[list(range(12))] * 3, sample=False)
+    emb = (torch.randn(4, cfg.hidden, generator=torch.Generator().manual_seed(3)) * 0.02).to(torch.bfloat16).cuda()
+    for trial in range(4):
+        ids = synth.make_token_ids(20, seed=10 + trial, vocab=cfg.vocab)
+        pos = [list(range(20))] * 3
+        a, la = cabi.generate(plain, 0, ids, 6, pos3=pos, collect_logits=True)
+        b, lb = cabi.generate(graph, 0, ids, 6, pos3=pos, collect_logits=True)
+        assert a == b and np.array_equal(la[0], lb[0]), trial
+        full = prefix + ids                                   # slot 1: resident prefix, prefill at kv_offset 12
+        pos = [list(range(32))] * 3
+        a, la = cabi.generate(plain, 1, full, 5, prefix_len=12, pos3=pos, collect_logits=True)
+        b, lb = cabi.generate(graph, 1, full, 5, prefix_len=12, pos3=pos, collect_logits=True)
+        assert a == b and np.array_equal(la[0], lb[0]), trial
+        vis = [cfg.vocab + i for i in range(4)] + ids[:10]     # injected embedding rows
+        pos = [list(range(14))] * 3
+        a, la = cabi.generate(plain, 0, vis, 4, embeds=emb, embed_token_id=cfg.vocab, pos3=pos, collect_logits=True)
+        b, lb = cabi.generate(graph, 0, vis, 4, embeds=emb, embed_token_id=cfg.vocab, pos3=pos, collect_logits=True)
+        assert a == b and np.array_equal(la[0], lb[0]), trial
+    captured, replays = graph.prefill_graph_stats()
+    assert captured == 3 and replays == 9                     # three shapes, each: eager, capture + launch, replay, replay
+    for be in (plain, graph):
+        be.set_sampling(0.8, 0.9, 5)                          # baked into the graphs: they must be dropped
+    ids = synth.make_token_ids(20, seed=40, vocab=cfg.vocab)
+    for _ in range(3):
+        a, _ = cabi.generate(plain, 0, ids, 6, pos3=[list(range(20))] * 3)
+        b, _ = cabi.generate(graph, 0, ids, 6, pos3=[list(range(20))] * 3)
+        assert a == b
+    assert graph.prefill_graph_stats()[0] == 1
+    plain.close()
+    graph.close()

@@ -16,6 +16,28 @@
 
 namespace efm {
 
+// One linear of the decode pass in group-wise INT4 (operators/gemv_w4.cuh): kernel-layout weights once `ready`;
+// until finalize the checkpoint tensors as they arrived (up to three stacked sources: q | k | v, gate | up).
+struct W4Linear {
+    uint8_t* q = nullptr;                 // [n_items][K]
+    void* s = nullptr;                    // [n_items][K / 128] half2
+    int n_items = 0, K = 0;
+    bool ready = false;
+    void* src_q[3] = {nullptr, nullptr, nullptr};
+    void* src_s[3] = {nullptr, nullptr, nullptr};
+    int src_s_bf16[3] = {0, 0, 0};
+    bool complete(int n_src) const {
+        for (int i = 0; i < n_src; ++i)
+            if (src_q[i] == nullptr || src_s[i] == nullptr) return false;
+        return true;
+    }
+    bool any() const {
+        for (int i = 0; i < 3; ++i)
+            if (src_q[i] != nullptr || src_s[i] != nullptr) return true;
+        return false;
+    }
+};
+
 struct LayerWeights {
     __nv_bfloat16* in_norm = nullptr;     // [H]
     __nv_bfloat16* post_norm = nullptr;   // [H]
@@ -25,6 +47,7 @@ struct LayerWeights {
     __nv_bfloat16* gate_up = nullptr;     // [2I, H] blocks of 64 gate rows then 64 up rows
     __nv_bfloat16* down = nullptr;        // [H, I]
     uint32_t seen = 0;                    // bit per HF tensor received
+    W4Linear w4_qkv, w4_o, w4_gate_up, w4_down;      // decode-only INT4 copies (efm_b200_set_decode_weight)
 };
 
 struct KvSlot {
@@ -34,7 +57,6 @@ struct KvSlot {
     cudaGraphExec_t graph = nullptr;      // decode step captured against this slot's pointers
     int graph_nodes = 0;
     int n_splits = 1, chunk_cap = 1, attn_cluster = 0;
-    void* mega_layers = nullptr;          // device array of per-layer pointers for the persistent decode kernel
 };
 
 // Scratch of the INT8 prefill attention (operators/sage_attention.cuh).
@@ -99,9 +121,6 @@ struct efm_b200_ctx {
     std::string error;
     bool finalized = false;
     bool pdl = true;
-    bool mega = true;                     // decode step as one persistent cooperative kernel
-    unsigned int* mega_barrier = nullptr; // [2] grid-barrier counters + [1] abort flag
-    unsigned long long* mega_timing = nullptr;   // [5L + 2] phase stamps (debug breakdown)
 
     // weights
     __nv_bfloat16* embed = nullptr;       // [V, H]
@@ -109,6 +128,8 @@ struct efm_b200_ctx {
     __nv_bfloat16* final_norm = nullptr;
     bool seen_embed = false, seen_lm_head = false, seen_final_norm = false;
     std::vector<efm::LayerWeights> layers;
+    efm::W4Linear w4_lm_head;
+    bool decode_w4 = false;               // every linear of the decode step has an INT4 copy
     float* inv_freq = nullptr;            // [D/2]
 
     // activations (prefill rows x width) and decode vectors
@@ -125,9 +146,10 @@ struct efm_b200_ctx {
     size_t custom_embeds_cap = 0;
     float* resid_d = nullptr;             // decode residual stream [H], fp32
     float* resid_d2 = nullptr;            // second copy (tensor parallel: the add-and-norm prologue ping-pongs)
-    __nv_bfloat16* q_d = nullptr;         // [q*D]
-    __nv_bfloat16* attn_d = nullptr;      // [q*D]
-    __nv_bfloat16* act_d = nullptr;       // [I]
+    // decode activations stay fp32 from kernel to kernel: a decode step rounds only the K / V rows it appends
+    float* q_d = nullptr;                 // [q*D] rotated q
+    float* attn_d = nullptr;              // [q*D] attention output
+    float* act_d = nullptr;               // [I] silu(gate) * up
     float* logits = nullptr;              // [V]
     float* part_val = nullptr;            // [max gemv grid]
     int* part_idx = nullptr;

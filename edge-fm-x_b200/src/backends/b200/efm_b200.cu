@@ -179,10 +179,6 @@ efm_status efm_b200_create(const efm_model_desc* desc, int32_t device_id, int32_
     c->tp_rank = tp_rank;
     c->tp_size = tp_size;
     c->pdl = std::getenv("EFM_B200_NO_PDL") == nullptr;
-    {   // decode step form: "1" = one persistent cooperative kernel, "0" = one launch per phase
-        const char* m = std::getenv("EFM_B200_MEGA");
-        c->mega = m != nullptr && m[0] == '1';
-    }
     auto bail = [&](cudaError_t e, const char* what) {
         efm_status s = cuda_fail(nullptr, e, what);
         efm_b200_destroy(c);
@@ -200,7 +196,6 @@ efm_status efm_b200_create(const efm_model_desc* desc, int32_t device_id, int32_
     if (d.tied_lm_head) c->lm_head = c->embed + (size_t)c->vocab_off * H;      // this rank's rows of the shared table
     else EFM_TRY(dev_alloc(c, &c->lm_head, (size_t)c->vocab_l * H, false));
     if (tp_size > 1) {
-        c->mega = false;      // the persistent decode kernel has no collective phase
         EFM_TRY(dev_alloc(c, &c->ybuf, S * H));
         EFM_TRY(dev_alloc(c, &c->ysum, S * H));
         EFM_TRY(dev_alloc(c, &c->logits_l, (size_t)c->vocab_l));
@@ -259,14 +254,15 @@ efm_status efm_b200_create(const efm_model_desc* desc, int32_t device_id, int32_
     EFM_TRY(dev_alloc(c, &c->attn_part_o, (size_t)dl.q_heads * 64 * D));
     EFM_TRY(dev_alloc(c, &c->attn_part_ml, (size_t)dl.q_heads * 64 * 2));
     EFM_TRY(dev_alloc(c, &c->attn_counters, (size_t)dl.kv_heads));
-    EFM_TRY(dev_alloc(c, &c->mega_barrier, 4));
-    EFM_TRY(dev_alloc(c, &c->mega_timing, (size_t)5 * d.num_layers + 8));
-    {
+    {   // the longest GEMV input row must fit the kernel's shared memory as fp32
         int optin = 0;
         EFM_TRY(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device_id));
-        const size_t need = mega_gemv_smem_bytes((int)H, (int)QD, (int)I) + decode_attention_smem_bytes((int)D, 0);
-        if (need > (size_t)optin) c->mega = false;       // does not fit: phase-per-launch form
-        else EFM_TRY(configure_decode_mega((int)need));
+        const size_t need = gemv_w4_smem_bytes((int)std::max(H, std::max(QD, I)));
+        if (need + 2048 > (size_t)optin) {
+            efm_status s = fail(nullptr, EFM_ERR_UNSUPPORTED, "hidden / intermediate size exceeds what the decode GEMV stages in shared memory");
+            efm_b200_destroy(c);
+            return s;
+        }
     }
     c->gemm_ws_floats = (size_t)c->num_sms * 128 * 256;      // splits x tiles never exceeds the SM count
     EFM_TRY(dev_alloc(c, &c->gemm_ws, c->gemm_ws_floats, false));
@@ -481,6 +477,105 @@ efm_status efm_b200_set_weight(efm_b200_ctx* c, const char* hf_name, const void*
     return EFM_OK;
 }
 
+efm_status efm_b200_set_decode_weight(efm_b200_ctx* c, const char* hf_name, const void* data, const int64_t* shape, int32_t ndim,
+                                      int32_t dtype, int32_t mem_kind) {
+    if (c == nullptr || hf_name == nullptr || data == nullptr || shape == nullptr)
+        return fail(c, EFM_ERR_INVALID_ARGUMENT, "null argument");
+    if (c->finalized) return fail(c, EFM_ERR_STATE, "weights are already finalized");
+    if (c->tp_size > 1) return fail(c, EFM_ERR_UNSUPPORTED, "INT4 decode weights are not sharded: tensor-parallel contexts decode in bf16");
+    EFM_CK(c, cudaSetDevice(c->device));
+    const efm_model_desc& d = c->d;
+    const int64_t H = d.hidden, D = d.head_dim, I = d.intermediate, V = d.vocab, QD = d.q_heads * D, KVD = d.kv_heads * D;
+    std::string name(hf_name);
+    bool is_q;
+    const std::string qs = ".qweight", ss = ".scaling_factors";
+    if (name.size() > qs.size() && name.compare(name.size() - qs.size(), qs.size(), qs) == 0) { is_q = true; name.resize(name.size() - qs.size()); }
+    else if (name.size() > ss.size() && name.compare(name.size() - ss.size(), ss.size(), ss) == 0) { is_q = false; name.resize(name.size() - ss.size()); }
+    else return EFM_OK;                                   // bf16 tensors of a decode checkpoint: the prefill copy serves
+    W4Linear* lin = nullptr;
+    int src = 0;
+    int64_t rows = 0, K = 0;
+    if (name == "lm_head") { lin = &c->w4_lm_head; rows = V; K = H; }
+    else if (name.rfind("model.layers.", 0) == 0) {
+        const size_t dot = name.find('.', 13);
+        if (dot == std::string::npos) return EFM_OK;
+        const int l = std::atoi(name.substr(13, dot - 13).c_str());
+        if (l < 0 || l >= d.num_layers) return EFM_OK;
+        const std::string rest = name.substr(dot + 1);
+        LayerWeights& w = c->layers[l];
+        if (rest == "self_attn.q_proj") { lin = &w.w4_qkv; src = 0; rows = QD; K = H; }
+        else if (rest == "self_attn.k_proj") { lin = &w.w4_qkv; src = 1; rows = KVD; K = H; }
+        else if (rest == "self_attn.v_proj") { lin = &w.w4_qkv; src = 2; rows = KVD; K = H; }
+        else if (rest == "self_attn.o_proj") { lin = &w.w4_o; rows = H; K = QD; }
+        else if (rest == "mlp.gate_proj") { lin = &w.w4_gate_up; src = 0; rows = I; K = H; }
+        else if (rest == "mlp.up_proj") { lin = &w.w4_gate_up; src = 1; rows = I; K = H; }
+        else if (rest == "mlp.down_proj") { lin = &w.w4_down; rows = H; K = I; }
+        else return EFM_OK;
+    } else {
+        return EFM_OK;
+    }
+    if (K % kW4Group != 0 || rows % 2 != 0)
+        return fail(c, EFM_ERR_UNSUPPORTED, "INT4 linear needs in_features % 128 == 0 and even out_features: " + std::string(hf_name));
+    size_t bytes;
+    if (is_q) {
+        if (dtype != EFM_I8 && dtype != EFM_U8) return fail(c, EFM_ERR_UNSUPPORTED, "qweight must be int8 (two 4-bit values per byte): " + std::string(hf_name));
+        if (!shape_is(shape, ndim, rows / 2, K)) return fail(c, EFM_ERR_INVALID_ARGUMENT, "unexpected shape for " + std::string(hf_name) + " (want [out_features / 2, in_features])");
+        bytes = (size_t)(rows / 2) * K;
+    } else {
+        if (dtype != EFM_F16 && dtype != EFM_BF16) return fail(c, EFM_ERR_UNSUPPORTED, "scaling_factors must be fp16 or bf16: " + std::string(hf_name));
+        if (!shape_is(shape, ndim, K / kW4Group, rows)) return fail(c, EFM_ERR_INVALID_ARGUMENT, "unexpected shape for " + std::string(hf_name) + " (want [in_features / 128, out_features])");
+        bytes = (size_t)(K / kW4Group) * rows * 2;
+        lin->src_s_bf16[src] = dtype == EFM_BF16;
+    }
+    void** slot = is_q ? &lin->src_q[src] : &lin->src_s[src];
+    if (*slot == nullptr) {
+        cudaError_t e = cudaMalloc(slot, bytes);          // released again by finalize_weights
+        if (e != cudaSuccess) { *slot = nullptr; return cuda_fail(c, e, "staging an INT4 tensor"); }
+    }
+    EFM_CK(c, cudaMemcpyAsync(*slot, data, bytes, mem_kind == EFM_MEM_DEVICE ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, c->stream));
+    EFM_CK(c, cudaStreamSynchronize(c->stream));
+    return EFM_OK;
+}
+
+namespace {
+// kind: 0 neighbours, 1 rotary partners, 2 gate / up
+efm_status finish_w4_linear(efm_b200_ctx* c, W4Linear& lin, int n_src, const int rows[3], int K, int kind, const char* what) {
+    if (!lin.any()) return EFM_OK;
+    if (!lin.complete(n_src)) return fail(c, EFM_ERR_STATE, std::string("INT4 decode weights incomplete (qweight and scaling_factors of every part): ") + what);
+    int total_rows = 0;
+    for (int i = 0; i < n_src; ++i) total_rows += rows[i];
+    lin.n_items = total_rows / 2;
+    lin.K = K;
+    EFM_CK(c, dev_alloc(c, &lin.q, (size_t)lin.n_items * K, false));
+    __half2* s = nullptr;
+    EFM_CK(c, dev_alloc(c, &s, (size_t)lin.n_items * (K / kW4Group), false));
+    lin.s = s;
+    W4RepackParams p{};
+    int row0 = 0;
+    for (int i = 0; i < n_src; ++i) {
+        p.q[i] = static_cast<const uint8_t*>(lin.src_q[i]);
+        p.s[i] = lin.src_s[i];
+        p.row0[i] = row0;
+        p.rows[i] = rows[i];
+        p.s_is_bf16[i] = lin.src_s_bf16[i];
+        row0 += rows[i];
+    }
+    p.n_src = n_src; p.K = K; p.n_items = lin.n_items; p.kind = kind; p.head_dim = c->d.head_dim; p.half = rows[0];
+    p.out_q = lin.q; p.out_s = s;
+    Launcher L = make_launcher(c);
+    L.counter = nullptr;
+    launch_w4_repack(L, p);
+    if (L.err != cudaSuccess) return cuda_fail(c, L.err, "INT4 repack launch");
+    EFM_CK(c, cudaStreamSynchronize(c->stream));
+    for (int i = 0; i < 3; ++i) {
+        if (lin.src_q[i] != nullptr) { cudaFree(lin.src_q[i]); lin.src_q[i] = nullptr; }
+        if (lin.src_s[i] != nullptr) { cudaFree(lin.src_s[i]); lin.src_s[i] = nullptr; }
+    }
+    lin.ready = true;
+    return EFM_OK;
+}
+}  // namespace
+
 efm_status efm_b200_finalize_weights(efm_b200_ctx* c) {
     if (c == nullptr) return fail(c, EFM_ERR_INVALID_ARGUMENT, "null context");
     if (!c->seen_embed) return fail(c, EFM_ERR_STATE, "missing model.embed_tokens.weight");
@@ -490,6 +585,29 @@ efm_status efm_b200_finalize_weights(efm_b200_ctx* c) {
         if ((c->layers[l].seen & kRequired) != kRequired)
             return fail(c, EFM_ERR_STATE, "missing weights in layer " + std::to_string(l));
     EFM_CK(c, cudaStreamSynchronize(c->stream));
+    {   // INT4 copies of the decode linears, when a decode checkpoint supplied them: all layers or none
+        const efm_model_desc& d = c->d;
+        const int D = d.head_dim, QD = d.q_heads * D, KVD = d.kv_heads * D;
+        bool all = true, any = c->w4_lm_head.any();
+        for (auto& w : c->layers) any = any || w.w4_qkv.any() || w.w4_o.any() || w.w4_gate_up.any() || w.w4_down.any();
+        if (any) {
+            for (int l = 0; l < d.num_layers; ++l) {
+                LayerWeights& w = c->layers[l];
+                const int r_qkv[3] = {QD, KVD, KVD}, r_o[3] = {d.hidden, 0, 0}, r_gu[3] = {d.intermediate, d.intermediate, 0};
+                efm_status st = finish_w4_linear(c, w.w4_qkv, 3, r_qkv, d.hidden, 1, "q/k/v_proj");
+                if (st == EFM_OK) st = finish_w4_linear(c, w.w4_o, 1, r_o, QD, 0, "o_proj");
+                if (st == EFM_OK) st = finish_w4_linear(c, w.w4_gate_up, 2, r_gu, d.hidden, 2, "gate/up_proj");
+                if (st == EFM_OK) st = finish_w4_linear(c, w.w4_down, 1, r_o, d.intermediate, 0, "down_proj");
+                if (st != EFM_OK) return st;
+                all = all && w.w4_qkv.ready && w.w4_o.ready && w.w4_gate_up.ready && w.w4_down.ready;
+            }
+            const int r_lm[3] = {d.vocab, 0, 0};
+            const efm_status st = finish_w4_linear(c, c->w4_lm_head, 1, r_lm, d.hidden, 0, "lm_head");
+            if (st != EFM_OK) return st;
+            if (!all) return fail(c, EFM_ERR_STATE, "INT4 decode weights must cover q/k/v/o/gate/up/down_proj of every layer (lm_head is optional)");
+            c->decode_w4 = true;
+        }
+    }
     c->finalized = true;
     return EFM_OK;
 }
@@ -512,18 +630,6 @@ efm_status efm_b200_alloc_kv_slot(efm_b200_ctx* c, int32_t slot, int32_t max_tok
     s.n_splits = plan.n_splits;
     s.chunk_cap = plan.chunk_cap;
     s.attn_cluster = plan.cluster;
-    {
-        std::vector<MegaLayer> ml(c->d.num_layers);
-        for (int l = 0; l < c->d.num_layers; ++l) {
-            const LayerWeights& w = c->layers[l];
-            ml[l] = MegaLayer{w.in_norm, w.post_norm, w.qkv, w.qkv_bias, w.o, w.gate_up, w.down, s.k[l], s.v[l]};
-        }
-        MegaLayer* dev = nullptr;
-        EFM_CK(c, dev_alloc(c, &dev, ml.size(), false));
-        EFM_CK(c, cudaMemcpyAsync(dev, ml.data(), ml.size() * sizeof(MegaLayer), cudaMemcpyHostToDevice, c->stream));
-        EFM_CK(c, cudaStreamSynchronize(c->stream));
-        s.mega_layers = dev;
-    }
     EFM_CK(c, cudaStreamSynchronize(c->stream));
     c->slots[slot] = s;
     return EFM_OK;
@@ -593,29 +699,60 @@ efm_status efm_b200_prefill(efm_b200_ctx* c, int32_t slot, const int32_t* token_
     } else {
         n_embeds = 0;
     }
-    if (sample) {
+    Launcher L = make_launcher(c);
+    // A sampled prefill runs its LAST token as a decode step (same arithmetic, K / V rows and logits as if it had been
+    // a row of the GEMMs, but with the decode kernels' fp32 activations): every logit vector the caller sees then
+    // comes from one set of kernels, and the first sample is as accurate as the later ones.  The rows before it go
+    // through the tensor-core GEMMs.  Not when the last token is an injected embedding row or outside the vocabulary.
+    const int32_t last_id = token_ids[n_tokens - 1];
+    const bool tail = sample != 0 && last_id >= 0 && last_id < c->d.vocab &&
+                      !(n_embeds > 0 && last_id >= embed_token_id && last_id < embed_token_id + n_embeds);
+    const int n_gemm = tail ? n_tokens - 1 : n_tokens;
+    if (sample != 0 && !tail) {
         DecodeState st{};
         st.token = -1;
         st.kv_len = (uint32_t)(kv_offset + n_tokens);
         EFM_CK(c, cudaMemcpyAsync(c->state, &st, sizeof(st), cudaMemcpyHostToDevice, c->stream));
     }
-    Launcher L = make_launcher(c);
+    if (tail) {
+        DecodeState st{};
+        st.token = last_id;
+        st.kv_len = (uint32_t)(kv_offset + n_tokens);
+        for (int r = 0; r < 3; ++r) st.pos[r] = pos_ids3 != nullptr ? pos_ids3[(size_t)r * n_tokens + n_tokens - 1] : 0;
+        EFM_CK(c, cudaMemcpyAsync(c->state, &st, sizeof(st), cudaMemcpyHostToDevice, c->stream));
+    }
+    auto run_tail = [&](Launcher& LL) {
+        if (!tail) return;
+        const bool w4 = c->decode_w4;
+        c->decode_w4 = false;            // the first token belongs to the prefill pass: bf16 weights even when decode runs on INT4
+        qwen_decode_step(*c, s, LL);
+        c->decode_w4 = w4;
+    };
     // ---- one chunk, graphs on: replay (or capture) the launch sequence of this shape ------------------------------
-    if (c->prefill_graphs && n_tokens <= c->max_s) {
-        const int S = n_tokens;
-        EFM_CK(c, cudaMemcpyAsync(c->ids, token_ids, (size_t)S * 4, cudaMemcpyHostToDevice, c->stream));
-        if (pos_ids3 != nullptr) EFM_CK(c, cudaMemcpyAsync(c->pos3, pos_ids3, (size_t)3 * S * 4, cudaMemcpyHostToDevice, c->stream));
+    if (c->prefill_graphs && n_gemm <= c->max_s) {
+        const int S = n_gemm;
+        if (S > 0) {
+            EFM_CK(c, cudaMemcpyAsync(c->ids, token_ids, (size_t)S * 4, cudaMemcpyHostToDevice, c->stream));
+            if (pos_ids3 != nullptr)
+                for (int r = 0; r < 3; ++r)
+                    EFM_CK(c, cudaMemcpyAsync(c->pos3 + (size_t)r * S, pos_ids3 + (size_t)r * n_tokens, (size_t)S * 4, cudaMemcpyHostToDevice, c->stream));
+        }
         PrefillGraph key;
-        key.slot = slot; key.rows = S; key.kv_offset = kv_offset; key.n_embeds = n_embeds; key.embed_token_id = embed_token_id;
-        key.sample = sample != 0; key.attention_kind = c->prefill_attention_kind; key.embeds_buf = n_embeds > 0 ? c->custom_embeds : nullptr;
+        key.slot = slot; key.rows = n_tokens; key.kv_offset = kv_offset; key.n_embeds = n_embeds; key.embed_token_id = embed_token_id;
+        key.sample = (sample != 0 ? 1 : 0) + (tail ? 2 : 0); key.attention_kind = c->prefill_attention_kind;
+        key.embeds_buf = n_embeds > 0 ? c->custom_embeds : nullptr;
         PrefillGraph* hit = nullptr;
         for (auto& g : c->prefill_cache)
             if (g.same_key(key)) { hit = &g; break; }
+        auto launch_all = [&]() {
+            if (S > 0) qwen_prefill_chunk(*c, s, S, kv_offset, n_embeds, embed_token_id, sample != 0 && !tail, L);
+            run_tail(L);
+        };
         if (hit != nullptr && hit->exec == nullptr) {          // second sighting: capture
             cudaGraph_t g = nullptr;
             const int64_t before = c->launches;
             EFM_CK(c, cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
-            qwen_prefill_chunk(*c, s, S, kv_offset, n_embeds, embed_token_id, sample != 0, L);
+            launch_all();
             cudaError_t e = cudaStreamEndCapture(c->stream, &g);
             hit->nodes = (int)(c->launches - before);
             c->launches = before;
@@ -632,7 +769,7 @@ efm_status efm_b200_prefill(efm_b200_ctx* c, int32_t slot, const int32_t* token_
             ++c->prefill_graph_replays;
             return EFM_OK;
         }
-        // first sighting: remember the shape (evicting the least recently used one), run kernel by kernel below
+        // first sighting: remember the shape (evicting the least recently used one), run kernel by kernel
         if (c->prefill_cache.size() >= kMaxPrefillGraphs) {
             size_t victim = 0;
             for (size_t i = 1; i < c->prefill_cache.size(); ++i)
@@ -642,21 +779,23 @@ efm_status efm_b200_prefill(efm_b200_ctx* c, int32_t slot, const int32_t* token_
         }
         key.last_use = ++c->prefill_clock;
         c->prefill_cache.push_back(key);
-        qwen_prefill_chunk(*c, s, S, kv_offset, n_embeds, embed_token_id, sample != 0, L);
+        launch_all();
         if (L.err != cudaSuccess) return cuda_fail(c, L.err, "prefill launch");
         return EFM_OK;
     }
-    for (int off = 0; off < n_tokens; off += c->max_s) {
-        const int S = std::min(c->max_s, n_tokens - off);
+    for (int off = 0; off < n_gemm; off += c->max_s) {
+        const int S = std::min(c->max_s, n_gemm - off);
         EFM_CK(c, cudaMemcpyAsync(c->ids, token_ids + off, (size_t)S * 4, cudaMemcpyHostToDevice, c->stream));
         if (pos_ids3 != nullptr)
             for (int r = 0; r < 3; ++r)
                 EFM_CK(c, cudaMemcpyAsync(c->pos3 + (size_t)r * S, pos_ids3 + (size_t)r * n_tokens + off, (size_t)S * 4,
                                           cudaMemcpyHostToDevice, c->stream));
-        const bool last = off + S >= n_tokens;
-        qwen_prefill_chunk(*c, s, S, kv_offset + off, n_embeds, embed_token_id, last && sample != 0, L);
+        const bool last = off + S >= n_gemm;
+        qwen_prefill_chunk(*c, s, S, kv_offset + off, n_embeds, embed_token_id, last && sample != 0 && !tail, L);
         if (L.err != cudaSuccess) return cuda_fail(c, L.err, "prefill launch");
     }
+    run_tail(L);
+    if (L.err != cudaSuccess) return cuda_fail(c, L.err, "prefill launch (last token)");
     return EFM_OK;
 }
 
@@ -674,7 +813,6 @@ efm_status efm_b200_decode_begin(efm_b200_ctx* c, int32_t slot, int32_t kv_len, 
     tail.error = 0;
     static_assert(offsetof(DecodeState, kv_len) == 4 && sizeof(tail) == 24, "DecodeState layout");
     EFM_CK(c, cudaMemcpyAsync(reinterpret_cast<char*>(c->state) + 4, &tail, sizeof(tail), cudaMemcpyHostToDevice, c->stream));
-    EFM_CK(c, cudaMemsetAsync(c->mega_barrier, 0, 4 * sizeof(unsigned int), c->stream));   // barrier counters, abort flag
     if (c->error_host != nullptr) *reinterpret_cast<volatile int*>(c->error_host) = 0;
     c->bound_slot = slot;
     return EFM_OK;
@@ -798,29 +936,6 @@ efm_status efm_b200_decode_breakdown(efm_b200_ctx* c, int32_t n_steps, float* ms
     EFM_CK(c, cudaSetDevice(c->device));
     for (int i = 0; i < 7; ++i) ms_out[i] = 0.f;
     const int per_step = 5 * c->d.num_layers + 2;
-    if (c->mega) {
-        // persistent kernel: block 0 stamps %globaltimer at every phase boundary
-        std::vector<unsigned long long> t((size_t)per_step + 1);
-        for (int step = 0; step < n_steps; ++step) {
-            Launcher L = make_launcher(c);
-            L.phase_timing = true;
-            cudaEvent_t e0 = nullptr, e1 = nullptr, e2 = nullptr;
-            cudaEventCreate(&e0); cudaEventCreate(&e1); cudaEventCreate(&e2);
-            qwen_decode_step(*c, s, L);
-            cudaError_t e = L.err != cudaSuccess ? L.err : cudaStreamSynchronize(c->stream);
-            if (e == cudaSuccess)
-                e = cudaMemcpy(t.data(), c->mega_timing, (size_t)per_step * sizeof(unsigned long long), cudaMemcpyDeviceToHost);
-            cudaEventDestroy(e0); cudaEventDestroy(e1); cudaEventDestroy(e2);
-            if (e != cudaSuccess) return cuda_fail(c, e, "decode breakdown");
-            // stamps: 0 = start, then one per barrier (5 per layer), then the end of lm_head
-            for (int i = 0; i + 1 < per_step; ++i) {
-                const float ms = (float)((double)(t[i + 1] - t[i]) * 1e-6);
-                const int kind = i < 5 * c->d.num_layers ? i % 5 : 5;
-                ms_out[kind] += ms;
-            }
-        }
-        return EFM_OK;
-    }
     for (int step = 0; step < n_steps; ++step) {
         std::vector<cudaEvent_t> ev;
         Launcher L = make_launcher(c);
@@ -854,8 +969,14 @@ efm_status efm_b200_decode_step_bytes(efm_b200_ctx* c, int32_t kv_len, int64_t* 
     const int64_t H = d.hidden, D = d.head_dim, q = d.q_heads, kv = d.kv_heads, I = d.intermediate, V = d.vocab, L = d.num_layers;
     // what THIS rank streams: its head shard, its o_proj columns, its MLP columns, its lm_head rows
     const int64_t per_layer = (q + 2 * kv) * D * H + (q + 2 * kv) * D + (int64_t)c->o_k * H + 3 * I * H + 2 * H;
-    const int64_t w = 2 * (L * per_layer + H + (int64_t)c->vocab_l * H) + 2 * H;      // + final norm, lm_head rows, one embedding row
-    (void)V;
+    int64_t w = 2 * (L * per_layer + H + (int64_t)c->vocab_l * H) + 2 * H;      // + final norm, lm_head rows, one embedding row
+    if (c->decode_w4) {
+        // INT4 linears: half a byte per weight + one fp16 scale per 128 weights; biases, norms, embedding row in bf16
+        const int64_t lin = (q + 2 * kv) * D * H + q * D * H + 3 * I * H;
+        const int64_t lm = V * H;
+        const auto w4 = [](int64_t n) { return n / 2 + n / kW4Group * 2; };
+        w = L * (w4(lin) + 2 * ((q + 2 * kv) * D + 2 * H)) + 2 * H + (c->w4_lm_head.ready ? w4(lm) : 2 * lm) + 2 * H;
+    }
     *bytes = w + L * 2 * (int64_t)kv_len * kv * D * 2;
     return EFM_OK;
 }

@@ -171,6 +171,26 @@ StandardEngine::StandardEngine(const EngineConfig& config) : config_(config) {
                 if (st != EFM_OK) throw ModelNotLoadedError(std::string("loading ") + name + ": " + efm_b200_last_error(ctx_));
             }
         }
+        // Two checkpoints (reference: engine_factory.cpp:64-72): when decode_model_path names another directory, its
+        // group-wise INT4 tensors (<linear>.qweight / .scaling_factors) become the decode pass's weights; prefill keeps
+        // the bf16 ones.  Tensors of other kinds in that directory are ignored.
+        const std::string decode_path = config_.decode_model_path();
+        if (!decode_path.empty() && decode_path != config_.prefill_model_path()) {
+            const std::vector<std::string> dfiles = collect_safetensors_files(decode_path);
+            if (dfiles.empty()) throw ConfigurationError("No model.safetensors or model-*-of-*.safetensors found in decode path");
+            for (const std::string& f : dfiles) {
+                SafeTensorsFile dm(f);
+                for (const SafeTensorEntry& e : dm.entries()) {
+                    std::string name = e.name;
+                    if (vlm && !map_vlm_weight_name(e.name, &name)) continue;
+                    const int32_t code = dtype_code(e.dtype);
+                    if (code < 0) continue;
+                    st = efm_b200_set_decode_weight(ctx_, name.c_str(), e.data, e.shape.data(), (int32_t)e.shape.size(), code, EFM_MEM_HOST);
+                    if (st == EFM_ERR_UNSUPPORTED) throw ConfigurationError(std::string("decode checkpoint, ") + name + ": " + efm_b200_last_error(ctx_));
+                    if (st != EFM_OK) throw ModelNotLoadedError(std::string("loading decode weight ") + name + ": " + efm_b200_last_error(ctx_));
+                }
+            }
+        }
         st = efm_b200_finalize_weights(ctx_);
         if (st != EFM_OK) throw ModelNotLoadedError(std::string("checkpoint incomplete: ") + efm_b200_last_error(ctx_));
         maps.clear();

@@ -10,8 +10,8 @@
 #include <vector>
 
 #include "../operators/decode_attention.cuh"
-#include "../operators/decode_mega.cuh"
 #include "../operators/gemv.cuh"
+#include "../operators/gemv_w4.cuh"
 
 namespace efm {
 
@@ -19,7 +19,6 @@ struct Launcher {
     cudaStream_t stream = nullptr;
     bool pdl = true;                 // programmatic stream serialization between consecutive kernels
     bool pdl_rows = false;           // keep `pdl` for the row / attention kernels of the prefill family too (they open with the wait)
-    bool cooperative = false;        // next launch only: all blocks co-resident (they wait on each other)
     int cluster_x = 0;               // next launch only: thread-block cluster of this many blocks along x
     float* gemm_ws = nullptr;        // split-K workspace of the owning context (nullptr: GEMMs never split)
     size_t gemm_ws_floats = 0;
@@ -27,7 +26,6 @@ struct Launcher {
     int64_t* counter = nullptr;
     cudaError_t err = cudaSuccess;   // first failure sticks
     std::vector<cudaEvent_t>* trace = nullptr;   // when set: one event recorded after every launch
-    bool phase_timing = false;       // persistent decode kernel: stamp %globaltimer at every phase boundary
 
     template <typename... KArgs, typename... Args>
     void launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, Args&&... args) {
@@ -39,10 +37,7 @@ struct Launcher {
         cfg.stream = stream;
         cudaLaunchAttribute attr[2];
         int na = 0;
-        if (cooperative) {
-            attr[na].id = cudaLaunchAttributeCooperative;
-            attr[na++].val.cooperative = 1;
-        } else if (pdl) {
+        if (pdl) {
             attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
             attr[na++].val.programmaticStreamSerializationAllowed = 1;
         }
@@ -54,7 +49,6 @@ struct Launcher {
         }
         cfg.attrs = na > 0 ? attr : nullptr;
         cfg.numAttrs = na;
-        cooperative = false;
         cluster_x = 0;
         err = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
         if (counter != nullptr) ++*counter;
@@ -89,6 +83,28 @@ inline void launch_gemv(Launcher& L, const GemvParams& p, int num_sms) {
     L.launch(gemv_kernel<EPI>, dim3(num_sms), dim3(kGemvThreads), gemv_smem_bytes(p.K), p, ks);
 }
 
+// INT4 form: the K split balances (row pairs per group) x (chunk slots per lane), as above with 16-byte chunks of
+// 16 columns x 2 rows.
+inline int plan_gemv_w4_ksplit(int n_items, int K, int n_blocks) {
+    const int nch = K / 16;
+    int best = 1;
+    long best_cost = -1;
+    for (int ks = 1; ks <= kGemvWarps; ks *= 2) {
+        const long slots = (long)n_blocks * (kGemvWarps / ks);
+        const long waves = (n_items + slots - 1) / slots;
+        const long cpl = (nch + 32 * ks - 1) / (32 * ks);
+        const long cost = waves * cpl * 8 + ks;
+        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = ks; }
+    }
+    return best;
+}
+
+template <Epi EPI>
+inline void launch_gemv_w4(Launcher& L, const GemvW4Params& p, int num_sms) {
+    const int ks = plan_gemv_w4_ksplit(p.g.n_items, p.g.K, num_sms);
+    L.launch(gemv_w4_kernel<EPI>, dim3(num_sms), dim3(kGemvThreads), gemv_w4_smem_bytes(p.g.K), p, ks);
+}
+
 inline cudaError_t configure_gemv(int max_smem_optin) {
     cudaError_t e = cudaFuncSetAttribute(gemv_kernel<Epi::Plain>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem_optin);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_kernel<Epi::Residual>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem_optin);
@@ -96,13 +112,12 @@ inline cudaError_t configure_gemv(int max_smem_optin) {
     if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_kernel<Epi::SwiGlu>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem_optin);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_kernel<Epi::Logits>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem_optin);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_kernel<Epi::Peers>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem_optin);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_w4_kernel<Epi::Plain>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem_optin);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_w4_kernel<Epi::Residual>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem_optin);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_w4_kernel<Epi::QkvRope>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem_optin);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_w4_kernel<Epi::SwiGlu>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem_optin);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_w4_kernel<Epi::Logits>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem_optin);
     return e;
-}
-
-inline cudaError_t configure_decode_mega(int max_smem_optin) {
-    cudaError_t e = cudaFuncSetAttribute(decode_mega_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem_optin);
-    if (e != cudaSuccess) return e;
-    return cudaFuncSetAttribute(decode_mega_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem_optin);
 }
 
 struct AttnPlan { int n_splits, chunk_cap, cluster; };

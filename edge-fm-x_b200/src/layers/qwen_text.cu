@@ -27,6 +27,22 @@ static GemvParams base_gemv(const __nv_bfloat16* W, int N, int K) {
     return p;
 }
 
+// One decode GEMV: the INT4 copy of the linear when the context decodes from INT4 weights, else bf16.
+template <Epi EPI>
+static void launch_decode_gemv(efm_b200_ctx& c, Launcher& L, const GemvParams& p, const W4Linear* w4, int swiglu_half = 0) {
+    if (c.decode_w4 && w4 != nullptr && w4->ready) {
+        GemvW4Params q{};
+        q.g = p;
+        q.g.W = nullptr;
+        q.Wq = w4->q;
+        q.scales = static_cast<const __half2*>(w4->s);
+        q.swiglu_half = swiglu_half;
+        launch_gemv_w4<EPI>(L, q, c.num_sms);
+        return;
+    }
+    launch_gemv<EPI>(L, p, c.num_sms);
+}
+
 static void tp_all_reduce(efm_b200_ctx& c, Launcher& L, const float* send, float* recv, size_t count);
 static void tp_all_gather(efm_b200_ctx& c, Launcher& L, const float* send, float* recv, size_t count);
 static void launch_sample_only(efm_b200_ctx& c, Launcher& L, int n_part, int advance);
@@ -70,7 +86,7 @@ void launch_sample(Launcher& L, const SampleParams& p) {
     L.launch(sample_kernel, dim3(cs), dim3(1024), 0, p);
 }
 
-void launch_lm_head_and_sample(efm_b200_ctx& c, Launcher& L, const float* resid_row, int advance) {
+void launch_lm_head_and_sample(efm_b200_ctx& c, Launcher& L, const float* resid_row, int advance, bool decode_pass) {
     const efm_model_desc& d = c.d;
     GemvParams p = base_gemv(c.lm_head, c.vocab_l, d.hidden);      // this rank's rows (all of them without TP)
     p.prologue = kProRmsNorm;
@@ -80,7 +96,8 @@ void launch_lm_head_and_sample(efm_b200_ctx& c, Launcher& L, const float* resid_
     p.logits = c.tp_size > 1 ? c.logits_l : c.logits;
     p.part_val = c.part_val;
     p.part_idx = c.part_idx;
-    launch_gemv<Epi::Logits>(L, p, c.num_sms);
+    if (decode_pass) launch_decode_gemv<Epi::Logits>(c, L, p, &c.w4_lm_head);
+    else launch_gemv<Epi::Logits>(L, p, c.num_sms);
     if (c.tp_size > 1) {
         const bool pdl = L.pdl;
         tp_all_gather(c, L, c.logits_l, c.logits, (size_t)c.vocab_l);
@@ -125,40 +142,6 @@ static void launch_sample_only(efm_b200_ctx& c, Launcher& L, int n_part, int adv
     s.wbuf = c.wbuf;
     s.xchg = sample_xchg(c.wbuf, d.vocab);
     launch_sample(L, s);
-}
-
-// One decode step as the persistent cooperative kernel + the sampler.
-static void qwen_decode_step_mega(efm_b200_ctx& c, KvSlot& slot, Launcher& L) {
-    const efm_model_desc& d = c.d;
-    const int D = d.head_dim, nb = c.num_sms;
-    MegaParams P{};
-    P.layers = static_cast<const MegaLayer*>(slot.mega_layers);
-    P.L = d.num_layers; P.H = d.hidden; P.QD = d.q_heads * D; P.KVD = d.kv_heads * D; P.I = d.intermediate;
-    P.V = d.vocab; P.vocab = d.vocab; P.q_heads = d.q_heads; P.kv_heads = d.kv_heads;
-    P.eps = d.rms_eps;
-    P.ks_qkv = plan_gemv_ksplit((P.QD + 2 * P.KVD) / 2, P.H, nb);
-    P.ks_o = plan_gemv_ksplit(P.H / 2, P.QD, nb);
-    P.ks_gu = plan_gemv_ksplit(P.I, P.H, nb);
-    P.ks_down = plan_gemv_ksplit(P.H / 2, P.I, nb);
-    P.ks_lm = plan_gemv_ksplit(P.V / 2, P.H, nb);
-    P.embed = c.embed; P.final_norm = c.final_norm; P.lm_head = c.lm_head;
-    P.resid = c.resid_d; P.q = c.q_d; P.attn = c.attn_d; P.act = c.act_d;
-    P.logits = c.logits; P.part_val = c.part_val; P.part_idx = c.part_idx;
-    P.state = c.state; P.inv_freq = c.inv_freq;
-    P.use_mrope = d.use_mrope; P.sec0 = d.mrope_section[0]; P.sec1 = d.mrope_section[0] + d.mrope_section[1];
-    P.max_tokens = slot.max_tokens;
-    P.n_splits = slot.n_splits; P.chunk_cap = slot.chunk_cap;
-    P.scale = 1.0f / sqrtf((float)D);
-    P.part_o = c.attn_part_o; P.part_ml = c.attn_part_ml; P.attn_counters = c.attn_counters;
-    P.barrier = c.mega_barrier;
-    P.abort_flag = reinterpret_cast<int*>(c.mega_barrier + 2);
-    P.gemv_smem_bytes = (unsigned int)mega_gemv_smem_bytes(P.H, P.QD, P.I);
-    P.timing = L.phase_timing ? c.mega_timing : nullptr;
-    const size_t smem = P.gemv_smem_bytes + decode_attention_smem_bytes(D, 0);
-    L.cooperative = true;
-    if (D == 128) L.launch(decode_mega_kernel<128>, dim3(nb), dim3(kMegaThreads), smem, P);
-    else L.launch(decode_mega_kernel<64>, dim3(nb), dim3(kMegaThreads), smem, P);
-    launch_sample_only(c, L, nb, /*advance=*/1);
 }
 
 // Collectives on the context stream (graph-capturable).  A failure is recorded like a launch failure.
@@ -262,14 +245,14 @@ static void qwen_decode_step_tp(efm_b200_ctx& c, KvSlot& slot, Launcher& L) {
             if (l > 0) { if (fused) peers_consumer(c, p, 1); else p.addend = c.ysum; }
             p.resid_out = RA;
             p.norm_w = w.in_norm; p.eps = d.rms_eps; p.embed_table = c.embed; p.vocab = d.vocab; p.state = c.state;
-            p.bias = w.qkv_bias; p.q_out = c.q_d; p.k_cache = slot.k[l]; p.v_cache = slot.v[l]; p.inv_freq = c.inv_freq;
+            p.bias = w.qkv_bias; p.q_out_f = c.q_d; p.k_cache = slot.k[l]; p.v_cache = slot.v[l]; p.inv_freq = c.inv_freq;
             p.q_heads = d.q_heads; p.kv_heads = d.kv_heads; p.head_dim = D; p.use_mrope = d.use_mrope;
             p.sec0 = d.mrope_section[0]; p.sec1 = d.mrope_section[0] + d.mrope_section[1]; p.max_tokens = slot.max_tokens;
             launch_gemv<Epi::QkvRope>(L, p, c.num_sms);
         }
         {
             DecodeAttnParams a{};
-            a.q = c.q_d; a.k_cache = slot.k[l]; a.v_cache = slot.v[l]; a.out = c.attn_d; a.state = c.state;
+            a.qf = c.q_d; a.k_cache = slot.k[l]; a.v_cache = slot.v[l]; a.outf = c.attn_d; a.state = c.state;
             a.q_heads = d.q_heads; a.kv_heads = d.kv_heads; a.group = d.q_heads / d.kv_heads;
             a.n_splits = slot.n_splits; a.chunk_cap = slot.chunk_cap; a.max_tokens = slot.max_tokens; a.cluster = slot.attn_cluster; a.early = l > 0 ? 1 : 0;
             a.scale = 1.0f / sqrtf((float)D);
@@ -278,7 +261,7 @@ static void qwen_decode_step_tp(efm_b200_ctx& c, KvSlot& slot, Launcher& L) {
         }
         {
             GemvParams p = base_gemv(w.o, H, c.o_k);
-            p.x = c.attn_d + (size_t)c.att_rep_idx * c.o_k;
+            p.xf = c.attn_d + (size_t)c.att_rep_idx * c.o_k;
             if (fused) {
                 peers_producer(c, p, 0);
                 launch_gemv<Epi::Peers>(L, p, c.num_sms);              // fp32 partial straight into every rank's buffer
@@ -293,12 +276,12 @@ static void qwen_decode_step_tp(efm_b200_ctx& c, KvSlot& slot, Launcher& L) {
             p.prologue = kProRmsNorm;
             p.xr = RA; p.resid_out = RB;
             if (fused) peers_consumer(c, p, 0); else p.addend = c.ysum;
-            p.norm_w = w.post_norm; p.eps = d.rms_eps; p.y = c.act_d;
+            p.norm_w = w.post_norm; p.eps = d.rms_eps; p.yf = c.act_d;
             launch_gemv<Epi::SwiGlu>(L, p, c.num_sms);
         }
         {
             GemvParams p = base_gemv(w.down, H, I);
-            p.x = c.act_d;
+            p.xf = c.act_d;
             if (fused) {
                 peers_producer(c, p, 1);
                 launch_gemv<Epi::Peers>(L, p, c.num_sms);
@@ -322,13 +305,16 @@ static void qwen_decode_step_tp(efm_b200_ctx& c, KvSlot& slot, Launcher& L) {
     launch_sample_only(c, L, /*n_part=*/0, /*advance=*/1);
 }
 
+void launch_w4_repack(Launcher& L, const W4RepackParams& p) {
+    const bool pdl = L.pdl;
+    L.pdl = false;
+    L.launch(w4_repack_kernel<0>, dim3(p.n_items), dim3(256), 0, p);
+    L.pdl = pdl;
+}
+
 void qwen_decode_step(efm_b200_ctx& c, KvSlot& slot, Launcher& L) {
     if (c.tp_size > 1) {
         qwen_decode_step_tp(c, slot, L);
-        return;
-    }
-    if (c.mega && L.trace == nullptr) {      // per-kernel tracing needs the phase-per-launch form
-        qwen_decode_step_mega(c, slot, L);
         return;
     }
     const efm_model_desc& d = c.d;
@@ -346,7 +332,7 @@ void qwen_decode_step(efm_b200_ctx& c, KvSlot& slot, Launcher& L) {
             p.resid_out = c.resid_d;
             p.state = c.state;
             p.bias = w.qkv_bias;
-            p.q_out = c.q_d;
+            p.q_out_f = c.q_d;
             p.k_cache = slot.k[l];
             p.v_cache = slot.v[l];
             p.inv_freq = c.inv_freq;
@@ -357,14 +343,14 @@ void qwen_decode_step(efm_b200_ctx& c, KvSlot& slot, Launcher& L) {
             p.sec0 = d.mrope_section[0];
             p.sec1 = d.mrope_section[0] + d.mrope_section[1];
             p.max_tokens = slot.max_tokens;
-            launch_gemv<Epi::QkvRope>(L, p, c.num_sms);
+            launch_decode_gemv<Epi::QkvRope>(c, L, p, &w.w4_qkv);
         }
         {
             DecodeAttnParams a{};
-            a.q = c.q_d;
+            a.qf = c.q_d;
             a.k_cache = slot.k[l];
             a.v_cache = slot.v[l];
-            a.out = c.attn_d;
+            a.outf = c.attn_d;
             a.state = c.state;
             a.q_heads = d.q_heads;
             a.kv_heads = d.kv_heads;
@@ -382,9 +368,9 @@ void qwen_decode_step(efm_b200_ctx& c, KvSlot& slot, Launcher& L) {
         }
         {
             GemvParams p = base_gemv(w.o, H, c.o_k);
-            p.x = c.attn_d;
+            p.xf = c.attn_d;
             p.residual = c.resid_d;
-            launch_gemv<Epi::Residual>(L, p, c.num_sms);
+            launch_decode_gemv<Epi::Residual>(c, L, p, &w.w4_o);
         }
         {
             GemvParams p = base_gemv(w.gate_up, 2 * I, H);
@@ -392,17 +378,17 @@ void qwen_decode_step(efm_b200_ctx& c, KvSlot& slot, Launcher& L) {
             p.xr = c.resid_d;
             p.norm_w = w.post_norm;
             p.eps = d.rms_eps;
-            p.y = c.act_d;
-            launch_gemv<Epi::SwiGlu>(L, p, c.num_sms);
+            p.yf = c.act_d;
+            launch_decode_gemv<Epi::SwiGlu>(c, L, p, &w.w4_gate_up, I);
         }
         {
             GemvParams p = base_gemv(w.down, H, I);
-            p.x = c.act_d;
+            p.xf = c.act_d;
             p.residual = c.resid_d;
-            launch_gemv<Epi::Residual>(L, p, c.num_sms);
+            launch_decode_gemv<Epi::Residual>(c, L, p, &w.w4_down);
         }
     }
-    launch_lm_head_and_sample(c, L, c.resid_d, /*advance=*/1);
+    launch_lm_head_and_sample(c, L, c.resid_d, /*advance=*/1, /*decode_pass=*/true);
 }
 
 // ---- tensor maps for the TMA-fed GEMM --------------------------------------------------------
@@ -654,7 +640,7 @@ void qwen_prefill_chunk(efm_b200_ctx& c, KvSlot& slot, int S, int kv_offset, int
             tp_prefill_sum(c, L, S, 1);
         }
     }
-    if (sample_last) launch_lm_head_and_sample(c, L, c.resid + (size_t)(S - 1) * H, /*advance=*/0);
+    if (sample_last) launch_lm_head_and_sample(c, L, c.resid + (size_t)(S - 1) * H, /*advance=*/0, /*decode_pass=*/false);
     L.pdl = pdl;
 }
 

@@ -16,7 +16,7 @@ void qwen_decode_step(efm_b200_ctx& c, KvSlot& slot, Launcher& L);
 void qwen_prefill_chunk(efm_b200_ctx& c, KvSlot& slot, int S, int kv_offset, int n_custom, int embed_token_id,
                         bool sample_last, Launcher& L);
 // Final norm + lm_head + sampler on one residual row.
-void launch_lm_head_and_sample(efm_b200_ctx& c, Launcher& L, const float* resid_row, int advance);
+void launch_lm_head_and_sample(efm_b200_ctx& c, Launcher& L, const float* resid_row, int advance, bool decode_pass = false);
 // Single operators (used by the per-operator C entry points).
 void launch_gemm_bf16(Launcher& L, const GemmParams& p);
 // C = A . B^T on the tensor cores with the named epilogue; error_word (device int, may be null) is
@@ -37,4 +37,8 @@ cudaError_t configure_sampler();      // once per device at set-up, never inside
 void launch_rmsnorm_rows(Launcher& L, const float* x, const __nv_bfloat16* w, __nv_bfloat16* y, int rows, int hidden, float eps);
 void launch_prefill_attention(Launcher& L, const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v,
                               __nv_bfloat16* out, int S, int kv_offset, int q_heads, int kv_heads, int D);
+// checkpoint layout -> kernel layout of one INT4 linear (operators/gemv_w4.cuh: w4_repack_kernel)
+struct W4RepackParams;
+void launch_w4_repack(Launcher& L, const W4RepackParams& p);
+
 }  // namespace efm

@@ -28,10 +28,12 @@ constexpr int kAttnThreads = 512;
 constexpr int kAttnWarps = kAttnThreads / 32;
 
 struct DecodeAttnParams {
-    const __nv_bfloat16* q;        // [q_heads, D]
+    const __nv_bfloat16* q;        // [q_heads, D] bf16 ...
+    const float* qf;               // ... or, when non-null, fp32 (the decode step keeps q unrounded)
     const __nv_bfloat16* k_cache;  // [max_tokens, kv_heads, D]
     const __nv_bfloat16* v_cache;
-    __nv_bfloat16* out;            // [q_heads, D]
+    __nv_bfloat16* out;            // [q_heads, D] bf16 ...
+    float* outf;                   // ... or, when non-null, fp32
     DecodeState* state;            // kv_len source when non-null
     int kv_len_static;
     int q_heads, kv_heads, group, n_splits, max_tokens, chunk_cap;
@@ -118,9 +120,18 @@ __device__ __forceinline__ void decode_attention_body(const DecodeAttnParams& p,
     }
     for (int i = tid * 2; i < G * D; i += NT * 2) {              // q: two channels per load
         const int g = i / D, d = i - g * D;
-        const uint32_t two = __ldcg(reinterpret_cast<const unsigned int*>(p.q + (size_t)(kvh * G) * D + i));
-        sm.q[g][d / DP][d % DP] = bf16lo(two);
-        sm.q[g][(d + 1) / DP][(d + 1) % DP] = bf16hi(two);
+        float q0, q1;
+        if (p.qf != nullptr) {
+            const float2 two = __ldcg(reinterpret_cast<const float2*>(p.qf + (size_t)(kvh * G) * D + i));
+            q0 = two.x;
+            q1 = two.y;
+        } else {
+            const uint32_t two = __ldcg(reinterpret_cast<const unsigned int*>(p.q + (size_t)(kvh * G) * D + i));
+            q0 = bf16lo(two);
+            q1 = bf16hi(two);
+        }
+        sm.q[g][d / DP][d % DP] = q0;
+        sm.q[g][(d + 1) / DP][(d + 1) % DP] = q1;
     }
     if (early) {
         if (0 < n && tok < min(kAttnTile, n) && start + tok == kv_len - 1) issue_tile(0, -1);
@@ -279,7 +290,9 @@ __device__ __forceinline__ void decode_attention_body(const DecodeAttnParams& p,
                 Lsum = fmaf(lr[r], w, Lsum);
                 o = fmaf(orr[r], w, o);
             }
-            p.out[(size_t)(kvh * G) * D + i] = __float2bfloat16_rn(Lsum > 0.f ? o / Lsum : 0.f);
+            const float res = Lsum > 0.f ? o / Lsum : 0.f;
+            if (p.outf != nullptr) p.outf[(size_t)(kvh * G) * D + i] = res;
+            else p.out[(size_t)(kvh * G) * D + i] = __float2bfloat16_rn(res);
         }
         // nobody leaves while a neighbour may still read its shared memory
         asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
@@ -348,7 +361,9 @@ __device__ __forceinline__ void decode_attention_body(const DecodeAttnParams& p,
                 o3 = fmaf(v[j + 3], sm.mw[g][s0 + j + 3], o3);
             }
         }
-        p.out[(size_t)(kvh * G + g) * D + d] = __float2bfloat16_rn((o0 + o1) + (o2 + o3));
+        const float res = (o0 + o1) + (o2 + o3);
+        if (p.outf != nullptr) p.outf[(size_t)(kvh * G + g) * D + d] = res;
+        else p.out[(size_t)(kvh * G + g) * D + d] = __float2bfloat16_rn(res);
     }
     if (tid == 0) p.counters[kvh] = 0u;
 }

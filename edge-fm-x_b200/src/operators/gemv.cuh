@@ -2,7 +2,7 @@
 // fused in so that one launch replaces a chain of the reference's kernels:
 //
 //   prologue  Plain            x is read as is                      (o_proj, down_proj)
-//             RmsNorm          x = bf16(rmsnorm(residual) * w), residual stream in fp32
+//             RmsNorm          x = rmsnorm(residual) * w, residual stream and x in fp32
 //                                                                   (K2/K3 + K4 of the reference:
 //                                                                    src/operators/norm_op.cu:20-106)
 //             EmbedRmsNorm     residual = embed_table[token] first  (src/layers/embed_head.cu:22-61)
@@ -19,7 +19,9 @@
 // loads.  A warp (or `ks` warps sharing one row pair) walks its rows in units of 8 x 2 loads: 16
 // loads of 16 bytes in flight per lane, ~19 MB chip-wide, which is what it takes to cover the
 // ~2 us loaded DRAM latency at full bandwidth (halving it to 8 measurably costs 20 %).  Activations
-// live in shared memory; dot products reduce with warp shuffles (and a named-barrier exchange
+// live in shared memory as fp32 (a decode step rounds nothing to bf16 but the K / V rows it appends: with bf16
+// activations the rounding noise of 28-36 layers alone exceeds a 2e-2 logit tolerance on the 3B / 7B shapes);
+// dot products reduce with warp shuffles (and a named-barrier exchange
 // when ks > 1).  The first unit and the norm weight are fetched BEFORE the dependency wait
 // (griddepcontrol.wait, or the grid barrier of the persistent decode kernel), because weights
 // do not depend on the previous phase.
@@ -37,7 +39,8 @@ struct GemvParams {
     int N, K, n_items;        // n_items = N / 2 (every epilogue consumes rows in pairs)
     // prologue
     int prologue;
-    const __nv_bfloat16* x;   // Plain: activations [K] bf16
+    const __nv_bfloat16* x;   // Plain: activations [K] bf16 ...
+    const float* xf;          // ... or, when non-null, fp32 (the decode step's own activations)
     const float* xr;          // norm prologues: residual stream [K] fp32
     const __nv_bfloat16* norm_w;
     float eps;
@@ -48,10 +51,12 @@ struct GemvParams {
                               // the previous row-parallel linear); resid_out must differ from xr
     DecodeState* state;
     // epilogue
-    __nv_bfloat16* y;         // Plain: [N]; SwiGlu: [N/2]
+    __nv_bfloat16* y;         // Plain: [N]; SwiGlu: [N/2] ...
+    float* yf;                // ... or, when non-null, SwiGlu output in fp32
     float* residual;          // Residual: [N] fp32 in/out
     const __nv_bfloat16* bias;
-    __nv_bfloat16* q_out;     // QkvRope
+    __nv_bfloat16* q_out;     // QkvRope: rotated q in bf16 (q, k, v rounded to bf16 before the rotation as the prefill does) ...
+    float* q_out_f;           // ... or, when non-null, in fp32: then nothing is rounded but the K / V rows written to the cache
     __nv_bfloat16* k_cache;
     __nv_bfloat16* v_cache;
     const float* inv_freq;
@@ -123,7 +128,8 @@ __device__ __forceinline__ void item_epilogue(const GemvParams& p, int item, flo
         *reinterpret_cast<float2*>(p.residual + item * 2) = make_float2(old.x + a0, old.y + a1);
     } else if constexpr (EPI == Epi::SwiGlu) {
         const float s = a0 / (1.0f + expf(-a0));
-        p.y[item] = __float2bfloat16_rn(s * a1);
+        if (p.yf != nullptr) p.yf[item] = s * a1;
+        else p.y[item] = __float2bfloat16_rn(s * a1);
     } else if constexpr (EPI == Epi::Peers) {
         const unsigned int e = (unsigned int)best_i;           // exchange count of this launch (see gemv_kernel)
         const unsigned long long w0 = peer_word(a0, e), w1 = peer_word(a1, e);
@@ -143,8 +149,11 @@ __device__ __forceinline__ void item_epilogue(const GemvParams& p, int item, flo
             y0 += __bfloat162float(p.bias[r0]);
             y1 += __bfloat162float(p.bias[r1]);
         }
-        y0 = round_bf16(y0);
-        y1 = round_bf16(y1);
+        const bool full = p.q_out_f != nullptr;
+        if (!full) {
+            y0 = round_bf16(y0);
+            y1 = round_bf16(y1);
+        }
         const uint32_t kv_len = p.state->kv_len;
         if (kv_len == 0 || kv_len > (uint32_t)p.max_tokens) {
             p.state->error = 1;   // refuse the out-of-range cache row instead of faulting
@@ -159,8 +168,13 @@ __device__ __forceinline__ void item_epilogue(const GemvParams& p, int item, flo
             sincosf((float)pos * p.inv_freq[d], &sn, &cs);
             const float o0 = y0 * cs - y1 * sn, o1 = y1 * cs + y0 * sn;
             if (head < p.q_heads) {
-                p.q_out[r0] = __float2bfloat16_rn(o0);
-                p.q_out[r1] = __float2bfloat16_rn(o1);
+                if (full) {
+                    p.q_out_f[r0] = o0;
+                    p.q_out_f[r1] = o1;
+                } else {
+                    p.q_out[r0] = __float2bfloat16_rn(o0);
+                    p.q_out[r1] = __float2bfloat16_rn(o1);
+                }
             } else {
                 const int kh = head - p.q_heads;
                 p.k_cache[row + kh * D + d] = __float2bfloat16_rn(o0);
@@ -221,40 +235,44 @@ __device__ __forceinline__ void gemv_load_unit(const GemvParams& p, const GemvSc
     }
 }
 
+// Shared memory of one GEMV phase: [xs: fp32 K][norm weight: bf16 K][red: 2 x 16 x 2 floats][misc: 16 floats].
+__host__ __device__ inline unsigned int gemv_xbytes(int K) { return ((unsigned int)K * 4u + 15u) & ~15u; }
+__host__ __device__ inline unsigned int gemv_wbytes(int K) { return ((unsigned int)K * 2u + 15u) & ~15u; }
+
 // Weights only: the first two units into registers, the norm weight into shared memory.
 template <Epi EPI>
 __device__ __forceinline__ void gemv_prefetch(const GemvParams& p, const GemvSched& sc, GemvRegs& r, unsigned char* smem,
                                               const unsigned int xbytes) {
     gemv_load_unit<EPI>(p, sc, 0, r.a);
     if (p.prologue != kProPlain) {
-        uint4* gs = reinterpret_cast<uint4*>(smem + xbytes);
+        uint4* gs = reinterpret_cast<uint4*>(smem + xbytes);        // xbytes = gemv_xbytes(K)
         for (int c = threadIdx.x; c < sc.nch; c += kGemvThreads) gs[c] = ld_cached(p.norm_w + (size_t)c * 8);
     }
 }
 
-// Stage activations (with the fused norm), stream the rows, reduce, epilogue.
-// smem: [xs: xbytes][norm weight: xbytes][red: 2 x 16 x 2 floats][misc: 16 floats][residual row: K floats]
-template <Epi EPI>
-__device__ __forceinline__ void gemv_run(const GemvParams& p, const GemvSched& sc, GemvRegs& r, unsigned char* smem,
-                                         const unsigned int xbytes, float& best_v, int& best_i) {
-    __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem);
+// Activations of one GEMV phase into shared memory as fp32 [K], with the fused prologue (embedding row / residual
+// stream + tensor-parallel partials -> RMSNorm).  Ends with a block barrier.  xbytes = gemv_xbytes(K).
+__device__ __forceinline__ void gemv_stage(const GemvParams& p, const int nch, unsigned char* smem, const unsigned int xbytes) {
+    float* xs = reinterpret_cast<float*>(smem);
     const uint4* gs = reinterpret_cast<const uint4*>(smem + xbytes);
-    float* red = reinterpret_cast<float*>(smem + 2 * xbytes);
+    float* red = reinterpret_cast<float*>(smem + xbytes + gemv_wbytes(p.K));
     float* misc = red + 2 * kGemvWarps * 2;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int nch = sc.nch;
-
-    // residual pair of the first item, fetched under the weight stream
-    float2 old_first = make_float2(0.f, 0.f);
-    if constexpr (EPI == Epi::Residual) {
-        if (sc.wk == 0 && lane == 0 && sc.total > 0)
-            old_first = __ldcg(reinterpret_cast<const float2*>(p.residual + sc.ig0 * 2));
-    }
     // ---- activations (L2 loads: another block may have produced them) ------------------------
     if (p.prologue == kProPlain) {
-        for (int c = tid; c < nch; c += kGemvThreads) reinterpret_cast<uint4*>(xs)[c] = ld_cg(p.x + (size_t)c * 8);
+        if (p.xf != nullptr) {
+            for (int c = tid; c < 2 * nch; c += kGemvThreads)
+                reinterpret_cast<float4*>(xs)[c] = __ldcg(reinterpret_cast<const float4*>(p.xf) + c);
+        } else {
+            for (int c = tid; c < nch; c += kGemvThreads) {
+                float f[8];
+                unpack8(ld_cg(p.x + (size_t)c * 8), f);
+                reinterpret_cast<float4*>(xs)[2 * c] = make_float4(f[0], f[1], f[2], f[3]);
+                reinterpret_cast<float4*>(xs)[2 * c + 1] = make_float4(f[4], f[5], f[6], f[7]);
+            }
+        }
     } else {
-        // residual stream in fp32 (or the embedding row); staged as fp32 until the scale is known
+        // residual stream in fp32 (or the embedding row); staged unscaled until the norm is known
         const __nv_bfloat16* table_row = nullptr;
         bool zero = false, from_table = false;
         if (p.prologue == kProEmbedRmsNorm) {
@@ -263,7 +281,7 @@ __device__ __forceinline__ void gemv_run(const GemvParams& p, const GemvSched& s
             table_row = p.embed_table + (size_t)(zero ? 0 : tok) * p.K;
             from_table = true;
         }
-        float* xf32 = reinterpret_cast<float*>(smem + 2 * xbytes + (2 * kGemvWarps * 2 + 16) * sizeof(float));   // [K]
+        float* xf32 = xs;                                          // normalised in place below
         // count to wait for: bumped by this GPU's producing kernel
         const unsigned int want = p.addend_parts == nullptr ? 0u : (p.want_override != 0u ? p.want_override : __ldcg(p.epoch));
         PeerWait pw = peer_wait_begin(p.addend_parts != nullptr ? p.error : nullptr);
@@ -326,15 +344,30 @@ __device__ __forceinline__ void gemv_run(const GemvParams& p, const GemvSched& s
             const float4 lo = reinterpret_cast<const float4*>(xf32)[2 * c], hi = reinterpret_cast<const float4*>(xf32)[2 * c + 1];
             float w[8];
             unpack8(gs[c], w);
-            uint4 o;
-            o.x = pack_bf16(lo.x * inv * w[0], lo.y * inv * w[1]);
-            o.y = pack_bf16(lo.z * inv * w[2], lo.w * inv * w[3]);
-            o.z = pack_bf16(hi.x * inv * w[4], hi.y * inv * w[5]);
-            o.w = pack_bf16(hi.z * inv * w[6], hi.w * inv * w[7]);
-            reinterpret_cast<uint4*>(xs)[c] = o;
+            reinterpret_cast<float4*>(xs)[2 * c] = make_float4(lo.x * inv * w[0], lo.y * inv * w[1], lo.z * inv * w[2], lo.w * inv * w[3]);
+            reinterpret_cast<float4*>(xs)[2 * c + 1] = make_float4(hi.x * inv * w[4], hi.y * inv * w[5], hi.z * inv * w[6], hi.w * inv * w[7]);
         }
     }
     __syncthreads();
+}
+
+// Stage activations (with the fused norm), stream the rows, reduce, epilogue.
+template <Epi EPI>
+__device__ __forceinline__ void gemv_run(const GemvParams& p, const GemvSched& sc, GemvRegs& r, unsigned char* smem,
+                                         const unsigned int xbytes, float& best_v, int& best_i) {
+    const float* xs = reinterpret_cast<const float*>(smem);
+    float* red = reinterpret_cast<float*>(smem + xbytes + gemv_wbytes(p.K));
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int nch = sc.nch;
+
+    // residual pair of the first item, fetched under the weight stream
+    float2 old_first = make_float2(0.f, 0.f);
+    if constexpr (EPI == Epi::Residual) {
+        if (sc.wk == 0 && lane == 0 && sc.total > 0)
+            old_first = __ldcg(reinterpret_cast<const float2*>(p.residual + sc.ig0 * 2));
+    }
+    gemv_stage(p, nch, smem, xbytes);
+    (void)tid;
 
     // ---- rows ------------------------------------------------------------------------------------
     float acc0 = 0.f, acc1 = 0.f;
@@ -345,8 +378,8 @@ __device__ __forceinline__ void gemv_run(const GemvParams& p, const GemvSched& s
         for (int uu = 0; uu < kGemvU; ++uu) {
             const int c = (part * kGemvU + uu) * sc.stride + sc.gl;
             if (c < nch) {
-                float xf[8];
-                unpack8(reinterpret_cast<const uint4*>(xs)[c], xf);
+                const float4 xlo = reinterpret_cast<const float4*>(xs)[2 * c], xhi = reinterpret_cast<const float4*>(xs)[2 * c + 1];
+                const float xf[8] = {xlo.x, xlo.y, xlo.z, xlo.w, xhi.x, xhi.y, xhi.z, xhi.w};
                 acc0 = dot8(buf[uu][0], xf, acc0);
                 acc1 = dot8(buf[uu][1], xf, acc1);
             }
@@ -410,7 +443,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
     extern __shared__ __align__(16) unsigned char gemv_smem[];
     __shared__ float bv[kGemvWarps];
     __shared__ int bi[kGemvWarps];
-    const unsigned int xbytes = ((unsigned int)p.K * 2 + 15) & ~15u;
+    const unsigned int xbytes = gemv_xbytes(p.K);
     GemvRegs regs;
     float best_v = -INFINITY;
     int best_i = 0x7fffffff;
@@ -436,8 +469,8 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
     }
 }
 
-inline size_t gemv_smem_bytes(int K) {      // xs | norm weight | red + misc | fp32 staging of the residual row
-    return 2 * (((size_t)K * 2 + 15) & ~(size_t)15) + (size_t)(2 * kGemvWarps * 2 + 16) * sizeof(float) + (size_t)K * sizeof(float);
+__host__ __device__ inline size_t gemv_smem_bytes(int K) {      // xs (fp32) | norm weight | red + misc
+    return (size_t)gemv_xbytes(K) + gemv_wbytes(K) + (size_t)(2 * kGemvWarps * 2 + 16) * sizeof(float);
 }
 
 }  // namespace efm

@@ -134,6 +134,19 @@ EFM_API efm_status efm_b200_tp_host_wait(void* nccl_comm, int (*ready)(void*), v
  * source (EFM_MEM_DEVICE) is read on the context's own stream: whatever produced it must have finished. */
 EFM_API efm_status efm_b200_set_weight(efm_b200_ctx* ctx, const char* hf_name, const void* data,
                                        const int64_t* shape, int32_t ndim, int32_t dtype, int32_t mem_kind);
+/* Group-wise INT4 (W4A16) weights for the DECODE pass only, from a second checkpoint (the reference's
+ * decode_model_path, src/engine/engine_factory.cpp:64-72; weight contract src/layers/linear.cu:536-565):
+ *   "<linear>.qweight"          int8 [out_features / 2, in_features]: byte [r][k] carries rows 2r (low nibble) and
+ *                               2r + 1 (high nibble) of column k as q + 8, q in [-8, 7];
+ *   "<linear>.scaling_factors"  fp16 or bf16 [in_features / 128, out_features];  w[n][k] = q[n][k] * scale[k / 128][n]
+ * for <linear> = model.layers.N.{self_attn.{q,k,v,o}_proj, mlp.{gate,up,down}_proj} (all layers or none) and, optionally,
+ * lm_head.  Prefill keeps the bf16 weights of efm_b200_set_weight; biases, norms and the embedding table are shared.
+ * finalize_weights re-packs the tensors into the decode kernel's layout.  The nibble order inside the reference's
+ * qweight is produced by a packer that is not part of its tree (TensorRT-Edge-LLM); the plain order above is this
+ * library's own, so checkpoints packed for the reference's kernels have to be re-packed.  Other tensor names are
+ * ignored; tensor-parallel contexts refuse INT4 weights (EFM_ERR_UNSUPPORTED). */
+EFM_API efm_status efm_b200_set_decode_weight(efm_b200_ctx* ctx, const char* hf_name, const void* data,
+                                              const int64_t* shape, int32_t ndim, int32_t dtype, int32_t mem_kind);
 /* Checks that every tensor arrived; after this call weights are immutable. */
 EFM_API efm_status efm_b200_finalize_weights(efm_b200_ctx* ctx);
 

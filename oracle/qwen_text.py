@@ -5,9 +5,14 @@ Two modes:
 * ``exact_fp32``  — every intermediate stays fp32 (weights are the bf16 checkpoint
   values upcast).  Logit tolerance (2e-2 relative) is graded against this mode.
 * ``bf16_points`` — same math, but every value the CUDA path stores as bf16 is
-  rounded to bf16 at that point (norm output, QKV outputs, rotated q/k,
-  attention output, SiLU-gated activation).  The residual stream is fp32 on the
-  GPU and here.  Greedy-token identity is graded against this mode.
+  rounded to bf16 at that point.  Rows that go through the prefill GEMMs round
+  the norm output, the QKV outputs, rotated q/k, the attention output and the
+  SiLU-gated activation.  A row that goes through the decode kernels (every
+  decode step, and the LAST row of a sampled prefill, which the CUDA path runs
+  as a decode step so that all logits come from one arithmetic) keeps fp32
+  activations and rounds only the K row (once, after the rotation) and the V row
+  it appends to the cache.  The residual stream is fp32 on the GPU and here.
+  Greedy-token identity is graded against this mode.
 
 Dataflow follows src/models/qwen2_5/qwen2_5.cpp:534-930 of the reference:
 embedding -> per layer [RMSNorm -> fused QKV (+bias) -> RoPE -> attention over the
@@ -177,12 +182,27 @@ class QwenTextOracle:
         return out
 
     def forward(self, ids: Sequence[int], embeds: Optional[torch.Tensor] = None, embed_token_id: int = -1,
-                position_ids: Optional[torch.Tensor] = None, all_logits: bool = False) -> torch.Tensor:
+                position_ids: Optional[torch.Tensor] = None, all_logits: bool = False, tail: bool = True) -> torch.Tensor:
         """Append len(ids) tokens to the cache; return fp32 logits of the last row ([V]),
         or of every row ([S, V]) when all_logits.  position_ids: [3, S] for M-RoPE models;
-        text models use the cache index as position (attention_op.cu: q at kv_len-1)."""
-        c, r = self.cfg, self.r
+        text models use the cache index as position (attention_op.cu: q at kv_len-1).
+        tail (bf16_points mode only): the last row is computed with the decode kernels' rounding
+        points (a sampled prefill or a decode step); False: every row takes the prefill GEMMs'
+        (a prefix prefill without sampling)."""
+        c = self.cfg
         S, P, D = len(ids), self.kv_len, c.head_dim
+        r_all = self.r
+        last_custom = embeds is not None and embed_token_id >= 0 and embed_token_id <= ids[-1] < embed_token_id + embeds.shape[0]
+        if self.mode == "bf16_points" and tail and not last_custom and 0 <= ids[-1] < c.vocab:
+            keep = torch.zeros(S, dtype=torch.bool)
+            keep[-1] = True                                  # rows that keep fp32 activations
+
+            def r(t):                                        # [S, ...]: round every row but the kept ones
+                k = keep.view(S, *([1] * (t.dim() - 1)))
+                return torch.where(k, t, _bf16_round(t))
+        else:
+            keep = None
+            r = r_all
         if self.pair_section is not None:
             assert position_ids is not None and tuple(position_ids.shape) == (3, S)
             pos = position_ids.to(torch.float32)[self.pair_section, :].T.contiguous()      # [S, D/2]
@@ -199,8 +219,9 @@ class QwenTextOracle:
             n = r(rmsnorm(R, w["in_norm"], c.rms_eps))
             qkv = r(n @ w["wqkv"].T + w["bqkv"])
             q = r(apply_rope(qkv[:, :qd].reshape(S, c.q_heads, D), pos, self.inv_freq))
-            k = r(apply_rope(qkv[:, qd:qd + kd].reshape(S, c.kv_heads, D), pos, self.inv_freq))
-            v = qkv[:, qd + kd:].reshape(S, c.kv_heads, D)
+            # the cache holds bf16 for every row: kept rows round K once (after the rotation) and V once
+            k = r_all(apply_rope(qkv[:, qd:qd + kd].reshape(S, c.kv_heads, D), pos, self.inv_freq))
+            v = r_all(qkv[:, qd + kd:].reshape(S, c.kv_heads, D))
             self.k_cache[l] = torch.cat([self.k_cache[l], k], dim=0)
             self.v_cache[l] = torch.cat([self.v_cache[l], v], dim=0)
             K = self.k_cache[l].repeat_interleave(group, dim=1)                 # [T, q_heads, D]
@@ -214,7 +235,9 @@ class QwenTextOracle:
             act = r(silu(n2 @ w["wg"].T) * (n2 @ w["wu"].T))
             R = R + act @ w["wd"].T
         rows = R if all_logits else R[-1:]
-        hn = r(rmsnorm(rows, self.final_norm, c.rms_eps))
+        hn = rmsnorm(rows, self.final_norm, c.rms_eps)
+        if keep is None or all_logits:
+            hn = r_all(hn) if keep is None else r(hn)
         logits = hn @ self.lm_head.T
         return logits if all_logits else logits[0]
 

@@ -61,6 +61,7 @@ SIGNATURES = {
     "efm_b200_tp_set_wait_limit": (I32, [P, C.c_int64, C.c_double]),
     "efm_b200_tp_host_wait": (I32, [P, C.CFUNCTYPE(C.c_int, P), P, C.c_double]),
     "efm_b200_set_weight": (I32, [P, C.c_char_p, P, C.POINTER(C.c_int64), I32, I32, I32]),
+    "efm_b200_set_decode_weight": (I32, [P, C.c_char_p, P, C.POINTER(C.c_int64), I32, I32, I32]),
     "efm_b200_finalize_weights": (I32, [P]),
     "efm_b200_alloc_kv_slot": (I32, [P, I32, I32]),
     "efm_b200_kv_layer_ptr": (I32, [P, I32, I32, C.POINTER(P), C.POINTER(I32)]),
@@ -205,6 +206,19 @@ class Backend:
                 torch.cuda.current_stream(t.device).synchronize()
             self.check(self.L.efm_b200_set_weight(self.ctx, name.encode(), P(t.data_ptr()), shape, t.dim(),
                                                   EFM_BF16, mem), "set_weight " + name)
+
+    def load_decode_weights_int4(self, tensors):
+        """tensors: dict '<linear>.qweight' -> int8 tensor, '<linear>.scaling_factors' -> fp16 / bf16 tensor (before finalize)."""
+        import torch
+        codes = {torch.int8: 6, torch.uint8: 5, torch.float16: EFM_F16, torch.bfloat16: EFM_BF16}
+        for name, t in tensors.items():
+            t = t.contiguous()
+            shape = (C.c_int64 * t.dim())(*t.shape)
+            mem = EFM_MEM_DEVICE if t.is_cuda else EFM_MEM_HOST
+            if t.is_cuda:
+                torch.cuda.current_stream(t.device).synchronize()
+            self.check(self.L.efm_b200_set_decode_weight(self.ctx, name.encode(), P(t.data_ptr()), shape, t.dim(), codes[t.dtype], mem),
+                       "set_decode_weight " + name)
 
     def finalize(self):
         self.check(self.L.efm_b200_finalize_weights(self.ctx), "finalize_weights")

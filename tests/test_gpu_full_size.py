@@ -5,7 +5,7 @@ oracle to finish in seconds, so it is checked against it directly: greedy ids fo
 (bf16_points oracle, teacher-forced; a differing id must be a tie within the observed logit error) and
 logits within 2e-2 relative of the exact fp32 oracle.  Config 1 (1.5B shape, top-p) and the config 2 text tower
 (3B shape, M-RoPE, injected embeddings) get the same teacher-forced 32-step comparison at their own sizes; config 1
-is also checked through size-independent properties: captured graph == plain launches == persistent kernel,
+is also checked through size-independent properties: captured graph == plain launches,
 resident prefix == full prefill, run-to-run determinism of the seeded top-p sampler.  Every comparison prints its
 worst logit error and the number of tie-limited steps (run pytest with -s to see them)."""
 import os
@@ -63,32 +63,20 @@ def test_config1_full_size_properties():
     w = synth.make_weights(cfg, seed=0, device="cuda")
     ids = synth.make_token_ids(prefix_n + prompt_n, seed=0)
     steps = 24
-    outs = {}
-    for name, env in (("phase_per_launch", "0"), ("persistent", "1")):
-        os.environ["EFM_B200_MEGA"] = env
-        be = cabi.Backend(cfg, max_prefill_tokens=1024, max_response_tokens=64)
-        be.load_weights(w)
-        for slot in (0, 1):
-            be.alloc_slot(slot, prefix_n + prompt_n + 64)
-        be.set_sampling(temp, top_p, 0)
-        be.prefill(1, ids[:prefix_n], kv_offset=0, sample=False)
-        graph, lg = cabi.generate(be, 0, ids, steps, use_graph=True, collect_logits=True)
-        eager, _ = cabi.generate(be, 0, ids, steps, use_graph=False)
-        again, _ = cabi.generate(be, 0, ids, steps, use_graph=True)
-        prefixed, lp = cabi.generate(be, 1, ids, steps, prefix_len=prefix_n, collect_logits=True)
-        assert graph == eager == again                          # seeded sampler: same ids every time
-        assert rel(lp[0], lg[0]) < 2e-2                          # resident prefix vs one full prefill
-        assert len(set(graph)) > steps // 2                      # top-p at T 0.7 actually samples
-        outs[name] = (graph, lg)
-        be.close()
-    os.environ.pop("EFM_B200_MEGA", None)
-    # the two decode forms differ only in how the attention partials are merged (cluster exchange vs scratch +
-    # ticket), i.e. in fp32 rounding: same first token, logits of the first decode step equal to rounding.  Later
-    # sampled ids may part ways once a rounding difference crosses a top-p boundary.
-    a, b = outs["phase_per_launch"], outs["persistent"]
-    assert a[0][0] == b[0][0]
-    assert rel(a[1][0], b[1][0]) < 1e-6                     # prefill: identical kernels
-    assert rel(a[1][1], b[1][1]) < 1e-2                     # bf16 rounding points amplify the fp32 merge difference
+    be = cabi.Backend(cfg, max_prefill_tokens=1024, max_response_tokens=64)
+    be.load_weights(w)
+    for slot in (0, 1):
+        be.alloc_slot(slot, prefix_n + prompt_n + 64)
+    be.set_sampling(temp, top_p, 0)
+    be.prefill(1, ids[:prefix_n], kv_offset=0, sample=False)
+    graph, lg = cabi.generate(be, 0, ids, steps, use_graph=True, collect_logits=True)
+    eager, _ = cabi.generate(be, 0, ids, steps, use_graph=False)
+    again, _ = cabi.generate(be, 0, ids, steps, use_graph=True)
+    prefixed, lp = cabi.generate(be, 1, ids, steps, prefix_len=prefix_n, collect_logits=True)
+    assert graph == eager == again                          # seeded sampler: same ids every time
+    assert rel(lp[0], lg[0]) < 2e-2                          # resident prefix vs one full prefill
+    assert len(set(graph)) > steps // 2                      # top-p at T 0.7 actually samples
+    be.close()
 
 
 def teacher_forced_check(cfg, w, be, ids, steps, *, prefix_n=0, embeds=None, embed_id=-1, pos=None, last_pos=None, sampler=None,

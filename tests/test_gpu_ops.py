@@ -217,4 +217,4 @@ def test_peer_wait_runs_out_and_the_device_stays_usable():
     assert waited < 2.0, waited                       # 20 ms budget for the whole kernel, not per wait
     words[2, 100, 1] = 5                              # the word arrives: same call succeeds, device still usable
     ok(L.efm_b200_op_gemv_peer_consume(P(w), P(resid), P(nw), 1e-6, P(words), parts, 5, 20_000, P(y), P(rout), n, k))
-    assert torch.equal(rout, resid + ((vals[0] + vals[1]) + vals[2]) + vals[3])
+    assert torch.equal(rout, resid + (((vals[0] + vals[1]) + vals[2]) + vals[3]))

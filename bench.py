@@ -15,6 +15,7 @@ runs the SAME request tensor parallel over the N ranks (heads + MLP columns + vo
 from __future__ import annotations
 
 import argparse
+import datetime
 import json
 import os
 import shutil
@@ -284,7 +285,8 @@ def run_tp(args, rank, world, local_rank):
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     torch.cuda.set_device(local_rank)
     if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        # a short collective timeout: a rank that raises must end the job, not leave the others waiting for ten minutes
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank), timeout=datetime.timedelta(seconds=240))
     else:
         dist = _Solo
     cfg, prefix, ids, gen_tokens, temp, top_p = workload(args.config)
@@ -375,7 +377,7 @@ def run_tp(args, rank, world, local_rank):
         req = edge_fm.Request(0, ids, edge_fm.Tensor(embeds.data_ptr(), [vlm["n_img"], cfg.hidden], edge_fm.DType.BFloat16,
                                                      edge_fm.Device.GPU, local_rank),
                               vlm["embed_id"], edge_fm.Tensor(pt.data_ptr(), [3, len(ids)], edge_fm.DType.Int32, edge_fm.Device.CPU),
-                              [vlm["last"]] * 3)
+                              [vlm["last"]] * 3, device=edge_fm.Device.GPU, device_id=local_rank)
         req.set_ignore_stop_tokens(True)
         return list(engine.generate(req).token_ids())
 
@@ -409,7 +411,8 @@ def run_tp(args, rank, world, local_rank):
         wall_s = time.perf_counter() - t0
         m = engine.last_generate_metrics()
     clocks = sampler.stop()
-    local = torch.tensor([dec_ms, pre_ms, wall_s or 0.0, vit_ms], dtype=torch.float64, device="cuda")
+    torch.cuda.set_device(local_rank)
+    local = torch.tensor([dec_ms, pre_ms, wall_s or 0.0, vit_ms], dtype=torch.float64, device=torch.device("cuda", local_rank))
     dist.all_reduce(local, op=dist.ReduceOp.MAX)
     dec_ms, pre_ms, wall_max, vit_ms = [float(x) for x in local.tolist()]
     dec_steps = args.steps * (gen_tokens - 1)
@@ -579,7 +582,8 @@ def run_text(args, cfg_id, rank, world, local_rank, *, steps, warmup, want_cpu, 
             req = edge_fm.Request(0, ids, edge_fm.Tensor(embeds.data_ptr(), [vlm["n_img"], cfg.hidden], edge_fm.DType.BFloat16,
                                                          edge_fm.Device.GPU, local_rank),
                                   vlm["embed_id"],
-                                  edge_fm.Tensor(pt.data_ptr(), [3, len(ids)], edge_fm.DType.Int32, edge_fm.Device.CPU), [vlm["last"]] * 3)
+                                  edge_fm.Tensor(pt.data_ptr(), [3, len(ids)], edge_fm.DType.Int32, edge_fm.Device.CPU), [vlm["last"]] * 3,
+                                  device=edge_fm.Device.GPU, device_id=local_rank)
         req.set_ignore_stop_tokens(True)
         return list(engine.generate(req).token_ids())
     e2e_s, e2e_tokens, m = None, None, {}
@@ -601,7 +605,8 @@ def run_text(args, cfg_id, rank, world, local_rank, *, steps, warmup, want_cpu, 
     step_bytes = be.decode_step_bytes(len(ids) + gen_tokens // 2)
 
     dec_steps = steps * (gen_tokens - 1)
-    local = torch.tensor([dec_ms, pre_ms, wall_s, e2e_s or 0.0, vit_ms], dtype=torch.float64, device="cuda")
+    torch.cuda.set_device(local_rank)
+    local = torch.tensor([dec_ms, pre_ms, wall_s, e2e_s or 0.0, vit_ms], dtype=torch.float64, device=torch.device("cuda", local_rank))
     if dist is not None:
         dist.all_reduce(local, op=dist.ReduceOp.MAX)
     dec_ms_max, pre_ms_max, wall_max, e2e_max, vit_ms_max = [float(x) for x in local.tolist()]
@@ -774,7 +779,7 @@ def run_vla(args, rank, world, local_rank, *, steps, warmup, want_cpu, dist=None
     pol.phase_ms()
     phases = pol.phase_ms()
     if dist is not None:
-        t = torch.tensor([dev_ms, wall_s], dtype=torch.float64, device="cuda")
+        t = torch.tensor([dev_ms, wall_s], dtype=torch.float64, device=torch.device("cuda", local_rank))
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dev_ms, wall_s = [float(x) for x in t.tolist()]
     fl = vla_flops(c)
@@ -881,7 +886,7 @@ def main():
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         torch.cuda.set_device(local_rank)
         dist = dist_mod
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank), timeout=datetime.timedelta(seconds=240))
     if args.config == 4:
         line = run_vla(args, rank, world, local_rank, steps=args.steps, warmup=args.warmup,
                        want_cpu=world == 1 and not args.no_cpu, dist=dist)
@@ -896,4 +901,13 @@ def main():
 
 
 if __name__ == "__main__":
-    main()
+    try:
+        main()
+    except BaseException:
+        # a failing rank must not linger in destructors that wait for its peers: report and leave at once, so that the
+        # launcher ends the other ranks instead of letting them wait out a collective timeout
+        import traceback
+        traceback.print_exc()
+        sys.stderr.flush()
+        sys.stdout.flush()
+        os._exit(1)

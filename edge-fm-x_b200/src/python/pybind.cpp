@@ -112,13 +112,24 @@ PYBIND11_MODULE(edge_fm, m) {
 
     py::class_<Request>(m, "Request")
         .def(py::init<int, const std::vector<int32_t>&>(), py::arg("request_id"), py::arg("token_ids"))
-        .def(py::init<int, const std::vector<int32_t>&, const Tensor&, int32_t>(), py::arg("request_id"),
-             py::arg("token_ids"), py::arg("embedding"), py::arg("embed_token_id") = -1)
-        .def(py::init<int, const std::vector<int32_t>&, const Tensor&, int32_t, const Tensor&>(), py::arg("request_id"),
-             py::arg("token_ids"), py::arg("embedding"), py::arg("embed_token_id"), py::arg("position_ids"))
-        .def(py::init<int, const std::vector<int32_t>&, const Tensor&, int32_t, const Tensor&, const std::vector<int32_t>&>(),
-             py::arg("request_id"), py::arg("token_ids"), py::arg("embedding"), py::arg("embed_token_id"),
-             py::arg("position_ids"), py::arg("mrope_last_pos"))
+        // device / device_id: where the request's deep copies of embedding and position_ids are placed (multi-GPU callers
+        // pass their own GPU; the defaults are the reference's: GPU 0)
+        .def(py::init([](int id, const std::vector<int32_t>& ids, const Tensor& emb, int32_t eid, Device dev, int32_t dev_id) {
+                 return new Request(id, ids, emb, eid, dev, dev_id);
+             }),
+             py::arg("request_id"), py::arg("token_ids"), py::arg("embedding"), py::arg("embed_token_id") = -1,
+             py::arg("device") = Device::GPU, py::arg("device_id") = 0)
+        .def(py::init([](int id, const std::vector<int32_t>& ids, const Tensor& emb, int32_t eid, const Tensor& pos, Device dev, int32_t dev_id) {
+                 return new Request(id, ids, emb, eid, pos, dev, dev_id);
+             }),
+             py::arg("request_id"), py::arg("token_ids"), py::arg("embedding"), py::arg("embed_token_id"), py::arg("position_ids"),
+             py::arg("device") = Device::GPU, py::arg("device_id") = 0)
+        .def(py::init([](int id, const std::vector<int32_t>& ids, const Tensor& emb, int32_t eid, const Tensor& pos,
+                         const std::vector<int32_t>& last, Device dev, int32_t dev_id) {
+                 return new Request(id, ids, emb, eid, pos, last, dev, dev_id);
+             }),
+             py::arg("request_id"), py::arg("token_ids"), py::arg("embedding"), py::arg("embed_token_id"), py::arg("position_ids"),
+             py::arg("mrope_last_pos"), py::arg("device") = Device::GPU, py::arg("device_id") = 0)
         .def("request_id", &Request::request_id)
         .def("token_ids", &Request::token_ids, py::return_value_policy::reference_internal)
         .def("embedding", &Request::embedding, py::return_value_policy::reference_internal)

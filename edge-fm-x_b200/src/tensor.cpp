@@ -56,6 +56,18 @@ float half_to_float(uint16_t h) {
 
 }  // namespace
 
+// Switches the calling thread to a device for the guard's lifetime and puts the caller's device back: copies and frees
+// on "the tensor's device" must not move a multi-GPU caller's current device from under it.
+struct DeviceGuard {
+    int prev = -1;
+    explicit DeviceGuard(int device_id) {
+        if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
+        if (prev != device_id) cuda_check(cudaSetDevice(device_id), "cudaSetDevice");
+        else prev = -1;
+    }
+    ~DeviceGuard() { if (prev >= 0) cudaSetDevice(prev); }
+};
+
 Tensor::Tensor() noexcept = default;
 Tensor::Tensor(Tensor&& other) noexcept = default;
 
@@ -65,12 +77,24 @@ static void free_impl(void* data, Device device, int32_t device_id, MemoryOwners
         case MemoryOwnership::ViewExternal: break;
         case MemoryOwnership::OwnCpuMalloc: std::free(data); break;
         case MemoryOwnership::OwnCudaMalloc:
-            if (device == Device::GPU) { cudaSetDevice(device_id); cudaFree(data); } else std::free(data);
+            if (device == Device::GPU) {
+                int prev = -1;
+                if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
+                cudaSetDevice(device_id);
+                cudaFree(data);
+                if (prev >= 0 && prev != device_id) cudaSetDevice(prev);
+            } else {
+                std::free(data);
+            }
             break;
-        case MemoryOwnership::OwnCudaPool:
+        case MemoryOwnership::OwnCudaPool: {
+            int prev = -1;
+            if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
             cudaSetDevice(device_id);
             cudaFreeAsync(data, static_cast<cudaStream_t>(stream));
+            if (prev >= 0 && prev != device_id) cudaSetDevice(prev);
             break;
+        }
     }
 }
 
@@ -121,12 +145,12 @@ Tensor Tensor::clone_from(const void* src, const std::vector<int64_t>& shape, DT
         if (dst == nullptr) throw OutOfMemoryError("host allocation failed");
         if (src_device == Device::CPU) std::memcpy(dst, src, bytes);
         else {
-            cuda_check(cudaSetDevice(src_device_id), "cudaSetDevice");
+            DeviceGuard guard(src_device_id);
             cuda_check(cudaMemcpy(dst, src, bytes, cudaMemcpyDeviceToHost), "copy to host");
         }
         return adopt(dst, shape, dtype, Device::CPU, dst_device_id, MemoryOwnership::OwnCpuMalloc == ownership ? ownership : MemoryOwnership::OwnCpuMalloc);
     }
-    cuda_check(cudaSetDevice(dst_device_id), "cudaSetDevice");
+    DeviceGuard guard(dst_device_id);
     if (ownership == MemoryOwnership::OwnCudaPool) {
         if (stream == nullptr) throw InvalidArgumentError("OwnCudaPool needs a stream");
         cuda_check(cudaMallocAsync(&dst, bytes, stream), "cudaMallocAsync");
@@ -224,7 +248,7 @@ void Tensor::dump(const std::string& file_path) const {
     const size_t esz = get_dtype_size(impl_->dtype);
     std::vector<char> host((size_t)n * esz);
     if (impl_->device == Device::GPU) {
-        cuda_check(cudaSetDevice(impl_->device_id), "cudaSetDevice");
+        DeviceGuard guard(impl_->device_id);
         cuda_check(cudaMemcpy(host.data(), impl_->data, host.size(), cudaMemcpyDeviceToHost), "dump copy");
     } else {
         std::memcpy(host.data(), impl_->data, host.size());

@@ -315,6 +315,7 @@ def run_tp(args, rank, world, local_rank):
     if args.prefill_attention == "int8":        # the benchmark's configuration 3 prefills with the INT8 attention scheme
         be.set_prefill_attention(1)
     be.set_sampling(temp, top_p, 0)
+    be.set_prefill_graph(True)       # as the engine does with runtime.use_cuda_graph: the request's prefill shape is captured once
     be.capture_decode(0)
     # vision encoder on the text context's stream; its windows are sharded over the ranks
     n_patches = sum(t * h * w for t, h, w in vlm["grids"])
@@ -500,6 +501,7 @@ def run_text(args, cfg_id, rank, world, local_rank, *, steps, warmup, want_cpu, 
     be.set_sampling(temp, top_p, 0)
     if prefix:
         be.prefill(0, prefix, kv_offset=0, pos3=None if pos is None else [r[:len(prefix)] for r in pos], sample=False)
+    be.set_prefill_graph(True)       # as the engine does with runtime.use_cuda_graph: the request's prefill shape is captured once
     be.capture_decode(0)
     enc = None
     if vlm is not None:

@@ -446,6 +446,8 @@ efm_status efm_b200_vit_encode(efm_b200_vit* v, const void* pixels, int32_t pixe
             a.q_stride = a.kv_stride = 3 * H; a.out_stride = H;
             a.S = n; a.kv_offset = 0; a.q_heads = a.kv_heads = d.heads;
             a.scale = 1.0f / sqrtf((float)D);
+            a.kv_rows = full && tp > 1 ? N : n;          // rows behind k / v: the gathered rows of every rank, or the local ones
+            a.error = err;
             launch_seg_attention(L, a, D);
             GemmParams g{v->attn, b.proj_w, b.proj_b, nullptr, v->resid, n, H, H};
             launch_gemm_epi(L, GemmEpi::Residual, g, err);
@@ -506,9 +508,10 @@ efm_status efm_b200_op_segment_attention(const void* q, const void* k, const voi
     a.q_stride = a.kv_stride = stride; a.out_stride = heads * head_dim;
     a.S = s; a.q_heads = a.kv_heads = heads;
     a.scale = 1.0f / sqrtf((float)head_dim);
+    a.kv_rows = s;                                   // q, k, v are rows of one buffer
     launch_seg_attention(L, a, head_dim);
-    if (L.err != cudaSuccess) return EFM_ERR_CUDA;
-    return cudaStreamSynchronize(nullptr) == cudaSuccess ? EFM_OK : EFM_ERR_CUDA;
+    cudaError_t e = L.err != cudaSuccess ? L.err : cudaStreamSynchronize(nullptr);
+    return e == cudaSuccess ? EFM_OK : EFM_ERR_CUDA;
 }
 
 }  // extern "C"

@@ -8,6 +8,7 @@
 #include "qwen_text.h"
 
 #include "../operators/attention_mma.cuh"
+#include "../operators/attention_tc.cuh"
 #include "../operators/sage_attention.cuh"
 #include "../operators/gemm_tc.cuh"
 #include "../operators/prefill.cuh"
@@ -532,8 +533,62 @@ void launch_seg_attention_short(Launcher& L, const SegAttnParams& p, int D, int 
     L.pdl = pdl;
 }
 
+// bf16 tensor of up to three dimensions for TMA: dims / box innermost first, byte strides of dimensions 1 and 2.
+static bool make_map_nd(CUtensorMap* map, const void* ptr, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
+                        const uint32_t* box) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (fn == nullptr) return false;
+    cuuint64_t gdim[3], gstride[2];
+    cuuint32_t bx[3], estride[3] = {1, 1, 1};
+    for (int i = 0; i < rank; ++i) { gdim[i] = dims[i]; bx[i] = box[i]; }
+    for (int i = 0; i + 1 < rank; ++i) gstride[i] = strides_bytes[i];
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(ptr), gdim, gstride, bx, estride,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+static bool attention_tc_enabled() {
+    static const bool on = [] { const char* e = std::getenv("EFM_B200_ATTN_TC"); return e == nullptr || e[0] != '0'; }();
+    return on;
+}
+
+// tcgen05 / TMEM form (attention_tc.cuh).
+template <int D>
+static bool launch_seg_attention_tc_d(Launcher& L, const SegAttnParams& p0) {
+    using C = at::Cfg<D>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaFuncSetAttribute(seg_attention_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM);
+        attr_set = true;
+    }
+    const SegAttnParams& p = p0;
+    CUtensorMap mq, mk, mv;
+    const uint64_t qd[3] = {(uint64_t)D, (uint64_t)p.q_heads, (uint64_t)p.S}, qs[2] = {(uint64_t)D * 2, (uint64_t)p.q_stride * 2};
+    const uint64_t kd[3] = {(uint64_t)D, (uint64_t)p.kv_heads, (uint64_t)p.kv_rows}, ks[2] = {(uint64_t)D * 2, (uint64_t)p.kv_stride * 2};
+    const uint32_t qb[3] = {64, 1, (uint32_t)at::BM}, kb[3] = {64, 1, (uint32_t)at::BN};
+    if (!make_map_nd(&mq, p.q, 3, qd, qs, qb) || !make_map_nd(&mk, p.k, 3, kd, ks, kb) || !make_map_nd(&mv, p.v, 3, kd, ks, kb)) return false;
+    const bool pdl = L.pdl;
+    L.pdl = false;
+    L.launch(seg_attention_tc_kernel<D>, dim3((p.S + at::BM - 1) / at::BM, p.q_heads), dim3(at::kThreads), C::SMEM, mq, mk, mv, p, p.error);
+    L.pdl = pdl;
+    return true;
+}
+
+static bool launch_seg_attention_tc(Launcher& L, const SegAttnParams& p, int D) {
+    // TMA needs 16-byte aligned bases and strides; anything else stays on the mma.sync kernel
+    if (p.kv_rows <= 0 || (p.q_stride & 7) || (p.kv_stride & 7) || (reinterpret_cast<uintptr_t>(p.q) & 15) ||
+        (reinterpret_cast<uintptr_t>(p.k) & 15) || (reinterpret_cast<uintptr_t>(p.v) & 15) || (p.out_stride & 7) ||
+        (reinterpret_cast<uintptr_t>(p.out) & 15) || !attention_tc_enabled())
+        return false;
+    if (D == 128) return launch_seg_attention_tc_d<128>(L, p);
+    if (D == 80) return launch_seg_attention_tc_d<80>(L, p);
+    if (D == 64) return launch_seg_attention_tc_d<64>(L, p);
+    return false;
+}
+
 void launch_seg_attention(Launcher& L, const SegAttnParams& p, int D) {
     if (p.S <= 0) return;
+    if (launch_seg_attention_tc(L, p, D)) return;
     if (D == 128) launch_seg_attention_d<128>(L, p);
     else if (D == 80) launch_seg_attention_d<80>(L, p);
     else if (D == 64) launch_seg_attention_d<64>(L, p);
@@ -542,12 +597,14 @@ void launch_seg_attention(Launcher& L, const SegAttnParams& p, int D) {
 
 // Causal GQA attention of a prefill chunk: queries at cache rows [kv_offset, kv_offset + S).
 void launch_prefill_attention(Launcher& L, const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v,
-                              __nv_bfloat16* out, int S, int kv_offset, int q_heads, int kv_heads, int D) {
+                              __nv_bfloat16* out, int S, int kv_offset, int q_heads, int kv_heads, int D, int* error) {
     SegAttnParams p{};
     p.q = q; p.k = k; p.v = v; p.out = out;
     p.q_stride = q_heads * D; p.kv_stride = kv_heads * D; p.out_stride = q_heads * D;
     p.S = S; p.kv_offset = kv_offset; p.q_heads = q_heads; p.kv_heads = kv_heads;
     p.scale = 1.0f / sqrtf((float)D);
+    p.kv_rows = kv_offset + S;
+    p.error = error;
     launch_seg_attention(L, p, D);
 }
 
@@ -616,7 +673,7 @@ void qwen_prefill_chunk(efm_b200_ctx& c, KvSlot& slot, int S, int kv_offset, int
         if (c.prefill_attention_kind == 1)
             launch_sage_prefill_attention(L, c.sage, c.qbuf, slot.k[l], slot.v[l], c.attn, S, kv_offset, d.q_heads, d.kv_heads, D);
         else
-            launch_prefill_attention(L, c.qbuf, slot.k[l], slot.v[l], c.attn, S, kv_offset, d.q_heads, d.kv_heads, D);
+            launch_prefill_attention(L, c.qbuf, slot.k[l], slot.v[l], c.attn, S, kv_offset, d.q_heads, d.kv_heads, D, &c.state->error);
         if (c.tp_size == 1) {
             GemmParams g{c.attn, w.o, nullptr, nullptr, c.resid, S, H, QD};
             launch_gemm<GemmEpi::Residual>(L, g, &c.state->error);

@@ -36,7 +36,8 @@ cudaError_t configure_sampler();      // once per device at set-up, never inside
 // y[r,:] = bf16(rmsnorm(x[r,:]) * w) over `rows` fp32 rows.
 void launch_rmsnorm_rows(Launcher& L, const float* x, const __nv_bfloat16* w, __nv_bfloat16* y, int rows, int hidden, float eps);
 void launch_prefill_attention(Launcher& L, const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v,
-                              __nv_bfloat16* out, int S, int kv_offset, int q_heads, int kv_heads, int D);
+                              __nv_bfloat16* out, int S, int kv_offset, int q_heads, int kv_heads, int D,
+                              int* error = nullptr);
 // checkpoint layout -> kernel layout of one INT4 linear (operators/gemv_w4.cuh: w4_repack_kernel)
 struct W4RepackParams;
 void launch_w4_repack(Launcher& L, const W4RepackParams& p);

@@ -25,6 +25,10 @@ struct SegAttnParams {
     int q_stride, kv_stride, out_stride;
     int S, kv_offset, q_heads, kv_heads;
     float scale;
+    // tcgen05 form (attention_tc.cuh) only: number of key / value rows behind k and v (0: the tensor-core-tile kernel of
+    // this file)
+    int kv_rows;
+    int* error;                  // raised (1) when a bounded pipeline wait of the tcgen05 form gives up; may be null
 };
 
 namespace sa {

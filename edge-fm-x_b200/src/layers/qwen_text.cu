@@ -535,14 +535,14 @@ void launch_seg_attention_short(Launcher& L, const SegAttnParams& p, int D, int 
 
 // bf16 tensor of up to three dimensions for TMA: dims / box innermost first, byte strides of dimensions 1 and 2.
 static bool make_map_nd(CUtensorMap* map, const void* ptr, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
-                        const uint32_t* box) {
+                        const uint32_t* box, CUtensorMapDataType dtype = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (fn == nullptr) return false;
     cuuint64_t gdim[3], gstride[2];
     cuuint32_t bx[3], estride[3] = {1, 1, 1};
     for (int i = 0; i < rank; ++i) { gdim[i] = dims[i]; bx[i] = box[i]; }
     for (int i = 0; i + 1 < rank; ++i) gstride[i] = strides_bytes[i];
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(ptr), gdim, gstride, bx, estride,
+    return fn(map, dtype, (cuuint32_t)rank, const_cast<void*>(ptr), gdim, gstride, bx, estride,
               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
@@ -620,7 +620,7 @@ static void launch_sage_d(Launcher& L, const SageAttnParams& p) {
 
 void launch_sage_prefill_attention(Launcher& L, const SageScratch& sc, const __nv_bfloat16* q, const __nv_bfloat16* k,
                                    const __nv_bfloat16* v, __nv_bfloat16* out, int S, int kv_offset, int q_heads,
-                                   int kv_heads, int D) {
+                                   int kv_heads, int D, int* error) {
     const int T = kv_offset + S;
     if (S <= 0) return;
     if ((D != 128 && D != 64) || S > sc.q_rows || T > sc.kv_rows) {
@@ -642,6 +642,31 @@ void launch_sage_prefill_attention(Launcher& L, const SageScratch& sc, const __n
     }
     L.launch(sage_to_half_kernel, dim3(std::min(((size_t)T * kvw / 2 + 255) / 256, (size_t)L.num_sms * 8)), dim3(256), 0, v, kvw, T,
              kvw, static_cast<__half*>(sc.vh));
+    if (D == 128 && attention_tc_enabled()) {
+        // tcgen05 form: Qi8 . Ki8^T as kind::i8 into TMEM, P . V in fp16 (attention_tc.cuh, I8 variant)
+        using C = at::Cfg<128, true>;
+        static bool attr_set = false;
+        if (!attr_set) {
+            cudaFuncSetAttribute(seg_attention_tc_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM);
+            attr_set = true;
+        }
+        CUtensorMap mq, mk, mv;
+        const uint64_t qd[3] = {128, (uint64_t)q_heads, (uint64_t)S}, qs[2] = {128, (uint64_t)q_heads * 128};
+        const uint64_t kd[3] = {128, (uint64_t)kv_heads, (uint64_t)T}, ks[2] = {128, (uint64_t)kv_heads * 128};
+        const uint64_t vd[3] = {128, (uint64_t)kv_heads, (uint64_t)T}, vs[2] = {256, (uint64_t)kv_heads * 256};
+        const uint32_t qb[3] = {128, 1, (uint32_t)at::BM}, kb[3] = {128, 1, (uint32_t)at::BN}, vb[3] = {64, 1, (uint32_t)at::BN};
+        if (make_map_nd(&mq, sc.q8, 3, qd, qs, qb, CU_TENSOR_MAP_DATA_TYPE_UINT8) && make_map_nd(&mk, sc.k8, 3, kd, ks, kb, CU_TENSOR_MAP_DATA_TYPE_UINT8) &&
+            make_map_nd(&mv, sc.vh, 3, vd, vs, vb, CU_TENSOR_MAP_DATA_TYPE_FLOAT16)) {
+            SegAttnParams a{};
+            a.out = out; a.out_stride = q_heads * D;
+            a.S = S; a.kv_offset = kv_offset; a.q_heads = q_heads; a.kv_heads = kv_heads; a.kv_rows = T;
+            a.scale = 1.0f / sqrtf((float)D);
+            a.sq = sc.sq; a.sk = sc.sk; a.error = error;
+            L.launch(seg_attention_tc_kernel<128, true>, dim3((S + at::BM - 1) / at::BM, q_heads), dim3(at::kThreads), C::SMEM, mq, mk, mv, a, error);
+            L.pdl = pdl;
+            return;
+        }
+    }
     SageAttnParams p{};
     p.q = sc.q8; p.k = sc.k8; p.v = static_cast<const __half*>(sc.vh); p.sq = sc.sq; p.sk = sc.sk; p.out = out;
     p.S = S; p.kv_offset = kv_offset; p.q_heads = q_heads; p.kv_heads = kv_heads;
@@ -671,7 +696,7 @@ void qwen_prefill_chunk(efm_b200_ctx& c, KvSlot& slot, int S, int kv_offset, int
                  (const int32_t*)c.pos3, S, d.q_heads, d.kv_heads, D, kv_offset, d.use_mrope, d.mrope_section[0],
                  d.mrope_section[0] + d.mrope_section[1]);
         if (c.prefill_attention_kind == 1)
-            launch_sage_prefill_attention(L, c.sage, c.qbuf, slot.k[l], slot.v[l], c.attn, S, kv_offset, d.q_heads, d.kv_heads, D);
+            launch_sage_prefill_attention(L, c.sage, c.qbuf, slot.k[l], slot.v[l], c.attn, S, kv_offset, d.q_heads, d.kv_heads, D, &c.state->error);
         else
             launch_prefill_attention(L, c.qbuf, slot.k[l], slot.v[l], c.attn, S, kv_offset, d.q_heads, d.kv_heads, D, &c.state->error);
         if (c.tp_size == 1) {

@@ -30,7 +30,7 @@ void launch_seg_attention_short(Launcher& L, const SegAttnParams& p, int D, int 
 // `sc`, then the attention kernel.  q: [S, q_heads*D] rotated queries; k/v: cache rows [0, kv_offset + S).
 void launch_sage_prefill_attention(Launcher& L, const SageScratch& sc, const __nv_bfloat16* q, const __nv_bfloat16* k,
                                    const __nv_bfloat16* v, __nv_bfloat16* out, int S, int kv_offset, int q_heads,
-                                   int kv_heads, int D);
+                                   int kv_heads, int D, int* error = nullptr);
 void launch_sample(Launcher& L, const SampleParams& p);
 cudaError_t configure_sampler();      // once per device at set-up, never inside a stream capture
 // y[r,:] = bf16(rmsnorm(x[r,:]) * w) over `rows` fp32 rows.

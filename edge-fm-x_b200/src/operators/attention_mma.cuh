@@ -28,6 +28,8 @@ struct SegAttnParams {
     // tcgen05 form (attention_tc.cuh) only: number of key / value rows behind k and v (0: the tensor-core-tile kernel of
     // this file)
     int kv_rows;
+    const float* sq;             // INT8 variant: scale of each 128-token block and head of q [ceil(S / 128), q_heads] ...
+    const float* sk;             // ... and of k [ceil(kv_rows / 128), kv_heads]
     int* error;                  // raised (1) when a bounded pipeline wait of the tcgen05 form gives up; may be null
 };
 

@@ -16,9 +16,13 @@
 // One elected thread issues every TMA load and MMA; K is double-buffered, V single (its next tile is requested as
 // soon as the P V product has read the current one).  Blocks take the query tiles last first: under the causal rule
 // the last tiles have the most keys and should start first.  Every mbarrier wait is bounded and raises *error.
+// INT8 variant (I8 = true; the "SageAttention"-style prefill attention of sage_attention.cuh, head_dim 128): Q and the
+// centred K arrive as int8 with one scale per 128-token block and head, S = Qi8 . Ki8^T is tcgen05.mma kind::i8 (K = 32
+// per instruction, exact int32 accumulators in TMEM) scaled by sq * sk / sqrt(D) when it is read; P and V are fp16.
 // Bound: tensor pipe / exp throughput (4 q D kv flops, q kv exponentials).
 #pragma once
 #include <cuda.h>
+#include <cuda_fp16.h>
 
 #include "attention_mma.cuh"
 #include "gemm_tc.cuh"
@@ -30,11 +34,12 @@ namespace at {
 constexpr int BM = 128, BN = 64, kThreads = 256;
 constexpr int S_COL = 0, O_COL = 64;
 
-template <int D>
+template <int D, bool I8 = false>
 struct Cfg {
-    static constexpr int DB = (D + 63) / 64;                 // 64-column boxes per Q / K row
-    static constexpr int Q_BYTES = BM * 128 * DB;
-    static constexpr int K_BYTES = BN * 128 * DB;
+    static constexpr int DB = (D + 63) / 64;                 // 64-channel boxes per V row (2-byte elements)
+    static constexpr int QB = I8 ? (D + 127) / 128 : DB;     // 128-byte boxes per Q / K row
+    static constexpr int Q_BYTES = BM * 128 * QB;
+    static constexpr int K_BYTES = BN * 128 * QB;
     static constexpr int V_BYTES = BN * 128 * DB;            // V tile: 64 keys x 128 bytes per box of 64 channels
     static constexpr int P_BYTES = BM * 128;
     static constexpr int TMEM_COLS = D == 64 ? 128 : 256;    // S (64 columns) + O tile (head_dim columns), power of two
@@ -50,6 +55,23 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
 // kind::f16, A = B = bf16, D = fp32, both operands K-major.
 __host__ __device__ constexpr uint32_t instr_desc(int M, int N) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+// kind::f16 with A = B = fp16 (format 0), D = fp32.
+__host__ __device__ constexpr uint32_t instr_desc_f16(int M, int N) {
+    return (1u << 4) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+// kind::i8, A = B = signed 8-bit (format 1), D = int32 (format 2), both operands K-major.
+__host__ __device__ constexpr uint32_t instr_desc_i8(int M, int N) {
+    return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+__device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n"
+        "}\n"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ void umma_d(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
@@ -86,7 +108,7 @@ __device__ __forceinline__ float ex2(float x) {
 
 }  // namespace at
 
-template <int D>
+template <int D, bool I8 = false>
 __global__ void __launch_bounds__(at::kThreads) seg_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                                                                         const __grid_constant__ CUtensorMap map_k,
                                                                         const __grid_constant__ CUtensorMap map_v,
@@ -98,7 +120,7 @@ __global__ void __launch_bounds__(at::kThreads) seg_attention_tc_kernel(const __
     using tc::smem_u32;
     using tc::umma_commit;
     using tc::umma_desc;
-    using C = Cfg<D>;
+    using C = Cfg<D, I8>;
     extern __shared__ unsigned char attn_tc_smem[];
     __shared__ int s_range[2];
     const uint32_t raw = smem_u32(attn_tc_smem);
@@ -146,7 +168,8 @@ __global__ void __launch_bounds__(at::kThreads) seg_attention_tc_kernel(const __
 
     // P V: B operand MN-major (bit 16).  Its shared-memory descriptor: 8-key groups 1024 bytes apart along K, boxes of 64
     // channels BN * 128 bytes apart along N.
-    constexpr uint32_t kDescS = instr_desc(BM, BN), kDescO = instr_desc(BM, D) | (1u << 16);
+    constexpr uint32_t kDescS = I8 ? instr_desc_i8(BM, BN) : instr_desc(BM, BN);
+    constexpr uint32_t kDescO = (I8 ? instr_desc_f16(BM, D) : instr_desc(BM, D)) | (1u << 16);
     const uint64_t vdesc = umma_desc_mn(sV, (uint32_t)(BN * 128), 1024u);
     const float sl2 = p.scale * 1.4426950408889634f;
     float o[C::HALF];
@@ -154,11 +177,13 @@ __global__ void __launch_bounds__(at::kThreads) seg_attention_tc_kernel(const __
     for (int e = 0; e < C::HALF; ++e) o[e] = 0.f;
     float m = -INFINITY, l = 0.f;
 
+    constexpr int QBOX = I8 ? 128 : 64;                      // elements per 128-byte box of a Q / K row
+    constexpr int KSTEP = I8 ? 32 : 16;                      // elements per MMA along head_dim
     auto load_k = [&](int tile, int buf) {
         mbar_expect_tx(kfull0 + 8 * buf, C::K_BYTES);
 #pragma unroll
-        for (int b = 0; b < C::DB; ++b)
-            tma_load_3d(sK + buf * C::K_BYTES + b * (BN * 128), &map_k, b * 64, kvh, kb0 + tile * BN, kfull0 + 8 * buf);
+        for (int b = 0; b < C::QB; ++b)
+            tma_load_3d(sK + buf * C::K_BYTES + b * (BN * 128), &map_k, b * QBOX, kvh, kb0 + tile * BN, kfull0 + 8 * buf);
     };
     auto load_v = [&](int tile) {
         mbar_expect_tx(vfull, C::V_BYTES);
@@ -167,10 +192,11 @@ __global__ void __launch_bounds__(at::kThreads) seg_attention_tc_kernel(const __
     };
     auto issue_s = [&](int buf) {
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k) {
+        for (int k = 0; k < D / KSTEP; ++k) {                 // one step = 32 bytes of a 128-byte box row, four per box
             const uint64_t da = umma_desc(sQ + (k >> 2) * (BM * 128)) + (uint64_t)((k & 3) * 2);
             const uint64_t db = umma_desc(sK + buf * C::K_BYTES + (k >> 2) * (BN * 128)) + (uint64_t)((k & 3) * 2);
-            umma_d(tmem + S_COL, da, db, kDescS, k != 0 ? 1u : 0u);
+            if constexpr (I8) umma_i8(tmem + S_COL, da, db, kDescS, k != 0 ? 1u : 0u);
+            else umma_d(tmem + S_COL, da, db, kDescS, k != 0 ? 1u : 0u);
         }
         umma_commit(sbar);
     };
@@ -178,7 +204,7 @@ __global__ void __launch_bounds__(at::kThreads) seg_attention_tc_kernel(const __
     if (ntiles > 0 && tid == 0) {
         mbar_expect_tx(qfull, C::Q_BYTES);
 #pragma unroll
-        for (int b = 0; b < C::DB; ++b) tma_load_3d(sQ + b * (BM * 128), &map_q, b * 64, h, q0, qfull);
+        for (int b = 0; b < C::QB; ++b) tma_load_3d(sQ + b * (BM * 128), &map_q, b * QBOX, h, q0, qfull);
         load_k(0, 0);
         if (ntiles > 1) load_k(1, 1);
         load_v(0);
@@ -198,10 +224,14 @@ __global__ void __launch_bounds__(at::kThreads) seg_attention_tc_kernel(const __
         const int key0 = kb0 + j * BN + hf * 32;
         float s[32];
         float mx = -INFINITY;
+        float f2 = sl2;
+        if constexpr (I8)       // one scale per 128-token block and head on either side (tiles never straddle a block)
+            f2 = sl2 * p.sq[(q0 / 128) * p.q_heads + h] * p.sk[((kb0 + j * BN) / 128) * p.kv_heads + kvh];
 #pragma unroll
         for (int e = 0; e < 32; ++e) {
             const int key = key0 + e;
-            s[e] = (key >= lo && key < hi) ? __uint_as_float(sr[e]) * sl2 : -INFINITY;
+            const float raw = I8 ? (float)(int)sr[e] : __uint_as_float(sr[e]);
+            s[e] = (key >= lo && key < hi) ? raw * f2 : -INFINITY;
             mx = fmaxf(mx, s[e]);
         }
         xch[hf * BM + row] = mx;
@@ -216,7 +246,12 @@ __global__ void __launch_bounds__(at::kThreads) seg_attention_tc_kernel(const __
         for (int e = 0; e < 32; e += 2) {
             const float p0 = ex2(s[e] - mb), p1 = ex2(s[e + 1] - mb);         // exp2(-inf) = 0 for masked keys
             rs += p0 + p1;
-            pk[e >> 1] = pack_bf16(p0, p1);
+            if constexpr (I8) {
+                const __half2 hp = __floats2half2_rn(p0, p1);
+                pk[e >> 1] = *reinterpret_cast<const uint32_t*>(&hp);
+            } else {
+                pk[e >> 1] = pack_bf16(p0, p1);
+            }
         }
         l = l * alpha + rs;
         {   // P row into the K-major, 128-byte-swizzled operand layout: chunk c of row r lives at chunk c ^ (r % 8)

@@ -5,7 +5,9 @@
 //  softmax, P in fp16, P . V in fp16 with fp32 accumulation.)
 //
 // Pre-pass (HBM-bound, a few microseconds): per-block key sums; Q and centred K to INT8 + scales; V to fp16.
-// Main kernel: same tiling as seg_attention_kernel (64 queries x 64-key tiles, cp.async double buffer,
+// Main kernel at head_dim 128: the INT8 variant of seg_attention_tc_kernel (attention_tc.cuh: tcgen05.mma kind::i8 into
+// TMEM for Q.K^T, kind::f16 for P.V).  The kernel of this file serves head_dim 64 and EFM_B200_ATTN_TC=0: same tiling as
+// seg_attention_kernel (64 queries x 64-key tiles, cp.async double buffer,
 // ldmatrix fragments) with mma.sync m16n8k32 s8 for Q.K^T and m16n8k16 f16 for P.V.  Causal rule only:
 // query i sees keys [0, kv_offset + i].  Bound: tensor pipe.
 #pragma once

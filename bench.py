@@ -477,8 +477,9 @@ def run_tp(args, rank, world, local_rank):
     return line
 
 
-def run_text(args, cfg_id, rank, world, local_rank, *, steps, warmup, want_cpu, dist=None):
-    """Configurations 0-2 on one GPU (world > 1: independent replicas, one per rank)."""
+def run_text(args, cfg_id, rank, world, local_rank, *, steps, warmup, want_cpu, dist=None, int4=False):
+    """Configurations 0-2 on one GPU (world > 1: independent replicas, one per rank).  int4: the decode pass runs on a
+    group-wise INT4 copy of every linear (two checkpoints: bf16 for prefill, INT4 for decode); C ABI only."""
     import torch
     import cabi
     from oracle import synth
@@ -496,7 +497,15 @@ def run_text(args, cfg_id, rank, world, local_rank, *, steps, warmup, want_cpu, 
     t_setup = time.perf_counter()
     w = synth.make_weights(cfg, seed=0, device="cuda")
     be = cabi.Backend(cfg, max_prefill_tokens=min(2048, max_tokens), max_response_tokens=gen_tokens + 8, device_id=local_rank)
-    be.load_weights(w)
+    if int4:
+        from oracle import int4 as int4_tools
+        packed, _ = int4_tools.quantize_checkpoint(w, cfg.num_layers, lm_head=True)     # quantised on the device
+        be.load_weights_partial(w)
+        be.load_decode_weights_int4(packed)
+        be.finalize()
+        del packed
+    else:
+        be.load_weights(w)
     be.alloc_slot(0, max_tokens)
     be.set_sampling(temp, top_p, 0)
     if prefix:
@@ -516,7 +525,7 @@ def run_text(args, cfg_id, rank, world, local_rank, *, steps, warmup, want_cpu, 
 
     # public API engine for the end-to-end leg (weights travel through a safetensors checkpoint)
     engine, tmp = None, None
-    if not args.no_e2e:
+    if not args.no_e2e and not int4:
         import edge_fm
         tmp = scratch_dir(rank, 8)
         model_dir = synth.write_checkpoint(os.path.join(tmp, "model"), cfg, w)
@@ -629,7 +638,15 @@ def run_text(args, cfg_id, rank, world, local_rank, *, steps, warmup, want_cpu, 
             kernels[k]["gbs"] = round(kbytes[k] / (us * 1e-6) / 1e9, 1)
             kernels[k]["frac"] = round(kbytes[k] / (us * 1e-6) / 1e9 / peak, 3)
     traffic = None
-    if cfg_id in NCU_LAYER_GEMV_DRAM_BYTES:       # measured for the layer GEMVs, algorithmic for the rest of the step
+    if int4:       # the bytes of the per-kernel table are those of the INT4 matrices
+        w4 = lambda n: n // 2 + n // 128 * 2
+        kbytes = {k: w4(v // 2) for k, v in kbytes.items()}
+        for k, item in kernels.items():
+            if k in kbytes:
+                us = item["us_per_launch"]
+                item["gbs"] = round(kbytes[k] / (us * 1e-6) / 1e9, 1)
+                item["frac"] = round(kbytes[k] / (us * 1e-6) / 1e9 / peak, 3)
+    if cfg_id in NCU_LAYER_GEMV_DRAM_BYTES and not int4:       # measured for the layer GEMVs, algorithmic for the rest of the step
         layer_alg = sum(v for k, v in kbytes.items() if k != "lm_head")
         traffic = step_bytes + L * (NCU_LAYER_GEMV_DRAM_BYTES[cfg_id] - layer_alg)
     line = None
@@ -652,7 +669,7 @@ def run_text(args, cfg_id, rank, world, local_rank, *, steps, warmup, want_cpu, 
                          "traffic": traffic,
                          "traffic_source": "constants from one ncu capture (dram__bytes_read+write of the per-layer GEMV launches, summary "
                                            "under profiles/) + algorithmic bytes of lm_head, attention and vectors" if traffic else None,
-                         "peak_kind": peak_kind,
+                         "peak_kind": peak_kind, "weights": "int4 group-128 (decode pass), bf16 (prefill)" if int4 else "bf16",
                          "launch": "one decode step (CUDA graph of %d kernel nodes: 5 per layer + lm_head + sampler)" % (5 * L + 2),
                          "bytes_per_launch": step_bytes, "us_per_launch": step_ms * 1e3, "frac_of_nominal_8tbs": achieved / 8000.0,
                          "kernels": kernels},
@@ -830,7 +847,8 @@ def summarise(line):
            "prefill_ms": line["prefill_ms"], "prefill_frac_of_bf16_peak": line["prefill"]["frac_of_bf16_peak"],
            "ttft_ms": line["ttft_ms"], "e2e": line.get("e2e", {}).get("value"), "e2e_tokens_equal": line.get("e2e_tokens_equal"),
            "kernel_us": {k: v["us_per_launch"] for k, v in line["roofline"]["kernels"].items()},
-           "steps": line["steps"], "workload": line["config"]["workload"]}
+           "steps": line["steps"], "workload": line["config"]["workload"], "weights": line["roofline"].get("weights", "bf16"),
+           "bytes_per_decode_step": line["roofline"]["bytes_per_launch"]}
     if "vit" in line:
         out["vit_ms"] = line["vit_ms"]
         out["vit_frac_of_bf16_peak"] = line["vit"]["frac_of_bf16_peak"]
@@ -850,6 +868,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the public-API end-to-end leg (profiling runs)")
     ap.add_argument("--no-per-config", action="store_true", help="headline run without the pass over configurations 0, 1, 2, 4")
+    ap.add_argument("--int4", action="store_true", help="configurations 0-2: decode on a group-wise INT4 copy of the linears (C ABI only)")
     ap.add_argument("--tp-exchange", default="peer", choices=["peer", "nccl"],
                     help="config 3 on several GPUs: how the decode step sums the row-parallel partials")
     ap.add_argument("--prefill-attention", default="auto", choices=["auto", "bf16", "int8"],
@@ -876,6 +895,7 @@ def main():
             per = {}
             for c in (0, 1, 2):
                 per[str(c)] = summarise(run_text(args, c, 0, 1, local_rank, steps=2, warmup=3, want_cpu=False))
+            per["1_int4"] = summarise(run_text(args, 1, 0, 1, local_rank, steps=2, warmup=3, want_cpu=False, int4=True))
             per["4"] = summarise(run_vla(args, 0, 1, local_rank, steps=5, warmup=3, want_cpu=False))
             line["per_config"] = per
         if rank == 0:
@@ -894,7 +914,7 @@ def main():
                        want_cpu=world == 1 and not args.no_cpu, dist=dist)
     else:
         line = run_text(args, args.config, rank, world, local_rank, steps=args.steps, warmup=args.warmup,
-                        want_cpu=world == 1 and not args.no_cpu, dist=dist)
+                        want_cpu=world == 1 and not args.no_cpu and not args.int4, dist=dist, int4=args.int4)
     if rank == 0:
         print(json.dumps(line), flush=True)
     if dist is not None:

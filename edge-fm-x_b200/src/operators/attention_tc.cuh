@@ -122,7 +122,7 @@ __global__ void __launch_bounds__(at::kThreads) seg_attention_tc_kernel(const __
     using tc::umma_desc;
     using C = Cfg<D, I8>;
     extern __shared__ unsigned char attn_tc_smem[];
-    __shared__ int s_range[2];
+    __shared__ int s_range[4];          // union of the rows' key ranges [0], [1]; largest lo [2] and smallest hi [3] of the rows
     const uint32_t raw = smem_u32(attn_tc_smem);
     const uint32_t base = (raw + 1023u) & ~1023u;
     unsigned char* base_ptr = attn_tc_smem + (base - raw);
@@ -142,6 +142,8 @@ __global__ void __launch_bounds__(at::kThreads) seg_attention_tc_kernel(const __
     if (tid == 0) {
         s_range[0] = 0x7fffffff;
         s_range[1] = 0;
+        s_range[2] = 0;
+        s_range[3] = 0x7fffffff;
         mbar_init(qfull, 1); mbar_init(kfull0, 1); mbar_init(kfull0 + 8, 1); mbar_init(vfull, 1); mbar_init(sbar, 1); mbar_init(obar, 1);
         *abort_s = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -157,12 +159,14 @@ __global__ void __launch_bounds__(at::kThreads) seg_attention_tc_kernel(const __
         hi = p.hi != nullptr ? p.hi[qi] : p.kv_offset + qi + 1;
         if (hi > p.kv_rows) hi = p.kv_rows;
         if (hf == 0 && hi > lo) { atomicMin(&s_range[0], lo); atomicMax(&s_range[1], hi); }
+        if (hf == 0) { atomicMax(&s_range[2], lo); atomicMin(&s_range[3], hi); }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = *tmem_slot;
     const int kend = s_range[1];
+    const int lo_max = s_range[2], hi_min = s_range[3];      // rows past S do not count: their output is never stored
     const int kb0 = s_range[0] == 0x7fffffff ? 0 : (s_range[0] & ~7);          // tile origin: a multiple of 8 keys (TMA alignment)
     const int ntiles = kend > kb0 ? (kend - kb0 + BN - 1) / BN : 0;
 
@@ -222,19 +226,29 @@ __global__ void __launch_bounds__(at::kThreads) seg_attention_tc_kernel(const __
         uint32_t sr[32];
         tc::tmem_ld32(tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(S_COL + hf * 32), sr);
         const int key0 = kb0 + j * BN + hf * 32;
-        float s[32];
+        float s[32];                                             // unscaled scores (-inf where the key is not visible)
         float mx = -INFINITY;
         float f2 = sl2;
         if constexpr (I8)       // one scale per 128-token block and head on either side (tiles never straddle a block)
             f2 = sl2 * p.sq[(q0 / 128) * p.q_heads + h] * p.sk[((kb0 + j * BN) / 128) * p.kv_heads + kvh];
+        // a tile every query row of the block sees completely needs no per-element visibility test
+        const bool interior = kb0 + j * BN >= lo_max && kb0 + (j + 1) * BN <= hi_min;
+        if (interior) {
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-            const int key = key0 + e;
-            const float raw = I8 ? (float)(int)sr[e] : __uint_as_float(sr[e]);
-            s[e] = (key >= lo && key < hi) ? raw * f2 : -INFINITY;
-            mx = fmaxf(mx, s[e]);
+            for (int e = 0; e < 32; ++e) {
+                s[e] = I8 ? (float)(int)sr[e] : __uint_as_float(sr[e]);
+                mx = fmaxf(mx, s[e]);
+            }
+        } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+                const int key = key0 + e;
+                const float raw = I8 ? (float)(int)sr[e] : __uint_as_float(sr[e]);
+                s[e] = (key >= lo && key < hi) ? raw : -INFINITY;
+                mx = fmaxf(mx, s[e]);
+            }
         }
-        xch[hf * BM + row] = mx;
+        xch[hf * BM + row] = mx * f2;                             // f2 > 0: the maximum commutes with the scale
         if (__syncthreads_or(*abort_s != 0)) break;             // every thread takes the same decision
         const float m_new = fmaxf(m, fmaxf(xch[row], xch[BM + row]));
         const float mb = m_new == -INFINITY ? 0.f : m_new;
@@ -244,7 +258,7 @@ __global__ void __launch_bounds__(at::kThreads) seg_attention_tc_kernel(const __
         uint32_t pk[16];
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
-            const float p0 = ex2(s[e] - mb), p1 = ex2(s[e + 1] - mb);         // exp2(-inf) = 0 for masked keys
+            const float p0 = ex2(fmaf(s[e], f2, -mb)), p1 = ex2(fmaf(s[e + 1], f2, -mb));     // exp2(-inf) = 0 for masked keys
             rs += p0 + p1;
             if constexpr (I8) {
                 const __half2 hp = __floats2half2_rn(p0, p1);

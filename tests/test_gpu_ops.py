@@ -107,7 +107,7 @@ def test_decode_attention(qh, kvh, D, kv_len, max_tokens):
 
 
 @pytest.mark.parametrize("qh,kvh,D,S,off", [(14, 2, 64, 64, 128), (12, 2, 128, 256, 512), (28, 4, 128, 200, 0),
-                                            (2, 1, 64, 1, 0), (2, 1, 64, 7, 3)])
+                                            (2, 1, 64, 1, 0), (2, 1, 64, 7, 3), (28, 4, 128, 1324, 0), (4, 2, 64, 300, 131)])
 def test_prefill_attention(qh, kvh, D, S, off):
     L = cabi.lib()
     T = off + S

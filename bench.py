@@ -9,7 +9,8 @@ sample + 255 decode steps.  N = 1 runs it on one GPU; N > 1 (one process per GPU
 runs the SAME request tensor parallel over the N ranks (heads + MLP columns + vocabulary rows; strong scaling).
   value  decode tok/s from CUDA events on the context stream around the decode phase (inputs resident);
   e2e    tokens/s of edge_fm.EdgeFM.generate() with host pixels / ids in and host ids out;
-  per_config (N = 1 only)  a short pass over configurations 0, 1, 2 and 4 on the same GPU.
+  per_config (N = 1 only)  a short pass over configurations 0, 1, 2 and 4 on the same GPU, plus configurations 1 and 3
+             with the decode pass on group-wise INT4 weights ("1_int4", "3_int4").
 --config k runs configuration k alone (0-2 and 4: replicas when N > 1).  Prints exactly one JSON line on rank 0.
 """
 from __future__ import annotations
@@ -33,7 +34,8 @@ for p in (ROOT, os.path.join(ROOT, "tests"), os.path.join(ROOT, "edge-fm-x_b200"
 METRIC, UNIT = "decode_tokens_per_second_batch1", "tok/s"
 # DRAM bytes (read + write) of the four per-layer GEMV launches of one decode step: constants taken from one ncu
 # capture per configuration (summaries under profiles/), not re-measured by this script.
-NCU_LAYER_GEMV_DRAM_BYTES = {1: 6.33984e6 + 4.758528e6 + 55.090432e6 + 77.824e3 + 27.579904e6}
+NCU_LAYER_GEMV_DRAM_BYTES = {1: 6.33984e6 + 4.758528e6 + 55.090432e6 + 77.824e3 + 27.579904e6,
+                             3: 33.099264e6 + 25.752576e6 + 271.638784e6 + 168.704e3 + 135.918848e6 + 327.168e3}
 NAMES = {0: "qwen2.5-0.5b", 1: "qwen2.5-1.5b", 2: "qwen2.5-vl-3b-llm", 3: "qwen2.5-vl-7b-llm"}
 HEADLINE = 3
 
@@ -254,11 +256,15 @@ class _Solo:
         pass
 
 
-def draw_weights_on_device(cfg, be, keep_host):
+def draw_weights_on_device(cfg, be, keep_host, int4=False):
     """Seeded weights drawn tensor by tensor on the GPU (identical on every rank: same generator, same order), handed
-    to the backend from device memory; rank 0 may keep host copies for the checkpoint the public-API engine loads."""
+    to the backend from device memory; rank 0 may keep host copies for the checkpoint the public-API engine loads.
+    int4: every linear is also quantised (group-wise, on the device) and handed over as the decode-pass checkpoint."""
     import torch
     from oracle import synth
+    if int4:
+        from oracle import int4 as int4_tools
+        linear = tuple("." + n + ".weight" for n in int4_tools.LINEARS)
     g = torch.Generator(device="cuda")
     g.manual_seed(0)
     host = {}
@@ -268,6 +274,11 @@ def draw_weights_on_device(cfg, be, keep_host):
             t += 1.0
         t = t.to(torch.bfloat16)
         be.load_weights_partial({name: t})
+        if int4 and (name.endswith(linear) or name == "lm_head.weight" or (cfg.tied and name == "model.embed_tokens.weight")):
+            q, sc = int4_tools.quantize(t)
+            stem = "lm_head" if name in ("lm_head.weight", "model.embed_tokens.weight") else name[:-len(".weight")]
+            be.load_decode_weights_int4({stem + ".qweight": int4_tools.pack(q), stem + ".scaling_factors": sc})
+            del q, sc
         if keep_host:
             host[name] = t.cpu()
         del t
@@ -295,8 +306,11 @@ def run_tp(args, rank, world, local_rank):
     vlm = vlm_request(args.config, cfg)
     ids, pos = vlm["ids"], vlm["pos"]
     max_tokens = len(ids) + gen_tokens + 8
-    want_e2e = not args.no_e2e
-    want_cpu = world == 1 and not args.no_cpu
+    int4 = bool(args.int4)
+    if int4 and world > 1:
+        raise SystemExit("--int4 runs on one GPU (the tensor-parallel decode step streams bf16 weights)")
+    want_e2e = not args.no_e2e and not int4
+    want_cpu = world == 1 and not args.no_cpu and not int4
     t_setup = time.perf_counter()
     be = cabi.Backend(cfg, max_prefill_tokens=min(2048, max_tokens), max_response_tokens=gen_tokens + 8,
                       device_id=local_rank, tp_rank=rank, tp_size=world)
@@ -304,7 +318,7 @@ def run_tp(args, rank, world, local_rank):
         box = [cabi.tp_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(box, src=0)
         be.tp_init(box[0])
-    host_w = draw_weights_on_device(cfg, be, keep_host=rank == 0 and (want_e2e or want_cpu))
+    host_w = draw_weights_on_device(cfg, be, keep_host=rank == 0 and (want_e2e or want_cpu), int4=int4)
     be.alloc_slot(0, max_tokens)
     fused = world > 1 and args.tp_exchange == "peer"
     if fused:        # the decode step's all-reduces inside the GEMVs, over peer memory (CUDA IPC handles via the host)
@@ -427,6 +441,11 @@ def run_tp(args, rank, world, local_rank):
         breakdown = {k: round(v / (4 * (Lc if k not in ("lm_head", "sampler") else 1)) * 1e3, 2) for k, v in bd.items()}
     peak, peak_kind = peaks()
     achieved = step_bytes / (step_ms * 1e-3) / 1e9
+    traffic = None
+    if world == 1 and not int4 and args.config in NCU_LAYER_GEMV_DRAM_BYTES:      # measured for the layer GEMVs, algorithmic for the rest
+        qD, kvD, H, I = cfg.q_heads * cfg.head_dim, cfg.kv_heads * cfg.head_dim, cfg.hidden, cfg.intermediate
+        layer_alg = 2 * ((qD + 2 * kvD) * H + qD * H + 3 * I * H)
+        traffic = step_bytes + cfg.num_layers * (NCU_LAYER_GEMV_DRAM_BYTES[args.config] - layer_alg)
     line = None
     if rank == 0:
         line = {"metric": METRIC, "value": dec_steps / (dec_ms / 1e3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
@@ -448,7 +467,11 @@ def run_tp(args, rank, world, local_rank):
                 "setup_s": setup_s,
                 "gpu_launches": launches, "clocks": clocks,
                 "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                             "traffic": None, "peak_kind": peak_kind,
+                             "traffic": traffic,
+                             "traffic_source": "constants from one ncu capture (dram__bytes_read+write of the per-layer GEMV launches, "
+                                               "summary under profiles/) + algorithmic bytes of lm_head, attention and vectors" if traffic else None,
+                             "peak_kind": peak_kind,
+                             "weights": "int4 group-128 (decode pass), bf16 (prefill)" if int4 else "bf16",
                              "launch": "one decode step on one rank (CUDA graph: 5 kernels per layer + lm_head + logits gather + sampler)",
                              "bytes_per_launch": step_bytes, "us_per_launch": step_ms * 1e3,
                              "frac_of_nominal_8tbs": achieved / 8000.0},
@@ -868,7 +891,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the public-API end-to-end leg (profiling runs)")
     ap.add_argument("--no-per-config", action="store_true", help="headline run without the pass over configurations 0, 1, 2, 4")
-    ap.add_argument("--int4", action="store_true", help="configurations 0-2: decode on a group-wise INT4 copy of the linears (C ABI only)")
+    ap.add_argument("--int4", action="store_true", help="one GPU: decode on a group-wise INT4 copy of the linears (C ABI only)")
     ap.add_argument("--tp-exchange", default="peer", choices=["peer", "nccl"],
                     help="config 3 on several GPUs: how the decode step sums the row-parallel partials")
     ap.add_argument("--prefill-attention", default="auto", choices=["auto", "bf16", "int8"],
@@ -897,6 +920,14 @@ def main():
                 per[str(c)] = summarise(run_text(args, c, 0, 1, local_rank, steps=2, warmup=3, want_cpu=False))
             per["1_int4"] = summarise(run_text(args, 1, 0, 1, local_rank, steps=2, warmup=3, want_cpu=False, int4=True))
             per["4"] = summarise(run_vla(args, 0, 1, local_rank, steps=5, warmup=3, want_cpu=False))
+            if not args.int4:       # the headline workload once more with the decode pass on INT4 weights
+                a4 = argparse.Namespace(**{**vars(args), "int4": True, "steps": 2, "no_e2e": True, "no_cpu": True})
+                l4 = run_tp(a4, 0, 1, local_rank)
+                per["3_int4"] = {"metric": METRIC, "value": l4["value"], "unit": UNIT, "decode_ms_per_token": l4["decode_ms_per_token"],
+                                 "hbm_frac": l4["roofline"]["frac"], "prefill_ms": l4["prefill_ms"], "vit_ms": l4["vit_ms"],
+                                 "ttft_ms": l4["ttft_ms"], "kernel_us": l4["roofline"].get("kernel_us_unoverlapped"), "steps": 2,
+                                 "workload": l4["config"]["workload"], "weights": l4["roofline"]["weights"],
+                                 "bytes_per_decode_step": l4["roofline"]["bytes_per_launch"], "tokens_head": l4["tokens_head"]}
             line["per_config"] = per
         if rank == 0:
             print(json.dumps(line), flush=True)

@@ -26,7 +26,7 @@
 namespace efm {
 
 constexpr int kW4Group = 128;     // columns per scale
-constexpr int kW4Batch = 16;      // 16-byte loads in flight per lane
+constexpr int kW4Batch = 12;      // 16-byte loads (+ their scale words) in flight per lane
 
 struct GemvW4Params {
     GemvParams g;                 // prologue / epilogue fields; g.W unused, g.N / g.K / g.n_items as for bf16
@@ -109,13 +109,18 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_w4_kernel(const GemvW4Pa
     const int n_groups = K / kW4Group;
 
     uint4 buf[kW4Batch];
+    uint32_t sbuf[kW4Batch];                                  // the chunks' scale pairs travel with them (no dependent load later)
     auto load_batch = [&](const int t0) {
         int j = t0 / cpl, jc = t0 - j * cpl;                  // one division per batch, then counters
 #pragma unroll
         for (int s = 0; s < kW4Batch; ++s) {
             if (t0 + s < total) {
                 const int c = jc * stride + wk * 32 + lane;
-                if (c < nch) buf[s] = ld_stream(p.Wq + (size_t)(ig0 + j * ig_stride) * K + (size_t)c * 16);
+                if (c < nch) {
+                    const int ig = ig0 + j * ig_stride;
+                    buf[s] = ld_stream(p.Wq + (size_t)ig * K + (size_t)c * 16);
+                    sbuf[s] = __ldg(reinterpret_cast<const uint32_t*>(p.scales) + (size_t)ig * n_groups + (c >> 3));
+                }
             }
             if (++jc == cpl) { jc = 0; ++j; }
         }
@@ -146,7 +151,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_w4_kernel(const GemvW4Pa
             const int c = jc * stride + wk * 32 + lane;
             if (++cjc == cpl) { cjc = 0; ++cj; }
             if (c < nch) {
-                const __half2 sc2 = __ldg(p.scales + (size_t)ig * n_groups + (c >> 3));
+                const __half2 sc2 = *reinterpret_cast<const __half2*>(&sbuf[s]);
                 const uint4 xa = xh[2 * c], xb = xh[2 * c + 1];
                 __half2 h0 = __float2half2_rn(0.f), h1 = __float2half2_rn(0.f);
                 w4_dot_word(buf[s].x, *reinterpret_cast<const __half2*>(&xa.x), *reinterpret_cast<const __half2*>(&xa.y), h0, h1);

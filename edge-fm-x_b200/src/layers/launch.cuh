@@ -130,9 +130,9 @@ inline int& decode_attention_max_cluster() {
 }
 
 inline AttnPlan plan_decode_attention(int max_tokens, int kv_heads, int num_sms) {
-    int n = (max_tokens + kAttnTile - 1) / kAttnTile;
+    int n = (max_tokens + 63) / 64;           // planned in units of 64 rows: as many blocks as that gives, up to the caps
     const int maxc = decode_attention_max_cluster();
-    if (maxc > 1 && n <= 2 * maxc) {          // at most two tiles per block: one cluster per kv head
+    if (maxc > 1 && n <= 2 * maxc) {          // at most one 128-row tile per block: one cluster per kv head
         int cs = 1;
         while (cs < n && cs < maxc) cs <<= 1;
         return AttnPlan{cs, (max_tokens + cs - 1) / cs, cs};

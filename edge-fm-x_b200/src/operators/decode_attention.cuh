@@ -4,9 +4,9 @@
 // captured graph serves every step.  q arrives rotated and K is cached rotated, so no RoPE here.
 //
 // Work item = (chunk of cache rows, kv head), 512 threads; it serves all `group` query heads that
-// share the kv head, so K and V are read once.  The chunk is walked in tiles of 64 rows (normally
+// share the kv head, so K and V are read once.  The chunk is walked in tiles of 128 rows (normally
 // exactly one tile):
-//   1. every thread issues its eighth of a K row and of a V row together (one DRAM round trip);
+//   1. every thread issues its eighth of two K rows and of two V rows together (one DRAM round trip);
 //   2. scores against q (fp32, shared memory), tile max, p = exp(s - max), running (m, l);
 //   3. o += P.V from shared memory, 4 channels per thread, folded over the row groups;
 //   4. (m, l, o) go to scratch; the last block to finish for a kv head (atomic ticket, nobody
@@ -22,7 +22,8 @@
 namespace efm {
 
 constexpr int kMaxGroup = 8;
-constexpr int kAttnTile = 64;
+constexpr int kAttnTile = 128;
+constexpr int kAttnRows = kAttnTile / 64;     // cache rows per thread and tile (512 threads, 8 per row)
 constexpr int kMaxSplits = 64;
 constexpr int kAttnThreads = 512;
 constexpr int kAttnWarps = kAttnThreads / 32;
@@ -104,18 +105,23 @@ __device__ __forceinline__ void decode_attention_body(const DecodeAttnParams& p,
 
     // ---- 1. K and V slices in flight together; the next tile's are issued as soon as this tile's
     //         registers are free, so that they fly during the softmax and P.V of the current tile
-    uint4 kq[QV], vq[QV];
-    auto issue_tile = [&](int t0, int skip_row) {
-        if (t0 < n && tok < min(kAttnTile, n - t0) && start + t0 + tok != skip_row) {
-            const size_t off = (size_t)(start + t0 + tok) * row_stride + (size_t)kvh * D + part * DP;
+    uint4 kq[kAttnRows][QV], vq[kAttnRows][QV];
+    // only_row >= 0: just that cache row (the one the preceding launch appended); skip_row: every row but that one
+    auto issue_tile = [&](int t0, int skip_row, int only_row) {
 #pragma unroll
-            for (int j = 0; j < QV; ++j) kq[j] = ld_cg(p.k_cache + off + j * 8);
+        for (int r = 0; r < kAttnRows; ++r) {
+            const int row = t0 + tok + 64 * r;
+            if (row < n && row < t0 + kAttnTile && start + row != skip_row && (only_row < 0 || start + row == only_row)) {
+                const size_t off = (size_t)(start + row) * row_stride + (size_t)kvh * D + part * DP;
 #pragma unroll
-            for (int j = 0; j < QV; ++j) vq[j] = ld_cg(p.v_cache + off + j * 8);
+                for (int j = 0; j < QV; ++j) kq[r][j] = ld_cg(p.k_cache + off + j * 8);
+#pragma unroll
+                for (int j = 0; j < QV; ++j) vq[r][j] = ld_cg(p.v_cache + off + j * 8);
+            }
         }
     };
     if (early) {
-        issue_tile(0, kv_len - 1);       // everything but the row the preceding launch appends
+        issue_tile(0, kv_len - 1, -1);   // everything but the row the preceding launch appends
         pdl_wait();
     }
     for (int i = tid * 2; i < G * D; i += NT * 2) {              // q: two channels per load
@@ -133,48 +139,55 @@ __device__ __forceinline__ void decode_attention_body(const DecodeAttnParams& p,
         sm.q[g][d / DP][d % DP] = q0;
         sm.q[g][(d + 1) / DP][(d + 1) % DP] = q1;
     }
-    if (early) {
-        if (0 < n && tok < min(kAttnTile, n) && start + tok == kv_len - 1) issue_tile(0, -1);
-    } else {
-        issue_tile(0, -1);
-    }
+    if (early) issue_tile(0, -1, kv_len - 1);
+    else issue_tile(0, -1, -1);
     for (int t0 = 0; t0 < n; t0 += kAttnTile) {
         const int nt = min(kAttnTile, n - t0);
-        const bool valid = tok < nt;
+        bool valid[kAttnRows];
+#pragma unroll
+        for (int r = 0; r < kAttnRows; ++r) valid[r] = tok + 64 * r < nt;
         __syncthreads();      // q staged (first tile) / previous tile's p and v fully consumed
         // ---- 2. scores ------------------------------------------------------------------------
-        float s[kMaxGroup];
+        float s[kAttnRows][kMaxGroup];
 #pragma unroll
-        for (int g = 0; g < kMaxGroup; ++g) s[g] = 0.f;
-        if (valid) {
+        for (int r = 0; r < kAttnRows; ++r)
+#pragma unroll
+            for (int g = 0; g < kMaxGroup; ++g) s[r][g] = 0.f;
+#pragma unroll
+        for (int r = 0; r < kAttnRows; ++r) {
+            if (!valid[r]) continue;
 #pragma unroll
             for (int j = 0; j < QV; ++j) {
                 float kf[8];
-                unpack8(kq[j], kf);
+                unpack8(kq[r][j], kf);
 #pragma unroll
                 for (int g = 0; g < kMaxGroup; ++g) {
                     if (g < G) {
                         const float4 qa = *reinterpret_cast<const float4*>(&sm.q[g][part][j * 8]);
                         const float4 qb = *reinterpret_cast<const float4*>(&sm.q[g][part][j * 8 + 4]);
-                        s[g] = fmaf(kf[0], qa.x, s[g]); s[g] = fmaf(kf[1], qa.y, s[g]);
-                        s[g] = fmaf(kf[2], qa.z, s[g]); s[g] = fmaf(kf[3], qa.w, s[g]);
-                        s[g] = fmaf(kf[4], qb.x, s[g]); s[g] = fmaf(kf[5], qb.y, s[g]);
-                        s[g] = fmaf(kf[6], qb.z, s[g]); s[g] = fmaf(kf[7], qb.w, s[g]);
+                        s[r][g] = fmaf(kf[0], qa.x, s[r][g]); s[r][g] = fmaf(kf[1], qa.y, s[r][g]);
+                        s[r][g] = fmaf(kf[2], qa.z, s[r][g]); s[r][g] = fmaf(kf[3], qa.w, s[r][g]);
+                        s[r][g] = fmaf(kf[4], qb.x, s[r][g]); s[r][g] = fmaf(kf[5], qb.y, s[r][g]);
+                        s[r][g] = fmaf(kf[6], qb.z, s[r][g]); s[r][g] = fmaf(kf[7], qb.w, s[r][g]);
                     }
                 }
             }
 #pragma unroll
             for (int j = 0; j < QV; ++j)
-                *reinterpret_cast<uint4*>(&sm.v[tok][part * DP + j * 8]) = vq[j];
+                *reinterpret_cast<uint4*>(&sm.v[tok + 64 * r][part * DP + j * 8]) = vq[r][j];
         }
-        issue_tile(t0 + kAttnTile, -1);
+        issue_tile(t0 + kAttnTile, -1, -1);
 #pragma unroll
         for (int g = 0; g < kMaxGroup; ++g) {
-            s[g] += __shfl_xor_sync(0xffffffffu, s[g], 1);
-            s[g] += __shfl_xor_sync(0xffffffffu, s[g], 2);
-            s[g] += __shfl_xor_sync(0xffffffffu, s[g], 4);
-            s[g] = valid ? s[g] * p.scale : -INFINITY;
-            float m = s[g];
+            float m = -INFINITY;
+#pragma unroll
+            for (int r = 0; r < kAttnRows; ++r) {
+                s[r][g] += __shfl_xor_sync(0xffffffffu, s[r][g], 1);
+                s[r][g] += __shfl_xor_sync(0xffffffffu, s[r][g], 2);
+                s[r][g] += __shfl_xor_sync(0xffffffffu, s[r][g], 4);
+                s[r][g] = valid[r] ? s[r][g] * p.scale : -INFINITY;
+                m = fmaxf(m, s[r][g]);
+            }
             m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 8));
             m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 16));
             if (lane == 0) sm.wmax[warp][g] = m;
@@ -186,9 +199,13 @@ __device__ __forceinline__ void decode_attention_body(const DecodeAttnParams& p,
                 float m_new = sm.run_m[g];
 #pragma unroll
                 for (int w = 0; w < NW; ++w) m_new = fmaxf(m_new, sm.wmax[w][g]);
-                const float pv = valid ? expf(s[g] - m_new) : 0.f;
-                if (part == 0) sm.p[g][tok] = pv;
-                float ps = pv;
+                float ps = 0.f;
+#pragma unroll
+                for (int r = 0; r < kAttnRows; ++r) {
+                    const float pv = valid[r] ? expf(s[r][g] - m_new) : 0.f;
+                    if (part == 0 && tok + 64 * r < kAttnTile) sm.p[g][tok + 64 * r] = pv;
+                    ps += pv;
+                }
                 ps += __shfl_xor_sync(0xffffffffu, ps, 8);
                 ps += __shfl_xor_sync(0xffffffffu, ps, 16);
                 if (lane == 0) sm.wsum[warp][g] = ps;

@@ -26,7 +26,9 @@
 namespace efm {
 
 constexpr int kW4Group = 128;     // columns per scale
-constexpr int kW4Batch = 12;      // 16-byte loads (+ their scale words) in flight per lane
+constexpr int kW4Batch = 6;       // 16-byte loads (+ their scale words) per buffer; two buffers alternate, so the next
+                                  // batch is in flight while this one is converted (the conversion costs about as
+                                  // much time as the loads' latency, unlike the bf16 kernel's)
 
 struct GemvW4Params {
     GemvParams g;                 // prologue / epilogue fields; g.W unused, g.N / g.K / g.n_items as for bf16
@@ -59,16 +61,20 @@ __device__ __forceinline__ void w4_dot_word(uint32_t w, __half2 x02, __half2 x13
     acc1 = __hfma2(q1b, x13, acc1);
 }
 
-// fp32 activations [K] (staged by gemv_stage) -> fp16 pairs in conversion order: per 16-column chunk two uint4,
-// word 2j = (x[4j], x[4j+2]), word 2j+1 = (x[4j+1], x[4j+3]).
+// fp32 activations [K] (staged by gemv_stage) -> fp16 pairs in conversion order: per 16-column chunk c two uint4,
+// words (x[4j], x[4j+2]), (x[4j+1], x[4j+3]) for j = 0..3.  The first uint4 of every chunk (j = 0, 1) lives in
+// xh[c], the second (j = 2, 3) in xh[K / 16 + c]: consecutive lanes read consecutive 16-byte words (no bank conflicts).
 __device__ __forceinline__ void w4_permute_activations(const float* xs, uint4* xh, int K) {
     const int nq = K >> 2;      // groups of 4 columns
+    const int nch = K >> 4;
     uint32_t* out = reinterpret_cast<uint32_t*>(xh);
     for (int q = threadIdx.x; q < nq; q += blockDim.x) {
         const float4 v = reinterpret_cast<const float4*>(xs)[q];
         const __half2 a = __floats2half2_rn(v.x, v.z), b = __floats2half2_rn(v.y, v.w);
-        out[2 * q] = *reinterpret_cast<const uint32_t*>(&a);
-        out[2 * q + 1] = *reinterpret_cast<const uint32_t*>(&b);
+        const int c = q >> 2, j = q & 3;
+        uint32_t* dst = out + ((j >> 1) * nch + c) * 4 + (j & 1) * 2;
+        dst[0] = *reinterpret_cast<const uint32_t*>(&a);
+        dst[1] = *reinterpret_cast<const uint32_t*>(&b);
     }
 }
 
@@ -108,9 +114,10 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_w4_kernel(const GemvW4Pa
     const int total = n_my * cpl;                             // (row pair, chunk slot) slots of this lane
     const int n_groups = K / kW4Group;
 
-    uint4 buf[kW4Batch];
-    uint32_t sbuf[kW4Batch];                                  // the chunks' scale pairs travel with them (no dependent load later)
-    auto load_batch = [&](const int t0) {
+    uint4 buf_a[kW4Batch], buf_b[kW4Batch];
+    uint32_t sc_a[kW4Batch], sc_b[kW4Batch];                  // the chunks' scale pairs travel with them (no dependent load later)
+    auto load_batch = [&](uint4 (&buf)[kW4Batch], uint32_t (&sbuf)[kW4Batch], const int t0) {
+        if (t0 >= total) return;
         int j = t0 / cpl, jc = t0 - j * cpl;                  // one division per batch, then counters
 #pragma unroll
         for (int s = 0; s < kW4Batch; ++s) {
@@ -125,7 +132,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_w4_kernel(const GemvW4Pa
             if (++jc == cpl) { jc = 0; ++j; }
         }
     };
-    load_batch(0);                                            // weights do not depend on the previous kernel
+    load_batch(buf_a, sc_a, 0);                               // weights do not depend on the previous kernel
     if (g.prologue != kProPlain) {
         uint4* gs = reinterpret_cast<uint4*>(gemv_smem + xbytes);
         for (int c = tid; c < (K >> 3); c += kGemvThreads) gs[c] = ld_cached(g.norm_w + (size_t)c * 8);
@@ -141,8 +148,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_w4_kernel(const GemvW4Pa
     float acc0 = 0.f, acc1 = 0.f;
     int parity = 0;
     int cj = 0, cjc = 0;                                      // compute-side counters: row pair index, chunk slot
-    for (int t0 = 0; t0 < total; t0 += kW4Batch) {
-        if (t0 > 0) load_batch(t0);
+    auto compute_batch = [&](const uint4 (&buf)[kW4Batch], const uint32_t (&sbuf)[kW4Batch], const int t0) {
 #pragma unroll
         for (int s = 0; s < kW4Batch; ++s) {
             if (t0 + s >= total) break;
@@ -152,7 +158,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_w4_kernel(const GemvW4Pa
             if (++cjc == cpl) { cjc = 0; ++cj; }
             if (c < nch) {
                 const __half2 sc2 = *reinterpret_cast<const __half2*>(&sbuf[s]);
-                const uint4 xa = xh[2 * c], xb = xh[2 * c + 1];
+                const uint4 xa = xh[c], xb = xh[nch + c];
                 __half2 h0 = __float2half2_rn(0.f), h1 = __float2half2_rn(0.f);
                 w4_dot_word(buf[s].x, *reinterpret_cast<const __half2*>(&xa.x), *reinterpret_cast<const __half2*>(&xa.y), h0, h1);
                 w4_dot_word(buf[s].y, *reinterpret_cast<const __half2*>(&xa.z), *reinterpret_cast<const __half2*>(&xa.w), h0, h1);
@@ -188,6 +194,12 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_w4_kernel(const GemvW4Pa
                 }
             }
         }
+    };
+    for (int t0 = 0; t0 < total; t0 += 2 * kW4Batch) {
+        load_batch(buf_b, sc_b, t0 + kW4Batch);
+        compute_batch(buf_a, sc_a, t0);
+        load_batch(buf_a, sc_a, t0 + 2 * kW4Batch);
+        compute_batch(buf_b, sc_b, t0 + kW4Batch);
     }
     if constexpr (EPI == Epi::Logits) gemv_publish_best(g, best_v, best_i, bv, bi);
 }

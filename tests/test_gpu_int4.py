@@ -32,7 +32,9 @@ def oracle_run(cfg, w, deq, prompt, steps, forced, pos=None, last=None):
     (dict(num_layers=3, hidden=384, q_heads=6, kv_heads=2, intermediate=1152, vocab=2000, tied=False), True),
     (dict(num_layers=2, hidden=512, q_heads=4, kv_heads=2, intermediate=640, vocab=1200, tied=True,
           mrope_section=[16, 24, 24], model_type="qwen2_5_vl"), False),
-])
+    # one layer at the 7B shape's widths (K = 3584 / 18944, head_dim 128): the sizes at which the kernel is bandwidth-relevant
+    (dict(num_layers=1, hidden=3584, q_heads=28, kv_heads=4, intermediate=18944, vocab=2048, tied=False), True),
+], ids=["h256", "h384-untied", "h512-mrope", "layer_7b_width"])
 def test_int4_decode_against_the_oracle(kw, lm_head):
     cfg = synth.tiny_config(**kw)
     w = synth.make_weights(cfg, seed=12)

@@ -546,9 +546,11 @@ efm_status finish_w4_linear(efm_b200_ctx* c, W4Linear& lin, int n_src, const int
     for (int i = 0; i < n_src; ++i) total_rows += rows[i];
     lin.n_items = total_rows / 2;
     lin.K = K;
-    EFM_CK(c, dev_alloc(c, &lin.q, (size_t)lin.n_items * K, false));
+    if (K % kW4Group != 0) return fail(c, EFM_ERR_UNSUPPORTED, std::string("INT4 decode weights need in_features % 128 == 0: ") + what);
+    const size_t padded = (size_t)((lin.n_items + 7) / 8) * 8;          // whole 16-row tiles; the padding holds zeros
+    EFM_CK(c, dev_alloc(c, &lin.q, padded * K, false));
     __half2* s = nullptr;
-    EFM_CK(c, dev_alloc(c, &s, (size_t)lin.n_items * (K / kW4Group), false));
+    EFM_CK(c, dev_alloc(c, &s, padded * (K / kW4Group), false));
     lin.s = s;
     W4RepackParams p{};
     int row0 = 0;

@@ -83,17 +83,17 @@ inline void launch_gemv(Launcher& L, const GemvParams& p, int num_sms) {
     L.launch(gemv_kernel<EPI>, dim3(num_sms), dim3(kGemvThreads), gemv_smem_bytes(p.K), p, ks);
 }
 
-// INT4 form: the K split balances (row pairs per group) x (chunk slots per lane), as above with 16-byte chunks of
-// 16 columns x 2 rows.
+// INT4 form: `ks` warps share one 16-row tile (8 row pairs), the 128-column groups of K go round-robin over them;
+// the split balances (tiles per warp group) x (groups per warp).
 inline int plan_gemv_w4_ksplit(int n_items, int K, int n_blocks) {
-    const int nch = K / 16;
+    const int n_groups = K / 128, tiles = (n_items + 7) / 8;
     int best = 1;
     long best_cost = -1;
     for (int ks = 1; ks <= kGemvWarps; ks *= 2) {
         const long slots = (long)n_blocks * (kGemvWarps / ks);
-        const long waves = (n_items + slots - 1) / slots;
-        const long cpl = (nch + 32 * ks - 1) / (32 * ks);
-        const long cost = waves * cpl * 8 + ks;
+        const long waves = (tiles + slots - 1) / slots;
+        const long gpw = (n_groups + ks - 1) / ks;
+        const long cost = waves * gpw * 4 + ks;
         if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = ks; }
     }
     return best;

@@ -309,7 +309,7 @@ static void qwen_decode_step_tp(efm_b200_ctx& c, KvSlot& slot, Launcher& L) {
 void launch_w4_repack(Launcher& L, const W4RepackParams& p) {
     const bool pdl = L.pdl;
     L.pdl = false;
-    L.launch(w4_repack_kernel<0>, dim3(p.n_items), dim3(256), 0, p);
+    L.launch(w4_repack_kernel<0>, dim3(((p.n_items + 7) / 8) * 8), dim3(256), 0, p);
     L.pdl = pdl;
 }
 
@@ -429,6 +429,12 @@ static int min_kb_per_split() {
     return v;
 }
 
+// EFM_B200_GEMM_TAIL=0 switches the tail split off (for A/B timing)
+static bool tail_split_enabled() {
+    static const bool on = [] { const char* e = std::getenv("EFM_B200_GEMM_TAIL"); return e == nullptr || e[0] != '0'; }();
+    return on;
+}
+
 template <GemmEpi EPI>
 static void launch_gemm(Launcher& L, const GemmParams& p, int* error_word = nullptr) {
     static bool attr_set = false;
@@ -469,6 +475,44 @@ static void launch_gemm(Launcher& L, const GemmParams& p, int* error_word = null
             L.launch(gemm_splitk_finish_kernel<EPI>, dim3(fin), dim3(256), 0, (const float*)L.gemm_ws, splits, p);
             L.pdl = pdl;
             return;
+        }
+    }
+    // Tail split: a few tiles more than a multiple of the SM count would cost a whole extra round in which most SMs
+    // idle (1324 x 3584 outputs = 154 tiles on 148 SMs: two rounds for 1.04 rounds of work).  The full rounds run as
+    // they are; the remaining tiles are cut along K into as many slices as fill the GPU once (compact fp32 slots in
+    // the workspace) and a small kernel sums the slices in order with the epilogue.  Worth it only when a tile's K
+    // loop is long against the two extra launches (about 12 us).
+    if constexpr (EPI == GemmEpi::Bf16Bias || EPI == GemmEpi::Residual || EPI == GemmEpi::F32) {
+        const int P = L.num_sms, rounds = tiles / P, rem = tiles % P;
+        const int KB = (p.K + tc::BK - 1) / tc::BK;
+        if (tail_split_enabled() && L.gemm_ws != nullptr && rounds >= 1 && rem > 0 && rem * 2 <= P && (p.N & 3) == 0 && p.kb_per_split == 0 &&
+            p.tile_count == 0) {
+            int splits = std::min(P / rem, KB / min_kb_per_split());
+            const int per = splits >= 2 ? (KB + splits - 1) / splits : KB;
+            splits = (KB + per - 1) / per;
+            const double tile_us = KB * 0.45, gain_us = tile_us * (1.0 - 1.0 / std::max(1, splits)) - 12.0;
+            if (splits >= 2 && gain_us > 5.0 && (size_t)splits * rem * tc::BM * tc::BN <= L.gemm_ws_floats) {
+                GemmParams full = p;
+                full.tile_begin = 0;
+                full.tile_count = rounds * P;
+                L.launch(gemm_tc_kernel<EPI>, dim3(P), block, tc::SMEM_BYTES, ma, mb, full, error_word);
+                GemmParams q = p;
+                q.tile_begin = rounds * P;
+                q.tile_count = rem;
+                q.kb_per_split = per;
+                q.Cf = L.gemm_ws;
+                q.bias = nullptr;
+                static bool attr_f32 = false;
+                if (!attr_f32) {
+                    cudaFuncSetAttribute(gemm_tc_kernel<GemmEpi::F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc::SMEM_BYTES);
+                    attr_f32 = true;
+                }
+                L.launch(gemm_tc_kernel<GemmEpi::F32>, dim3(std::min(P, rem * splits)), block, tc::SMEM_BYTES, ma, mb, q, error_word);
+                const int per_tile = std::max(1, std::min(32, (P * 4) / rem));
+                L.launch(gemm_tail_finish_kernel<EPI>, dim3(per_tile, rem), dim3(256), 0, (const float*)L.gemm_ws, splits, rounds * P, rem, p);
+                L.pdl = pdl;
+                return;
+            }
         }
     }
     L.launch(gemm_tc_kernel<EPI>, dim3(std::min(L.num_sms, tiles)), block, tc::SMEM_BYTES, ma, mb, p, error_word);

@@ -35,6 +35,10 @@ struct GemmParams {
     int lda = 0;              // row stride of A in elements (0: K)
     int kb_per_split = 0;     // split-K: split z covers 64-wide k-blocks [z * kb_per_split, (z+1) * kb_per_split) and
                               // writes its raw fp32 partial tile to Cf + z * M * N (F32 epilogue, no bias); 0: no split
+    int tile_begin = 0;       // this launch covers the output tiles [tile_begin, tile_begin + tile_count) of the
+    int tile_count = 0;       // m-fastest tile order (0: all of them).  With kb_per_split > 0 and tile_count > 0 the
+                              // partial of (split z, tile t) goes to the compact slot Cf + (z * tile_count + t -
+                              // tile_begin) * 128 * 256, row-major inside the tile ("tail split", see the launcher)
 };
 
 namespace tc {
@@ -138,7 +142,9 @@ __global__ void __launch_bounds__(tc::kThreads) gemm_tc_kernel(const __grid_cons
     const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
     const int KB_all = (p.K + BK - 1) / BK;
     const int splits = p.kb_per_split > 0 ? (KB_all + p.kb_per_split - 1) / p.kb_per_split : 1;
-    const int n_items = tiles_m * tiles_n * splits;                   // item = (split, n tile, m tile), m fastest
+    const int n_tiles = p.tile_count > 0 ? p.tile_count : tiles_m * tiles_n;
+    const int n_items = n_tiles * splits;                             // item = (split, n tile, m tile), m fastest
+    const bool compact = p.tile_count > 0 && p.kb_per_split > 0;      // partial tiles in compact slots
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
@@ -156,9 +162,9 @@ __global__ void __launch_bounds__(tc::kThreads) gemm_tc_kernel(const __grid_cons
     const uint32_t tmem = *tmem_slot;
 
     auto item_coords = [&](int item, int& m0, int& n0, int& kb0, int& kb1, int& z) {
-        const int mt = item % tiles_m, rest = item / tiles_m;
-        const int nt = rest % tiles_n;
-        z = rest / tiles_n;
+        z = item / n_tiles;
+        const int tile = p.tile_begin + (item - z * n_tiles);
+        const int mt = tile % tiles_m, nt = tile / tiles_m;
         m0 = mt * BM;
         n0 = nt * BN;
         kb0 = p.kb_per_split > 0 ? z * p.kb_per_split : 0;
@@ -229,7 +235,8 @@ __global__ void __launch_bounds__(tc::kThreads) gemm_tc_kernel(const __grid_cons
             const int ldc = EPI == GemmEpi::SwiGlu ? (p.N >> 1) : p.N;         // output row length
             const int nc0 = EPI == GemmEpi::SwiGlu ? (n0 >> 1) : n0;           // first output column of the tile
             const bool vec = (ldc & 3) == 0;
-            const size_t split_off = p.kb_per_split > 0 ? (size_t)z * (size_t)p.M * (size_t)p.N : 0;
+            const size_t split_off = compact ? (size_t)item * (size_t)(BM * BN)
+                                             : (p.kb_per_split > 0 ? (size_t)z * (size_t)p.M * (size_t)p.N : 0);
 #pragma unroll 1
             for (int c0 = 0; c0 < OUT_COLS; c0 += 32) {
                 if (nc0 + c0 >= ldc && c0 > 0) break;                          // whole chunk outside the matrix
@@ -295,7 +302,10 @@ __global__ void __launch_bounds__(tc::kThreads) gemm_tc_kernel(const __grid_cons
                     const int n = nc0 + c0 + cl;
                     if (m >= p.M || n >= ldc) continue;
                     const float4 v = *reinterpret_cast<const float4*>(stage + r * LD + cl);
-                    const size_t off = (size_t)m * ldc + n;
+                    size_t off = (size_t)m * ldc + n;
+                    if constexpr (EPI == GemmEpi::F32) {
+                        if (compact) off = (size_t)(m - m0) * BN + (size_t)(n - n0);      // slot-local (item = z * n_tiles + t)
+                    }
                     if (vec && n + 3 < ldc) {
                         if constexpr (EPI == GemmEpi::F32) {
                             *reinterpret_cast<float4*>(p.Cf + split_off + off) = v;
@@ -382,6 +392,42 @@ __global__ void __launch_bounds__(256) gemm_splitk_finish_kernel(const float* __
             *reinterpret_cast<float4*>(p.Cf + i * 4) = make_float4(o.x + a.x, o.y + a.y, o.z + a.z, o.w + a.w);
         } else {
             *reinterpret_cast<uint2*>(p.C + i * 4) = make_uint2(pack_bf16(a.x, a.y), pack_bf16(a.z, a.w));
+        }
+    }
+}
+
+// Second half of a tail split: the last tiles of a product whose tile count is a little more than a multiple of the
+// SM count were computed as `splits` K-slices each (compact fp32 slots, see GemmParams::tile_count); sum them in
+// split order and apply the epilogue.  grid = (blocks per tile, tile_count).
+template <GemmEpi EPI>
+__global__ void __launch_bounds__(256) gemm_tail_finish_kernel(const float* __restrict__ ws, int splits, int tile_begin, int tile_count,
+                                                               const GemmParams p) {
+    constexpr int BM = tc::BM, BN = tc::BN;
+    const int tiles_m = (p.M + BM - 1) / BM;
+    const int t = blockIdx.y, tile = tile_begin + t;
+    const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+    for (int i = blockIdx.x * 256 + threadIdx.x; i < BM * BN / 4; i += gridDim.x * 256) {
+        const int row = i / (BN / 4), c = (i - row * (BN / 4)) * 4;
+        const int m = m0 + row, n = n0 + c;
+        if (m >= p.M || n >= p.N) continue;                  // N % 4 == 0 (checked by the launcher)
+        const float* src = ws + ((size_t)t * BM + row) * BN + c;
+        float4 a = *reinterpret_cast<const float4*>(src);
+        for (int z = 1; z < splits; ++z) {
+            const float4 b = *reinterpret_cast<const float4*>(src + (size_t)z * tile_count * (BM * BN));
+            a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+        }
+        if (p.bias != nullptr) {
+            a.x += __bfloat162float(p.bias[n]); a.y += __bfloat162float(p.bias[n + 1]);
+            a.z += __bfloat162float(p.bias[n + 2]); a.w += __bfloat162float(p.bias[n + 3]);
+        }
+        const size_t off = (size_t)m * p.N + n;
+        if constexpr (EPI == GemmEpi::F32) {
+            *reinterpret_cast<float4*>(p.Cf + off) = a;
+        } else if constexpr (EPI == GemmEpi::Residual) {
+            const float4 o = *reinterpret_cast<const float4*>(p.Cf + off);
+            *reinterpret_cast<float4*>(p.Cf + off) = make_float4(o.x + a.x, o.y + a.y, o.z + a.z, o.w + a.w);
+        } else {
+            *reinterpret_cast<uint2*>(p.C + off) = make_uint2(pack_bf16(a.x, a.y), pack_bf16(a.z, a.w));
         }
     }
 }

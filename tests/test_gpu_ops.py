@@ -62,8 +62,10 @@ def test_gemv_rmsnorm_prologue_and_residual_epilogue(n, k):
     assert torch.allclose(r, r0 + refb, atol=1e-4, rtol=1e-4)
 
 
+# the last three have a few more output tiles than a multiple of the SM count: their tail tiles are split along K
 @pytest.mark.parametrize("m,n,k", [(64, 1152, 896), (256, 2048, 1536), (320, 2048, 2048), (1324, 4608, 3584),
-                                   (200, 896, 4864), (1, 256, 128), (131, 130, 96)])
+                                   (200, 896, 4864), (1, 256, 128), (131, 130, 96),
+                                   (1324, 3584, 3584), (1300, 3600, 4096), (1323, 3584, 18944)])
 def test_prefill_gemm(m, n, k):
     L = cabi.lib()
     x, w, b = bf16(m, k, seed=6), bf16(n, k, scale=0.02, seed=7), bf16(n, scale=0.02, seed=8)

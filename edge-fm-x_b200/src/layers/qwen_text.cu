@@ -735,7 +735,7 @@ void qwen_prefill_chunk(efm_b200_ctx& c, KvSlot& slot, int S, int kv_offset, int
             GemmParams g{c.norm, w.qkv, w.qkv_bias, c.qkv, nullptr, S, QD + 2 * KVD, H};
             launch_gemm<GemmEpi::Bf16Bias>(L, g, &c.state->error);
         }
-        L.launch(rope_scatter_kernel, dim3(S, d.q_heads + 2 * d.kv_heads), dim3(D / 2), 0,
+        L.launch(rope_scatter_kernel, dim3(S), dim3(256), 0,
                  (const __nv_bfloat16*)c.qkv, c.qbuf, slot.k[l], slot.v[l], (const float*)c.inv_freq,
                  (const int32_t*)c.pos3, S, d.q_heads, d.kv_heads, D, kv_offset, d.use_mrope, d.mrope_section[0],
                  d.mrope_section[0] + d.mrope_section[1]);

@@ -263,14 +263,20 @@ __global__ void __launch_bounds__(tc::kThreads) gemm_tc_kernel(const __grid_cons
                     tmem_ld32(acc + (uint32_t)(blk * 128 + 64 + cc), ru);
                     const int n = n0 + blk * 128 + cc;                        // gate column in the fused output
                     const bool in = n0 + blk * 128 + 128 <= p.N;
+                    // one gate and one up bias element per lane, handed round by shuffles (64 loads per thread otherwise)
+                    const bool has_bias = p.bias != nullptr && in;
+                    const float bias_g = has_bias ? __bfloat162float(p.bias[n + lane]) : 0.f;
+                    const float bias_u = has_bias ? __bfloat162float(p.bias[n + 64 + lane]) : 0.f;
 #pragma unroll
                     for (int e = 0; e < 32; ++e) {
                         float g = __uint_as_float(rg[e]), u = __uint_as_float(ru[e]);
-                        if (p.bias != nullptr && in) {
-                            g += __bfloat162float(p.bias[n + e]);
-                            u += __bfloat162float(p.bias[n + 64 + e]);
+                        if (has_bias) {
+                            g += __shfl_sync(0xffffffffu, bias_g, e);
+                            u += __shfl_sync(0xffffffffu, bias_u, e);
                         }
-                        o[e] = g / (1.0f + __expf(-g)) * u;
+                        // four epilogue warps drain a tile while one warp feeds the tensor cores: their issue slots are
+                        // the limit when K is short, hence the approximate reciprocal instead of an IEEE division
+                        o[e] = __fdividef(g, 1.0f + __expf(-g)) * u;
                     }
                 } else {
                     uint32_t r[32];

@@ -36,7 +36,8 @@
 namespace efm {
 
 constexpr int kW4Group = 128;     // columns per scale = two 64-column chunks
-constexpr int kW4Batch = 6;       // groups in flight per lane (12 x 16-byte loads)
+constexpr int kW4Batch = 3;       // groups per load buffer (2 x 16 bytes + the scale word each); two buffers alternate, so
+                                  // the next batch is in flight while this one goes through the tensor cores
 
 struct GemvW4Params {
     GemvParams g;                 // prologue / epilogue fields; g.W unused, g.N / g.K / g.n_items as for bf16
@@ -125,9 +126,10 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_w4_kernel(const GemvW4Pa
     const int total = n_my * gpw;                             // (tile, group) slots of this warp
     const size_t tile_bytes = (size_t)K * 8;
 
-    uint4 buf[kW4Batch][2];
-    uint32_t sbuf[kW4Batch];                                  // the groups' scale pairs travel with them
-    auto load_batch = [&](const int t0) {
+    uint4 buf_a[kW4Batch][2], buf_b[kW4Batch][2];
+    uint32_t sc_a[kW4Batch], sc_b[kW4Batch];                  // the groups' scale pairs travel with them
+    auto load_batch = [&](uint4 (&buf)[kW4Batch][2], uint32_t (&sbuf)[kW4Batch], const int t0) {
+        if (t0 >= total) return;
         int j = t0 / gpw, jg = t0 - j * gpw;                  // one division per batch, then counters
 #pragma unroll
         for (int s = 0; s < kW4Batch; ++s) {
@@ -144,7 +146,8 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_w4_kernel(const GemvW4Pa
             if (++jg == gpw) { jg = 0; ++j; }
         }
     };
-    load_batch(0);                                            // weights do not depend on the previous kernel
+    load_batch(buf_a, sc_a, 0);                               // weights do not depend on the previous kernel
+    load_batch(buf_b, sc_b, kW4Batch);
     if (g.prologue != kProPlain) {
         uint4* gs = reinterpret_cast<uint4*>(gemv_smem + xbytes);
         for (int c = tid; c < (K >> 3); c += kGemvThreads) gs[c] = ld_cached(g.norm_w + (size_t)c * 8);
@@ -162,8 +165,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_w4_kernel(const GemvW4Pa
     float res0 = 0.f, res1 = 0.f;
     int parity = 0;
     int cj = 0, cjg = 0;                                      // compute-side counters: tile index, group slot
-    for (int t0 = 0; t0 < total; t0 += kW4Batch) {
-        if (t0 > 0) load_batch(t0);
+    auto compute_batch = [&](const uint4 (&buf)[kW4Batch][2], const uint32_t (&sbuf)[kW4Batch], const int t0) {
 #pragma unroll
         for (int s = 0; s < kW4Batch; ++s) {
             if (t0 + s >= total) break;                       // warp-uniform, like every branch around the mma
@@ -172,20 +174,21 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_w4_kernel(const GemvW4Pa
             const int grp = jg * ks + wk;
             if (++cjg == gpw) { cjg = 0; ++cj; }
             if (grp < n_groups) {
-                float c[4] = {0.f, 0.f, 0.f, 0.f};
+                float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};      // two chains: the mma latency overlaps
                 const uint4* xp = xh + ((size_t)(2 * grp) * 4 + tq) * 2;
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const uint4 xa = xp[h * 8], xb = xp[h * 8 + 1];
-                    w4_mma_word(buf[s][h].x, xa.x, xa.y, c);
-                    w4_mma_word(buf[s][h].y, xa.z, xa.w, c);
-                    w4_mma_word(buf[s][h].z, xb.x, xb.y, c);
-                    w4_mma_word(buf[s][h].w, xb.z, xb.w, c);
-                }
+                const uint4 xa0 = xp[0], xb0 = xp[1], xa1 = xp[8], xb1 = xp[9];
+                w4_mma_word(buf[s][0].x, xa0.x, xa0.y, c0);
+                w4_mma_word(buf[s][1].x, xa1.x, xa1.y, c1);
+                w4_mma_word(buf[s][0].y, xa0.z, xa0.w, c0);
+                w4_mma_word(buf[s][1].y, xa1.z, xa1.w, c1);
+                w4_mma_word(buf[s][0].z, xb0.x, xb0.y, c0);
+                w4_mma_word(buf[s][1].z, xb1.x, xb1.y, c1);
+                w4_mma_word(buf[s][0].w, xb0.z, xb0.w, c0);
+                w4_mma_word(buf[s][1].w, xb1.z, xb1.w, c1);
                 const float sxg = sx[grp];
                 const float2 sf = __half22float2(*reinterpret_cast<const __half2*>(&sbuf[s]));
-                res0 = fmaf(sf.x, fmaf(-1032.f, sxg, c[0]), res0);
-                res1 = fmaf(sf.y, fmaf(c[2], 0.0625f, -72.f * sxg), res1);
+                res0 = fmaf(sf.x, fmaf(-1032.f, sxg, c0[0] + c1[0]), res0);
+                res1 = fmaf(sf.y, fmaf(c0[2] + c1[2], 0.0625f, -72.f * sxg), res1);
             }
             if (jg != gpw - 1) continue;
             // tile complete for this warp: lanes with t == 0 hold the partial results of item 8 tile + g
@@ -214,6 +217,12 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_w4_kernel(const GemvW4Pa
                 }
             }
         }
+    };
+    for (int t0 = 0; t0 < total; t0 += 2 * kW4Batch) {
+        compute_batch(buf_a, sc_a, t0);
+        load_batch(buf_a, sc_a, t0 + 2 * kW4Batch);
+        compute_batch(buf_b, sc_b, t0 + kW4Batch);
+        load_batch(buf_b, sc_b, t0 + 3 * kW4Batch);
     }
     if constexpr (EPI == Epi::Logits) gemv_publish_best(g, best_v, best_i, bv, bi);
 }

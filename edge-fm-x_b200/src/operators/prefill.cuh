@@ -76,39 +76,41 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float* __restri
 // scatter: q -> [S, q_heads, D]; rotated k and raw v -> cache rows kv_offset + s.
 // Convention of the reference: angle = pos * theta^(-2d/D); o[d] = x0 cos - x1 sin,
 // o[d+D/2] = x1 cos + x0 sin (src/operators/attention_op.cu:327-371); M-RoPE picks the position
-// row by rotary-pair section (src/layers/attention.cu:17-72).  Grid (S, q+2kv), block D/2.
-__global__ void rope_scatter_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ q_out,
-                                    __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
-                                    const float* __restrict__ inv_freq, const int32_t* __restrict__ pos3,
-                                    int S, int q_heads, int kv_heads, int D, int kv_offset, int use_mrope,
-                                    int sec0, int sec1) {
-    const int s = blockIdx.x, head = blockIdx.y, d = threadIdx.x, half = D >> 1;
-    if (d >= half) return;
-    const int width = (q_heads + 2 * kv_heads) * D;
-    const __nv_bfloat16* src = qkv + (size_t)s * width + (size_t)head * D;
-    const float x0 = __bfloat162float(src[d]), x1 = __bfloat162float(src[d + half]);
-    const size_t row = (size_t)(kv_offset + s) * kv_heads * D;
-    if (head < q_heads + kv_heads) {
+// row by rotary-pair section (src/layers/attention.cu:17-72).  One block per row: the row's D/2 (sin, cos) pairs are
+// computed once and shared by all heads; two channels per thread and access.  head_dim <= 256, even D/2.
+__global__ void __launch_bounds__(256) rope_scatter_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ q_out,
+                                                           __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
+                                                           const float* __restrict__ inv_freq, const int32_t* __restrict__ pos3,
+                                                           int S, int q_heads, int kv_heads, int D, int kv_offset, int use_mrope,
+                                                           int sec0, int sec1) {
+    __shared__ float s_sn[128], s_cs[128];
+    const int s = blockIdx.x, half = D >> 1;
+    for (int d = threadIdx.x; d < half; d += 256) {
         int pos;
         if (use_mrope) pos = pos3[(d < sec0 ? 0 : (d < sec1 ? 1 : 2)) * S + s];
         else pos = kv_offset + s;
-        float sn, cs;
-        sincosf((float)pos * inv_freq[d], &sn, &cs);
-        const __nv_bfloat16 o0 = __float2bfloat16_rn(x0 * cs - x1 * sn);
-        const __nv_bfloat16 o1 = __float2bfloat16_rn(x1 * cs + x0 * sn);
-        if (head < q_heads) {
-            __nv_bfloat16* dst = q_out + ((size_t)s * q_heads + head) * D;
-            dst[d] = o0;
-            dst[d + half] = o1;
+        sincosf((float)pos * inv_freq[d], &s_sn[d], &s_cs[d]);
+    }
+    __syncthreads();
+    const int width = (q_heads + 2 * kv_heads) * D, hp = half >> 1;
+    const size_t row = (size_t)(kv_offset + s) * kv_heads * D;
+    for (int i = threadIdx.x; i < (q_heads + 2 * kv_heads) * hp; i += 256) {
+        const int head = i / hp, d = (i - head * hp) * 2;
+        const __nv_bfloat16* src = qkv + (size_t)s * width + (size_t)head * D;
+        const uint32_t lo = *reinterpret_cast<const uint32_t*>(src + d), hi = *reinterpret_cast<const uint32_t*>(src + d + half);
+        if (head < q_heads + kv_heads) {
+            const float a0 = bf16lo(lo), a1 = bf16hi(lo), b0 = bf16lo(hi), b1 = bf16hi(hi);
+            const uint32_t o_lo = pack_bf16(a0 * s_cs[d] - b0 * s_sn[d], a1 * s_cs[d + 1] - b1 * s_sn[d + 1]);
+            const uint32_t o_hi = pack_bf16(b0 * s_cs[d] + a0 * s_sn[d], b1 * s_cs[d + 1] + a1 * s_sn[d + 1]);
+            __nv_bfloat16* dst = head < q_heads ? q_out + ((size_t)s * q_heads + head) * D
+                                                : k_cache + row + (size_t)(head - q_heads) * D;
+            *reinterpret_cast<uint32_t*>(dst + d) = o_lo;
+            *reinterpret_cast<uint32_t*>(dst + d + half) = o_hi;
         } else {
-            __nv_bfloat16* dst = k_cache + row + (size_t)(head - q_heads) * D;
-            dst[d] = o0;
-            dst[d + half] = o1;
+            __nv_bfloat16* dst = v_cache + row + (size_t)(head - q_heads - kv_heads) * D;
+            *reinterpret_cast<uint32_t*>(dst + d) = lo;
+            *reinterpret_cast<uint32_t*>(dst + d + half) = hi;
         }
-    } else {
-        __nv_bfloat16* dst = v_cache + row + (size_t)(head - q_heads - kv_heads) * D;
-        dst[d] = src[d];
-        dst[d + half] = src[d + half];
     }
 }
 

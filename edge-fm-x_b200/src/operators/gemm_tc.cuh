@@ -3,15 +3,17 @@
 // (reference: cublasLtMatmul / CUTLASS sm80 prefill linears, src/operators/linear_impl.cu:457-469,482-706;
 //  the reference has no sm_100 kernel.)
 //
-// Persistent blocks (one per SM, 192 threads) walk the 128 x 256 output tiles (and K splits) round-robin:
+// Persistent blocks (one per SM, 320 threads) walk the 128 x 256 output tiles (and K splits) round-robin:
 //   warp 0      one lane issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle, no multicast) of
 //               a 128 x 64 A tile and a 256 x 64 B tile per stage into a 4-stage ring;
 //   warp 1      owns all 512 TMEM columns = two 128 x 256 fp32 accumulators; one lane issues tcgen05.mma
 //               (M 128, N 256, K 16, four per stage) and tcgen05.commit, which releases the stage to the
 //               producer, and after the last k-block of a tile marks the accumulator complete;
-//   warps 2-5   epilogue of tile j while the MMA warp already fills the other accumulator with tile j+1:
+//   warps 2-9   epilogue of tile j while the MMA warp already fills the other accumulator with tile j+1; two warps
+//               per TMEM lane quarter, one per half of the tile's columns (with four warps the drain of a tile took
+//               longer than its MMAs whenever K was short):
 //               tcgen05.ld (row = TMEM lane, 32 columns at a time), bias / activation, staging through
-//               shared memory so that global rows are written as contiguous 128-byte segments:
+//               shared memory (XOR-swizzled 16-byte columns) so that global rows are written as contiguous segments:
 //               bf16 (+bias, optionally erf-GELU) | fp32 residual add | fp32 | silu(gate)*up in bf16.
 // Rows past M and columns past N are zero-filled by TMA on load and masked on store.
 // Every mbarrier wait is bounded; a wait that gives up raises *error, all roles leave their loops, the
@@ -45,9 +47,10 @@ namespace tc {
 
 constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4, UMMA_K = 16;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;
+constexpr int kEpiWarps = 8;
 constexpr int TMEM_COLS = 512;                             // two accumulators of BN columns
-constexpr int STAGING_BYTES = 4 * 32 * 36 * 4;             // per epilogue warp: 32 rows x (32 + 4) floats
+constexpr int STAGING_BYTES = kEpiWarps * 32 * 32 * 4;     // per epilogue warp: 32 rows x 32 floats, 16-byte columns swizzled
 constexpr int kWaitLimit = 1 << 20;                        // try_wait polls before giving up
 constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + STAGING_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 
@@ -148,7 +151,7 @@ __global__ void __launch_bounds__(tc::kThreads) gemm_tc_kernel(const __grid_cons
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
-        for (int a = 0; a < 2; ++a) { mbar_init(accf0 + 8 * a, 1); mbar_init(acce0 + 8 * a, 4); }
+        for (int a = 0; a < 2; ++a) { mbar_init(accf0 + 8 * a, 1); mbar_init(acce0 + 8 * a, kEpiWarps); }
         *abort_s = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -216,12 +219,13 @@ __global__ void __launch_bounds__(tc::kThreads) gemm_tc_kernel(const __grid_cons
             }
         }
     } else {
-        // Epilogue warps 2..5: TMEM lane group = warp % 4.  Per 32-column chunk: each lane owns one accumulator row
-        // (tcgen05.ld), applies bias / activation and parks the row in a padded staging tile; then the warp
-        // writes the chunk out four rows per instruction, eight lanes of 16 bytes per row.
-        const int q = warp & 3;
-        constexpr int LD = 36;
-        float* stage = stage_all + (size_t)q * 32 * LD;
+        // Epilogue warps 2..9: TMEM lane group = warp % 4, column half = (warp - 2) / 4.  Per 32-column chunk: each lane
+        // owns one accumulator row (tcgen05.ld), applies bias / activation and parks the row in a staging tile (16-byte
+        // column index XOR row & 7: conflict-free both ways); then the warp writes the chunk out four rows per
+        // instruction, eight lanes of 16 bytes per row.
+        const int q = warp & 3, ch = (warp - 2) >> 2;
+        constexpr int LD = 32;
+        float* stage = stage_all + (size_t)(warp - 2) * 32 * LD;
         int j = 0;
         for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++j) {
             int m0, n0, kb0, kb1, z;
@@ -238,8 +242,8 @@ __global__ void __launch_bounds__(tc::kThreads) gemm_tc_kernel(const __grid_cons
             const size_t split_off = compact ? (size_t)item * (size_t)(BM * BN)
                                              : (p.kb_per_split > 0 ? (size_t)z * (size_t)p.M * (size_t)p.N : 0);
 #pragma unroll 1
-            for (int c0 = 0; c0 < OUT_COLS; c0 += 32) {
-                if (nc0 + c0 >= ldc && c0 > 0) break;                          // whole chunk outside the matrix
+            for (int c0 = ch * (OUT_COLS / 2); c0 < (ch + 1) * (OUT_COLS / 2); c0 += 32) {
+                if (nc0 + c0 >= ldc) break;                                    // whole chunk outside the matrix
                 const int cl = (lane & 7) * 4;
                 // residual epilogue: all eight old values of the chunk are requested up front, before the accumulator is
                 // read and long before the first store (the
@@ -299,7 +303,7 @@ __global__ void __launch_bounds__(tc::kThreads) gemm_tc_kernel(const __grid_cons
                 __syncwarp();                                                  // previous chunk fully written out
 #pragma unroll
                 for (int e = 0; e < 32; e += 4)
-                    *reinterpret_cast<float4*>(stage + lane * LD + e) = make_float4(o[e], o[e + 1], o[e + 2], o[e + 3]);
+                    *reinterpret_cast<float4*>(stage + lane * LD + (((e >> 2) ^ (lane & 7)) << 2)) = make_float4(o[e], o[e + 1], o[e + 2], o[e + 3]);
                 __syncwarp();
 #pragma unroll
                 for (int r0 = 0; r0 < 32; r0 += 4) {
@@ -307,7 +311,7 @@ __global__ void __launch_bounds__(tc::kThreads) gemm_tc_kernel(const __grid_cons
                     const int m = m0 + q * 32 + r;
                     const int n = nc0 + c0 + cl;
                     if (m >= p.M || n >= ldc) continue;
-                    const float4 v = *reinterpret_cast<const float4*>(stage + r * LD + cl);
+                    const float4 v = *reinterpret_cast<const float4*>(stage + r * LD + ((((cl >> 2) ^ (r & 7))) << 2));
                     size_t off = (size_t)m * ldc + n;
                     if constexpr (EPI == GemmEpi::F32) {
                         if (compact) off = (size_t)(m - m0) * BN + (size_t)(n - n0);      // slot-local (item = z * n_tiles + t)

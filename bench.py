@@ -341,34 +341,6 @@ def run_tp(args, rank, world, local_rank):
     embeds = torch.zeros(vlm["n_img"], cfg.hidden, dtype=torch.bfloat16, device="cuda")
     be.synchronize()
 
-    # public-API engine for the end-to-end leg: every rank builds edge_fm.EdgeFM from the same JSON
-    engine, tmp = None, None
-    if want_e2e:
-        import edge_fm
-        box = [scratch_dir(rank, 16) if rank == 0 else None]
-        dist.broadcast_object_list(box, src=0)
-        tmp = box[0]
-        model_dir = os.path.join(tmp, "model")
-        if rank == 0:
-            synth.write_checkpoint(model_dir, cfg, host_w)
-            eng_path = synth.write_engine_config(os.path.join(tmp, "engine.json"), model_dir, model_name="Qwen2.5-VL", prefix_ids=[],
-                                                 max_tokens=max_tokens, max_new_tokens=gen_tokens, temperature=temp, top_p=top_p,
-                                                 seed=0, use_cuda_graph=True, device_id=local_rank)
-            ej = json.load(open(eng_path))
-            ej["runtime"]["prefill_attention"] = args.prefill_attention
-            if world > 1:
-                ej["runtime"]["tensor_parallel"] = world
-                ej["runtime"]["tp_rendezvous"] = os.path.join(tmp, "meet")
-            json.dump(ej, open(eng_path, "w"))
-        dist.barrier()
-        os.environ["EFM_TP_RANK"] = str(rank)
-        os.environ["LOCAL_RANK"] = str(local_rank)
-        engine = edge_fm.EdgeFM(os.path.join(tmp, "engine.json"))
-        dist.barrier()
-        if rank == 0:
-            os.remove(os.path.join(model_dir, "model.safetensors"))
-    if not want_cpu:
-        host_w = None
     setup_s = time.perf_counter() - t_setup
     mp = [vlm["last"] + 1] * 3
 
@@ -386,9 +358,10 @@ def run_tp(args, rank, world, local_rank):
 
     pt = torch.tensor(pos, dtype=torch.int32)
 
-    def e2e_request():       # host pixels -> vision encoder (C ABI) -> embeddings stay on the device -> public generate()
-        enc.encode(pixels_host, vlm["grids"], embeds)
-        be.synchronize()
+    def e2e_request(engine, enc2, eb):       # host pixels -> vision encoder (C ABI) -> embeddings stay on the device -> public generate()
+        import edge_fm
+        enc2.encode(pixels_host, vlm["grids"], embeds)
+        eb.synchronize()
         req = edge_fm.Request(0, ids, edge_fm.Tensor(embeds.data_ptr(), [vlm["n_img"], cfg.hidden], edge_fm.DType.BFloat16,
                                                      edge_fm.Device.GPU, local_rank),
                               vlm["embed_id"], edge_fm.Tensor(pt.data_ptr(), [3, len(ids)], edge_fm.DType.Int32, edge_fm.Device.CPU),
@@ -412,24 +385,11 @@ def run_tp(args, rank, world, local_rank):
     dist.barrier()
     torch.cuda.synchronize()
     launches = be.launch_count() - launches0
-    wall_s, e2e_tokens, m = None, None, {}
-    if engine is not None:
-        for _ in range(max(1, min(2, args.warmup))):
-            e2e_tokens = e2e_request()
-        dist.barrier()
-        torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        for _ in range(args.steps):
-            e2e_tokens = e2e_request()
-        dist.barrier()
-        torch.cuda.synchronize()
-        wall_s = time.perf_counter() - t0
-        m = engine.last_generate_metrics()
     clocks = sampler.stop()
     torch.cuda.set_device(local_rank)
-    local = torch.tensor([dec_ms, pre_ms, wall_s or 0.0, vit_ms], dtype=torch.float64, device=torch.device("cuda", local_rank))
+    local = torch.tensor([dec_ms, pre_ms, vit_ms], dtype=torch.float64, device=torch.device("cuda", local_rank))
     dist.all_reduce(local, op=dist.ReduceOp.MAX)
-    dec_ms, pre_ms, wall_max, vit_ms = [float(x) for x in local.tolist()]
+    dec_ms, pre_ms, vit_ms = [float(x) for x in local.tolist()]
     dec_steps = args.steps * (gen_tokens - 1)
     step_ms = dec_ms / dec_steps
     step_bytes = be.decode_step_bytes(len(ids) + gen_tokens // 2)          # this rank's share
@@ -476,28 +436,95 @@ def run_tp(args, rank, world, local_rank):
                              "bytes_per_launch": step_bytes, "us_per_launch": step_ms * 1e3,
                              "frac_of_nominal_8tbs": achieved / 8000.0},
                 "tokens_head": tokens[:8]}
-        if wall_s is not None:
-            line["wall_s"] = wall_max
-            line["e2e"] = {"value": args.steps * gen_tokens / wall_max, "unit": UNIT,
-                           "h2d_bytes_per_step": 16 * len(ids) + pixels.numel() * 2, "d2h_bytes_per_step": 4 * gen_tokens + 32,
-                           "api": "efm_b200_vit_encode (host pixels) -> edge_fm.EdgeFM.generate (host ids in / out)" +
-                                  ("" if world == 1 else f", runtime.tensor_parallel = {world}"),
-                           "engine_decode_tok_s": m.get("decode_tokens_per_second"), "engine_prefill_ms": m.get("prefill_ms")}
-            line["e2e_tokens_equal"] = e2e_tokens == tokens
         if breakdown is not None:
             line["roofline"]["kernel_us_unoverlapped"] = breakdown
     enc.close()
     be.close()
-    engine = None
+    del be, enc
+    torch.cuda.empty_cache()
     dist.barrier()
-    if rank == 0 and tmp is not None:
-        shutil.rmtree(tmp, ignore_errors=True)
+
+    # ---- end to end through the public API: every rank builds edge_fm.EdgeFM from the same JSON; the vision encoder is
+    #      created on the ENGINE's device backend (EdgeFM.backend_handle), so one context, one stream and one
+    #      tensor-parallel communicator serve the whole request
+    if want_e2e:
+        import edge_fm
+        box = [scratch_dir(rank, 16) if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        tmp = box[0]
+        model_dir = os.path.join(tmp, "model")
+        if rank == 0:
+            synth.write_checkpoint(model_dir, cfg, host_w)
+            eng_path = synth.write_engine_config(os.path.join(tmp, "engine.json"), model_dir, model_name="Qwen2.5-VL", prefix_ids=[],
+                                                 max_tokens=max_tokens, max_new_tokens=gen_tokens, temperature=temp, top_p=top_p,
+                                                 seed=0, use_cuda_graph=True, device_id=local_rank)
+            ej = json.load(open(eng_path))
+            ej["runtime"]["prefill_attention"] = args.prefill_attention
+            if world > 1:
+                ej["runtime"]["tensor_parallel"] = world
+                ej["runtime"]["tp_rendezvous"] = os.path.join(tmp, "meet")
+            json.dump(ej, open(eng_path, "w"))
+        dist.barrier()
+        os.environ["EFM_TP_RANK"] = str(rank)
+        os.environ["LOCAL_RANK"] = str(local_rank)
+        engine = edge_fm.EdgeFM(os.path.join(tmp, "engine.json"))
+        dist.barrier()
+        if rank == 0:
+            shutil.rmtree(tmp, ignore_errors=True)
+        eb = EngineBackend(engine)
+        enc2 = cabi.VitEncoder(eb, vlm["vcfg"], max_patches=n_patches)
+        enc2.load_weights(qwen_vit.make_weights(vlm["vcfg"], seed=0, device="cuda"))
+        eb.synchronize()
+        e2e_tokens = None
+        for _ in range(max(2, min(3, args.warmup))):          # first request eager, second captures the prefill graph
+            e2e_tokens = e2e_request(engine, enc2, eb)
+        dist.barrier()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            e2e_tokens = e2e_request(engine, enc2, eb)
+        dist.barrier()
+        torch.cuda.synchronize()
+        wall = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device=torch.device("cuda", local_rank))
+        dist.all_reduce(wall, op=dist.ReduceOp.MAX)
+        wall_max = float(wall.item())
+        m = engine.last_generate_metrics()
+        if rank == 0:
+            line["wall_s"] = wall_max
+            line["e2e"] = {"value": args.steps * gen_tokens / wall_max, "unit": UNIT,
+                           "h2d_bytes_per_step": 16 * len(ids) + pixels.numel() * 2, "d2h_bytes_per_step": 4 * gen_tokens + 32,
+                           "api": "efm_b200_vit_encode on the engine's backend (host pixels) -> edge_fm.EdgeFM.generate (host ids in / out)" +
+                                  ("" if world == 1 else f", runtime.tensor_parallel = {world}"),
+                           "engine_decode_tok_s": m.get("decode_tokens_per_second"), "engine_prefill_ms": m.get("prefill_ms"),
+                           "engine_metrics": {k: round(float(v), 3) for k, v in m.items()}}
+            line["e2e_tokens_equal"] = e2e_tokens == tokens
+        enc2.close()
+        engine = None
+        dist.barrier()
     if world > 1:
         dist.destroy_process_group()
     if rank == 0 and want_cpu:
         torch.cuda.empty_cache()
         line["cpu_baseline"] = cpu_baseline(args.config, host_w)
     return line
+
+
+class EngineBackend:
+    """The device backend of an edge_fm.EdgeFM engine seen through the C ABI (for the vision encoder that feeds it)."""
+
+    def __init__(self, engine):
+        import cabi
+        self.L = cabi.lib()
+        self.ctx = cabi.P(engine.backend_handle())
+        if not self.ctx:
+            raise RuntimeError("the engine has no device backend handle")
+
+    def check(self, st, what=""):
+        if st != 0:
+            raise RuntimeError(f"{what} failed ({st}): {self.L.efm_b200_last_error(self.ctx).decode()}")
+
+    def synchronize(self):
+        self.check(self.L.efm_b200_synchronize(self.ctx), "synchronize")
 
 
 def run_text(args, cfg_id, rank, world, local_rank, *, steps, warmup, want_cpu, dist=None, int4=False):
@@ -702,7 +729,8 @@ def run_text(args, cfg_id, rank, world, local_rank, *, steps, warmup, want_cpu, 
             line["e2e"] = {"value": world * steps * gen_tokens / e2e_max, "unit": UNIT,
                            "h2d_bytes_per_step": 4 * prompt_n + (12 * len(ids) + pixels.numel() * 2 if vlm is not None else 0),
                            "d2h_bytes_per_step": 4 * gen_tokens + 32, "api": "edge_fm.EdgeFM.generate",
-                           "engine_decode_tok_s": m.get("decode_tokens_per_second"), "engine_prefill_ms": m.get("prefill_ms")}
+                           "engine_decode_tok_s": m.get("decode_tokens_per_second"), "engine_prefill_ms": m.get("prefill_ms"),
+                           "engine_metrics": {k: round(float(v), 3) for k, v in m.items()}}
             line["e2e_tokens_equal"] = e2e_tokens == tokens
         if vlm is not None:
             line["vit_ms"] = vit_ms_max / steps

@@ -39,6 +39,11 @@ public:
     // Accepted for compatibility; there is no operator table to tune in this backend.
     void tune();
 
+    // The device backend of a token-generation engine as an `efm_b200_ctx*` of include/efm_b200.h (nullptr for other
+    // tasks): lets a caller put companions of the model -- the vision encoder, efm_b200_vit_create -- on the engine's own
+    // device, stream and tensor-parallel communicator instead of a second context.  Not part of the reference's API.
+    void* backend_handle() const;
+
 private:
     struct Impl;
     std::unique_ptr<Impl> impl_;

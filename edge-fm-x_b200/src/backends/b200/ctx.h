@@ -106,7 +106,8 @@ struct efm_b200_ctx {
     // prefill exchange (reduce-scatter + all-gather over peer stores): exchange count at byte 96, ticket at 100,
     // scatter flags [2][8] at 128, gather flags [2][8] at 192; receive slots [2][tp][tp_slot_floats] fp32 at
     // tp_prefill_off (one slot = the rows one rank owns: ceil(max_s / tp) x H), gather buffers [2][max_s x H] at tp_gather_off
-    size_t tp_prefill_off = 0, tp_gather_off = 0, tp_slot_floats = 0;
+    // greedy sampling exchange: count at byte 104, receive words [2][tp] of {fp32 maximum, count << 18 | id} at tp_sample_off
+    size_t tp_prefill_off = 0, tp_gather_off = 0, tp_slot_floats = 0, tp_sample_off = 0;
     double tp_timeout_s = 300.0;          // host-side limit of a synchronising call on a tensor-parallel context
     unsigned long long peer_wait_ns = 0;  // total wait budget of one kernel on its peers (0 = built-in default)
     int* error_host = nullptr;            // mapped host mirror of DecodeState.error, written by a kernel that gave up a

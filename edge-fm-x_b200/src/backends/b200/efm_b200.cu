@@ -203,7 +203,8 @@ efm_status efm_b200_create(const efm_model_desc* desc, int32_t device_id, int32_
         c->tp_prefill_off = 256 + (((size_t)2 * tp_size * H * 8 + 255) & ~(size_t)255);
         c->tp_slot_floats = ((S + tp_size - 1) / tp_size) * H;
         c->tp_gather_off = c->tp_prefill_off + (((size_t)2 * tp_size * c->tp_slot_floats * sizeof(float) + 255) & ~(size_t)255);
-        EFM_TRY(dev_alloc(c, &c->tp_xchg, c->tp_gather_off + (size_t)2 * S * H * sizeof(float)));
+        c->tp_sample_off = c->tp_gather_off + (((size_t)2 * S * H * sizeof(float) + 255) & ~(size_t)255);
+        EFM_TRY(dev_alloc(c, &c->tp_xchg, c->tp_sample_off + 256));
         EFM_TRY(cudaHostAlloc(reinterpret_cast<void**>(&c->error_host), sizeof(int), cudaHostAllocMapped));
         *c->error_host = 0;
         if (const char* ms = std::getenv("EFM_B200_PEER_WAIT_MS")) {
@@ -903,6 +904,12 @@ efm_status efm_b200_read_logits(efm_b200_ctx* c, float* host_out, int32_t n) {
     if (c == nullptr || host_out == nullptr) return fail(c, EFM_ERR_INVALID_ARGUMENT, "null argument");
     if (n < 0 || n > c->d.vocab) return fail(c, EFM_ERR_INVALID_ARGUMENT, "n exceeds vocab");
     EFM_CK(c, cudaSetDevice(c->device));
+    if (tp_greedy_exchange(*c)) {       // the step exchanged maxima only: gather the ranks' logits rows now (a collective)
+        Launcher L = make_launcher(c);
+        L.counter = nullptr;
+        tp_gather_logits(*c, L);
+        if (L.err != cudaSuccess) return cuda_fail(c, L.err, "gathering the logits of the tensor-parallel ranks");
+    }
     EFM_CK(c, cudaMemcpyAsync(host_out, c->logits, (size_t)n * 4, cudaMemcpyDeviceToHost, c->stream));
     return ctx_sync(c);
 }

@@ -60,4 +60,6 @@ std::unordered_map<std::string, double> EdgeFM::last_stage_metrics() const {
 
 void EdgeFM::tune() {}
 
+void* EdgeFM::backend_handle() const { return impl_->engine ? impl_->engine->backend_handle() : nullptr; }
+
 }  // namespace edge_fm

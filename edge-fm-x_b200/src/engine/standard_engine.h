@@ -40,6 +40,7 @@ public:
     // in the engine's own slot between calls.
     TensorMap run_stage(int32_t request_id, const std::string& stage_name, const TensorRefMap& inputs);
     std::unordered_map<std::string, double> last_stage_metrics() const { return stage_metrics_; }
+    void* backend_handle() const { return ctx_; }
 
 private:
     void load_weights();

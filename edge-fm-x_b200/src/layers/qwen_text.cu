@@ -47,6 +47,7 @@ static void launch_decode_gemv(efm_b200_ctx& c, Launcher& L, const GemvParams& p
 static void tp_all_reduce(efm_b200_ctx& c, Launcher& L, const float* send, float* recv, size_t count);
 static void tp_all_gather(efm_b200_ctx& c, Launcher& L, const float* send, float* recv, size_t count);
 static void launch_sample_only(efm_b200_ctx& c, Launcher& L, int n_part, int advance);
+bool tp_greedy_exchange(const efm_b200_ctx& c);
 
 // Widest cluster the sampler can run with on this device: 16, 8, ... or 1 (single block; also with
 // EFM_B200_SAMPLER_CLUSTER=1).  Found once, outside any stream capture.
@@ -101,8 +102,14 @@ void launch_lm_head_and_sample(efm_b200_ctx& c, Launcher& L, const float* resid_
     else launch_gemv<Epi::Logits>(L, p, c.num_sms);
     if (c.tp_size > 1) {
         const bool pdl = L.pdl;
-        tp_all_gather(c, L, c.logits_l, c.logits, (size_t)c.vocab_l);
-        launch_sample_only(c, L, /*n_part=*/0, advance);
+        if (tp_greedy_exchange(c)) {
+            // greedy: the ranks exchange their (maximum, id) as one word each inside the sampler; no collective, no
+            // gathered logits (efm_b200_read_logits gathers on demand)
+            launch_sample_only(c, L, /*n_part=*/c.num_sms, advance);
+        } else {
+            tp_all_gather(c, L, c.logits_l, c.logits, (size_t)c.vocab_l);
+            launch_sample_only(c, L, /*n_part=*/0, advance);
+        }
         L.pdl = pdl;
         return;
     }
@@ -125,6 +132,11 @@ void launch_lm_head_and_sample(efm_b200_ctx& c, Launcher& L, const float* resid_
     launch_sample(L, s);
 }
 
+// Tensor parallel with imported peer buffers and greedy sampling: the sampler exchanges the ranks' maxima itself.
+bool tp_greedy_exchange(const efm_b200_ctx& c) {
+    return c.tp_size > 1 && c.peers_ready && c.sampling.temperature < 1e-6f;
+}
+
 static void launch_sample_only(efm_b200_ctx& c, Launcher& L, int n_part, int advance) {
     const efm_model_desc& d = c.d;
     SampleParams s{};
@@ -133,6 +145,16 @@ static void launch_sample_only(efm_b200_ctx& c, Launcher& L, int n_part, int adv
     s.part_val = c.part_val;
     s.part_idx = c.part_idx;
     s.n_part = n_part;
+    if (n_part > 0 && tp_greedy_exchange(c)) {
+        s.tp_n = c.tp_size;
+        s.tp_rank = c.tp_rank;
+        s.tp_vocab_offset = c.vocab_off;
+        s.tp_count = reinterpret_cast<unsigned int*>(c.tp_xchg + 104);
+        for (int r = 0; r < c.tp_size; ++r) s.tp_peer_slot[r] = reinterpret_cast<unsigned long long*>(c.peer_base[r] + c.tp_sample_off);
+        s.tp_error = &c.state->error;
+        s.tp_error_host = c.error_host;
+        s.tp_wait_ns = c.peer_wait_ns;
+    }
     s.temperature = c.sampling.temperature;
     s.top_p = c.sampling.top_p;
     s.seed = c.sampling.seed;
@@ -160,6 +182,8 @@ static void tp_all_gather(efm_b200_ctx& c, Launcher& L, const float* send, float
         L.err = cudaErrorUnknown;
     else if (L.counter != nullptr) ++*L.counter;
 }
+
+void tp_gather_logits(efm_b200_ctx& c, Launcher& L) { tp_all_gather(c, L, c.logits_l, c.logits, (size_t)c.vocab_l); }
 
 // Exchange buffer layout (ctx.h): count at byte 64, ticket at 68, receive buffer [2][tp][H] of {fp32, count} at 256.
 static void peers_producer(const efm_b200_ctx& c, GemvParams& p, int parity) {

@@ -17,6 +17,10 @@ void qwen_prefill_chunk(efm_b200_ctx& c, KvSlot& slot, int S, int kv_offset, int
                         bool sample_last, Launcher& L);
 // Final norm + lm_head + sampler on one residual row.
 void launch_lm_head_and_sample(efm_b200_ctx& c, Launcher& L, const float* resid_row, int advance, bool decode_pass = false);
+// Tensor parallel + imported peer buffers + greedy sampling: the sampler exchanges the ranks' maxima itself and the full
+// logits vector is not gathered (tp_gather_logits does that on demand).
+bool tp_greedy_exchange(const efm_b200_ctx& c);
+void tp_gather_logits(efm_b200_ctx& c, Launcher& L);
 // Single operators (used by the per-operator C entry points).
 void launch_gemm_bf16(Launcher& L, const GemmParams& p);
 // C = A . B^T on the tensor cores with the named epilogue; error_word (device int, may be null) is

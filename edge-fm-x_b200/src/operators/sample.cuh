@@ -42,7 +42,25 @@ struct SampleParams {
     int advance;             // 1: move kv_len / positions / step on to the next decode step
     uint32_t* wbuf;          // [vocab] scratch: integer weights
     unsigned long long* xchg;  // [1040] scratch of the multi-block form: segment masses [512] | masses before the pick [512] | pick
+    // Tensor parallel, greedy only (tp_n > 1): part_val / part_idx are this rank's maxima with row indices local to its
+    // vocabulary shard; the ranks exchange one 8-byte word {fp32 maximum, exchange count << 18 | global id} each through
+    // peer memory instead of gathering the logits.
+    int tp_n, tp_rank, tp_vocab_offset;
+    unsigned int* tp_count;                  // exchanges this context has completed (device word, advanced here)
+    unsigned long long* tp_peer_slot[8];     // rank r's receive words [2][tp_n] (ours included)
+    int* tp_error;                           // DecodeState.error and its host-mapped copy, raised when a wait runs out
+    volatile int* tp_error_host;
+    unsigned long long tp_wait_ns;
 };
+
+__device__ __forceinline__ void st_sys_b64(unsigned long long* p, unsigned long long v) {
+    asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_sys_b64(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.sys.global.b64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
 
 // Sampler scratch is one allocation of sample_scratch_words(vocab) 32-bit words: the integer weights,
 // then (16-byte aligned) the exchange area of the multi-block form.
@@ -158,6 +176,53 @@ __global__ void __launch_bounds__(1024) sample_kernel(const SampleParams p) {
         if (lane == 0) { rv[0] = bv; ri[0] = bi; }
     }
     __syncthreads();
+    if (p.tp_n > 1) {
+        // every rank publishes its (maximum, global id) into its word of every rank's receive row and reads the others':
+        // value and count travel in one 64-bit word, two rows alternate (a rank is never two exchanges ahead: the layers'
+        // exchanges lie between two of these).  Waits are limited by time; on expiry the error word is raised.
+        __shared__ unsigned int s_epoch;
+        if (tid == 0) {
+            const unsigned int epoch = *p.tp_count + 1u;
+            s_epoch = epoch;
+            int gid = ri[0] + p.tp_vocab_offset;
+            if (ri[0] < 0 || ri[0] == 0x7fffffff) gid = 0x3ffff;                // nothing found on this rank
+            const unsigned long long word = (unsigned long long)__float_as_uint(rv[0]) |
+                                            ((unsigned long long)(((epoch & 0x3fffu) << 18) | ((unsigned int)gid & 0x3ffffu)) << 32);
+            const int row = (int)(epoch & 1u) * p.tp_n;
+            for (int r = 0; r < p.tp_n; ++r) st_sys_b64(p.tp_peer_slot[r] + row + p.tp_rank, word);
+        }
+        __syncthreads();
+        if (tid < p.tp_n) {
+            const unsigned int epoch = s_epoch;
+            const unsigned long long* src = p.tp_peer_slot[p.tp_rank] + (int)(epoch & 1u) * p.tp_n + tid;
+            PeerWait pw = peer_wait_begin(p.tp_error);
+            unsigned long long w = 0ull;
+            unsigned int spins = 0;
+            bool ok = false;
+            for (;;) {
+                w = ld_sys_b64(src);
+                ok = ((unsigned int)(w >> 50) & 0x3fffu) == (epoch & 0x3fffu);
+                if (ok || pw.dead) break;
+                if ((++spins & 15u) == 0u) {
+                    if (peer_wait_expired(pw, p.tp_error, p.tp_error_host, p.tp_wait_ns)) break;
+                    __nanosleep(32);
+                }
+            }
+            rv[tid] = ok ? __uint_as_float((unsigned int)w) : -INFINITY;
+            ri[tid] = ok ? (int)((unsigned int)(w >> 32) & 0x3ffffu) : 0x7fffffff;
+        }
+        __syncthreads();
+        if (tid == 0) {
+            float v = rv[0];
+            int ix = ri[0];
+            for (int r = 1; r < p.tp_n; ++r)
+                if (rv[r] > v || (rv[r] == v && ri[r] < ix)) { v = rv[r]; ix = ri[r]; }
+            rv[0] = v;
+            ri[0] = ix;
+            *p.tp_count = s_epoch;
+        }
+        __syncthreads();
+    }
     const float M = rv[0];
     int token = ri[0];
     if (token < 0 || token >= p.vocab) token = p.vocab - 1;     // all-NaN / empty guard

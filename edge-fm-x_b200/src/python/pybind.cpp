@@ -198,5 +198,7 @@ PYBIND11_MODULE(edge_fm, m) {
         .def("last_stage_metrics", &EdgeFM::last_stage_metrics)
         .def("last_plan_metrics", &EdgeFM::last_plan_metrics)
         .def("last_generate_metrics", &EdgeFM::last_generate_metrics)
+        .def("backend_handle", [](const EdgeFM& e) { return reinterpret_cast<std::uintptr_t>(e.backend_handle()); },
+             "address of the engine's efm_b200_ctx (0 for engines without one), for C-ABI companions such as the vision encoder")
         .def("tune", &EdgeFM::tune);
 }

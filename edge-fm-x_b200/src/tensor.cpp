@@ -8,6 +8,9 @@
 #include <cstring>
 #include <fstream>
 #include <iomanip>
+#include <mutex>
+#include <unordered_map>
+#include <vector>
 
 namespace edge_fm {
 
@@ -71,6 +74,49 @@ struct DeviceGuard {
 Tensor::Tensor() noexcept = default;
 Tensor::Tensor(Tensor&& other) noexcept = default;
 
+// Device buffers of released OwnCudaMalloc tensors, kept for the next tensor of the same size on the same device: a
+// request's embedding tensor is cloned once per request, and cudaMalloc / cudaFree cost milliseconds (and a device
+// synchronisation) in a process whose memory is mapped into peers.  At most kCacheSlots buffers / kCacheBytes in total.
+namespace {
+struct CachedBuffer { void* ptr; size_t bytes; int32_t device_id; };
+constexpr size_t kCacheSlots = 8, kCacheBytes = (size_t)256 << 20;
+std::mutex g_cache_mutex;
+std::vector<CachedBuffer> g_cache;
+std::unordered_map<void*, size_t> g_sizes;      // sizes of live buffers that came from device_alloc
+
+void* device_alloc(size_t bytes, int32_t device_id) {
+    {
+        std::lock_guard<std::mutex> lock(g_cache_mutex);
+        for (size_t i = 0; i < g_cache.size(); ++i)
+            if (g_cache[i].bytes == bytes && g_cache[i].device_id == device_id) {
+                void* p = g_cache[i].ptr;
+                g_cache.erase(g_cache.begin() + (long)i);
+                g_sizes[p] = bytes;
+                return p;
+            }
+    }
+    void* p = nullptr;
+    cuda_check(cudaMalloc(&p, bytes), "cudaMalloc");
+    std::lock_guard<std::mutex> lock(g_cache_mutex);
+    g_sizes[p] = bytes;
+    return p;
+}
+
+// true: the buffer went into the cache (the caller must not free it)
+bool device_release(void* p, int32_t device_id) {
+    std::lock_guard<std::mutex> lock(g_cache_mutex);
+    auto it = g_sizes.find(p);
+    if (it == g_sizes.end()) return false;
+    const size_t bytes = it->second;
+    g_sizes.erase(it);
+    size_t held = 0;
+    for (const CachedBuffer& b : g_cache) held += b.bytes;
+    if (g_cache.size() >= kCacheSlots || held + bytes > kCacheBytes) return false;
+    g_cache.push_back({p, bytes, device_id});
+    return true;
+}
+}  // namespace
+
 static void free_impl(void* data, Device device, int32_t device_id, MemoryOwnership own, void* stream) {
     if (data == nullptr) return;
     switch (own) {
@@ -78,6 +124,7 @@ static void free_impl(void* data, Device device, int32_t device_id, MemoryOwners
         case MemoryOwnership::OwnCpuMalloc: std::free(data); break;
         case MemoryOwnership::OwnCudaMalloc:
             if (device == Device::GPU) {
+                if (device_release(data, device_id)) break;
                 int prev = -1;
                 if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
                 cudaSetDevice(device_id);
@@ -156,14 +203,17 @@ Tensor Tensor::clone_from(const void* src, const std::vector<int64_t>& shape, DT
         cuda_check(cudaMallocAsync(&dst, bytes, stream), "cudaMallocAsync");
     } else {
         ownership = MemoryOwnership::OwnCudaMalloc;
-        cuda_check(cudaMalloc(&dst, bytes), "cudaMalloc");
+        dst = device_alloc(bytes, dst_device_id);
     }
     cudaError_t e;
     if (src_device == Device::CPU) e = cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, stream);
     else if (src_device_id == dst_device_id) e = cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, stream);
     else e = cudaMemcpyPeerAsync(dst, dst_device_id, src, src_device_id, bytes, stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(stream);     // the source may be released on return
-    if (e != cudaSuccess) { cudaFree(dst); cuda_check(e, "clone_from copy"); }
+    if (e != cudaSuccess) {
+        if (!device_release(dst, dst_device_id)) cudaFree(dst);
+        cuda_check(e, "clone_from copy");
+    }
     return adopt(dst, shape, dtype, Device::GPU, dst_device_id, ownership, stream_handle);
 }
 

@@ -210,7 +210,9 @@ EFM_API efm_status efm_b200_capture_decode(efm_b200_ctx* ctx, int32_t slot);
 /* One D2H copy of response tokens [first, first+n) + stream sync (standard_engine.cpp:1043-1057).
  * Also surfaces device-side status words (EFM_ERR_DEVICE_WAIT). */
 EFM_API efm_status efm_b200_read_tokens(efm_b200_ctx* ctx, int32_t* host_out, int32_t first, int32_t n);
-/* fp32 logits of the most recent forward ([vocab]); synchronises. */
+/* fp32 logits of the most recent forward ([vocab]); synchronises.  On a tensor-parallel context with imported peer
+ * buffers and greedy sampling the ranks exchange only their maxima during a step, so this call gathers the ranks'
+ * logits rows first: it is then a collective, to be made by every rank. */
 EFM_API efm_status efm_b200_read_logits(efm_b200_ctx* ctx, float* host_out, int32_t n);
 EFM_API efm_status efm_b200_synchronize(efm_b200_ctx* ctx);
 

@@ -237,6 +237,13 @@ def test_edge_fm_module_generate(tmp_path, built):
         got = list(eng.generate(rs).token_ids())
         assert got == outs[graph][:outs[graph].index(stop) + 1]
         assert eng.last_generate_metrics()["executed_generated_tokens_total"] == 16
+        # the engine's device backend is reachable for C-ABI companions (vision encoder on the same stream / communicator)
+        handle = eng.backend_handle()
+        assert handle != 0
+        L = cabi.lib()
+        assert L.efm_b200_synchronize(cabi.P(handle)) == 0
+        n_launch = cabi.C.c_int64(0)
+        assert L.efm_b200_launch_count(cabi.P(handle), cabi.C.byref(n_launch)) == 0 and n_launch.value > 0
         # request errors surface as ValueError, like the reference's binding
         with pytest.raises(ValueError, match="prefix"):
             eng.generate(edge_fm.Request(0, [1, 2, 3] + prompt))

@@ -101,6 +101,23 @@ def vlm_request(cfg_id, cfg):
     return synth.vlm_request(cfg_id)
 
 
+def workload_text(cfg_id, gen_tokens=None):
+    """The workload sentence of configurations 0-3, the same in both arms (the reference arm samples its decode steps)."""
+    cfg, prefix, ids, gen, temp, top_p = workload(cfg_id)
+    gen = gen_tokens or gen
+    if cfg.mrope_section is None:
+        return (f"{NAMES[cfg_id]}: {len(prefix)}-token resident prefix + {len(ids) - len(prefix)}-token prompt, "
+                f"{gen} generated tokens, batch 1, temperature {temp}, top_p {top_p}")
+    vlm = vlm_request(cfg_id, cfg)
+    n_patches = sum(t * h * w for t, h, w in vlm["grids"])
+    n_text = len(vlm["ids"]) - vlm["n_img"]
+    if cfg_id == 3:
+        return (f"{NAMES[cfg_id]}: 1288x728 image ({n_patches} patches -> {vlm['n_img']} tokens through the vision encoder) + {n_text} text "
+                f"tokens = {len(vlm['ids'])}-token prompt, {gen} generated tokens, batch 1, temperature {temp}, top_p {top_p}")
+    return (f"{NAMES[cfg_id]}: 448x448 image ({n_patches} patches -> {vlm['n_img']} tokens through the vision encoder) + {n_text} text "
+            f"tokens, {gen} generated tokens, batch 1, temperature {temp}, top_p {top_p}")
+
+
 def vit_flops(vcfg, grids):
     """Algorithmic flops of one encode: 2 m n k per GEMM, 4 D per (query, visible key, head)."""
     from oracle import qwen_vit
@@ -209,8 +226,10 @@ def run_reference(args, rank):
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
             "scaling": "strong" if args.config == 3 else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"{NAMES[args.config]} decode at context {cpu.ctx} (CPU restatement of the reference path; the reference "
-                                   "itself has no CPU implementation of token generation)"},
+            "config": {"workload": workload_text(args.config),
+                       "parallelism": f"{cpu.cores} host threads",
+                       "reference_path": f"CPU restatement of the reference path, decode steps at context {cpu.ctx} (the reference "
+                                         "itself has no CPU implementation of token generation and cannot be built here)"},
             "cpu_baseline": {"value": value, "unit": UNIT, "cores": cpu.cores, "kind": "port", "sample": sample,
                              "prefill_s": cpu.prefill_s},
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
@@ -411,9 +430,7 @@ def run_tp(args, rank, world, local_rank):
         line = {"metric": METRIC, "value": dec_steps / (dec_ms / 1e3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": (vit_ms + pre_ms + dec_ms) / args.steps, "higher_is_better": True,
                 "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-                "config": {"workload": f"{NAMES[args.config]}: 1288x728 image ({n_patches} patches -> {vlm['n_img']} tokens through the vision "
-                                       f"encoder) + {len(ids) - vlm['n_img']} text tokens = {len(ids)}-token prompt, {gen_tokens} generated "
-                                       f"tokens, batch 1, temperature {temp}, top_p {top_p}",
+                "config": {"workload": workload_text(args.config, gen_tokens),
                            "parallelism": "single GPU" if world == 1 else f"tp{world} (heads + MLP columns + vocab rows; decode all-reduce: " +
                                           ("fused into the GEMVs over peer memory" if fused else "NCCL in the decode graph") +
                                           "; prefill: reduce-scatter + all-gather over peer stores; vision windows sharded)",
@@ -649,7 +666,7 @@ def run_text(args, cfg_id, rank, world, local_rank, *, steps, warmup, want_cpu, 
         return list(engine.generate(req).token_ids())
     e2e_s, e2e_tokens, m = None, None, {}
     if engine is not None:
-        for _ in range(max(1, warmup // 2)):
+        for _ in range(max(2, min(3, warmup))):        # first request eager, second captures the prefill graph
             e2e_tokens = e2e_request()
         barrier()
         t1 = time.perf_counter()
@@ -705,8 +722,7 @@ def run_text(args, cfg_id, rank, world, local_rank, *, steps, warmup, want_cpu, 
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
             "ms_per_step": (vit_ms_max + pre_ms_max + dec_ms_max) / steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"{NAMES[cfg_id]}: {len(prefix)}-token resident prefix + {prompt_n}-token prompt, "
-                                   f"{gen_tokens} generated tokens, batch 1, temperature {temp}, top_p {top_p}",
+            "config": {"workload": workload_text(cfg_id, gen_tokens),
                        "parallelism": "single GPU" if world == 1 else f"{world} independent replicas",
                        "l2_policy": "weights streamed per decode step exceed L2 (%.2f GB vs 126 MB)" % (step_bytes / 1e9),
                        "cuda_graph": True},
@@ -735,9 +751,6 @@ def run_text(args, cfg_id, rank, world, local_rank, *, steps, warmup, want_cpu, 
         if vlm is not None:
             line["vit_ms"] = vit_ms_max / steps
             line["vit"] = tensor_report(vit_flops(vlm["vcfg"], vlm["grids"]), vit_ms_max / steps)
-            line["config"]["workload"] = (f"{NAMES[cfg_id]}: 448x448 image ({n_patches} patches -> {vlm['n_img']} tokens through the "
-                                          f"vision encoder) + {prompt_n - vlm['n_img']} text tokens, {gen_tokens} generated tokens, batch 1, "
-                                          f"temperature {temp}, top_p {top_p}")
     if enc is not None:
         enc.close()
     be.close()

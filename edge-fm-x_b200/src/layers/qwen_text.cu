@@ -548,7 +548,11 @@ void launch_gemm_bf16(Launcher& L, const GemmParams& p) { launch_gemm<GemmEpi::B
 void launch_rmsnorm_rows(Launcher& L, const float* x, const __nv_bfloat16* w, __nv_bfloat16* y, int rows, int hidden, float eps) {
     const bool pdl = L.pdl;
     L.pdl = pdl && L.pdl_rows;
-    L.launch(rmsnorm_rows_kernel, dim3(rows), dim3(256), 0, x, w, y, hidden, eps);
+    // many short rows (vision tower, action model): one warp per row; otherwise one block per row
+    if (hidden <= 2048 && (hidden & 3) == 0 && rows >= 256)
+        L.launch(rmsnorm_rows_warp_kernel, dim3((rows + 7) / 8), dim3(256), 0, x, w, y, rows, hidden, eps);
+    else
+        L.launch(rmsnorm_rows_kernel, dim3(rows), dim3(256), 0, x, w, y, hidden, eps);
     L.pdl = pdl;
 }
 
@@ -753,8 +757,7 @@ void qwen_prefill_chunk(efm_b200_ctx& c, KvSlot& slot, int S, int kv_offset, int
              (const __nv_bfloat16*)(n_custom > 0 ? c.custom_embeds : nullptr), c.resid, d.vocab, H, embed_token_id, n_custom);
     for (int l = 0; l < d.num_layers; ++l) {
         const LayerWeights& w = c.layers[l];
-        L.launch(rmsnorm_rows_kernel, dim3(S), dim3(256), 0, (const float*)c.resid,
-                 (const __nv_bfloat16*)w.in_norm, c.norm, H, d.rms_eps);
+        launch_rmsnorm_rows(L, c.resid, w.in_norm, c.norm, S, H, d.rms_eps);
         {
             GemmParams g{c.norm, w.qkv, w.qkv_bias, c.qkv, nullptr, S, QD + 2 * KVD, H};
             launch_gemm<GemmEpi::Bf16Bias>(L, g, &c.state->error);
@@ -775,8 +778,7 @@ void qwen_prefill_chunk(efm_b200_ctx& c, KvSlot& slot, int S, int kv_offset, int
             launch_gemm<GemmEpi::F32>(L, g, &c.state->error);
             tp_prefill_sum(c, L, S, 0);
         }
-        L.launch(rmsnorm_rows_kernel, dim3(S), dim3(256), 0, (const float*)c.resid,
-                 (const __nv_bfloat16*)w.post_norm, c.norm, H, d.rms_eps);
+        launch_rmsnorm_rows(L, c.resid, w.post_norm, c.norm, S, H, d.rms_eps);
         {     // gate|up with silu(gate) * up in the epilogue
             GemmParams g{c.norm, w.gate_up, nullptr, c.act, nullptr, S, 2 * I, H};
             launch_gemm<GemmEpi::SwiGlu>(L, g, &c.state->error);

@@ -72,6 +72,42 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float* __restri
     }
 }
 
+// The same for rows of at most 2048 channels (hidden % 4 == 0): one warp per row, the row stays in registers between the
+// sum of squares and the scaling (one read of x, no block barrier); 8 rows per block.
+__global__ void __launch_bounds__(256) rmsnorm_rows_warp_kernel(const float* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                                                                __nv_bfloat16* __restrict__ y, int rows, int hidden, float eps) {
+    constexpr int MAXV = 16;                                   // float4 per lane: 16 x 32 x 4 = 2048 channels
+    const int row = blockIdx.x * 8 + (int)(threadIdx.x >> 5), lane = threadIdx.x & 31;
+    pdl_launch_dependents();
+    pdl_wait();            // no-ops unless launched with programmatic stream serialization
+    if (row >= rows) return;
+    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)row * hidden);
+    const int nv = hidden >> 2;
+    float4 v[MAXV];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+        const int c = lane + 32 * i;
+        if (c < nv) {
+            v[i] = xr[c];
+            ss = fmaf(v[i].x, v[i].x, ss); ss = fmaf(v[i].y, v[i].y, ss); ss = fmaf(v[i].z, v[i].z, ss); ss = fmaf(v[i].w, v[i].w, ss);
+        }
+    }
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
+    uint2* yr = reinterpret_cast<uint2*>(y + (size_t)row * hidden);
+    const uint2* wr = reinterpret_cast<const uint2*>(w);
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+        const int c = lane + 32 * i;
+        if (c < nv) {
+            const uint2 g = __ldg(wr + c);
+            yr[c] = make_uint2(pack_bf16(v[i].x * inv * bf16lo(g.x), v[i].y * inv * bf16hi(g.x)),
+                               pack_bf16(v[i].z * inv * bf16lo(g.y), v[i].w * inv * bf16hi(g.y)));
+        }
+    }
+}
+
 // Rotate-half RoPE / M-RoPE on the q and k parts of a fused [S, (q+2kv)*D] projection, then
 // scatter: q -> [S, q_heads, D]; rotated k and raw v -> cache rows kv_offset + s.
 // Convention of the reference: angle = pos * theta^(-2d/D); o[d] = x0 cos - x1 sin,

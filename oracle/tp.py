@@ -111,3 +111,20 @@ class TpOracle:
         parts = [torch.empty_like(local) for _ in range(self.tp)]
         dist.all_gather(parts, local)
         return torch.cat(parts)
+
+
+def greedy_by_exchange(local: torch.Tensor, rank: int, tp: int) -> int:
+    """Greedy sampling as the tensor-parallel decode step does it (sample kernel, tensor-parallel branch): every rank
+    reduces its own vocabulary rows to (maximum, lowest local id), the ranks exchange those pairs -- one 8-byte word
+    {fp32 maximum, global id} each on the GPU -- and every rank picks the largest value, the lowest global id on ties:
+    the id a greedy pass over the gathered logits returns (reference tie rule: src/layers/sampler.cu, lowest index)."""
+    v = local.max()
+    i = int((local == v).nonzero()[0])
+    pair = torch.tensor([float(v), float(rank * local.numel() + i)], dtype=torch.float64)
+    if tp == 1:
+        return int(pair[1])
+    pairs = [torch.empty_like(pair) for _ in range(tp)]
+    dist.all_gather(pairs, pair)
+    best = max(float(q[0]) for q in pairs)
+    return int(min(float(q[1]) for q in pairs if float(q[0]) == best))
+

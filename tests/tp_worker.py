@@ -24,11 +24,18 @@ def cpu_rank(rank, world, port, cfg_kw, seed, n_prompt, steps, out_dir):
     o = tp_oracle.TpOracle(cfg, w, rank, world, "exact_fp32")
     logits, toks = [], []
     lg = o.forward(prompt)
+    n_l = cfg.vocab // world
     for s in range(steps):
         logits.append(lg.clone())
         toks.append(qwen_text.greedy(lg))
+        # the exchange of per-rank maxima picks the same id as a greedy pass over the gathered logits
+        assert tp_oracle.greedy_by_exchange(lg[rank * n_l:(rank + 1) * n_l], rank, world) == toks[-1]
         if s + 1 < steps:
             lg = o.forward([toks[-1]])
+    # ties across ranks and inside a rank: the lowest global id wins
+    tie = torch.zeros(cfg.vocab)
+    tie[[n_l - 1, n_l + 3, n_l + 5, cfg.vocab - 1]] = 7.0
+    assert tp_oracle.greedy_by_exchange(tie[rank * n_l:(rank + 1) * n_l], rank, world) == n_l - 1 == qwen_text.greedy(tie)
     torch.save({"tokens": toks, "logits": torch.stack(logits)}, os.path.join(out_dir, f"rank{rank}.pt"))
     dist.barrier()
     dist.destroy_process_group()

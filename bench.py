@@ -449,7 +449,7 @@ def run_tp(args, rank, world, local_rank):
                                                "summary under profiles/) + algorithmic bytes of lm_head, attention and vectors" if traffic else None,
                              "peak_kind": peak_kind,
                              "weights": "int4 group-128 (decode pass), bf16 (prefill)" if int4 else "bf16",
-                             "launch": "one decode step on one rank (CUDA graph: 5 kernels per layer + lm_head + logits gather + sampler)",
+                             "launch": "one decode step on one rank (CUDA graph: 5 kernels per layer + lm_head + sampler; the ranks exchange inside the kernels)",
                              "bytes_per_launch": step_bytes, "us_per_launch": step_ms * 1e3,
                              "frac_of_nominal_8tbs": achieved / 8000.0},
                 "tokens_head": tokens[:8]}

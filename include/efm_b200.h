@@ -144,7 +144,7 @@ EFM_API efm_status efm_b200_set_weight(efm_b200_ctx* ctx, const char* hf_name, c
  * finalize_weights re-packs the tensors into the decode kernel's layout.  The nibble order inside the reference's
  * qweight is produced by a packer that is not part of its tree (TensorRT-Edge-LLM); the plain order above is this
  * library's own, so checkpoints packed for the reference's kernels have to be re-packed.  Other tensor names are
- * ignored; tensor-parallel contexts refuse INT4 weights (EFM_ERR_UNSUPPORTED). */
+ * ignored; tensor-parallel contexts refuse INT4 weights, and in_features must be a multiple of 128 (EFM_ERR_UNSUPPORTED). */
 EFM_API efm_status efm_b200_set_decode_weight(efm_b200_ctx* ctx, const char* hf_name, const void* data,
                                               const int64_t* shape, int32_t ndim, int32_t dtype, int32_t mem_kind);
 /* Checks that every tensor arrived; after this call weights are immutable. */
